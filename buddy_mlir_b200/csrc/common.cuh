@@ -1,0 +1,110 @@
+// Shared helpers for the sm_100a kernels: status handling, launch counting,
+// warp reductions and the packed-row index map.
+#pragma once
+#include <cuda_fp16.h>
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+#include <cstdarg>
+#include <cstdio>
+
+#include "../../include/buddy_b200.h"
+
+namespace b200 {
+
+// Message of the calling thread's last failure.
+char *error_buffer();
+int fail(int code, const char *fmt, ...);
+extern std::atomic<uint64_t> g_launches;
+inline void count_launch(uint64_t n = 1) {
+  g_launches.fetch_add(n, std::memory_order_relaxed);
+}
+int ensure_device();
+
+#define B200_CUDA(expr)                                                        \
+  do {                                                                         \
+    cudaError_t e_ = (expr);                                                   \
+    if (e_ != cudaSuccess)                                                     \
+      return ::b200::fail(B200_ECUDA, "%s: %s (%s:%d)", #expr,                 \
+                          cudaGetErrorString(e_), __FILE__, __LINE__);         \
+  } while (0)
+
+#define B200_LAUNCH_CHECK()                                                    \
+  do {                                                                         \
+    ::b200::count_launch();                                                    \
+    cudaError_t e_ = cudaGetLastError();                                       \
+    if (e_ != cudaSuccess)                                                     \
+      return ::b200::fail(B200_ECUDA, "kernel launch: %s (%s:%d)",             \
+                          cudaGetErrorString(e_), __FILE__, __LINE__);         \
+  } while (0)
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+    v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+// ---- packed-row index map -------------------------------------------------
+// A packed row is a sequence of blocks of up to 32 sixteen-byte units.  Unit
+// (lane) l of a block holds G groups of 4 consecutive k; group j of lane l
+// covers k = blk_k0 + j*(Bs/G) + 4*l .. +3, where Bs is the block's element
+// count.  G = 4 for int8 (4 B per group), 8 for int4 (2 B per group), 1 for
+// f32 (16 B per group).
+__host__ __device__ inline int elems_per_unit(int kind) {
+  return kind == B200_W_I8 ? 16 : (kind == B200_W_U4 ? 32 : 4);
+}
+__host__ __device__ inline int groups_per_unit(int kind) {
+  return kind == B200_W_I8 ? 4 : (kind == B200_W_U4 ? 8 : 1);
+}
+__host__ __device__ inline int64_t packed_k(int kind, int64_t K) {
+  const int e = elems_per_unit(kind);
+  return (K + e - 1) / e * e;
+}
+__host__ __device__ inline int64_t packed_row_bytes(int kind, int64_t K) {
+  return packed_k(kind, K) / elems_per_unit(kind) * 16;
+}
+// Byte offset (and nibble for U4) of element k inside a packed row.
+__host__ __device__ inline int64_t packed_offset(int kind, int64_t K, int64_t k,
+                                                 int *nibble) {
+  const int e = elems_per_unit(kind), G = groups_per_unit(kind);
+  const int64_t Kp = packed_k(kind, K);
+  const int64_t blk_elems = 32 * (int64_t)e;
+  const int64_t b = k / blk_elems;
+  const int64_t k0 = b * blk_elems;
+  const int64_t Bs = (Kp - k0) < blk_elems ? (Kp - k0) : blk_elems;
+  const int64_t q = Bs / G;  // k distance between a lane's groups
+  const int64_t kk = k - k0;
+  const int64_t j = kk / q, r = kk % q;
+  const int64_t l = r / 4, el = r % 4;
+  const int64_t unit_off = b * 512 + l * 16;
+  if (nibble)
+    *nibble = 0;
+  if (kind == B200_W_I8)
+    return unit_off + j * 4 + el;
+  if (kind == B200_W_U4) {
+    if (nibble)
+      *nibble = (int)(el & 1);
+    return unit_off + j * 2 + el / 2;
+  }
+  return unit_off + el * 4; // f32: one group of 4 floats, byte offset
+}
+
+__device__ __forceinline__ float load_as_float(const void *p, int dtype,
+                                               int64_t i) {
+  if (dtype == B200_F32)
+    return ((const float *)p)[i];
+  if (dtype == B200_F16)
+    return __half2float(((const __half *)p)[i]);
+  return __bfloat162float(((const __nv_bfloat16 *)p)[i]);
+}
+
+} // namespace b200

@@ -1,0 +1,936 @@
+// Device-resident decode session: packed weights, KV cache, and one CUDA graph
+// holding every kernel of a decode step.
+//
+// This is the body that stands behind _mlir_ciface_forward_decode: the op
+// sequence is the decode subgraph of
+// examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:46-260 (+ tail); the
+// weight blobs are walked in the order the reference packs them
+// (frontend/Python/graph/graph.py:836-863,
+// frontend/Python/graph/transform/quantization/quantize.py:577-589); tensor
+// parallel sharding follows examples/BuddyTensorParallel (column-parallel
+// q/k/v/gate/up, row-parallel o/down, sum after each, vocab-sharded lm_head;
+// buddy-deepseek-r1-distributed.cpp:521-617) with NCCL in place of MPI.
+#include "common.cuh"
+
+#include <dlfcn.h>
+
+#include <cmath>
+#include <cstring>
+#include <string>
+#include <vector>
+
+namespace b200 {
+
+int gqa_decode_launch(const float *q, const float *kc, const float *vc,
+                      float *out, float *scratch, int q_heads, int kv_heads,
+                      int D, int max_len, int splits, const int32_t *pos,
+                      cudaStream_t st);
+int rope_kv_write_launch(float *q, float *k, const float *v, float *k_cache,
+                         float *v_cache, const float *inv_freq,
+                         const float *q_norm, const float *k_norm, float eps,
+                         int q_heads, int kv_heads, int D, int max_len,
+                         const int32_t *pos, float *k_stage, float *v_stage,
+                         cudaStream_t st);
+
+// ---- NCCL, bound at run time so single-GPU users need no NCCL ---------------
+struct Id128 {  // ncclUniqueId: 128 opaque bytes, passed by value
+  char bytes[128];
+};
+struct Nccl {
+  void *lib = nullptr;
+  void *comm = nullptr;
+  int rank = 0, size = 1;
+  int (*GetUniqueId)(void *) = nullptr;
+  int (*CommInitRank)(void **, int, Id128, int) = nullptr;
+  int (*AllReduce)(const void *, void *, size_t, int, int, void *,
+                   cudaStream_t) = nullptr;
+  int (*AllGather)(const void *, void *, size_t, int, void *,
+                   cudaStream_t) = nullptr;
+  int (*CommDestroy)(void *) = nullptr;
+  const char *(*GetErrorString)(int) = nullptr;
+};
+static Nccl g_nccl;
+constexpr int kNcclFloat = 7;  // ncclFloat32
+constexpr int kNcclSum = 0;    // ncclSum
+
+static int nccl_bind() {
+  if (g_nccl.lib)
+    return B200_OK;
+  void *lib = dlopen("libnccl.so.2", RTLD_NOW | RTLD_GLOBAL);
+  if (!lib)
+    return fail(B200_ESTATE, "cannot load libnccl.so.2: %s", dlerror());
+  g_nccl.lib = lib;
+#define B200_SYM(field, name)                                                  \
+  *(void **)(&g_nccl.field) = dlsym(lib, name);                                \
+  if (!g_nccl.field)                                                           \
+    return fail(B200_ESTATE, "libnccl.so.2 lacks %s", name);
+  B200_SYM(GetUniqueId, "ncclGetUniqueId")
+  B200_SYM(CommInitRank, "ncclCommInitRank")
+  B200_SYM(AllReduce, "ncclAllReduce")
+  B200_SYM(AllGather, "ncclAllGather")
+  B200_SYM(CommDestroy, "ncclCommDestroy")
+  B200_SYM(GetErrorString, "ncclGetErrorString")
+#undef B200_SYM
+  return B200_OK;
+}
+#define B200_NCCL(expr)                                                        \
+  do {                                                                         \
+    int r_ = (expr);                                                           \
+    if (r_ != 0)                                                               \
+      return fail(B200_ECUDA, "%s: %s", #expr, g_nccl.GetErrorString(r_));     \
+  } while (0)
+
+// x += part (after the tensor-parallel sum)
+__global__ void add_inplace_kernel(float *x, const float *part, int n) {
+  const int i = blockIdx.x * blockDim.x + threadIdx.x;
+  if (i < n)
+    x[i] = __fadd_rn(x[i], part[i]);
+}
+// end of a step: feed the argmax back and advance the position
+__global__ void advance_kernel(int32_t *token, int32_t *pos,
+                               const int32_t *next, int32_t *history,
+                               int32_t *count, int cap) {
+  if (threadIdx.x == 0 && blockIdx.x == 0) {
+    const int c = *count;
+    if (c < cap)
+      history[c] = *next;
+    *count = c + 1;
+    *token = *next;
+    *pos = *pos + 1;
+  }
+}
+
+struct DevLinear {
+  b200_weight w{};
+  void *w_buf = nullptr, *scale_buf = nullptr;
+  float *bias_buf = nullptr;
+  bool set = false;
+  int64_t bytes() const {
+    if (!set)
+      return 0;
+    int64_t b = packed_row_bytes(w.kind, w.K) * w.N;
+    if (w.scale) {
+      const int64_t ng =
+          (w.kind == B200_W_U4 && w.group > 0 && w.group < w.K) ? w.K / w.group : 1;
+      b += w.N * ng * (w.scale_dtype == B200_F32 ? 4 : 2);
+    }
+    if (w.bias)
+      b += w.N * 4;
+    return b;
+  }
+  void release() {
+    cudaFree(w_buf);
+    cudaFree(scale_buf);
+    cudaFree(bias_buf);
+    w_buf = scale_buf = nullptr;
+    bias_buf = nullptr;
+    set = false;
+  }
+};
+
+struct Layer {
+  float *in_norm = nullptr, *post_norm = nullptr, *q_norm = nullptr,
+        *k_norm = nullptr;
+  DevLinear q, k, v, o, gate, up, down;
+  DevLinear qkv, gateup;  // fused at finalize
+};
+
+} // namespace b200
+
+using namespace b200;
+
+struct b200_model {
+  b200_model_config cfg{};
+  int tp = 1, rank = 0;
+  int qh = 0, kvh = 0, ffn = 0, vocab = 0;  // local (sharded) sizes
+  float *embed = nullptr, *inv_freq = nullptr, *final_norm = nullptr;
+  std::vector<Layer> layers;
+  DevLinear lm_head;
+  std::vector<float *> kv;
+  float **kv_dev = nullptr;
+  float *x = nullptr, *qkv = nullptr, *attn = nullptr, *mid = nullptr,
+        *part = nullptr, *logits = nullptr, *logits_shard = nullptr;
+  float *attn_scratch = nullptr, *argmax_scratch = nullptr;
+  float *kv_stage = nullptr;  // [2*layers][kv_heads*D]: the rows written this step
+  int32_t *d_state = nullptr;  // token, pos, next, count
+  int32_t *d_history = nullptr;
+  int history_cap = 0;
+  int splits = 1;
+  cudaStream_t stream = nullptr;
+  cudaGraph_t graph = nullptr;
+  cudaGraphExec_t exec = nullptr;
+  cudaEvent_t ev0 = nullptr, ev1 = nullptr;
+  float last_ms = 0.f;
+  int kernels_per_step = 0;
+  bool finalized = false;
+  float *h_logits_pinned = nullptr;
+  int32_t *h_state_pinned = nullptr;
+};
+
+namespace {
+
+int dev_alloc(void **p, size_t bytes) {
+  cudaError_t e = cudaMalloc(p, bytes ? bytes : 16);
+  if (e != cudaSuccess) {
+    (void)cudaGetLastError();
+    return fail(B200_ENOMEM, "cudaMalloc(%zu): %s", bytes, cudaGetErrorString(e));
+  }
+  return B200_OK;
+}
+
+DevLinear *linear_slot(b200_model *m, int layer, int slot) {
+  if (slot == B200_T_LM_HEAD)
+    return &m->lm_head;
+  if (layer < 0 || layer >= (int)m->layers.size())
+    return nullptr;
+  Layer &L = m->layers[layer];
+  switch (slot) {
+  case B200_T_Q: return &L.q;
+  case B200_T_K: return &L.k;
+  case B200_T_V: return &L.v;
+  case B200_T_O: return &L.o;
+  case B200_T_GATE: return &L.gate;
+  case B200_T_UP: return &L.up;
+  case B200_T_DOWN: return &L.down;
+  default: return nullptr;
+  }
+}
+
+bool is_row_parallel(int slot) { return slot == B200_T_O || slot == B200_T_DOWN; }
+
+// Concatenate (interleave = 0) or row-interleave (interleave = 1, two parts)
+// packed linears that share K and kind into one.
+int fuse_linears(const std::vector<DevLinear *> &parts, bool interleave,
+                 DevLinear *out, cudaStream_t st) {
+  const DevLinear &a = *parts[0];
+  int64_t N = 0;
+  bool bias = false;
+  for (auto *p : parts) {
+    if (!p->set || p->w.kind != a.w.kind || p->w.K != a.w.K ||
+        p->w.group != a.w.group || p->w.scale_dtype != a.w.scale_dtype)
+      return fail(B200_EINVAL, "fused projections must share kind, K and scale type");
+    N += p->w.N;
+    bias = bias || p->w.bias;
+  }
+  const int64_t rb = packed_row_bytes(a.w.kind, a.w.K);
+  const bool grouped = a.w.kind == B200_W_U4 && a.w.group > 0 && a.w.group < a.w.K;
+  const int64_t ng = grouped ? a.w.K / a.w.group : 1;
+  const int64_t sb = a.w.scale ? ng * (a.w.scale_dtype == B200_F32 ? 4 : 2) : 0;
+  if (int rc = dev_alloc(&out->w_buf, rb * N)) return rc;
+  if (sb)
+    if (int rc = dev_alloc(&out->scale_buf, sb * N)) return rc;
+  if (bias) {
+    if (int rc = dev_alloc((void **)&out->bias_buf, N * 4)) return rc;
+    B200_CUDA(cudaMemsetAsync(out->bias_buf, 0, N * 4, st));
+  }
+  int64_t row = 0;
+  const size_t np = parts.size();
+  for (size_t i = 0; i < np; ++i) {
+    const DevLinear &p = *parts[i];
+    if (interleave) {
+      B200_CUDA(cudaMemcpy2DAsync((char *)out->w_buf + i * rb, np * rb, p.w_buf,
+                                  rb, rb, p.w.N, cudaMemcpyDeviceToDevice, st));
+      if (sb)
+        B200_CUDA(cudaMemcpy2DAsync((char *)out->scale_buf + i * sb, np * sb,
+                                    p.scale_buf, sb, sb, p.w.N,
+                                    cudaMemcpyDeviceToDevice, st));
+      if (p.w.bias)
+        B200_CUDA(cudaMemcpy2DAsync(out->bias_buf + i, np * 4, p.bias_buf, 4, 4,
+                                    p.w.N, cudaMemcpyDeviceToDevice, st));
+    } else {
+      B200_CUDA(cudaMemcpyAsync((char *)out->w_buf + row * rb, p.w_buf,
+                                rb * p.w.N, cudaMemcpyDeviceToDevice, st));
+      if (sb)
+        B200_CUDA(cudaMemcpyAsync((char *)out->scale_buf + row * sb, p.scale_buf,
+                                  sb * p.w.N, cudaMemcpyDeviceToDevice, st));
+      if (p.w.bias)
+        B200_CUDA(cudaMemcpyAsync(out->bias_buf + row, p.bias_buf, p.w.N * 4,
+                                  cudaMemcpyDeviceToDevice, st));
+      row += p.w.N;
+    }
+  }
+  out->w = a.w;
+  out->w.N = N;
+  out->w.w = out->w_buf;
+  out->w.scale = out->scale_buf;
+  out->w.bias = out->bias_buf;
+  out->set = true;
+  B200_CUDA(cudaStreamSynchronize(st));
+  return B200_OK;
+}
+
+int gemv(b200_model *m, const DevLinear &L, const float *x, float *y,
+         const float *residual, const float *norm_w, bool silu) {
+  b200_gemv_args a{};
+  a.x = x;
+  a.x_dtype = B200_F32;
+  a.y_dtype = B200_F32;
+  a.y = y;
+  a.residual = residual;
+  a.norm_weight = norm_w;
+  a.norm_eps = m->cfg.eps;
+  a.M = 1;
+  a.silu_pairs = silu ? 1 : 0;
+  return b200_gemv(&L.w, &a, m->stream);
+}
+
+// Issue every kernel of one decode step on m->stream.
+int issue_step(b200_model *m, int *n_kernels) {
+  const b200_model_config &c = m->cfg;
+  const int D = c.head_dim, H = c.hidden;
+  const int QD = m->qh * D, KD = m->kvh * D;
+  int32_t *d_token = m->d_state, *d_pos = m->d_state + 1,
+          *d_next = m->d_state + 2, *d_count = m->d_state + 3;
+  cudaStream_t st = m->stream;
+  const uint64_t before = b200_launch_count();
+  if (int rc = b200_embed(m->embed, d_token, m->x, H, st)) return rc;
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer &L = m->layers[l];
+    float *q = m->qkv, *k = m->qkv + QD, *v = m->qkv + QD + KD;
+    if (int rc = gemv(m, L.qkv, m->x, m->qkv, nullptr, L.in_norm, false)) return rc;
+    if (int rc = rope_kv_write_launch(q, k, v, m->kv[2 * l], m->kv[2 * l + 1],
+                                      m->inv_freq, L.q_norm, L.k_norm, c.eps,
+                                      m->qh, m->kvh, D, c.max_len, d_pos,
+                                      m->kv_stage + (size_t)(2 * l) * KD,
+                                      m->kv_stage + (size_t)(2 * l + 1) * KD, st))
+      return rc;
+    if (int rc = gqa_decode_launch(q, m->kv[2 * l], m->kv[2 * l + 1], m->attn,
+                                   m->attn_scratch, m->qh, m->kvh, D, c.max_len,
+                                   m->splits, d_pos, st))
+      return rc;
+    if (m->tp == 1) {
+      if (int rc = gemv(m, L.o, m->attn, m->x, m->x, nullptr, false)) return rc;
+    } else {
+      if (int rc = gemv(m, L.o, m->attn, m->part, nullptr, nullptr, false)) return rc;
+      B200_NCCL(g_nccl.AllReduce(m->part, m->part, H, kNcclFloat, kNcclSum,
+                                 g_nccl.comm, st));
+      add_inplace_kernel<<<(H + 255) / 256, 256, 0, st>>>(m->x, m->part, H);
+      B200_LAUNCH_CHECK();
+    }
+    if (int rc = gemv(m, L.gateup, m->x, m->mid, nullptr, L.post_norm, true)) return rc;
+    if (m->tp == 1) {
+      if (int rc = gemv(m, L.down, m->mid, m->x, m->x, nullptr, false)) return rc;
+    } else {
+      if (int rc = gemv(m, L.down, m->mid, m->part, nullptr, nullptr, false)) return rc;
+      B200_NCCL(g_nccl.AllReduce(m->part, m->part, H, kNcclFloat, kNcclSum,
+                                 g_nccl.comm, st));
+      add_inplace_kernel<<<(H + 255) / 256, 256, 0, st>>>(m->x, m->part, H);
+      B200_LAUNCH_CHECK();
+    }
+  }
+  if (m->tp == 1) {
+    if (int rc = gemv(m, m->lm_head, m->x, m->logits, nullptr, m->final_norm, false))
+      return rc;
+  } else {
+    if (int rc = gemv(m, m->lm_head, m->x, m->logits_shard, nullptr,
+                      m->final_norm, false))
+      return rc;
+    B200_NCCL(g_nccl.AllGather(m->logits_shard, m->logits, m->vocab, kNcclFloat,
+                               g_nccl.comm, st));
+  }
+  if (int rc = b200_argmax_first(m->logits, c.vocab, d_next, m->argmax_scratch, st))
+    return rc;
+  advance_kernel<<<1, 32, 0, st>>>(d_token, d_pos, d_next, m->d_history, d_count,
+                                   m->history_cap);
+  B200_LAUNCH_CHECK();
+  if (n_kernels)
+    *n_kernels = (int)(b200_launch_count() - before);
+  return B200_OK;
+}
+
+int set_state(b200_model *m, int token, int pos) {
+  m->h_state_pinned[0] = token;
+  m->h_state_pinned[1] = pos;
+  m->h_state_pinned[2] = 0;
+  m->h_state_pinned[3] = 0;
+  B200_CUDA(cudaMemcpyAsync(m->d_state, m->h_state_pinned, 4 * sizeof(int32_t),
+                            cudaMemcpyHostToDevice, m->stream));
+  return B200_OK;
+}
+
+} // namespace
+
+extern "C" {
+
+int b200_tp_unique_id(void *id128) {
+  if (!id128)
+    return fail(B200_EINVAL, "tp_unique_id: null");
+  if (int rc = nccl_bind()) return rc;
+  B200_NCCL(g_nccl.GetUniqueId(id128));
+  return B200_OK;
+}
+
+int b200_tp_init(const void *id128, int rank, int size) {
+  if (!id128 || size < 1 || rank < 0 || rank >= size)
+    return fail(B200_EINVAL, "tp_init: bad argument");
+  if (int rc = ensure_device()) return rc;
+  if (int rc = nccl_bind()) return rc;
+  if (g_nccl.comm)
+    return fail(B200_ESTATE, "tp_init: already initialised");
+  Id128 id;
+  memcpy(id.bytes, id128, 128);
+  B200_NCCL(g_nccl.CommInitRank(&g_nccl.comm, size, id, rank));
+  g_nccl.rank = rank;
+  g_nccl.size = size;
+  return B200_OK;
+}
+
+void b200_tp_shutdown(void) {
+  if (g_nccl.comm) {
+    g_nccl.CommDestroy(g_nccl.comm);
+    g_nccl.comm = nullptr;
+  }
+  g_nccl.size = 1;
+  g_nccl.rank = 0;
+}
+
+int b200_model_create(const b200_model_config *cfg, b200_model **out) {
+  if (!cfg || !out)
+    return fail(B200_EINVAL, "model_create: null argument");
+  const b200_model_config &c = *cfg;
+  const int tp = c.tp_size < 1 ? 1 : c.tp_size;
+  if (c.hidden < 1 || c.n_layers < 1 || c.q_heads < 1 || c.kv_heads < 1 ||
+      c.q_heads % c.kv_heads || c.ffn < 1 || c.vocab < 1 || c.max_len < 1 ||
+      (c.head_dim != 64 && c.head_dim != 128))
+    return fail(B200_EINVAL, "model_create: bad architecture");
+  if (c.tp_rank < 0 || c.tp_rank >= tp || c.kv_heads % tp || c.q_heads % tp ||
+      c.ffn % tp || c.vocab % tp)
+    return fail(B200_EINVAL,
+                "model_create: tp_size %d must divide kv_heads, q_heads, ffn and vocab", tp);
+  if (tp > 1 && (!g_nccl.comm || g_nccl.size != tp || g_nccl.rank != c.tp_rank))
+    return fail(B200_ESTATE, "model_create: call b200_tp_init(rank, size) first");
+  if (int rc = ensure_device()) return rc;
+
+  b200_model *m = new b200_model();
+  m->cfg = c;
+  m->cfg.tp_size = tp;
+  m->tp = tp;
+  m->rank = c.tp_rank;
+  m->qh = c.q_heads / tp;
+  m->kvh = c.kv_heads / tp;
+  m->ffn = c.ffn / tp;
+  m->vocab = c.vocab / tp;
+  m->layers.resize(c.n_layers);
+  m->kv.assign(2 * c.n_layers, nullptr);
+  const int D = c.head_dim;
+  m->splits = c.max_len / 64;
+  if (m->splits < 1) m->splits = 1;
+  if (m->splits > 32) m->splits = 32;
+  m->history_cap = 65536;
+
+  int rc = B200_OK;
+  auto A = [&](void **p, size_t bytes) {
+    if (rc == B200_OK) {
+      rc = dev_alloc(p, bytes);
+      if (rc == B200_OK && cudaMemset(*p, 0, bytes ? bytes : 16) != cudaSuccess)
+        rc = fail(B200_ECUDA, "cudaMemset failed");
+    }
+  };
+  const size_t kv_bytes = (size_t)m->kvh * c.max_len * D * sizeof(float);
+  for (auto &p : m->kv) A((void **)&p, kv_bytes);
+  A((void **)&m->kv_dev, m->kv.size() * sizeof(float *));
+  A((void **)&m->x, c.hidden * 4);
+  A((void **)&m->qkv, (size_t)(m->qh + 2 * m->kvh) * D * 4);
+  A((void **)&m->attn, (size_t)m->qh * D * 4);
+  A((void **)&m->mid, (size_t)m->ffn * 4);
+  A((void **)&m->part, c.hidden * 4);
+  A((void **)&m->logits, (size_t)c.vocab * 4);
+  A((void **)&m->logits_shard, (size_t)m->vocab * 4);
+  A((void **)&m->attn_scratch, b200_gqa_scratch_floats(m->qh, D, m->splits) * 4);
+  A((void **)&m->argmax_scratch, 2048 * 4);
+  A((void **)&m->kv_stage, (size_t)2 * c.n_layers * m->kvh * D * 4);
+  A((void **)&m->d_state, 4 * sizeof(int32_t));
+  A((void **)&m->d_history, m->history_cap * sizeof(int32_t));
+  if (rc == B200_OK &&
+      cudaMemcpy(m->kv_dev, m->kv.data(), m->kv.size() * sizeof(float *),
+                 cudaMemcpyHostToDevice) != cudaSuccess)
+    rc = fail(B200_ECUDA, "kv pointer table upload failed");
+  if (rc == B200_OK && cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking) != cudaSuccess)
+    rc = fail(B200_ECUDA, "stream create failed");
+  if (rc == B200_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
+    rc = fail(B200_ECUDA, "event create failed");
+  if (rc == B200_OK && (cudaMallocHost((void **)&m->h_logits_pinned, (size_t)c.vocab * 4) != cudaSuccess ||
+                        cudaMallocHost((void **)&m->h_state_pinned, 16) != cudaSuccess))
+    rc = fail(B200_ENOMEM, "pinned host allocation failed");
+  if (rc != B200_OK) {
+    b200_model_destroy(m);
+    return rc;
+  }
+  *out = m;
+  return B200_OK;
+}
+
+void b200_model_destroy(b200_model *m) {
+  if (!m) return;
+  if (m->stream) cudaStreamSynchronize(m->stream);
+  if (m->exec) cudaGraphExecDestroy(m->exec);
+  if (m->graph) cudaGraphDestroy(m->graph);
+  for (auto &L : m->layers) {
+    cudaFree(L.in_norm); cudaFree(L.post_norm); cudaFree(L.q_norm); cudaFree(L.k_norm);
+    L.q.release(); L.k.release(); L.v.release(); L.o.release();
+    L.gate.release(); L.up.release(); L.down.release();
+    L.qkv.release(); L.gateup.release();
+  }
+  m->lm_head.release();
+  for (auto p : m->kv) cudaFree(p);
+  cudaFree(m->kv_dev); cudaFree(m->embed); cudaFree(m->inv_freq); cudaFree(m->final_norm);
+  cudaFree(m->x); cudaFree(m->qkv); cudaFree(m->attn); cudaFree(m->mid);
+  cudaFree(m->part); cudaFree(m->logits); cudaFree(m->logits_shard);
+  cudaFree(m->attn_scratch); cudaFree(m->argmax_scratch); cudaFree(m->kv_stage);
+  cudaFree(m->d_state); cudaFree(m->d_history);
+  if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
+  if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
+  if (m->ev0) cudaEventDestroy(m->ev0);
+  if (m->ev1) cudaEventDestroy(m->ev1);
+  if (m->stream) cudaStreamDestroy(m->stream);
+  delete m;
+}
+
+int b200_model_set_vector(b200_model *m, int layer, int slot, const float *host,
+                          int64_t n) {
+  if (!m || !host || n < 1)
+    return fail(B200_EINVAL, "set_vector: bad argument");
+  if (m->finalized)
+    return fail(B200_ESTATE, "set_vector: model already finalised");
+  const b200_model_config &c = m->cfg;
+  float **dst = nullptr;
+  int64_t want = 0, off = 0, take = 0;
+  DevLinear *bias_of = nullptr;
+  switch (slot) {
+  case B200_T_EMBED: dst = &m->embed; want = (int64_t)c.vocab * c.hidden; break;
+  case B200_T_INV_FREQ: dst = &m->inv_freq; want = c.head_dim / 2; break;
+  case B200_T_FINAL_NORM: dst = &m->final_norm; want = c.hidden; break;
+  default: break;
+  }
+  if (!dst && layer >= 0 && layer < c.n_layers) {
+    Layer &L = m->layers[layer];
+    switch (slot) {
+    case B200_T_IN_NORM: dst = &L.in_norm; want = c.hidden; break;
+    case B200_T_POST_NORM: dst = &L.post_norm; want = c.hidden; break;
+    case B200_T_Q_NORM: dst = &L.q_norm; want = c.head_dim; break;
+    case B200_T_K_NORM: dst = &L.k_norm; want = c.head_dim; break;
+    case B200_T_Q_BIAS: bias_of = &L.q; want = (int64_t)c.q_heads * c.head_dim; break;
+    case B200_T_K_BIAS: bias_of = &L.k; want = (int64_t)c.kv_heads * c.head_dim; break;
+    case B200_T_V_BIAS: bias_of = &L.v; want = (int64_t)c.kv_heads * c.head_dim; break;
+    default: break;
+    }
+  }
+  if (!dst && !bias_of)
+    return fail(B200_EINVAL, "set_vector: unknown slot %d (layer %d)", slot, layer);
+  if (n != want)
+    return fail(B200_EINVAL, "set_vector: slot %d expects %lld elements, got %lld",
+                slot, (long long)want, (long long)n);
+  take = want;
+  if (bias_of) {  // column-parallel bias: this rank's slice
+    take = want / m->tp;
+    off = take * m->rank;
+    if (!bias_of->set)
+      return fail(B200_ESTATE, "set_vector: set the projection before its bias");
+    dst = &bias_of->bias_buf;
+  }
+  if (*dst) { cudaFree(*dst); *dst = nullptr; }
+  if (int rc = dev_alloc((void **)dst, take * 4)) return rc;
+  B200_CUDA(cudaMemcpy(*dst, host + off, take * 4, cudaMemcpyHostToDevice));
+  if (bias_of)
+    bias_of->w.bias = *dst;
+  return B200_OK;
+}
+
+int b200_model_set_linear(b200_model *m, int layer, int slot, int src_kind,
+                          const void *host_w, const void *host_scale,
+                          int scale_dtype, int src_signed, int64_t K, int64_t N,
+                          int quantize_to, int group) {
+  if (!m || !host_w || K < 1 || N < 1)
+    return fail(B200_EINVAL, "set_linear: bad argument");
+  if (m->finalized)
+    return fail(B200_ESTATE, "set_linear: model already finalised");
+  DevLinear *L = linear_slot(m, layer, slot);
+  if (!L)
+    return fail(B200_EINVAL, "set_linear: unknown slot %d (layer %d)", slot, layer);
+  if (src_kind != B200_W_F32 && quantize_to >= 0)
+    return fail(B200_EINVAL, "set_linear: only f32 sources can be quantised");
+  if (src_kind != B200_W_F32 && !host_scale)
+    return fail(B200_EINVAL, "set_linear: quantised source without scales");
+  const int tp = m->tp, rank = m->rank;
+  const bool rowp = is_row_parallel(slot);
+  if ((rowp && K % tp) || (!rowp && N % tp))
+    return fail(B200_EINVAL, "set_linear: shape not divisible by tp_size");
+  cudaStream_t st = m->stream;
+  L->release();
+
+  const int kind = quantize_to >= 0 ? quantize_to : src_kind;
+  if (kind == B200_W_U4 && (N & 1))
+    return fail(B200_EINVAL, "set_linear: int4 needs an even N");
+  int64_t G = (kind == B200_W_U4 && group > 0 && group < K) ? group : K;
+  if (kind == B200_W_U4 && (K % G || (rowp && (K / tp) % G && G != K)))
+    return fail(B200_EINVAL, "set_linear: group %lld incompatible with K/tp", (long long)G);
+  const int64_t ng = K / G;
+
+  // 1. full tensor in the reference layout on the device
+  const int64_t src_elem_bytes = src_kind == B200_W_F32 ? 4 : 1;
+  const int64_t src_bytes = src_kind == B200_W_U4 ? K * N / 2 : K * N * src_elem_bytes;
+  void *d_src = nullptr, *d_q = nullptr, *d_scale = nullptr, *d_full = nullptr;
+  int rc = dev_alloc(&d_src, src_bytes);
+  auto cleanup = [&]() { cudaFree(d_src); cudaFree(d_q); cudaFree(d_scale); cudaFree(d_full); };
+#define B200_TRY(expr)                                                         \
+  do { if (rc == B200_OK) rc = (expr); } while (0)
+#define B200_TRYCUDA(expr)                                                     \
+  do { if (rc == B200_OK && (expr) != cudaSuccess)                             \
+      rc = fail(B200_ECUDA, "%s failed: %s", #expr, cudaGetErrorString(cudaGetLastError())); } while (0)
+  B200_TRYCUDA(cudaMemcpyAsync(d_src, host_w, src_bytes, cudaMemcpyHostToDevice, st));
+
+  // 2. quantise on the device when asked; scales end up as [ng, N] (ref layout)
+  const void *ref_w = d_src;
+  int sdt = scale_dtype;
+  if (quantize_to == B200_W_I8) {
+    B200_TRY(dev_alloc(&d_q, K * N));
+    B200_TRY(dev_alloc(&d_scale, N * 4));
+    B200_TRY(b200_quantize_per_channel((const float *)d_src, K, N, 8, (int8_t *)d_q,
+                                       (float *)d_scale, st));
+    ref_w = d_q;
+    sdt = B200_F32;
+  } else if (quantize_to == B200_W_U4) {
+    B200_TRY(dev_alloc(&d_q, K * N / 2));
+    B200_TRY(dev_alloc(&d_scale, ng * N * 2));
+    B200_TRY(b200_quantize_w4_group((const float *)d_src, K, N, G, (uint8_t *)d_q,
+                                    (uint16_t *)d_scale, st));
+    ref_w = d_q;
+    sdt = B200_F16;
+    src_signed = 0;
+  } else if (quantize_to >= 0) {
+    rc = fail(B200_EINVAL, "set_linear: cannot quantise to kind %d", quantize_to);
+  } else if (kind != B200_W_F32) {
+    const int64_t sb = ng * N * (sdt == B200_F32 ? 4 : 2);
+    B200_TRY(dev_alloc(&d_scale, sb));
+    B200_TRYCUDA(cudaMemcpyAsync(d_scale, host_scale, sb, cudaMemcpyHostToDevice, st));
+  }
+
+  // 3. pack this rank's shard
+  const int64_t Kl = rowp ? K / tp : K, Nl = rowp ? N : N / tp;
+  const int64_t rb = packed_row_bytes(kind, Kl);
+  const int64_t ssz = sdt == B200_F32 ? 4 : 2;
+  const int64_t ngl = (G == K) ? 1 : Kl / G;
+  B200_TRY(dev_alloc(&L->w_buf, rb * Nl));
+  if (kind != B200_W_F32)
+    B200_TRY(dev_alloc(&L->scale_buf, ngl * Nl * ssz));
+  if (rc == B200_OK) {
+    if (rowp || tp == 1) {
+      // K-slice: rows [rank*Kl, (rank+1)*Kl) of the [K,N] source are contiguous
+      const int64_t row_bytes_src = src_bytes / K;
+      const int64_t ref_row = (ref_w == d_src) ? row_bytes_src
+                                               : (kind == B200_W_U4 ? N / 2 : N);
+      const char *shard = (const char *)ref_w + (rowp ? rank * Kl * ref_row : 0);
+      B200_TRY(b200_pack_weight(kind, shard, Kl, N, src_signed, L->w_buf, st));
+      if (kind != B200_W_F32) {
+        // per-channel scales are shared by every K-shard; group scales split by rows
+        const char *sshard = (const char *)d_scale +
+                             ((rowp && G != K) ? rank * ngl * N * ssz : 0);
+        B200_TRY(b200_pack_scales(sshard, sdt, ngl, N, L->scale_buf, st));
+      }
+    } else {
+      // N-slice: pack the full tensor, keep rows [rank*Nl, (rank+1)*Nl)
+      B200_TRY(dev_alloc(&d_full, rb * N));
+      B200_TRY(b200_pack_weight(kind, ref_w, K, N, src_signed, d_full, st));
+      B200_TRYCUDA(cudaMemcpyAsync(L->w_buf, (char *)d_full + rank * Nl * rb, rb * Nl,
+                                   cudaMemcpyDeviceToDevice, st));
+      if (kind != B200_W_F32) {
+        void *d_sfull = nullptr;
+        B200_TRY(dev_alloc(&d_sfull, ng * N * ssz));
+        B200_TRY(b200_pack_scales(d_scale, sdt, ng, N, d_sfull, st));
+        B200_TRYCUDA(cudaMemcpyAsync(L->scale_buf, (char *)d_sfull + rank * Nl * ng * ssz,
+                                     ng * Nl * ssz, cudaMemcpyDeviceToDevice, st));
+        B200_TRYCUDA(cudaStreamSynchronize(st));
+        cudaFree(d_sfull);
+      }
+    }
+  }
+  B200_TRYCUDA(cudaStreamSynchronize(st));
+#undef B200_TRY
+#undef B200_TRYCUDA
+  cleanup();
+  if (rc != B200_OK) {
+    L->release();
+    return rc;
+  }
+  L->w.kind = kind;
+  L->w.group = (kind == B200_W_U4 && G != K) ? (int)G : 0;
+  L->w.K = Kl;
+  L->w.N = Nl;
+  L->w.w = L->w_buf;
+  L->w.scale = L->scale_buf;
+  L->w.scale_dtype = sdt;
+  L->w.bias = nullptr;
+  L->set = true;
+  return B200_OK;
+}
+
+int b200_blob_elements(const b200_model_config *cfg, const char *variant,
+                       int64_t *n_float, int64_t *n_int) {
+  if (!cfg || !variant)
+    return fail(B200_EINVAL, "blob_elements: null argument");
+  const b200_model_config &c = *cfg;
+  const int64_t H = c.hidden, D = c.head_dim, QD = (int64_t)c.q_heads * D,
+                KD = (int64_t)c.kv_heads * D, F = c.ffn, V = c.vocab;
+  const int64_t qkv = H * QD + 2 * H * KD + (c.qkv_bias ? QD + 2 * KD : 0);
+  const int64_t quant_layer = QD * H + 2 * H * F + F * H;
+  const int64_t small_layer = 2 * H;
+  const int64_t common = V * H + D / 2 + H;  // embedding, inv_freq, final norm
+  int64_t nf = 0, ni = 0;
+  if (!strcmp(variant, "f32")) {
+    nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
+  } else if (!strcmp(variant, "w8a32")) {
+    ni = c.n_layers * quant_layer + H * V;
+    nf = common + c.n_layers * (small_layer + qkv) +
+         c.n_layers * (H + 2 * F + H) + V;  // + one scale per quantised column
+  } else {
+    return fail(B200_EINVAL, "blob_elements: unknown variant '%s'", variant);
+  }
+  if (n_float) *n_float = nf;
+  if (n_int) *n_int = ni;
+  return B200_OK;
+}
+
+int b200_model_load_blobs(b200_model *m, const char *variant,
+                          const void *float_blob, int64_t n_float,
+                          const void *int_blob, int64_t n_int,
+                          int all_linear_w8) {
+  if (!m || !variant || !float_blob)
+    return fail(B200_EINVAL, "load_blobs: null argument");
+  const b200_model_config &c = m->cfg;
+  if (c.qk_norm)
+    return fail(B200_EINVAL, "load_blobs: blob order is defined for Qwen2 models only");
+  int64_t want_f = 0, want_i = 0;
+  if (int rc = b200_blob_elements(&c, variant, &want_f, &want_i)) return rc;
+  const bool w8 = !strcmp(variant, "w8a32");
+  if (n_float != want_f || (w8 && (n_int != want_i || !int_blob)))
+    return fail(B200_EINVAL,
+                "load_blobs(%s): expected %lld float / %lld int8 elements, got %lld / %lld",
+                variant, (long long)want_f, (long long)want_i, (long long)n_float,
+                (long long)n_int);
+  const int64_t H = c.hidden, D = c.head_dim, QD = (int64_t)c.q_heads * D,
+                KD = (int64_t)c.kv_heads * D, F = c.ffn, V = c.vocab;
+  const float *fp = (const float *)float_blob;
+  const int8_t *ip = (const int8_t *)int_blob;
+  const int qf = all_linear_w8 ? B200_W_I8 : -1;  // float linears: keep or quantise
+  auto takef = [&](int64_t n) { const float *p = fp; fp += n; return p; };
+  auto takei = [&](int64_t n) { const int8_t *p = ip; ip += n; return p; };
+  struct Pending { int layer, slot; const int8_t *w; int64_t K, N; };
+  std::vector<Pending> pend;
+  int rc = B200_OK;
+#define B200_DO(expr) do { if (rc == B200_OK) rc = (expr); } while (0)
+  B200_DO(b200_model_set_vector(m, -1, B200_T_EMBED, takef(V * H), V * H));
+  B200_DO(b200_model_set_vector(m, -1, B200_T_INV_FREQ, takef(D / 2), D / 2));
+  auto flinear = [&](int l, int slot, int64_t K, int64_t N) {
+    B200_DO(b200_model_set_linear(m, l, slot, B200_W_F32, takef(K * N), nullptr,
+                                  B200_F32, 0, K, N, qf, 0));
+  };
+  auto qlinear = [&](int l, int slot, int64_t K, int64_t N) {
+    if (w8)
+      pend.push_back({l, slot, takei(K * N), K, N});
+    else
+      flinear(l, slot, K, N);
+  };
+  for (int l = 0; l < c.n_layers && rc == B200_OK; ++l) {
+    B200_DO(b200_model_set_vector(m, l, B200_T_IN_NORM, takef(H), H));
+    const float *bq = c.qkv_bias ? takef(QD) : nullptr;
+    flinear(l, B200_T_Q, H, QD);
+    if (bq) B200_DO(b200_model_set_vector(m, l, B200_T_Q_BIAS, bq, QD));
+    const float *bk = c.qkv_bias ? takef(KD) : nullptr;
+    flinear(l, B200_T_K, H, KD);
+    if (bk) B200_DO(b200_model_set_vector(m, l, B200_T_K_BIAS, bk, KD));
+    const float *bv = c.qkv_bias ? takef(KD) : nullptr;
+    flinear(l, B200_T_V, H, KD);
+    if (bv) B200_DO(b200_model_set_vector(m, l, B200_T_V_BIAS, bv, KD));
+    qlinear(l, B200_T_O, QD, H);
+    B200_DO(b200_model_set_vector(m, l, B200_T_POST_NORM, takef(H), H));
+    qlinear(l, B200_T_GATE, H, F);
+    qlinear(l, B200_T_UP, H, F);
+    qlinear(l, B200_T_DOWN, F, H);
+  }
+  B200_DO(b200_model_set_vector(m, -1, B200_T_FINAL_NORM, takef(H), H));
+  qlinear(-1, B200_T_LM_HEAD, H, V);
+  // quantize.py:577-589: the scaler params follow every original param, in
+  // original-weight order.
+  for (auto &p : pend)
+    B200_DO(b200_model_set_linear(m, p.layer, p.slot, B200_W_I8, p.w, takef(p.N),
+                                  B200_F32, 1, p.K, p.N, -1, 0));
+#undef B200_DO
+  return rc;
+}
+
+int b200_model_finalize(b200_model *m) {
+  if (!m)
+    return fail(B200_EINVAL, "finalize: null model");
+  if (m->finalized)
+    return B200_OK;
+  const b200_model_config &c = m->cfg;
+  if (!m->embed || !m->final_norm || !m->lm_head.set)
+    return fail(B200_ESTATE, "finalize: embedding, final norm or lm_head missing");
+  if (!m->inv_freq) {
+    std::vector<float> f(c.head_dim / 2);
+    for (int j = 0; j < c.head_dim / 2; ++j)
+      f[j] = (float)(1.0 / std::pow((double)c.rope_theta, (2.0 * j) / c.head_dim));
+    if (int rc = b200_model_set_vector(m, -1, B200_T_INV_FREQ, f.data(), f.size()))
+      return rc;
+  }
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer &L = m->layers[l];
+    if (!L.in_norm || !L.post_norm || !L.q.set || !L.k.set || !L.v.set ||
+        !L.o.set || !L.gate.set || !L.up.set || !L.down.set)
+      return fail(B200_ESTATE, "finalize: layer %d is incomplete", l);
+    if (c.qk_norm && (!L.q_norm || !L.k_norm))
+      return fail(B200_ESTATE, "finalize: layer %d lacks q_norm/k_norm", l);
+    if (int rc = fuse_linears({&L.q, &L.k, &L.v}, false, &L.qkv, m->stream)) return rc;
+    if (int rc = fuse_linears({&L.gate, &L.up}, true, &L.gateup, m->stream)) return rc;
+    L.q.release(); L.k.release(); L.v.release(); L.gate.release(); L.up.release();
+  }
+  // Warm every kernel once outside capture (sets shared-memory attributes),
+  // then capture the step.
+  if (int rc = set_state(m, 0, 0)) return rc;
+  if (int rc = issue_step(m, &m->kernels_per_step)) return rc;
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  for (auto p : m->kv)  // the warm-up wrote row 0
+    B200_CUDA(cudaMemsetAsync(p, 0, (size_t)m->kvh * c.max_len * c.head_dim * 4, m->stream));
+  B200_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+  int rc = issue_step(m, nullptr);
+  cudaGraph_t g = nullptr;
+  cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+  if (rc != B200_OK) {
+    if (g) cudaGraphDestroy(g);
+    return rc;
+  }
+  if (e != cudaSuccess)
+    return fail(B200_ECUDA, "graph capture: %s", cudaGetErrorString(e));
+  m->graph = g;
+  B200_CUDA(cudaGraphInstantiate(&m->exec, m->graph, 0));
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  m->finalized = true;
+  return B200_OK;
+}
+
+static int kv_copy(b200_model *m, int buffer, float *host, int pos0, int n_pos,
+                   bool upload) {
+  if (!m || !host || buffer < 0 || buffer >= (int)m->kv.size() || pos0 < 0 ||
+      n_pos < 0 || pos0 + n_pos > m->cfg.max_len)
+    return fail(B200_EINVAL, "kv copy: bad argument");
+  if (n_pos == 0)
+    return B200_OK;
+  const int D = m->cfg.head_dim;
+  const size_t pitch = (size_t)m->cfg.max_len * D * 4, width = (size_t)n_pos * D * 4;
+  // this rank's kv heads out of the host's full [kv_heads, max_len, D]
+  float *h0 = host + ((size_t)m->rank * m->kvh * m->cfg.max_len + pos0) * D;
+  float *d0 = m->kv[buffer] + (size_t)pos0 * D;
+  if (upload)
+    B200_CUDA(cudaMemcpy2DAsync(d0, pitch, h0, pitch, width, m->kvh,
+                                cudaMemcpyHostToDevice, m->stream));
+  else
+    B200_CUDA(cudaMemcpy2DAsync(h0, pitch, d0, pitch, width, m->kvh,
+                                cudaMemcpyDeviceToHost, m->stream));
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  return B200_OK;
+}
+int b200_model_kv_upload(b200_model *m, int buffer, const float *host, int pos0,
+                         int n_pos) {
+  return kv_copy(m, buffer, const_cast<float *>(host), pos0, n_pos, true);
+}
+int b200_model_kv_download(b200_model *m, int buffer, float *host, int pos0,
+                           int n_pos) {
+  return kv_copy(m, buffer, host, pos0, n_pos, false);
+}
+
+int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
+                      int *next_token) {
+  if (!m)
+    return fail(B200_EINVAL, "decode: null model");
+  if (!m->finalized)
+    return fail(B200_ESTATE, "decode: call b200_model_finalize first");
+  if (token < 0 || token >= m->cfg.vocab || pos < 0 || pos >= m->cfg.max_len)
+    return fail(B200_EINVAL, "decode: token %d / position %d out of range", token, pos);
+  if (int rc = set_state(m, token, pos)) return rc;
+  B200_CUDA(cudaEventRecord(m->ev0, m->stream));
+  B200_CUDA(cudaGraphLaunch(m->exec, m->stream));
+  count_launch(m->kernels_per_step);
+  B200_CUDA(cudaEventRecord(m->ev1, m->stream));
+  if (logits_host)
+    B200_CUDA(cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->cfg.vocab * 4,
+                              cudaMemcpyDeviceToHost, m->stream));
+  if (next_token)
+    B200_CUDA(cudaMemcpyAsync(m->h_state_pinned + 2, m->d_state + 2, 4,
+                              cudaMemcpyDeviceToHost, m->stream));
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+  if (logits_host)
+    memcpy(logits_host, m->h_logits_pinned, (size_t)m->cfg.vocab * 4);
+  if (next_token)
+    *next_token = m->h_state_pinned[2];
+  return B200_OK;
+}
+
+int b200_model_generate(b200_model *m, int token, int pos, int steps,
+                        int *tokens_out) {
+  if (!m || !tokens_out)
+    return fail(B200_EINVAL, "generate: null argument");
+  if (!m->finalized)
+    return fail(B200_ESTATE, "generate: call b200_model_finalize first");
+  if (steps < 1 || steps > m->history_cap || token < 0 || token >= m->cfg.vocab ||
+      pos < 0 || pos + steps > m->cfg.max_len)
+    return fail(B200_EINVAL, "generate: %d steps from position %d exceed max_len %d",
+                steps, pos, m->cfg.max_len);
+  if (int rc = set_state(m, token, pos)) return rc;
+  B200_CUDA(cudaEventRecord(m->ev0, m->stream));
+  for (int s = 0; s < steps; ++s)
+    B200_CUDA(cudaGraphLaunch(m->exec, m->stream));
+  count_launch((uint64_t)m->kernels_per_step * steps);
+  B200_CUDA(cudaEventRecord(m->ev1, m->stream));
+  B200_CUDA(cudaMemcpyAsync(tokens_out, m->d_history, (size_t)steps * 4,
+                            cudaMemcpyDeviceToHost, m->stream));
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+  return B200_OK;
+}
+
+int b200_model_read_new_kv_rows(b200_model *m, float *host) {
+  if (!m || !host)
+    return fail(B200_EINVAL, "read_new_kv_rows: null argument");
+  B200_CUDA(cudaMemcpyAsync(host, m->kv_stage,
+                            (size_t)2 * m->cfg.n_layers * m->kvh * m->cfg.head_dim * 4,
+                            cudaMemcpyDeviceToHost, m->stream));
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  return B200_OK;
+}
+
+float b200_model_last_ms(const b200_model *m) { return m ? m->last_ms : 0.f; }
+int b200_model_kernels_per_step(const b200_model *m) { return m ? m->kernels_per_step : 0; }
+float *b200_model_kv_ptr(b200_model *m, int buffer) {
+  return (m && buffer >= 0 && buffer < (int)m->kv.size()) ? m->kv[buffer] : nullptr;
+}
+
+int64_t b200_model_step_bytes(const b200_model *m, int ctx) {
+  if (!m) return 0;
+  const b200_model_config &c = m->cfg;
+  int64_t b = 0;
+  for (const auto &L : m->layers) {
+    b += L.qkv.bytes() + L.o.bytes() + L.gateup.bytes() + L.down.bytes();
+    b += 2 * (int64_t)c.hidden * 4;  // two RMSNorm weights
+    if (L.q_norm) b += 2 * (int64_t)c.head_dim * 4;
+  }
+  b += m->lm_head.bytes() + (int64_t)c.hidden * 4;  // final norm
+  b += (int64_t)c.hidden * 4 + (int64_t)c.head_dim / 2 * 4;  // embedding row, inv_freq
+  // live KV rows read by attention + the row written this step
+  b += (int64_t)c.n_layers * 2 * m->kvh * c.head_dim * 4 * ((int64_t)ctx + 1);
+  return b;
+}
+
+int b200_model_kv_overflow(b200_model *m, int position, int keep, float theta,
+                           int *new_position) {
+  if (!m || !new_position)
+    return fail(B200_EINVAL, "model_kv_overflow: null argument");
+  if (int rc = b200_kv_overflow(m->kv_dev, (int)m->kv.size(), m->kvh, m->cfg.max_len,
+                                m->cfg.head_dim, position, keep, theta, new_position,
+                                m->stream))
+    return rc;
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  return B200_OK;
+}
+
+} // extern "C"

@@ -1,0 +1,426 @@
+// Decode GEMV over the packed device layout, M = 1..16 activation rows.
+//
+// One warp streams R output rows: every lane issues one 16-byte load per row
+// and block (32 lanes x 16 B = 512 contiguous bytes of each row), dequantises
+// in registers, multiplies with the activation groups read from shared
+// memory, and the per-lane partial sums meet in a warp-shuffle tree.  HBM
+// bound: each weight byte is read exactly once.
+//
+// Replaces the loops emitted by buddy-mlir's decode passes
+//   midend/lib/Conversion/MatMulOptimization/DequantMatMulVectorizationDecode.cpp:250-321
+//   midend/lib/Conversion/MatMulOptimization/Int4DequantMatMulVectorizationDecode.cpp:359-430
+//   midend/lib/Conversion/MatMulOptimization/MatMulVectorizationDecode.cpp:94-192
+// and, as fused prologue/epilogue, the RMSNorm, bias, residual and SiLU-gate
+// ops of examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:60-72,75-76,
+// 209,226-231,235.
+#include "common.cuh"
+
+namespace b200 {
+
+struct GemvP {
+  const void *x;
+  const uint8_t *w;
+  const void *scale;
+  const float *bias;
+  const float *residual;
+  const float *norm_w;
+  void *y;
+  int64_t x_ld, y_ld, row_bytes;
+  int K, Kp, N, M;
+  int x_dtype, y_dtype, scale_dtype;
+  int group, ngroups;
+  int accumulate, silu_pairs;
+  int kc;  // activation slab (elements) staged in shared memory at a time
+  float eps;
+};
+
+__device__ __forceinline__ uint4 ld_stream(const void *p) {
+  uint4 v;
+  asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p));
+  return v;
+}
+
+// Byte i of `word` as float(byte) + 2^23: the byte lands in the mantissa of
+// 0x4B000000.  One PRMT; the caller subtracts the bias with one FADD.
+__device__ __forceinline__ float byte_magic(uint32_t word, int i) {
+  return __uint_as_float(__byte_perm(word, 0x4B000000u, 0x7650 + i));
+}
+
+template <int KIND> struct Dequant;
+
+template <> struct Dequant<B200_W_I8> {
+  static constexpr int G = 4;  // groups of 4 k per 16-byte unit
+  // group j of the unit -> 4 floats
+  static __device__ __forceinline__ void group(const uint4 &u, int j,
+                                               float (&w)[4]) {
+    const uint32_t word = (j == 0 ? u.x : j == 1 ? u.y : j == 2 ? u.z : u.w) ^
+                          0x80808080u;  // signed -> offset-128
+    constexpr float C = 8388608.0f + 128.0f;
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      w[e] = byte_magic(word, e) - C;
+  }
+};
+
+template <> struct Dequant<B200_W_U4> {
+  static constexpr int G = 8;
+  static __device__ __forceinline__ void group(const uint4 &u, int j,
+                                               float (&w)[4]) {
+    const uint32_t word32 =
+        (j >> 1) == 0 ? u.x : (j >> 1) == 1 ? u.y : (j >> 1) == 2 ? u.z : u.w;
+    const uint32_t lo = word32 & 0x0F0F0F0Fu;         // elements 0 and 2
+    const uint32_t hi = (word32 >> 4) & 0x0F0F0F0Fu;  // elements 1 and 3
+    const int b = (j & 1) * 2;
+    constexpr float C = 8388608.0f + 8.0f;  // zero-point 8 folded in
+    w[0] = byte_magic(lo, b) - C;
+    w[1] = byte_magic(hi, b) - C;
+    w[2] = byte_magic(lo, b + 1) - C;
+    w[3] = byte_magic(hi, b + 1) - C;
+  }
+};
+
+template <> struct Dequant<B200_W_F32> {
+  static constexpr int G = 1;
+  static __device__ __forceinline__ void group(const uint4 &u, int,
+                                               float (&w)[4]) {
+    w[0] = __uint_as_float(u.x);
+    w[1] = __uint_as_float(u.y);
+    w[2] = __uint_as_float(u.z);
+    w[3] = __uint_as_float(u.w);
+  }
+};
+
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  // subgraph0_decode_simplify.mlir:226-231: (g * sigmoid(g)) * u
+  const float s = 1.0f / (1.0f + expf(-g));
+  return (g * s) * u;
+}
+
+template <int KIND, int MT, int R, bool GROUPED>
+__global__ void __launch_bounds__(256)
+gemv_kernel(const GemvP p) {
+  extern __shared__ __align__(16) float xs[];  // [MT][kc]
+  __shared__ float s_red[8 * 16];
+  __shared__ float s_rinv[16];
+
+  using DQ = Dequant<KIND>;
+  constexpr int E = KIND == B200_W_I8 ? 16 : (KIND == B200_W_U4 ? 32 : 4);
+  constexpr int BLK = 32 * E;  // elements per full block
+
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int nwarps = blockDim.x >> 5;
+  const int64_t row0 = ((int64_t)blockIdx.x * nwarps + warp) * R;
+
+  // ---- optional fused RMSNorm statistics --------------------------------
+  if (p.norm_w != nullptr) {
+    for (int m = 0; m < p.M; ++m) {
+      float s = 0.f;
+      for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+        const float v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
+        s = fmaf(v, v, s);
+      }
+      s = warp_sum(s);
+      if (lane == 0)
+        s_red[warp] = s;
+      __syncthreads();
+      if (threadIdx.x == 0) {
+        float t = 0.f;
+        for (int w = 0; w < nwarps; ++w)
+          t += s_red[w];
+        s_rinv[m] = rsqrtf(t * (1.0f / (float)p.K) + p.eps);
+      }
+      __syncthreads();
+    }
+  }
+
+  float acc[R][MT];
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+      acc[r][m] = 0.f;
+
+  const uint8_t *rowp[R];
+#pragma unroll
+  for (int r = 0; r < R; ++r) {
+    int64_t row = row0 + r;
+    if (row >= p.N)
+      row = p.N - 1;  // clamp: loads stay in bounds, result is discarded
+    rowp[r] = p.w + row * p.row_bytes;
+  }
+
+  for (int k0 = 0; k0 < p.Kp; k0 += p.kc) {
+    const int kc = min(p.kc, p.Kp - k0);
+    if (k0 > 0)
+      __syncthreads();
+    // ---- stage the activation slab (zero beyond K and beyond M) ----------
+    for (int i = threadIdx.x; i < MT * kc; i += blockDim.x) {
+      const int m = i / kc, k = k0 + (i - m * kc);
+      float v = 0.f;
+      if (m < p.M && k < p.K) {
+        v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
+        if (p.norm_w != nullptr)
+          v = p.norm_w[k] * (v * s_rinv[m]);
+      }
+      xs[m * p.kc + (k - k0)] = v;
+    }
+    __syncthreads();
+
+    const int nblk = (kc + BLK - 1) / BLK;
+#pragma unroll 2
+    for (int b = 0; b < nblk; ++b) {
+      const int kb = b * BLK;              // slab-relative element offset
+      const int Bs = min(BLK, kc - kb);    // elements in this block
+      if (lane * E < Bs) {
+        const int q = Bs / DQ::G;
+        const int64_t boff = (int64_t)((k0 + kb) / E) * 16 + lane * 16;
+        uint4 wv[R];
+#pragma unroll
+        for (int r = 0; r < R; ++r)
+          wv[r] = ld_stream(rowp[r] + boff);
+#pragma unroll
+        for (int j = 0; j < DQ::G; ++j) {
+          const int kx = kb + j * q + 4 * lane;
+          float wf[R][4];
+#pragma unroll
+          for (int r = 0; r < R; ++r)
+            DQ::group(wv[r], j, wf[r]);
+          float sc[R];
+          if (GROUPED) {
+            const int g = (k0 + kx) / p.group;
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              int64_t row = row0 + r;
+              if (row >= p.N)
+                row = p.N - 1;
+              sc[r] = load_as_float(p.scale, p.scale_dtype,
+                                    row * p.ngroups + g);
+            }
+          }
+#pragma unroll
+          for (int m = 0; m < MT; ++m) {
+            const float4 xv =
+                *reinterpret_cast<const float4 *>(&xs[m * p.kc + kx]);
+#pragma unroll
+            for (int r = 0; r < R; ++r) {
+              if (GROUPED) {
+                float t = xv.x * wf[r][0];
+                t = fmaf(xv.y, wf[r][1], t);
+                t = fmaf(xv.z, wf[r][2], t);
+                t = fmaf(xv.w, wf[r][3], t);
+                acc[r][m] = fmaf(t, sc[r], acc[r][m]);
+              } else {
+                acc[r][m] = fmaf(xv.x, wf[r][0], acc[r][m]);
+                acc[r][m] = fmaf(xv.y, wf[r][1], acc[r][m]);
+                acc[r][m] = fmaf(xv.z, wf[r][2], acc[r][m]);
+                acc[r][m] = fmaf(xv.w, wf[r][3], acc[r][m]);
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- reduce across lanes, epilogue --------------------------------------
+#pragma unroll
+  for (int r = 0; r < R; ++r)
+#pragma unroll
+    for (int m = 0; m < MT; ++m)
+      acc[r][m] = warp_sum(acc[r][m]);
+
+  if (lane == 0) {
+#pragma unroll
+    for (int r = 0; r < R; ++r) {
+      const int64_t row = row0 + r;
+      if (row >= p.N)
+        continue;
+      float s = 1.f;
+      if (!GROUPED && p.scale != nullptr)
+        s = load_as_float(p.scale, p.scale_dtype, row);
+#pragma unroll
+      for (int m = 0; m < MT; ++m)
+        if (m < p.M) {
+          float v = acc[r][m];
+          if (!GROUPED && p.scale != nullptr)
+            v = v * s;
+          if (p.bias != nullptr)
+            v = p.bias[row] + v;
+          acc[r][m] = v;
+        }
+    }
+    if (p.silu_pairs) {
+      // rows (2j, 2j+1) = (gate_j, up_j); R is even and row0 is even.
+#pragma unroll
+      for (int r = 0; r + 1 < R; r += 2) {
+        const int64_t row = row0 + r;
+        if (row + 1 >= p.N)
+          continue;
+        const int64_t col = row >> 1;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+          if (m < p.M) {
+            const float v = silu_mul(acc[r][m], acc[r + 1][m]);
+            const int64_t o = (int64_t)m * p.y_ld + col;
+            if (p.y_dtype == B200_F32)
+              ((float *)p.y)[o] = v;
+            else
+              ((__half *)p.y)[o] = __float2half_rn(v);
+          }
+      }
+    } else {
+#pragma unroll
+      for (int r = 0; r < R; ++r) {
+        const int64_t row = row0 + r;
+        if (row >= p.N)
+          continue;
+#pragma unroll
+        for (int m = 0; m < MT; ++m)
+          if (m < p.M) {
+            const int64_t o = (int64_t)m * p.y_ld + row;
+            float v = acc[r][m];
+            if (p.residual != nullptr)
+              v = p.residual[o] + v;
+            if (p.y_dtype == B200_F32) {
+              if (p.accumulate)
+                v = ((float *)p.y)[o] + v;
+              ((float *)p.y)[o] = v;
+            } else {
+              if (p.accumulate)
+                v = __half2float(((__half *)p.y)[o]) + v;
+              ((__half *)p.y)[o] = __float2half_rn(v);
+            }
+          }
+      }
+    }
+  }
+}
+
+template <int KIND, int MT, int R, bool GROUPED>
+static int launch(const GemvP &p, int warps, cudaStream_t st) {
+  auto kern = gemv_kernel<KIND, MT, R, GROUPED>;
+  const size_t smem = (size_t)MT * p.kc * sizeof(float);
+  if (smem > 48 * 1024) {
+    static thread_local size_t configured = 0;
+    if (smem > configured) {
+      B200_CUDA(cudaFuncSetAttribute(
+          kern, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024));
+      configured = 200 * 1024;
+    }
+  }
+  const int64_t rows_per_cta = (int64_t)warps * R;
+  const int64_t grid = (p.N + rows_per_cta - 1) / rows_per_cta;
+  kern<<<(unsigned)grid, warps * 32, smem, st>>>(p);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+template <int KIND, bool GROUPED>
+static int dispatch(const GemvP &p, int mt, int R, int warps,
+                    cudaStream_t st) {
+#define B200_CASE(MT_, R_)                                                     \
+  if (mt == MT_ && R == R_)                                                    \
+    return launch<KIND, MT_, R_, GROUPED>(p, warps, st);
+  B200_CASE(1, 1) B200_CASE(1, 2) B200_CASE(1, 4)
+  B200_CASE(2, 2) B200_CASE(4, 2) B200_CASE(8, 2) B200_CASE(16, 2)
+#undef B200_CASE
+  return fail(B200_EINVAL, "gemv: no kernel for M tile %d, R %d", mt, R);
+}
+
+} // namespace b200
+
+using namespace b200;
+
+extern "C" int b200_gemv(const b200_weight *w, const b200_gemv_args *a,
+                         void *stream) {
+  if (!w || !a || !w->w || !a->x || !a->y)
+    return fail(B200_EINVAL, "gemv: null argument");
+  if (a->M < 1 || a->M > 16)
+    return fail(B200_EINVAL, "gemv: M=%d outside 1..16", a->M);
+  if (w->K < 1 || w->N < 1 || w->K > (1 << 24))
+    return fail(B200_EINVAL, "gemv: bad shape K=%lld N=%lld",
+                (long long)w->K, (long long)w->N);
+  if (w->kind != B200_W_F32 && w->kind != B200_W_I8 && w->kind != B200_W_U4)
+    return fail(B200_EINVAL, "gemv: unknown weight kind %d", w->kind);
+  if (w->kind != B200_W_F32 && !w->scale)
+    return fail(B200_EINVAL, "gemv: quantised weight without scales");
+  if (a->silu_pairs && (w->N & 1))
+    return fail(B200_EINVAL, "gemv: silu_pairs needs an even N");
+  if (a->silu_pairs && (a->accumulate || a->residual))
+    return fail(B200_EINVAL, "gemv: silu_pairs excludes accumulate/residual");
+  if (int rc = ensure_device())
+    return rc;
+
+  GemvP p{};
+  p.x = a->x;
+  p.w = (const uint8_t *)w->w;
+  p.scale = w->scale;
+  p.bias = w->bias;
+  p.residual = a->residual;
+  p.norm_w = a->norm_weight;
+  p.y = a->y;
+  p.x_ld = a->x_ld ? a->x_ld : w->K;
+  p.y_ld = a->y_ld ? a->y_ld : (a->silu_pairs ? w->N / 2 : w->N);
+  p.K = (int)w->K;
+  p.Kp = (int)packed_k(w->kind, w->K);
+  p.row_bytes = packed_row_bytes(w->kind, w->K);
+  p.N = (int)w->N;
+  p.M = a->M;
+  p.x_dtype = a->x_dtype;
+  p.y_dtype = a->y_dtype;
+  p.scale_dtype = w->scale_dtype;
+  p.accumulate = a->accumulate;
+  p.silu_pairs = a->silu_pairs;
+  p.eps = a->norm_eps;
+  bool grouped = false;
+  p.group = p.Kp;
+  p.ngroups = 1;
+  if (w->kind == B200_W_U4 && w->group > 0 && w->group < w->K) {
+    if (w->K % w->group != 0 || w->group % 4 != 0)
+      return fail(B200_EINVAL, "gemv: group %d does not divide K=%lld",
+                  w->group, (long long)w->K);
+    grouped = true;
+    p.group = w->group;
+    p.ngroups = (int)(w->K / w->group);
+  }
+
+  const int mt = a->M == 1 ? 1 : a->M == 2 ? 2 : a->M <= 4 ? 4 : a->M <= 8 ? 8 : 16;
+  // Activation slab: whole K when it fits, else a multiple of the largest
+  // block (1024 elements) that keeps the staged tile under ~64 KB.
+  int kc = p.Kp;
+  const int budget = (64 * 1024) / (4 * mt);
+  if (kc > budget)
+    kc = (budget / 1024) * 1024;
+  p.kc = kc;
+
+  // Rows per warp and warps per CTA: aim for >= 4 CTAs per SM.
+  int R = 2, warps = 8;
+  if (mt == 1) {
+    const int64_t want = 4 * 148;
+    if (w->N / (8 * 4) >= want)
+      R = 4;
+    else if (w->N / (8 * 2) >= want)
+      R = 2;
+    else if (w->N / (4 * 2) >= want) {
+      R = 2;
+      warps = 4;
+    } else {
+      R = a->silu_pairs ? 2 : 1;
+      warps = 4;
+    }
+  } else if (w->N / (8 * 2) < 2 * 148) {
+    warps = 4;
+  }
+  cudaStream_t st = (cudaStream_t)stream;
+  switch (w->kind) {
+  case B200_W_I8:
+    return dispatch<B200_W_I8, false>(p, mt, R, warps, st);
+  case B200_W_F32:
+    return dispatch<B200_W_F32, false>(p, mt, R, warps, st);
+  default:
+    return grouped ? dispatch<B200_W_U4, true>(p, mt, R, warps, st)
+                   : dispatch<B200_W_U4, false>(p, mt, R, warps, st);
+  }
+}

@@ -1,0 +1,92 @@
+"""Seeded synthetic weights in buddy-mlir's flat-blob order.
+
+Order of the f32 blob (frontend/Python/graph/graph.py:836-863 packs the params
+in graph order; the order itself is read off the argument list of
+examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:4): embedding,
+inv_freq, per layer {input norm, q bias, Wq, k bias, Wk, v bias, Wv, Wo,
+post-attention norm, Wgate, Wup, Wdown}, final norm, lm_head.  Every matmul
+weight is [K,N] row-major (eliminate_weight_transpose.py:163-219).
+
+For the w8a32 variant the same walk is split by dtype
+(tools/buddy-codegen/import_model.py:818-887): o, gate, up, down and lm_head go
+to the int8 blob, everything else to the float blob, followed by the scales in
+original-weight order (quantize.py:577-589).
+
+No real checkpoint is used anywhere: weights are N(0, 0.02) from a seeded
+numpy generator, norm weights 1 + N(0, 0.02).
+"""
+import numpy as np
+
+from .config import ModelConfig
+
+QUANTISED_BY_REFERENCE = ("o", "gate", "up", "down", "lm_head")
+
+
+def tensor_list(cfg: ModelConfig):
+    """[(name, layer, shape)] in blob order."""
+    H, QD, KD, F, V, D = cfg.hidden, cfg.q_dim, cfg.kv_dim, cfg.ffn, cfg.vocab, cfg.head_dim
+    out = [("embed", -1, (V, H)), ("inv_freq", -1, (D // 2,))]
+    for l in range(cfg.n_layers):
+        out.append(("in_norm", l, (H,)))
+        if cfg.qkv_bias:
+            out += [("q_bias", l, (QD,)), ("q", l, (H, QD)), ("k_bias", l, (KD,)),
+                    ("k", l, (H, KD)), ("v_bias", l, (KD,)), ("v", l, (H, KD))]
+        else:
+            out += [("q", l, (H, QD)), ("k", l, (H, KD)), ("v", l, (H, KD))]
+        if cfg.qk_norm:
+            out += [("q_norm", l, (D,)), ("k_norm", l, (D,))]
+        out += [("o", l, (QD, H)), ("post_norm", l, (H,)), ("gate", l, (H, F)),
+                ("up", l, (H, F)), ("down", l, (F, H))]
+    out += [("final_norm", -1, (H,)), ("lm_head", -1, (H, V))]
+    return out
+
+
+def blob_elements(cfg: ModelConfig):
+    return sum(int(np.prod(s)) for _, _, s in tensor_list(cfg))
+
+
+def inv_freq(cfg: ModelConfig):
+    j = np.arange(0, cfg.head_dim, 2, dtype=np.float32) / np.float32(cfg.head_dim)
+    return (np.float32(1.0) / np.power(np.float32(cfg.rope_theta), j)).astype(np.float32)
+
+
+def make_f32_blob(cfg: ModelConfig, seed: int):
+    """Returns (blob, views): blob is one float32 array, views maps
+    (name, layer) -> the tensor as a view into the blob."""
+    rng = np.random.default_rng(seed)
+    blob = np.empty(blob_elements(cfg), dtype=np.float32)
+    views, off = {}, 0
+    for name, layer, shape in tensor_list(cfg):
+        n = int(np.prod(shape))
+        v = blob[off:off + n]
+        if name == "inv_freq":
+            v[:] = inv_freq(cfg)
+        else:
+            rng.standard_normal(n, dtype=np.float32, out=v)
+            v *= np.float32(0.02)
+            if name.endswith("norm"):
+                v += np.float32(1.0)
+        views[(name, layer)] = v.reshape(shape)
+        off += n
+    return blob, views
+
+
+def split_w8a32(cfg: ModelConfig, views, quantize):
+    """Reference-faithful w8a32 blobs from the f32 tensors.
+
+    quantize(W [K,N] f32) -> (Q [K,N] int8, scale [N] f32).
+    Returns (float_blob, int8_blob)."""
+    floats, ints, scales = [], [], []
+    for name, layer, _ in tensor_list(cfg):
+        t = views[(name, layer)]
+        if name in QUANTISED_BY_REFERENCE:
+            q, s = quantize(t)
+            ints.append(np.ascontiguousarray(q).reshape(-1))
+            scales.append(np.ascontiguousarray(s, dtype=np.float32).reshape(-1))
+        else:
+            floats.append(t.reshape(-1))
+    return np.concatenate(floats + scales), np.concatenate(ints)
+
+
+def prompt_tokens(cfg: ModelConfig, seed: int, n: int = 32):
+    return np.random.default_rng(seed).integers(0, cfg.vocab, size=n).astype(np.int64)

@@ -1,0 +1,290 @@
+/*
+ * buddy_b200 -- hand-written sm_100a kernels for buddy-mlir's LLM decode path,
+ * behind a plain C ABI.
+ *
+ * Three layers, lowest first:
+ *
+ *   1. b200_*            device-pointer entry points (weights, activations and
+ *                        KV already resident in HBM; every call takes a CUDA
+ *                        stream as void*).  This is the performance surface.
+ *   2. b200_model_*      a device-resident decode session: weights in the
+ *                        packed device layout, KV cache, one CUDA graph per
+ *                        decode step.
+ *   3. _mlir_ciface_*    the symbols buddy-mlir's compiled code and generated
+ *                        ModelSession bind: per-op external kernels in the
+ *                        convention of runtime/external_kernels (MemRef
+ *                        descriptors on the host, callee-allocated result) and
+ *                        the model entry _mlir_ciface_forward_decode.
+ *                        Declared in buddy_b200_memref.h.
+ *
+ * All functions return 0 on success and a negative B200_E* code on failure;
+ * b200_last_error() gives the message of the calling thread's last failure.
+ * Nothing here falls back to the CPU: without a CUDA device every compute
+ * entry point fails with B200_ENODEV.
+ */
+#ifndef BUDDY_B200_H
+#define BUDDY_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_OK 0
+#define B200_EINVAL (-1)  /* bad argument (shape, alignment, null pointer) */
+#define B200_ECUDA (-2)   /* a CUDA runtime call failed */
+#define B200_ENODEV (-3)  /* no usable CUDA device */
+#define B200_ENOMEM (-4)  /* device or host allocation failed */
+#define B200_ELIMIT (-5)  /* size beyond a documented fixed limit */
+#define B200_ESTATE (-6)  /* call sequence error (e.g. decode before load) */
+
+const char *b200_last_error(void);
+/* Library version, and the number of kernels launched by this process so far
+ * (counted at every launch site; graph replays add the node count). */
+const char *b200_version(void);
+uint64_t b200_launch_count(void);
+
+/* Element types of activation / scale buffers. */
+enum { B200_F32 = 0, B200_F16 = 1, B200_BF16 = 2 };
+
+/* Weight kinds of the packed device layout. */
+enum {
+  B200_W_F32 = 0, /* f32, row n = output channel, K contiguous            */
+  B200_W_I8 = 1,  /* int8, per-output-channel scale                       */
+  B200_W_U4 = 2   /* 4-bit, value = nibble - 8, one scale per `group` k    */
+};
+
+/* ------------------------------------------------------------------------
+ * Packed device layout ("packed decode weights").
+ *
+ * buddy-mlir keeps every matmul weight as [K,N] row-major after
+ * eliminate_transpose (frontend/Python/graph/transform/eliminate_weight_transpose.py:163-219),
+ * which its CPU GEMV walks with a stride of N between consecutive k
+ * (docs/DecodeWeightPacking.md:27-46), and panel-packs only float weights
+ * (frontend/Python/graph/transform/pack_decode_weights.py:32-124).  The device
+ * layout here is one row per OUTPUT channel n with the row's K weights
+ * contiguous, so that a warp streams one output row with 32 x 16-byte loads.
+ * Inside a row, k is permuted within blocks of 32 sixteen-byte units so that
+ * the four (int8) or eight (int4) 4-element groups a lane holds are a quarter
+ * (an eighth) of a block apart: the activation reads from shared memory are
+ * then contiguous across lanes.  b200_packed_offset() states the map.
+ * ---------------------------------------------------------------------- */
+
+/* Padded K (elements) and bytes per packed row for a weight kind. */
+int64_t b200_packed_k(int kind, int64_t K);
+int64_t b200_packed_row_bytes(int kind, int64_t K);
+/* Byte offset inside a packed row of element k (for U4: of the byte holding
+ * it; *nibble = 0 low, 1 high).  Pure host function. */
+int64_t b200_packed_offset(int kind, int64_t K, int64_t k, int *nibble);
+
+/* Reference layout -> device layout.  src is the reference's [K,N] row-major
+ * tensor: f32, int8, or nibble-packed [K,N/2] (even column = low nibble,
+ * tools/buddy-codegen/import_model.py:810-815).  src_signed = 1 means the
+ * nibbles are two's complement (-8..7, the reference's w4a16 format) and are
+ * stored as nibble+8; 0 means they already are zero-point-8 codes. */
+int b200_pack_weight(int kind, const void *src_kn, int64_t K, int64_t N,
+                     int src_signed, void *dst, void *stream);
+/* Device layout -> reference layout (exact inverse of b200_pack_weight). */
+int b200_unpack_weight(int kind, const void *packed, int64_t K, int64_t N,
+                       int dst_signed, void *dst_kn, void *stream);
+/* Scales: reference [K/G, N] (or [N] when G == K) -> device [N, K/G]. */
+int b200_pack_scales(const void *src, int dtype, int64_t groups, int64_t N,
+                     void *dst, void *stream);
+
+/* Replaces extract_quantized_weights (tools/buddy-codegen/import_model.py:790-892):
+ * W [K,N] f32 -> Q [K,N] int8 values (bits = 8: -128..127, bits = 4: -8..7)
+ * and scale [N] f32 = max(1e-10, absmax_k / qmax). */
+int b200_quantize_per_channel(const float *W, int64_t K, int64_t N, int bits,
+                              int8_t *Q, float *scale, void *stream);
+/* Group-wise zero-point-8 int4 quantiser (this library's superset format):
+ * P [K,N/2] nibble codes, scales [K/G,N] f16. */
+int b200_quantize_w4_group(const float *W, int64_t K, int64_t N, int64_t G,
+                           uint8_t *P, uint16_t *scale_f16, void *stream);
+/* Replaces pack_int4_nibbles (import_model.py:810-815) and int4_unpack_op
+ * (frontend/Python/ops/tosa.py:12158-12203). */
+int b200_pack_int4(const int8_t *flat, int64_t n, int8_t *packed, void *stream);
+int b200_unpack_int4(const int8_t *packed, int64_t nbytes, int8_t *flat,
+                     void *stream);
+
+/* ------------------------------------------------------------------------
+ * Decode GEMV, M = 1..16 activation rows.
+ * Replaces the loops emitted by
+ *   midend/lib/Conversion/MatMulOptimization/DequantMatMulVectorizationDecode.cpp:191-366      (I8)
+ *   midend/lib/Conversion/MatMulOptimization/Int4DequantMatMulVectorizationDecode.cpp:320-562  (U4)
+ *   midend/lib/Conversion/MatMulOptimization/MatMulVectorizationDecode.cpp:94-192              (F32)
+ * y[m,n] = (accumulate ? y[m,n] : 0) + bias[n] + residual[m,n]
+ *          + sum_g scale[n,g] * sum_{k in g} x[m,k] * w[n,k]
+ * with f32 accumulation.  When norm_weight != NULL, x is first replaced by
+ * norm_weight * (x * rsqrt(mean(x^2) + eps)) (the RMSNorm of
+ * examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:60-72).  When
+ * silu_pairs != 0 the N rows are (gate_j, up_j) pairs and y has N/2 columns:
+ * y[m,j] = silu(row 2j) * row 2j+1 (subgraph0_decode_simplify.mlir:226-231).
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t kind;        /* B200_W_*                                         */
+  int32_t group;       /* U4: k per scale; I8/F32: ignored                 */
+  int64_t K, N;
+  const void *w;       /* packed device layout                             */
+  const void *scale;   /* I8: [N]; U4: [N, K/group]; F32: NULL             */
+  int32_t scale_dtype; /* B200_F32 or B200_F16                             */
+  int32_t reserved;
+  const float *bias;   /* [N] or NULL                                      */
+} b200_weight;
+
+typedef struct {
+  const void *x;          /* [M,K] activations                             */
+  int32_t x_dtype;        /* B200_F32 / F16 / BF16                         */
+  int32_t y_dtype;        /* B200_F32 / F16                                */
+  int64_t x_ld, y_ld;     /* row strides in elements                       */
+  void *y;                /* [M,N] (or [M,N/2] with silu_pairs)            */
+  const float *residual;  /* [M,N] f32, stride y_ld, or NULL; may alias y  */
+  const float *norm_weight; /* [K] or NULL                                 */
+  float norm_eps;
+  int32_t M;
+  int32_t accumulate;
+  int32_t silu_pairs;
+} b200_gemv_args;
+
+int b200_gemv(const b200_weight *w, const b200_gemv_args *a, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Small fused ops (f32).
+ * ---------------------------------------------------------------------- */
+/* RMSNorm, subgraph0_decode_simplify.mlir:60-72. x,y [rows,H]. */
+int b200_rmsnorm(const float *x, const float *w, float *y, int64_t rows,
+                 int64_t H, float eps, void *stream);
+/* silu(g) * u, subgraph0_decode_simplify.mlir:226-231. */
+int b200_silu_mul(const float *g, const float *u, float *y, int64_t n,
+                  void *stream);
+/* RoPE on q [q_heads,D] and k [kv_heads,D] in place at position *pos, then
+ * write k and v into cache row *pos (subgraph0_decode_simplify.mlir:52-59,
+ * 86-142).  Optional per-head RMSNorm of q and k first (Qwen3). pos is a
+ * device pointer so the call can live in a CUDA graph. */
+int b200_rope_kv_write(float *q, float *k, const float *v, float *k_cache,
+                       float *v_cache, const float *inv_freq,
+                       const float *q_norm, const float *k_norm, float eps,
+                       int q_heads, int kv_heads, int D, int max_len,
+                       const int32_t *pos, void *stream);
+/* GQA decode attention, frontend/Python/ops/tosa.py:13931-14635: one query
+ * row per head against cache rows [0, *pos].  scratch holds the split
+ * partials and one arrival counter per kv head: b200_gqa_scratch_floats()
+ * floats, zeroed once by the caller before the first call (every call leaves
+ * the counters at zero again). */
+int64_t b200_gqa_scratch_floats(int q_heads, int D, int splits);
+int b200_gqa_decode(const float *q, const float *k_cache, const float *v_cache,
+                    float *out, float *scratch, int q_heads, int kv_heads,
+                    int D, int max_len, int splits, const int32_t *pos,
+                    void *stream);
+/* Embedding row gather (subgraph0_decode_simplify.mlir:46-49). */
+int b200_embed(const float *table, const int32_t *token, float *x, int64_t H,
+               void *stream);
+/* Greedy sampling: lowest index among equal maxima
+ * (runtime/include/buddy/runtime/llm/Sampler.h:101-104). scratch: 2*1024
+ * floats. */
+int b200_argmax_first(const float *v, int64_t n, int32_t *out, float *scratch,
+                      void *stream);
+/* KV overflow: discard + move + zero + RoPE re-rotation of K
+ * (runtime/include/buddy/runtime/llm/KVCacheManager.h:151-273 as driven by
+ * tools/buddy-codegen/gen_session.py:1471-1506).  kv_dev: device array of
+ * n_buffers device pointers (K at even index).  Returns new position in
+ * *new_position (host), or -1 there when position < max_len. */
+int b200_kv_overflow(float **kv_dev, int n_buffers, int kv_heads, int max_len,
+                     int D, int position, int keep, float theta,
+                     int *new_position, void *stream);
+
+/* ------------------------------------------------------------------------
+ * Device-resident decode session.
+ * ---------------------------------------------------------------------- */
+typedef struct {
+  int32_t hidden, n_layers, q_heads, kv_heads, head_dim, ffn, vocab, max_len;
+  float eps, rope_theta;
+  int32_t qkv_bias; /* Qwen2: 1 */
+  int32_t qk_norm;  /* Qwen3: 1 */
+  int32_t tp_rank, tp_size; /* tensor parallel shard of this process */
+} b200_model_config;
+
+typedef struct b200_model b200_model;
+
+/* Tensor slots for b200_model_set_*; layer = -1 for model-level slots. */
+enum {
+  B200_T_EMBED = 0, B200_T_INV_FREQ, B200_T_FINAL_NORM, B200_T_LM_HEAD,
+  B200_T_IN_NORM, B200_T_POST_NORM, B200_T_Q_NORM, B200_T_K_NORM,
+  B200_T_Q, B200_T_K, B200_T_V, B200_T_O, B200_T_GATE, B200_T_UP, B200_T_DOWN,
+  B200_T_Q_BIAS, B200_T_K_BIAS, B200_T_V_BIAS
+};
+
+int b200_model_create(const b200_model_config *cfg, b200_model **out);
+void b200_model_destroy(b200_model *m);
+/* Upload a float vector / table from HOST memory (full, unsharded tensor). */
+int b200_model_set_vector(b200_model *m, int layer, int slot,
+                          const float *host, int64_t n);
+/* Upload one linear layer from HOST memory in the reference's layout
+ * ([K,N] row-major f32 / int8 / nibble-packed) and repack it on the device.
+ * src_kind: B200_W_*; quantize_to: -1 keep, B200_W_I8 / B200_W_U4 quantise an
+ * f32 source on the device first (group = U4 group size, 0 = per channel). */
+int b200_model_set_linear(b200_model *m, int layer, int slot, int src_kind,
+                          const void *host_w, const void *host_scale,
+                          int scale_dtype, int src_signed, int64_t K,
+                          int64_t N, int quantize_to, int group);
+/* Walk buddy-mlir's flat weight blobs (frontend/Python/graph/graph.py:836-863,
+ * frontend/Python/graph/transform/quantization/quantize.py:577-589; file
+ * table tools/buddy-codegen/gen_config.py:51-71) and load every tensor.
+ * variant: "f32" (one blob) or "w8a32" (float blob + int8 blob: o, gate, up,
+ * down and lm_head quantised, q/k/v float, scales at the end of the float
+ * blob). all_linear_w8 != 0 additionally quantises every remaining f32 linear
+ * layer to int8 on the device. */
+int b200_model_load_blobs(b200_model *m, const char *variant,
+                          const void *float_blob, int64_t n_float,
+                          const void *int_blob, int64_t n_int,
+                          int all_linear_w8);
+/* Expected element counts of the blobs for a variant (pure host function). */
+int b200_blob_elements(const b200_model_config *cfg, const char *variant,
+                       int64_t *n_float, int64_t *n_int);
+/* Finish loading: fuse q|k|v and gate|up rows, build the decode graph. */
+int b200_model_finalize(b200_model *m);
+/* Copy KV rows [pos0, pos0 + n_pos) of every head of one cache buffer (index
+ * 2*layer + (0 K | 1 V)) between a host buffer laid out like the reference's
+ * [1, kv_heads, max_len, head_dim] f32 cache and the device cache. */
+int b200_model_kv_upload(b200_model *m, int buffer, const float *host,
+                         int pos0, int n_pos);
+int b200_model_kv_download(b200_model *m, int buffer, float *host, int pos0,
+                           int n_pos);
+/* The K and V rows the last decode step wrote, gathered:
+ * host [2*n_layers][local kv_heads][head_dim] (K of layer l at index 2l). */
+int b200_model_read_new_kv_rows(b200_model *m, float *host);
+/* One decode step (the body of _mlir_ciface_forward_decode): token at cache
+ * row `pos`.  logits_host (vocab floats, may be NULL) receives the logits;
+ * next_token (may be NULL) the device-side greedy argmax. */
+int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
+                      int *next_token);
+/* Device-resident loop: `steps` greedy decode steps starting from `token` at
+ * `pos`, feeding each argmax back without leaving the GPU; tokens_out
+ * receives the `steps` generated ids. */
+int b200_model_generate(b200_model *m, int token, int pos, int steps,
+                        int *tokens_out);
+/* Timing of the last decode/generate call, CUDA events on the session's
+ * stream (ms). */
+float b200_model_last_ms(const b200_model *m);
+/* Algorithmic HBM bytes one decode step reads at context length ctx
+ * (weights + scales + small tensors + embedding row + live KV rows). */
+int64_t b200_model_step_bytes(const b200_model *m, int ctx);
+int b200_model_kernels_per_step(const b200_model *m);
+/* Session handle -> device pointers, for tests. */
+float *b200_model_kv_ptr(b200_model *m, int buffer);
+/* KV overflow on the device-resident cache; see b200_kv_overflow. */
+int b200_model_kv_overflow(b200_model *m, int position, int keep, float theta,
+                           int *new_position);
+
+/* Tensor parallel plumbing: the caller creates an NCCL unique id
+ * (b200_tp_unique_id on rank 0), distributes the 128 bytes with its own
+ * transport, and every rank calls b200_tp_init before b200_model_create. */
+int b200_tp_unique_id(void *id128);
+int b200_tp_init(const void *id128, int rank, int size);
+void b200_tp_shutdown(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

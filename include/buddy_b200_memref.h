@@ -1,0 +1,141 @@
+/*
+ * buddy_b200 -- the symbols buddy-mlir's compiled code binds.
+ *
+ * Calling convention (identical to runtime/external_kernels in buddy-mlir):
+ * after bufferisation and -llvm-request-c-wrappers (tools/buddy-codegen/
+ * compile_pipeline.py:66) a graph-level `func.call @name(tensor...) -> tensor`
+ * (frontend/Python/ops/func.py:115-147) becomes
+ *     void _mlir_ciface_<name>(ResultDesc *out, ArgDesc *a0, ArgDesc *a1, ...)
+ * with every descriptor
+ *     { T *allocated; T *aligned; intptr_t offset; intptr_t sizes[R]; intptr_t strides[R]; }
+ * (frontend/Interfaces/buddy/Core/Container.h:126-138; the StridedMemRefType
+ * of runtime/external_kernels/rng/RNGUtils.cpp:87-118).  Strides are in
+ * elements and may be non-contiguous.  `out` arrives uninitialised: the callee
+ * mallocs the result and fills every field (RNGUtils.cpp:104-117,
+ * runtime/external_kernels/matmul/MatmulTorq.cpp:149-165); the generated code
+ * frees it later.  The functions return void; on failure they leave
+ * out->allocated = out->aligned = NULL (MatmulTorq.cpp:150-151 returns
+ * silently on OOM) and the reason is available from b200_last_error().
+ *
+ * All buffers here are HOST memory.  Weight operands are uploaded and
+ * repacked once and cached by host address; b200_release_cached_weights()
+ * drops the cache.
+ */
+#ifndef BUDDY_B200_MEMREF_H
+#define BUDDY_B200_MEMREF_H
+
+#include "buddy_b200.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define B200_MEMREF(NAME, T, R)                                                \
+  typedef struct {                                                             \
+    T *allocated;                                                              \
+    T *aligned;                                                                \
+    intptr_t offset;                                                           \
+    intptr_t sizes[R];                                                         \
+    intptr_t strides[R];                                                       \
+  } NAME
+
+B200_MEMREF(b200_memref_f32_1, float, 1);
+B200_MEMREF(b200_memref_f32_2, float, 2);
+B200_MEMREF(b200_memref_f32_3, float, 3);
+B200_MEMREF(b200_memref_f32_4, float, 4);
+B200_MEMREF(b200_memref_f16_2, uint16_t, 2);
+B200_MEMREF(b200_memref_i8_2, int8_t, 2);
+B200_MEMREF(b200_memref_i64_1, long long, 1);
+B200_MEMREF(b200_memref_i64_2, long long, 2);
+
+/* Same symbol, same signature as runtime/include/buddy/runtime/Matmul.h:35-36
+ * (implemented there for RISC-V only, MatmulTorq.cpp:116-166): result = A*B,
+ * A [M,K], B [K,N] f32. */
+void _mlir_ciface_buddy_matmul_f32(b200_memref_f32_2 *result,
+                                   b200_memref_f32_2 *A, b200_memref_f32_2 *B);
+
+/* int8 weight-only decode matmul: C[m,n] = scale[0,n] * sum_k A[m,k]*W[k,n].
+ * Replaces the code DequantMatMulVectorizationDecode.cpp:191-366 generates
+ * for the chain sitofp(W) * scale -> linalg.matmul. A [M,K] f32, W [K,N]
+ * int8, scale [1,N] f32. */
+void _mlir_ciface_buddy_gemv_w8_f32(b200_memref_f32_2 *result,
+                                    b200_memref_f32_2 *A, b200_memref_i8_2 *W,
+                                    b200_memref_f32_2 *scale);
+
+/* packed-int4 decode matmul, f16 in / f16 out
+ * (Int4DequantMatMulVectorizationDecode.cpp:320-562): A [M,K] f16,
+ * P [K,N/2] signed nibbles, scale [1,N] f16. Accumulates in f32. */
+void _mlir_ciface_buddy_gemv_w4_f16(b200_memref_f16_2 *result,
+                                    b200_memref_f16_2 *A, b200_memref_i8_2 *P,
+                                    b200_memref_f16_2 *scale);
+
+/* group-wise zero-point-8 int4 (this library's format): A [M,K] f32,
+ * P [K,N/2] codes, scale [K/G,N] f16; G = K / scale->sizes[0]. */
+void _mlir_ciface_buddy_gemv_w4g_f32(b200_memref_f32_2 *result,
+                                     b200_memref_f32_2 *A, b200_memref_i8_2 *P,
+                                     b200_memref_f16_2 *scale);
+
+/* RMSNorm over the last dim (subgraph0_decode_simplify.mlir:60-72):
+ * x [rows,H], w [H]; eps is a one-element memref. */
+void _mlir_ciface_buddy_rmsnorm_f32(b200_memref_f32_2 *result,
+                                    b200_memref_f32_2 *x, b200_memref_f32_1 *w,
+                                    b200_memref_f32_1 *eps);
+
+/* silu(g) * u (subgraph0_decode_simplify.mlir:226-231). */
+void _mlir_ciface_buddy_silu_mul_f32(b200_memref_f32_2 *result,
+                                     b200_memref_f32_2 *g,
+                                     b200_memref_f32_2 *u);
+
+/* RoPE at one position (subgraph0_decode_simplify.mlir:52-59, 86-105):
+ * x [1,heads,1,D], inv_freq [D/2], pos [1]. */
+void _mlir_ciface_buddy_rope_f32(b200_memref_f32_4 *result,
+                                 b200_memref_f32_4 *x,
+                                 b200_memref_f32_1 *inv_freq,
+                                 b200_memref_i64_1 *pos);
+
+/* GQA decode attention (frontend/Python/ops/tosa.py:13931-14635):
+ * q [1,q_heads,1,D], caches [1,kv_heads,max_len,D], pos [1] (rows 0..pos are
+ * live; the reference expresses the same thing with its additive mask). */
+void _mlir_ciface_buddy_gqa_decode_f32(b200_memref_f32_4 *result,
+                                       b200_memref_f32_4 *q,
+                                       b200_memref_f32_4 *k_cache,
+                                       b200_memref_f32_4 *v_cache,
+                                       b200_memref_i64_1 *pos);
+
+void b200_release_cached_weights(void);
+
+/* ------------------------------------------------------------------------
+ * Whole-entry model ABI.  The generated ModelSession resolves
+ * _mlir_ciface_forward_decode in the model .so by dlsym and calls it with
+ *   (DecodeABI *result, MemRef<Tw,1> *w0 [, *w1], MemRef<i64,2> *token,
+ *    MemRef<i64,1> *cache_position, KV4 *kv0, KV4 *kv1, Dummy1 *dummy0,
+ *    KV4 *kv2, KV4 *kv3, Dummy1 *dummy1, ...)
+ * (tools/buddy-codegen/gen_session.py:979-1008, 1381-1414); DecodeABI is
+ * { i64_1 cache_position_out; f32_4 kv0, kv1; i64_1 dummy0; f32_4 kv2, kv3;
+ *   i64_1 dummy1; ...; f32_3 logits } (gen_session.py:924-972).  Because the
+ * arity depends on the model, that symbol lives in a small per-variant shim
+ * (buddy_mlir_b200/gen_model_entry.py writes it) which unpacks the
+ * descriptors and calls this function.
+ *
+ * host_kv: 2*n_layers host cache buffers [1,kv_heads,max_len,head_dim], K at
+ * even index.  The device cache is authoritative between consecutive
+ * positions; when `pos` is not the previous call's pos + 1 (first decode after
+ * the CPU prefill, or after the host-side handleKVCacheOverflow of
+ * gen_session.py:1471-1506) rows [0,pos) are uploaded from host_kv first.
+ * Every call writes the new K/V row `pos` back into host_kv, so the host
+ * buffers stay what the reference's in-place KV write would have left.
+ * logits_out receives a malloc'ed [vocab] f32 buffer the caller frees
+ * (gen_session.py:1416-1442 copies it out and destroys the descriptor).
+ * ---------------------------------------------------------------------- */
+int b200_forward_decode(const b200_model_config *cfg, const char *variant,
+                        int all_linear_w8, const void *w0, int64_t n0,
+                        const void *w1, int64_t n1, long long token,
+                        long long pos, float *const *host_kv,
+                        float **logits_out);
+/* Drop the session b200_forward_decode keeps (weights, KV, graph). */
+void b200_forward_reset(void);
+
+#ifdef __cplusplus
+}
+#endif
+#endif

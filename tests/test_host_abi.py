@@ -1,0 +1,100 @@
+"""Host-side checks that need no GPU: the library loads and exports every
+declared symbol, the packed-row index map is a bijection, the blob walk
+counts match buddy-mlir's specs, and compute entry points refuse to run
+without a device instead of falling back."""
+import ctypes as C
+
+import numpy as np
+import pytest
+
+from buddy_mlir_b200 import DEEPSEEK_R1_1P5B, TINY_QWEN2, _lib, synthetic
+
+
+def _has_gpu():
+    try:
+        import torch
+        return torch.cuda.is_available()
+    except Exception:
+        return False
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _lib.exported_symbols()
+    assert len(names) > 40
+    missing = [n for n in names if not hasattr(lib, n)]
+    assert not missing, missing
+
+
+@pytest.mark.parametrize("kind,unit", [(_lib.W_I8, 16), (_lib.W_U4, 32), (_lib.W_F32, 4)])
+@pytest.mark.parametrize("K", [8, 16, 100, 512, 1536, 8960, 4096 + 64])
+def test_packed_offset_is_a_bijection(kind, unit, K):
+    lib = _lib.load()
+    Kp = lib.b200_packed_k(kind, K)
+    assert Kp % unit == 0 and Kp >= K and Kp - K < unit
+    rb = lib.b200_packed_row_bytes(kind, K)
+    assert rb == Kp // unit * 16
+    seen = set()
+    nib = C.c_int(0)
+    for k in range(Kp):
+        off = lib.b200_packed_offset(kind, K, k, C.byref(nib))
+        assert 0 <= off < rb
+        if kind == _lib.W_F32:
+            assert off % 4 == 0
+        seen.add((off, nib.value))
+    assert len(seen) == Kp
+
+
+def test_packed_offset_lane_groups_are_contiguous_across_lanes():
+    # group j of lane l covers k = j*(Bs/G) + 4l .. +3: lanes walk x contiguously
+    lib = _lib.load()
+    K = 1536
+    nib = C.c_int(0)
+    for k in range(0, 512, 4):
+        off = lib.b200_packed_offset(_lib.W_I8, K, k, C.byref(nib))
+        j, l = k // 128, (k % 128) // 4
+        assert off == l * 16 + j * 4
+
+
+def test_blob_counts_match_reference_specs():
+    # models/deepseek_r1/specs/f32.json and w8a32.json
+    lib = _lib.load()
+    c = DEEPSEEK_R1_1P5B.to_c()
+    nf, ni = C.c_int64(), C.c_int64()
+    assert lib.b200_blob_elements(C.byref(c), b"f32", C.byref(nf), C.byref(ni)) == 0
+    assert (nf.value, ni.value) == (1777088064, 0)
+    assert lib.b200_blob_elements(C.byref(c), b"w8a32", C.byref(nf), C.byref(ni)) == 0
+    assert (nf.value, ni.value) == (322338752, 1455489024)
+    assert synthetic.blob_elements(DEEPSEEK_R1_1P5B) == 1777088064
+    assert lib.b200_blob_elements(C.byref(c), b"w4a16", C.byref(nf), C.byref(ni)) != 0
+
+
+def test_w8a32_split_sizes():
+    cfg = TINY_QWEN2
+    _, views = synthetic.make_f32_blob(cfg, 1)
+    fb, ib = synthetic.split_w8a32(
+        cfg, views, lambda W: (np.zeros(W.shape, np.int8), np.ones(W.shape[1], np.float32)))
+    lib = _lib.load()
+    c = cfg.to_c()
+    nf, ni = C.c_int64(), C.c_int64()
+    lib.b200_blob_elements(C.byref(c), b"w8a32", C.byref(nf), C.byref(ni))
+    assert (fb.size, ib.size) == (nf.value, ni.value)
+
+
+def test_argument_errors_are_reported():
+    lib = _lib.load()
+    assert lib.b200_pack_int4(None, 3, None, None) == -1
+    assert b"pack_int4" in lib.b200_last_error()
+    with pytest.raises(_lib.B200Error):
+        _lib.check(lib.b200_gemv(None, None, None))
+
+
+@pytest.mark.skipif(_has_gpu(), reason="only meaningful without a CUDA device")
+def test_no_cpu_fallback_without_a_device():
+    lib = _lib.load()
+    a = np.zeros(16, dtype=np.int8)
+    rc = lib.b200_unpack_int4(a.ctypes.data, 8, a.ctypes.data, None)
+    assert rc == -3 and b"no CUDA device" in lib.b200_last_error()
+    h = C.c_void_p()
+    c = TINY_QWEN2.to_c()
+    assert lib.b200_model_create(C.byref(c), C.byref(h)) == -3

@@ -1,0 +1,156 @@
+"""The CPU checker against everything that pins it: buddy-mlir's runnable
+known-answer examples, its own host headers compiled from source, the
+HuggingFace eager cross-check and the committed fixtures."""
+import os
+
+import numpy as np
+import pytest
+
+import oracle_lib as orc
+from buddy_mlir_b200 import TINY_QWEN2, TINY_QWEN3, synthetic
+
+G = os.path.join(os.path.dirname(__file__), "golden")
+
+
+def test_known_answer_w8_decode():
+    # examples/BuddyMatmul/dequant-matmul-vectorization-decode.mlir:93-133
+    k = np.load(os.path.join(G, "known_answers.npz"))
+    y = orc.gemv_w8_f32(k["w8_A"], k["w8_W"], k["w8_scale"])
+    assert np.array_equal(y, k["w8_expect"])
+
+
+def test_known_answer_w4_decode():
+    # examples/BuddyMatmul/int4-dequant-matmul-vectorization-decode.mlir:160-206
+    k = np.load(os.path.join(G, "known_answers.npz"))
+    y = orc.gemv_w4_f16(k["w4_A"], k["w4_P"], k["w4_scale"])
+    assert np.array_equal(y, k["w4_expect"])
+
+
+def test_known_answer_w8_prefill():
+    # examples/BuddyMatmul/dequant-matmul-vectorization-blis-prefill.mlir:113-115
+    k = np.load(os.path.join(G, "known_answers.npz"))
+    y = orc.gemm_w8_prefill_f32(k["pf_A"], k["pf_W"], k["pf_scale"], np.zeros((4, 4), np.float32))
+    assert np.array_equal(y, k["pf_expect"])
+
+
+def test_nibble_rules():
+    # import_model.py:810-815 and ops/tosa.py:12158-12203
+    vals = np.arange(-8, 8, dtype=np.int8)
+    flat = np.stack(np.meshgrid(vals, vals, indexing="ij"), -1).reshape(-1)
+    packed = orc.pack_int4(flat)
+    lo, hi = flat[0::2], flat[1::2]
+    assert np.array_equal(packed.view(np.uint8), (lo.view(np.uint8) & 0xF) | ((hi.view(np.uint8) & 0xF) << 4))
+    assert np.array_equal(orc.unpack_int4(packed), flat)
+
+
+def test_quantiser_matches_torch_statement():
+    # import_model.py:830-850 restated with torch, the library the reference uses
+    import torch
+    rng = np.random.default_rng(3)
+    W = (rng.standard_normal((64, 24)) * 0.02).astype(np.float32)
+    W[:, 5] = 0
+    t = torch.from_numpy(W)
+    for bits, qmax, lo, hi in ((8, 127.0, -128, 127), (4, 7.0, -8, 7)):
+        amax = t.abs().amax(dim=[0], keepdim=True)
+        scale = (amax / qmax).clamp(min=1e-10)
+        q = torch.clamp(torch.round(t / scale), lo, hi).to(torch.int8)
+        Q, s = orc.quantize_per_channel(W, bits)
+        assert np.array_equal(Q, q.numpy())
+        assert np.array_equal(s, scale.numpy().reshape(-1))
+
+
+def test_panel_packing_address_math():
+    # tests/Conversion/matmul-vectorization-decode-packed.mlir:18-28:
+    # flat offset = nIdx*K + k*V + v with nIdx = n0 (a multiple of V)
+    K, N, V = 64, 128, 32
+    B = np.arange(K * N, dtype=np.float32).reshape(K, N)
+    p = orc.pack_panels_f32(B, V)
+    for n in (0, 31, 32, 100, 127):
+        for k in (0, 1, 63):
+            n0 = n // V * V
+            assert p[n0 * K + k * V + n % V] == B[k, n]
+    x = np.random.default_rng(0).standard_normal(K).astype(np.float32)
+    assert np.array_equal(orc.gemv_f32_packed(x, p, K, N, V), orc.gemv_f32(x[None], B)[0])
+
+
+def test_greedy_tie_rule_against_reference_sampler():
+    ref = orc.ref_host()
+    rng = np.random.default_rng(5)
+    cases = [np.array([0, 3, 3, 1], np.float32)]
+    for _ in range(20):
+        v = rng.integers(0, 4, 257).astype(np.float32)
+        cases.append(v)
+    for v in cases:
+        mine = orc.argmax_first(v)
+        assert mine == int(np.argmax(v))
+        if ref is not None:
+            assert mine == ref.ref_greedy_sample(orc._p(v), orc.i64(v.size))
+    assert orc.argmax_first(cases[0]) == 1
+
+
+@pytest.mark.skipif(orc.ref_host() is None, reason="oracle/_ref was never built (no reference tree)")
+@pytest.mark.parametrize("position,keep", [(64, 16), (64, 0), (64, 63), (80, 16), (63, 16)])
+def test_kv_overflow_against_reference_headers(position, keep):
+    # KVCacheManager.h:151-273 driven as in gen_session.py:1471-1506
+    rng = np.random.default_rng(11)
+    nb, H, L, D = 4, 2, 64, 128
+    base = [rng.standard_normal((H, L, D)).astype(np.float32) for _ in range(nb)]
+    a = [b.copy() for b in base]
+    b = [b.copy() for b in base]
+    pa = orc.kv_overflow(a, H, L, D, position, keep, 10000.0)
+    pb = orc.kv_overflow(b, H, L, D, position, keep, 10000.0, use_ref=True)
+    assert pa == pb
+    for x, y in zip(a, b):
+        assert np.array_equal(x, y)
+
+
+@pytest.mark.parametrize("valid_len", [9, 37, 613, 1024])
+def test_attention_equals_two_pass_softmax(valid_len):
+    # the equivalence buddy-mlir checked by hand (ops/tosa.py:14075-14080)
+    g = np.load(os.path.join(G, "ops_golden.npz"))
+    q = g["at_q"]
+    K, V = g["at_K"].astype(np.float32), g["at_V"].astype(np.float32)
+    out = orc.gqa_decode(q, K, V, valid_len - 1)
+    assert np.array_equal(out, g[f"at_out_{valid_len}"])
+    for h in range(q.shape[0]):
+        s = (K[h // 6, :valid_len].astype(np.float64) @ q[h].astype(np.float64)) / np.sqrt(128.0)
+        p = np.exp(s - s.max())
+        ref = (p / p.sum()) @ V[h // 6, :valid_len].astype(np.float64)
+        assert np.abs(out[h] - ref).max() < 2e-6
+
+
+def test_ops_fixture_regression():
+    g = np.load(os.path.join(G, "ops_golden.npz"))
+    Q, s = orc.quantize_per_channel(g["q_W"], 8)
+    assert np.array_equal(Q, g["q8_Q"]) and np.array_equal(s, g["q8_s"])
+    assert s[3] == np.float32(1e-10)
+    Q4, s4 = orc.quantize_per_channel(g["q_W"], 4)
+    assert np.array_equal(Q4, g["q4_Q"]) and np.array_equal(orc.pack_int4(Q4).reshape(96, 20), g["q4_P"])
+    P, gs = orc.quantize_w4_group(g["g_W"], 128)
+    assert np.array_equal(P, g["g_P"]) and np.array_equal(gs, g["g_s"])
+    for tag in "abc":
+        assert np.array_equal(orc.gemv_w8_f32(g[f"w8{tag}_x"], g[f"w8{tag}_Q"], g[f"w8{tag}_s"]), g[f"w8{tag}_y"])
+        assert np.array_equal(orc.gemv_f32(g[f"w8{tag}_x"], g[f"f{tag}_B"]), g[f"f{tag}_y"])
+    assert np.array_equal(orc.gemv_w4_f16(g["w4_x"], g["w4_P"], g["w4_s"]), g["w4_y"])
+    assert np.array_equal(orc.gemv_w4g_f32(g["w4g_x"], g["g_P"], g["g_s"], 128), g["w4g_y"])
+    assert np.array_equal(orc.rmsnorm(g["rn_x"], g["rn_w"], 1e-6), g["rn_y"])
+    assert np.array_equal(orc.rope(g["rp_x"], g["rp_inv"], 613), g["rp_y"])
+    assert np.array_equal(orc.silu_mul(g["sm_g"], g["sm_u"]), g["sm_y"])
+
+
+def test_w8_gemv_is_dequantised_matmul():
+    g = np.load(os.path.join(G, "ops_golden.npz"))
+    x, Q, s = g["w8b_x"], g["w8b_Q"], g["w8b_s"]
+    ref = (x.astype(np.float64) @ Q.astype(np.float64)) * s.astype(np.float64)
+    assert np.abs(g["w8b_y"] - ref).max() / np.abs(ref).max() < 1e-5
+
+
+@pytest.mark.parametrize("cfg,name", [(TINY_QWEN2, "hf_tiny_qwen2.npz"), (TINY_QWEN3, "hf_tiny_qwen3.npz")])
+def test_model_against_huggingface_fixture(cfg, name):
+    f = np.load(os.path.join(G, name))
+    _, views = synthetic.make_f32_blob(cfg, int(f["seed_w"]))
+    om = orc.OracleModel(cfg, views)
+    for i, t in enumerate(f["tokens"]):
+        lo = om.decode(int(t))
+        assert np.abs(lo - f["logits"][i]).max() / np.abs(f["logits"][i]).max() < 1e-4
+        assert int(np.argmax(lo)) == int(np.argmax(f["logits"][i]))
