@@ -1,0 +1,318 @@
+#!/usr/bin/env python
+"""Decode-throughput bench of the buddy-mlir decode hot path on B200.
+
+    python bench.py --gpus 1 --steps 256 --warmup 8
+    python bench.py --impl reference --steps 64 --warmup 3
+
+N = 1 workload (the configuration the headline metric is quoted on): the
+DeepSeek-R1-Distill-Qwen-1.5B architecture with int8 per-output-channel
+weight-only quantisation of every linear layer, f32 activations, batch 1,
+greedy decode with the KV context growing to 1024 over the timed steps.  A
+"step" is one decode token.  Weights are seeded N(0, 0.02); KV rows before the
+first timed position are seeded N(0, 1) (no checkpoint, no dataset).
+
+N > 1 workload: the Qwen3-8B architecture with int4 group-128 weights,
+context 4096, tensor-parallel over the N GPUs (column-parallel q/k/v/gate/up,
+row-parallel o/down, NCCL all-reduce after each, vocab-sharded lm_head):
+strong scaling, one rank per GPU.
+
+`value` is tokens/s with everything resident in HBM (the device-resident
+greedy loop, CUDA events on the session's stream).  `e2e` is the same metric
+through the reference-facing entry `_mlir_ciface_forward_decode` with HOST
+buffers: token in, logits and the new KV rows back to host memory every step,
+greedy argmax on the host as buddy-mlir's runGeneration does.
+
+`--impl reference` times the CPU restatement of buddy-mlir's generated decode
+code (oracle/, OpenMP over the same 32-column tiles) on the host cores, same
+configuration; the reference's compiled path itself cannot be produced
+without its LLVM toolchain.
+"""
+import argparse
+import json
+import os
+import subprocess
+import sys
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+import numpy as np  # noqa: E402
+
+SEED_W, SEED_KV, SEED_P = 20260101, 5, 17
+ALL_LINEAR = ("q", "k", "v", "o", "gate", "up", "down", "lm_head")
+METRIC = "decode tokens/s (bs=1, ctx 1k)"
+
+
+def peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        d = json.load(open(p))
+        return float(d["hbm_gbs"]), "measured"
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index):
+        self.index = index
+        self.proc = None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(
+                ["nvidia-smi", "-i", str(self.index), f"--query-gpu={self.Q}",
+                 "--format=csv,noheader,nounits", "-lms", "100"],
+                stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            self.proc = None
+
+    def stop(self):
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        time.sleep(0.15)
+        self.proc.terminate()
+        out, _ = self.proc.communicate(timeout=5)
+        sm, mx, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for line in out.strip().splitlines():
+            f = [x.strip() for x in line.split(",")]
+            if len(f) < 6:
+                continue
+            try:
+                sm.append(float(f[0]))
+                mx.append(float(f[1]))
+            except ValueError:
+                continue
+            for n, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(n)
+        return {"sm_mhz": float(np.median(sm)) if sm else None,
+                "sm_max_mhz": max(mx) if mx else None, "reasons": sorted(reasons),
+                "samples": len(sm)}
+
+
+def kv_prefix(cfg, n_pos, buffer):
+    rng = np.random.default_rng([SEED_KV, buffer])
+    a = np.zeros((cfg.kv_heads, cfg.max_len, cfg.head_dim), dtype=np.float32)
+    a[:, :n_pos] = rng.standard_normal((cfg.kv_heads, n_pos, cfg.head_dim)).astype(np.float32)
+    return a
+
+
+def plan_positions(cfg, steps, warmup):
+    if steps + warmup > cfg.max_len:
+        raise SystemExit(f"--steps + --warmup must be <= {cfg.max_len}")
+    return cfg.max_len - steps - warmup
+
+
+# ------------------------------------------------------------------------------
+def cpu_baseline(cfg, views, start, budget_s=12.0, max_steps=64, warm=2):
+    """The CPU restatement (oracle/) on the host cores: a bounded sample of the
+    same workload."""
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as orc
+    om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in ALL_LINEAR})
+    for b in range(2 * cfg.n_layers):
+        om.kv[b][:] = kv_prefix(cfg, start, b)
+    om.position = start
+    tok = 11
+    for _ in range(warm):
+        tok = int(np.argmax(om.decode(tok)))
+    t0, n = time.perf_counter(), 0
+    while n < max_steps and time.perf_counter() - t0 < budget_s and om.position < cfg.max_len:
+        tok = int(np.argmax(om.decode(tok)))
+        n += 1
+    dt = time.perf_counter() - t0
+    return {"value": n / dt, "unit": "tokens/s", "cores": orc.lib().orc_num_threads(),
+            "kind": "port",
+            "sample": f"{n} decode steps of the same int8 1.5B model from context {start + warm} "
+                      f"({dt:.1f} s, after {warm} warm-up steps)"}
+
+
+def run_reference(args):
+    """--impl reference: the CPU restatement timed alone, same config."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, synthetic
+    sys.path.insert(0, os.path.join(ROOT, "tests"))
+    import oracle_lib as orc
+    _, views = synthetic.make_f32_blob(cfg, SEED_W)
+    start = plan_positions(cfg, args.steps, args.warmup)
+    om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in ALL_LINEAR})
+    for b in range(2 * cfg.n_layers):
+        om.kv[b][:] = kv_prefix(cfg, start, b)
+    om.position = start
+    tok = 11
+    for _ in range(args.warmup):
+        tok = int(np.argmax(om.decode(tok)))
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        tok = int(np.argmax(om.decode(tok)))
+    dt = time.perf_counter() - t0
+    v = args.steps / dt
+    cores = orc.lib().orc_num_threads()
+    line = {"impl": "reference", "metric": METRIC, "value": v, "unit": "tokens/s",
+            "n_gpus": args.gpus, "steps": args.steps, "warmup": args.warmup,
+            "ms_per_step": 1000.0 * dt / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, int8 weights",
+            "data": "synthetic",
+            "config": workload_config(cfg, start, args),
+            "cpu_baseline": {"value": v, "unit": "tokens/s", "cores": cores, "kind": "port",
+                             "sample": f"{args.steps} decode steps, context {start + args.warmup}..{cfg.max_len}"},
+            "e2e": {"value": v, "unit": "tokens/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "gpu_launches": 0}
+    print(json.dumps(line))
+
+
+def workload_config(cfg, start, args):
+    return {"workload": "deepseek-r1-distill-qwen-1.5b architecture, int8 per-output-channel weight-only "
+                        "(all linear layers), f32 activations, batch 1, greedy decode",
+            "context": f"{start + args.warmup}..{cfg.max_len}", "l2": "inputs larger than L2 (1.55 GB of weights per step)",
+            "weights": "seeded N(0,0.02)", "kv_prefix": "seeded N(0,1)"}
+
+
+def gemv_microbench(lib):
+    """Isolated int8 GEMV launches over weights that do not fit L2, CUDA events
+    on the launching (current) stream."""
+    import ctypes as C
+    import torch
+    from buddy_mlir_b200 import _lib
+    out = {}
+    hbm, _ = peaks()
+    for name, N, K in (("gate_up", 17920, 1536), ("down", 1536, 8960), ("o", 1536, 1536),
+                       ("lm_head", 151936, 1536)):
+        copies = max(2, int(400e6 // (N * K)) + 1)
+        ws = [torch.randint(-127, 128, (N * K,), dtype=torch.int8, device="cuda") for _ in range(copies)]
+        sc = torch.rand(N, device="cuda") * 0.01
+        x = torch.randn(1, K, device="cuda")
+        y = torch.zeros(1, N, device="cuda")
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def launch(i):
+            w = _lib.Weight(_lib.W_I8, 0, K, N, ws[i % copies].data_ptr(), sc.data_ptr(), _lib.F32, 0, None)
+            a = _lib.GemvArgs(x.data_ptr(), 0, 0, 0, 0, y.data_ptr(), None, None, 0.0, 1, 0, 0)
+            _lib.check(lib.b200_gemv(C.byref(w), C.byref(a), st))
+        for i in range(copies):
+            launch(i)
+        torch.cuda.synchronize()
+        reps = 4 * copies
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize()
+        us = e0.elapsed_time(e1) * 1000.0 / reps
+        gbs = (N * K + 4 * N + 4 * K + 4 * N) / us / 1e3
+        out[name] = {"N": N, "K": K, "us": round(us, 2), "GB/s": round(gbs, 1), "frac": round(gbs / hbm, 3)}
+    return out
+
+
+def run_single(args):
+    import torch
+    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, _lib, synthetic
+    from buddy_mlir_b200.model_entry import EntrySession
+    from buddy_mlir_b200.session import ModelSession
+    lib = _lib.load()          # raises if the CUDA library is missing: no fallback
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    steps, warmup = args.steps, args.warmup
+    start = plan_positions(cfg, steps, warmup)
+    t_setup = time.perf_counter()
+    blob, views = synthetic.make_f32_blob(cfg, SEED_W)
+
+    # ---- resident-in-HBM number ------------------------------------------------
+    s = ModelSession(cfg)
+    s.load_blobs("f32", blob, all_linear_w8=True)
+    for b in range(2 * cfg.n_layers):
+        s.kv_upload(b, kv_prefix(cfg, start, b), 0, start)
+    s.position_ = start
+    tok = 11
+    warm_ids = s.generate(tok, warmup) if warmup > 0 else [tok]
+    tok = int(warm_ids[-1])
+    torch.cuda.synchronize()
+    sampler = ClockSampler(0)
+    sampler.start()
+    time.sleep(0.3)
+    launches0 = lib.b200_launch_count()
+    ids = s.generate(tok, steps)
+    ms = s.last_ms()
+    launches = lib.b200_launch_count() - launches0
+    clocks = sampler.stop()
+    value = steps / (ms / 1000.0)
+    ctx_mid = cfg.max_len - steps // 2
+    step_bytes = s.step_bytes(ctx_mid)
+    hbm, which = peaks()
+    achieved = step_bytes / (ms / steps) / 1e6        # GB/s
+    traffic = None
+    tpath = os.path.join(ROOT, "profiles", "decode_step_traffic.json")
+    if os.path.exists(tpath):
+        traffic = json.load(open(tpath)).get("dram_bytes_per_step")
+    gemv = gemv_microbench(lib)
+    s.close()
+
+    # ---- end to end through the model entry, host buffers --------------------------
+    es = EntrySession(cfg, "f32", [blob], all_linear_w8=True)
+    for b in range(2 * cfg.n_layers):
+        es.kv[b][0] = kv_prefix(cfg, start, b)
+    es.position_ = start
+    tok = 11
+    for _ in range(warmup):
+        es.decode(tok)
+        tok = int(np.argmax(es.logits))
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e2e_ids = []
+    for _ in range(steps):
+        es.decode(tok)
+        tok = int(np.argmax(es.logits))
+        e2e_ids.append(tok)
+    torch.cuda.synchronize()
+    e2e_dt = time.perf_counter() - t0
+    es.close()
+    same = bool(np.array_equal(np.asarray(e2e_ids), np.asarray(ids)))
+    d2h = cfg.vocab * 4 + 2 * cfg.n_layers * cfg.kv_heads * cfg.head_dim * 4
+    setup_s = time.perf_counter() - t_setup
+
+    base = cpu_baseline(cfg, views, start)
+    line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps,
+            "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, int8 weights",
+            "data": "synthetic", "config": workload_config(cfg, start, args),
+            "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
+                         "frac": achieved / hbm, "traffic": traffic, "peak_source": which,
+                         "kernel": "whole decode step (CUDA graph replay)",
+                         "bytes_per_step": step_bytes, "frac_of_8TBs_nominal": achieved / 8000.0},
+            "gemv_int8_isolated": gemv,
+            "cpu_baseline": base,
+            "e2e": {"value": steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": 16,
+                    "d2h_bytes_per_step": d2h, "tokens_match_resident_run": same},
+            "gpu_launches": int(launches), "kernels_per_step": int(launches // steps),
+            "clocks": clocks, "setup_s": round(setup_s, 1)}
+    print(json.dumps(line))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=256)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        return run_reference(args)
+    if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
+        return run_single(args)
+    from buddy_mlir_b200 import tp_bench
+    return tp_bench.run(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -1,0 +1,81 @@
+"""Host harness that drives a model-entry shim the way buddy-mlir's generated
+ModelSession does: dlopen the model .so, dlsym `_mlir_ciface_forward_decode`,
+own the KV cache and logits on the HOST, and call the entry with MemRef
+descriptors (tools/buddy-codegen/gen_session.py:1106-1141, 1176-1294,
+1381-1452).  buddy-cli itself cannot be linked here (it needs LLVMSupport and
+FlatBuffers), so this is the closest stand-in for the reference's host."""
+import ctypes as C
+import os
+
+import numpy as np
+
+from . import _lib
+from .config import ModelConfig
+from .gen_model_entry import HERE, build, shim_name
+from .memref import _libc, memref_type, to_memref
+
+
+class EntrySession:
+    def __init__(self, cfg: ModelConfig, variant: str, blobs, all_linear_w8: bool = False):
+        _lib.load()
+        so = os.path.join(HERE, shim_name(cfg, variant, all_linear_w8))
+        if not os.path.exists(so):
+            build(cfg, variant, all_linear_w8)
+        self.dll = C.CDLL(so)          # RTLD_LOCAL, like ModelSession::Impl::loadSo
+        self.fn = self.dll._mlir_ciface_forward_decode
+        self.fn.restype = None
+        self.cfg = cfg
+        self.blobs = [np.ascontiguousarray(b) for b in blobs]
+        self.blob_desc = [to_memref(b) for b in self.blobs]
+        kvs = (1, cfg.kv_heads, cfg.max_len, cfg.head_dim)
+        self.kv = [np.zeros(kvs, dtype=np.float32) for _ in range(2 * cfg.n_layers)]
+        self.kv_desc = [to_memref(k) for k in self.kv]
+        self.token = np.zeros((1, 1), dtype=np.int64)
+        self.cache_position = np.zeros(1, dtype=np.int64)
+        self.dummies = [np.zeros(1, dtype=np.int64) for _ in range(cfg.n_layers - 1)]
+        self.logits = np.zeros(cfg.vocab, dtype=np.float32)
+        self.position_ = 0
+        # DecodeABI: cache_position_out, kv0, kv1, (dummy_i, kv, kv)*, logits
+        I1, K4, L3 = memref_type(np.int64, 1), memref_type(np.float32, 4), memref_type(np.float32, 3)
+        fields = [("cache_position_out", I1), ("kv0", K4), ("kv1", K4)]
+        for i in range(cfg.n_layers - 1):
+            fields += [(f"dummy{i}", I1), (f"kv{2 + 2 * i}", K4), (f"kv{3 + 2 * i}", K4)]
+        fields.append(("logits", L3))
+        self.ABI = type("DecodeABI", (C.Structure,), {"_fields_": fields})
+        # descriptors are built once; decode() only rewrites the scalars
+        self._tok_d, self._pos_d = to_memref(self.token), to_memref(self.cache_position)
+        self._dum_d = [to_memref(d) for d in self.dummies]
+        self._result = self.ABI()
+        args = [C.byref(self._result)] + [C.byref(d) for d in self.blob_desc]
+        args += [C.byref(self._tok_d), C.byref(self._pos_d), C.byref(self.kv_desc[0]),
+                 C.byref(self.kv_desc[1])]
+        for i in range(cfg.n_layers - 1):
+            args += [C.byref(self._dum_d[i]), C.byref(self.kv_desc[2 + 2 * i]),
+                     C.byref(self.kv_desc[3 + 2 * i])]
+        self._args = args
+        self.fn.argtypes = None
+
+    def decode(self, token_id: int, check_alias: bool = False):
+        self.token[0, 0] = token_id
+        self.cache_position[0] = self.position_
+        for d in self.dummies:
+            d[0] = self.position_
+        result = self._result
+        self.fn(*self._args)
+        if not result.logits.aligned:
+            raise _lib.B200Error(_lib.load().b200_last_error().decode())
+        # gen_session.py:1416-1442: copy the logits out, KV results alias the state
+        src = np.ctypeslib.as_array(result.logits.aligned, shape=(self.cfg.vocab,))
+        np.copyto(self.logits, src)
+        _libc.free(C.cast(result.logits.allocated, C.c_void_p))
+        if check_alias:
+            for i, k in enumerate(self.kv):
+                got = getattr(result, f"kv{i}")
+                assert C.addressof(got.aligned.contents) == k.ctypes.data
+        self.position_ += 1
+
+    def reset_position(self):
+        self.position_ = 0
+
+    def close(self):
+        _lib.load().b200_forward_reset()

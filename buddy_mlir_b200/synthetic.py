@@ -50,22 +50,40 @@ def inv_freq(cfg: ModelConfig):
     return (np.float32(1.0) / np.power(np.float32(cfg.rope_theta), j)).astype(np.float32)
 
 
+_CHUNK = 1 << 24
+
+
+def _fill_normal(blob, seed):
+    """blob[:] = N(0,1) from `seed`, in fixed 16 Mi-element chunks, each chunk
+    from its own spawned PCG64 stream so the fill can use every host core and
+    still depends on nothing but the seed."""
+    from concurrent.futures import ThreadPoolExecutor
+    import os
+    n_chunks = (blob.size + _CHUNK - 1) // _CHUNK
+    streams = np.random.SeedSequence(seed).spawn(n_chunks)
+
+    def work(i):
+        v = blob[i * _CHUNK:(i + 1) * _CHUNK]
+        np.random.Generator(np.random.PCG64(streams[i])).standard_normal(
+            v.size, dtype=np.float32, out=v)
+    with ThreadPoolExecutor(max_workers=min(32, os.cpu_count() or 1)) as ex:
+        list(ex.map(work, range(n_chunks)))
+
+
 def make_f32_blob(cfg: ModelConfig, seed: int):
     """Returns (blob, views): blob is one float32 array, views maps
     (name, layer) -> the tensor as a view into the blob."""
-    rng = np.random.default_rng(seed)
     blob = np.empty(blob_elements(cfg), dtype=np.float32)
+    _fill_normal(blob, seed)
+    blob *= np.float32(0.02)
     views, off = {}, 0
     for name, layer, shape in tensor_list(cfg):
         n = int(np.prod(shape))
         v = blob[off:off + n]
         if name == "inv_freq":
             v[:] = inv_freq(cfg)
-        else:
-            rng.standard_normal(n, dtype=np.float32, out=v)
-            v *= np.float32(0.02)
-            if name.endswith("norm"):
-                v += np.float32(1.0)
+        elif name.endswith("norm"):
+            v += np.float32(1.0)
         views[(name, layer)] = v.reshape(shape)
         off += n
     return blob, views
