@@ -51,3 +51,6 @@ QWEN3_8B = ModelConfig("qwen3_8b", 4096, 36, 32, 8, 128, 12288, 151936, 4096,
 TINY_QWEN2 = ModelConfig("tiny_qwen2", 256, 2, 4, 2, 64, 512, 1024, 128)
 TINY_QWEN3 = ModelConfig("tiny_qwen3", 256, 2, 8, 2, 128, 512, 1024, 128,
                          qkv_bias=False, qk_norm=True)
+# Small shapes that still reach both row modes of the persistent decode kernel
+# (K = 512 and 1536 warp-per-row; K = 2112 shared rows with a ragged last block).
+TINY_MEGA = ModelConfig("tiny_mega", 512, 2, 12, 2, 128, 2112, 2048, 256)

@@ -11,10 +11,12 @@
 // q/k/v/gate/up, row-parallel o/down, sum after each, vocab-sharded lm_head;
 // buddy-deepseek-r1-distributed.cpp:521-617) with NCCL in place of MPI.
 #include "common.cuh"
+#include "mega.cuh"
 
 #include <dlfcn.h>
 
 #include <cmath>
+#include <cstdlib>
 #include <cstring>
 #include <string>
 #include <vector>
@@ -152,7 +154,7 @@ struct b200_model {
         *part = nullptr, *logits = nullptr, *logits_shard = nullptr;
   float *attn_scratch = nullptr, *argmax_scratch = nullptr;
   float *kv_stage = nullptr;  // [2*layers][kv_heads*D]: the rows written this step
-  int32_t *d_state = nullptr;  // token, pos, next, count
+  int32_t *d_state = nullptr;  // token, pos, next, count, launches, -, error, -
   int32_t *d_history = nullptr;
   int history_cap = 0;
   int splits = 1;
@@ -165,6 +167,19 @@ struct b200_model {
   bool finalized = false;
   float *h_logits_pinned = nullptr;
   int32_t *h_state_pinned = nullptr;
+  // persistent decode-step kernel (batch 1, int8): see mega.cu
+  bool mega = false;
+  MegaParams mp{};
+  int mega_grid = 0;
+  size_t mega_smem = 0;
+  int64_t mega_stream_bytes = 0;
+  uint8_t *mega_stream = nullptr;
+  int64_t *mega_offsets = nullptr;   // [(4L+1)+1][grid]: per-phase and per-CTA stream offsets
+  const float **lvec_dev = nullptr;
+  float *xa = nullptr, *xb = nullptr, *gu = nullptr, *cand_val = nullptr;
+  int *cand_idx = nullptr;
+  unsigned *d_barrier = nullptr;
+  long long *d_trace = nullptr;
 };
 
 namespace {
@@ -338,6 +353,189 @@ int issue_step(b200_model *m, int *n_kernels) {
   return B200_OK;
 }
 
+
+// ---- persistent-kernel path ------------------------------------------------------
+void rows_of_host(int N, int cta, int grid, int &begin, int &count) {
+  const int base = N / grid, rem = N % grid;
+  begin = cta * base + (cta < rem ? cta : rem);
+  count = base + (cta < rem ? 1 : 0);
+}
+
+bool mega_eligible(const b200_model *m, const Layer &L0) {
+  const char *env = std::getenv("BUDDY_B200_DECODE");
+  if (env && !strcmp(env, "graph"))
+    return false;
+  const b200_model_config &c = m->cfg;
+  if (m->tp != 1 || c.head_dim != 128)
+    return false;
+  const int G = c.q_heads / c.kv_heads;
+  if (G != 1 && G != 2 && G != 4 && G != 6 && G != 8)
+    return false;
+  auto ok = [](const DevLinear &l) {
+    return l.set && l.w.kind == B200_W_I8 && l.w.scale_dtype == B200_F32 && l.w.K % 16 == 0 &&
+           l.w.K <= 12288;
+  };
+  for (const auto &L : m->layers)
+    if (!ok(L.qkv) || !ok(L.o) || !ok(L.gate) || !ok(L.up) || !ok(L.down))
+      return false;
+  (void)L0;
+  return ok(m->lm_head);
+}
+
+int build_mega(b200_model *m) {
+  const b200_model_config &c = m->cfg;
+  int dev = 0, sms = 0, coop = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  B200_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
+  if (!coop || sms < c.kv_heads)
+    return B200_OK;  // stays on the graph path
+  const int grid = sms, L = c.n_layers, D = c.head_dim;
+  const int H = c.hidden, QD = c.q_heads * D, KD = c.kv_heads * D, F = c.ffn, V = c.vocab;
+  MegaParams &p = m->mp;
+  const int Ks[5] = {H, QD, H, F, H}, Ns[5] = {QD + 2 * KD, H, 2 * F, H, V};
+  int slot_bytes = 0;
+  for (int i = 0; i < 5; ++i) {
+    MegaPhase &ph = p.phase[i];
+    ph.K = Ks[i];
+    ph.N = Ns[i];
+    ph.row_bytes = Ks[i] + kMegaTrailer;
+    ph.mode = Ks[i] <= 1536 ? 0 : 1;
+    if (ph.mode == 0) {
+      ph.rps = 16;   // two rows per consumer warp
+    } else {
+      ph.rps = 25000 / ph.row_bytes;
+      if (ph.rps < 1) ph.rps = 1;
+      if (ph.rps > 8) ph.rps = 8;
+    }
+    if (ph.rps * ph.row_bytes > slot_bytes)
+      slot_bytes = ph.rps * ph.row_bytes;
+  }
+  slot_bytes = (slot_bytes + 127) / 128 * 128;
+  int slots = (int)((227 * 1024 - mega_shared_bytes(0, 0) - 1024) / slot_bytes);
+  if (slots > kMegaMaxSlots) slots = kMegaMaxSlots;
+  if (slots < 3)
+    return B200_OK;
+  // per-phase, per-CTA stream offsets
+  const int nph = 4 * L + 1;
+  std::vector<int64_t> table((size_t)(nph + 1) * grid);
+  int64_t total = 0;
+  for (int cta = 0; cta < grid; ++cta) {
+    table[(size_t)nph * grid + cta] = total;  // start of this CTA's stream
+    for (int i = 0; i < nph; ++i) {
+      const MegaPhase &ph = p.phase[i < 4 * L ? i % 4 : 4];
+      int b, n;
+      rows_of_host(ph.N, cta, grid, b, n);
+      table[(size_t)i * grid + cta] = total;
+      total += (int64_t)n * ph.row_bytes;
+    }
+  }
+  if (int rc = dev_alloc((void **)&m->mega_stream, total)) return rc;
+  if (int rc = dev_alloc((void **)&m->mega_offsets, table.size() * 8)) return rc;
+  B200_CUDA(cudaMemcpy(m->mega_offsets, table.data(), table.size() * 8, cudaMemcpyHostToDevice));
+  cudaStream_t st = m->stream;
+  for (int l = 0; l < L; ++l) {
+    Layer &Ly = m->layers[l];
+    const int64_t *o0 = m->mega_offsets + (size_t)(4 * l) * grid;
+    if (int rc = mega_build_rows(Ly.qkv.w_buf, H, Ns[0], 0, Ns[0], (const float *)Ly.qkv.scale_buf,
+                                 Ly.qkv.bias_buf, grid, p.phase[0].row_bytes, o0, m->mega_stream, st))
+      return rc;
+    if (int rc = mega_build_rows(Ly.o.w_buf, QD, H, 0, H, (const float *)Ly.o.scale_buf, nullptr, grid,
+                                 p.phase[1].row_bytes, o0 + grid, m->mega_stream, st))
+      return rc;
+    if (int rc = mega_build_rows(Ly.gate.w_buf, H, F, 0, 2 * F, (const float *)Ly.gate.scale_buf, nullptr,
+                                 grid, p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
+      return rc;
+    if (int rc = mega_build_rows(Ly.up.w_buf, H, F, F, 2 * F, (const float *)Ly.up.scale_buf, nullptr, grid,
+                                 p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
+      return rc;
+    if (int rc = mega_build_rows(Ly.down.w_buf, F, H, 0, H, (const float *)Ly.down.scale_buf, nullptr, grid,
+                                 p.phase[3].row_bytes, o0 + 3 * grid, m->mega_stream, st))
+      return rc;
+  }
+  if (int rc = mega_build_rows(m->lm_head.w_buf, H, V, 0, V, (const float *)m->lm_head.scale_buf, nullptr,
+                               grid, p.phase[4].row_bytes, m->mega_offsets + (size_t)(4 * L) * grid,
+                               m->mega_stream, st))
+    return rc;
+  std::vector<const float *> lvec(4 * L);
+  for (int l = 0; l < L; ++l) {
+    lvec[4 * l] = m->layers[l].in_norm;
+    lvec[4 * l + 1] = m->layers[l].post_norm;
+    lvec[4 * l + 2] = m->layers[l].q_norm;
+    lvec[4 * l + 3] = m->layers[l].k_norm;
+  }
+  if (int rc = dev_alloc((void **)&m->lvec_dev, lvec.size() * sizeof(float *))) return rc;
+  B200_CUDA(cudaMemcpy(m->lvec_dev, lvec.data(), lvec.size() * sizeof(float *), cudaMemcpyHostToDevice));
+  if (int rc = dev_alloc((void **)&m->xa, H * 4)) return rc;
+  if (int rc = dev_alloc((void **)&m->xb, H * 4)) return rc;
+  if (int rc = dev_alloc((void **)&m->gu, (size_t)2 * F * 4)) return rc;
+  if (int rc = dev_alloc((void **)&m->cand_val, grid * 4)) return rc;
+  if (int rc = dev_alloc((void **)&m->cand_idx, grid * 4)) return rc;
+  if (int rc = dev_alloc((void **)&m->d_barrier, 4)) return rc;
+  B200_CUDA(cudaMemset(m->d_barrier, 0, 4));
+  p.stream = m->mega_stream;
+  p.cta_off = m->mega_offsets + (size_t)nph * grid;
+  p.H = H; p.F = F; p.V = V; p.D = D; p.qh = c.q_heads; p.kvh = c.kv_heads; p.L = L;
+  p.max_len = c.max_len;
+  p.splits = grid / c.kv_heads;
+  if (p.splits > 16) p.splits = 16;
+  p.slots = slots;
+  p.slot_bytes = slot_bytes;
+  p.eps = c.eps;
+  p.embed = m->embed; p.inv_freq = m->inv_freq; p.final_norm = m->final_norm;
+  p.lvec = m->lvec_dev;
+  p.kv = m->kv_dev;
+  p.xa = m->xa; p.xb = m->xb; p.qkv = m->qkv; p.attn = m->attn; p.gu = m->gu; p.logits = m->logits;
+  p.kv_stage = m->kv_stage;
+  p.state = m->d_state;
+  p.history = m->d_history;
+  p.history_cap = m->history_cap;
+  p.cand_val = m->cand_val; p.cand_idx = m->cand_idx;
+  p.barrier = m->d_barrier;
+  p.error = m->d_state + 6;
+  p.trace = nullptr;
+  p.trace_stride = 1;
+  if (const char *t = std::getenv("BUDDY_B200_TRACE")) {
+    p.trace_stride = std::atoi(t) > 0 ? std::atoi(t) : 1;
+    const size_t n = (size_t)(grid / p.trace_stride + 1) * (L + 1) * 12;
+    if (int rc = dev_alloc((void **)&m->d_trace, n * 8)) return rc;
+    B200_CUDA(cudaMemset(m->d_trace, 0, n * 8));
+    p.trace = m->d_trace;
+  }
+  // split partials + counters for the persistent kernel's own split count
+  cudaFree(m->attn_scratch);
+  m->attn_scratch = nullptr;
+  const int64_t sf = b200_gqa_scratch_floats(c.q_heads, D, p.splits > m->splits ? p.splits : m->splits);
+  if (int rc = dev_alloc((void **)&m->attn_scratch, sf * 4)) return rc;
+  B200_CUDA(cudaMemset(m->attn_scratch, 0, sf * 4));
+  p.attn_part = m->attn_scratch;
+  p.attn_count = reinterpret_cast<unsigned *>(m->attn_scratch + (size_t)c.q_heads * p.splits * (D + 2));
+  m->mega_grid = grid;
+  m->mega_smem = mega_shared_bytes(slots, slot_bytes);
+  m->mega_stream_bytes = total;
+  B200_CUDA(cudaStreamSynchronize(st));
+  m->mega = true;
+  return B200_OK;
+}
+
+int run_step(b200_model *m) {
+  if (m->mega)
+    return mega_launch(m->mp, m->mega_grid, m->mega_smem, m->stream);
+  B200_CUDA(cudaGraphLaunch(m->exec, m->stream));
+  count_launch(m->kernels_per_step);
+  return B200_OK;
+}
+
+int check_step_error(b200_model *m) {
+  // h_state_pinned holds the 8 state words read back after the step
+  if (m->h_state_pinned[6] != 0) {
+    const int code = m->h_state_pinned[6];
+    cudaMemsetAsync(m->d_state + 6, 0, 4, m->stream);
+    return fail(B200_ECUDA, "decode step kernel gave up on a bounded wait (code %d)", code);
+  }
+  return B200_OK;
+}
+
 int set_state(b200_model *m, int token, int pos) {
   m->h_state_pinned[0] = token;
   m->h_state_pinned[1] = pos;
@@ -439,7 +637,7 @@ int b200_model_create(const b200_model_config *cfg, b200_model **out) {
   A((void **)&m->attn_scratch, b200_gqa_scratch_floats(m->qh, D, m->splits) * 4);
   A((void **)&m->argmax_scratch, 2048 * 4);
   A((void **)&m->kv_stage, (size_t)2 * c.n_layers * m->kvh * D * 4);
-  A((void **)&m->d_state, 4 * sizeof(int32_t));
+  A((void **)&m->d_state, 8 * sizeof(int32_t));
   A((void **)&m->d_history, m->history_cap * sizeof(int32_t));
   if (rc == B200_OK &&
       cudaMemcpy(m->kv_dev, m->kv.data(), m->kv.size() * sizeof(float *),
@@ -450,7 +648,7 @@ int b200_model_create(const b200_model_config *cfg, b200_model **out) {
   if (rc == B200_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
     rc = fail(B200_ECUDA, "event create failed");
   if (rc == B200_OK && (cudaMallocHost((void **)&m->h_logits_pinned, (size_t)c.vocab * 4) != cudaSuccess ||
-                        cudaMallocHost((void **)&m->h_state_pinned, 16) != cudaSuccess))
+                        cudaMallocHost((void **)&m->h_state_pinned, 32) != cudaSuccess))
     rc = fail(B200_ENOMEM, "pinned host allocation failed");
   if (rc != B200_OK) {
     b200_model_destroy(m);
@@ -478,6 +676,9 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->part); cudaFree(m->logits); cudaFree(m->logits_shard);
   cudaFree(m->attn_scratch); cudaFree(m->argmax_scratch); cudaFree(m->kv_stage);
   cudaFree(m->d_state); cudaFree(m->d_history);
+  cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
+  cudaFree(m->xa); cudaFree(m->xb); cudaFree(m->gu); cudaFree(m->cand_val);
+  cudaFree(m->cand_idx); cudaFree(m->d_barrier); cudaFree(m->d_trace);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
   if (m->ev0) cudaEventDestroy(m->ev0);
@@ -782,7 +983,24 @@ int b200_model_finalize(b200_model *m) {
       return fail(B200_ESTATE, "finalize: layer %d lacks q_norm/k_norm", l);
     if (int rc = fuse_linears({&L.q, &L.k, &L.v}, false, &L.qkv, m->stream)) return rc;
     if (int rc = fuse_linears({&L.gate, &L.up}, true, &L.gateup, m->stream)) return rc;
-    L.q.release(); L.k.release(); L.v.release(); L.gate.release(); L.up.release();
+    L.q.release(); L.k.release(); L.v.release();
+  }
+  if (mega_eligible(m, m->layers[0]))
+    if (int rc = build_mega(m)) return rc;
+  for (auto &L : m->layers) { L.gate.release(); L.up.release(); }
+  if (m->mega) {
+    // warm the kernel once (shared-memory attribute, module load), then clear the row it wrote
+    if (int rc = set_state(m, 0, 0)) return rc;
+    if (int rc = run_step(m)) return rc;
+    B200_CUDA(cudaMemcpyAsync(m->h_state_pinned, m->d_state, 32, cudaMemcpyDeviceToHost, m->stream));
+    B200_CUDA(cudaStreamSynchronize(m->stream));
+    if (int rc = check_step_error(m)) return rc;
+    for (auto p : m->kv)
+      B200_CUDA(cudaMemsetAsync(p, 0, (size_t)m->kvh * c.max_len * c.head_dim * 4, m->stream));
+    B200_CUDA(cudaStreamSynchronize(m->stream));
+    m->kernels_per_step = 1;
+    m->finalized = true;
+    return B200_OK;
   }
   // Warm every kernel once outside capture (sets shared-memory attributes),
   // then capture the step.
@@ -848,17 +1066,15 @@ int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
     return fail(B200_EINVAL, "decode: token %d / position %d out of range", token, pos);
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
-  B200_CUDA(cudaGraphLaunch(m->exec, m->stream));
-  count_launch(m->kernels_per_step);
+  if (int rc = run_step(m)) return rc;
   B200_CUDA(cudaEventRecord(m->ev1, m->stream));
   if (logits_host)
     B200_CUDA(cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->cfg.vocab * 4,
                               cudaMemcpyDeviceToHost, m->stream));
-  if (next_token)
-    B200_CUDA(cudaMemcpyAsync(m->h_state_pinned + 2, m->d_state + 2, 4,
-                              cudaMemcpyDeviceToHost, m->stream));
+  B200_CUDA(cudaMemcpyAsync(m->h_state_pinned, m->d_state, 32, cudaMemcpyDeviceToHost, m->stream));
   B200_CUDA(cudaStreamSynchronize(m->stream));
   B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+  if (int rc = check_step_error(m)) return rc;
   if (logits_host)
     memcpy(logits_host, m->h_logits_pinned, (size_t)m->cfg.vocab * 4);
   if (next_token)
@@ -879,14 +1095,14 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   for (int s = 0; s < steps; ++s)
-    B200_CUDA(cudaGraphLaunch(m->exec, m->stream));
-  count_launch((uint64_t)m->kernels_per_step * steps);
+    if (int rc = run_step(m)) return rc;
   B200_CUDA(cudaEventRecord(m->ev1, m->stream));
   B200_CUDA(cudaMemcpyAsync(tokens_out, m->d_history, (size_t)steps * 4,
                             cudaMemcpyDeviceToHost, m->stream));
+  B200_CUDA(cudaMemcpyAsync(m->h_state_pinned, m->d_state, 32, cudaMemcpyDeviceToHost, m->stream));
   B200_CUDA(cudaStreamSynchronize(m->stream));
   B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
-  return B200_OK;
+  return check_step_error(m);
 }
 
 int b200_model_read_new_kv_rows(b200_model *m, float *host) {
@@ -903,6 +1119,17 @@ float b200_model_last_ms(const b200_model *m) { return m ? m->last_ms : 0.f; }
 int b200_model_kernels_per_step(const b200_model *m) { return m ? m->kernels_per_step : 0; }
 float *b200_model_kv_ptr(b200_model *m, int buffer) {
   return (m && buffer >= 0 && buffer < (int)m->kv.size()) ? m->kv[buffer] : nullptr;
+}
+
+int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega ? 1 : 0; }
+
+int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity) {
+  if (!m || !host || !m->d_trace)
+    return fail(B200_ESTATE, "read_trace: tracing is off (set BUDDY_B200_TRACE=<cta stride>)");
+  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * 12;
+  B200_CUDA(cudaMemcpy(host, m->d_trace, (size_t)(n < capacity ? n : capacity) * 8,
+                       cudaMemcpyDeviceToHost));
+  return (int)(n < capacity ? n : capacity);
 }
 
 int64_t b200_model_step_bytes(const b200_model *m, int ctx) {

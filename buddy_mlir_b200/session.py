@@ -170,6 +170,9 @@ class ModelSession:
     def kernels_per_step(self) -> int:
         return int(self.lib.b200_model_kernels_per_step(self._h))
 
+    def uses_persistent_kernel(self) -> bool:
+        return bool(self.lib.b200_model_uses_persistent_kernel(self._h))
+
     def kv_upload(self, buffer: int, host: np.ndarray, pos0: int, n_pos: int):
         host = np.ascontiguousarray(host, dtype=np.float32)
         _lib.check(self.lib.b200_model_kv_upload(self._h, buffer, host.ctypes.data, pos0, n_pos))

@@ -271,6 +271,15 @@ float b200_model_last_ms(const b200_model *m);
  * (weights + scales + small tensors + embedding row + live KV rows). */
 int64_t b200_model_step_bytes(const b200_model *m, int ctx);
 int b200_model_kernels_per_step(const b200_model *m);
+/* 1 when decode steps run as the single persistent kernel (batch 1, every
+ * linear layer int8, one GPU); 0 when they replay the multi-kernel CUDA graph.
+ * The environment variable BUDDY_B200_DECODE=graph forces the graph. */
+int b200_model_uses_persistent_kernel(const b200_model *m);
+/* Tuning aid: with BUDDY_B200_TRACE=<stride> set at load time, every
+ * stride-th CTA of the persistent kernel records the SM clock at each phase
+ * boundary of the last step: host[cta/stride][layer][12]. Returns the number
+ * of values copied (negative on error). */
+int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity);
 /* Session handle -> device pointers, for tests. */
 float *b200_model_kv_ptr(b200_model *m, int buffer);
 /* KV overflow on the device-resident cache; see b200_kv_overflow. */

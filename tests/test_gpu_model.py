@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 
 import oracle_lib as orc
-from buddy_mlir_b200 import (DEEPSEEK_R1_1P5B, TINY_QWEN2, TINY_QWEN3, _lib, synthetic)
+from buddy_mlir_b200 import (DEEPSEEK_R1_1P5B, TINY_MEGA, TINY_QWEN2, TINY_QWEN3, _lib, synthetic)
 from buddy_mlir_b200.model_entry import EntrySession
 from buddy_mlir_b200.session import ModelSession, greedy_sample, run_generation
 
@@ -170,6 +170,46 @@ def test_session_kv_overflow_matches_checker():
     s.close()
 
 
+@pytest.mark.parametrize("cfg", [TINY_MEGA, TINY_QWEN3])
+def test_persistent_kernel_matches_checker_and_graph_path(cfg, monkeypatch):
+    """Batch-1 int8 decode runs as one persistent kernel; it must agree with
+    the CPU checker, with the multi-kernel graph path, and with itself."""
+    blob, views = synthetic.make_f32_blob(cfg, 21)
+    om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in ALL_LINEAR})
+    s = ModelSession(cfg)
+    s.load_tensors(views, quantize_to="w8")
+    assert s.uses_persistent_kernel() and s.kernels_per_step() == 1
+    prompt = synthetic.prompt_tokens(cfg, 4, 8)
+
+    def step(t):
+        s.decode(t)
+        return s.logits_data().copy()
+    check_stream(step, om, prompt, 1e-3, n_greedy=40)
+    for b in range(2 * cfg.n_layers):
+        assert maxrel(s.kv_download(b)[:, :48], om.kv[b][:, :48]) < 1e-4
+    # device loop == host loop, twice (determinism)
+    host_ids, _ = run_generation(s, prompt, len(prompt) + 30)
+    runs = []
+    for _ in range(2):
+        s.reset_position()
+        s.prefill(prompt)
+        first = greedy_sample(s.logits_data())
+        runs.append([first] + [int(t) for t in s.generate(first, 30)])
+    assert runs[0] == runs[1] == host_ids
+    # the multi-kernel graph path on the same weights
+    monkeypatch.setenv("BUDDY_B200_DECODE", "graph")
+    g = ModelSession(cfg)
+    g.load_tensors(views, quantize_to="w8")
+    assert not g.uses_persistent_kernel() and g.kernels_per_step() > 1
+    s.reset_position()
+    for t in prompt:
+        s.decode(int(t))
+        g.decode(int(t))
+        assert maxrel(s.logits_data(), g.logits_data()) < 1e-4
+    s.close()
+    g.close()
+
+
 # ---- full-size shapes -------------------------------------------------------------------
 @pytest.fixture(scope="module")
 def full_weights():
@@ -202,6 +242,7 @@ def test_1p5b_int8_all_linear_with_long_context(full_weights):
     om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in ALL_LINEAR})
     s = ModelSession(cfg)
     s.load_blobs("f32", blob, all_linear_w8=True)
+    assert s.uses_persistent_kernel()
 
     def step(t):
         s.decode(t)
