@@ -176,9 +176,7 @@ struct b200_model {
   uint8_t *mega_stream = nullptr;
   int64_t *mega_offsets = nullptr;   // [(4L+1)+1][grid]: per-phase and per-CTA stream offsets
   const float **lvec_dev = nullptr;
-  float *xa = nullptr, *xb = nullptr, *gu = nullptr, *cand_val = nullptr;
-  int *cand_idx = nullptr;
-  unsigned *d_barrier = nullptr;
+  uint2 *ll_buf = nullptr;           // tagged activation buffers
   long long *d_trace = nullptr;
 };
 
@@ -355,7 +353,7 @@ int issue_step(b200_model *m, int *n_kernels) {
 
 
 // ---- persistent-kernel path ------------------------------------------------------
-void rows_of_host(int N, int cta, int grid, int &begin, int &count) {
+void rows_of_host(int N, int cta, int grid, int &begin, int &count) {  // N in dealing units
   const int base = N / grid, rem = N % grid;
   begin = cta * base + (cta < rem ? cta : rem);
   count = base + (cta < rem ? 1 : 0);
@@ -388,31 +386,42 @@ int build_mega(b200_model *m) {
   B200_CUDA(cudaGetDevice(&dev));
   B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
   B200_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
-  if (!coop || sms < c.kv_heads)
-    return B200_OK;  // stays on the graph path
+  const int G = c.q_heads / c.kv_heads;
   const int grid = sms, L = c.n_layers, D = c.head_dim;
+  int splits = grid / c.kv_heads;
+  if (splits > 16) splits = 16;
+  if (!coop || splits < 1 || (G * D + splits - 1) / splits > 256 || G * splits > 256)
+    return B200_OK;  // stays on the graph path
   const int H = c.hidden, QD = c.q_heads * D, KD = c.kv_heads * D, F = c.ffn, V = c.vocab;
   MegaParams &p = m->mp;
   const int Ks[5] = {H, QD, H, F, H}, Ns[5] = {QD + 2 * KD, H, 2 * F, H, V};
-  int slot_bytes = 0;
+  int slot_bytes = 0, maxK = 0;
   for (int i = 0; i < 5; ++i) {
     MegaPhase &ph = p.phase[i];
     ph.K = Ks[i];
     ph.N = Ns[i];
     ph.row_bytes = Ks[i] + kMegaTrailer;
     ph.mode = Ks[i] <= 1536 ? 0 : 1;
+    ph.unit = i == 2 ? 2 : 1;
     if (ph.mode == 0) {
       ph.rps = 16;   // two rows per consumer warp
     } else {
-      ph.rps = 25000 / ph.row_bytes;
-      if (ph.rps < 1) ph.rps = 1;
+      ph.rps = (25000 / ph.row_bytes) & ~1;
+      if (ph.rps < 2) ph.rps = 2;
       if (ph.rps > 8) ph.rps = 8;
     }
     if (ph.rps * ph.row_bytes > slot_bytes)
       slot_bytes = ph.rps * ph.row_bytes;
+    if (Ks[i] > maxK) maxK = Ks[i];
   }
   slot_bytes = (slot_bytes + 127) / 128 * 128;
-  int slots = (int)((227 * 1024 - mega_shared_bytes(0, 0) - 1024) / slot_bytes);
+  int xs_floats = maxK;
+  if (xs_floats < 8 * G * D) xs_floats = 8 * G * D;       // attention warp fold
+  if (xs_floats < (G + 2) * D) xs_floats = (G + 2) * D;   // staged q | k | v
+  xs_floats = (xs_floats + 31) / 32 * 32;
+  const int nws_floats = (H + 31) / 32 * 32;
+  const size_t fixed = mega_fixed_shared_bytes() + (size_t)(xs_floats + nws_floats) * 4;
+  int slots = (int)((227 * 1024 - 1024 - (long)fixed) / slot_bytes);
   if (slots > kMegaMaxSlots) slots = kMegaMaxSlots;
   if (slots < 3)
     return B200_OK;
@@ -425,9 +434,9 @@ int build_mega(b200_model *m) {
     for (int i = 0; i < nph; ++i) {
       const MegaPhase &ph = p.phase[i < 4 * L ? i % 4 : 4];
       int b, n;
-      rows_of_host(ph.N, cta, grid, b, n);
+      rows_of_host(ph.N / ph.unit, cta, grid, b, n);
       table[(size_t)i * grid + cta] = total;
-      total += (int64_t)n * ph.row_bytes;
+      total += (int64_t)n * ph.unit * ph.row_bytes;
     }
   }
   if (int rc = dev_alloc((void **)&m->mega_stream, total)) return rc;
@@ -437,25 +446,26 @@ int build_mega(b200_model *m) {
   for (int l = 0; l < L; ++l) {
     Layer &Ly = m->layers[l];
     const int64_t *o0 = m->mega_offsets + (size_t)(4 * l) * grid;
-    if (int rc = mega_build_rows(Ly.qkv.w_buf, H, Ns[0], 0, Ns[0], (const float *)Ly.qkv.scale_buf,
+    if (int rc = mega_build_rows(Ly.qkv.w_buf, H, Ns[0], 1, 0, Ns[0], 1, (const float *)Ly.qkv.scale_buf,
                                  Ly.qkv.bias_buf, grid, p.phase[0].row_bytes, o0, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_rows(Ly.o.w_buf, QD, H, 0, H, (const float *)Ly.o.scale_buf, nullptr, grid,
-                                 p.phase[1].row_bytes, o0 + grid, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.o.w_buf, QD, H, 1, 0, H, 1, (const float *)Ly.o.scale_buf, nullptr,
+                                 grid, p.phase[1].row_bytes, o0 + grid, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_rows(Ly.gate.w_buf, H, F, 0, 2 * F, (const float *)Ly.gate.scale_buf, nullptr,
+    // gate_j -> row 2j, up_j -> row 2j+1: one warp then holds the pair of a SiLU gate
+    if (int rc = mega_build_rows(Ly.gate.w_buf, H, F, 2, 0, 2 * F, 2, (const float *)Ly.gate.scale_buf,
+                                 nullptr, grid, p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
+      return rc;
+    if (int rc = mega_build_rows(Ly.up.w_buf, H, F, 2, 1, 2 * F, 2, (const float *)Ly.up.scale_buf, nullptr,
                                  grid, p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_rows(Ly.up.w_buf, H, F, F, 2 * F, (const float *)Ly.up.scale_buf, nullptr, grid,
-                                 p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
-      return rc;
-    if (int rc = mega_build_rows(Ly.down.w_buf, F, H, 0, H, (const float *)Ly.down.scale_buf, nullptr, grid,
-                                 p.phase[3].row_bytes, o0 + 3 * grid, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.down.w_buf, F, H, 1, 0, H, 1, (const float *)Ly.down.scale_buf, nullptr,
+                                 grid, p.phase[3].row_bytes, o0 + 3 * grid, m->mega_stream, st))
       return rc;
   }
-  if (int rc = mega_build_rows(m->lm_head.w_buf, H, V, 0, V, (const float *)m->lm_head.scale_buf, nullptr,
-                               grid, p.phase[4].row_bytes, m->mega_offsets + (size_t)(4 * L) * grid,
-                               m->mega_stream, st))
+  if (int rc = mega_build_rows(m->lm_head.w_buf, H, V, 1, 0, V, 1, (const float *)m->lm_head.scale_buf,
+                               nullptr, grid, p.phase[4].row_bytes,
+                               m->mega_offsets + (size_t)(4 * L) * grid, m->mega_stream, st))
     return rc;
   std::vector<const float *> lvec(4 * L);
   for (int l = 0; l < L; ++l) {
@@ -466,52 +476,52 @@ int build_mega(b200_model *m) {
   }
   if (int rc = dev_alloc((void **)&m->lvec_dev, lvec.size() * sizeof(float *))) return rc;
   B200_CUDA(cudaMemcpy(m->lvec_dev, lvec.data(), lvec.size() * sizeof(float *), cudaMemcpyHostToDevice));
-  if (int rc = dev_alloc((void **)&m->xa, H * 4)) return rc;
-  if (int rc = dev_alloc((void **)&m->xb, H * 4)) return rc;
-  if (int rc = dev_alloc((void **)&m->gu, (size_t)2 * F * 4)) return rc;
-  if (int rc = dev_alloc((void **)&m->cand_val, grid * 4)) return rc;
-  if (int rc = dev_alloc((void **)&m->cand_idx, grid * 4)) return rc;
-  if (int rc = dev_alloc((void **)&m->d_barrier, 4)) return rc;
-  B200_CUDA(cudaMemset(m->d_barrier, 0, 4));
+  // tagged activation buffers, all in one allocation (zero tags never match)
+  const size_t n_qkv = 2 * (size_t)(QD + 2 * KD), n_attn = 2 * (size_t)QD, n_x = 2 * (size_t)H,
+               n_mid = 2 * (size_t)F, n_part = 2 * (size_t)c.q_heads * splits * (D + 2),
+               n_cand = 2 * (size_t)grid;
+  const size_t n_ll = n_qkv + n_attn + 2 * n_x + n_mid + n_part + n_cand + 16;
+  if (int rc = dev_alloc((void **)&m->ll_buf, n_ll * sizeof(uint2))) return rc;
+  B200_CUDA(cudaMemset(m->ll_buf, 0, n_ll * sizeof(uint2)));
+  uint2 *q = m->ll_buf;
+  auto take = [&](size_t n) { uint2 *r = q; q += (n + 1) / 2 * 2; return r; };   // keep 16-byte alignment
+  p.ll_qkv = take(n_qkv);
+  p.ll_attn = take(n_attn);
+  p.ll_xb = take(n_x);
+  p.ll_mid = take(n_mid);
+  p.ll_xa = take(n_x);
+  p.ll_part = take(n_part);
+  p.ll_cand = take(n_cand);
   p.stream = m->mega_stream;
   p.cta_off = m->mega_offsets + (size_t)nph * grid;
-  p.H = H; p.F = F; p.V = V; p.D = D; p.qh = c.q_heads; p.kvh = c.kv_heads; p.L = L;
+  p.H = H; p.F = F; p.V = V; p.qh = c.q_heads; p.kvh = c.kv_heads; p.L = L;
   p.max_len = c.max_len;
-  p.splits = grid / c.kv_heads;
-  if (p.splits > 16) p.splits = 16;
+  p.splits = splits;
   p.slots = slots;
   p.slot_bytes = slot_bytes;
+  p.xs_floats = xs_floats;
+  p.nws_floats = nws_floats;
   p.eps = c.eps;
   p.embed = m->embed; p.inv_freq = m->inv_freq; p.final_norm = m->final_norm;
   p.lvec = m->lvec_dev;
   p.kv = m->kv_dev;
-  p.xa = m->xa; p.xb = m->xb; p.qkv = m->qkv; p.attn = m->attn; p.gu = m->gu; p.logits = m->logits;
+  p.logits = m->logits;
   p.kv_stage = m->kv_stage;
   p.state = m->d_state;
   p.history = m->d_history;
   p.history_cap = m->history_cap;
-  p.cand_val = m->cand_val; p.cand_idx = m->cand_idx;
-  p.barrier = m->d_barrier;
   p.error = m->d_state + 6;
   p.trace = nullptr;
   p.trace_stride = 1;
   if (const char *t = std::getenv("BUDDY_B200_TRACE")) {
     p.trace_stride = std::atoi(t) > 0 ? std::atoi(t) : 1;
-    const size_t n = (size_t)(grid / p.trace_stride + 1) * (L + 1) * 12;
+    const size_t n = (size_t)(grid / p.trace_stride + 1) * (L + 1) * 32;
     if (int rc = dev_alloc((void **)&m->d_trace, n * 8)) return rc;
     B200_CUDA(cudaMemset(m->d_trace, 0, n * 8));
     p.trace = m->d_trace;
   }
-  // split partials + counters for the persistent kernel's own split count
-  cudaFree(m->attn_scratch);
-  m->attn_scratch = nullptr;
-  const int64_t sf = b200_gqa_scratch_floats(c.q_heads, D, p.splits > m->splits ? p.splits : m->splits);
-  if (int rc = dev_alloc((void **)&m->attn_scratch, sf * 4)) return rc;
-  B200_CUDA(cudaMemset(m->attn_scratch, 0, sf * 4));
-  p.attn_part = m->attn_scratch;
-  p.attn_count = reinterpret_cast<unsigned *>(m->attn_scratch + (size_t)c.q_heads * p.splits * (D + 2));
   m->mega_grid = grid;
-  m->mega_smem = mega_shared_bytes(slots, slot_bytes);
+  m->mega_smem = fixed + (size_t)slots * slot_bytes;
   m->mega_stream_bytes = total;
   B200_CUDA(cudaStreamSynchronize(st));
   m->mega = true;
@@ -530,7 +540,12 @@ int check_step_error(b200_model *m) {
   // h_state_pinned holds the 8 state words read back after the step
   if (m->h_state_pinned[6] != 0) {
     const int code = m->h_state_pinned[6];
-    cudaMemsetAsync(m->d_state + 6, 0, 4, m->stream);
+    // clear the flag and move the launch counter on, so that tags written by
+    // the failed step can never match a later one
+    m->h_state_pinned[6] = 0;
+    m->h_state_pinned[4] += 2;
+    cudaMemcpyAsync(m->d_state + 4, m->h_state_pinned + 4, 12, cudaMemcpyHostToDevice, m->stream);
+    cudaStreamSynchronize(m->stream);
     return fail(B200_ECUDA, "decode step kernel gave up on a bounded wait (code %d)", code);
   }
   return B200_OK;
@@ -677,8 +692,7 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->attn_scratch); cudaFree(m->argmax_scratch); cudaFree(m->kv_stage);
   cudaFree(m->d_state); cudaFree(m->d_history);
   cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
-  cudaFree(m->xa); cudaFree(m->xb); cudaFree(m->gu); cudaFree(m->cand_val);
-  cudaFree(m->cand_idx); cudaFree(m->d_barrier); cudaFree(m->d_trace);
+  cudaFree(m->ll_buf); cudaFree(m->d_trace);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
   if (m->ev0) cudaEventDestroy(m->ev0);
@@ -1126,7 +1140,7 @@ int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega
 int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity) {
   if (!m || !host || !m->d_trace)
     return fail(B200_ESTATE, "read_trace: tracing is off (set BUDDY_B200_TRACE=<cta stride>)");
-  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * 12;
+  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * 32;
   B200_CUDA(cudaMemcpy(host, m->d_trace, (size_t)(n < capacity ? n : capacity) * 8,
                        cudaMemcpyDeviceToHost));
   return (int)(n < capacity ? n : capacity);

@@ -3,17 +3,30 @@
 // Why: at batch 1 a decode step of the 1.5B model is 140 dependent GEMVs of
 // 0.4-2 us each; launched one by one (even from a CUDA graph) every kernel
 // boundary drains the memory pipeline.  Here one CTA per SM stays resident for
-// the whole token.  Each CTA owns a fixed slice of the output rows of every
-// projection, and ALL weight bytes that CTA will ever need are laid out
-// back to back in one private stream (built once at load time).  A producer
-// warp walks that stream with bulk async copies (cp.async.bulk, completion on
-// mbarriers) into a ring of shared-memory slots and never waits for
-// activations, so HBM stays busy across the dependency points; eight consumer
-// warps dequantise from shared memory with the activations held in registers
-// and meet in warp-shuffle reductions.  The dependency points of the graph
-// (q/k/v -> attention -> o -> gate/up -> down) are grid-wide barriers on a
-// global counter.  Every wait is bounded: on expiry the kernel records an
-// error code and returns.
+// the whole token.
+//
+//  * Weights.  Each CTA owns a fixed slice of the output rows of every
+//    projection, and ALL weight bytes that CTA will ever need are laid out back
+//    to back in one private stream (built once at load time).  A producer warp
+//    walks that stream with bulk async copies (cp.async.bulk, completion on
+//    mbarriers) into a ring of shared-memory slots.  It never waits for
+//    activations, so HBM stays busy across the dependency points of the graph.
+//  * Activations.  There is no grid-wide barrier.  Every activation vector
+//    that crosses CTAs (q|k|v, attention output, the two residual streams, the
+//    SiLU-gated MLP intermediate, attention split partials, argmax candidates)
+//    is stored as 8-byte (value, tag) pairs written with one 64-bit store; the
+//    tag names launch, layer and producer phase.  A consumer simply loads the
+//    pairs it needs and retries until the tags match: data arrival IS the
+//    synchronisation (no fence, no counter, no barrier), and CTAs drift apart
+//    by at most one phase because every phase needs all outputs of the one
+//    before.  Buffers alternate by layer parity, so a producer can never
+//    overwrite a value a slower CTA still has to read.
+//  * Math.  Eight consumer warps dequantise from shared memory with the
+//    activations in registers and meet in warp-shuffle reductions.
+//
+// Every wait (mbarrier or tag poll) is bounded: on expiry the kernel records an
+// error code, all later waits fall through, control flow stays identical (so
+// CTA barriers stay matched), and the host call fails.
 //
 // Arithmetic is that of examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir
 // :46-260 with the int8 GEMV of
@@ -30,8 +43,18 @@ namespace {
 
 constexpr int kCW = 8;            // consumer warps
 constexpr int kCT = kCW * 32;     // consumer threads
-constexpr uint32_t kSpinLimit = 1u << 24;
+constexpr uint32_t kSpinLimit = 1u << 26;      // poll count bound, and
+constexpr unsigned long long kWaitNs = 1000000000ull;  // wall-time bound (1 s) of any single wait
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
 constexpr float kSeed = -1.0e30f;
+constexpr int D = 128;            // head_dim (checked on the host)
+
+// producer phases that tag their outputs
+enum { T_QKV = 1, T_ATTN = 2, T_XB = 3, T_MID = 4, T_XA = 5, T_PART = 6, T_CAND = 7 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -58,18 +81,25 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
-// Bounded wait.  Returns false when it gave up or the grid is already in the
-// failed state; callers carry on with the same control flow (so CTA barriers
-// stay matched) and the host discards the step.
+// Bounded wait.  Returns false when it gave up or the CTA is already in the
+// failed state; callers carry on with the same control flow.
 __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *err,
                                           volatile int *abort_flag) {
   if (*abort_flag)
     return false;
+  unsigned long long t0 = 0;
   for (uint32_t it = 0; it < kSpinLimit; ++it) {
     if (mbar_try_wait(bar, parity))
       return true;
-    if ((it & 0xFFF) == 0xFFF && *err != 0)
-      break;
+    if ((it & 0x3FF) == 0x3FF) {
+      if (*err != 0)
+        break;
+      const unsigned long long t = now_ns();
+      if (t0 == 0)
+        t0 = t;
+      else if (t - t0 > kWaitNs)
+        break;
+    }
   }
   *abort_flag = 1;
   return false;
@@ -85,17 +115,154 @@ __device__ __forceinline__ void bulk_g2s(void *dst, const void *src, uint32_t by
 __device__ __forceinline__ void consumer_sync() {
   asm volatile("bar.sync 1, %0;" ::"n"(kCT) : "memory");
 }
-__device__ __forceinline__ unsigned ld_relaxed(const unsigned *p) {
-  unsigned v;
-  asm volatile("ld.relaxed.gpu.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-  return v;
-}
-__device__ __forceinline__ void red_relaxed(unsigned *p, unsigned v) {
-  asm volatile("red.relaxed.gpu.global.add.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
-}
 __device__ __forceinline__ float4 ldcg4(const float *p) {
   return __ldcg(reinterpret_cast<const float4 *>(p));
 }
+
+// ---- tagged (value, tag) pairs ------------------------------------------------------
+__device__ __forceinline__ void ll_store(uint2 *p, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
+               "r"(tag)
+               : "memory");
+}
+__device__ __forceinline__ uint2 ll_load1(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+// two consecutive pairs (p is 16-byte aligned)
+__device__ __forceinline__ uint4 ll_load2(const uint2 *p) {
+  uint4 v;
+  asm volatile("ld.volatile.global.v4.u32 {%0, %1, %2, %3}, [%4];"
+               : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w)
+               : "l"(p)
+               : "memory");
+  return v;
+}
+
+struct Shared {
+  uint64_t full[kMegaMaxSlots];
+  uint64_t empty[kMegaMaxSlots];
+  float cs[64], sn[64];                 // cos / sin of this step's position
+  float part[kCW][kMegaMaxRowsB];       // shared-row phases: per-warp partial sums
+  float2 rowinfo[kMegaMaxRowsB];        // (scale, bias) of those rows
+  float red[kCW];
+  float bestv[kCW];
+  int besti[kCW];
+  int abort_flag;
+  float am[kCW][8], al[kCW][8];         // attention: per-warp (m, l)
+  float cm[8 * 32], cl[8 * 32], cw[8 * 32], cL[8];  // attention: split fold
+};
+static_assert(offsetof(Shared, rowinfo) % 8 == 0, "rowinfo must be 8-byte aligned");
+
+struct Ctx {
+  const MegaParams &p;
+  Shared &sh;
+  float *xs;          // staged activations (shared memory)
+  float *nws;         // staged norm weight (shared memory)
+  uint8_t *ring;
+  volatile int *err;
+  int ctid, lane, warp;
+  int slot;           // ring slot of the next stage (same sequence as the producer's)
+  uint32_t parity;    // parity of that slot's current use
+  uint32_t tag_base;
+};
+
+__device__ __forceinline__ uint32_t tag_of(const Ctx &c, int layer, int what) {
+  return c.tag_base + (uint32_t)((layer + 1) * 8 + what);
+}
+
+// Spin (bounded) until the pair at p carries `tag`.
+__device__ __forceinline__ float ll_wait1(Ctx &c, const uint2 *p, uint32_t tag) {
+  volatile int *ab = &c.sh.abort_flag;
+  uint2 v = ll_load1(p);
+  uint32_t it = 0;
+  unsigned long long t0 = 0;
+  while (v.y != tag && !*ab) {
+    bool give_up = ++it >= kSpinLimit;
+    if ((it & 0x3FF) == 0) {
+      const unsigned long long t = now_ns();
+      if (t0 == 0)
+        t0 = t;
+      give_up = give_up || *c.err != 0 || t - t0 > kWaitNs;
+    }
+    if (give_up) {
+      atomicCAS((int *)c.err, 0, 400 + (int)(tag & 7));
+      *ab = 1;
+      break;
+    }
+    v = ll_load1(p);
+  }
+  return __uint_as_float(v.x);
+}
+__device__ __forceinline__ uint4 ll_wait2(Ctx &c, const uint2 *p, uint32_t tag, uint4 v) {
+  volatile int *ab = &c.sh.abort_flag;
+  uint32_t it = 0;
+  unsigned long long t0 = 0;
+  while ((v.y != tag || v.w != tag) && !*ab) {
+    bool give_up = ++it >= kSpinLimit;
+    if ((it & 0x3FF) == 0) {
+      const unsigned long long t = now_ns();
+      if (t0 == 0)
+        t0 = t;
+      give_up = give_up || *c.err != 0 || t - t0 > kWaitNs;
+    }
+    if (give_up) {
+      atomicCAS((int *)c.err, 0, 400 + (int)(tag & 7));
+      *ab = 1;
+      break;
+    }
+    v = ll_load2(p);
+  }
+  return v;
+}
+
+// Cooperative load of n tagged values (n even) into shared memory; returns this
+// thread's partial sum of squares.  The first vector of every thread is polled
+// alone (cheap on L2) before the rest is requested.
+__device__ __forceinline__ float stage_tagged(Ctx &c, const uint2 *src, uint32_t tag, int n, float *dst) {
+  const int nv = n >> 1;
+  float ss = 0.f;
+  for (int base = 0; base < nv; base += kCT * 8) {
+    uint4 r[8];
+    int idx[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      idx[i] = base + i * kCT + c.ctid;
+    if (idx[0] < nv) {
+      r[0] = ll_load2(src + 2 * idx[0]);
+      r[0] = ll_wait2(c, src + 2 * idx[0], tag, r[0]);
+    }
+#pragma unroll
+    for (int i = 1; i < 8; ++i)
+      if (idx[i] < nv)
+        r[i] = ll_load2(src + 2 * idx[i]);
+#pragma unroll
+    for (int i = 0; i < 8; ++i)
+      if (idx[i] < nv) {
+        if (i > 0)
+          r[i] = ll_wait2(c, src + 2 * idx[i], tag, r[i]);
+        const float a = __uint_as_float(r[i].x), b = __uint_as_float(r[i].z);
+        *reinterpret_cast<float2 *>(dst + 2 * idx[i]) = make_float2(a, b);
+        ss = __fadd_rn(ss, __fmul_rn(a, a));
+        ss = __fadd_rn(ss, __fmul_rn(b, b));
+      }
+  }
+  return ss;
+}
+__device__ __forceinline__ float stage_plain(Ctx &c, const float *src, int n, float *dst) {
+  float ss = 0.f;
+  for (int i = c.ctid * 4; i < n; i += kCT * 4) {
+    const float4 v = __ldg(reinterpret_cast<const float4 *>(src + i));
+    *reinterpret_cast<float4 *>(dst + i) = v;
+    ss = __fadd_rn(ss, __fmul_rn(v.x, v.x));
+    ss = __fadd_rn(ss, __fmul_rn(v.y, v.y));
+    ss = __fadd_rn(ss, __fmul_rn(v.z, v.z));
+    ss = __fadd_rn(ss, __fmul_rn(v.w, v.w));
+  }
+  return ss;
+}
+
 // Streamed rows hold u = q + 128 (the int8 weight with its sign bit flipped).
 // Byte e of a word, moved to the low byte of an otherwise zero word, IS the
 // float u * 2^-149 (a denormal), so the dequantisation is one PRMT and the
@@ -103,7 +270,7 @@ __device__ __forceinline__ float4 ldcg4(const float *p) {
 // 2^64 to keep every product in the normal range (products are exact up to
 // the usual single rounding of the FMA), and the offset 128 * sum(x) is
 // subtracted once per row: sum x*q = 2^85 * sum (x*2^64)*(u*2^-149) - 128*sum x.
-constexpr float kXScale = 18446744073709551616.0f;      // 2^64
+constexpr float kXScale = 18446744073709551616.0f;          // 2^64
 constexpr float kAccScale = 38685626227668133590597632.0f;  // 2^85
 __device__ __forceinline__ void dot_unit(const uint4 &w, const float (&x)[16], float (&a)[4]) {
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
@@ -114,211 +281,154 @@ __device__ __forceinline__ void dot_unit(const uint4 &w, const float (&x)[16], f
       a[e] = fmaf(x[4 * j + e], __uint_as_float(__byte_perm(ws[j], 0u, 0x4440 + e)), a[e]);
 }
 
-__device__ __forceinline__ void rows_of(int N, int cta, int grid, int &begin, int &count) {
-  const int base = N / grid, rem = N % grid;
-  begin = cta * base + min(cta, rem);
-  count = base + (cta < rem ? 1 : 0);
+__device__ __forceinline__ void rows_of(const MegaPhase &ph, int cta, int grid, int &begin,
+                                        int &count) {
+  // rows are dealt out in units of ph.unit rows (2 keeps gate/up pairs together)
+  const int n = ph.N / ph.unit;
+  const int base = n / grid, rem = n % grid;
+  begin = (cta * base + min(cta, rem)) * ph.unit;
+  count = (base + (cta < rem ? 1 : 0)) * ph.unit;
 }
-
-struct Shared {
-  uint64_t full[kMegaMaxSlots];
-  uint64_t empty[kMegaMaxSlots];
-  float cs[64], sn[64];                 // cos / sin of this step's position
-  float part[kCW][kMegaMaxRowsB];       // mode-B per-warp partial sums
-  float2 rowinfo[kMegaMaxRowsB];        // (scale, bias) of the rows of a mode-B phase
-  float red[kCW];
-  float bestv[kCW];
-  int besti[kCW];
-  int abort_flag;
-  int last_flag;
-  // attention fold (aacc is written with 16-byte stores)
-  float am[kCW][8], al[kCW][8];
-  alignas(16) float aacc[kCW][8][128];
-};
-static_assert(offsetof(Shared, aacc) % 16 == 0, "aacc must be 16-byte aligned");
-static_assert(offsetof(Shared, rowinfo) % 8 == 0, "rowinfo must be 8-byte aligned");
-
-struct Ctx {
-  const MegaParams &p;
-  Shared &sh;
-  uint8_t *ring;
-  volatile int *err;
-  int ctid, lane, warp;
-  uint32_t stage;     // running stage counter (same sequence as the producer's)
-  unsigned epoch;     // grid barriers passed
-  unsigned barrier_base;
-};
 
 // Optional per-phase timeline (SM clock) of a few CTAs, for tuning.
 __device__ __forceinline__ void trace(Ctx &c, int layer, int slot) {
   if (c.p.trace != nullptr && c.ctid == 0 && (blockIdx.x % c.p.trace_stride) == 0)
-    c.p.trace[((size_t)(blockIdx.x / c.p.trace_stride) * (c.p.L + 1) + layer) * 12 + slot] =
+    c.p.trace[((size_t)(blockIdx.x / c.p.trace_stride) * (c.p.L + 1) + layer) * 32 + slot] =
         clock64();
 }
 
-// Grid-wide barrier over the consumer warps of every CTA.  After a failure
-// anywhere in the grid it degenerates to the CTA-local barriers.
-__device__ void grid_barrier(Ctx &c) {
-  ++c.epoch;
-  consumer_sync();
-  if (c.ctid == 0) {
-    __threadfence();   // release: this CTA's writes (ordered by the CTA barrier) before the arrival
-    red_relaxed(c.p.barrier, 1u);
-    // the counter is never reset: this launch's arrivals start at barrier_base
-    const unsigned target = c.barrier_base + c.epoch * gridDim.x;
-    volatile int *ab = &c.sh.abort_flag;
-    uint32_t it = 0;
-    while (!*ab && (int)(ld_relaxed(c.p.barrier) - target) < 0) {
-      if (++it >= kSpinLimit) {
-        atomicCAS((int *)c.err, 0, 100 + (int)c.epoch);
-        *ab = 1;
-        break;
-      }
-      if ((it & 0xFFF) == 0 && *c.err != 0)
-        *ab = 1;
-    }
-    __threadfence();   // acquire: other CTAs' writes are visible after the CTA barrier below
-  }
-  consumer_sync();
-}
-
-// ---- activation sources ----------------------------------------------------------
-// kind 0: vector v (optionally RMSNorm'ed with weight nw); kind 1: silu(g)*u.
+// ---- activation source / result sink of a projection -----------------------------
 struct XSrc {
-  int kind;
-  const float *v, *nw, *g, *u;
+  const uint2 *ll;      // tagged source, or
+  const float *plain;   // plain f32 source (the embedding row)
+  uint32_t tag;
+  const float *nw;      // RMSNorm weight or null
 };
-
-__device__ __forceinline__ void load_x4(const XSrc &xs, int k, float *dst) {
-  if (xs.kind == 0) {
-    const float4 t = ldcg4(xs.v + k);
-    dst[0] = t.x; dst[1] = t.y; dst[2] = t.z; dst[3] = t.w;
-  } else {
-    const float4 g = ldcg4(xs.g + k), u = ldcg4(xs.u + k);
-    const float gs[4] = {g.x, g.y, g.z, g.w}, us[4] = {u.x, u.y, u.z, u.w};
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      // subgraph0_decode_simplify.mlir:226-231: (g * sigmoid(g)) * u
-      const float s = 1.0f / (1.0f + expf(-gs[e]));
-      dst[e] = __fmul_rn(__fmul_rn(gs[e], s), us[e]);
-    }
-  }
-}
-
-// epilogue kinds
-enum { EP_STORE = 0, EP_RESIDUAL = 1, EP_LOGITS = 2 };
+enum { EP_STORE = 0, EP_RESIDUAL = 1, EP_LOGITS = 2, EP_SILU = 3 };
 struct Epi {
   int kind;
-  float *dst;
-  const float *res;
+  uint2 *dst;
+  uint32_t tag;
+  const uint2 *res_ll;   // residual (tagged) or
+  const float *res_plain;
+  uint32_t res_tag;
+  float *logits;
 };
 
-__device__ __forceinline__ void emit(const Epi &e, int n, float v, float &bestv, int &besti) {
+__device__ __forceinline__ void emit(Ctx &c, const Epi &e, int n, float v, float &bestv,
+                                     int &besti) {
   if (e.kind == EP_RESIDUAL) {
-    e.dst[n] = __fadd_rn(__ldcg(e.res + n), v);
-  } else {
-    e.dst[n] = v;
-    if (e.kind == EP_LOGITS && (v > bestv || (v == bestv && n < besti))) {
+    const float r = e.res_ll ? ll_wait1(c, e.res_ll + n, e.res_tag) : __ldg(e.res_plain + n);
+    ll_store(e.dst + n, __fadd_rn(r, v), e.tag);
+  } else if (e.kind == EP_LOGITS) {
+    e.logits[n] = v;
+    if (v > bestv || (v == bestv && n < besti)) {
       bestv = v;
       besti = n;
     }
+  } else {
+    ll_store(e.dst + n, v, e.tag);
   }
 }
+__device__ __forceinline__ float silu_mul(float g, float u) {
+  // subgraph0_decode_simplify.mlir:226-231: (g * sigmoid(g)) * u
+  const float s = 1.0f / (1.0f + expf(-g));
+  return __fmul_rn(__fmul_rn(g, s), u);
+}
 
-// One projection.  Mode A (K <= 1536): a warp owns two rows of every slot,
-// activations in 48 registers per lane; mode B: all consumer threads share
-// each row and the per-warp partial sums meet in shared memory.
-__device__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XSrc &xs, const Epi &ep,
-                           float &bestv, int &besti) {
-  const MegaParams &p = c.p;
+// One projection.  Mode A (K <= 1536): a warp owns two adjacent rows of every
+// slot; mode B: all consumer threads share each row and the per-warp partial
+// sums meet in shared memory.
+__device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XSrc &xs, const Epi &ep,
+                                           float &bestv, int &besti, int tl) {
+  // Everything the row loop needs is copied into registers first: the inline
+  // asm in the loop clobbers memory, so fields read through `ph` / `c.p` would
+  // otherwise be re-fetched from constant memory at every stage.
   int row_begin, nrows;
-  rows_of(ph.N, blockIdx.x, gridDim.x, row_begin, nrows);
-  float xr[3][16];
-  const int K = ph.K;
+  rows_of(ph, blockIdx.x, gridDim.x, row_begin, nrows);
+  const int K = ph.K, row_bytes = ph.row_bytes, rps = ph.rps, mode = ph.mode;
   const int units = K / 16;
+  const int n_slots = c.p.slots, slot_bytes = c.p.slot_bytes;
+  const float eps = c.p.eps;
+  Shared &sh = c.sh;
+  const int lane = c.lane, warp = c.warp, ctid = c.ctid;
+  uint8_t *const ring = c.ring;
+  float *const xsm = c.xs, *const nwsm = c.nws;
+  int slot = c.slot;
+  uint32_t parity = c.parity;
 
-  // ---- activations into registers (same k permutation as the packed rows) ----
-  float ss = 0.f;
+  // ---- stage the activation vector (and the norm weight) in shared memory ----
+  if (xs.nw != nullptr)
+    for (int i = ctid * 4; i < K; i += kCT * 4)
+      *reinterpret_cast<float4 *>(nwsm + i) = __ldg(reinterpret_cast<const float4 *>(xs.nw + i));
+  float ss = xs.ll ? stage_tagged(c, xs.ll, xs.tag, K, xsm) : stage_plain(c, xs.plain, K, xsm);
+  float rinv = 1.f;
+  if (xs.nw != nullptr) {
+    // RMSNorm, subgraph0_decode_simplify.mlir:60-72
+    ss = warp_sum(ss);
+    if (lane == 0)
+      sh.red[warp] = ss;
+  }
+  consumer_sync();
+  trace(c, tl, 12 + 4 * (int)(&ph - c.p.phase));
+  if (xs.nw != nullptr) {
+    float t = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCW; ++w)
+      t += sh.red[w];
+    rinv = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), eps));
+  }
+  // ---- gather this thread's activations (same k permutation as the packed rows) ----
+  float xr[3][16];
+  float sx = 0.f;
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
-    const int u = ph.mode == 0 ? (i * 32 + c.lane) : (i * kCT + c.ctid);
-    const bool active = nrows > 0 && u < units;
+    const int u = mode == 0 ? (i * 32 + lane) : (i * kCT + ctid);
 #pragma unroll
     for (int e = 0; e < 16; ++e)
       xr[i][e] = 0.f;
-    if (active) {
+    if (u < units) {
       const int b = u >> 5, l = u & 31;
       const int Bs = min(512, K - 512 * b), q = Bs >> 2;
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
-        load_x4(xs, 512 * b + j * q + 4 * l, &xr[i][4 * j]);
-#pragma unroll
-        for (int e = 0; e < 4; ++e)
-          ss = __fadd_rn(ss, __fmul_rn(xr[i][4 * j + e], xr[i][4 * j + e]));
-      }
-    }
-  }
-  if (xs.kind == 0 && xs.nw != nullptr) {
-    // RMSNorm, subgraph0_decode_simplify.mlir:60-72
-    ss = warp_sum(ss);
-    if (ph.mode == 1) {
-      if (c.lane == 0)
-        c.sh.red[c.warp] = ss;
-      consumer_sync();
-      ss = 0.f;
-#pragma unroll
-      for (int w = 0; w < kCW; ++w)
-        ss += c.sh.red[w];
-      consumer_sync();
-    }
-    const float rinv = rsqrtf(__fadd_rn(__fmul_rn(ss, 1.0f / (float)K), p.eps));
-#pragma unroll
-    for (int i = 0; i < 3; ++i) {
-      const int u = ph.mode == 0 ? (i * 32 + c.lane) : (i * kCT + c.ctid);
-      if (nrows > 0 && u < units) {
-        const int b = u >> 5, l = u & 31;
-        const int Bs = min(512, K - 512 * b), q = Bs >> 2;
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          const float4 w4 = __ldg(reinterpret_cast<const float4 *>(xs.nw + 512 * b + j * q + 4 * l));
-          xr[i][4 * j + 0] = __fmul_rn(w4.x, __fmul_rn(xr[i][4 * j + 0], rinv));
-          xr[i][4 * j + 1] = __fmul_rn(w4.y, __fmul_rn(xr[i][4 * j + 1], rinv));
-          xr[i][4 * j + 2] = __fmul_rn(w4.z, __fmul_rn(xr[i][4 * j + 2], rinv));
-          xr[i][4 * j + 3] = __fmul_rn(w4.w, __fmul_rn(xr[i][4 * j + 3], rinv));
+        const int k = 512 * b + j * q + 4 * l;
+        float4 v = *reinterpret_cast<const float4 *>(xsm + k);
+        if (xs.nw != nullptr) {
+          const float4 w4 = *reinterpret_cast<const float4 *>(nwsm + k);
+          v.x = __fmul_rn(w4.x, __fmul_rn(v.x, rinv));
+          v.y = __fmul_rn(w4.y, __fmul_rn(v.y, rinv));
+          v.z = __fmul_rn(w4.z, __fmul_rn(v.z, rinv));
+          v.w = __fmul_rn(w4.w, __fmul_rn(v.w, rinv));
         }
+        sx += (v.x + v.y) + (v.z + v.w);
+        xr[i][4 * j + 0] = v.x * kXScale;
+        xr[i][4 * j + 1] = v.y * kXScale;
+        xr[i][4 * j + 2] = v.z * kXScale;
+        xr[i][4 * j + 3] = v.w * kXScale;
       }
     }
   }
-  // offset term 128 * sum(x) of this thread's activations, then the 2^64 pre-scale
-  float sx = 0.f;
-#pragma unroll
-  for (int i = 0; i < 3; ++i)
-#pragma unroll
-    for (int e = 0; e < 16; ++e) {
-      sx += xr[i][e];
-      xr[i][e] *= kXScale;
-    }
-  const float off = -128.0f * sx;
+  const float off = -128.0f * sx;   // this thread's share of the offset term
+  trace(c, tl, 13 + 4 * (int)(&ph - c.p.phase));
 
   // ---- stream the rows --------------------------------------------------------
-  volatile int *ab = &c.sh.abort_flag;
+  volatile int *ab = &sh.abort_flag;
   int flush_base = 0;
-  for (int r0 = 0; r0 < nrows; r0 += ph.rps) {
-    const int rows = min(ph.rps, nrows - r0);
-    const int slot = c.stage % p.slots;
-    const uint32_t use = c.stage / p.slots;
-    if (!mbar_wait(&c.sh.full[slot], use & 1, c.err, ab))
+  for (int r0 = 0; r0 < nrows; r0 += rps) {
+    const int rows = min(rps, nrows - r0);
+    if (!mbar_wait(&sh.full[slot], parity, c.err, ab))
       atomicCAS((int *)c.err, 0, 200 + slot);
-    const uint8_t *base = c.ring + (size_t)slot * p.slot_bytes;
-    if (ph.mode == 0) {
-      // rows c.warp and c.warp + 8 of the slot; clamp keeps the loads inside the slot
-      const int ra = c.warp, rb = c.warp + kCW;
-      const uint8_t *rowa = base + (size_t)min(ra, rows - 1) * ph.row_bytes;
-      const uint8_t *rowb = base + (size_t)min(rb, rows - 1) * ph.row_bytes;
+    const uint8_t *base = ring + (size_t)slot * slot_bytes;
+    if (mode == 0) {
+      // rows 2w and 2w+1 of the slot; the clamp keeps the loads inside the slot
+      const int ra = 2 * warp, rb = ra + 1;
+      const uint8_t *rowa = base + (size_t)min(ra, rows - 1) * row_bytes;
+      const uint8_t *rowb = base + (size_t)min(rb, rows - 1) * row_bytes;
       float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
       for (int i = 0; i < 3; ++i) {
-        const int u = i * 32 + c.lane;
+        const int u = i * 32 + lane;
         if (u < units) {
           const uint4 wa = *reinterpret_cast<const uint4 *>(rowa + u * 16);
           const uint4 wb = *reinterpret_cast<const uint4 *>(rowb + u * 16);
@@ -330,22 +440,28 @@ __device__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XSrc &xs, const Ep
       float vb = fmaf((b[0] + b[1]) + (b[2] + b[3]), kAccScale, off);
       va = warp_sum(va);
       vb = warp_sum(vb);
-      if (c.lane == 0 && ra < rows) {
-        const float2 t = *reinterpret_cast<const float2 *>(rowa + K);
-        emit(ep, row_begin + r0 + ra, __fadd_rn(__fmul_rn(va, t.x), t.y), bestv, besti);
-      }
-      if (c.lane == 1 && rb < rows) {
-        const float2 t = *reinterpret_cast<const float2 *>(rowb + K);
-        emit(ep, row_begin + r0 + rb, __fadd_rn(__fmul_rn(vb, t.x), t.y), bestv, besti);
+      const float2 ta = *reinterpret_cast<const float2 *>(rowa + K);
+      const float2 tb = *reinterpret_cast<const float2 *>(rowb + K);
+      va = __fadd_rn(__fmul_rn(va, ta.x), ta.y);
+      vb = __fadd_rn(__fmul_rn(vb, tb.x), tb.y);
+      if (ep.kind == EP_SILU) {
+        // rows (2j, 2j+1) = (gate_j, up_j)
+        if (lane == 0 && rb < rows)
+          ll_store(ep.dst + ((row_begin + r0 + ra) >> 1), silu_mul(va, vb), ep.tag);
+      } else {
+        if (lane == 0 && ra < rows)
+          emit(c, ep, row_begin + r0 + ra, va, bestv, besti);
+        if (lane == 1 && rb < rows)
+          emit(c, ep, row_begin + r0 + rb, vb, bestv, besti);
       }
     } else {
       for (int r = 0; r < rows; r += 2) {
-        const uint8_t *rowa = base + (size_t)r * ph.row_bytes;
-        const uint8_t *rowb = base + (size_t)min(r + 1, rows - 1) * ph.row_bytes;
+        const uint8_t *rowa = base + (size_t)r * row_bytes;
+        const uint8_t *rowb = base + (size_t)min(r + 1, rows - 1) * row_bytes;
         float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
-          const int u = i * kCT + c.ctid;
+          const int u = i * kCT + ctid;
           if (u < units) {
             const uint4 wa = *reinterpret_cast<const uint4 *>(rowa + u * 16);
             const uint4 wb = *reinterpret_cast<const uint4 *>(rowb + u * 16);
@@ -357,67 +473,103 @@ __device__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XSrc &xs, const Ep
         float vb = fmaf((b[0] + b[1]) + (b[2] + b[3]), kAccScale, off);
         va = warp_sum(va);
         vb = warp_sum(vb);
-        if (c.lane == 0) {
-          c.sh.part[c.warp][r0 + r - flush_base] = va;
+        if (lane == 0) {
+          sh.part[warp][r0 + r - flush_base] = va;
           if (r + 1 < rows)
-            c.sh.part[c.warp][r0 + r + 1 - flush_base] = vb;
+            sh.part[warp][r0 + r + 1 - flush_base] = vb;
         }
-        if (c.ctid == 0) {
-          c.sh.rowinfo[r0 + r - flush_base] = *reinterpret_cast<const float2 *>(rowa + K);
+        if (ctid == 0) {
+          sh.rowinfo[r0 + r - flush_base] = *reinterpret_cast<const float2 *>(rowa + K);
           if (r + 1 < rows)
-            c.sh.rowinfo[r0 + r + 1 - flush_base] = *reinterpret_cast<const float2 *>(rowb + K);
+            sh.rowinfo[r0 + r + 1 - flush_base] = *reinterpret_cast<const float2 *>(rowb + K);
         }
       }
     }
     __syncwarp();
-    if (c.lane == 0)
-      mbar_arrive(&c.sh.empty[slot]);
-    ++c.stage;
-    if (ph.mode == 1) {
+    if (lane == 0)
+      mbar_arrive(&sh.empty[slot]);
+    if (++slot == n_slots) {
+      slot = 0;
+      parity ^= 1u;
+    }
+    if (mode == 1) {
       const int pending = r0 + rows - flush_base;
-      if (pending + ph.rps > kMegaMaxRowsB || r0 + rows >= nrows) {
+      if (pending + rps > kMegaMaxRowsB || r0 + rows >= nrows) {
         // fold the per-warp partial sums of the pending rows (fixed warp order)
         consumer_sync();
-        if (c.ctid < pending) {
+        auto row_value = [&](int i) {
           float s = 0.f;
 #pragma unroll
           for (int w = 0; w < kCW; ++w)
-            s += c.sh.part[w][c.ctid];
-          const float2 t = c.sh.rowinfo[c.ctid];
-          emit(ep, row_begin + flush_base + c.ctid, __fadd_rn(__fmul_rn(s, t.x), t.y), bestv,
-               besti);
+            s += sh.part[w][i];
+          const float2 t = sh.rowinfo[i];
+          return __fadd_rn(__fmul_rn(s, t.x), t.y);
+        };
+        if (ep.kind == EP_SILU) {
+          if (ctid < pending / 2)
+            ll_store(ep.dst + ((row_begin + flush_base) >> 1) + ctid,
+                     silu_mul(row_value(2 * ctid), row_value(2 * ctid + 1)), ep.tag);
+        } else if (ctid < pending) {
+          emit(c, ep, row_begin + flush_base + ctid, row_value(ctid), bestv, besti);
         }
         consumer_sync();
         flush_base = r0 + rows;
       }
     }
   }
+  c.slot = slot;
+  c.parity = parity;
+  // the staged vector is reused by the next phase
+  consumer_sync();
 }
 
 // ---- attention -------------------------------------------------------------------
-// Work item = (kv head, split).  The CTA applies (QK-norm and) RoPE to the G
-// query heads of its kv head, the CTA whose range holds `pos` also rotates the
-// new key and writes the K/V row, every warp scans every 8th row of the range,
-// the CTA folds its warps, and the last CTA of a kv head to arrive folds the
-// splits (in split order, so the result does not depend on arrival order).
+// Work item = (kv head, split).  The CTA stages q|k|v of its kv head, applies
+// (QK-norm and) RoPE to the G query heads, the CTA whose range holds `pos` also
+// rotates the new key and writes the K/V row; every warp scans every 8th row of
+// the range with four rows in flight; the CTA folds its warps and publishes the
+// split partial; then every CTA of the kv head folds one slice of the outputs
+// over all splits (in split order: the result does not depend on timing).
 template <int G>
-__device__ void attention_phase(Ctx &c, int layer, int pos) {
+__device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
   const MegaParams &p = c.p;
-  constexpr int D = 128;
-  const int items = p.kvh * p.splits;
-  if ((int)blockIdx.x >= items)
+  const int S = p.splits;
+  if ((int)blockIdx.x >= p.kvh * S)
     return;
-  const int hk = blockIdx.x / p.splits, split = blockIdx.x % p.splits;
+  const int hk = blockIdx.x / S, split = blockIdx.x % S;
   const int len = pos + 1;
-  const int chunk = (len + p.splits - 1) / p.splits;
+  const int chunk = (len + S - 1) / S;
   const int s0 = split * chunk, s1 = min(len, s0 + chunk);
   const int lane = c.lane, warp = c.warp;
+  const int par = layer & 1;
+  const int QD = p.qh * D, KD = p.kvh * D;
   const float *qn = p.lvec[4 * layer + 2], *kn = p.lvec[4 * layer + 3];
   float *kc = p.kv[2 * layer] + (size_t)hk * p.max_len * D;
   float *vc = p.kv[2 * layer + 1] + (size_t)hk * p.max_len * D;
   const float scale = rsqrtf((float)D);
   const int jj = 4 * (lane & 15);       // rotary index of this lane's 4 dims
   const bool upper = lane >= 16;
+
+  // ---- stage q (G heads), k, v of this kv head: xs[0 .. (G+2)*D) ----------------
+  {
+    const uint2 *src = p.ll_qkv + (size_t)par * (QD + 2 * KD);
+    const uint32_t tag = tag_of(c, layer, T_QKV);
+    const int nv = (G + 2) * (D / 2);
+    for (int v = c.ctid; v < nv; v += kCT) {
+      const int e = 2 * v;   // element in the staged [q | k | v] order
+      int srce;
+      if (e < G * D)
+        srce = hk * G * D + e;
+      else if (e < (G + 1) * D)
+        srce = QD + hk * D + (e - G * D);
+      else
+        srce = QD + KD + hk * D + (e - (G + 1) * D);
+      uint4 r = ll_load2(src + srce);
+      r = ll_wait2(c, src + srce, tag, r);
+      *reinterpret_cast<float2 *>(c.xs + e) = make_float2(__uint_as_float(r.x), __uint_as_float(r.z));
+    }
+  }
+  consumer_sync();
 
   auto rope4 = [&](float (&v)[4], const float *nw) {
     if (nw != nullptr) {
@@ -444,8 +596,8 @@ __device__ void attention_phase(Ctx &c, int layer, int pos) {
 
   // new K / V row (written by the CTA whose range contains pos)
   if (pos >= s0 && pos < s1 && warp == 0) {
-    const float4 k4 = ldcg4(p.qkv + p.qh * D + hk * D + 4 * lane);
-    const float4 v4 = ldcg4(p.qkv + p.qh * D + p.kvh * D + hk * D + 4 * lane);
+    const float4 k4 = *reinterpret_cast<const float4 *>(c.xs + G * D + 4 * lane);
+    const float4 v4 = *reinterpret_cast<const float4 *>(c.xs + (G + 1) * D + 4 * lane);
     float kv[4] = {k4.x, k4.y, k4.z, k4.w};
     rope4(kv, kn);
     const float4 ko = make_float4(kv[0], kv[1], kv[2], kv[3]);
@@ -459,11 +611,12 @@ __device__ void attention_phase(Ctx &c, int layer, int pos) {
   float qr[G][4];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
-    const float4 q4 = ldcg4(p.qkv + (size_t)(hk * G + g) * D + 4 * lane);
+    const float4 q4 = *reinterpret_cast<const float4 *>(c.xs + g * D + 4 * lane);
     qr[g][0] = q4.x; qr[g][1] = q4.y; qr[g][2] = q4.z; qr[g][3] = q4.w;
     rope4(qr[g], qn);
   }
-  consumer_sync();  // the new row is visible to the whole CTA
+  consumer_sync();  // the new row is visible to the whole CTA; xs may be reused
+  trace(c, layer, 8);
 
   float m[G], l[G], acc[G][4];
 #pragma unroll
@@ -472,55 +625,64 @@ __device__ void attention_phase(Ctx &c, int layer, int pos) {
     l[g] = 0.f;
     acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
   }
-  for (int j = s0 + warp; j < s1; j += 2 * kCW) {
-    // two rows per iteration: their loads, dots and reductions are independent
-    const int j2 = j + kCW;
-    const bool two = j2 < s1;
-    const float4 ka = ldcg4(kc + (size_t)j * D + 4 * lane);
-    const float4 va = ldcg4(vc + (size_t)j * D + 4 * lane);
-    const float4 kb = ldcg4(kc + (size_t)(two ? j2 : j) * D + 4 * lane);
-    const float4 vb = ldcg4(vc + (size_t)(two ? j2 : j) * D + 4 * lane);
-    float sa[G], sb[G];
+  constexpr int NB = G <= 6 ? 4 : 2;   // rows in flight per warp
+  for (int j0 = s0 + warp; j0 < s1; j0 += NB * kCW) {
+    // NB rows in flight: all loads are issued before the first use
+    float4 kr[NB], vr[NB];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float d = qr[g][0] * ka.x;
-      d = fmaf(qr[g][1], ka.y, d);
-      d = fmaf(qr[g][2], ka.z, d);
-      sa[g] = fmaf(qr[g][3], ka.w, d);
-      float e = qr[g][0] * kb.x;
-      e = fmaf(qr[g][1], kb.y, e);
-      e = fmaf(qr[g][2], kb.z, e);
-      sb[g] = fmaf(qr[g][3], kb.w, e);
+    for (int i = 0; i < NB; ++i) {
+      const int j = min(j0 + i * kCW, s1 - 1);
+      kr[i] = ldcg4(kc + (size_t)j * D + 4 * lane);
+      vr[i] = ldcg4(vc + (size_t)j * D + 4 * lane);
     }
+    float s[NB][G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      sa[g] = warp_sum(sa[g]) * scale;
-      sb[g] = warp_sum(sb[g]) * scale;
-    }
+    for (int i = 0; i < NB; ++i)
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float nm = fmaxf(m[g], two ? fmaxf(sa[g], sb[g]) : sa[g]);
-      const float alpha = expf(m[g] - nm), pa = expf(sa[g] - nm);
-      const float pb = two ? expf(sb[g] - nm) : 0.f;
-      l[g] = fmaf(l[g], alpha, pa + pb);
-      acc[g][0] = fmaf(acc[g][0], alpha, fmaf(pa, va.x, pb * vb.x));
-      acc[g][1] = fmaf(acc[g][1], alpha, fmaf(pa, va.y, pb * vb.y));
-      acc[g][2] = fmaf(acc[g][2], alpha, fmaf(pa, va.z, pb * vb.z));
-      acc[g][3] = fmaf(acc[g][3], alpha, fmaf(pa, va.w, pb * vb.w));
-      m[g] = nm;
+      for (int g = 0; g < G; ++g) {
+        float d = qr[g][0] * kr[i].x;
+        d = fmaf(qr[g][1], kr[i].y, d);
+        d = fmaf(qr[g][2], kr[i].z, d);
+        s[i][g] = fmaf(qr[g][3], kr[i].w, d);
+      }
+#pragma unroll
+    for (int i = 0; i < NB; ++i)
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        s[i][g] = warp_sum(s[i][g]) * scale;
+#pragma unroll
+    for (int i = 0; i < NB; ++i) {
+      if (j0 + i * kCW < s1) {   // warp-uniform
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          const float nm = fmaxf(m[g], s[i][g]);
+          const float alpha = expf(m[g] - nm), pw = expf(s[i][g] - nm);
+          l[g] = fmaf(l[g], alpha, pw);
+          acc[g][0] = fmaf(acc[g][0], alpha, pw * vr[i].x);
+          acc[g][1] = fmaf(acc[g][1], alpha, pw * vr[i].y);
+          acc[g][2] = fmaf(acc[g][2], alpha, pw * vr[i].z);
+          acc[g][3] = fmaf(acc[g][3], alpha, pw * vr[i].w);
+          m[g] = nm;
+        }
+      }
     }
   }
+  trace(c, layer, 9);
+  // ---- fold the warps of this CTA (fixed warp order) ------------------------------
+  float *aacc = c.xs;   // [kCW][G][D]
 #pragma unroll
   for (int g = 0; g < G; ++g) {
     if (lane == 0) {
       c.sh.am[warp][g] = m[g];
       c.sh.al[warp][g] = l[g];
     }
-    *reinterpret_cast<float4 *>(&c.sh.aacc[warp][g][4 * lane]) =
+    *reinterpret_cast<float4 *>(aacc + ((size_t)warp * G + g) * D + 4 * lane) =
         make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
   }
   consumer_sync();
   const int stride = D + 2;
+  uint2 *part = p.ll_part + (size_t)par * p.qh * S * stride;
+  const uint32_t ptag = tag_of(c, layer, T_PART);
   for (int idx = c.ctid; idx < G * D; idx += kCT) {
     const int g = idx / D, d = idx - g * D;
     float M = kSeed;
@@ -532,64 +694,72 @@ __device__ void attention_phase(Ctx &c, int layer, int pos) {
     for (int w = 0; w < kCW; ++w) {
       const float b = expf(c.sh.am[w][g] - M);
       L = fmaf(c.sh.al[w][g], b, L);
-      A = fmaf(c.sh.aacc[w][g][d], b, A);
+      A = fmaf(aacc[((size_t)w * G + g) * D + d], b, A);
     }
-    float *part = p.attn_part + ((size_t)(hk * G + g) * p.splits + split) * stride;
-    part[d] = A;
+    uint2 *dst = part + ((size_t)(hk * G + g) * S + split) * stride;
+    ll_store(dst + d, A, ptag);
     if (d == 0) {
-      part[D] = M;
-      part[D + 1] = L;
+      ll_store(dst + D, M, ptag);
+      ll_store(dst + D + 1, L, ptag);
     }
   }
-  __threadfence();
-  consumer_sync();
-  if (c.ctid == 0) {
-    const unsigned done = atomicAdd(&p.attn_count[hk], 1u);
-    c.sh.last_flag = (done == (unsigned)p.splits - 1);
-    if (c.sh.last_flag)
-      p.attn_count[hk] = 0;
+  trace(c, layer, 10);
+  // ---- fold the splits for this CTA's slice of the G*D outputs ----------------------
+  // (frontend/Python/ops/tosa.py:14502-14594): weights exp(m_s - M), then sums
+  for (int idx = c.ctid; idx < G * S; idx += kCT) {
+    const int g = idx / S, si = idx - g * S;
+    const uint2 *src = part + ((size_t)(hk * G + g) * S + si) * stride + D;
+    uint4 r = ll_load2(src);
+    r = ll_wait2(c, src, ptag, r);
+    c.sh.cm[idx] = __uint_as_float(r.x);
+    c.sh.cl[idx] = __uint_as_float(r.z);
   }
   consumer_sync();
-  if (c.sh.last_flag) {
-    __threadfence();
-    // fold the splits of this kv head (frontend/Python/ops/tosa.py:14502-14594):
-    // weights exp(m_s - M) once per (head, split), then sums with independent loads
-    const int S = p.splits;
-    float *wts = &c.sh.aacc[0][0][0];           // [G][S] weights, then [G] totals
-    for (int idx = c.ctid; idx < G * S; idx += kCT) {
-      const int g = idx / S, sidx = idx - g * S;
-      const float *part = p.attn_part + ((size_t)(hk * G + g) * S + sidx) * stride;
-      c.sh.aacc[1][0][idx] = __ldcg(part + D);        // m
-      c.sh.aacc[2][0][idx] = __ldcg(part + D + 1);    // l
+  if (c.ctid < G) {
+    const int g = c.ctid;
+    float M = kSeed;
+    for (int si = 0; si < S; ++si)
+      M = fmaxf(M, c.sh.cm[g * S + si]);
+    float L = 0.f;
+    for (int si = 0; si < S; ++si) {
+      const float b = expf(c.sh.cm[g * S + si] - M);
+      c.sh.cw[g * S + si] = b;
+      L = fmaf(c.sh.cl[g * S + si], b, L);
     }
-    consumer_sync();
-    if (c.ctid < G) {
-      const int g = c.ctid;
-      float M = kSeed;
-      for (int sidx = 0; sidx < S; ++sidx)
-        M = fmaxf(M, c.sh.aacc[1][0][g * S + sidx]);
-      float L = 0.f;
-      for (int sidx = 0; sidx < S; ++sidx) {
-        const float b = expf(c.sh.aacc[1][0][g * S + sidx] - M);
-        wts[g * S + sidx] = b;
-        L = fmaf(c.sh.aacc[2][0][g * S + sidx], b, L);
-      }
-      c.sh.aacc[3][0][g] = L;
-    }
-    consumer_sync();
-    for (int idx = c.ctid; idx < G * D; idx += kCT) {
-      const int g = idx / D, d = idx - g * D;
-      const float *parts = p.attn_part + (size_t)(hk * G + g) * S * stride + d;
+    c.sh.cL[g] = L;
+  }
+  consumer_sync();
+  trace(c, layer, 11);
+  {
+    const int per = (G * D + S - 1) / S;          // outputs folded by this CTA
+    const int o = split * per + c.ctid;
+    if (c.ctid < per && o < G * D) {
+      const int g = o / D, d = o - g * D;
+      const uint2 *src = part + (size_t)(hk * G + g) * S * stride + d;
       float ar = 0.f;
-#pragma unroll 8
-      for (int sidx = 0; sidx < S; ++sidx)
-        ar = fmaf(__ldcg(parts + (size_t)sidx * stride), wts[g * S + sidx], ar);
-      p.attn[(size_t)(hk * G + g) * D + d] = __fdiv_rn(ar, c.sh.aacc[3][0][g]);
+      for (int sb = 0; sb < S; sb += 8) {
+        uint2 r[8];
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (sb + i < S)
+            r[i] = ll_load1(src + (size_t)(sb + i) * stride);
+#pragma unroll
+        for (int i = 0; i < 8; ++i)
+          if (sb + i < S) {
+            float v = __uint_as_float(r[i].x);
+            if (r[i].y != ptag)
+              v = ll_wait1(c, src + (size_t)(sb + i) * stride, ptag);
+            ar = fmaf(v, c.sh.cw[g * S + sb + i], ar);
+          }
+      }
+      ll_store(p.ll_attn + (size_t)par * QD + (size_t)(hk * G + g) * D + d,
+               __fdiv_rn(ar, c.sh.cL[g]), tag_of(c, layer, T_ATTN));
     }
   }
+  consumer_sync();
 }
 
-__device__ void attention_dispatch(Ctx &c, int layer, int pos) {
+__device__ __forceinline__ void attention_dispatch(Ctx &c, int layer, int pos) {
   switch (c.p.qh / c.p.kvh) {
   case 1: attention_phase<1>(c, layer, pos); break;
   case 2: attention_phase<2>(c, layer, pos); break;
@@ -602,10 +772,13 @@ __device__ void attention_dispatch(Ctx &c, int layer, int pos) {
 
 } // namespace
 
-__global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const MegaParams p) {
+__global__ void __launch_bounds__(kMegaThreads, 1)
+decode_step_kernel(const __grid_constant__ MegaParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Shared &sh = *reinterpret_cast<Shared *>(smem_raw);
-  uint8_t *ring = smem_raw + ((sizeof(Shared) + 127) / 128) * 128;
+  float *xs = reinterpret_cast<float *>(smem_raw + ((sizeof(Shared) + 127) / 128) * 128);
+  float *nws = xs + p.xs_floats;
+  uint8_t *ring = reinterpret_cast<uint8_t *>(nws + p.nws_floats);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *err = p.error;
 
@@ -615,11 +788,10 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
       mbar_init(&sh.empty[s], kCW);
     }
     sh.abort_flag = 0;
-    sh.last_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   const int token = p.state[0], pos = p.state[1];
-  if (threadIdx.x < p.D / 2) {
+  if (threadIdx.x < D / 2) {
     // subgraph0_decode_simplify.mlir:52-59
     const float th = __fmul_rn(__ldg(p.inv_freq + threadIdx.x), (float)pos);
     sh.cs[threadIdx.x] = cosf(th);
@@ -631,19 +803,18 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
     // ================= producer: walk this CTA's weight stream =================
     if (lane == 0) {
       const uint8_t *src = p.stream + p.cta_off[blockIdx.x];
-      uint32_t g = 0;
+      uint32_t g = 0, par = 0;
+      int slot = 0;
       bool ok = true;
       for (int l = 0; l <= p.L && ok; ++l) {
         const int np = l < p.L ? 4 : 1;
         for (int pi = 0; pi < np && ok; ++pi) {
           const MegaPhase &ph = p.phase[l < p.L ? pi : 4];
           int rb, nrows;
-          rows_of(ph.N, blockIdx.x, gridDim.x, rb, nrows);
+          rows_of(ph, blockIdx.x, gridDim.x, rb, nrows);
           for (int r0 = 0; r0 < nrows; r0 += ph.rps) {
             const uint32_t bytes = (uint32_t)min(ph.rps, nrows - r0) * ph.row_bytes;
-            const int slot = g % p.slots;
-            const uint32_t use = g / p.slots;
-            if (!mbar_wait(&sh.empty[slot], (use & 1) ^ 1, err, &sh.abort_flag)) {
+            if (!mbar_wait(&sh.empty[slot], par ^ 1u, err, &sh.abort_flag)) {
               atomicCAS((int *)err, 0, 300 + slot);
               ok = false;
               break;
@@ -652,14 +823,20 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
             bulk_g2s(ring + (size_t)slot * p.slot_bytes, src, bytes, &sh.full[slot]);
             src += bytes;
             ++g;
+            if (++slot == p.slots) {
+              slot = 0;
+              par ^= 1u;
+            }
           }
         }
       }
       // never leave with copies of this CTA still in flight
       const uint32_t first = g > (uint32_t)p.slots ? g - p.slots : 0;
+      const unsigned long long t0 = now_ns();
       for (uint32_t s = first; s < g; ++s) {
         uint32_t it = 0;
-        while (!mbar_try_wait(&sh.full[s % p.slots], (s / p.slots) & 1) && ++it < (1u << 20)) {
+        while (!mbar_try_wait(&sh.full[s % p.slots], (s / p.slots) & 1) && ++it < (1u << 20) &&
+               now_ns() - t0 < kWaitNs) {
         }
       }
     }
@@ -667,61 +844,65 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
   }
 
   // ================= consumers ===================================================
-  const unsigned barriers_per_launch = 5u * (unsigned)p.L + 1u;
-  Ctx c{p, sh, ring, err, (int)threadIdx.x, lane, warp, 0u, 0u,
-        (unsigned)p.state[4] * barriers_per_launch * gridDim.x};
+  const uint32_t tags_per_launch = 8u * (uint32_t)(p.L + 3);
+  Ctx c{p, sh, xs, nws, ring, err, (int)threadIdx.x, lane, warp, 0, 0u,
+        ((uint32_t)p.state[4] + 1u) * tags_per_launch};
   float bestv = -INFINITY;
   int besti = 0x7fffffff;
-  const float *x_in = p.embed + (size_t)token * p.H;   // residual stream entering the layer
-  for (int l = 0; l < p.L; ++l) {
-    const float *in_norm = p.lvec[4 * l], *post_norm = p.lvec[4 * l + 1];
-    trace(c, l, 0);
-    {  // q | k | v  (+ bias) <- RMSNorm(x)
-      const XSrc xs{0, x_in, in_norm, nullptr, nullptr};
-      const Epi ep{EP_STORE, p.qkv, nullptr};
-      gemv_phase(c, p.phase[0], xs, ep, bestv, besti);
+  const int H = p.H, QD = p.qh * D, KD = p.kvh * D;
+  const float *embed_row = p.embed + (size_t)token * H;
+  // One loop over (layer, projection) so that the projection body exists once:
+  // step 0..3 of layer l = q|k|v, o, gate|up, down; layer L has the lm_head only.
+  for (int l = 0; l <= p.L; ++l) {
+    const int par = l & 1, ppar = par ^ 1;
+    const bool last = l == p.L;
+    // residual stream entering the layer: the embedding row, or layer l-1's output
+    const uint2 *xin_ll = l == 0 ? nullptr : p.ll_xa + (size_t)ppar * H;
+    const uint32_t xin_tag = tag_of(c, l - 1, T_XA);
+    const int nsteps = last ? 1 : 4;
+    for (int step = 0; step < nsteps; ++step) {
+      XSrc xsrc;
+      Epi ep;
+      int phase_index;
+      if (last) {              // logits <- RMSNorm(x) @ lm_head, with a running first-max
+        phase_index = 4;
+        xsrc = XSrc{xin_ll, embed_row, xin_tag, p.final_norm};
+        ep = Epi{EP_LOGITS, nullptr, 0u, nullptr, nullptr, 0u, p.logits};
+      } else if (step == 0) {  // q | k | v (+ bias) <- RMSNorm(x)
+        phase_index = 0;
+        xsrc = XSrc{xin_ll, embed_row, xin_tag, p.lvec[4 * l]};
+        ep = Epi{EP_STORE, p.ll_qkv + (size_t)par * (QD + 2 * KD), tag_of(c, l, T_QKV),
+                 nullptr, nullptr, 0u, nullptr};
+      } else if (step == 1) {  // x1 = x + attn @ Wo
+        phase_index = 1;
+        xsrc = XSrc{p.ll_attn + (size_t)par * QD, nullptr, tag_of(c, l, T_ATTN), nullptr};
+        ep = Epi{EP_RESIDUAL, p.ll_xb + (size_t)par * H, tag_of(c, l, T_XB),
+                 xin_ll, embed_row, xin_tag, nullptr};
+      } else if (step == 2) {  // silu(gate) * up <- RMSNorm(x1)
+        phase_index = 2;
+        xsrc = XSrc{p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), p.lvec[4 * l + 1]};
+        ep = Epi{EP_SILU, p.ll_mid + (size_t)par * p.F, tag_of(c, l, T_MID),
+                 nullptr, nullptr, 0u, nullptr};
+      } else {                 // x2 = x1 + mid @ Wdown
+        phase_index = 3;
+        xsrc = XSrc{p.ll_mid + (size_t)par * p.F, nullptr, tag_of(c, l, T_MID), nullptr};
+        ep = Epi{EP_RESIDUAL, p.ll_xa + (size_t)par * H, tag_of(c, l, T_XA),
+                 p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), nullptr};
+      }
+      trace(c, l, step);
+      gemv_phase(c, p.phase[phase_index], xsrc, ep, bestv, besti, l);
+      if (!last && step == 0) {
+        trace(c, l, 6);
+        {
+          Ctx ca = c;   // the attention functions take the context by address; keep `c` in registers
+          attention_dispatch(ca, l, pos);
+        }
+        trace(c, l, 7);
+      }
     }
-    trace(c, l, 1);
-    grid_barrier(c);
-    trace(c, l, 2);
-    attention_dispatch(c, l, pos);
-    trace(c, l, 3);
-    grid_barrier(c);
     trace(c, l, 4);
-    {  // x1 = x + attn @ Wo
-      const XSrc xs{0, p.attn, nullptr, nullptr, nullptr};
-      const Epi ep{EP_RESIDUAL, p.xb, x_in};
-      gemv_phase(c, p.phase[1], xs, ep, bestv, besti);
-    }
-    trace(c, l, 5);
-    grid_barrier(c);
-    trace(c, l, 6);
-    {  // gate | up <- RMSNorm(x1)
-      const XSrc xs{0, p.xb, post_norm, nullptr, nullptr};
-      const Epi ep{EP_STORE, p.gu, nullptr};
-      gemv_phase(c, p.phase[2], xs, ep, bestv, besti);
-    }
-    trace(c, l, 7);
-    grid_barrier(c);
-    trace(c, l, 8);
-    {  // x2 = x1 + (silu(gate) * up) @ Wdown
-      const XSrc xs{1, nullptr, nullptr, p.gu, p.gu + p.F};
-      const Epi ep{EP_RESIDUAL, p.xa, p.xb};
-      gemv_phase(c, p.phase[3], xs, ep, bestv, besti);
-    }
-    trace(c, l, 9);
-    grid_barrier(c);
-    trace(c, l, 10);
-    x_in = p.xa;
   }
-  {  // logits <- RMSNorm(x) @ lm_head, with a running first-max
-    const XSrc xs{0, x_in, p.final_norm, nullptr, nullptr};
-    const Epi ep{EP_LOGITS, p.logits, nullptr};
-    bestv = -INFINITY;
-    besti = 0x7fffffff;
-    trace(c, p.L, 0);
-    gemv_phase(c, p.phase[4], xs, ep, bestv, besti);
-    trace(c, p.L, 1);
+  {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
       const float ov = __shfl_xor_sync(0xffffffffu, bestv, o);
@@ -742,18 +923,21 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
           bestv = sh.bestv[w];
           besti = sh.besti[w];
         }
-      p.cand_val[blockIdx.x] = bestv;
-      p.cand_idx[blockIdx.x] = besti;
+      const uint32_t ctag = tag_of(c, p.L, T_CAND);
+      ll_store(p.ll_cand + 2 * blockIdx.x, bestv, ctag);
+      ll_store(p.ll_cand + 2 * blockIdx.x + 1, __int_as_float(besti), ctag);
     }
-    grid_barrier(c);
   }
-  if (blockIdx.x == 0 && c.warp == 0 && sh.abort_flag == 0) {
-    // Sampler.h:101-104: first maximum
+  if (blockIdx.x == 0 && c.warp == 0) {
+    // Sampler.h:101-104: first maximum over the per-CTA candidates
+    const uint32_t ctag = tag_of(c, p.L, T_CAND);
     float bv = -INFINITY;
     int bi = 0x7fffffff;
     for (int i = c.lane; i < (int)gridDim.x; i += 32) {
-      const float v = __ldcg(p.cand_val + i);
-      const int ix = __ldcg(p.cand_idx + i);
+      uint4 r = ll_load2(p.ll_cand + 2 * i);
+      r = ll_wait2(c, p.ll_cand + 2 * i, ctag, r);
+      const float v = __uint_as_float(r.x);
+      const int ix = (int)r.z;
       if (v > bv || (v == bv && ix < bi)) {
         bv = v;
         bi = ix;
@@ -768,7 +952,7 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
         bi = oi;
       }
     }
-    if (c.lane == 0) {
+    if (c.lane == 0 && sh.abort_flag == 0) {
       const int next = bi == 0x7fffffff ? 0 : bi;
       const int cnt = p.state[3];
       if (cnt < p.history_cap)
@@ -777,34 +961,35 @@ __global__ void __launch_bounds__(kMegaThreads, 1) decode_step_kernel(const Mega
       p.state[2] = next;
       p.state[0] = next;
       p.state[1] = pos + 1;
-      p.state[4] = p.state[4] + 1;   // launches completed (base of the barrier counter)
+      p.state[4] = p.state[4] + 1;   // launches completed (base of the tags)
     }
   }
 }
 
 // ---- stream builder: packed rows of one projection -> per-CTA streams ---------------
-// One CTA per source row: copies its K packed bytes and appends the 16-byte
-// trailer {scale, bias, 0, 0}.  The source holds rows [row_offset,
-// row_offset + gridDim.x) of a projection with N_total rows.
-__global__ void mega_build_rows_kernel(const uint8_t *src, int K, int row_offset, int N_total,
-                                       const float *scale, const float *bias, int grid_ctas,
-                                       int row_bytes, const int64_t *cta_phase_off,
-                                       uint8_t *stream) {
-  const int n = blockIdx.x + row_offset;
-  const int base = N_total / grid_ctas, rem = N_total % grid_ctas;
-  // owner CTA of row n under rows_of()
+// One CTA per source row: copies its K packed bytes (flipping the sign bit:
+// int8 q -> u = q + 128) and appends the 16-byte trailer {scale, bias, 0, 0}.
+// Source row r becomes row r * row_stride + row_phase of a projection with
+// N_total rows, dealt out to the CTAs in units of `unit` rows.
+__global__ void mega_build_rows_kernel(const uint8_t *src, int K, int row_stride, int row_phase,
+                                       int N_total, int unit, const float *scale,
+                                       const float *bias, int grid_ctas, int row_bytes,
+                                       const int64_t *cta_phase_off, uint8_t *stream) {
+  const int n = blockIdx.x * row_stride + row_phase;
+  const int nu = N_total / unit, un = n / unit;
+  const int base = nu / grid_ctas, rem = nu % grid_ctas;
   int cta;
   const int split = rem * (base + 1);
-  if (n < split)
-    cta = n / (base + 1);
+  if (un < split)
+    cta = un / (base + 1);
   else
-    cta = rem + (n - split) / base;
-  const int begin = cta * base + min(cta, rem);
+    cta = rem + (un - split) / base;
+  const int begin = (cta * base + min(cta, rem)) * unit;
   uint8_t *dst = stream + cta_phase_off[cta] + (int64_t)(n - begin) * row_bytes;
   const uint4 *s4 = reinterpret_cast<const uint4 *>(src + (int64_t)blockIdx.x * K);
   uint4 *d4 = reinterpret_cast<uint4 *>(dst);
   for (int i = threadIdx.x; i < K / 16; i += blockDim.x) {
-    uint4 v = s4[i];   // int8 q -> u = q + 128
+    uint4 v = s4[i];
     v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u;
     d4[i] = v;
   }
@@ -813,19 +998,18 @@ __global__ void mega_build_rows_kernel(const uint8_t *src, int K, int row_offset
         make_float4(scale[blockIdx.x], bias ? bias[blockIdx.x] : 0.f, 0.f, 0.f);
 }
 
-int mega_build_rows(const void *packed, int K, int n_rows, int row_offset, int N_total,
-                    const float *scale, const float *bias, int grid_ctas, int row_bytes,
-                    const int64_t *cta_phase_off_dev, void *stream_buf, cudaStream_t st) {
-  mega_build_rows_kernel<<<n_rows, 128, 0, st>>>((const uint8_t *)packed, K, row_offset, N_total,
-                                                 scale, bias, grid_ctas, row_bytes,
+int mega_build_rows(const void *packed, int K, int n_rows, int row_stride, int row_phase,
+                    int N_total, int unit, const float *scale, const float *bias, int grid_ctas,
+                    int row_bytes, const int64_t *cta_phase_off_dev, void *stream_buf,
+                    cudaStream_t st) {
+  mega_build_rows_kernel<<<n_rows, 128, 0, st>>>((const uint8_t *)packed, K, row_stride, row_phase,
+                                                 N_total, unit, scale, bias, grid_ctas, row_bytes,
                                                  cta_phase_off_dev, (uint8_t *)stream_buf);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
 
-size_t mega_shared_bytes(int slots, int slot_bytes) {
-  return ((sizeof(Shared) + 127) / 128) * 128 + (size_t)slots * slot_bytes;
-}
+size_t mega_fixed_shared_bytes() { return ((sizeof(Shared) + 127) / 128) * 128; }
 
 int mega_launch(const MegaParams &p, int grid, size_t smem, cudaStream_t st) {
   static bool configured = false;

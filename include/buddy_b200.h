@@ -277,7 +277,7 @@ int b200_model_kernels_per_step(const b200_model *m);
 int b200_model_uses_persistent_kernel(const b200_model *m);
 /* Tuning aid: with BUDDY_B200_TRACE=<stride> set at load time, every
  * stride-th CTA of the persistent kernel records the SM clock at each phase
- * boundary of the last step: host[cta/stride][layer][12]. Returns the number
+ * boundary of the last step: host[cta/stride][layer][32]. Returns the number
  * of values copied (negative on error). */
 int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity);
 /* Session handle -> device pointers, for tests. */
