@@ -390,7 +390,7 @@ int build_mega(b200_model *m) {
   const int grid = sms, L = c.n_layers, D = c.head_dim;
   int splits = grid / c.kv_heads;
   if (splits > 16) splits = 16;
-  if (!coop || splits < 1 || (G * D + splits - 1) / splits > 256 || G * splits > 256)
+  if (!coop || splits < 1 || (G * D + splits - 1) / splits > 512 || G * splits > 256)
     return B200_OK;  // stays on the graph path
   const int H = c.hidden, QD = c.q_heads * D, KD = c.kv_heads * D, F = c.ffn, V = c.vocab;
   MegaParams &p = m->mp;
@@ -404,7 +404,7 @@ int build_mega(b200_model *m) {
     ph.mode = Ks[i] <= 1536 ? 0 : 1;
     ph.unit = i == 2 ? 2 : 1;
     if (ph.mode == 0) {
-      ph.rps = 16;   // two rows per consumer warp
+      ph.rps = 16;   // one row per warp
     } else {
       ph.rps = (25000 / ph.row_bytes) & ~1;
       if (ph.rps < 2) ph.rps = 2;
@@ -416,14 +416,14 @@ int build_mega(b200_model *m) {
   }
   slot_bytes = (slot_bytes + 127) / 128 * 128;
   int xs_floats = maxK;
-  if (xs_floats < 8 * G * D) xs_floats = 8 * G * D;       // attention warp fold
+  if (xs_floats < 8 * G * D) xs_floats = 8 * G * D;       // attention fold of the 8 scanning warps
   if (xs_floats < (G + 2) * D) xs_floats = (G + 2) * D;   // staged q | k | v
   xs_floats = (xs_floats + 31) / 32 * 32;
   const int nws_floats = (H + 31) / 32 * 32;
   const size_t fixed = mega_fixed_shared_bytes() + (size_t)(xs_floats + nws_floats) * 4;
   int slots = (int)((227 * 1024 - 1024 - (long)fixed) / slot_bytes);
   if (slots > kMegaMaxSlots) slots = kMegaMaxSlots;
-  if (slots < 3)
+  if (slots < 4)   // the four stage groups of the kernel each need a slot
     return B200_OK;
   // per-phase, per-CTA stream offsets
   const int nph = 4 * L + 1;
@@ -519,6 +519,10 @@ int build_mega(b200_model *m) {
     if (int rc = dev_alloc((void **)&m->d_trace, n * 8)) return rc;
     B200_CUDA(cudaMemset(m->d_trace, 0, n * 8));
     p.trace = m->d_trace;
+    if (std::getenv("BUDDY_B200_DEBUG_STAGES"))
+      p.trace_stride |= 0x2000;   // tuning experiment: per-stage timestamps of the lm_head phase
+    if (std::getenv("BUDDY_B200_DEBUG_SKIP_DOT"))
+      p.trace_stride |= 0x1000;   // tuning experiment: consume the stream without the dot products
   }
   m->mega_grid = grid;
   m->mega_smem = fixed + (size_t)slots * slot_bytes;
@@ -1140,7 +1144,7 @@ int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega
 int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity) {
   if (!m || !host || !m->d_trace)
     return fail(B200_ESTATE, "read_trace: tracing is off (set BUDDY_B200_TRACE=<cta stride>)");
-  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * 32;
+  const int64_t n = (int64_t)(m->mega_grid / (m->mp.trace_stride & 0xFFF) + 1) * (m->cfg.n_layers + 1) * 32;
   B200_CUDA(cudaMemcpy(host, m->d_trace, (size_t)(n < capacity ? n : capacity) * 8,
                        cudaMemcpyDeviceToHost));
   return (int)(n < capacity ? n : capacity);

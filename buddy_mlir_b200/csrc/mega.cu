@@ -7,10 +7,12 @@
 //
 //  * Weights.  Each CTA owns a fixed slice of the output rows of every
 //    projection, and ALL weight bytes that CTA will ever need are laid out back
-//    to back in one private stream (built once at load time).  A producer warp
-//    walks that stream with bulk async copies (cp.async.bulk, completion on
-//    mbarriers) into a ring of shared-memory slots.  It never waits for
-//    activations, so HBM stays busy across the dependency points of the graph.
+//    to back in one private stream (built once at load time).  The stream is
+//    pulled with bulk async copies (cp.async.bulk, completion on mbarriers)
+//    into a ring of shared-memory slots; the warp that finishes a slot last
+//    immediately refills it with the stage one ring-length ahead.  Refills never
+//    wait for activations, so HBM stays busy across the dependency points of
+//    the graph (the ring holds about one projection's worth of weights).
 //  * Activations.  There is no grid-wide barrier.  Every activation vector
 //    that crosses CTAs (q|k|v, attention output, the two residual streams, the
 //    SiLU-gated MLP intermediate, attention split partials, argmax candidates)
@@ -21,8 +23,9 @@
 //    by at most one phase because every phase needs all outputs of the one
 //    before.  Buffers alternate by layer parity, so a producer can never
 //    overwrite a value a slower CTA still has to read.
-//  * Math.  Eight consumer warps dequantise from shared memory with the
-//    activations in registers and meet in warp-shuffle reductions.
+//  * Math.  Sixteen warps dequantise from shared memory with the activations
+//    in registers and meet in warp-shuffle reductions; groups of warps work on
+//    different ring slots at the same time.
 //
 // Every wait (mbarrier or tag poll) is bounded: on expiry the kernel records an
 // error code, all later waits fall through, control flow stays identical (so
@@ -41,8 +44,9 @@ namespace b200 {
 
 namespace {
 
-constexpr int kCW = 8;            // consumer warps
-constexpr int kCT = kCW * 32;     // consumer threads
+constexpr int kCW = 16;           // warps (all of them consume)
+constexpr int kCT = kCW * 32;     // threads
+constexpr int kAW = 8;            // warps that scan the KV cache in the attention phase
 constexpr uint32_t kSpinLimit = 1u << 26;      // poll count bound, and
 constexpr unsigned long long kWaitNs = 1000000000ull;  // wall-time bound (1 s) of any single wait
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -67,9 +71,6 @@ __device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
   asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)),
                "r"(bytes)
                : "memory");
-}
-__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
   uint32_t ok;
@@ -140,9 +141,24 @@ __device__ __forceinline__ uint4 ll_load2(const uint2 *p) {
   return v;
 }
 
+// Where stage g of this CTA's stream lives: stages per projection, rows, bytes.
+struct StreamPlan {
+  int n[5];            // stages of projection p in one layer (p = 4: lm_head)
+  int rows[5];         // rows of projection p owned by this CTA
+  int rps[5], row_bytes[5];
+  long long off[5];    // byte offset of projection p inside a layer's part of the stream
+  long long layer_bytes;
+  int per_layer;       // stages per layer
+  int total;           // stages per token
+  int L;
+};
+
 struct Shared {
   uint64_t full[kMegaMaxSlots];
-  uint64_t empty[kMegaMaxSlots];
+  int done[kMegaMaxSlots];              // warps that finished the slot's current stage
+  int issued[kMegaMaxSlots];            // stage last requested into the slot
+  StreamPlan plan;
+  const uint8_t *stream_base;
   float cs[64], sn[64];                 // cos / sin of this step's position
   float part[kCW][kMegaMaxRowsB];       // shared-row phases: per-warp partial sums
   float2 rowinfo[kMegaMaxRowsB];        // (scale, bias) of those rows
@@ -150,7 +166,7 @@ struct Shared {
   float bestv[kCW];
   int besti[kCW];
   int abort_flag;
-  float am[kCW][8], al[kCW][8];         // attention: per-warp (m, l)
+  float am[kAW][8], al[kAW][8];         // attention: per-warp (m, l)
   float cm[8 * 32], cl[8 * 32], cw[8 * 32], cL[8];  // attention: split fold
 };
 static_assert(offsetof(Shared, rowinfo) % 8 == 0, "rowinfo must be 8-byte aligned");
@@ -163,8 +179,9 @@ struct Ctx {
   uint8_t *ring;
   volatile int *err;
   int ctid, lane, warp;
-  int slot;           // ring slot of the next stage (same sequence as the producer's)
+  int slot;           // ring slot of the next stage
   uint32_t parity;    // parity of that slot's current use
+  int g;              // index of the next stage in this CTA's stream
   uint32_t tag_base;
 };
 
@@ -264,21 +281,32 @@ __device__ __forceinline__ float stage_plain(Ctx &c, const float *src, int n, fl
 }
 
 // Streamed rows hold u = q + 128 (the int8 weight with its sign bit flipped).
-// Byte e of a word, moved to the low byte of an otherwise zero word, IS the
-// float u * 2^-149 (a denormal), so the dequantisation is one PRMT and the
-// multiply-accumulate one FFMA per weight.  The activations are pre-scaled by
-// 2^64 to keep every product in the normal range (products are exact up to
-// the usual single rounding of the FMA), and the offset 128 * sum(x) is
-// subtracted once per row: sum x*q = 2^85 * sum (x*2^64)*(u*2^-149) - 128*sum x.
+// A byte left in place inside an otherwise zeroed word IS a float: bits 0-7
+// give u * 2^-149 (a denormal), bits 8-15 give u * 2^-141, bits 16-23 give
+// u * 2^-133 (the step from denormal to normal numbers is continuous), and
+// the top byte shifted down gives u * 2^-149 again.  So the dequantisation of
+// a weight is ONE logic op (LOP3 / SHF, which issue at twice the rate of a
+// byte permute) and its multiply-accumulate one FFMA.  The four byte positions
+// accumulate separately and are rescaled when they are added up.  The
+// activations are pre-scaled by 2^64 to keep every product in the normal range
+// (a product is exact up to the single rounding of the FMA), and the offset
+// 128 * sum(x) is subtracted once per row:
+//   sum x*q = 2^85 * (a0 + a1*2^-8 + a2*2^-16 + a3) - 128 * sum x.
 constexpr float kXScale = 18446744073709551616.0f;          // 2^64
 constexpr float kAccScale = 38685626227668133590597632.0f;  // 2^85
 __device__ __forceinline__ void dot_unit(const uint4 &w, const float (&x)[16], float (&a)[4]) {
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-  for (int j = 0; j < 4; ++j)
-#pragma unroll
-    for (int e = 0; e < 4; ++e)
-      a[e] = fmaf(x[4 * j + e], __uint_as_float(__byte_perm(ws[j], 0u, 0x4440 + e)), a[e]);
+  for (int j = 0; j < 4; ++j) {
+    a[0] = fmaf(x[4 * j + 0], __uint_as_float(ws[j] & 0x000000FFu), a[0]);
+    a[1] = fmaf(x[4 * j + 1], __uint_as_float(ws[j] & 0x0000FF00u), a[1]);
+    a[2] = fmaf(x[4 * j + 2], __uint_as_float(ws[j] & 0x00FF0000u), a[2]);
+    a[3] = fmaf(x[4 * j + 3], __uint_as_float(ws[j] >> 24), a[3]);
+  }
+}
+// a0 + a1 * 2^-8 + a2 * 2^-16 + a3 (the scalings are exact)
+__device__ __forceinline__ float dot_total(const float (&a)[4]) {
+  return (a[0] + a[3]) + fmaf(a[1], 0.00390625f, a[2] * 0.0000152587890625f);
 }
 
 __device__ __forceinline__ void rows_of(const MegaPhase &ph, int cta, int grid, int &begin,
@@ -290,10 +318,61 @@ __device__ __forceinline__ void rows_of(const MegaPhase &ph, int cta, int grid, 
   count = (base + (cta < rem ? 1 : 0)) * ph.unit;
 }
 
+// Request stage g of this CTA's stream into ring slot `slot` (one thread).
+__device__ __forceinline__ void issue_stage(Shared &sh, uint8_t *ring, int slot_bytes, int slot,
+                                            int g) {
+  const StreamPlan &pl = sh.plan;
+  if (g >= pl.total)
+    return;
+  int l = g / pl.per_layer, r = g - l * pl.per_layer, ph = 0;
+  if (l >= pl.L) {   // the lm_head follows the layers
+    ph = 4;
+    r = g - pl.L * pl.per_layer;
+    l = pl.L;
+  } else {
+    while (r >= pl.n[ph]) {
+      r -= pl.n[ph];
+      ++ph;
+    }
+  }
+  const int rows = min(pl.rps[ph], pl.rows[ph] - r * pl.rps[ph]);
+  const uint32_t bytes = (uint32_t)rows * pl.row_bytes[ph];
+  const uint8_t *src = sh.stream_base + (long long)l * pl.layer_bytes + (ph == 4 ? 0 : pl.off[ph]) +
+                       (long long)r * pl.rps[ph] * pl.row_bytes[ph];
+  *(volatile int *)&sh.issued[slot] = g;
+  mbar_expect_tx(&sh.full[slot], bytes);
+  bulk_g2s(ring + (size_t)slot * slot_bytes, src, bytes, &sh.full[slot]);
+}
+
+// Wait until stage `want` has landed in `slot`.  The parity of an mbarrier only
+// tells consecutive uses of a slot apart; warp groups work on different stages
+// and can run more than one use ahead of the group that still owns the slot, so
+// the wait first makes sure the slot has been re-requested for the wanted stage.
+__device__ __forceinline__ bool stage_wait(Shared &sh, int slot, uint32_t parity, int want,
+                                           volatile int *err, volatile int *ab) {
+  volatile int *iq = &sh.issued[slot];
+  if (*iq != want) {
+    unsigned long long t0 = 0;
+    uint32_t it = 0;
+    while (*iq != want && !*ab) {
+      if ((++it & 0x3FF) == 0) {
+        const unsigned long long t = now_ns();
+        if (t0 == 0)
+          t0 = t;
+        if (*err != 0 || t - t0 > kWaitNs) {
+          *ab = 1;
+          break;
+        }
+      }
+    }
+  }
+  return mbar_wait(&sh.full[slot], parity, err, ab);
+}
+
 // Optional per-phase timeline (SM clock) of a few CTAs, for tuning.
 __device__ __forceinline__ void trace(Ctx &c, int layer, int slot) {
-  if (c.p.trace != nullptr && c.ctid == 0 && (blockIdx.x % c.p.trace_stride) == 0)
-    c.p.trace[((size_t)(blockIdx.x / c.p.trace_stride) * (c.p.L + 1) + layer) * 32 + slot] =
+  if (c.p.trace != nullptr && c.ctid == 0 && (blockIdx.x % (c.p.trace_stride & 0xFFF)) == 0)
+    c.p.trace[((size_t)(blockIdx.x / (c.p.trace_stride & 0xFFF)) * (c.p.L + 1) + layer) * 32 + slot] =
         clock64();
 }
 
@@ -354,7 +433,7 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
   const int lane = c.lane, warp = c.warp, ctid = c.ctid;
   uint8_t *const ring = c.ring;
   float *const xsm = c.xs, *const nwsm = c.nws;
-  int slot = c.slot;
+  int slot = c.slot, g = c.g;
   uint32_t parity = c.parity;
 
   // ---- stage the activation vector (and the norm weight) in shared memory ----
@@ -383,7 +462,7 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
   float sx = 0.f;
 #pragma unroll
   for (int i = 0; i < 3; ++i) {
-    const int u = mode == 0 ? (i * 32 + lane) : (i * kCT + ctid);
+    const int u = mode == 0 ? (i * 32 + lane) : (i * 256 + (ctid & 255));
 #pragma unroll
     for (int e = 0; e < 16; ++e)
       xr[i][e] = 0.f;
@@ -413,97 +492,141 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
   trace(c, tl, 13 + 4 * (int)(&ph - c.p.phase));
 
   // ---- stream the rows --------------------------------------------------------
+  // The warps are split into stage groups that work on DIFFERENT stages at the
+  // same time (mode A: 4 groups of 4 warps, a warp takes 4 rows of its stage;
+  // mode B: 2 groups of 8 warps sharing each row).  Each visit of a warp to a
+  // stage then carries enough arithmetic to amortise the fixed latencies of a
+  // visit (barrier wait, reduction, trailer, stores, slot release), and the
+  // groups hide each other's latencies.
   volatile int *ab = &sh.abort_flag;
+  const int NG = mode == 0 ? 4 : 2;
+  const int gw = kCW / NG;                       // warps per group
+  const int grp = warp / gw, wig = warp - grp * gw;
+  const int nstages = (nrows + rps - 1) / rps;
+  const int nrounds = (nstages + NG - 1) / NG;
+  int my_slot = slot + grp;
+  uint32_t my_par = parity;
+  if (my_slot >= n_slots) {
+    my_slot -= n_slots;
+    my_par ^= 1u;
+  }
   int flush_base = 0;
-  for (int r0 = 0; r0 < nrows; r0 += rps) {
-    const int rows = min(rps, nrows - r0);
-    if (!mbar_wait(&sh.full[slot], parity, c.err, ab))
-      atomicCAS((int *)c.err, 0, 200 + slot);
-    const uint8_t *base = ring + (size_t)slot * slot_bytes;
-    if (mode == 0) {
-      // rows 2w and 2w+1 of the slot; the clamp keeps the loads inside the slot
-      const int ra = 2 * warp, rb = ra + 1;
-      const uint8_t *rowa = base + (size_t)min(ra, rows - 1) * row_bytes;
-      const uint8_t *rowb = base + (size_t)min(rb, rows - 1) * row_bytes;
-      float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+  for (int rd = 0; rd < nrounds; ++rd) {
+    const int st = rd * NG + grp;
+    if (st < nstages) {
+      const int r0 = st * rps;
+      const int rows = min(rps, nrows - r0);
+      if (!stage_wait(sh, my_slot, my_par, g + st, c.err, ab))
+        atomicCAS((int *)c.err, 0, 200 + my_slot);
+      const uint8_t *base = ring + (size_t)my_slot * slot_bytes;
+      if (mode == 0) {
+        // rows 4*wig .. 4*wig+3 of the stage; the clamp keeps the loads inside it
+        const uint8_t *rp[4];
+        float a[4][4];
 #pragma unroll
-      for (int i = 0; i < 3; ++i) {
-        const int u = i * 32 + lane;
-        if (u < units) {
-          const uint4 wa = *reinterpret_cast<const uint4 *>(rowa + u * 16);
-          const uint4 wb = *reinterpret_cast<const uint4 *>(rowb + u * 16);
-          dot_unit(wa, xr[i], a);
-          dot_unit(wb, xr[i], b);
+        for (int q = 0; q < 4; ++q) {
+          rp[q] = base + (size_t)min(4 * wig + q, rows - 1) * row_bytes;
+          a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
         }
-      }
-      float va = fmaf((a[0] + a[1]) + (a[2] + a[3]), kAccScale, off);
-      float vb = fmaf((b[0] + b[1]) + (b[2] + b[3]), kAccScale, off);
-      va = warp_sum(va);
-      vb = warp_sum(vb);
-      const float2 ta = *reinterpret_cast<const float2 *>(rowa + K);
-      const float2 tb = *reinterpret_cast<const float2 *>(rowb + K);
-      va = __fadd_rn(__fmul_rn(va, ta.x), ta.y);
-      vb = __fadd_rn(__fmul_rn(vb, tb.x), tb.y);
-      if (ep.kind == EP_SILU) {
-        // rows (2j, 2j+1) = (gate_j, up_j)
-        if (lane == 0 && rb < rows)
-          ll_store(ep.dst + ((row_begin + r0 + ra) >> 1), silu_mul(va, vb), ep.tag);
-      } else {
-        if (lane == 0 && ra < rows)
-          emit(c, ep, row_begin + r0 + ra, va, bestv, besti);
-        if (lane == 1 && rb < rows)
-          emit(c, ep, row_begin + r0 + rb, vb, bestv, besti);
-      }
-    } else {
-      for (int r = 0; r < rows; r += 2) {
-        const uint8_t *rowa = base + (size_t)r * row_bytes;
-        const uint8_t *rowb = base + (size_t)min(r + 1, rows - 1) * row_bytes;
-        float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int i = 0; i < 3; ++i) {
-          const int u = i * kCT + ctid;
-          if (u < units) {
-            const uint4 wa = *reinterpret_cast<const uint4 *>(rowa + u * 16);
-            const uint4 wb = *reinterpret_cast<const uint4 *>(rowb + u * 16);
-            dot_unit(wa, xr[i], a);
-            dot_unit(wb, xr[i], b);
+          const int u = i * 32 + lane;
+          if (u < units && !(c.p.trace_stride & 0x1000)) {
+            uint4 w[4];
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              w[q] = *reinterpret_cast<const uint4 *>(rp[q] + u * 16);
+#pragma unroll
+            for (int q = 0; q < 4; ++q)
+              dot_unit(w[q], xr[i], a[q]);
           }
         }
-        float va = fmaf((a[0] + a[1]) + (a[2] + a[3]), kAccScale, off);
-        float vb = fmaf((b[0] + b[1]) + (b[2] + b[3]), kAccScale, off);
-        va = warp_sum(va);
-        vb = warp_sum(vb);
-        if (lane == 0) {
-          sh.part[warp][r0 + r - flush_base] = va;
-          if (r + 1 < rows)
-            sh.part[warp][r0 + r + 1 - flush_base] = vb;
+        float v[4];
+#pragma unroll
+        for (int q = 0; q < 4; ++q)
+          v[q] = fmaf(dot_total(a[q]), kAccScale, off);
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+          for (int q = 0; q < 4; ++q)
+            v[q] += __shfl_xor_sync(0xffffffffu, v[q], o);
+        // lane q finishes row q
+        const int q = lane & 3;
+        const float mine = q == 0 ? v[0] : q == 1 ? v[1] : q == 2 ? v[2] : v[3];
+        const uint8_t *myrow = q == 0 ? rp[0] : q == 1 ? rp[1] : q == 2 ? rp[2] : rp[3];
+        const float2 t = *reinterpret_cast<const float2 *>(myrow + K);
+        const float val = __fadd_rn(__fmul_rn(mine, t.x), t.y);
+        const int row = 4 * wig + q;
+        if (ep.kind == EP_SILU) {
+          // rows (2j, 2j+1) = (gate_j, up_j)
+          const float upv = __shfl_down_sync(0xffffffffu, val, 1);
+          if (lane < 4 && (lane & 1) == 0 && row + 1 < rows)
+            ll_store(ep.dst + ((row_begin + r0 + row) >> 1), silu_mul(val, upv), ep.tag);
+        } else if (lane < 4 && row < rows) {
+          emit(c, ep, row_begin + r0 + row, val, bestv, besti);
         }
-        if (ctid == 0) {
-          sh.rowinfo[r0 + r - flush_base] = *reinterpret_cast<const float2 *>(rowa + K);
-          if (r + 1 < rows)
-            sh.rowinfo[r0 + r + 1 - flush_base] = *reinterpret_cast<const float2 *>(rowb + K);
+      } else {
+        const int tig = ctid & 255;   // thread within the group
+        for (int r = 0; r < rows; r += 2) {
+          const uint8_t *rowa = base + (size_t)r * row_bytes;
+          const uint8_t *rowb = base + (size_t)min(r + 1, rows - 1) * row_bytes;
+          float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+          for (int i = 0; i < 3; ++i) {
+            const int u = i * 256 + tig;
+            if (u < units) {
+              const uint4 wa = *reinterpret_cast<const uint4 *>(rowa + u * 16);
+              const uint4 wb = *reinterpret_cast<const uint4 *>(rowb + u * 16);
+              dot_unit(wa, xr[i], a);
+              dot_unit(wb, xr[i], b);
+            }
+          }
+          float va = fmaf(dot_total(a), kAccScale, off);
+          float vb = fmaf(dot_total(b), kAccScale, off);
+          va = warp_sum(va);
+          vb = warp_sum(vb);
+          if (lane == 0) {
+            sh.part[warp][r0 + r - flush_base] = va;
+            if (r + 1 < rows)
+              sh.part[warp][r0 + r + 1 - flush_base] = vb;
+          }
+          if (tig == 0) {
+            sh.rowinfo[r0 + r - flush_base] = *reinterpret_cast<const float2 *>(rowa + K);
+            if (r + 1 < rows)
+              sh.rowinfo[r0 + r + 1 - flush_base] = *reinterpret_cast<const float2 *>(rowb + K);
+          }
         }
       }
+      // Release the slot; the warp of the group that finishes it last refills it
+      // with the stage one ring-length ahead.  (No fence on purpose: the slot's
+      // bytes were consumed by arithmetic the values above depend on, so every
+      // read has completed; the counter reset is ordered before the next use of
+      // the slot by the arrival of that stage's data.)
+      __syncwarp();
+      if (lane == 0 && atomicAdd(&sh.done[my_slot], 1) == gw - 1) {
+        sh.done[my_slot] = 0;
+        issue_stage(sh, ring, slot_bytes, my_slot, g + st + n_slots);
+      }
     }
-    __syncwarp();
-    if (lane == 0)
-      mbar_arrive(&sh.empty[slot]);
-    if (++slot == n_slots) {
-      slot = 0;
-      parity ^= 1u;
+    my_slot += NG;
+    if (my_slot >= n_slots) {
+      my_slot -= n_slots;
+      my_par ^= 1u;
     }
     if (mode == 1) {
-      const int pending = r0 + rows - flush_base;
-      if (pending + rps > kMegaMaxRowsB || r0 + rows >= nrows) {
+      const int covered = min(nrows, (rd + 1) * NG * rps);
+      const int pending = covered - flush_base;
+      if (pending + NG * rps > kMegaMaxRowsB || rd + 1 == nrounds) {
         // fold the per-warp partial sums of the pending rows (fixed warp order)
         consumer_sync();
         auto row_value = [&](int i) {
-          float s = 0.f;
+          const int owner = ((flush_base + i) / rps) % NG;   // group that streamed this row
+          float sacc = 0.f;
 #pragma unroll
-          for (int w = 0; w < kCW; ++w)
-            s += sh.part[w][i];
+          for (int w = 0; w < 8; ++w)
+            sacc += sh.part[owner * 8 + w][i];
           const float2 t = sh.rowinfo[i];
-          return __fadd_rn(__fmul_rn(s, t.x), t.y);
+          return __fadd_rn(__fmul_rn(sacc, t.x), t.y);
         };
         if (ep.kind == EP_SILU) {
           if (ctid < pending / 2)
@@ -513,12 +636,21 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
           emit(c, ep, row_begin + flush_base + ctid, row_value(ctid), bestv, besti);
         }
         consumer_sync();
-        flush_base = r0 + rows;
+        flush_base = covered;
       }
     }
   }
+  // this phase used `nstages` stages of the ring
+  g += nstages;
+  slot += nstages % n_slots;
+  parity ^= (uint32_t)((nstages / n_slots) & 1);
+  if (slot >= n_slots) {
+    slot -= n_slots;
+    parity ^= 1u;
+  }
   c.slot = slot;
   c.parity = parity;
+  c.g = g;
   // the staged vector is reused by the next phase
   consumer_sync();
 }
@@ -526,8 +658,8 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
 // ---- attention -------------------------------------------------------------------
 // Work item = (kv head, split).  The CTA stages q|k|v of its kv head, applies
 // (QK-norm and) RoPE to the G query heads, the CTA whose range holds `pos` also
-// rotates the new key and writes the K/V row; every warp scans every 8th row of
-// the range with four rows in flight; the CTA folds its warps and publishes the
+// rotates the new key and writes the K/V row; eight warps scan every 8th row of
+// the range with several rows in flight; the CTA folds its warps and publishes the
 // split partial; then every CTA of the kv head folds one slice of the outputs
 // over all splits (in split order: the result does not depend on timing).
 template <int G>
@@ -625,13 +757,13 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
     l[g] = 0.f;
     acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
   }
-  constexpr int NB = G <= 6 ? 4 : 2;   // rows in flight per warp
-  for (int j0 = s0 + warp; j0 < s1; j0 += NB * kCW) {
+  constexpr int NB = G <= 4 ? 4 : 2;   // rows in flight per warp (register budget: 128)
+  for (int j0 = s0 + warp; j0 < s1 && warp < kAW; j0 += NB * kAW) {
     // NB rows in flight: all loads are issued before the first use
     float4 kr[NB], vr[NB];
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
-      const int j = min(j0 + i * kCW, s1 - 1);
+      const int j = min(j0 + i * kAW, s1 - 1);
       kr[i] = ldcg4(kc + (size_t)j * D + 4 * lane);
       vr[i] = ldcg4(vc + (size_t)j * D + 4 * lane);
     }
@@ -652,7 +784,7 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
         s[i][g] = warp_sum(s[i][g]) * scale;
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
-      if (j0 + i * kCW < s1) {   // warp-uniform
+      if (j0 + i * kAW < s1) {   // warp-uniform
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           const float nm = fmaxf(m[g], s[i][g]);
@@ -669,15 +801,17 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
   }
   trace(c, layer, 9);
   // ---- fold the warps of this CTA (fixed warp order) ------------------------------
-  float *aacc = c.xs;   // [kCW][G][D]
+  float *aacc = c.xs;   // [kAW][G][D]
+  if (warp < kAW) {
 #pragma unroll
-  for (int g = 0; g < G; ++g) {
-    if (lane == 0) {
-      c.sh.am[warp][g] = m[g];
-      c.sh.al[warp][g] = l[g];
+    for (int g = 0; g < G; ++g) {
+      if (lane == 0) {
+        c.sh.am[warp][g] = m[g];
+        c.sh.al[warp][g] = l[g];
+      }
+      *reinterpret_cast<float4 *>(aacc + ((size_t)warp * G + g) * D + 4 * lane) =
+          make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
     }
-    *reinterpret_cast<float4 *>(aacc + ((size_t)warp * G + g) * D + 4 * lane) =
-        make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
   }
   consumer_sync();
   const int stride = D + 2;
@@ -687,11 +821,11 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
     const int g = idx / D, d = idx - g * D;
     float M = kSeed;
 #pragma unroll
-    for (int w = 0; w < kCW; ++w)
+    for (int w = 0; w < kAW; ++w)
       M = fmaxf(M, c.sh.am[w][g]);
     float L = 0.f, A = 0.f;
 #pragma unroll
-    for (int w = 0; w < kCW; ++w) {
+    for (int w = 0; w < kAW; ++w) {
       const float b = expf(c.sh.am[w][g] - M);
       L = fmaf(c.sh.al[w][g], b, L);
       A = fmaf(aacc[((size_t)w * G + g) * D + d], b, A);
@@ -785,10 +919,34 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.slots; ++s) {
       mbar_init(&sh.full[s], 1);
-      mbar_init(&sh.empty[s], kCW);
+      sh.done[s] = 0;
+      sh.issued[s] = -1;
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    // this CTA's stream plan
+    StreamPlan &pl = sh.plan;
+    long long off = 0;
+    pl.per_layer = 0;
+    for (int i = 0; i < 5; ++i) {
+      int rb, nr;
+      rows_of(p.phase[i], blockIdx.x, gridDim.x, rb, nr);
+      pl.rows[i] = nr;
+      pl.rps[i] = p.phase[i].rps;
+      pl.row_bytes[i] = p.phase[i].row_bytes;
+      pl.n[i] = (nr + pl.rps[i] - 1) / pl.rps[i];
+      if (i < 4) {
+        pl.off[i] = off;
+        off += (long long)nr * pl.row_bytes[i];
+        pl.per_layer += pl.n[i];
+      } else {
+        pl.off[i] = 0;
+      }
+    }
+    pl.layer_bytes = off;
+    pl.L = p.L;
+    pl.total = p.L * pl.per_layer + pl.n[4];
+    sh.stream_base = p.stream + p.cta_off[blockIdx.x];
   }
   const int token = p.state[0], pos = p.state[1];
   if (threadIdx.x < D / 2) {
@@ -798,54 +956,13 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
     sh.sn[threadIdx.x] = sinf(th);
   }
   __syncthreads();
-
-  if (warp == kCW) {
-    // ================= producer: walk this CTA's weight stream =================
-    if (lane == 0) {
-      const uint8_t *src = p.stream + p.cta_off[blockIdx.x];
-      uint32_t g = 0, par = 0;
-      int slot = 0;
-      bool ok = true;
-      for (int l = 0; l <= p.L && ok; ++l) {
-        const int np = l < p.L ? 4 : 1;
-        for (int pi = 0; pi < np && ok; ++pi) {
-          const MegaPhase &ph = p.phase[l < p.L ? pi : 4];
-          int rb, nrows;
-          rows_of(ph, blockIdx.x, gridDim.x, rb, nrows);
-          for (int r0 = 0; r0 < nrows; r0 += ph.rps) {
-            const uint32_t bytes = (uint32_t)min(ph.rps, nrows - r0) * ph.row_bytes;
-            if (!mbar_wait(&sh.empty[slot], par ^ 1u, err, &sh.abort_flag)) {
-              atomicCAS((int *)err, 0, 300 + slot);
-              ok = false;
-              break;
-            }
-            mbar_expect_tx(&sh.full[slot], bytes);
-            bulk_g2s(ring + (size_t)slot * p.slot_bytes, src, bytes, &sh.full[slot]);
-            src += bytes;
-            ++g;
-            if (++slot == p.slots) {
-              slot = 0;
-              par ^= 1u;
-            }
-          }
-        }
-      }
-      // never leave with copies of this CTA still in flight
-      const uint32_t first = g > (uint32_t)p.slots ? g - p.slots : 0;
-      const unsigned long long t0 = now_ns();
-      for (uint32_t s = first; s < g; ++s) {
-        uint32_t it = 0;
-        while (!mbar_try_wait(&sh.full[s % p.slots], (s / p.slots) & 1) && ++it < (1u << 20) &&
-               now_ns() - t0 < kWaitNs) {
-        }
-      }
-    }
-    return;
-  }
+  if (threadIdx.x == 0)   // fill the ring
+    for (int s = 0; s < p.slots; ++s)
+      issue_stage(sh, ring, p.slot_bytes, s, s);
 
   // ================= consumers ===================================================
   const uint32_t tags_per_launch = 8u * (uint32_t)(p.L + 3);
-  Ctx c{p, sh, xs, nws, ring, err, (int)threadIdx.x, lane, warp, 0, 0u,
+  Ctx c{p, sh, xs, nws, ring, err, (int)threadIdx.x, lane, warp, 0, 0u, 0,
         ((uint32_t)p.state[4] + 1u) * tags_per_launch};
   float bestv = -INFINITY;
   int besti = 0x7fffffff;
@@ -962,6 +1079,13 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
       p.state[0] = next;
       p.state[1] = pos + 1;
       p.state[4] = p.state[4] + 1;   // launches completed (base of the tags)
+    }
+  }
+  if (sh.abort_flag) {
+    // an abandoned step may still have ring copies in flight: give them time
+    // to land before the CTA (and its shared memory) goes away
+    const unsigned long long t0 = now_ns();
+    while (now_ns() - t0 < 2000000ull) {
     }
   }
 }

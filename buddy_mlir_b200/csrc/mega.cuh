@@ -5,7 +5,7 @@
 
 namespace b200 {
 
-constexpr int kMegaThreads = 288;      // 8 consumer warps + 1 producer warp
+constexpr int kMegaThreads = 512;      // 16 warps
 constexpr int kMegaMaxSlots = 16;
 constexpr int kMegaMaxRowsB = 64;      // rows of a shared-row phase finalised per flush
 constexpr int kMegaTrailer = 16;       // bytes appended to every streamed row: scale, bias
@@ -14,7 +14,7 @@ struct MegaPhase {
   int K, N;
   int row_bytes;   // K + trailer
   int rps;         // rows per ring slot (even)
-  int mode;        // 0: a warp owns two rows of a slot; 1: all consumer threads share each row
+  int mode;        // 0: a warp owns one row of a slot; 1: all threads share each row
   int unit;        // rows are dealt to CTAs in multiples of this (2 keeps gate/up pairs together)
 };
 
