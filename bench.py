@@ -231,6 +231,7 @@ def run_single(args):
     s.load_blobs("f32", blob, all_linear_w8=True)
     for b in range(2 * cfg.n_layers):
         s.kv_upload(b, kv_prefix(cfg, start, b), 0, start)
+    persistent = s.uses_persistent_kernel()
     s.position_ = start
     tok = 11
     warm_ids = s.generate(tok, warmup) if warmup > 0 else [tok]
@@ -286,7 +287,7 @@ def run_single(args):
             "data": "synthetic", "config": workload_config(cfg, start, args),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
                          "frac": achieved / hbm, "traffic": traffic, "peak_source": which,
-                         "kernel": "whole decode step (CUDA graph replay)",
+                         "kernel": "decode_step_kernel (one persistent launch per token)" if persistent else "whole decode step (CUDA graph replay)",
                          "bytes_per_step": step_bytes, "frac_of_8TBs_nominal": achieved / 8000.0},
             "gemv_int8_isolated": gemv,
             "cpu_baseline": base,

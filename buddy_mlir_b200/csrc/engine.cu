@@ -519,10 +519,6 @@ int build_mega(b200_model *m) {
     if (int rc = dev_alloc((void **)&m->d_trace, n * 8)) return rc;
     B200_CUDA(cudaMemset(m->d_trace, 0, n * 8));
     p.trace = m->d_trace;
-    if (std::getenv("BUDDY_B200_DEBUG_STAGES"))
-      p.trace_stride |= 0x2000;   // tuning experiment: per-stage timestamps of the lm_head phase
-    if (std::getenv("BUDDY_B200_DEBUG_SKIP_DOT"))
-      p.trace_stride |= 0x1000;   // tuning experiment: consume the stream without the dot products
   }
   m->mega_grid = grid;
   m->mega_smem = fixed + (size_t)slots * slot_bytes;
@@ -1144,7 +1140,7 @@ int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega
 int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity) {
   if (!m || !host || !m->d_trace)
     return fail(B200_ESTATE, "read_trace: tracing is off (set BUDDY_B200_TRACE=<cta stride>)");
-  const int64_t n = (int64_t)(m->mega_grid / (m->mp.trace_stride & 0xFFF) + 1) * (m->cfg.n_layers + 1) * 32;
+  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * 32;
   B200_CUDA(cudaMemcpy(host, m->d_trace, (size_t)(n < capacity ? n : capacity) * 8,
                        cudaMemcpyDeviceToHost));
   return (int)(n < capacity ? n : capacity);

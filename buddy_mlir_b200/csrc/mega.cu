@@ -208,6 +208,7 @@ __device__ __forceinline__ float ll_wait1(Ctx &c, const uint2 *p, uint32_t tag) 
       *ab = 1;
       break;
     }
+    __nanosleep(it < 4 ? 40 : 200);   // keep the pollers of 148 CTAs from flooding L2
     v = ll_load1(p);
   }
   return __uint_as_float(v.x);
@@ -229,6 +230,7 @@ __device__ __forceinline__ uint4 ll_wait2(Ctx &c, const uint2 *p, uint32_t tag, 
       *ab = 1;
       break;
     }
+    __nanosleep(it < 4 ? 40 : 200);   // keep the pollers of 148 CTAs from flooding L2
     v = ll_load2(p);
   }
   return v;
@@ -371,8 +373,8 @@ __device__ __forceinline__ bool stage_wait(Shared &sh, int slot, uint32_t parity
 
 // Optional per-phase timeline (SM clock) of a few CTAs, for tuning.
 __device__ __forceinline__ void trace(Ctx &c, int layer, int slot) {
-  if (c.p.trace != nullptr && c.ctid == 0 && (blockIdx.x % (c.p.trace_stride & 0xFFF)) == 0)
-    c.p.trace[((size_t)(blockIdx.x / (c.p.trace_stride & 0xFFF)) * (c.p.L + 1) + layer) * 32 + slot] =
+  if (c.p.trace != nullptr && c.ctid == 0 && (blockIdx.x % c.p.trace_stride) == 0)
+    c.p.trace[((size_t)(blockIdx.x / c.p.trace_stride) * (c.p.L + 1) + layer) * 32 + slot] =
         clock64();
 }
 
@@ -413,6 +415,67 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   // subgraph0_decode_simplify.mlir:226-231: (g * sigmoid(g)) * u
   const float s = 1.0f / (1.0f + expf(-g));
   return __fmul_rn(__fmul_rn(g, s), u);
+}
+
+// One visit of a warp to a stage of a warp-per-row projection: the warp takes
+// rows R*wig .. R*wig+R-1 of the stage (R = 4, or 1 when all 16 warps share a
+// single stage), multiplies them with its 48 activations and finishes them.
+template <int R>
+__device__ __forceinline__ void visit_rows(Ctx &c, const Epi &ep, const uint8_t *base, int rows,
+                                           int row_bytes, int K, int units, int wig, int lane,
+                                           const float (&xr)[3][16], float off, int first_row,
+                                           float &bestv, int &besti) {
+  // the clamp keeps the loads inside the stage
+  const uint8_t *rp[R];
+  float a[R][4];
+#pragma unroll
+  for (int q = 0; q < R; ++q) {
+    rp[q] = base + (size_t)min(R * wig + q, rows - 1) * row_bytes;
+    a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
+  }
+#pragma unroll
+  for (int i = 0; i < 3; ++i) {
+    const int u = i * 32 + lane;
+    if (u < units) {
+      uint4 w[R];
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+        w[q] = *reinterpret_cast<const uint4 *>(rp[q] + u * 16);
+#pragma unroll
+      for (int q = 0; q < R; ++q)
+        dot_unit(w[q], xr[i], a[q]);
+    }
+  }
+  float v[R];
+#pragma unroll
+  for (int q = 0; q < R; ++q)
+    v[q] = fmaf(dot_total(a[q]), kAccScale, off);
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+    for (int q = 0; q < R; ++q)
+      v[q] += __shfl_xor_sync(0xffffffffu, v[q], o);
+  // lane q finishes row q
+  const int q = lane & (R - 1);
+  float mine = v[0];
+  const uint8_t *myrow = rp[0];
+#pragma unroll
+  for (int t = 1; t < R; ++t)
+    if (q == t) {
+      mine = v[t];
+      myrow = rp[t];
+    }
+  const float2 tr = *reinterpret_cast<const float2 *>(myrow + K);
+  const float val = __fadd_rn(__fmul_rn(mine, tr.x), tr.y);
+  const int row = R * wig + q;
+  if (ep.kind == EP_SILU) {
+    // rows (2j, 2j+1) = (gate_j, up_j); only reached with R = 4
+    const float upv = __shfl_down_sync(0xffffffffu, val, 1);
+    if (lane < R && (lane & 1) == 0 && row + 1 < rows)
+      ll_store(ep.dst + ((first_row + row) >> 1), silu_mul(val, upv), ep.tag);
+  } else if (lane < R && row < rows) {
+    emit(c, ep, first_row + row, val, bestv, besti);
+  }
 }
 
 // One projection.  Mode A (K <= 1536): a warp owns two adjacent rows of every
@@ -499,10 +562,13 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
   // visit (barrier wait, reduction, trailer, stores, slot release), and the
   // groups hide each other's latencies.
   volatile int *ab = &sh.abort_flag;
-  const int NG = mode == 0 ? 4 : 2;
+  const int nstages = (nrows + rps - 1) / rps;
+  // mode A: 4 rows per warp, except for projections of one or two stages (q|k|v,
+  // o), where all 16 warps take one row each of the same stage
+  const int R = (nstages >= 3 || ep.kind == EP_SILU) ? 4 : 1;
+  const int NG = mode == 0 ? R : 2;
   const int gw = kCW / NG;                       // warps per group
   const int grp = warp / gw, wig = warp - grp * gw;
-  const int nstages = (nrows + rps - 1) / rps;
   const int nrounds = (nstages + NG - 1) / NG;
   int my_slot = slot + grp;
   uint32_t my_par = parity;
@@ -520,51 +586,12 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
         atomicCAS((int *)c.err, 0, 200 + my_slot);
       const uint8_t *base = ring + (size_t)my_slot * slot_bytes;
       if (mode == 0) {
-        // rows 4*wig .. 4*wig+3 of the stage; the clamp keeps the loads inside it
-        const uint8_t *rp[4];
-        float a[4][4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          rp[q] = base + (size_t)min(4 * wig + q, rows - 1) * row_bytes;
-          a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
-        }
-#pragma unroll
-        for (int i = 0; i < 3; ++i) {
-          const int u = i * 32 + lane;
-          if (u < units && !(c.p.trace_stride & 0x1000)) {
-            uint4 w[4];
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              w[q] = *reinterpret_cast<const uint4 *>(rp[q] + u * 16);
-#pragma unroll
-            for (int q = 0; q < 4; ++q)
-              dot_unit(w[q], xr[i], a[q]);
-          }
-        }
-        float v[4];
-#pragma unroll
-        for (int q = 0; q < 4; ++q)
-          v[q] = fmaf(dot_total(a[q]), kAccScale, off);
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-          for (int q = 0; q < 4; ++q)
-            v[q] += __shfl_xor_sync(0xffffffffu, v[q], o);
-        // lane q finishes row q
-        const int q = lane & 3;
-        const float mine = q == 0 ? v[0] : q == 1 ? v[1] : q == 2 ? v[2] : v[3];
-        const uint8_t *myrow = q == 0 ? rp[0] : q == 1 ? rp[1] : q == 2 ? rp[2] : rp[3];
-        const float2 t = *reinterpret_cast<const float2 *>(myrow + K);
-        const float val = __fadd_rn(__fmul_rn(mine, t.x), t.y);
-        const int row = 4 * wig + q;
-        if (ep.kind == EP_SILU) {
-          // rows (2j, 2j+1) = (gate_j, up_j)
-          const float upv = __shfl_down_sync(0xffffffffu, val, 1);
-          if (lane < 4 && (lane & 1) == 0 && row + 1 < rows)
-            ll_store(ep.dst + ((row_begin + r0 + row) >> 1), silu_mul(val, upv), ep.tag);
-        } else if (lane < 4 && row < rows) {
-          emit(c, ep, row_begin + r0 + row, val, bestv, besti);
-        }
+        if (R == 4)
+          visit_rows<4>(c, ep, base, rows, row_bytes, K, units, wig, lane, xr, off, row_begin + r0,
+                        bestv, besti);
+        else
+          visit_rows<1>(c, ep, base, rows, row_bytes, K, units, wig, lane, xr, off, row_begin + r0,
+                        bestv, besti);
       } else {
         const int tig = ctid & 255;   // thread within the group
         for (int r = 0; r < rows; r += 2) {
@@ -662,6 +689,26 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
 // the range with several rows in flight; the CTA folds its warps and publishes the
 // split partial; then every CTA of the kv head folds one slice of the outputs
 // over all splits (in split order: the result does not depend on timing).
+// Ask L2 for the cache rows this CTA will scan in the coming attention phase.
+// Called before the q|k|v projection, so the rows arrive while it runs.
+__device__ __forceinline__ void attention_prefetch(const Ctx &c, int layer, int pos) {
+  const MegaParams &p = c.p;
+  const int S = p.splits;
+  if ((int)blockIdx.x >= p.kvh * S)
+    return;
+  const int hk = blockIdx.x / S, split = blockIdx.x % S;
+  const int len = pos + 1;
+  const int chunk = (len + S - 1) / S;
+  const int s0 = split * chunk, s1 = min(pos, s0 + chunk);   // row `pos` is written this step
+  const char *kc = reinterpret_cast<const char *>(p.kv[2 * layer] + ((size_t)hk * p.max_len + s0) * D);
+  const char *vc = reinterpret_cast<const char *>(p.kv[2 * layer + 1] + ((size_t)hk * p.max_len + s0) * D);
+  const int lines = (s1 - s0) * (D * 4 / 128);
+  for (int i = c.ctid; i < lines; i += kCT) {
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(kc + (size_t)i * 128));
+    asm volatile("prefetch.global.L2 [%0];" ::"l"(vc + (size_t)i * 128));
+  }
+}
+
 template <int G>
 __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
   const MegaParams &p = c.p;
@@ -758,12 +805,12 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
     acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
   }
   constexpr int NB = G <= 4 ? 4 : 2;   // rows in flight per warp (register budget: 128)
-  for (int j0 = s0 + warp; j0 < s1 && warp < kAW; j0 += NB * kAW) {
+  for (int j0 = s0 + warp; j0 < s1; j0 += NB * kCW) {
     // NB rows in flight: all loads are issued before the first use
     float4 kr[NB], vr[NB];
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
-      const int j = min(j0 + i * kAW, s1 - 1);
+      const int j = min(j0 + i * kCW, s1 - 1);
       kr[i] = ldcg4(kc + (size_t)j * D + 4 * lane);
       vr[i] = ldcg4(vc + (size_t)j * D + 4 * lane);
     }
@@ -784,7 +831,7 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
         s[i][g] = warp_sum(s[i][g]) * scale;
 #pragma unroll
     for (int i = 0; i < NB; ++i) {
-      if (j0 + i * kAW < s1) {   // warp-uniform
+      if (j0 + i * kCW < s1) {   // warp-uniform
 #pragma unroll
         for (int g = 0; g < G; ++g) {
           const float nm = fmaxf(m[g], s[i][g]);
@@ -802,6 +849,36 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
   trace(c, layer, 9);
   // ---- fold the warps of this CTA (fixed warp order) ------------------------------
   float *aacc = c.xs;   // [kAW][G][D]
+  // round 1: warps 8..15 hand their state to warps 0..7 (online-softmax merge)
+  if (warp >= kAW) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      if (lane == 0) {
+        c.sh.am[warp - kAW][g] = m[g];
+        c.sh.al[warp - kAW][g] = l[g];
+      }
+      *reinterpret_cast<float4 *>(aacc + ((size_t)(warp - kAW) * G + g) * D + 4 * lane) =
+          make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
+    }
+  }
+  consumer_sync();
+  if (warp < kAW) {
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      const float om = c.sh.am[warp][g], ol = c.sh.al[warp][g];
+      const float4 oa = *reinterpret_cast<const float4 *>(aacc + ((size_t)warp * G + g) * D + 4 * lane);
+      const float nm = fmaxf(m[g], om);
+      const float a = expf(m[g] - nm), b = expf(om - nm);
+      l[g] = fmaf(l[g], a, ol * b);
+      acc[g][0] = fmaf(acc[g][0], a, oa.x * b);
+      acc[g][1] = fmaf(acc[g][1], a, oa.y * b);
+      acc[g][2] = fmaf(acc[g][2], a, oa.z * b);
+      acc[g][3] = fmaf(acc[g][3], a, oa.w * b);
+      m[g] = nm;
+    }
+  }
+  consumer_sync();
+  // round 2: warps 0..7 publish, then the CTA folds them (fixed warp order)
   if (warp < kAW) {
 #pragma unroll
     for (int g = 0; g < G; ++g) {
@@ -814,29 +891,41 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
     }
   }
   consumer_sync();
+  // weights of the 8 warp states, once per head
+  if (c.ctid < G) {
+    const int g = c.ctid;
+    float M = kSeed;
+#pragma unroll
+    for (int w = 0; w < kAW; ++w)
+      M = fmaxf(M, c.sh.am[w][g]);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kAW; ++w) {
+      const float b = expf(c.sh.am[w][g] - M);
+      c.sh.cw[g * kAW + w] = b;
+      L = fmaf(c.sh.al[w][g], b, L);
+    }
+    c.sh.cm[g] = M;
+    c.sh.cl[g] = L;
+  }
+  consumer_sync();
   const int stride = D + 2;
   uint2 *part = p.ll_part + (size_t)par * p.qh * S * stride;
   const uint32_t ptag = tag_of(c, layer, T_PART);
   for (int idx = c.ctid; idx < G * D; idx += kCT) {
     const int g = idx / D, d = idx - g * D;
-    float M = kSeed;
+    float A = 0.f;
 #pragma unroll
     for (int w = 0; w < kAW; ++w)
-      M = fmaxf(M, c.sh.am[w][g]);
-    float L = 0.f, A = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAW; ++w) {
-      const float b = expf(c.sh.am[w][g] - M);
-      L = fmaf(c.sh.al[w][g], b, L);
-      A = fmaf(aacc[((size_t)w * G + g) * D + d], b, A);
-    }
+      A = fmaf(aacc[((size_t)w * G + g) * D + d], c.sh.cw[g * kAW + w], A);
     uint2 *dst = part + ((size_t)(hk * G + g) * S + split) * stride;
     ll_store(dst + d, A, ptag);
     if (d == 0) {
-      ll_store(dst + D, M, ptag);
-      ll_store(dst + D + 1, L, ptag);
+      ll_store(dst + D, c.sh.cm[g], ptag);
+      ll_store(dst + D + 1, c.sh.cl[g], ptag);
     }
   }
+  consumer_sync();   // cm / cl / cw are reused below
   trace(c, layer, 10);
   // ---- fold the splits for this CTA's slice of the G*D outputs ----------------------
   // (frontend/Python/ops/tosa.py:14502-14594): weights exp(m_s - M), then sums
@@ -871,21 +960,19 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
       const int g = o / D, d = o - g * D;
       const uint2 *src = part + (size_t)(hk * G + g) * S * stride + d;
       float ar = 0.f;
-      for (int sb = 0; sb < S; sb += 8) {
-        uint2 r[8];
+      uint2 r[16];   // splits <= 16
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (sb + i < S)
-            r[i] = ll_load1(src + (size_t)(sb + i) * stride);
+      for (int i = 0; i < 16; ++i)
+        if (i < S)
+          r[i] = ll_load1(src + (size_t)i * stride);
 #pragma unroll
-        for (int i = 0; i < 8; ++i)
-          if (sb + i < S) {
-            float v = __uint_as_float(r[i].x);
-            if (r[i].y != ptag)
-              v = ll_wait1(c, src + (size_t)(sb + i) * stride, ptag);
-            ar = fmaf(v, c.sh.cw[g * S + sb + i], ar);
-          }
-      }
+      for (int i = 0; i < 16; ++i)
+        if (i < S) {
+          float v = __uint_as_float(r[i].x);
+          if (r[i].y != ptag)
+            v = ll_wait1(c, src + (size_t)i * stride, ptag);
+          ar = fmaf(v, c.sh.cw[g * S + i], ar);
+        }
       ll_store(p.ll_attn + (size_t)par * QD + (size_t)(hk * G + g) * D + d,
                __fdiv_rn(ar, c.sh.cL[g]), tag_of(c, layer, T_ATTN));
     }
@@ -1007,6 +1094,8 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
                  p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), nullptr};
       }
       trace(c, l, step);
+      if (!last && step == 0)
+        attention_prefetch(c, l, pos);
       gemv_phase(c, p.phase[phase_index], xsrc, ep, bestv, besti, l);
       if (!last && step == 0) {
         trace(c, l, 6);
