@@ -80,6 +80,7 @@ def load():
                                      i32, i32, i32, vp, vp]),
         "b200_gqa_scratch_floats": (i64, [i32, i32, i32]),
         "b200_gqa_decode": (i32, [vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
+        "b200_gqa_decode_static": (i32, [vp, vp, vp, vp, i32, i32, i32, i32, i32, vp, vp]),
         "b200_embed": (i32, [vp, vp, vp, i64, vp]),
         "b200_argmax_first": (i32, [vp, i64, vp, vp, vp]),
         "b200_kv_overflow": (i32, [vp, i32, i32, i32, i32, i32, i32, f32,

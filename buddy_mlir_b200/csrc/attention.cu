@@ -15,6 +15,8 @@
 // result does not depend on CTA scheduling.
 #include "common.cuh"
 
+#include <mutex>
+
 namespace b200 {
 
 constexpr int kAttnWarps = 4;
@@ -204,6 +206,13 @@ int gqa_decode_launch(const float *q, const float *kc, const float *vc,
   }
 }
 
+// ---- scratch that lives in the library image ------------------------------------
+// Split partials for b200_gqa_decode_static(): enough for 64 query heads x 32
+// splits x (128 + 2) floats plus the arrival counters, about 1.07 MB.  Every
+// GPU that loads this library keeps the array until the process exits.
+constexpr int64_t kStaticScratchFloats = B200_GQA_STATIC_SCRATCH_FLOATS;
+static __device__ __align__(256) float g_gqa_static_scratch[kStaticScratchFloats];
+
 } // namespace b200
 
 using namespace b200;
@@ -213,6 +222,51 @@ extern "C" {
 int64_t b200_gqa_scratch_floats(int q_heads, int D, int splits) {
   // partials [q_heads][splits][D+2] + one arrival counter per kv head
   return (int64_t)q_heads * splits * (D + 2) + q_heads;
+}
+
+int b200_gqa_decode_static(const float *q, const float *k_cache, const float *v_cache, float *out,
+                           int q_heads, int kv_heads, int D, int max_len, int splits,
+                           const int32_t *pos, void *stream) {
+  if (int rc = ensure_device())
+    return rc;
+  if (q_heads < 1 || kv_heads < 1 || splits < 1 || D < 1)
+    return fail(B200_EINVAL, "gqa_decode_static: bad shape");
+  const int64_t need = b200_gqa_scratch_floats(q_heads, D, splits);
+  if (need > kStaticScratchFloats)
+    return fail(B200_ELIMIT,
+                "gqa_decode_static: q_heads=%d x splits=%d x (D=%d + 2) needs %lld scratch floats, "
+                "the built-in array holds %lld; use b200_gqa_decode with caller-owned scratch",
+                q_heads, splits, D, (long long)need, (long long)kStaticScratchFloats);
+  // Device address of the array, looked up once per device with that device
+  // current.  (In host code the array's name is only a handle for this lookup,
+  // never a pointer a kernel could use.)
+  constexpr int kMaxDevices = 64;
+  static float *addr[kMaxDevices] = {};
+  static std::mutex mu;
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices)
+    return fail(B200_ELIMIT, "gqa_decode_static: device ordinal %d beyond %d", dev, kMaxDevices);
+  float *scratch = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    if (addr[dev] == nullptr) {
+      void *p = nullptr;
+      cudaError_t e = cudaGetSymbolAddress(&p, g_gqa_static_scratch);
+      if (e != cudaSuccess || p == nullptr)
+        return fail(B200_ECUDA, "gqa_decode_static: cudaGetSymbolAddress: %s",
+                    cudaGetErrorString(e));
+      addr[dev] = static_cast<float *>(p);
+    }
+    scratch = addr[dev];
+  }
+  // The array keeps whatever the previous call (possibly of another shape)
+  // left behind; only the arrival counters have to start at zero.
+  cudaStream_t st = (cudaStream_t)stream;
+  float *counters = scratch + (int64_t)q_heads * splits * (D + 2);
+  B200_CUDA(cudaMemsetAsync(counters, 0, (size_t)kv_heads * sizeof(unsigned int), st));
+  return gqa_decode_launch(q, k_cache, v_cache, out, scratch, q_heads, kv_heads, D, max_len,
+                           splits, pos, st);
 }
 
 int b200_gqa_decode(const float *q, const float *k_cache, const float *v_cache,

@@ -177,6 +177,24 @@ int b200_gqa_decode(const float *q, const float *k_cache, const float *v_cache,
                     float *out, float *scratch, int q_heads, int kv_heads,
                     int D, int max_len, int splits, const int32_t *pos,
                     void *stream);
+/* The same attention for callers that must not allocate device memory.
+ * (No counterpart in buddy-mlir.)  Some hosts hand every byte of device memory
+ * to a planner before inference starts, and some run decode inside loops where
+ * a cudaMalloc -- which can stall the whole device -- is not acceptable; such
+ * callers have nowhere to get the split-partial scratch from.  This entry point
+ * uses an array built into the library image instead: B200_GQA_STATIC_SCRATCH_FLOATS
+ * floats (about 1.07 MB, resident on every GPU that loads the library until
+ * the process exits).  It calls no cudaMalloc, cudaFree or allocating library
+ * routine.  Shapes whose scratch (b200_gqa_scratch_floats) exceeds the array
+ * are refused with B200_ELIMIT.  The first call on a device looks up the
+ * array's device address; make that first call before any stream capture
+ * begins.  All calls share the one array: calls that can overlap on the GPU
+ * (different streams, different threads) race and must be serialised by the
+ * caller.  Inputs, outputs and results are exactly those of b200_gqa_decode. */
+#define B200_GQA_STATIC_SCRATCH_FLOATS (64 * 32 * 130 + 64)
+int b200_gqa_decode_static(const float *q, const float *k_cache, const float *v_cache, float *out,
+                           int q_heads, int kv_heads, int D, int max_len, int splits,
+                           const int32_t *pos, void *stream);
 /* Embedding row gather (subgraph0_decode_simplify.mlir:46-49). */
 int b200_embed(const float *table, const int32_t *token, float *x, int64_t H,
                void *stream);
