@@ -254,8 +254,15 @@ def run_single(args):
     tpath = os.path.join(ROOT, "profiles", "decode_step_traffic.json")
     if os.path.exists(tpath):
         traffic = json.load(open(tpath)).get("dram_bytes_per_step")
-    gemv = gemv_microbench(lib)
+    gemv = None if args.resident_only else gemv_microbench(lib)
     s.close()
+    if args.resident_only:
+        # profiling runs: only the resident-in-HBM leg, so a capture stays small
+        print(json.dumps({"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1,
+                          "steps": steps, "warmup": warmup, "ms_per_step": ms / steps,
+                          "resident_only": True, "gpu_launches": int(launches),
+                          "bytes_per_step": step_bytes, "clocks": clocks}))
+        return
 
     # ---- end to end through the model entry, host buffers --------------------------
     es = EntrySession(cfg, "f32", [blob], all_linear_w8=True)
@@ -304,6 +311,8 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--resident-only", action="store_true",
+                    help="skip the isolated-GEMV, end-to-end and CPU legs (for profiler captures)")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3
