@@ -251,9 +251,12 @@ def run_single(args):
     hbm, which = peaks()
     achieved = step_bytes / (ms / steps) / 1e6        # GB/s
     traffic = None
-    tpath = os.path.join(ROOT, "profiles", "decode_step_traffic.json")
-    if os.path.exists(tpath):
-        traffic = json.load(open(tpath)).get("dram_bytes_per_step")
+    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu summary
+    tpath = os.path.join(ROOT, "profiles", "decode_step_kernel_qwen1p5b_int8_full.md")
+    if persistent and os.path.exists(tpath):
+        import re
+        found = re.search(r"^dram_bytes_per_step:\s*(\d+)", open(tpath).read(), re.M)
+        traffic = int(found.group(1)) if found else None
     gemv = None if args.resident_only else gemv_microbench(lib)
     s.close()
     if args.resident_only:
