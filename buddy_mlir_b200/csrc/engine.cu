@@ -388,9 +388,14 @@ int build_mega(b200_model *m) {
   B200_CUDA(cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, dev));
   const int G = c.q_heads / c.kv_heads;
   const int grid = sms, L = c.n_layers, D = c.head_dim;
+  // attention work items: every CTA takes one (kv head, split) pair
   int splits = grid / c.kv_heads;
-  if (splits > 16) splits = 16;
-  if (!coop || splits < 1 || (G * D + splits - 1) / splits > 512 || G * splits > 256)
+  if (splits > 128) splits = 128;
+  while (splits > 1 && G * splits > 768) --splits;
+  // the split fold keeps (outputs per warp) x (splits per lane) partials in registers
+  const bool fold_fits =
+      splits >= 1 && (((G * D + splits - 1) / splits + 15) / 16) * ((splits + 31) / 32) <= 8;
+  if (!coop || !fold_fits)
     return B200_OK;  // stays on the graph path
   const int H = c.hidden, QD = c.q_heads * D, KD = c.kv_heads * D, F = c.ffn, V = c.vocab;
   MegaParams &p = m->mp;
@@ -418,6 +423,7 @@ int build_mega(b200_model *m) {
   int xs_floats = maxK;
   if (xs_floats < 8 * G * D) xs_floats = 8 * G * D;       // attention fold of the 8 scanning warps
   if (xs_floats < (G + 2) * D) xs_floats = (G + 2) * D;   // staged q | k | v
+  if (xs_floats < 3 * G * splits + 8) xs_floats = 3 * G * splits + 8;   // split fold: m, l, weights
   xs_floats = (xs_floats + 31) / 32 * 32;
   const int nws_floats = (H + 31) / 32 * 32;
   const size_t fixed = mega_fixed_shared_bytes() + (size_t)(xs_floats + nws_floats) * 4;
@@ -515,7 +521,7 @@ int build_mega(b200_model *m) {
   p.trace_stride = 1;
   if (const char *t = std::getenv("BUDDY_B200_TRACE")) {
     p.trace_stride = std::atoi(t) > 0 ? std::atoi(t) : 1;
-    const size_t n = (size_t)(grid / p.trace_stride + 1) * (L + 1) * 32;
+    const size_t n = (size_t)(grid / p.trace_stride + 1) * (L + 1) * kMegaTraceSlots;
     if (int rc = dev_alloc((void **)&m->d_trace, n * 8)) return rc;
     B200_CUDA(cudaMemset(m->d_trace, 0, n * 8));
     p.trace = m->d_trace;
@@ -1140,7 +1146,7 @@ int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega
 int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity) {
   if (!m || !host || !m->d_trace)
     return fail(B200_ESTATE, "read_trace: tracing is off (set BUDDY_B200_TRACE=<cta stride>)");
-  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * 32;
+  const int64_t n = (int64_t)(m->mega_grid / m->mp.trace_stride + 1) * (m->cfg.n_layers + 1) * kMegaTraceSlots;
   B200_CUDA(cudaMemcpy(host, m->d_trace, (size_t)(n < capacity ? n : capacity) * 8,
                        cudaMemcpyDeviceToHost));
   return (int)(n < capacity ? n : capacity);

@@ -167,7 +167,7 @@ struct Shared {
   int besti[kCW];
   int abort_flag;
   float am[kAW][8], al[kAW][8];         // attention: per-warp (m, l)
-  float cm[8 * 32], cl[8 * 32], cw[8 * 32], cL[8];  // attention: split fold
+  float fw[8 * kAW], fm[8], fl[8];      // attention: fold of the warps (weights, m, l per head)
 };
 static_assert(offsetof(Shared, rowinfo) % 8 == 0, "rowinfo must be 8-byte aligned");
 
@@ -183,6 +183,7 @@ struct Ctx {
   uint32_t parity;    // parity of that slot's current use
   int g;              // index of the next stage in this CTA's stream
   uint32_t tag_base;
+  long long *tr;      // this CTA's trace rows, or null
 };
 
 __device__ __forceinline__ uint32_t tag_of(const Ctx &c, int layer, int what) {
@@ -373,11 +374,9 @@ __device__ __forceinline__ bool stage_wait(Shared &sh, int slot, uint32_t parity
 
 // Optional per-phase timeline (SM clock) of a few CTAs, for tuning.
 __device__ __forceinline__ void trace(Ctx &c, int layer, int slot) {
-  if (c.p.trace != nullptr && c.ctid == 0 && (blockIdx.x % c.p.trace_stride) == 0)
-    c.p.trace[((size_t)(blockIdx.x / c.p.trace_stride) * (c.p.L + 1) + layer) * 32 + slot] =
-        clock64();
+  if (c.tr != nullptr && c.ctid == 0)
+    c.tr[layer * kMegaTraceSlots + slot] = clock64();
 }
-
 // ---- activation source / result sink of a projection -----------------------------
 struct XSrc {
   const uint2 *ll;      // tagged source, or
@@ -902,11 +901,11 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
 #pragma unroll
     for (int w = 0; w < kAW; ++w) {
       const float b = expf(c.sh.am[w][g] - M);
-      c.sh.cw[g * kAW + w] = b;
+      c.sh.fw[g * kAW + w] = b;
       L = fmaf(c.sh.al[w][g], b, L);
     }
-    c.sh.cm[g] = M;
-    c.sh.cl[g] = L;
+    c.sh.fm[g] = M;
+    c.sh.fl[g] = L;
   }
   consumer_sync();
   const int stride = D + 2;
@@ -917,64 +916,94 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
     float A = 0.f;
 #pragma unroll
     for (int w = 0; w < kAW; ++w)
-      A = fmaf(aacc[((size_t)w * G + g) * D + d], c.sh.cw[g * kAW + w], A);
+      A = fmaf(aacc[((size_t)w * G + g) * D + d], c.sh.fw[g * kAW + w], A);
     uint2 *dst = part + ((size_t)(hk * G + g) * S + split) * stride;
     ll_store(dst + d, A, ptag);
     if (d == 0) {
-      ll_store(dst + D, c.sh.cm[g], ptag);
-      ll_store(dst + D + 1, c.sh.cl[g], ptag);
+      ll_store(dst + D, c.sh.fm[g], ptag);
+      ll_store(dst + D + 1, c.sh.fl[g], ptag);
     }
   }
-  consumer_sync();   // cm / cl / cw are reused below
+  consumer_sync();   // aacc (in xs) has been read: xs is reused below
   trace(c, layer, 10);
   // ---- fold the splits for this CTA's slice of the G*D outputs ----------------------
-  // (frontend/Python/ops/tosa.py:14502-14594): weights exp(m_s - M), then sums
+  // (frontend/Python/ops/tosa.py:14502-14594): weights exp(m_s - M), then sums in
+  // split order.  A warp takes outputs warp, warp + 16, ..; its lanes take splits
+  // lane, lane + 32, ..; the raw partials are requested first and stay in
+  // registers while the (m, l) pairs of all splits are turned into weights.
+  float *cm = c.xs, *cl = cm + G * S, *cw = cl + G * S, *cL = cw + G * S;
+  const int per = (G * D + S - 1) / S;
+  const int o_begin = split * per;
+  const int o_cnt = max(0, min(per, G * D - o_begin));
+  const int sl = (S + 31) >> 5;       // splits per lane
+  constexpr int kMaxR = 8;            // (outputs per warp) x (splits per lane), checked on the host
+  uint2 r[kMaxR];
+  {
+    int oo = 0, ss = 0;
+#pragma unroll
+    for (int a = 0; a < kMaxR; ++a) {
+      const int o = warp + kCW * oo, si = lane + 32 * ss;
+      r[a] = make_uint2(0u, 0u);
+      if (o < o_cnt && si < S) {
+        const int og = o_begin + o, g = og / D, d = og - g * D;
+        r[a] = ll_load1(part + ((size_t)(hk * G + g) * S + si) * stride + d);
+      }
+      if (++ss == sl) {
+        ss = 0;
+        ++oo;
+      }
+    }
+  }
   for (int idx = c.ctid; idx < G * S; idx += kCT) {
-    const int g = idx / S, si = idx - g * S;
-    const uint2 *src = part + ((size_t)(hk * G + g) * S + si) * stride + D;
-    uint4 r = ll_load2(src);
-    r = ll_wait2(c, src, ptag, r);
-    c.sh.cm[idx] = __uint_as_float(r.x);
-    c.sh.cl[idx] = __uint_as_float(r.z);
+    const uint2 *src = part + ((size_t)hk * G * S + idx) * stride + D;   // idx = g * S + split
+    uint4 v = ll_load2(src);
+    v = ll_wait2(c, src, ptag, v);
+    cm[idx] = __uint_as_float(v.x);
+    cl[idx] = __uint_as_float(v.z);
   }
   consumer_sync();
-  if (c.ctid < G) {
-    const int g = c.ctid;
+  if (warp < G) {
+    const int g = warp;
     float M = kSeed;
-    for (int si = 0; si < S; ++si)
-      M = fmaxf(M, c.sh.cm[g * S + si]);
+    for (int si = lane; si < S; si += 32)
+      M = fmaxf(M, cm[g * S + si]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
     float L = 0.f;
-    for (int si = 0; si < S; ++si) {
-      const float b = expf(c.sh.cm[g * S + si] - M);
-      c.sh.cw[g * S + si] = b;
-      L = fmaf(c.sh.cl[g * S + si], b, L);
+    for (int si = lane; si < S; si += 32) {
+      const float b = expf(cm[g * S + si] - M);
+      cw[g * S + si] = b;
+      L = fmaf(cl[g * S + si], b, L);
     }
-    c.sh.cL[g] = L;
+    L = warp_sum(L);
+    if (lane == 0)
+      cL[g] = L;
   }
   consumer_sync();
   trace(c, layer, 11);
   {
-    const int per = (G * D + S - 1) / S;          // outputs folded by this CTA
-    const int o = split * per + c.ctid;
-    if (c.ctid < per && o < G * D) {
-      const int g = o / D, d = o - g * D;
-      const uint2 *src = part + (size_t)(hk * G + g) * S * stride + d;
-      float ar = 0.f;
-      uint2 r[16];   // splits <= 16
+    int oo = 0, ss = 0;
+    float ar = 0.f;
 #pragma unroll
-      for (int i = 0; i < 16; ++i)
-        if (i < S)
-          r[i] = ll_load1(src + (size_t)i * stride);
-#pragma unroll
-      for (int i = 0; i < 16; ++i)
-        if (i < S) {
-          float v = __uint_as_float(r[i].x);
-          if (r[i].y != ptag)
-            v = ll_wait1(c, src + (size_t)i * stride, ptag);
-          ar = fmaf(v, c.sh.cw[g * S + i], ar);
-        }
-      ll_store(p.ll_attn + (size_t)par * QD + (size_t)(hk * G + g) * D + d,
-               __fdiv_rn(ar, c.sh.cL[g]), tag_of(c, layer, T_ATTN));
+    for (int a = 0; a < kMaxR; ++a) {
+      const int o = warp + kCW * oo, si = lane + 32 * ss;   // o is the same for the whole warp
+      const int og = o_begin + o, g = og / D, d = og - g * D;
+      if (o < o_cnt && si < S) {
+        float v = __uint_as_float(r[a].x);
+        if (r[a].y != ptag)
+          v = ll_wait1(c, part + ((size_t)(hk * G + g) * S + si) * stride + d, ptag);
+        ar = fmaf(v, cw[g * S + si], ar);
+      }
+      if (++ss == sl) {
+        ar = warp_sum(ar);
+        if (lane == 0 && o < o_cnt)
+          ll_store(p.ll_attn + (size_t)par * QD + (size_t)(hk * G + g) * D + d,
+                   __fdiv_rn(ar, cL[g]), tag_of(c, layer, T_ATTN));
+        ar = 0.f;
+        ss = 0;
+        ++oo;
+      }
     }
   }
   consumer_sync();
@@ -1050,7 +1079,10 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
   // ================= consumers ===================================================
   const uint32_t tags_per_launch = 8u * (uint32_t)(p.L + 3);
   Ctx c{p, sh, xs, nws, ring, err, (int)threadIdx.x, lane, warp, 0, 0u, 0,
-        ((uint32_t)p.state[4] + 1u) * tags_per_launch};
+        ((uint32_t)p.state[4] + 1u) * tags_per_launch,
+        (p.trace != nullptr && blockIdx.x % p.trace_stride == 0)
+            ? p.trace + (size_t)(blockIdx.x / p.trace_stride) * (p.L + 1) * kMegaTraceSlots
+            : nullptr};
   float bestv = -INFINITY;
   int besti = 0x7fffffff;
   const int H = p.H, QD = p.qh * D, KD = p.kvh * D;

@@ -8,6 +8,7 @@ namespace b200 {
 constexpr int kMegaThreads = 512;      // 16 warps
 constexpr int kMegaMaxSlots = 16;
 constexpr int kMegaMaxRowsB = 64;      // rows of a shared-row phase finalised per flush
+constexpr int kMegaTraceSlots = 64;   // trace points per (CTA, layer)
 constexpr int kMegaTrailer = 16;       // bytes appended to every streamed row: scale, bias
 
 struct MegaPhase {
@@ -43,7 +44,7 @@ struct MegaParams {
   int32_t *history;
   int history_cap;
   int *error;                  // 0, or the code of the first wait that gave up
-  long long *trace;            // optional [grid/stride][L+1][32] SM-clock timeline, or null
+  long long *trace;            // optional [grid/stride][L+1][kMegaTraceSlots] SM-clock timeline, or null
   int trace_stride;
 };
 
