@@ -46,7 +46,7 @@ namespace {
 
 constexpr int kCW = 16;           // warps (all of them consume)
 constexpr int kCT = kCW * 32;     // threads
-constexpr int kAW = 8;            // warps that scan the KV cache in the attention phase
+constexpr int kAW = 7;            // warps that scan the KV cache in the attention phase
 constexpr uint32_t kSpinLimit = 1u << 26;      // poll count bound, and
 constexpr unsigned long long kWaitNs = 1000000000ull;  // wall-time bound (1 s) of any single wait
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -58,7 +58,7 @@ constexpr float kSeed = -1.0e30f;
 constexpr int D = 128;            // head_dim (checked on the host)
 
 // producer phases that tag their outputs
-enum { T_QKV = 1, T_ATTN = 2, T_XB = 3, T_MID = 4, T_XA = 5, T_PART = 6, T_CAND = 7 };
+enum { T_QKV = 1, T_ATTN = 2, T_XB = 3, T_DPART = 4, T_XA = 5, T_PART = 6, T_CAND = 7 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -151,6 +151,8 @@ struct StreamPlan {
   int per_layer;       // stages per layer
   int total;           // stages per token
   int L;
+  uint2 tab[kMegaMaxLayerStages];   // stage r of a layer: (byte offset inside the layer's part, bytes)
+  int next_l[kMegaMaxSlots], next_r[kMegaMaxSlots];   // per ring slot: the stage it receives next
 };
 
 struct Shared {
@@ -160,22 +162,19 @@ struct Shared {
   StreamPlan plan;
   const uint8_t *stream_base;
   float cs[64], sn[64];                 // cos / sin of this step's position
-  float part[kCW][kMegaMaxRowsB];       // shared-row phases: per-warp partial sums
-  float2 rowinfo[kMegaMaxRowsB];        // (scale, bias) of those rows
-  float red[kCW];
+  float red[kCW], red2[kCW];
+  float mids[kMegaMaxMid];              // silu(gate) * up of this CTA's gate|up pairs
   float bestv[kCW];
   int besti[kCW];
   int abort_flag;
   float am[kAW][8], al[kAW][8];         // attention: per-warp (m, l)
-  float fw[8 * kAW], fm[8], fl[8];      // attention: fold of the warps (weights, m, l per head)
+  float fw[8 * kAW], fm[8];             // attention: fold of the warps (weights, m per head)
 };
-static_assert(offsetof(Shared, rowinfo) % 8 == 0, "rowinfo must be 8-byte aligned");
 
 struct Ctx {
   const MegaParams &p;
   Shared &sh;
   float *xs;          // staged activations (shared memory)
-  float *nws;         // staged norm weight (shared memory)
   uint8_t *ring;
   volatile int *err;
   int ctid, lane, warp;
@@ -237,50 +236,57 @@ __device__ __forceinline__ uint4 ll_wait2(Ctx &c, const uint2 *p, uint32_t tag, 
   return v;
 }
 
-// Cooperative load of n tagged values (n even) into shared memory; returns this
-// thread's partial sum of squares.  The first vector of every thread is polled
-// alone (cheap on L2) before the rest is requested.
-__device__ __forceinline__ float stage_tagged(Ctx &c, const uint2 *src, uint32_t tag, int n, float *dst) {
+constexpr float kXScale = 18446744073709551616.0f;          // 2^64
+constexpr float kAccScale = 38685626227668133590597632.0f;  // 2^85
+// Cooperative load of n activations (n even) into shared memory, ready for the
+// row loops: multiplied by the RMSNorm weight (if any) and by 2^64.  `ss`
+// receives this thread's share of sum(x^2) (of the raw values), `sx` its share
+// of sum(x * weight).  The first vector of every thread is polled alone (cheap
+// on L2) before the rest is requested.
+__device__ __forceinline__ void put2(float *dst, const float *nw, int e, float a, float b, float &ss,
+                                     float &sx) {
+  ss = __fadd_rn(ss, __fmul_rn(a, a));
+  ss = __fadd_rn(ss, __fmul_rn(b, b));
+  if (nw != nullptr) {
+    const float2 w = __ldg(reinterpret_cast<const float2 *>(nw + e));
+    a = __fmul_rn(a, w.x);
+    b = __fmul_rn(b, w.y);
+  }
+  sx += a + b;
+  *reinterpret_cast<float2 *>(dst + e) = make_float2(a * kXScale, b * kXScale);
+}
+__device__ __forceinline__ void stage_tagged(Ctx &c, const uint2 *src, uint32_t tag, int n, float *dst,
+                                             const float *nw, float &ss, float &sx) {
   const int nv = n >> 1;
-  float ss = 0.f;
-  for (int base = 0; base < nv; base += kCT * 8) {
-    uint4 r[8];
-    int idx[8];
+  for (int base = 0; base < nv; base += kCT * 4) {
+    uint4 r[4];
+    int idx[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
       idx[i] = base + i * kCT + c.ctid;
     if (idx[0] < nv) {
       r[0] = ll_load2(src + 2 * idx[0]);
       r[0] = ll_wait2(c, src + 2 * idx[0], tag, r[0]);
     }
 #pragma unroll
-    for (int i = 1; i < 8; ++i)
+    for (int i = 1; i < 4; ++i)
       if (idx[i] < nv)
         r[i] = ll_load2(src + 2 * idx[i]);
 #pragma unroll
-    for (int i = 0; i < 8; ++i)
+    for (int i = 0; i < 4; ++i)
       if (idx[i] < nv) {
         if (i > 0)
           r[i] = ll_wait2(c, src + 2 * idx[i], tag, r[i]);
-        const float a = __uint_as_float(r[i].x), b = __uint_as_float(r[i].z);
-        *reinterpret_cast<float2 *>(dst + 2 * idx[i]) = make_float2(a, b);
-        ss = __fadd_rn(ss, __fmul_rn(a, a));
-        ss = __fadd_rn(ss, __fmul_rn(b, b));
+        put2(dst, nw, 2 * idx[i], __uint_as_float(r[i].x), __uint_as_float(r[i].z), ss, sx);
       }
   }
-  return ss;
 }
-__device__ __forceinline__ float stage_plain(Ctx &c, const float *src, int n, float *dst) {
-  float ss = 0.f;
-  for (int i = c.ctid * 4; i < n; i += kCT * 4) {
-    const float4 v = __ldg(reinterpret_cast<const float4 *>(src + i));
-    *reinterpret_cast<float4 *>(dst + i) = v;
-    ss = __fadd_rn(ss, __fmul_rn(v.x, v.x));
-    ss = __fadd_rn(ss, __fmul_rn(v.y, v.y));
-    ss = __fadd_rn(ss, __fmul_rn(v.z, v.z));
-    ss = __fadd_rn(ss, __fmul_rn(v.w, v.w));
+__device__ __forceinline__ void stage_plain(Ctx &c, const float *src, int n, float *dst, const float *nw,
+                                            float &ss, float &sx) {
+  for (int i = c.ctid * 2; i < n; i += kCT * 2) {
+    const float2 v = __ldg(reinterpret_cast<const float2 *>(src + i));
+    put2(dst, nw, i, v.x, v.y, ss, sx);
   }
-  return ss;
 }
 
 // Streamed rows hold u = q + 128 (the int8 weight with its sign bit flipped).
@@ -288,15 +294,12 @@ __device__ __forceinline__ float stage_plain(Ctx &c, const float *src, int n, fl
 // give u * 2^-149 (a denormal), bits 8-15 give u * 2^-141, bits 16-23 give
 // u * 2^-133 (the step from denormal to normal numbers is continuous), and
 // the top byte shifted down gives u * 2^-149 again.  So the dequantisation of
-// a weight is ONE logic op (LOP3 / SHF, which issue at twice the rate of a
-// byte permute) and its multiply-accumulate one FFMA.  The four byte positions
-// accumulate separately and are rescaled when they are added up.  The
-// activations are pre-scaled by 2^64 to keep every product in the normal range
-// (a product is exact up to the single rounding of the FMA), and the offset
-// 128 * sum(x) is subtracted once per row:
+// a weight is ONE logic op (LOP3 / SHF) and its multiply-accumulate one FFMA.
+// The four byte positions accumulate separately and are rescaled when they are
+// added up.  The activations are pre-scaled by 2^64 to keep every product in
+// the normal range (a product is exact up to the single rounding of the FMA),
+// and the offset 128 * sum(x) is subtracted once per row:
 //   sum x*q = 2^85 * (a0 + a1*2^-8 + a2*2^-16 + a3) - 128 * sum x.
-constexpr float kXScale = 18446744073709551616.0f;          // 2^64
-constexpr float kAccScale = 38685626227668133590597632.0f;  // 2^85
 __device__ __forceinline__ void dot_unit(const uint4 &w, const float (&x)[16], float (&a)[4]) {
   const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
@@ -321,30 +324,37 @@ __device__ __forceinline__ void rows_of(const MegaPhase &ph, int cta, int grid, 
   count = (base + (cta < rem ? 1 : 0)) * ph.unit;
 }
 
-// Request stage g of this CTA's stream into ring slot `slot` (one thread).
+// Request stage g of this CTA's stream into ring slot `slot` (one thread).  A slot
+// receives stages slot, slot + n_slots, .. in order, so its cursor (layer, stage
+// within the layer) only ever moves forward by n_slots; the per-layer table
+// turns the cursor into (address, bytes) without divisions.
 __device__ __forceinline__ void issue_stage(Shared &sh, uint8_t *ring, int slot_bytes, int slot,
-                                            int g) {
-  const StreamPlan &pl = sh.plan;
+                                            int g, int n_slots) {
+  StreamPlan &pl = sh.plan;
   if (g >= pl.total)
     return;
-  int l = g / pl.per_layer, r = g - l * pl.per_layer, ph = 0;
-  if (l >= pl.L) {   // the lm_head follows the layers
-    ph = 4;
-    r = g - pl.L * pl.per_layer;
-    l = pl.L;
-  } else {
-    while (r >= pl.n[ph]) {
-      r -= pl.n[ph];
-      ++ph;
-    }
+  int l = pl.next_l[slot], r = pl.next_r[slot];
+  const uint8_t *src;
+  uint32_t bytes;
+  if (l < pl.L) {
+    const uint2 e = pl.tab[r];
+    src = sh.stream_base + (long long)l * pl.layer_bytes + e.x;
+    bytes = e.y;
+  } else {   // the lm_head follows the layers
+    const int rows = min(pl.rps[4], pl.rows[4] - r * pl.rps[4]);
+    bytes = (uint32_t)rows * pl.row_bytes[4];
+    src = sh.stream_base + (long long)pl.L * pl.layer_bytes + (long long)r * pl.rps[4] * pl.row_bytes[4];
   }
-  const int rows = min(pl.rps[ph], pl.rows[ph] - r * pl.rps[ph]);
-  const uint32_t bytes = (uint32_t)rows * pl.row_bytes[ph];
-  const uint8_t *src = sh.stream_base + (long long)l * pl.layer_bytes + (ph == 4 ? 0 : pl.off[ph]) +
-                       (long long)r * pl.rps[ph] * pl.row_bytes[ph];
   *(volatile int *)&sh.issued[slot] = g;
   mbar_expect_tx(&sh.full[slot], bytes);
   bulk_g2s(ring + (size_t)slot * slot_bytes, src, bytes, &sh.full[slot]);
+  r += n_slots;
+  while (l < pl.L && r >= pl.per_layer) {
+    r -= pl.per_layer;
+    ++l;
+  }
+  pl.next_l[slot] = l;
+  pl.next_r[slot] = r;
 }
 
 // Wait until stage `want` has landed in `slot`.  The parity of an mbarrier only
@@ -377,6 +387,7 @@ __device__ __forceinline__ void trace(Ctx &c, int layer, int slot) {
   if (c.tr != nullptr && c.ctid == 0)
     c.tr[layer * kMegaTraceSlots + slot] = clock64();
 }
+
 // ---- activation source / result sink of a projection -----------------------------
 struct XSrc {
   const uint2 *ll;      // tagged source, or
@@ -416,166 +427,174 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return __fmul_rn(__fmul_rn(g, s), u);
 }
 
-// One visit of a warp to a stage of a warp-per-row projection: the warp takes
-// rows R*wig .. R*wig+R-1 of the stage (R = 4, or 1 when all 16 warps share a
-// single stage), multiplies them with its 48 activations and finishes them.
+// One visit of a warp to a ring stage: the warp takes rows R*wig .. R*wig+R-1 of
+// the stage.  The activations come from shared memory (already normalised and
+// scaled; four LDS.128 per 16-byte weight unit, shared by the R rows), so the
+// loop needs few registers whatever K is.  The R row sums are reduced across
+// the warp "transposed": at each of the first log2(R) steps a lane hands half of
+// its rows to its partner, so R rows cost R + 4 - log2(R).. shuffles instead of
+// 5 R, and every lane ends up with the total of ONE row:
+//   R = 8: row (lane>>2)&7 with bit order (16, 8, 4);  R = 4: (16, 8);  R = 1: row 0.
 template <int R>
 __device__ __forceinline__ void visit_rows(Ctx &c, const Epi &ep, const uint8_t *base, int rows,
                                            int row_bytes, int K, int units, int wig, int lane,
-                                           const float (&xr)[3][16], float off, int first_row,
-                                           float &bestv, int &besti) {
-  // the clamp keeps the loads inside the stage
-  const uint8_t *rp[R];
+                                           const float *xsm, float off, float rinv, int first_row,
+                                           int local_row, float &bestv, int &besti) {
+  int ro[R];   // byte offsets of the warp's rows (clamped: loads stay inside the stage)
   float a[R][4];
 #pragma unroll
   for (int q = 0; q < R; ++q) {
-    rp[q] = base + (size_t)min(R * wig + q, rows - 1) * row_bytes;
+    ro[q] = min(R * wig + q, rows - 1) * row_bytes + lane * 16;
     a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
   }
 #pragma unroll
-  for (int i = 0; i < 3; ++i) {
+  for (int i = 0; i < 3; ++i) {   // K <= 1536: at most three 16-byte units per lane
     const int u = i * 32 + lane;
     if (u < units) {
+      const int qd = min(512, K - 512 * i) >> 2;   // k distance between the unit's four groups
+      const float *xp = xsm + 512 * i + 4 * lane;
+      float x[16];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float4 t = *reinterpret_cast<const float4 *>(xp + j * qd);
+        x[4 * j + 0] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+      }
       uint4 w[R];
 #pragma unroll
       for (int q = 0; q < R; ++q)
-        w[q] = *reinterpret_cast<const uint4 *>(rp[q] + u * 16);
+        w[q] = *reinterpret_cast<const uint4 *>(base + ro[q] + i * 512);
 #pragma unroll
       for (int q = 0; q < R; ++q)
-        dot_unit(w[q], xr[i], a[q]);
+        dot_unit(w[q], x, a[q]);
     }
   }
   float v[R];
 #pragma unroll
   for (int q = 0; q < R; ++q)
-    v[q] = fmaf(dot_total(a[q]), kAccScale, off);
+    v[q] = dot_total(a[q]);
+  float tot;
+  int rowc;
+  if (R == 8) {
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    float t[4], s2[2];
 #pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-    for (int q = 0; q < R; ++q)
-      v[q] += __shfl_xor_sync(0xffffffffu, v[q], o);
-  // lane q finishes row q
-  const int q = lane & (R - 1);
-  float mine = v[0];
-  const uint8_t *myrow = rp[0];
-#pragma unroll
-  for (int t = 1; t < R; ++t)
-    if (q == t) {
-      mine = v[t];
-      myrow = rp[t];
+    for (int q = 0; q < 4; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, b4 ? v[q] : v[q + 4], 16);
+      t[q] = (b4 ? v[q + 4] : v[q]) + got;
     }
-  const float2 tr = *reinterpret_cast<const float2 *>(myrow + K);
-  const float val = __fadd_rn(__fmul_rn(mine, tr.x), tr.y);
-  const int row = R * wig + q;
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, b3 ? t[q] : t[q + 2], 8);
+      s2[q] = (b3 ? t[q + 2] : t[q]) + got;
+    }
+    const float got = __shfl_xor_sync(0xffffffffu, b2 ? s2[0] : s2[1], 4);
+    tot = (b2 ? s2[1] : s2[0]) + got;
+    tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+    rowc = (b4 ? 4 : 0) + (b3 ? 2 : 0) + (b2 ? 1 : 0);
+  } else if (R == 4) {
+    const bool b4 = lane & 16, b3 = lane & 8;
+    float t[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, b4 ? v[q] : v[q + 2], 16);
+      t[q] = (b4 ? v[q + 2] : v[q]) + got;
+    }
+    const float got = __shfl_xor_sync(0xffffffffu, b3 ? t[0] : t[1], 8);
+    tot = (b3 ? t[1] : t[0]) + got;
+    tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+    rowc = (b4 ? 2 : 0) + (b3 ? 1 : 0);
+  } else {
+    tot = v[0];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    rowc = 0;
+  }
+  constexpr int kOwnerMask = R == 8 ? 3 : (R == 4 ? 7 : 31);   // one lane per row finishes it
+  const int row = R * wig + rowc;
+  const int rclamp = min(row, rows - 1);
+  const float2 tr = *reinterpret_cast<const float2 *>(base + (size_t)rclamp * row_bytes + K);
+  // sum x*q = 2^85 * tot - 128 * sum x; the RMSNorm factor applies to the whole row
+  const float dotv = __fmul_rn(fmaf(tot, kAccScale, off), rinv);
+  const float val = __fadd_rn(__fmul_rn(dotv, tr.x), tr.y);
   if (ep.kind == EP_SILU) {
-    // rows (2j, 2j+1) = (gate_j, up_j); only reached with R = 4
-    const float upv = __shfl_down_sync(0xffffffffu, val, 1);
-    if (lane < R && (lane & 1) == 0 && row + 1 < rows)
-      ll_store(ep.dst + ((first_row + row) >> 1), silu_mul(val, upv), ep.tag);
-  } else if (lane < R && row < rows) {
+    // rows (2j, 2j+1) = (gate_j, up_j) sit in partner lanes
+    const float upv = __shfl_xor_sync(0xffffffffu, val, R == 8 ? 4 : 8);
+    if ((lane & kOwnerMask) == 0 && (rowc & 1) == 0 && row + 1 < rows)
+      c.sh.mids[(local_row + row) >> 1] = silu_mul(val, upv);   // consumed by this CTA's down columns
+  } else if ((lane & kOwnerMask) == 0 && row < rows) {
     emit(c, ep, first_row + row, val, bestv, besti);
   }
 }
 
-// One projection.  Mode A (K <= 1536): a warp owns two adjacent rows of every
-// slot; mode B: all consumer threads share each row and the per-warp partial
-// sums meet in shared memory.
-__device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XSrc &xs, const Epi &ep,
-                                           float &bestv, int &besti, int tl) {
-  // Everything the row loop needs is copied into registers first: the inline
-  // asm in the loop clobbers memory, so fields read through `ph` / `c.p` would
-  // otherwise be re-fetched from constant memory at every stage.
+// One projection with rows of K <= 1536 weights.  All rows of the CTA are
+// streamed through the ring in stages of 16 rows; R rows per warp and visit:
+// 8 for long phases (two warps per stage, eight stages in flight), 4 for the
+// gate|up pairs of short phases, 1 when the whole phase is one or two stages
+// (q|k|v, o: all 16 warps take one row each).
+__device__ __forceinline__ void gemv_phase(Ctx &c, int phase_index, const XSrc &xs, const Epi &ep,
+                                           int tl) {
+  const MegaPhase &ph = c.p.phase[phase_index];
   int row_begin, nrows;
   rows_of(ph, blockIdx.x, gridDim.x, row_begin, nrows);
-  const int K = ph.K, row_bytes = ph.row_bytes, rps = ph.rps, mode = ph.mode;
+  const int K = ph.K, row_bytes = ph.row_bytes, rps = ph.rps;
   const int units = K / 16;
   const int n_slots = c.p.slots, slot_bytes = c.p.slot_bytes;
   const float eps = c.p.eps;
   Shared &sh = c.sh;
-  const int lane = c.lane, warp = c.warp, ctid = c.ctid;
+  const int lane = c.lane, warp = c.warp;
   uint8_t *const ring = c.ring;
-  float *const xsm = c.xs, *const nwsm = c.nws;
+  float *const xsm = c.xs;
   int slot = c.slot, g = c.g;
   uint32_t parity = c.parity;
-
-  // ---- stage the activation vector (and the norm weight) in shared memory ----
-  if (xs.nw != nullptr)
-    for (int i = ctid * 4; i < K; i += kCT * 4)
-      *reinterpret_cast<float4 *>(nwsm + i) = __ldg(reinterpret_cast<const float4 *>(xs.nw + i));
-  float ss = xs.ll ? stage_tagged(c, xs.ll, xs.tag, K, xsm) : stage_plain(c, xs.plain, K, xsm);
-  float rinv = 1.f;
-  if (xs.nw != nullptr) {
-    // RMSNorm, subgraph0_decode_simplify.mlir:60-72
-    ss = warp_sum(ss);
-    if (lane == 0)
-      sh.red[warp] = ss;
-  }
-  consumer_sync();
-  trace(c, tl, 12 + 4 * (int)(&ph - c.p.phase));
-  if (xs.nw != nullptr) {
-    float t = 0.f;
-#pragma unroll
-    for (int w = 0; w < kCW; ++w)
-      t += sh.red[w];
-    rinv = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), eps));
-  }
-  // ---- gather this thread's activations (same k permutation as the packed rows) ----
-  float xr[3][16];
-  float sx = 0.f;
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {
-    const int u = mode == 0 ? (i * 32 + lane) : (i * 256 + (ctid & 255));
-#pragma unroll
-    for (int e = 0; e < 16; ++e)
-      xr[i][e] = 0.f;
-    if (u < units) {
-      const int b = u >> 5, l = u & 31;
-      const int Bs = min(512, K - 512 * b), q = Bs >> 2;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const int k = 512 * b + j * q + 4 * l;
-        float4 v = *reinterpret_cast<const float4 *>(xsm + k);
-        if (xs.nw != nullptr) {
-          const float4 w4 = *reinterpret_cast<const float4 *>(nwsm + k);
-          v.x = __fmul_rn(w4.x, __fmul_rn(v.x, rinv));
-          v.y = __fmul_rn(w4.y, __fmul_rn(v.y, rinv));
-          v.z = __fmul_rn(w4.z, __fmul_rn(v.z, rinv));
-          v.w = __fmul_rn(w4.w, __fmul_rn(v.w, rinv));
-        }
-        sx += (v.x + v.y) + (v.z + v.w);
-        xr[i][4 * j + 0] = v.x * kXScale;
-        xr[i][4 * j + 1] = v.y * kXScale;
-        xr[i][4 * j + 2] = v.z * kXScale;
-        xr[i][4 * j + 3] = v.w * kXScale;
-      }
-    }
-  }
-  const float off = -128.0f * sx;   // this thread's share of the offset term
-  trace(c, tl, 13 + 4 * (int)(&ph - c.p.phase));
-
-  // ---- stream the rows --------------------------------------------------------
-  // The warps are split into stage groups that work on DIFFERENT stages at the
-  // same time (mode A: 4 groups of 4 warps, a warp takes 4 rows of its stage;
-  // mode B: 2 groups of 8 warps sharing each row).  Each visit of a warp to a
-  // stage then carries enough arithmetic to amortise the fixed latencies of a
-  // visit (barrier wait, reduction, trailer, stores, slot release), and the
-  // groups hide each other's latencies.
-  volatile int *ab = &sh.abort_flag;
   const int nstages = (nrows + rps - 1) / rps;
-  // mode A: 4 rows per warp, except for projections of one or two stages (q|k|v,
-  // o), where all 16 warps take one row each of the same stage
-  const int R = (nstages >= 3 || ep.kind == EP_SILU) ? 4 : 1;
-  const int NG = mode == 0 ? R : 2;
-  const int gw = kCW / NG;                       // warps per group
+  const int R = nstages >= 5 ? 8 : ((nstages >= 3 || ep.kind == EP_SILU) ? 4 : 1);
+  const int NG = R;                  // stage groups
+  const int gw = kCW / NG;           // warps per group (= per stage)
   const int grp = warp / gw, wig = warp - grp * gw;
   const int nrounds = (nstages + NG - 1) / NG;
+
+  // ---- stage the activation vector in shared memory ----------------------------
+  float ss = 0.f, sx = 0.f;
+  if (xs.ll != nullptr)
+    stage_tagged(c, xs.ll, xs.tag, K, xsm, xs.nw, ss, sx);
+  else
+    stage_plain(c, xs.plain, K, xsm, xs.nw, ss, sx);
+  ss = warp_sum(ss);
+  sx = warp_sum(sx);
+  if (lane == 0) {
+    sh.red[warp] = ss;
+    sh.red2[warp] = sx;
+  }
+  consumer_sync();
+  trace(c, tl, 12 + 4 * phase_index);
+  float rinv = 1.f, off;
+  {
+    float t = 0.f, t2 = 0.f;
+#pragma unroll
+    for (int w = 0; w < kCW; ++w) {
+      t += sh.red[w];
+      t2 += sh.red2[w];
+    }
+    // RMSNorm, subgraph0_decode_simplify.mlir:60-72 (the factor multiplies the row sums)
+    if (xs.nw != nullptr)
+      rinv = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), eps));
+    off = -128.0f * t2;
+  }
+
+  // ---- stream the rows --------------------------------------------------------
+  volatile int *ab = &sh.abort_flag;
+  float bestv = -INFINITY;
+  int besti = 0x7fffffff;
   int my_slot = slot + grp;
   uint32_t my_par = parity;
-  if (my_slot >= n_slots) {
+  while (my_slot >= n_slots) {
     my_slot -= n_slots;
     my_par ^= 1u;
   }
-  int flush_base = 0;
   for (int rd = 0; rd < nrounds; ++rd) {
     const int st = rd * NG + grp;
     if (st < nstages) {
@@ -584,45 +603,15 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
       if (!stage_wait(sh, my_slot, my_par, g + st, c.err, ab))
         atomicCAS((int *)c.err, 0, 200 + my_slot);
       const uint8_t *base = ring + (size_t)my_slot * slot_bytes;
-      if (mode == 0) {
-        if (R == 4)
-          visit_rows<4>(c, ep, base, rows, row_bytes, K, units, wig, lane, xr, off, row_begin + r0,
-                        bestv, besti);
-        else
-          visit_rows<1>(c, ep, base, rows, row_bytes, K, units, wig, lane, xr, off, row_begin + r0,
-                        bestv, besti);
-      } else {
-        const int tig = ctid & 255;   // thread within the group
-        for (int r = 0; r < rows; r += 2) {
-          const uint8_t *rowa = base + (size_t)r * row_bytes;
-          const uint8_t *rowb = base + (size_t)min(r + 1, rows - 1) * row_bytes;
-          float a[4] = {0.f, 0.f, 0.f, 0.f}, b[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-          for (int i = 0; i < 3; ++i) {
-            const int u = i * 256 + tig;
-            if (u < units) {
-              const uint4 wa = *reinterpret_cast<const uint4 *>(rowa + u * 16);
-              const uint4 wb = *reinterpret_cast<const uint4 *>(rowb + u * 16);
-              dot_unit(wa, xr[i], a);
-              dot_unit(wb, xr[i], b);
-            }
-          }
-          float va = fmaf(dot_total(a), kAccScale, off);
-          float vb = fmaf(dot_total(b), kAccScale, off);
-          va = warp_sum(va);
-          vb = warp_sum(vb);
-          if (lane == 0) {
-            sh.part[warp][r0 + r - flush_base] = va;
-            if (r + 1 < rows)
-              sh.part[warp][r0 + r + 1 - flush_base] = vb;
-          }
-          if (tig == 0) {
-            sh.rowinfo[r0 + r - flush_base] = *reinterpret_cast<const float2 *>(rowa + K);
-            if (r + 1 < rows)
-              sh.rowinfo[r0 + r + 1 - flush_base] = *reinterpret_cast<const float2 *>(rowb + K);
-          }
-        }
-      }
+      if (R == 8)
+        visit_rows<8>(c, ep, base, rows, row_bytes, K, units, wig, lane, xsm, off, rinv,
+                      row_begin + r0, r0, bestv, besti);
+      else if (R == 4)
+        visit_rows<4>(c, ep, base, rows, row_bytes, K, units, wig, lane, xsm, off, rinv,
+                      row_begin + r0, r0, bestv, besti);
+      else
+        visit_rows<1>(c, ep, base, rows, row_bytes, K, units, wig, lane, xsm, off, rinv,
+                      row_begin + r0, r0, bestv, besti);
       // Release the slot; the warp of the group that finishes it last refills it
       // with the stage one ring-length ahead.  (No fence on purpose: the slot's
       // bytes were consumed by arithmetic the values above depend on, so every
@@ -631,39 +620,13 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
       __syncwarp();
       if (lane == 0 && atomicAdd(&sh.done[my_slot], 1) == gw - 1) {
         sh.done[my_slot] = 0;
-        issue_stage(sh, ring, slot_bytes, my_slot, g + st + n_slots);
+        issue_stage(sh, ring, slot_bytes, my_slot, g + st + n_slots, n_slots);
       }
     }
     my_slot += NG;
-    if (my_slot >= n_slots) {
+    while (my_slot >= n_slots) {
       my_slot -= n_slots;
       my_par ^= 1u;
-    }
-    if (mode == 1) {
-      const int covered = min(nrows, (rd + 1) * NG * rps);
-      const int pending = covered - flush_base;
-      if (pending + NG * rps > kMegaMaxRowsB || rd + 1 == nrounds) {
-        // fold the per-warp partial sums of the pending rows (fixed warp order)
-        consumer_sync();
-        auto row_value = [&](int i) {
-          const int owner = ((flush_base + i) / rps) % NG;   // group that streamed this row
-          float sacc = 0.f;
-#pragma unroll
-          for (int w = 0; w < 8; ++w)
-            sacc += sh.part[owner * 8 + w][i];
-          const float2 t = sh.rowinfo[i];
-          return __fadd_rn(__fmul_rn(sacc, t.x), t.y);
-        };
-        if (ep.kind == EP_SILU) {
-          if (ctid < pending / 2)
-            ll_store(ep.dst + ((row_begin + flush_base) >> 1) + ctid,
-                     silu_mul(row_value(2 * ctid), row_value(2 * ctid + 1)), ep.tag);
-        } else if (ctid < pending) {
-          emit(c, ep, row_begin + flush_base + ctid, row_value(ctid), bestv, besti);
-        }
-        consumer_sync();
-        flush_base = covered;
-      }
     }
   }
   // this phase used `nstages` stages of the ring
@@ -677,8 +640,163 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, const MegaPhase &ph, const XS
   c.slot = slot;
   c.parity = parity;
   c.g = g;
+  if (ep.kind == EP_LOGITS) {
+    // this warp's first maximum, for the CTA's candidate
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float ov = __shfl_xor_sync(0xffffffffu, bestv, o);
+      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
+      if (ov > bestv || (ov == bestv && oi < besti)) {
+        bestv = ov;
+        besti = oi;
+      }
+    }
+    if (lane == 0) {
+      sh.bestv[warp] = bestv;
+      sh.besti[warp] = besti;
+    }
+  }
   // the staged vector is reused by the next phase
   consumer_sync();
+}
+
+// ---- down projection, by columns -------------------------------------------------
+// x2 = x1 + mid @ Wdown (subgraph0_decode_simplify.mlir:232-244).  The CTA that
+// produced mid[k] (its gate|up pairs) also owns COLUMN k of Wdown: H bytes, one
+// per output channel.  So the MLP intermediate never leaves the CTA; what crosses
+// CTAs instead is each CTA's vector of H partial sums, and every CTA then adds up
+// the partials of its own few output channels (in CTA order: the result does not
+// depend on timing), applies the channel scale, adds the residual and publishes
+// its slice of x2.
+// Threads: 4 groups of 4 warps; group kg takes columns kg, kg+4, .. of a stage,
+// thread t of a group takes the 32-bit words t, t+128, .. of a column (4 output
+// channels each).  No shuffles: one accumulator per (thread, channel).
+constexpr int kColWords = 3;   // 32-bit words of a column per thread: H <= 1536
+__device__ __forceinline__ void down_cols_phase(Ctx &c, int layer) {
+  const MegaParams &p = c.p;
+  Shared &sh = c.sh;
+  const MegaPhase &ph = p.phase[3];
+  int col_begin, ncols;
+  rows_of(ph, blockIdx.x, gridDim.x, col_begin, ncols);
+  const int H = p.H, rps = ph.rps, nwords = H >> 2;
+  const int n_slots = p.slots, slot_bytes = p.slot_bytes;
+  const int lane = c.lane, warp = c.warp, ctid = c.ctid;
+  const int kg = warp >> 2, t128 = ctid & 127;
+  const int par = layer & 1;
+  uint8_t *const ring = c.ring;
+  volatile int *ab = &sh.abort_flag;
+  const int nstages = (ncols + rps - 1) / rps;
+  int slot = c.slot, g = c.g;
+  uint32_t parity = c.parity;
+
+  // this CTA's output channels: residual and channel scale are requested now,
+  // long before they are needed
+  const int grid = gridDim.x;
+  const int base_n = H / grid, rem_n = H % grid;
+  const int nb = blockIdx.x * base_n + min((int)blockIdx.x, rem_n);
+  const int ncnt = base_n + ((int)blockIdx.x < rem_n ? 1 : 0);
+  float my_res = 0.f, my_scale = 0.f;   // of channel nb + warp (lane 0; one channel per warp, checked on the host)
+  if (lane == 0 && warp < ncnt) {
+    my_scale = __ldg(p.down_scale[layer] + nb + warp);
+    my_res = ll_wait1(c, p.ll_xb + (size_t)par * H + nb + warp, tag_of(c, layer, T_XB));
+  }
+
+  float acc[kColWords][4];
+#pragma unroll
+  for (int w = 0; w < kColWords; ++w)
+    acc[w][0] = acc[w][1] = acc[w][2] = acc[w][3] = 0.f;
+  for (int st = 0; st < nstages; ++st) {
+    const int cols = min(rps, ncols - st * rps);
+    if (!stage_wait(sh, slot, parity, g + st, c.err, ab))
+      atomicCAS((int *)c.err, 0, 300 + slot);
+    const uint8_t *base = ring + (size_t)slot * slot_bytes;
+    for (int kk = kg; kk < cols; kk += 4) {
+      const float x = sh.mids[st * rps + kk] * kXScale;
+      const uint32_t *col = reinterpret_cast<const uint32_t *>(base + (size_t)kk * H);
+#pragma unroll
+      for (int w = 0; w < kColWords; ++w) {
+        const int wi = t128 + 128 * w;
+        if (wi < nwords) {
+          const uint32_t u = col[wi];
+          acc[w][0] = fmaf(x, __uint_as_float(u & 0x000000FFu), acc[w][0]);
+          acc[w][1] = fmaf(x, __uint_as_float(u & 0x0000FF00u), acc[w][1]);
+          acc[w][2] = fmaf(x, __uint_as_float(u & 0x00FF0000u), acc[w][2]);
+          acc[w][3] = fmaf(x, __uint_as_float(u >> 24), acc[w][3]);
+        }
+      }
+    }
+    __syncwarp();
+    if (lane == 0 && atomicAdd(&sh.done[slot], 1) == kCW - 1) {
+      sh.done[slot] = 0;
+      issue_stage(sh, ring, slot_bytes, slot, g + st + n_slots, n_slots);
+    }
+    if (++slot == n_slots) {
+      slot = 0;
+      parity ^= 1u;
+    }
+  }
+  c.slot = slot;
+  c.parity = parity;
+  c.g = g + nstages;
+  trace(c, layer, 24);
+
+  // ---- add up the four column groups (fixed order), publish the CTA's partial sums ----
+  float *gs = c.xs;   // [4][H]
+#pragma unroll
+  for (int w = 0; w < kColWords; ++w) {
+    const int wi = t128 + 128 * w;
+    if (wi < nwords)
+      *reinterpret_cast<float4 *>(gs + (size_t)kg * H + 4 * wi) =
+          make_float4(acc[w][0], acc[w][1] * 0.00390625f, acc[w][2] * 0.0000152587890625f, acc[w][3]);
+  }
+  if (warp == 0) {
+    float sx = 0.f;
+    for (int k = lane; k < ncols; k += 32)
+      sx += sh.mids[k];
+    sx = warp_sum(sx);
+    if (lane == 0)
+      sh.red[0] = sx;
+  }
+  consumer_sync();
+  const float off = -128.0f * sh.red[0];
+  uint2 *dpart = p.ll_dpart + ((size_t)par * grid + blockIdx.x) * H;
+  const uint32_t dtag = tag_of(c, layer, T_DPART);
+  for (int n = ctid; n < H; n += kCT) {
+    const float t = (gs[n] + gs[H + n]) + (gs[2 * H + n] + gs[3 * H + n]);
+    ll_store(dpart + n, fmaf(t, kAccScale, off), dtag);
+  }
+  trace(c, layer, 25);
+  // ---- this CTA's output channels: sum over all CTAs, scale, residual ------------------
+  if (warp < ncnt) {
+    const int n = nb + warp;
+    const uint2 *all = p.ll_dpart + (size_t)par * grid * H + n;
+    float sum = 0.f;
+    for (int c0 = 0; c0 < grid; c0 += 32 * 8) {
+      uint2 r[8];
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int cta = c0 + lane + 32 * q;
+        if (cta < grid)
+          r[q] = ll_load1(all + (size_t)cta * H);
+      }
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const int cta = c0 + lane + 32 * q;
+        if (cta < grid) {
+          float v = __uint_as_float(r[q].x);
+          if (r[q].y != dtag)
+            v = ll_wait1(c, all + (size_t)cta * H, dtag);
+          sum += v;
+        }
+      }
+    }
+    sum = warp_sum(sum);
+    if (lane == 0)
+      ll_store(p.ll_xa + (size_t)par * H + n, __fadd_rn(my_res, __fmul_rn(sum, my_scale)),
+               tag_of(c, layer, T_XA));
+  }
+  trace(c, layer, 26);
+  consumer_sync();   // xs and mids are reused by the next phase
 }
 
 // ---- attention -------------------------------------------------------------------
@@ -727,158 +845,191 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
   const float scale = rsqrtf((float)D);
   const int jj = 4 * (lane & 15);       // rotary index of this lane's 4 dims
   const bool upper = lane >= 16;
+  const bool scanner = warp < kAW;      // warps 0..kAW-1 scan; warp kAW writes the new cache row
+  const bool has_new = pos >= s0 && pos < s1;
+  constexpr int NB = G <= 4 ? 4 : 2;    // rows in flight per warp (register budget: 128)
 
-  // ---- stage q (G heads), k, v of this kv head: xs[0 .. (G+2)*D) ----------------
-  {
-    const uint2 *src = p.ll_qkv + (size_t)par * (QD + 2 * KD);
-    const uint32_t tag = tag_of(c, layer, T_QKV);
-    const int nv = (G + 2) * (D / 2);
-    for (int v = c.ctid; v < nv; v += kCT) {
-      const int e = 2 * v;   // element in the staged [q | k | v] order
-      int srce;
-      if (e < G * D)
-        srce = hk * G * D + e;
-      else if (e < (G + 1) * D)
-        srce = QD + hk * D + (e - G * D);
-      else
-        srce = QD + KD + hk * D + (e - (G + 1) * D);
-      uint4 r = ll_load2(src + srce);
-      r = ll_wait2(c, src + srce, tag, r);
-      *reinterpret_cast<float2 *>(c.xs + e) = make_float2(__uint_as_float(r.x), __uint_as_float(r.z));
-    }
-  }
-  consumer_sync();
-
-  auto rope4 = [&](float (&v)[4], const float *nw) {
-    if (nw != nullptr) {
-      float s = 0.f;
+  // ---- request the first rows of this warp: they do not depend on this step
+  //      (row `pos` is this step's own k / v and is taken from shared memory below)
+  float4 kr[NB], vr[NB];
 #pragma unroll
-      for (int e = 0; e < 4; ++e)
-        s = __fadd_rn(s, __fmul_rn(v[e], v[e]));
-      s = warp_sum(s);
-      const float r = rsqrtf(__fadd_rn(__fmul_rn(s, 1.0f / (float)D), p.eps));
-      const float4 w4 = __ldg(reinterpret_cast<const float4 *>(nw + 4 * lane));
-      v[0] = __fmul_rn(w4.x, __fmul_rn(v[0], r));
-      v[1] = __fmul_rn(w4.y, __fmul_rn(v[1], r));
-      v[2] = __fmul_rn(w4.z, __fmul_rn(v[2], r));
-      v[3] = __fmul_rn(w4.w, __fmul_rn(v[3], r));
-    }
-#pragma unroll
-    for (int e = 0; e < 4; ++e) {
-      const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
-      const float cs = c.sh.cs[jj + e], sn = c.sh.sn[jj + e];
-      // lower half: x*cos + (-x[j+64])*sin ; upper half: x*cos + x[j-64]*sin
-      v[e] = __fadd_rn(__fmul_rn(v[e], cs), __fmul_rn(upper ? other : -other, sn));
-    }
-  };
-
-  // new K / V row (written by the CTA whose range contains pos)
-  if (pos >= s0 && pos < s1 && warp == 0) {
-    const float4 k4 = *reinterpret_cast<const float4 *>(c.xs + G * D + 4 * lane);
-    const float4 v4 = *reinterpret_cast<const float4 *>(c.xs + (G + 1) * D + 4 * lane);
-    float kv[4] = {k4.x, k4.y, k4.z, k4.w};
-    rope4(kv, kn);
-    const float4 ko = make_float4(kv[0], kv[1], kv[2], kv[3]);
-    *reinterpret_cast<float4 *>(kc + (size_t)pos * D + 4 * lane) = ko;
-    *reinterpret_cast<float4 *>(vc + (size_t)pos * D + 4 * lane) = v4;
-    float *ks = p.kv_stage + (size_t)(2 * layer) * p.kvh * D + hk * D;
-    float *vs = p.kv_stage + (size_t)(2 * layer + 1) * p.kvh * D + hk * D;
-    *reinterpret_cast<float4 *>(ks + 4 * lane) = ko;
-    *reinterpret_cast<float4 *>(vs + 4 * lane) = v4;
-  }
-  float qr[G][4];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    const float4 q4 = *reinterpret_cast<const float4 *>(c.xs + g * D + 4 * lane);
-    qr[g][0] = q4.x; qr[g][1] = q4.y; qr[g][2] = q4.z; qr[g][3] = q4.w;
-    rope4(qr[g], qn);
-  }
-  consumer_sync();  // the new row is visible to the whole CTA; xs may be reused
-  trace(c, layer, 8);
-
-  float m[G], l[G], acc[G][4];
-#pragma unroll
-  for (int g = 0; g < G; ++g) {
-    m[g] = kSeed;
-    l[g] = 0.f;
-    acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
-  }
-  constexpr int NB = G <= 4 ? 4 : 2;   // rows in flight per warp (register budget: 128)
-  for (int j0 = s0 + warp; j0 < s1; j0 += NB * kCW) {
-    // NB rows in flight: all loads are issued before the first use
-    float4 kr[NB], vr[NB];
-#pragma unroll
-    for (int i = 0; i < NB; ++i) {
-      const int j = min(j0 + i * kCW, s1 - 1);
+  for (int i = 0; i < NB; ++i) {
+    const int j = s0 + warp + i * kAW;
+    kr[i] = vr[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (scanner && j < s1 && j != pos) {
       kr[i] = ldcg4(kc + (size_t)j * D + 4 * lane);
       vr[i] = ldcg4(vc + (size_t)j * D + 4 * lane);
     }
-    float s[NB][G];
-#pragma unroll
-    for (int i = 0; i < NB; ++i)
-#pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float d = qr[g][0] * kr[i].x;
-        d = fmaf(qr[g][1], kr[i].y, d);
-        d = fmaf(qr[g][2], kr[i].z, d);
-        s[i][g] = fmaf(qr[g][3], kr[i].w, d);
+  }
+
+  // ---- stage q (G heads), k, v of this kv head: xs[0 .. (G+2)*D), q and k rotated ----
+  // subgraph0_decode_simplify.mlir:111-150: out[j] = x[j]*cos - x[j+64]*sin,
+  // out[j+64] = x[j+64]*cos + x[j]*sin.  Without QK-norm the thread that stages
+  // elements (j, j+1) of a head also stages (j+64, j+65) and rotates both pairs.
+  {
+    const uint2 *src = p.ll_qkv + (size_t)par * (QD + 2 * KD);
+    const uint32_t tag = tag_of(c, layer, T_QKV);
+    const bool fused_rope = qn == nullptr && kn == nullptr;
+    const int t = c.ctid;
+    if (t < (G + 1) * (D / 4)) {
+      const int hh = t / (D / 4), j = 2 * (t - hh * (D / 4));   // head (G = the key), pair index
+      const int base = hh < G ? hk * G * D + hh * D : QD + hk * D;
+      uint4 lo = ll_load2(src + base + j), hi = ll_load2(src + base + j + D / 2);
+      lo = ll_wait2(c, src + base + j, tag, lo);
+      hi = ll_wait2(c, src + base + j + D / 2, tag, hi);
+      float x0 = __uint_as_float(lo.x), x1 = __uint_as_float(lo.z);
+      float y0 = __uint_as_float(hi.x), y1 = __uint_as_float(hi.z);
+      if (fused_rope) {
+        const float c0 = c.sh.cs[j], c1 = c.sh.cs[j + 1], n0 = c.sh.sn[j], n1 = c.sh.sn[j + 1];
+        const float a0 = __fadd_rn(__fmul_rn(x0, c0), __fmul_rn(-y0, n0));
+        const float a1 = __fadd_rn(__fmul_rn(x1, c1), __fmul_rn(-y1, n1));
+        const float b0 = __fadd_rn(__fmul_rn(y0, c0), __fmul_rn(x0, n0));
+        const float b1 = __fadd_rn(__fmul_rn(y1, c1), __fmul_rn(x1, n1));
+        x0 = a0; x1 = a1; y0 = b0; y1 = b1;
       }
+      *reinterpret_cast<float2 *>(c.xs + hh * D + j) = make_float2(x0, x1);
+      *reinterpret_cast<float2 *>(c.xs + hh * D + j + D / 2) = make_float2(y0, y1);
+    } else if (t < (G + 1) * (D / 4) + D / 2) {
+      const int j = 2 * (t - (G + 1) * (D / 4));
+      const uint2 *sp = src + QD + KD + hk * D + j;
+      uint4 r = ll_load2(sp);
+      r = ll_wait2(c, sp, tag, r);
+      *reinterpret_cast<float2 *>(c.xs + (G + 1) * D + j) = make_float2(__uint_as_float(r.x), __uint_as_float(r.z));
+    }
+    consumer_sync();
+    if (!fused_rope) {
+      // QK-norm first (needs the whole head): warp hh normalises and rotates head hh in place
+      if (warp <= G) {
+        const float4 x4 = *reinterpret_cast<const float4 *>(c.xs + warp * D + 4 * lane);
+        float v[4] = {x4.x, x4.y, x4.z, x4.w};
+        const float *nw = warp < G ? qn : kn;
+        if (nw != nullptr) {
+          float ss = 0.f;
 #pragma unroll
-    for (int i = 0; i < NB; ++i)
+          for (int e = 0; e < 4; ++e)
+            ss = __fadd_rn(ss, __fmul_rn(v[e], v[e]));
+          ss = warp_sum(ss);
+          const float r = rsqrtf(__fadd_rn(__fmul_rn(ss, 1.0f / (float)D), p.eps));
+          const float4 w4 = __ldg(reinterpret_cast<const float4 *>(nw + 4 * lane));
+          v[0] = __fmul_rn(w4.x, __fmul_rn(v[0], r));
+          v[1] = __fmul_rn(w4.y, __fmul_rn(v[1], r));
+          v[2] = __fmul_rn(w4.z, __fmul_rn(v[2], r));
+          v[3] = __fmul_rn(w4.w, __fmul_rn(v[3], r));
+        }
 #pragma unroll
-      for (int g = 0; g < G; ++g)
-        s[i][g] = warp_sum(s[i][g]) * scale;
+        for (int e = 0; e < 4; ++e) {
+          const float other = __shfl_xor_sync(0xffffffffu, v[e], 16);
+          const float cs = c.sh.cs[jj + e], sn = c.sh.sn[jj + e];
+          v[e] = __fadd_rn(__fmul_rn(v[e], cs), __fmul_rn(upper ? other : -other, sn));
+        }
+        *reinterpret_cast<float4 *>(c.xs + warp * D + 4 * lane) = make_float4(v[0], v[1], v[2], v[3]);
+      }
+      consumer_sync();
+    }
+  }
+  // this step's own key (rotated) and value: used by the scanning warps of the CTA
+  // whose range holds `pos`, written to the cache by warp kAW of that CTA
+  float4 knew = make_float4(0.f, 0.f, 0.f, 0.f), vnew = knew;
+  if (has_new && warp <= kAW) {
+    knew = *reinterpret_cast<const float4 *>(c.xs + G * D + 4 * lane);
+    vnew = *reinterpret_cast<const float4 *>(c.xs + (G + 1) * D + 4 * lane);
+    if (warp == kAW) {
+      *reinterpret_cast<float4 *>(kc + (size_t)pos * D + 4 * lane) = knew;
+      *reinterpret_cast<float4 *>(vc + (size_t)pos * D + 4 * lane) = vnew;
+      float *ks = p.kv_stage + (size_t)(2 * layer) * p.kvh * D + hk * D;
+      float *vs = p.kv_stage + (size_t)(2 * layer + 1) * p.kvh * D + hk * D;
+      *reinterpret_cast<float4 *>(ks + 4 * lane) = knew;
+      *reinterpret_cast<float4 *>(vs + 4 * lane) = vnew;
+    }
+  }
+  trace(c, layer, 8);
+
+  float *aacc = c.xs + (G + 2) * D;   // [kAW][G][D], beside the staged q | k | v
+  if (scanner) {
+    float qr[G][4];
 #pragma unroll
-    for (int i = 0; i < NB; ++i) {
-      if (j0 + i * kCW < s1) {   // warp-uniform
+    for (int g = 0; g < G; ++g) {
+      const float4 q4 = *reinterpret_cast<const float4 *>(c.xs + g * D + 4 * lane);
+      qr[g][0] = q4.x; qr[g][1] = q4.y; qr[g][2] = q4.z; qr[g][3] = q4.w;
+    }
+    float m[G], l[G], acc[G][4];
 #pragma unroll
-        for (int g = 0; g < G; ++g) {
-          const float nm = fmaxf(m[g], s[i][g]);
-          const float alpha = expf(m[g] - nm), pw = expf(s[i][g] - nm);
-          l[g] = fmaf(l[g], alpha, pw);
-          acc[g][0] = fmaf(acc[g][0], alpha, pw * vr[i].x);
-          acc[g][1] = fmaf(acc[g][1], alpha, pw * vr[i].y);
-          acc[g][2] = fmaf(acc[g][2], alpha, pw * vr[i].z);
-          acc[g][3] = fmaf(acc[g][3], alpha, pw * vr[i].w);
-          m[g] = nm;
+    for (int g = 0; g < G; ++g) {
+      m[g] = kSeed;
+      l[g] = 0.f;
+      acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
+    }
+    for (int j0 = s0 + warp; j0 < s1; j0 += NB * kAW) {
+      if (j0 != s0 + warp) {
+        // later rounds: NB rows in flight, all loads issued before the first use
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+          const int j = min(j0 + i * kAW, s1 - 1);
+          if (j != pos) {
+            kr[i] = ldcg4(kc + (size_t)j * D + 4 * lane);
+            vr[i] = ldcg4(vc + (size_t)j * D + 4 * lane);
+          }
         }
       }
-    }
-  }
-  trace(c, layer, 9);
-  // ---- fold the warps of this CTA (fixed warp order) ------------------------------
-  float *aacc = c.xs;   // [kAW][G][D]
-  // round 1: warps 8..15 hand their state to warps 0..7 (online-softmax merge)
-  if (warp >= kAW) {
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      if (lane == 0) {
-        c.sh.am[warp - kAW][g] = m[g];
-        c.sh.al[warp - kAW][g] = l[g];
+      for (int i = 0; i < NB; ++i)
+        if (j0 + i * kAW == pos) {
+          kr[i] = knew;
+          vr[i] = vnew;
+        }
+      float s[NB][G];
+#pragma unroll
+      for (int i = 0; i < NB; ++i)
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+          float d = qr[g][0] * kr[i].x;
+          d = fmaf(qr[g][1], kr[i].y, d);
+          d = fmaf(qr[g][2], kr[i].z, d);
+          s[i][g] = fmaf(qr[g][3], kr[i].w, d);
+        }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)   // the NB * G reductions advance together
+#pragma unroll
+        for (int i = 0; i < NB; ++i)
+#pragma unroll
+          for (int g = 0; g < G; ++g)
+            s[i][g] += __shfl_xor_sync(0xffffffffu, s[i][g], o);
+#pragma unroll
+      for (int i = 0; i < NB; ++i)
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          s[i][g] *= scale;
+      // one softmax update for the NB rows (tosa.py:14245-14252 applied to a block):
+      // rows beyond the range get weight 0.  __expf: the arguments are <= 0 and
+      // the error (about 1e-6 relative) is far inside the logits tolerance.
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float nm = m[g];
+#pragma unroll
+        for (int i = 0; i < NB; ++i)
+          if (j0 + i * kAW < s1)
+            nm = fmaxf(nm, s[i][g]);
+        const float alpha = __expf(m[g] - nm);
+        float pw[NB];
+#pragma unroll
+        for (int i = 0; i < NB; ++i)
+          pw[i] = (j0 + i * kAW < s1) ? __expf(s[i][g] - nm) : 0.f;
+        float ll = l[g] * alpha, a0 = acc[g][0] * alpha, a1 = acc[g][1] * alpha,
+              a2 = acc[g][2] * alpha, a3 = acc[g][3] * alpha;
+#pragma unroll
+        for (int i = 0; i < NB; ++i) {
+          ll += pw[i];
+          a0 = fmaf(pw[i], vr[i].x, a0);
+          a1 = fmaf(pw[i], vr[i].y, a1);
+          a2 = fmaf(pw[i], vr[i].z, a2);
+          a3 = fmaf(pw[i], vr[i].w, a3);
+        }
+        l[g] = ll;
+        acc[g][0] = a0; acc[g][1] = a1; acc[g][2] = a2; acc[g][3] = a3;
+        m[g] = nm;
       }
-      *reinterpret_cast<float4 *>(aacc + ((size_t)(warp - kAW) * G + g) * D + 4 * lane) =
-          make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
     }
-  }
-  consumer_sync();
-  if (warp < kAW) {
-#pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float om = c.sh.am[warp][g], ol = c.sh.al[warp][g];
-      const float4 oa = *reinterpret_cast<const float4 *>(aacc + ((size_t)warp * G + g) * D + 4 * lane);
-      const float nm = fmaxf(m[g], om);
-      const float a = expf(m[g] - nm), b = expf(om - nm);
-      l[g] = fmaf(l[g], a, ol * b);
-      acc[g][0] = fmaf(acc[g][0], a, oa.x * b);
-      acc[g][1] = fmaf(acc[g][1], a, oa.y * b);
-      acc[g][2] = fmaf(acc[g][2], a, oa.z * b);
-      acc[g][3] = fmaf(acc[g][3], a, oa.w * b);
-      m[g] = nm;
-    }
-  }
-  consumer_sync();
-  // round 2: warps 0..7 publish, then the CTA folds them (fixed warp order)
-  if (warp < kAW) {
+    // publish this warp's state to the CTA
 #pragma unroll
     for (int g = 0; g < G; ++g) {
       if (lane == 0) {
@@ -889,23 +1040,19 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
           make_float4(acc[g][0], acc[g][1], acc[g][2], acc[g][3]);
     }
   }
+  trace(c, layer, 9);
   consumer_sync();
-  // weights of the 8 warp states, once per head
-  if (c.ctid < G) {
-    const int g = c.ctid;
+  // ---- fold the warps of this CTA (fixed warp order) ------------------------------
+  // weights of the scanning warps' states: thread (g, w) takes one
+  if (c.ctid < G * kAW) {
+    const int g = c.ctid / kAW, w = c.ctid - g * kAW;
     float M = kSeed;
 #pragma unroll
-    for (int w = 0; w < kAW; ++w)
-      M = fmaxf(M, c.sh.am[w][g]);
-    float L = 0.f;
-#pragma unroll
-    for (int w = 0; w < kAW; ++w) {
-      const float b = expf(c.sh.am[w][g] - M);
-      c.sh.fw[g * kAW + w] = b;
-      L = fmaf(c.sh.al[w][g], b, L);
-    }
-    c.sh.fm[g] = M;
-    c.sh.fl[g] = L;
+    for (int x = 0; x < kAW; ++x)
+      M = fmaxf(M, c.sh.am[x][g]);
+    c.sh.fw[g * kAW + w] = expf(c.sh.am[w][g] - M);
+    if (w == 0)
+      c.sh.fm[g] = M;
   }
   consumer_sync();
   const int stride = D + 2;
@@ -920,11 +1067,15 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
     uint2 *dst = part + ((size_t)(hk * G + g) * S + split) * stride;
     ll_store(dst + d, A, ptag);
     if (d == 0) {
+      float L = 0.f;
+#pragma unroll
+      for (int w = 0; w < kAW; ++w)
+        L = fmaf(c.sh.al[w][g], c.sh.fw[g * kAW + w], L);
       ll_store(dst + D, c.sh.fm[g], ptag);
-      ll_store(dst + D + 1, c.sh.fl[g], ptag);
+      ll_store(dst + D + 1, L, ptag);
     }
   }
-  consumer_sync();   // aacc (in xs) has been read: xs is reused below
+  consumer_sync();   // q | k | v and aacc (in xs) have been read: xs is reused below
   trace(c, layer, 10);
   // ---- fold the splits for this CTA's slice of the G*D outputs ----------------------
   // (frontend/Python/ops/tosa.py:14502-14594): weights exp(m_s - M), then sums in
@@ -1027,8 +1178,7 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Shared &sh = *reinterpret_cast<Shared *>(smem_raw);
   float *xs = reinterpret_cast<float *>(smem_raw + ((sizeof(Shared) + 127) / 128) * 128);
-  float *nws = xs + p.xs_floats;
-  uint8_t *ring = reinterpret_cast<uint8_t *>(nws + p.nws_floats);
+  uint8_t *ring = reinterpret_cast<uint8_t *>(xs + p.xs_floats);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *err = p.error;
 
@@ -1062,6 +1212,24 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
     pl.layer_bytes = off;
     pl.L = p.L;
     pl.total = p.L * pl.per_layer + pl.n[4];
+    {
+      int r = 0;
+      for (int i = 0; i < 4; ++i)
+        for (int q = 0; q < pl.n[i]; ++q, ++r) {
+          const int rows = min(pl.rps[i], pl.rows[i] - q * pl.rps[i]);
+          pl.tab[r] = make_uint2((uint32_t)(pl.off[i] + (long long)q * pl.rps[i] * pl.row_bytes[i]),
+                                 (uint32_t)rows * pl.row_bytes[i]);
+        }
+      for (int sl = 0; sl < p.slots; ++sl) {
+        int l = 0, rr = sl;
+        while (l < pl.L && rr >= pl.per_layer) {
+          rr -= pl.per_layer;
+          ++l;
+        }
+        pl.next_l[sl] = l;
+        pl.next_r[sl] = rr;
+      }
+    }
     sh.stream_base = p.stream + p.cta_off[blockIdx.x];
   }
   const int token = p.state[0], pos = p.state[1];
@@ -1074,17 +1242,15 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
   __syncthreads();
   if (threadIdx.x == 0)   // fill the ring
     for (int s = 0; s < p.slots; ++s)
-      issue_stage(sh, ring, p.slot_bytes, s, s);
+      issue_stage(sh, ring, p.slot_bytes, s, s, p.slots);
 
   // ================= consumers ===================================================
   const uint32_t tags_per_launch = 8u * (uint32_t)(p.L + 3);
-  Ctx c{p, sh, xs, nws, ring, err, (int)threadIdx.x, lane, warp, 0, 0u, 0,
+  Ctx c{p, sh, xs, ring, err, (int)threadIdx.x, lane, warp, 0, 0u, 0,
         ((uint32_t)p.state[4] + 1u) * tags_per_launch,
         (p.trace != nullptr && blockIdx.x % p.trace_stride == 0)
             ? p.trace + (size_t)(blockIdx.x / p.trace_stride) * (p.L + 1) * kMegaTraceSlots
             : nullptr};
-  float bestv = -INFINITY;
-  int besti = 0x7fffffff;
   const int H = p.H, QD = p.qh * D, KD = p.kvh * D;
   const float *embed_row = p.embed + (size_t)token * H;
   // One loop over (layer, projection) so that the projection body exists once:
@@ -1114,21 +1280,19 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
         xsrc = XSrc{p.ll_attn + (size_t)par * QD, nullptr, tag_of(c, l, T_ATTN), nullptr};
         ep = Epi{EP_RESIDUAL, p.ll_xb + (size_t)par * H, tag_of(c, l, T_XB),
                  xin_ll, embed_row, xin_tag, nullptr};
-      } else if (step == 2) {  // silu(gate) * up <- RMSNorm(x1)
+      } else if (step == 2) {  // silu(gate) * up <- RMSNorm(x1), kept in shared memory
         phase_index = 2;
         xsrc = XSrc{p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), p.lvec[4 * l + 1]};
-        ep = Epi{EP_SILU, p.ll_mid + (size_t)par * p.F, tag_of(c, l, T_MID),
-                 nullptr, nullptr, 0u, nullptr};
-      } else {                 // x2 = x1 + mid @ Wdown
-        phase_index = 3;
-        xsrc = XSrc{p.ll_mid + (size_t)par * p.F, nullptr, tag_of(c, l, T_MID), nullptr};
-        ep = Epi{EP_RESIDUAL, p.ll_xa + (size_t)par * H, tag_of(c, l, T_XA),
-                 p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), nullptr};
+        ep = Epi{EP_SILU, nullptr, 0u, nullptr, nullptr, 0u, nullptr};
+      } else {                 // x2 = x1 + mid @ Wdown, by columns
+        trace(c, l, step);
+        down_cols_phase(c, l);
+        continue;
       }
       trace(c, l, step);
       if (!last && step == 0)
         attention_prefetch(c, l, pos);
-      gemv_phase(c, p.phase[phase_index], xsrc, ep, bestv, besti, l);
+      gemv_phase(c, phase_index, xsrc, ep, l);
       if (!last && step == 0) {
         trace(c, l, 6);
         {
@@ -1140,31 +1304,18 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
     }
     trace(c, l, 4);
   }
-  {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-      const float ov = __shfl_xor_sync(0xffffffffu, bestv, o);
-      const int oi = __shfl_xor_sync(0xffffffffu, besti, o);
-      if (ov > bestv || (ov == bestv && oi < besti)) {
-        bestv = ov;
-        besti = oi;
+  if (c.ctid == 0) {
+    // the lm_head phase left one candidate per warp (and ended with a CTA barrier)
+    float bestv = sh.bestv[0];
+    int besti = sh.besti[0];
+    for (int w = 1; w < kCW; ++w)
+      if (sh.bestv[w] > bestv || (sh.bestv[w] == bestv && sh.besti[w] < besti)) {
+        bestv = sh.bestv[w];
+        besti = sh.besti[w];
       }
-    }
-    if (c.lane == 0) {
-      sh.bestv[c.warp] = bestv;
-      sh.besti[c.warp] = besti;
-    }
-    consumer_sync();
-    if (c.ctid == 0) {
-      for (int w = 1; w < kCW; ++w)
-        if (sh.bestv[w] > bestv || (sh.bestv[w] == bestv && sh.besti[w] < besti)) {
-          bestv = sh.bestv[w];
-          besti = sh.besti[w];
-        }
-      const uint32_t ctag = tag_of(c, p.L, T_CAND);
-      ll_store(p.ll_cand + 2 * blockIdx.x, bestv, ctag);
-      ll_store(p.ll_cand + 2 * blockIdx.x + 1, __int_as_float(besti), ctag);
-    }
+    const uint32_t ctag = tag_of(c, p.L, T_CAND);
+    ll_store(p.ll_cand + 2 * blockIdx.x, bestv, ctag);
+    ll_store(p.ll_cand + 2 * blockIdx.x + 1, __int_as_float(besti), ctag);
   }
   if (blockIdx.x == 0 && c.warp == 0) {
     // Sampler.h:101-104: first maximum over the per-CTA candidates
@@ -1250,6 +1401,29 @@ int mega_build_rows(const void *packed, int K, int n_rows, int row_stride, int r
   mega_build_rows_kernel<<<n_rows, 128, 0, st>>>((const uint8_t *)packed, K, row_stride, row_phase,
                                                  N_total, unit, scale, bias, grid_ctas, row_bytes,
                                                  cta_phase_off_dev, (uint8_t *)stream_buf);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// Column k of a projection (packed rows of K bytes, `koff` = byte offset of k inside
+// a packed row) -> H contiguous bytes u = q ^ 0x80 in the owning CTA's stream.
+__global__ void mega_build_cols_kernel(const uint8_t *src, int K, int H, const int32_t *koff,
+                                       int grid_ctas, const int64_t *cta_phase_off, uint8_t *stream) {
+  const int k = blockIdx.x;   // column = input channel
+  const int base = K / grid_ctas, rem = K % grid_ctas;
+  const int split = rem * (base + 1);
+  const int cta = k < split ? k / (base + 1) : rem + (k - split) / base;
+  const int begin = cta * base + min(cta, rem);
+  uint8_t *dst = stream + cta_phase_off[cta] + (int64_t)(k - begin) * H;
+  const int ko = koff[k];
+  for (int n = threadIdx.x; n < H; n += blockDim.x)
+    dst[n] = src[(int64_t)n * K + ko] ^ 0x80u;
+}
+
+int mega_build_cols(const void *packed, int K, int H, const int32_t *koff_dev, int grid_ctas,
+                    const int64_t *cta_phase_off_dev, void *stream_buf, cudaStream_t st) {
+  mega_build_cols_kernel<<<K, 256, 0, st>>>((const uint8_t *)packed, K, H, koff_dev, grid_ctas,
+                                            cta_phase_off_dev, (uint8_t *)stream_buf);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
