@@ -173,8 +173,6 @@ struct b200_model {
   int mega_grid = 0;
   size_t mega_smem = 0;
   int64_t mega_stream_bytes = 0;
-  int32_t *mega_koff = nullptr;
-  const float **mega_down_scale = nullptr;
   uint8_t *mega_stream = nullptr;
   int64_t *mega_offsets = nullptr;   // [(4L+1)+1][grid]: per-phase and per-CTA stream offsets
   const float **lvec_dev = nullptr;
@@ -402,13 +400,12 @@ int build_mega(b200_model *m) {
   const int H = c.hidden, QD = c.q_heads * D, KD = c.kv_heads * D, F = c.ffn, V = c.vocab;
   MegaParams &p = m->mp;
   const int Ks[5] = {H, QD, H, F, H}, Ns[5] = {QD + 2 * KD, H, 2 * F, H, V};
-  // the row loop of the kernel holds at most three 16-byte units per lane
-  if (H > 1536 || QD > 1536 || H % 16 != 0 || QD % 16 != 0)
+  if (H > 1536 || QD > 1536 || H % 16 != 0 || QD % 16 != 0 || F % 16 != 0)
     return B200_OK;
   int slot_bytes = 0;
   for (int i = 0; i < 5; ++i) {
     if (i == 3)
-      continue;   // the down projection is streamed by columns, see below
+      continue;
     MegaPhase &ph = p.phase[i];
     ph.K = Ks[i];
     ph.N = Ns[i];
@@ -420,22 +417,24 @@ int build_mega(b200_model *m) {
       slot_bytes = ph.rps * ph.row_bytes;
   }
   {
-    // down projection: F columns of H bytes, dealt to the CTAs like the gate|up pairs
+    // down projection: long rows, a few per stage, one warp per row
     MegaPhase &ph = p.phase[3];
-    ph.K = H;
-    ph.N = F;
-    ph.row_bytes = H;
-    ph.mode = 2;
+    ph.K = F;
+    ph.N = H;
+    ph.row_bytes = F + kMegaTrailer;
+    ph.mode = 0;
     ph.unit = 1;
-    ph.rps = (slot_bytes / H) & ~3;
-    if (ph.rps > 32) ph.rps = 32;
-    // one output channel per warp in the partial-sum fold; the MLP values of a CTA stay in shared memory
-    if (ph.rps < 4 || (H + grid - 1) / grid > 16 || (F + grid - 1) / grid > kMegaMaxMid || F < grid)
-      return B200_OK;
+    ph.rps = slot_bytes / ph.row_bytes;
+    if (ph.rps > 8) ph.rps = 8;
+    if (ph.rps < 1 || (ph.rps & (ph.rps - 1)) != 0) {   // 1, 2, 4 or 8 rows: the warps split evenly over stages
+      if (ph.rps >= 4) ph.rps = 4;
+      else if (ph.rps >= 2) ph.rps = 2;
+      else if (ph.rps < 1) return B200_OK;
+    }
   }
   slot_bytes = (slot_bytes + 127) / 128 * 128;
   int xs_floats = H > QD ? H : QD;                          // staged activations of a projection
-  if (xs_floats < 4 * H) xs_floats = 4 * H;                 // the four column groups of the down projection
+  if (xs_floats < F) xs_floats = F;
   if (xs_floats < (G + 2 + 7 * G) * D) xs_floats = (G + 2 + 7 * G) * D;   // staged q | k | v + states of the 7 scanning warps
   if (xs_floats < 3 * G * splits + 8) xs_floats = 3 * G * splits + 8;   // split fold: m, l, weights
   xs_floats = (xs_floats + 31) / 32 * 32;
@@ -472,19 +471,6 @@ int build_mega(b200_model *m) {
   if (int rc = dev_alloc((void **)&m->mega_offsets, table.size() * 8)) return rc;
   B200_CUDA(cudaMemcpy(m->mega_offsets, table.data(), table.size() * 8, cudaMemcpyHostToDevice));
   cudaStream_t st = m->stream;
-  {
-    // byte offset of input channel k inside a packed row of the down projection
-    std::vector<int32_t> koff(F);
-    for (int k = 0; k < F; ++k)
-      koff[k] = (int32_t)packed_offset(B200_W_I8, F, k, nullptr);
-    if (int rc = dev_alloc((void **)&m->mega_koff, (size_t)F * 4)) return rc;
-    B200_CUDA(cudaMemcpy(m->mega_koff, koff.data(), (size_t)F * 4, cudaMemcpyHostToDevice));
-    std::vector<const float *> ds(L);
-    for (int l = 0; l < L; ++l)
-      ds[l] = (const float *)m->layers[l].down.scale_buf;
-    if (int rc = dev_alloc((void **)&m->mega_down_scale, (size_t)L * sizeof(float *))) return rc;
-    B200_CUDA(cudaMemcpy(m->mega_down_scale, ds.data(), (size_t)L * sizeof(float *), cudaMemcpyHostToDevice));
-  }
   for (int l = 0; l < L; ++l) {
     Layer &Ly = m->layers[l];
     const int64_t *o0 = m->mega_offsets + (size_t)(4 * l) * grid;
@@ -501,7 +487,8 @@ int build_mega(b200_model *m) {
     if (int rc = mega_build_rows(Ly.up.w_buf, H, F, 2, 1, 2 * F, 2, (const float *)Ly.up.scale_buf, nullptr,
                                  grid, p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_cols(Ly.down.w_buf, F, H, m->mega_koff, grid, o0 + 3 * grid, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.down.w_buf, F, H, 1, 0, H, 1, (const float *)Ly.down.scale_buf, nullptr,
+                                 grid, p.phase[3].row_bytes, o0 + 3 * grid, m->mega_stream, st))
       return rc;
   }
   if (int rc = mega_build_rows(m->lm_head.w_buf, H, V, 1, 0, V, 1, (const float *)m->lm_head.scale_buf,
@@ -519,9 +506,9 @@ int build_mega(b200_model *m) {
   B200_CUDA(cudaMemcpy(m->lvec_dev, lvec.data(), lvec.size() * sizeof(float *), cudaMemcpyHostToDevice));
   // tagged activation buffers, all in one allocation (zero tags never match)
   const size_t n_qkv = 2 * (size_t)(QD + 2 * KD), n_attn = 2 * (size_t)QD, n_x = 2 * (size_t)H,
-               n_dpart = 2 * (size_t)grid * H, n_part = 2 * (size_t)c.q_heads * splits * (D + 2),
+               n_mid = 2 * (size_t)F, n_part = 2 * (size_t)c.q_heads * splits * (D + 2),
                n_cand = 2 * (size_t)grid;
-  const size_t n_ll = n_qkv + n_attn + 2 * n_x + n_dpart + n_part + n_cand + 16;
+  const size_t n_ll = n_qkv + n_attn + 2 * n_x + n_mid + n_part + n_cand + 16;
   if (int rc = dev_alloc((void **)&m->ll_buf, n_ll * sizeof(uint2))) return rc;
   B200_CUDA(cudaMemset(m->ll_buf, 0, n_ll * sizeof(uint2)));
   uint2 *q = m->ll_buf;
@@ -529,8 +516,7 @@ int build_mega(b200_model *m) {
   p.ll_qkv = take(n_qkv);
   p.ll_attn = take(n_attn);
   p.ll_xb = take(n_x);
-  p.ll_dpart = take(n_dpart);
-  p.down_scale = m->mega_down_scale;
+  p.ll_mid = take(n_mid);
   p.ll_xa = take(n_x);
   p.ll_part = take(n_part);
   p.ll_cand = take(n_cand);
@@ -733,7 +719,7 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->attn_scratch); cudaFree(m->argmax_scratch); cudaFree(m->kv_stage);
   cudaFree(m->d_state); cudaFree(m->d_history);
   cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
-  cudaFree(m->ll_buf); cudaFree(m->d_trace); cudaFree(m->mega_koff); cudaFree((void *)m->mega_down_scale);
+  cudaFree(m->ll_buf); cudaFree(m->d_trace);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
   if (m->ev0) cudaEventDestroy(m->ev0);

@@ -58,7 +58,7 @@ constexpr float kSeed = -1.0e30f;
 constexpr int D = 128;            // head_dim (checked on the host)
 
 // producer phases that tag their outputs
-enum { T_QKV = 1, T_ATTN = 2, T_XB = 3, T_DPART = 4, T_XA = 5, T_PART = 6, T_CAND = 7 };
+enum { T_QKV = 1, T_ATTN = 2, T_XB = 3, T_MID = 4, T_XA = 5, T_PART = 6, T_CAND = 7 };
 
 // ---- PTX wrappers ---------------------------------------------------------------
 __device__ __forceinline__ uint32_t smem_u32(const void *p) {
@@ -163,7 +163,6 @@ struct Shared {
   const uint8_t *stream_base;
   float cs[64], sn[64];                 // cos / sin of this step's position
   float red[kCW], red2[kCW];
-  float mids[kMegaMaxMid];              // silu(gate) * up of this CTA's gate|up pairs
   float bestv[kCW];
   int besti[kCW];
   int abort_flag;
@@ -447,8 +446,8 @@ __device__ __forceinline__ void visit_rows(Ctx &c, const Epi &ep, const uint8_t 
     ro[q] = min(R * wig + q, rows - 1) * row_bytes + lane * 16;
     a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
   }
-#pragma unroll
-  for (int i = 0; i < 3; ++i) {   // K <= 1536: at most three 16-byte units per lane
+#pragma unroll 3
+  for (int i = 0; i * 32 < units; ++i) {   // K / 512 blocks of 32 sixteen-byte units (the last may be short)
     const int u = i * 32 + lane;
     if (u < units) {
       const int qd = min(512, K - 512 * i) >> 2;   // k distance between the unit's four groups
@@ -524,7 +523,7 @@ __device__ __forceinline__ void visit_rows(Ctx &c, const Epi &ep, const uint8_t 
     // rows (2j, 2j+1) = (gate_j, up_j) sit in partner lanes
     const float upv = __shfl_xor_sync(0xffffffffu, val, R == 8 ? 4 : 8);
     if ((lane & kOwnerMask) == 0 && (rowc & 1) == 0 && row + 1 < rows)
-      c.sh.mids[(local_row + row) >> 1] = silu_mul(val, upv);   // consumed by this CTA's down columns
+      ll_store(ep.dst + ((first_row + row) >> 1), silu_mul(val, upv), ep.tag);
   } else if ((lane & kOwnerMask) == 0 && row < rows) {
     emit(c, ep, first_row + row, val, bestv, besti);
   }
@@ -551,9 +550,11 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, int phase_index, const XSrc &
   int slot = c.slot, g = c.g;
   uint32_t parity = c.parity;
   const int nstages = (nrows + rps - 1) / rps;
-  const int R = nstages >= 5 ? 8 : ((nstages >= 3 || ep.kind == EP_SILU) ? 4 : 1);
-  const int NG = R;                  // stage groups
-  const int gw = kCW / NG;           // warps per group (= per stage)
+  // rows per warp and visit: 8 when a ring slot is left for each of the 8 stage groups
+  const int R = rps < 16 ? 1
+                         : (nstages >= 5 && n_slots >= 8 ? 8 : ((nstages >= 3 || ep.kind == EP_SILU) ? 4 : 1));
+  const int gw = rps / R;            // warps per group (= per stage)
+  const int NG = kCW / gw;           // stage groups
   const int grp = warp / gw, wig = warp - grp * gw;
   const int nrounds = (nstages + NG - 1) / NG;
 
@@ -658,145 +659,6 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, int phase_index, const XSrc &
   }
   // the staged vector is reused by the next phase
   consumer_sync();
-}
-
-// ---- down projection, by columns -------------------------------------------------
-// x2 = x1 + mid @ Wdown (subgraph0_decode_simplify.mlir:232-244).  The CTA that
-// produced mid[k] (its gate|up pairs) also owns COLUMN k of Wdown: H bytes, one
-// per output channel.  So the MLP intermediate never leaves the CTA; what crosses
-// CTAs instead is each CTA's vector of H partial sums, and every CTA then adds up
-// the partials of its own few output channels (in CTA order: the result does not
-// depend on timing), applies the channel scale, adds the residual and publishes
-// its slice of x2.
-// Threads: 4 groups of 4 warps; group kg takes columns kg, kg+4, .. of a stage,
-// thread t of a group takes the 32-bit words t, t+128, .. of a column (4 output
-// channels each).  No shuffles: one accumulator per (thread, channel).
-constexpr int kColWords = 3;   // 32-bit words of a column per thread: H <= 1536
-__device__ __forceinline__ void down_cols_phase(Ctx &c, int layer) {
-  const MegaParams &p = c.p;
-  Shared &sh = c.sh;
-  const MegaPhase &ph = p.phase[3];
-  int col_begin, ncols;
-  rows_of(ph, blockIdx.x, gridDim.x, col_begin, ncols);
-  const int H = p.H, rps = ph.rps, nwords = H >> 2;
-  const int n_slots = p.slots, slot_bytes = p.slot_bytes;
-  const int lane = c.lane, warp = c.warp, ctid = c.ctid;
-  const int kg = warp >> 2, t128 = ctid & 127;
-  const int par = layer & 1;
-  uint8_t *const ring = c.ring;
-  volatile int *ab = &sh.abort_flag;
-  const int nstages = (ncols + rps - 1) / rps;
-  int slot = c.slot, g = c.g;
-  uint32_t parity = c.parity;
-
-  // this CTA's output channels: residual and channel scale are requested now,
-  // long before they are needed
-  const int grid = gridDim.x;
-  const int base_n = H / grid, rem_n = H % grid;
-  const int nb = blockIdx.x * base_n + min((int)blockIdx.x, rem_n);
-  const int ncnt = base_n + ((int)blockIdx.x < rem_n ? 1 : 0);
-  float my_res = 0.f, my_scale = 0.f;   // of channel nb + warp (lane 0; one channel per warp, checked on the host)
-  if (lane == 0 && warp < ncnt) {
-    my_scale = __ldg(p.down_scale[layer] + nb + warp);
-    my_res = ll_wait1(c, p.ll_xb + (size_t)par * H + nb + warp, tag_of(c, layer, T_XB));
-  }
-
-  float acc[kColWords][4];
-#pragma unroll
-  for (int w = 0; w < kColWords; ++w)
-    acc[w][0] = acc[w][1] = acc[w][2] = acc[w][3] = 0.f;
-  for (int st = 0; st < nstages; ++st) {
-    const int cols = min(rps, ncols - st * rps);
-    if (!stage_wait(sh, slot, parity, g + st, c.err, ab))
-      atomicCAS((int *)c.err, 0, 300 + slot);
-    const uint8_t *base = ring + (size_t)slot * slot_bytes;
-    for (int kk = kg; kk < cols; kk += 4) {
-      const float x = sh.mids[st * rps + kk] * kXScale;
-      const uint32_t *col = reinterpret_cast<const uint32_t *>(base + (size_t)kk * H);
-#pragma unroll
-      for (int w = 0; w < kColWords; ++w) {
-        const int wi = t128 + 128 * w;
-        if (wi < nwords) {
-          const uint32_t u = col[wi];
-          acc[w][0] = fmaf(x, __uint_as_float(u & 0x000000FFu), acc[w][0]);
-          acc[w][1] = fmaf(x, __uint_as_float(u & 0x0000FF00u), acc[w][1]);
-          acc[w][2] = fmaf(x, __uint_as_float(u & 0x00FF0000u), acc[w][2]);
-          acc[w][3] = fmaf(x, __uint_as_float(u >> 24), acc[w][3]);
-        }
-      }
-    }
-    __syncwarp();
-    if (lane == 0 && atomicAdd(&sh.done[slot], 1) == kCW - 1) {
-      sh.done[slot] = 0;
-      issue_stage(sh, ring, slot_bytes, slot, g + st + n_slots, n_slots);
-    }
-    if (++slot == n_slots) {
-      slot = 0;
-      parity ^= 1u;
-    }
-  }
-  c.slot = slot;
-  c.parity = parity;
-  c.g = g + nstages;
-  trace(c, layer, 24);
-
-  // ---- add up the four column groups (fixed order), publish the CTA's partial sums ----
-  float *gs = c.xs;   // [4][H]
-#pragma unroll
-  for (int w = 0; w < kColWords; ++w) {
-    const int wi = t128 + 128 * w;
-    if (wi < nwords)
-      *reinterpret_cast<float4 *>(gs + (size_t)kg * H + 4 * wi) =
-          make_float4(acc[w][0], acc[w][1] * 0.00390625f, acc[w][2] * 0.0000152587890625f, acc[w][3]);
-  }
-  if (warp == 0) {
-    float sx = 0.f;
-    for (int k = lane; k < ncols; k += 32)
-      sx += sh.mids[k];
-    sx = warp_sum(sx);
-    if (lane == 0)
-      sh.red[0] = sx;
-  }
-  consumer_sync();
-  const float off = -128.0f * sh.red[0];
-  uint2 *dpart = p.ll_dpart + ((size_t)par * grid + blockIdx.x) * H;
-  const uint32_t dtag = tag_of(c, layer, T_DPART);
-  for (int n = ctid; n < H; n += kCT) {
-    const float t = (gs[n] + gs[H + n]) + (gs[2 * H + n] + gs[3 * H + n]);
-    ll_store(dpart + n, fmaf(t, kAccScale, off), dtag);
-  }
-  trace(c, layer, 25);
-  // ---- this CTA's output channels: sum over all CTAs, scale, residual ------------------
-  if (warp < ncnt) {
-    const int n = nb + warp;
-    const uint2 *all = p.ll_dpart + (size_t)par * grid * H + n;
-    float sum = 0.f;
-    for (int c0 = 0; c0 < grid; c0 += 32 * 8) {
-      uint2 r[8];
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int cta = c0 + lane + 32 * q;
-        if (cta < grid)
-          r[q] = ll_load1(all + (size_t)cta * H);
-      }
-#pragma unroll
-      for (int q = 0; q < 8; ++q) {
-        const int cta = c0 + lane + 32 * q;
-        if (cta < grid) {
-          float v = __uint_as_float(r[q].x);
-          if (r[q].y != dtag)
-            v = ll_wait1(c, all + (size_t)cta * H, dtag);
-          sum += v;
-        }
-      }
-    }
-    sum = warp_sum(sum);
-    if (lane == 0)
-      ll_store(p.ll_xa + (size_t)par * H + n, __fadd_rn(my_res, __fmul_rn(sum, my_scale)),
-               tag_of(c, layer, T_XA));
-  }
-  trace(c, layer, 26);
-  consumer_sync();   // xs and mids are reused by the next phase
 }
 
 // ---- attention -------------------------------------------------------------------
@@ -1280,14 +1142,16 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
         xsrc = XSrc{p.ll_attn + (size_t)par * QD, nullptr, tag_of(c, l, T_ATTN), nullptr};
         ep = Epi{EP_RESIDUAL, p.ll_xb + (size_t)par * H, tag_of(c, l, T_XB),
                  xin_ll, embed_row, xin_tag, nullptr};
-      } else if (step == 2) {  // silu(gate) * up <- RMSNorm(x1), kept in shared memory
+      } else if (step == 2) {  // silu(gate) * up <- RMSNorm(x1)
         phase_index = 2;
         xsrc = XSrc{p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), p.lvec[4 * l + 1]};
-        ep = Epi{EP_SILU, nullptr, 0u, nullptr, nullptr, 0u, nullptr};
-      } else {                 // x2 = x1 + mid @ Wdown, by columns
-        trace(c, l, step);
-        down_cols_phase(c, l);
-        continue;
+        ep = Epi{EP_SILU, p.ll_mid + (size_t)par * p.F, tag_of(c, l, T_MID),
+                 nullptr, nullptr, 0u, nullptr};
+      } else {                 // x2 = x1 + mid @ Wdown
+        phase_index = 3;
+        xsrc = XSrc{p.ll_mid + (size_t)par * p.F, nullptr, tag_of(c, l, T_MID), nullptr};
+        ep = Epi{EP_RESIDUAL, p.ll_xa + (size_t)par * H, tag_of(c, l, T_XA),
+                 p.ll_xb + (size_t)par * H, nullptr, tag_of(c, l, T_XB), nullptr};
       }
       trace(c, l, step);
       if (!last && step == 0)
@@ -1401,29 +1265,6 @@ int mega_build_rows(const void *packed, int K, int n_rows, int row_stride, int r
   mega_build_rows_kernel<<<n_rows, 128, 0, st>>>((const uint8_t *)packed, K, row_stride, row_phase,
                                                  N_total, unit, scale, bias, grid_ctas, row_bytes,
                                                  cta_phase_off_dev, (uint8_t *)stream_buf);
-  B200_LAUNCH_CHECK();
-  return B200_OK;
-}
-
-// Column k of a projection (packed rows of K bytes, `koff` = byte offset of k inside
-// a packed row) -> H contiguous bytes u = q ^ 0x80 in the owning CTA's stream.
-__global__ void mega_build_cols_kernel(const uint8_t *src, int K, int H, const int32_t *koff,
-                                       int grid_ctas, const int64_t *cta_phase_off, uint8_t *stream) {
-  const int k = blockIdx.x;   // column = input channel
-  const int base = K / grid_ctas, rem = K % grid_ctas;
-  const int split = rem * (base + 1);
-  const int cta = k < split ? k / (base + 1) : rem + (k - split) / base;
-  const int begin = cta * base + min(cta, rem);
-  uint8_t *dst = stream + cta_phase_off[cta] + (int64_t)(k - begin) * H;
-  const int ko = koff[k];
-  for (int n = threadIdx.x; n < H; n += blockDim.x)
-    dst[n] = src[(int64_t)n * K + ko] ^ 0x80u;
-}
-
-int mega_build_cols(const void *packed, int K, int H, const int32_t *koff_dev, int grid_ctas,
-                    const int64_t *cta_phase_off_dev, void *stream_buf, cudaStream_t st) {
-  mega_build_cols_kernel<<<K, 256, 0, st>>>((const uint8_t *)packed, K, H, koff_dev, grid_ctas,
-                                            cta_phase_off_dev, (uint8_t *)stream_buf);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }

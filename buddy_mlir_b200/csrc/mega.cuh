@@ -9,23 +9,20 @@ constexpr int kMegaThreads = 512;      // 16 warps
 constexpr int kMegaMaxSlots = 16;
 constexpr int kMegaMaxLayerStages = 96;   // ring stages one CTA consumes per layer
 constexpr int kMegaTraceSlots = 64;   // trace points per (CTA, layer)
-constexpr int kMegaMaxMid = 128;       // SiLU-gated MLP values one CTA produces (and consumes) per layer
 constexpr int kMegaTrailer = 16;       // bytes appended to every streamed row: scale, bias
 
 struct MegaPhase {
   int K, N;
   int row_bytes;   // K + trailer
-  int rps;         // rows per ring slot (even)
-  int mode;        // 0: rows (a warp owns whole rows of a stage); 2: columns
+  int rps;         // rows per ring stage
+  int mode;        // unused (0)
   int unit;        // rows are dealt to CTAs in multiples of this (2 keeps gate/up pairs together)
 };
 
 struct MegaParams {
   const uint8_t *stream;       // every CTA's private weight stream, back to back
   const int64_t *cta_off;      // [grid] start of each CTA's stream
-  // qkv, o, gate|up (interleaved pairs), down (COLUMNS: K = N = ffn columns dealt to the CTAs,
-  // row_bytes = hidden bytes per column, no trailer), lm_head
-  MegaPhase phase[5];
+  MegaPhase phase[5];          // qkv, o, gate|up (interleaved pairs), down, lm_head
   int H, F, V, qh, kvh, L, max_len, splits;
   int slots, slot_bytes;
   int xs_floats;               // shared-memory staging area (activations, attention and column scratch)
@@ -37,8 +34,7 @@ struct MegaParams {
   uint2 *ll_qkv;               // [2][QD + 2*KD]
   uint2 *ll_attn;              // [2][QD]
   uint2 *ll_xb;                // [2][H]   residual stream after attention
-  uint2 *ll_dpart;             // [2][grid][H] per-CTA partial sums of the down projection
-  const float *const *down_scale;   // [L] per-channel scales of the down projection
+  uint2 *ll_mid;               // [2][F]   silu(gate) * up
   uint2 *ll_xa;                // [2][H]   residual stream after the MLP
   uint2 *ll_part;              // [2][qh][splits][D + 2] attention split partials
   uint2 *ll_cand;              // [grid][2] per-CTA argmax candidates (value, index)
@@ -56,8 +52,6 @@ int mega_build_rows(const void *packed, int K, int n_rows, int row_stride, int r
                     int N_total, int unit, const float *scale, const float *bias, int grid_ctas,
                     int row_bytes, const int64_t *cta_phase_off_dev, void *stream_buf,
                     cudaStream_t st);
-int mega_build_cols(const void *packed, int K, int H, const int32_t *koff_dev, int grid_ctas,
-                    const int64_t *cta_phase_off_dev, void *stream_buf, cudaStream_t st);
 size_t mega_fixed_shared_bytes();
 int mega_launch(const MegaParams &p, int grid, size_t smem, cudaStream_t st);
 
