@@ -446,25 +446,59 @@ __device__ __forceinline__ void visit_rows(Ctx &c, const Epi &ep, const uint8_t 
     ro[q] = min(R * wig + q, rows - 1) * row_bytes + lane * 16;
     a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
   }
-#pragma unroll 3
-  for (int i = 0; i * 32 < units; ++i) {   // K / 512 blocks of 32 sixteen-byte units (the last may be short)
-    const int u = i * 32 + lane;
-    if (u < units) {
-      const int qd = min(512, K - 512 * i) >> 2;   // k distance between the unit's four groups
-      const float *xp = xsm + 512 * i + 4 * lane;
-      float x[16];
+  if (R == 1) {
+    // a single row per warp: four 512-byte blocks in flight, each with its own
+    // accumulators, so that the loads and the FMA chains of the blocks overlap
+    float b[3][4];
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        const float4 t = *reinterpret_cast<const float4 *>(xp + j * qd);
-        x[4 * j + 0] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+    for (int s = 0; s < 3; ++s)
+      b[s][0] = b[s][1] = b[s][2] = b[s][3] = 0.f;
+#pragma unroll 1
+    for (int i0 = 0; i0 * 32 < units; i0 += 4) {
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int i = i0 + s;
+        if (i * 32 + lane < units) {
+          const int qd = min(512, K - 512 * i) >> 2;
+          const float *xp = xsm + 512 * i + 4 * lane;
+          float x[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 t = *reinterpret_cast<const float4 *>(xp + j * qd);
+            x[4 * j + 0] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+          }
+          const uint4 w = *reinterpret_cast<const uint4 *>(base + ro[0] + i * 512);
+          if (s == 0)
+            dot_unit(w, x, a[0]);
+          else
+            dot_unit(w, x, b[s - 1]);
+        }
       }
-      uint4 w[R];
+    }
 #pragma unroll
-      for (int q = 0; q < R; ++q)
-        w[q] = *reinterpret_cast<const uint4 *>(base + ro[q] + i * 512);
+    for (int e = 0; e < 4; ++e)
+      a[0][e] = (a[0][e] + b[0][e]) + (b[1][e] + b[2][e]);
+  } else {
+#pragma unroll 3
+    for (int i = 0; i * 32 < units; ++i) {   // K / 512 blocks of 32 sixteen-byte units (the last may be short)
+      const int u = i * 32 + lane;
+      if (u < units) {
+        const int qd = min(512, K - 512 * i) >> 2;   // k distance between the unit's four groups
+        const float *xp = xsm + 512 * i + 4 * lane;
+        float x[16];
 #pragma unroll
-      for (int q = 0; q < R; ++q)
-        dot_unit(w[q], x, a[q]);
+        for (int j = 0; j < 4; ++j) {
+          const float4 t = *reinterpret_cast<const float4 *>(xp + j * qd);
+          x[4 * j + 0] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+        }
+        uint4 w[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+          w[q] = *reinterpret_cast<const uint4 *>(base + ro[q] + i * 512);
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+          dot_unit(w[q], x, a[q]);
+      }
     }
   }
   float v[R];
