@@ -56,42 +56,56 @@ gqa_decode_kernel(const float *__restrict__ q, const float *__restrict__ kc,
 
   const float *kbase = kc + (int64_t)hk * max_len * D + lane * VEC;
   const float *vbase = vc + (int64_t)hk * max_len * D + lane * VEC;
-  for (int j = s0 + warp; j < s1; j += kAttnWarps) {
-    float kr[VEC], vr[VEC];
-    if (VEC == 4) {
-      const float4 k4 = *reinterpret_cast<const float4 *>(kbase + (int64_t)j * D);
-      const float4 v4 = *reinterpret_cast<const float4 *>(vbase + (int64_t)j * D);
-      kr[0] = k4.x; kr[1] = k4.y; kr[2] = k4.z; kr[3] = k4.w;
-      vr[0] = v4.x; vr[1] = v4.y; vr[2] = v4.z; vr[3] = v4.w;
-    } else {
+  // NB rows in flight per warp: all loads of a round are issued before the first use
+  constexpr int NB = G <= 4 ? 4 : 2;
+  for (int j0 = s0 + warp; j0 < s1; j0 += NB * kAttnWarps) {
+    float kr[NB][VEC], vr[NB][VEC];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e) {
-        kr[e] = kbase[(int64_t)j * D + e];
-        vr[e] = vbase[(int64_t)j * D + e];
+    for (int i = 0; i < NB; ++i) {
+      const int j = min(j0 + i * kAttnWarps, s1 - 1);
+      if (VEC == 4) {
+        const float4 k4 = *reinterpret_cast<const float4 *>(kbase + (int64_t)j * D);
+        const float4 v4 = *reinterpret_cast<const float4 *>(vbase + (int64_t)j * D);
+        kr[i][0] = k4.x; kr[i][1] = k4.y; kr[i][2] = k4.z; kr[i][3] = k4.w;
+        vr[i][0] = v4.x; vr[i][1] = v4.y; vr[i][2] = v4.z; vr[i][3] = v4.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < VEC; ++e) {
+          kr[i][e] = kbase[(int64_t)j * D + e];
+          vr[i][e] = vbase[(int64_t)j * D + e];
+        }
       }
     }
-    float s[G];
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      float d = 0.f;
+    for (int i = 0; i < NB; ++i) {
+      if (j0 + i * kAttnWarps >= s1)   // warp-uniform
+        break;
+      float s[G];
 #pragma unroll
-      for (int e = 0; e < VEC; ++e)
-        d = fmaf(qr[g][e], kr[e], d);
-      s[g] = d;
-    }
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
 #pragma unroll
-    for (int g = 0; g < G; ++g)
-      s[g] = warp_sum(s[g]) * scale;
+        for (int e = 0; e < VEC; ++e)
+          d = fmaf(qr[g][e], kr[i][e], d);
+        s[g] = d;
+      }
 #pragma unroll
-    for (int g = 0; g < G; ++g) {
-      const float nm = fmaxf(m[g], s[g]);
-      const float alpha = expf(m[g] - nm);
-      const float p = expf(s[g] - nm);
-      l[g] = fmaf(l[g], alpha, p);
+      for (int o = 16; o > 0; o >>= 1)
 #pragma unroll
-      for (int e = 0; e < VEC; ++e)
-        acc[g][e] = fmaf(acc[g][e], alpha, p * vr[e]);
-      m[g] = nm;
+        for (int g = 0; g < G; ++g)
+          s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        s[g] *= scale;
+        const float nm = fmaxf(m[g], s[g]);
+        const float alpha = expf(m[g] - nm);
+        const float p = expf(s[g] - nm);
+        l[g] = fmaf(l[g], alpha, p);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          acc[g][e] = fmaf(acc[g][e], alpha, p * vr[i][e]);
+        m[g] = nm;
+      }
     }
   }
 

@@ -31,6 +31,7 @@ struct GemvP {
   int group, ngroups;
   int accumulate, silu_pairs;
   int kc;  // activation slab (elements) staged in shared memory at a time
+  int fast_scales;  // int4 groups: the 8 f16 scales of a 1024-element block are one aligned 16-byte load
   float eps;
 };
 
@@ -111,7 +112,11 @@ gemv_kernel(const GemvP p) {
 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int nwarps = blockDim.x >> 5;
-  const int64_t row0 = ((int64_t)blockIdx.x * nwarps + warp) * R;
+  // A CTA takes row groups base, base + gridDim.x * nwarps * R, ..: with a grid
+  // capped at a few CTAs per SM the activation vector is staged (and its
+  // RMSNorm statistics computed) once per CTA, not once per handful of rows.
+  const int64_t gstride = (int64_t)gridDim.x * nwarps * R;
+  const bool one_slab = p.kc >= p.Kp;
 
   // ---- optional fused RMSNorm statistics --------------------------------
   if (p.norm_w != nullptr) {
@@ -135,164 +140,186 @@ gemv_kernel(const GemvP p) {
     }
   }
 
-  float acc[R][MT];
+  bool staged = false;
+  for (int64_t base = (int64_t)blockIdx.x * nwarps * R; base < p.N; base += gstride) {
+    const int64_t row0 = base + (int64_t)warp * R;
+    float acc[R][MT];
 #pragma unroll
-  for (int r = 0; r < R; ++r)
+    for (int r = 0; r < R; ++r)
 #pragma unroll
-    for (int m = 0; m < MT; ++m)
-      acc[r][m] = 0.f;
+      for (int m = 0; m < MT; ++m)
+        acc[r][m] = 0.f;
 
-  const uint8_t *rowp[R];
+    const uint8_t *rowp[R];
+    int64_t srow[R];
 #pragma unroll
-  for (int r = 0; r < R; ++r) {
-    int64_t row = row0 + r;
-    if (row >= p.N)
-      row = p.N - 1;  // clamp: loads stay in bounds, result is discarded
-    rowp[r] = p.w + row * p.row_bytes;
-  }
-
-  for (int k0 = 0; k0 < p.Kp; k0 += p.kc) {
-    const int kc = min(p.kc, p.Kp - k0);
-    if (k0 > 0)
-      __syncthreads();
-    // ---- stage the activation slab (zero beyond K and beyond M) ----------
-    for (int i = threadIdx.x; i < MT * kc; i += blockDim.x) {
-      const int m = i / kc, k = k0 + (i - m * kc);
-      float v = 0.f;
-      if (m < p.M && k < p.K) {
-        v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
-        if (p.norm_w != nullptr)
-          v = p.norm_w[k] * (v * s_rinv[m]);
-      }
-      xs[m * p.kc + (k - k0)] = v;
+    for (int r = 0; r < R; ++r) {
+      int64_t row = row0 + r;
+      if (row >= p.N)
+        row = p.N - 1;  // clamp: loads stay in bounds, result is discarded
+      rowp[r] = p.w + row * p.row_bytes;
+      srow[r] = row * p.ngroups;
     }
-    __syncthreads();
 
-    const int nblk = (kc + BLK - 1) / BLK;
+    for (int k0 = 0; k0 < p.Kp; k0 += p.kc) {
+      const int kc = min(p.kc, p.Kp - k0);
+      if (!(one_slab && staged)) {
+        if (staged)
+          __syncthreads();
+        // ---- stage the activation slab (zero beyond K and beyond M) ----------
+        for (int i = threadIdx.x; i < MT * kc; i += blockDim.x) {
+          const int m = i / kc, k = k0 + (i - m * kc);
+          float v = 0.f;
+          if (m < p.M && k < p.K) {
+            v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
+            if (p.norm_w != nullptr)
+              v = p.norm_w[k] * (v * s_rinv[m]);
+          }
+          xs[m * p.kc + (k - k0)] = v;
+        }
+        __syncthreads();
+        staged = true;
+      }
+
+      const int nblk = (kc + BLK - 1) / BLK;
 #pragma unroll 2
-    for (int b = 0; b < nblk; ++b) {
-      const int kb = b * BLK;              // slab-relative element offset
-      const int Bs = min(BLK, kc - kb);    // elements in this block
-      if (lane * E < Bs) {
-        const int q = Bs / DQ::G;
-        const int64_t boff = (int64_t)((k0 + kb) / E) * 16 + lane * 16;
-        uint4 wv[R];
-#pragma unroll
-        for (int r = 0; r < R; ++r)
-          wv[r] = ld_stream(rowp[r] + boff);
-#pragma unroll
-        for (int j = 0; j < DQ::G; ++j) {
-          const int kx = kb + j * q + 4 * lane;
-          float wf[R][4];
+      for (int b = 0; b < nblk; ++b) {
+        const int kb = b * BLK;              // slab-relative element offset
+        const int Bs = min(BLK, kc - kb);    // elements in this block
+        if (lane * E < Bs) {
+          const int q = Bs / DQ::G;
+          const int64_t boff = (int64_t)((k0 + kb) / E) * 16 + lane * 16;
+          uint4 wv[R];
 #pragma unroll
           for (int r = 0; r < R; ++r)
-            DQ::group(wv[r], j, wf[r]);
-          float sc[R];
-          if (GROUPED) {
-            const int g = (k0 + kx) / p.group;
+            wv[r] = ld_stream(rowp[r] + boff);
+          // int4 group scales of this block: eight consecutive f16 values per row
+          uint4 sv[R];
+          const bool vec_scales = GROUPED && p.fast_scales && Bs == BLK;
+          if (vec_scales) {
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              int64_t row = row0 + r;
-              if (row >= p.N)
-                row = p.N - 1;
-              sc[r] = load_as_float(p.scale, p.scale_dtype,
-                                    row * p.ngroups + g);
-            }
+            for (int r = 0; r < R; ++r)
+              sv[r] = __ldg(reinterpret_cast<const uint4 *>(
+                  reinterpret_cast<const __half *>(p.scale) + srow[r] + (k0 + kb) / p.group));
           }
 #pragma unroll
-          for (int m = 0; m < MT; ++m) {
-            const float4 xv =
-                *reinterpret_cast<const float4 *>(&xs[m * p.kc + kx]);
+          for (int j = 0; j < DQ::G; ++j) {
+            const int kx = kb + j * q + 4 * lane;
+            float wf[R][4];
 #pragma unroll
-            for (int r = 0; r < R; ++r) {
-              if (GROUPED) {
-                float t = xv.x * wf[r][0];
-                t = fmaf(xv.y, wf[r][1], t);
-                t = fmaf(xv.z, wf[r][2], t);
-                t = fmaf(xv.w, wf[r][3], t);
-                acc[r][m] = fmaf(t, sc[r], acc[r][m]);
+            for (int r = 0; r < R; ++r)
+              DQ::group(wv[r], j, wf[r]);
+            float sc[R];
+            if (GROUPED) {
+              if (vec_scales) {
+#pragma unroll
+                for (int r = 0; r < R; ++r) {
+                  const uint32_t w32 = (j >> 1) == 0 ? sv[r].x : (j >> 1) == 1 ? sv[r].y
+                                     : (j >> 1) == 2 ? sv[r].z : sv[r].w;
+                  sc[r] = __half2float(__ushort_as_half((unsigned short)((j & 1) ? (w32 >> 16) : (w32 & 0xFFFFu))));
+                }
               } else {
-                acc[r][m] = fmaf(xv.x, wf[r][0], acc[r][m]);
-                acc[r][m] = fmaf(xv.y, wf[r][1], acc[r][m]);
-                acc[r][m] = fmaf(xv.z, wf[r][2], acc[r][m]);
-                acc[r][m] = fmaf(xv.w, wf[r][3], acc[r][m]);
+                const int g = (k0 + kx) / p.group;
+#pragma unroll
+                for (int r = 0; r < R; ++r)
+                  sc[r] = load_as_float(p.scale, p.scale_dtype, srow[r] + g);
+              }
+            }
+#pragma unroll
+            for (int m = 0; m < MT; ++m) {
+              const float4 xv =
+                  *reinterpret_cast<const float4 *>(&xs[m * p.kc + kx]);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                if (GROUPED) {
+                  float t = xv.x * wf[r][0];
+                  t = fmaf(xv.y, wf[r][1], t);
+                  t = fmaf(xv.z, wf[r][2], t);
+                  t = fmaf(xv.w, wf[r][3], t);
+                  acc[r][m] = fmaf(t, sc[r], acc[r][m]);
+                } else {
+                  acc[r][m] = fmaf(xv.x, wf[r][0], acc[r][m]);
+                  acc[r][m] = fmaf(xv.y, wf[r][1], acc[r][m]);
+                  acc[r][m] = fmaf(xv.z, wf[r][2], acc[r][m]);
+                  acc[r][m] = fmaf(xv.w, wf[r][3], acc[r][m]);
+                }
               }
             }
           }
         }
       }
     }
-  }
 
-  // ---- reduce across lanes, epilogue --------------------------------------
+    // ---- reduce across lanes, epilogue --------------------------------------
 #pragma unroll
-  for (int r = 0; r < R; ++r)
-#pragma unroll
-    for (int m = 0; m < MT; ++m)
-      acc[r][m] = warp_sum(acc[r][m]);
-
-  if (lane == 0) {
-#pragma unroll
-    for (int r = 0; r < R; ++r) {
-      const int64_t row = row0 + r;
-      if (row >= p.N)
-        continue;
-      float s = 1.f;
-      if (!GROUPED && p.scale != nullptr)
-        s = load_as_float(p.scale, p.scale_dtype, row);
+    for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int m = 0; m < MT; ++m)
-        if (m < p.M) {
-          float v = acc[r][m];
-          if (!GROUPED && p.scale != nullptr)
-            v = v * s;
-          if (p.bias != nullptr)
-            v = p.bias[row] + v;
-          acc[r][m] = v;
-        }
-    }
-    if (p.silu_pairs) {
-      // rows (2j, 2j+1) = (gate_j, up_j); R is even and row0 is even.
-#pragma unroll
-      for (int r = 0; r + 1 < R; r += 2) {
-        const int64_t row = row0 + r;
-        if (row + 1 >= p.N)
-          continue;
-        const int64_t col = row >> 1;
-#pragma unroll
-        for (int m = 0; m < MT; ++m)
-          if (m < p.M) {
-            const float v = silu_mul(acc[r][m], acc[r + 1][m]);
-            const int64_t o = (int64_t)m * p.y_ld + col;
-            if (p.y_dtype == B200_F32)
-              ((float *)p.y)[o] = v;
-            else
-              ((__half *)p.y)[o] = __float2half_rn(v);
-          }
-      }
-    } else {
+        acc[r][m] = warp_sum(acc[r][m]);
+
+    if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const int64_t row = row0 + r;
         if (row >= p.N)
           continue;
+        float s = 1.f;
+        if (!GROUPED && p.scale != nullptr)
+          s = load_as_float(p.scale, p.scale_dtype, row);
 #pragma unroll
         for (int m = 0; m < MT; ++m)
           if (m < p.M) {
-            const int64_t o = (int64_t)m * p.y_ld + row;
             float v = acc[r][m];
-            if (p.residual != nullptr)
-              v = p.residual[o] + v;
-            if (p.y_dtype == B200_F32) {
-              if (p.accumulate)
-                v = ((float *)p.y)[o] + v;
-              ((float *)p.y)[o] = v;
-            } else {
-              if (p.accumulate)
-                v = __half2float(((__half *)p.y)[o]) + v;
-              ((__half *)p.y)[o] = __float2half_rn(v);
-            }
+            if (!GROUPED && p.scale != nullptr)
+              v = v * s;
+            if (p.bias != nullptr)
+              v = p.bias[row] + v;
+            acc[r][m] = v;
           }
+      }
+      if (p.silu_pairs) {
+        // rows (2j, 2j+1) = (gate_j, up_j); R is even and row0 is even.
+#pragma unroll
+        for (int r = 0; r + 1 < R; r += 2) {
+          const int64_t row = row0 + r;
+          if (row + 1 >= p.N)
+            continue;
+          const int64_t col = row >> 1;
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < p.M) {
+              const float v = silu_mul(acc[r][m], acc[r + 1][m]);
+              const int64_t o = (int64_t)m * p.y_ld + col;
+              if (p.y_dtype == B200_F32)
+                ((float *)p.y)[o] = v;
+              else
+                ((__half *)p.y)[o] = __float2half_rn(v);
+            }
+        }
+      } else {
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int64_t row = row0 + r;
+          if (row >= p.N)
+            continue;
+#pragma unroll
+          for (int m = 0; m < MT; ++m)
+            if (m < p.M) {
+              const int64_t o = (int64_t)m * p.y_ld + row;
+              float v = acc[r][m];
+              if (p.residual != nullptr)
+                v = p.residual[o] + v;
+              if (p.y_dtype == B200_F32) {
+                if (p.accumulate)
+                  v = ((float *)p.y)[o] + v;
+                ((float *)p.y)[o] = v;
+              } else {
+                if (p.accumulate)
+                  v = __half2float(((__half *)p.y)[o]) + v;
+                ((__half *)p.y)[o] = __float2half_rn(v);
+              }
+            }
+        }
       }
     }
   }
@@ -311,7 +338,18 @@ static int launch(const GemvP &p, int warps, cudaStream_t st) {
     }
   }
   const int64_t rows_per_cta = (int64_t)warps * R;
-  const int64_t grid = (p.N + rows_per_cta - 1) / rows_per_cta;
+  int64_t grid = (p.N + rows_per_cta - 1) / rows_per_cta;
+  // one resident wave: as many CTAs as fit on the device at once, each looping
+  // over its row groups
+  int occ = 0, dev = 0, sms = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  B200_CUDA(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+  B200_CUDA(cudaOccupancyMaxActiveBlocksPerMultiprocessor(&occ, kern, warps * 32, smem));
+  if (occ < 1)
+    occ = 1;
+  const int64_t cap = (int64_t)sms * occ;
+  if (grid > cap)
+    grid = cap;
   kern<<<(unsigned)grid, warps * 32, smem, st>>>(p);
   B200_LAUNCH_CHECK();
   return B200_OK;
@@ -395,21 +433,19 @@ extern "C" int b200_gemv(const b200_weight *w, const b200_gemv_args *a,
     kc = (budget / 1024) * 1024;
   p.kc = kc;
 
-  // Rows per warp and warps per CTA: aim for >= 4 CTAs per SM.
+  p.fast_scales = grouped && w->scale_dtype == B200_F16 && p.group * 8 == 1024 && p.ngroups % 8 == 0 &&
+                  (reinterpret_cast<uintptr_t>(w->scale) & 15) == 0;
+
+  // Rows per warp: the most that still gives every SM two CTAs of 8 warps.
   int R = 2, warps = 8;
   if (mt == 1) {
-    const int64_t want = 4 * 148;
+    const int64_t want = 2 * 148;
     if (w->N / (8 * 4) >= want)
       R = 4;
-    else if (w->N / (8 * 2) >= want)
+    else if (w->N / (8 * 2) >= want || a->silu_pairs)
       R = 2;
-    else if (w->N / (4 * 2) >= want) {
-      R = 2;
-      warps = 4;
-    } else {
-      R = a->silu_pairs ? 2 : 1;
-      warps = 4;
-    }
+    else
+      R = 1;
   } else if (w->N / (8 * 2) < 2 * 148) {
     warps = 4;
   }
