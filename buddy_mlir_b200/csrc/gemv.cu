@@ -122,9 +122,21 @@ gemv_kernel(const GemvP p) {
   if (p.norm_w != nullptr) {
     for (int m = 0; m < p.M; ++m) {
       float s = 0.f;
-      for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
-        const float v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
-        s = fmaf(v, v, s);
+      if (p.x_dtype == B200_F32 && (p.K & 3) == 0 && (p.x_ld & 3) == 0 &&
+          (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+        const float *xg = reinterpret_cast<const float *>(p.x) + (int64_t)m * p.x_ld;
+        for (int k = threadIdx.x * 4; k < p.K; k += blockDim.x * 4) {
+          const float4 v = __ldg(reinterpret_cast<const float4 *>(xg + k));
+          s = fmaf(v.x, v.x, s);
+          s = fmaf(v.y, v.y, s);
+          s = fmaf(v.z, v.z, s);
+          s = fmaf(v.w, v.w, s);
+        }
+      } else {
+        for (int k = threadIdx.x; k < p.K; k += blockDim.x) {
+          const float v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
+          s = fmaf(v, v, s);
+        }
       }
       s = warp_sum(s);
       if (lane == 0)
@@ -167,15 +179,37 @@ gemv_kernel(const GemvP p) {
         if (staged)
           __syncthreads();
         // ---- stage the activation slab (zero beyond K and beyond M) ----------
-        for (int i = threadIdx.x; i < MT * kc; i += blockDim.x) {
-          const int m = i / kc, k = k0 + (i - m * kc);
-          float v = 0.f;
-          if (m < p.M && k < p.K) {
-            v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
-            if (p.norm_w != nullptr)
-              v = p.norm_w[k] * (v * s_rinv[m]);
+        if (MT == 1 && p.x_dtype == B200_F32 && (p.K & 3) == 0 &&
+            (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
+          // one f32 row: 16-byte loads, no index arithmetic per element
+          const float *xg = reinterpret_cast<const float *>(p.x);
+          const float rinv = p.norm_w != nullptr ? s_rinv[0] : 1.f;
+          for (int i = threadIdx.x * 4; i < kc; i += blockDim.x * 4) {
+            const int k = k0 + i;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            if (k < p.K) {
+              v = __ldg(reinterpret_cast<const float4 *>(xg + k));
+              if (p.norm_w != nullptr) {
+                const float4 w4 = __ldg(reinterpret_cast<const float4 *>(p.norm_w + k));
+                v.x = w4.x * (v.x * rinv);
+                v.y = w4.y * (v.y * rinv);
+                v.z = w4.z * (v.z * rinv);
+                v.w = w4.w * (v.w * rinv);
+              }
+            }
+            *reinterpret_cast<float4 *>(&xs[i]) = v;
           }
-          xs[m * p.kc + (k - k0)] = v;
+        } else {
+          for (int i = threadIdx.x; i < MT * kc; i += blockDim.x) {
+            const int m = i / kc, k = k0 + (i - m * kc);
+            float v = 0.f;
+            if (m < p.M && k < p.K) {
+              v = load_as_float(p.x, p.x_dtype, (int64_t)m * p.x_ld + k);
+              if (p.norm_w != nullptr)
+                v = p.norm_w[k] * (v * s_rinv[m]);
+            }
+            xs[m * p.kc + (k - k0)] = v;
+          }
         }
         __syncthreads();
         staged = true;
