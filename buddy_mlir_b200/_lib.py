@@ -103,6 +103,7 @@ def load():
         "b200_model_step_bytes": (i64, [vp, i32]),
         "b200_model_kernels_per_step": (i32, [vp]),
         "b200_model_uses_persistent_kernel": (i32, [vp]),
+        "b200_model_tp_sum_kind": (i32, [vp]),
         "b200_model_read_trace": (i32, [vp, vp, i64]),
         "b200_model_kv_ptr": (vp, [vp, i32]),
         "b200_model_kv_overflow": (i32, [vp, i32, i32, f32, C.POINTER(C.c_int)]),

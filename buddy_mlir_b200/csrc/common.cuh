@@ -53,6 +53,34 @@ __device__ __forceinline__ float warp_max(float v) {
   return v;
 }
 
+// ---- tensor-parallel sum without a collective library -----------------------
+// A row-parallel projection (o, down) leaves a partial sum on every rank.  Its
+// GEMV stores each partial result straight into the staging buffers of ALL ranks
+// (plain 8-byte peer stores over NVLink) as (value, tag) pairs; the tag numbers
+// the reduction (decode step x reductions per step + index), so a receiver just
+// polls for the tag: the data's arrival is the synchronisation.  Four regions
+// are used in turn; a rank cannot run more than one reduction ahead of the
+// slowest one, so a region is never overwritten before it has been read.
+constexpr int kTpMaxRanks = 8;
+constexpr int kTpRegions = 4;
+struct TpPush {
+  uint2 *peer[kTpMaxRanks];   // staging buffer of every rank: [kTpRegions][ranks][H] pairs
+  int ranks, rank, H;
+  const int32_t *step;        // device counter of decode steps (the same on every rank)
+  int index, per_step;        // which reduction of the step this is, and how many there are
+};
+int gemv_run(const b200_weight *w, const b200_gemv_args *a, const TpPush *push, cudaStream_t stream);
+__device__ __forceinline__ void tagged_store(uint2 *p, float v, uint32_t tag) {
+  asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(__float_as_uint(v)),
+               "r"(tag)
+               : "memory");
+}
+__device__ __forceinline__ uint2 tagged_load(const uint2 *p) {
+  uint2 v;
+  asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
+
 // ---- packed-row index map -------------------------------------------------
 // A packed row is a sequence of blocks of up to 32 sixteen-byte units.  Unit
 // (lane) l of a block holds G groups of 4 consecutive k; group j of lane l

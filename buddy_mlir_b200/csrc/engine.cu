@@ -88,11 +88,49 @@ __global__ void add_inplace_kernel(float *x, const float *part, int n) {
   if (i < n)
     x[i] = __fadd_rn(x[i], part[i]);
 }
+// x[n] += sum over ranks (in rank order, the same on every rank) of the partial
+// results that the ranks' GEMVs pushed into this rank's staging buffer.  Every
+// wait is bounded (poll count and 10 s of wall time: the ranks are separate
+// processes that enter a step at slightly different times); on expiry the
+// kernel records code 500 in *err, and later waits of the step fall through.
+__global__ void tp_reduce_add_kernel(float *x, const uint2 *buf, int H, int ranks,
+                                     const int32_t *step, int index, int per_step, int *err) {
+  const int n = blockIdx.x * blockDim.x + threadIdx.x;
+  if (n >= H)
+    return;
+  const uint32_t seq = (uint32_t)(*step) * per_step + index, tag = seq + 1u;
+  const uint2 *src = buf + (size_t)(seq % kTpRegions) * ranks * H + n;
+  float sum = x[n];
+  for (int r = 0; r < ranks; ++r) {
+    const uint2 *p = src + (size_t)r * H;
+    uint2 v = tagged_load(p);
+    if (v.y != tag) {
+      unsigned long long t0 = 0;
+      for (uint32_t it = 1; v.y != tag; ++it) {
+        if ((it & 0xFF) == 0) {
+          unsigned long long t;
+          asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+          if (t0 == 0)
+            t0 = t;
+          if (*(volatile int *)err != 0 || t - t0 > 10000000000ull || it > (1u << 30)) {
+            atomicCAS(err, 0, 500);
+            break;
+          }
+        }
+        __nanosleep(100);
+        v = tagged_load(p);
+      }
+    }
+    sum = __fadd_rn(sum, __uint_as_float(v.x));
+  }
+  x[n] = sum;
+}
 // end of a step: feed the argmax back and advance the position
 __global__ void advance_kernel(int32_t *token, int32_t *pos,
                                const int32_t *next, int32_t *history,
-                               int32_t *count, int cap) {
+                               int32_t *count, int cap, int32_t *steps_done) {
   if (threadIdx.x == 0 && blockIdx.x == 0) {
+    *steps_done = *steps_done + 1;   // numbers the tensor-parallel reductions
     const int c = *count;
     if (c < cap)
       history[c] = *next;
@@ -178,6 +216,10 @@ struct b200_model {
   const float **lvec_dev = nullptr;
   uint2 *ll_buf = nullptr;           // tagged activation buffers
   long long *d_trace = nullptr;
+  // tensor-parallel sums by peer stores (see TpPush): this rank's staging buffer and everybody's
+  uint2 *tp_ll = nullptr;
+  void *tp_opened[kTpMaxRanks] = {};
+  TpPush tp_push{};   // ranks == 0: the NCCL all-reduce is used instead
 };
 
 namespace {
@@ -287,6 +329,32 @@ int gemv(b200_model *m, const DevLinear &L, const float *x, float *y,
   return b200_gemv(&L.w, &a, m->stream);
 }
 
+// Row-parallel projection of a tensor-parallel model: x += sum over ranks of (input @ W_rank).
+int gemv_tp_sum(b200_model *m, const DevLinear &L, const float *input, int index) {
+  const int H = m->cfg.hidden;
+  cudaStream_t st = m->stream;
+  if (m->tp_push.ranks > 0) {
+    b200_gemv_args a{};
+    a.x = input;
+    a.x_dtype = B200_F32;
+    a.y_dtype = B200_F32;
+    a.y = m->part;   // not written: the results go to the ranks' staging buffers
+    a.M = 1;
+    TpPush push = m->tp_push;
+    push.index = index;
+    if (int rc = gemv_run(&L.w, &a, &push, st)) return rc;
+    tp_reduce_add_kernel<<<(H + 127) / 128, 128, 0, st>>>(m->x, m->tp_ll, H, push.ranks, push.step, index,
+                                                        push.per_step, m->d_state + 6);
+    B200_LAUNCH_CHECK();
+    return B200_OK;
+  }
+  if (int rc = gemv(m, L, input, m->part, nullptr, nullptr, false)) return rc;
+  B200_NCCL(g_nccl.AllReduce(m->part, m->part, H, kNcclFloat, kNcclSum, g_nccl.comm, st));
+  add_inplace_kernel<<<(H + 255) / 256, 256, 0, st>>>(m->x, m->part, H);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 // Issue every kernel of one decode step on m->stream.
 int issue_step(b200_model *m, int *n_kernels) {
   const b200_model_config &c = m->cfg;
@@ -314,21 +382,13 @@ int issue_step(b200_model *m, int *n_kernels) {
     if (m->tp == 1) {
       if (int rc = gemv(m, L.o, m->attn, m->x, m->x, nullptr, false)) return rc;
     } else {
-      if (int rc = gemv(m, L.o, m->attn, m->part, nullptr, nullptr, false)) return rc;
-      B200_NCCL(g_nccl.AllReduce(m->part, m->part, H, kNcclFloat, kNcclSum,
-                                 g_nccl.comm, st));
-      add_inplace_kernel<<<(H + 255) / 256, 256, 0, st>>>(m->x, m->part, H);
-      B200_LAUNCH_CHECK();
+      if (int rc = gemv_tp_sum(m, L.o, m->attn, 2 * l)) return rc;
     }
     if (int rc = gemv(m, L.gateup, m->x, m->mid, nullptr, L.post_norm, true)) return rc;
     if (m->tp == 1) {
       if (int rc = gemv(m, L.down, m->mid, m->x, m->x, nullptr, false)) return rc;
     } else {
-      if (int rc = gemv(m, L.down, m->mid, m->part, nullptr, nullptr, false)) return rc;
-      B200_NCCL(g_nccl.AllReduce(m->part, m->part, H, kNcclFloat, kNcclSum,
-                                 g_nccl.comm, st));
-      add_inplace_kernel<<<(H + 255) / 256, 256, 0, st>>>(m->x, m->part, H);
-      B200_LAUNCH_CHECK();
+      if (int rc = gemv_tp_sum(m, L.down, m->mid, 2 * l + 1)) return rc;
     }
   }
   if (m->tp == 1) {
@@ -344,7 +404,7 @@ int issue_step(b200_model *m, int *n_kernels) {
   if (int rc = b200_argmax_first(m->logits, c.vocab, d_next, m->argmax_scratch, st))
     return rc;
   advance_kernel<<<1, 32, 0, st>>>(d_token, d_pos, d_next, m->d_history, d_count,
-                                   m->history_cap);
+                                   m->history_cap, m->d_state + 7);
   B200_LAUNCH_CHECK();
   if (n_kernels)
     *n_kernels = (int)(b200_launch_count() - before);
@@ -720,6 +780,9 @@ void b200_model_destroy(b200_model *m) {
   for (auto p : m->kv) cudaFree(p);
   cudaFree(m->kv_dev); cudaFree(m->embed); cudaFree(m->inv_freq); cudaFree(m->final_norm);
   cudaFree(m->x); cudaFree(m->qkv); cudaFree(m->attn); cudaFree(m->mid);
+  for (void *p : m->tp_opened)
+    if (p) cudaIpcCloseMemHandle(p);
+  cudaFree(m->tp_ll);
   cudaFree(m->part); cudaFree(m->logits); cudaFree(m->logits_shard);
   cudaFree(m->attn_scratch); cudaFree(m->argmax_scratch); cudaFree(m->kv_stage);
   cudaFree(m->d_state); cudaFree(m->d_history);
@@ -1005,6 +1068,73 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   return rc;
 }
 
+// Staging buffers for the peer-store sums: allocate this rank's, trade CUDA IPC
+// handles through NCCL, map the peers'.  All ranks agree (a min-reduction) on
+// whether the path is usable; otherwise every rank keeps the NCCL all-reduce.
+static int tp_push_setup(b200_model *m) {
+  const int tp = m->tp, H = m->cfg.hidden;
+  const char *env = std::getenv("BUDDY_B200_TP_SUM");
+  int ok = !(env && !strcmp(env, "nccl")) && tp <= kTpMaxRanks;
+  cudaStream_t st = m->stream;
+  const size_t pairs = (size_t)kTpRegions * tp * H;
+  char *d_send = nullptr, *d_recv = nullptr;
+  float *d_flag = nullptr;
+  if (int rc = dev_alloc((void **)&d_send, 64)) return rc;
+  if (int rc = dev_alloc((void **)&d_recv, 64 * (size_t)tp)) return rc;
+  if (int rc = dev_alloc((void **)&d_flag, 4)) return rc;
+  cudaIpcMemHandle_t mine{};
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+  if (ok) {
+    if (dev_alloc((void **)&m->tp_ll, pairs * sizeof(uint2)) != B200_OK ||
+        cudaMemset(m->tp_ll, 0, pairs * sizeof(uint2)) != cudaSuccess ||
+        cudaIpcGetMemHandle(&mine, m->tp_ll) != cudaSuccess) {
+      (void)cudaGetLastError();
+      ok = 0;
+    }
+  }
+  B200_CUDA(cudaMemcpy(d_send, &mine, 64, cudaMemcpyHostToDevice));
+  B200_NCCL(g_nccl.AllGather(d_send, d_recv, 64, 0 /* ncclChar */, g_nccl.comm, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  std::vector<cudaIpcMemHandle_t> all(tp);
+  B200_CUDA(cudaMemcpy(all.data(), d_recv, 64 * (size_t)tp, cudaMemcpyDeviceToHost));
+  TpPush push{};
+  if (ok) {
+    for (int r = 0; r < tp; ++r) {
+      if (r == g_nccl.rank) {
+        push.peer[r] = m->tp_ll;
+        continue;
+      }
+      void *p = nullptr;
+      if (cudaIpcOpenMemHandle(&p, all[r], cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) {
+        (void)cudaGetLastError();
+        ok = 0;
+        break;
+      }
+      m->tp_opened[r] = p;
+      push.peer[r] = (uint2 *)p;
+    }
+  }
+  // every rank must take the same path (this also lines the ranks up before the first step)
+  const float mine_ok = ok ? 1.f : 0.f;
+  B200_CUDA(cudaMemcpy(d_flag, &mine_ok, 4, cudaMemcpyHostToDevice));
+  B200_NCCL(g_nccl.AllReduce(d_flag, d_flag, 1, kNcclFloat, 3 /* ncclMin */, g_nccl.comm, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  float all_ok = 0.f;
+  B200_CUDA(cudaMemcpy(&all_ok, d_flag, 4, cudaMemcpyDeviceToHost));
+  cudaFree(d_send); cudaFree(d_recv); cudaFree(d_flag);
+  if (all_ok > 0.5f) {
+    push.ranks = tp;
+    push.rank = g_nccl.rank;
+    push.H = H;
+    push.step = m->d_state + 7;
+    push.per_step = 2 * m->cfg.n_layers;
+    m->tp_push = push;
+  } else {
+    m->tp_push = TpPush{};
+  }
+  return B200_OK;
+}
+
 int b200_model_finalize(b200_model *m) {
   if (!m)
     return fail(B200_EINVAL, "finalize: null model");
@@ -1048,6 +1178,8 @@ int b200_model_finalize(b200_model *m) {
     m->finalized = true;
     return B200_OK;
   }
+  if (m->tp > 1)
+    if (int rc = tp_push_setup(m)) return rc;
   // Warm every kernel once outside capture (sets shared-memory attributes),
   // then capture the step.
   if (int rc = set_state(m, 0, 0)) return rc;
@@ -1168,6 +1300,9 @@ float *b200_model_kv_ptr(b200_model *m, int buffer) {
 }
 
 int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega ? 1 : 0; }
+int b200_model_tp_sum_kind(const b200_model *m) {
+  return !m || m->tp <= 1 ? 0 : (m->tp_push.ranks > 0 ? 2 : 1);
+}
 
 int b200_model_read_trace(b200_model *m, long long *host, int64_t capacity) {
   if (!m || !host || !m->d_trace)

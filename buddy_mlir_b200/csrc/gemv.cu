@@ -32,6 +32,7 @@ struct GemvP {
   int accumulate, silu_pairs;
   int kc;  // activation slab (elements) staged in shared memory at a time
   int fast_scales;  // int4 groups: the 8 f16 scales of a 1024-element block are one aligned 16-byte load
+  TpPush push;      // ranks > 0: results go to every rank's staging buffer instead of y
   float eps;
 };
 
@@ -341,6 +342,14 @@ gemv_kernel(const GemvP p) {
             if (m < p.M) {
               const int64_t o = (int64_t)m * p.y_ld + row;
               float v = acc[r][m];
+              if (p.push.ranks > 0) {
+                // this rank's share of a tensor-parallel sum (M = 1): one tagged pair per rank
+                const uint32_t seq = (uint32_t)(*p.push.step) * p.push.per_step + p.push.index;
+                const size_t at = ((size_t)(seq % kTpRegions) * p.push.ranks + p.push.rank) * p.push.H + row;
+                for (int t = 0; t < p.push.ranks; ++t)
+                  tagged_store(p.push.peer[t] + at, v, seq + 1u);
+                continue;
+              }
               if (p.residual != nullptr)
                 v = p.residual[o] + v;
               if (p.y_dtype == B200_F32) {
@@ -407,6 +416,11 @@ using namespace b200;
 
 extern "C" int b200_gemv(const b200_weight *w, const b200_gemv_args *a,
                          void *stream) {
+  return gemv_run(w, a, nullptr, (cudaStream_t)stream);
+}
+
+int b200::gemv_run(const b200_weight *w, const b200_gemv_args *a, const TpPush *push,
+                   cudaStream_t stream) {
   if (!w || !a || !w->w || !a->x || !a->y)
     return fail(B200_EINVAL, "gemv: null argument");
   if (a->M < 1 || a->M > 16)
@@ -426,6 +440,11 @@ extern "C" int b200_gemv(const b200_weight *w, const b200_gemv_args *a,
     return rc;
 
   GemvP p{};
+  if (push != nullptr) {
+    if (a->M != 1 || a->silu_pairs || push->ranks < 2 || push->ranks > kTpMaxRanks || push->H != w->N)
+      return fail(B200_EINVAL, "gemv: bad tensor-parallel push request");
+    p.push = *push;
+  }
   p.x = a->x;
   p.w = (const uint8_t *)w->w;
   p.scale = w->scale;
@@ -483,7 +502,7 @@ extern "C" int b200_gemv(const b200_weight *w, const b200_gemv_args *a,
   } else if (w->N / (8 * 2) < 2 * 148) {
     warps = 4;
   }
-  cudaStream_t st = (cudaStream_t)stream;
+  cudaStream_t st = stream;
   switch (w->kind) {
   case B200_W_I8:
     return dispatch<B200_W_I8, false>(p, mt, R, warps, st);

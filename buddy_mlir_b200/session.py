@@ -173,6 +173,10 @@ class ModelSession:
     def uses_persistent_kernel(self) -> bool:
         return bool(self.lib.b200_model_uses_persistent_kernel(self._h))
 
+    def tp_sum_kind(self):
+        """0: single GPU, 1: NCCL all-reduce, 2: peer stores from the GEMV epilogue."""
+        return int(self.lib.b200_model_tp_sum_kind(self._h))
+
     def kv_upload(self, buffer: int, host: np.ndarray, pos0: int, n_pos: int):
         host = np.ascontiguousarray(host, dtype=np.float32)
         _lib.check(self.lib.b200_model_kv_upload(self._h, buffer, host.ctypes.data, pos0, n_pos))

@@ -76,6 +76,9 @@ def run(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     local = int(os.environ.get("LOCAL_RANK", str(rank)))
     torch.cuda.set_device(local)
+    # no in-switch (multicast) reductions: the library's own sums are plain peer stores, and a
+    # rank that dies with memory bound to a multicast object can take its peers down
+    os.environ.setdefault("NCCL_NVLS_ENABLE", "0")
     if world > 1:
         dist.init_process_group("nccl")
     lib = _lib.load()
@@ -150,7 +153,10 @@ def run(args):
                                        "weight-only, f32 activations and KV, batch 1, greedy decode",
                            "context": f"{start + warmup}..{cfg.max_len}", "tp": world,
                            "tp1_tokens_per_s_same_run": tp1,
-                           "collectives": "2 NCCL all-reduce of 16 KB per layer + 1 all-gather of logits",
+                           "collectives": ("2 sums of 16 KB per layer by peer stores from the GEMV epilogue over NVLink "
+                                           "(tagged pairs, no collective library) + 1 NCCL all-gather of logits")
+                                          if s.tp_sum_kind() == 2 else
+                                          "2 NCCL all-reduce of 16 KB per layer + 1 all-gather of logits",
                            "l2": "inputs larger than L2 (3.9 GB of weights per step across ranks)",
                            "weights": "seeded N(0,0.02) block, tiled"},
                 "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
@@ -162,6 +168,8 @@ def run(args):
                 "gpu_launches": int(launches) * world, "kernels_per_step": int(launches // steps),
                 "clocks": clocks}
         print(json.dumps(line))
+    if world > 1:
+        dist.barrier()   # nobody unmaps its staging buffer while a peer may still store into it
     s.close()
     if world > 1:
         lib.b200_tp_shutdown()

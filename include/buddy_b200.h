@@ -293,6 +293,11 @@ int b200_model_kernels_per_step(const b200_model *m);
  * linear layer int8, one GPU); 0 when they replay the multi-kernel CUDA graph.
  * The environment variable BUDDY_B200_DECODE=graph forces the graph. */
 int b200_model_uses_persistent_kernel(const b200_model *m);
+/* How the sums of a tensor-parallel model's row-parallel projections are formed:
+ * 0 = single GPU, 1 = NCCL all-reduce, 2 = every rank's GEMV stores its partial
+ * results straight into all ranks' staging buffers over NVLink (tagged pairs),
+ * a small kernel adds them up in rank order. */
+int b200_model_tp_sum_kind(const b200_model *m);
 /* Tuning aid: with BUDDY_B200_TRACE=<stride> set at load time, every
  * stride-th CTA of the persistent kernel records the SM clock at each phase
  * boundary of the last step: host[cta/stride][layer][32]. Returns the number

@@ -39,7 +39,7 @@ for tok in synthetic.prompt_tokens(cfg, 2, 6):
     out.append(s.logits_data().copy())
 ids = s.generate(int(np.argmax(out[-1])), 8)
 if rank == 0:
-    np.savez(sys.argv[2], logits=np.stack(out), ids=ids)
+    np.savez(sys.argv[2], logits=np.stack(out), ids=ids, sum_kind=s.tp_sum_kind())
 dist.barrier()
 s.close()
 lib.b200_tp_shutdown()
@@ -56,8 +56,9 @@ def _two_gpus():
 
 
 @pytest.mark.skipif(not _two_gpus(), reason="needs two CUDA devices")
+@pytest.mark.parametrize("sum_path", ["peer", "nccl"])
 @pytest.mark.parametrize("kind,tol", [("f32", 1e-3), ("w8", 1e-3), ("w4", 2e-2)])
-def test_tp2_matches_unsharded_checker(tmp_path, kind, tol):
+def test_tp2_matches_unsharded_checker(tmp_path, kind, tol, sum_path):
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as orc
     from buddy_mlir_b200 import TINY_QWEN3, synthetic
@@ -69,10 +70,15 @@ def test_tp2_matches_unsharded_checker(tmp_path, kind, tol):
     out = str(tmp_path / "out.npz")
     # NVLS off: a rank that dies with multicast-bound memory can fault its peers
     env = dict(os.environ, NCCL_NVLS_ENABLE="0", MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    # the sums of the row-parallel projections: peer stores from the GEMV epilogue (default) or NCCL
+    env.pop("BUDDY_B200_TP_SUM", None)
+    if sum_path == "nccl":
+        env["BUDDY_B200_TP_SUM"] = "nccl"
     subprocess.check_call([sys.executable, "-m", "torch.distributed.run", "--nnodes=1",
                            "--nproc-per-node=2", "--master-addr", "127.0.0.1", "--master-port",
                            str(port), str(script), ROOT, out, kind], env=env, timeout=600)
     got = np.load(out)
+    assert int(got["sum_kind"]) == (2 if sum_path == "peer" else 1)
     cfg = TINY_QWEN3
     _, views = synthetic.make_f32_blob(cfg, 31)
     okind = {"f32": "f32", "w8": "w8", "w4": "w4g"}[kind]
