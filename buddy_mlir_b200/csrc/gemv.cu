@@ -32,6 +32,7 @@ struct GemvP {
   int accumulate, silu_pairs;
   int kc;  // activation slab (elements) staged in shared memory at a time
   int fast_scales;  // int4 groups: the 8 f16 scales of a 1024-element block are one aligned 16-byte load
+  int in_place4;    // int4 group-128, M = 1, f32 input: nibbles used in place (see gemv_kernel)
   TpPush push;      // ranks > 0: results go to every rank's staging buffer instead of y
   float eps;
 };
@@ -100,10 +101,32 @@ __device__ __forceinline__ float silu_mul(float g, float u) {
   return (g * s) * u;
 }
 
+// Single-row int8 decode (M = 1, per-channel scales): a weight byte is used in
+// place.  With its sign bit flipped (u = q + 128) and the other bytes of the
+// word masked off, the word read as a float is u * 2^-149 (byte 0, a denormal),
+// u * 2^-141, u * 2^-133 (bytes 1, 2) or, shifted down, u * 2^-149 (byte 3).  So
+// a weight costs one logic op and one FMA.  The staged activations carry a
+// factor 2^64 (products stay in the normal range and are exact up to the FMA's
+// single rounding), the four byte positions have their own accumulators, and
+//   sum x*q = 2^85 * (a0 + a1*2^-8 + a2*2^-16 + a3) - 128 * sum x.
+constexpr float kInPlaceX = 18446744073709551616.0f;          // 2^64
+constexpr float kInPlaceAcc = 38685626227668133590597632.0f;  // 2^85
+
 template <int KIND, int MT, int R, bool GROUPED>
 __global__ void __launch_bounds__(256)
 gemv_kernel(const GemvP p) {
+  constexpr bool IN_PLACE = KIND == B200_W_I8 && MT == 1 && !GROUPED;
+  // The same idea for group-wise int4 (zero-point 8): nibble e of a group of four
+  // sits at bit 4e of a 16-bit half word, so masked in place it reads as
+  // n * 2^(4e-149).  The staged activation k carries 2^(64 - 4*(k%4)), which
+  // puts the four products of a group on one scale (2^-85); the zero-point term
+  // -8 * (x0+x1+x2+x3) * 2^-85 of every group of four is staged beside the
+  // activations.  One logic op and one FMA per weight, one FMA per four weights
+  // for the group scale.
+  const bool in_place4 = KIND == B200_W_U4 && MT == 1 && GROUPED && p.in_place4;
+  __shared__ float s_sx[8];   // per-warp sums of the staged activations (IN_PLACE)
   extern __shared__ __align__(16) float xs[];  // [MT][kc]
+  float *c4 = xs + (size_t)MT * p.kc;   // in_place4: zero-point terms, one per 4 activations
   __shared__ float s_red[8 * 16];
   __shared__ float s_rinv[16];
 
@@ -154,14 +177,20 @@ gemv_kernel(const GemvP p) {
   }
 
   bool staged = false;
+  float sx_cta = 0.f;   // IN_PLACE: sum of the activations of the slab staged last
   for (int64_t base = (int64_t)blockIdx.x * nwarps * R; base < p.N; base += gstride) {
     const int64_t row0 = base + (int64_t)warp * R;
     float acc[R][MT];
+    float a4[IN_PLACE ? R : 1][4];   // IN_PLACE: one accumulator per byte position
+    float sx_total = 0.f;            // IN_PLACE: sum of the activations seen so far
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int m = 0; m < MT; ++m)
         acc[r][m] = 0.f;
+#pragma unroll
+    for (int r = 0; r < (IN_PLACE ? R : 1); ++r)
+      a4[r][0] = a4[r][1] = a4[r][2] = a4[r][3] = 0.f;
 
     const uint8_t *rowp[R];
     int64_t srow[R];
@@ -180,6 +209,7 @@ gemv_kernel(const GemvP p) {
         if (staged)
           __syncthreads();
         // ---- stage the activation slab (zero beyond K and beyond M) ----------
+        float sx = 0.f;
         if (MT == 1 && p.x_dtype == B200_F32 && (p.K & 3) == 0 &&
             (reinterpret_cast<uintptr_t>(p.x) & 15) == 0) {
           // one f32 row: 16-byte loads, no index arithmetic per element
@@ -198,6 +228,17 @@ gemv_kernel(const GemvP p) {
                 v.w = w4.w * (v.w * rinv);
               }
             }
+            if (IN_PLACE) {
+              sx += (v.x + v.y) + (v.z + v.w);
+              v.x *= kInPlaceX; v.y *= kInPlaceX; v.z *= kInPlaceX; v.w *= kInPlaceX;
+            }
+            if (in_place4) {
+              c4[i >> 2] = -8.0f * ((v.x + v.y) + (v.z + v.w)) * (1.0f / kInPlaceAcc);
+              v.x *= kInPlaceX;                       // 2^64
+              v.y *= kInPlaceX * 0.0625f;             // 2^60
+              v.z *= kInPlaceX * 0.00390625f;         // 2^56
+              v.w *= kInPlaceX * 0.000244140625f;     // 2^52
+            }
             *reinterpret_cast<float4 *>(&xs[i]) = v;
           }
         } else {
@@ -209,13 +250,29 @@ gemv_kernel(const GemvP p) {
               if (p.norm_w != nullptr)
                 v = p.norm_w[k] * (v * s_rinv[m]);
             }
+            if (IN_PLACE) {
+              sx += v;
+              v *= kInPlaceX;
+            }
             xs[m * p.kc + (k - k0)] = v;
           }
         }
+        if (IN_PLACE) {
+          sx = warp_sum(sx);
+          if (lane == 0)
+            s_sx[warp] = sx;
+        }
         __syncthreads();
         staged = true;
+        if (IN_PLACE) {
+          sx_cta = 0.f;
+          for (int w = 0; w < nwarps; ++w)
+            sx_cta += s_sx[w];
+        }
       }
 
+      if (IN_PLACE)
+        sx_total += sx_cta;
       const int nblk = (kc + BLK - 1) / BLK;
 #pragma unroll 2
       for (int b = 0; b < nblk; ++b) {
@@ -237,6 +294,46 @@ gemv_kernel(const GemvP p) {
               sv[r] = __ldg(reinterpret_cast<const uint4 *>(
                   reinterpret_cast<const __half *>(p.scale) + srow[r] + (k0 + kb) / p.group));
           }
+          if (IN_PLACE) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const float4 xv = *reinterpret_cast<const float4 *>(&xs[kb + j * q + 4 * lane]);
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                const uint32_t u = (j == 0 ? wv[r].x : j == 1 ? wv[r].y : j == 2 ? wv[r].z : wv[r].w) ^
+                                   0x80808080u;
+                a4[r][0] = fmaf(xv.x, __uint_as_float(u & 0x000000FFu), a4[r][0]);
+                a4[r][1] = fmaf(xv.y, __uint_as_float(u & 0x0000FF00u), a4[r][1]);
+                a4[r][2] = fmaf(xv.z, __uint_as_float(u & 0x00FF0000u), a4[r][2]);
+                a4[r][3] = fmaf(xv.w, __uint_as_float(u >> 24), a4[r][3]);
+              }
+            }
+          } else if (in_place4) {
+#pragma unroll
+            for (int wi = 0; wi < 4; ++wi) {   // word wi of the unit holds groups 2*wi (low half) and 2*wi+1
+              const int ka = kb + (2 * wi) * q + 4 * lane, kb2 = ka + q;
+              const float4 xa = *reinterpret_cast<const float4 *>(&xs[ka]);
+              const float4 xb = *reinterpret_cast<const float4 *>(&xs[kb2]);
+              const float ca = c4[ka >> 2], cb = c4[kb2 >> 2];
+#pragma unroll
+              for (int r = 0; r < R; ++r) {
+                const uint32_t w32 = wi == 0 ? wv[r].x : wi == 1 ? wv[r].y : wi == 2 ? wv[r].z : wv[r].w;
+                const uint32_t s32 = wi == 0 ? sv[r].x : wi == 1 ? sv[r].y : wi == 2 ? sv[r].z : sv[r].w;
+                const uint32_t hw = w32 >> 16;
+                float ta = fmaf(xa.x, __uint_as_float(w32 & 0x000Fu), ca);
+                ta = fmaf(xa.y, __uint_as_float(w32 & 0x00F0u), ta);
+                ta = fmaf(xa.z, __uint_as_float(w32 & 0x0F00u), ta);
+                ta = fmaf(xa.w, __uint_as_float(w32 & 0xF000u), ta);
+                float tb = fmaf(xb.x, __uint_as_float(hw & 0x000Fu), cb);
+                tb = fmaf(xb.y, __uint_as_float(hw & 0x00F0u), tb);
+                tb = fmaf(xb.z, __uint_as_float(hw & 0x0F00u), tb);
+                tb = fmaf(xb.w, __uint_as_float(hw & 0xF000u), tb);
+                const float2 sc2 = __half22float2(*reinterpret_cast<const __half2 *>(&s32));
+                acc[r][0] = fmaf(ta, sc2.x, acc[r][0]);
+                acc[r][0] = fmaf(tb, sc2.y, acc[r][0]);
+              }
+            }
+          } else {
 #pragma unroll
           for (int j = 0; j < DQ::G; ++j) {
             const int kx = kb + j * q + 4 * lane;
@@ -281,16 +378,32 @@ gemv_kernel(const GemvP p) {
               }
             }
           }
+          }
         }
       }
     }
 
     // ---- reduce across lanes, epilogue --------------------------------------
+    if (IN_PLACE) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        acc[r][0] = (a4[r][0] + a4[r][3]) + fmaf(a4[r][1], 0.00390625f, a4[r][2] * 0.0000152587890625f);
+    }
 #pragma unroll
     for (int r = 0; r < R; ++r)
 #pragma unroll
       for (int m = 0; m < MT; ++m)
         acc[r][m] = warp_sum(acc[r][m]);
+    if (IN_PLACE) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        acc[r][0] = fmaf(acc[r][0], kInPlaceAcc, -128.0f * sx_total);
+    }
+    if (in_place4) {
+#pragma unroll
+      for (int r = 0; r < R; ++r)
+        acc[r][0] *= kInPlaceAcc;
+    }
 
     if (lane == 0) {
 #pragma unroll
@@ -371,7 +484,7 @@ gemv_kernel(const GemvP p) {
 template <int KIND, int MT, int R, bool GROUPED>
 static int launch(const GemvP &p, int warps, cudaStream_t st) {
   auto kern = gemv_kernel<KIND, MT, R, GROUPED>;
-  const size_t smem = (size_t)MT * p.kc * sizeof(float);
+  const size_t smem = ((size_t)MT * p.kc + (p.in_place4 ? p.kc / 4 : 0)) * sizeof(float);
   if (smem > 40 * 1024) {  // dynamic + static shared memory may exceed the 48 KB default
     static thread_local size_t configured = 0;
     if (smem > configured) {
@@ -488,6 +601,9 @@ int b200::gemv_run(const b200_weight *w, const b200_gemv_args *a, const TpPush *
 
   p.fast_scales = grouped && w->scale_dtype == B200_F16 && p.group * 8 == 1024 && p.ngroups % 8 == 0 &&
                   (reinterpret_cast<uintptr_t>(w->scale) & 15) == 0;
+
+  p.in_place4 = p.fast_scales && a->M == 1 && a->x_dtype == B200_F32 && (w->K & 1023) == 0 &&
+                (reinterpret_cast<uintptr_t>(a->x) & 15) == 0;
 
   // Rows per warp: the most that still gives every SM two CTAs of 8 warps.
   int R = 2, warps = 8;
