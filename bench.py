@@ -175,25 +175,39 @@ def workload_config(cfg, start, args):
             "weights": "seeded N(0,0.02)", "kv_prefix": "seeded N(0,1)"}
 
 
-def gemv_microbench(lib):
-    """Isolated int8 GEMV launches over weights that do not fit L2, CUDA events
-    on the launching (current) stream."""
+GEMV_SHAPES = {
+    # name: (weight kind, N, K, group)
+    "gate_up": ("i8", 17920, 1536, 0), "down": ("i8", 1536, 8960, 0), "o": ("i8", 1536, 1536, 0),
+    "lm_head": ("i8", 151936, 1536, 0),
+    "u4_qkv_8b": ("u4", 6144, 4096, 128), "u4_gate_up_8b": ("u4", 24576, 4096, 128),
+    "u4_down_8b": ("u4", 4096, 12288, 128), "u4_lm_head_8b": ("u4", 151936, 4096, 128),
+}
+
+
+def gemv_microbench(lib, only=None):
+    """Isolated M = 1 GEMV launches (b200_gemv) over weights that do not fit L2,
+    CUDA events on the launching (current) stream.  int8 per-channel shapes of
+    the 1.5B model and int4 group-128 shapes of the 8B model."""
     import ctypes as C
     import torch
     from buddy_mlir_b200 import _lib
     out = {}
     hbm, _ = peaks()
-    for name, N, K in (("gate_up", 17920, 1536), ("down", 1536, 8960), ("o", 1536, 1536),
-                       ("lm_head", 151936, 1536)):
-        copies = max(2, int(400e6 // (N * K)) + 1)
-        ws = [torch.randint(-127, 128, (N * K,), dtype=torch.int8, device="cuda") for _ in range(copies)]
-        sc = torch.rand(N, device="cuda") * 0.01
+    for name, (kind, N, K, group) in GEMV_SHAPES.items():
+        if only and name != only:
+            continue
+        nbytes = N * K if kind == "i8" else N * K // 2
+        copies = max(2, int(400e6 // nbytes) + 1)
+        ws = [torch.randint(0, 255, (nbytes,), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+        ng = K // group if group else 1
+        sc = (torch.rand(N * ng, device="cuda") * 0.01).half() if group else torch.rand(N, device="cuda") * 0.01
         x = torch.randn(1, K, device="cuda")
         y = torch.zeros(1, N, device="cuda")
         st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
 
         def launch(i):
-            w = _lib.Weight(_lib.W_I8, 0, K, N, ws[i % copies].data_ptr(), sc.data_ptr(), _lib.F32, 0, None)
+            w = _lib.Weight(_lib.W_I8 if kind == "i8" else _lib.W_U4, group, K, N, ws[i % copies].data_ptr(),
+                            sc.data_ptr(), _lib.F16 if group else _lib.F32, 0, None)
             a = _lib.GemvArgs(x.data_ptr(), 0, 0, 0, 0, y.data_ptr(), None, None, 0.0, 1, 0, 0)
             _lib.check(lib.b200_gemv(C.byref(w), C.byref(a), st))
         for i in range(copies):
@@ -207,9 +221,22 @@ def gemv_microbench(lib):
         e1.record()
         torch.cuda.synchronize()
         us = e0.elapsed_time(e1) * 1000.0 / reps
-        gbs = (N * K + 4 * N + 4 * K + 4 * N) / us / 1e3
-        out[name] = {"N": N, "K": K, "us": round(us, 2), "GB/s": round(gbs, 1), "frac": round(gbs / hbm, 3)}
+        gbs = (nbytes + N * ng * (2 if group else 4) + 4 * K + 4 * N) / us / 1e3
+        out[name] = {"N": N, "K": K, "weights": "int8 per-channel" if kind == "i8" else "int4 group-128",
+                     "us": round(us, 2), "GB/s": round(gbs, 1), "frac": round(gbs / hbm, 3)}
     return out
+
+
+def run_gemv_only(args):
+    """--gemv-only: just the isolated GEMV sweep (one JSON line); --gemv-shape picks one shape,
+    which keeps a profiler capture of that kernel small."""
+    import torch
+    from buddy_mlir_b200 import _lib
+    lib = _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    print(json.dumps({"gemv_isolated": gemv_microbench(lib, args.gemv_shape)}))
 
 
 def run_single(args):
@@ -299,7 +326,7 @@ def run_single(args):
                          "frac": achieved / hbm, "traffic": traffic, "peak_source": which,
                          "kernel": "decode_step_kernel (one persistent launch per token)" if persistent else "whole decode step (CUDA graph replay)",
                          "bytes_per_step": step_bytes, "frac_of_8TBs_nominal": achieved / 8000.0},
-            "gemv_int8_isolated": gemv,
+            "gemv_isolated": gemv,
             "cpu_baseline": base,
             "e2e": {"value": steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": 16,
                     "d2h_bytes_per_step": d2h, "tokens_match_resident_run": same},
@@ -314,6 +341,8 @@ def main():
     ap.add_argument("--steps", type=int, default=256)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
+    ap.add_argument("--gemv-only", action="store_true", help="run only the isolated GEMV sweep")
+    ap.add_argument("--gemv-shape", default=None, help="with --gemv-only: one shape of GEMV_SHAPES")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the isolated-GEMV, end-to-end and CPU legs (for profiler captures)")
     args = ap.parse_args()
@@ -321,6 +350,8 @@ def main():
         args.warmup = 3
     if args.impl == "reference":
         return run_reference(args)
+    if args.gemv_only:
+        return run_gemv_only(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single(args)
     from buddy_mlir_b200 import tp_bench

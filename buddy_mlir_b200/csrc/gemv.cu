@@ -611,7 +611,7 @@ int b200::gemv_run(const b200_weight *w, const b200_gemv_args *a, const TpPush *
     const int64_t want = 2 * 148;
     if (w->N / (8 * 4) >= want)
       R = 4;
-    else if (w->N / (8 * 2) >= want || a->silu_pairs)
+    else if (w->N / (8 * 2) >= want / 2 || a->silu_pairs)   // two rows share the staged activations
       R = 2;
     else
       R = 1;
