@@ -19,7 +19,7 @@
 
 namespace b200 {
 
-constexpr int kAttnWarps = 4;
+constexpr int kAttnWarps = 8;
 constexpr float kSeed = -1.0e30f;
 
 template <int G, int VEC>

@@ -713,10 +713,10 @@ int b200_model_create(const b200_model_config *cfg, b200_model **out) {
   m->layers.resize(c.n_layers);
   m->kv.assign(2 * c.n_layers, nullptr);
   const int D = c.head_dim;
-  // attention splits: about two CTAs per SM over this rank's kv heads, at least 32 rows each
+  // attention splits: about four CTAs per SM over this rank's kv heads, at least 32 rows each
   {
     const int local_kv = c.kv_heads / tp;
-    m->splits = (2 * 148 + local_kv - 1) / local_kv;
+    m->splits = (4 * 148 + local_kv - 1) / local_kv;
     if (m->splits > c.max_len / 32) m->splits = c.max_len / 32;
     if (m->splits > 128) m->splits = 128;
     if (m->splits < 1) m->splits = 1;
