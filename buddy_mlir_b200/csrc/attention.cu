@@ -161,6 +161,64 @@ gqa_decode_kernel(const float *__restrict__ q, const float *__restrict__ kc,
   if (!s_last)
     return;
   __threadfence();
+  constexpr int kFoldSplits = 128;   // splits the parallel fold below keeps in shared memory
+  if (splits <= kFoldSplits) {
+    // Weights first (one warp per head: M = max m_s, w_s = exp(m_s - M), L = sum l_s w_s),
+    // then every output is a sum of independent loads.  Same result as the running
+    // recurrence of tosa.py:14502-14594 up to rounding, without its chain of
+    // dependent loads over the splits.
+    __shared__ float f_w[G][kFoldSplits];
+    __shared__ float f_L[G];
+    if (warp < G) {
+      const float *parts = scratch + (int64_t)(hk * G + warp) * splits * stride + D;
+      float ms[kFoldSplits / 32], ls[kFoldSplits / 32];
+      float M = kSeed;
+#pragma unroll
+      for (int i = 0; i < kFoldSplits / 32; ++i) {
+        const int sidx = lane + 32 * i;
+        ms[i] = kSeed;
+        ls[i] = 0.f;
+        if (sidx < splits) {
+          ms[i] = __ldcg(&parts[(int64_t)sidx * stride]);
+          ls[i] = __ldcg(&parts[(int64_t)sidx * stride + 1]);
+        }
+        M = fmaxf(M, ms[i]);
+      }
+      M = warp_max(M);
+      float L = 0.f;
+#pragma unroll
+      for (int i = 0; i < kFoldSplits / 32; ++i) {
+        const int sidx = lane + 32 * i;
+        const float b = expf(ms[i] - M);
+        if (sidx < splits)
+          f_w[warp][sidx] = b;
+        L = fmaf(ls[i], b, L);
+      }
+      L = warp_sum(L);
+      if (lane == 0)
+        f_L[warp] = L;
+    }
+    __syncthreads();
+    for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+      const int g = idx / D, d = idx - g * D;
+      const float *parts = scratch + (int64_t)(hk * G + g) * splits * stride + d;
+      float ar = 0.f;
+      int sidx = 0;
+      for (; sidx + 8 <= splits; sidx += 8) {
+        float v[8];
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          v[u] = __ldcg(&parts[(int64_t)(sidx + u) * stride]);
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          ar = fmaf(v[u], f_w[g][sidx + u], ar);
+      }
+      for (; sidx < splits; ++sidx)
+        ar = fmaf(__ldcg(&parts[(int64_t)sidx * stride]), f_w[g][sidx], ar);
+      out[(int64_t)(hk * G + g) * D + d] = __fdiv_rn(ar, f_L[g]);
+    }
+    return;
+  }
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, d = idx - g * D;
     const float *parts = scratch + (int64_t)(hk * G + g) * splits * stride;
