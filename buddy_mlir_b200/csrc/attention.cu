@@ -204,13 +204,13 @@ gqa_decode_kernel(const float *__restrict__ q, const float *__restrict__ kc,
       const float *parts = scratch + (int64_t)(hk * G + g) * splits * stride + d;
       float ar = 0.f;
       int sidx = 0;
-      for (; sidx + 8 <= splits; sidx += 8) {
-        float v[8];
+      for (; sidx + 16 <= splits; sidx += 16) {   // 16 independent loads in flight
+        float v[16];
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < 16; ++u)
           v[u] = __ldcg(&parts[(int64_t)(sidx + u) * stride]);
 #pragma unroll
-        for (int u = 0; u < 8; ++u)
+        for (int u = 0; u < 16; ++u)
           ar = fmaf(v[u], f_w[g][sidx + u], ar);
       }
       for (; sidx < splits; ++sidx)
