@@ -125,6 +125,30 @@ __global__ void tp_reduce_add_kernel(float *x, const uint2 *buf, int H, int rank
   }
   x[n] = sum;
 }
+// One-off check of the peer mappings before they are used: every rank stores a
+// marker into every rank's buffer (behind the staging regions) and waits, at most
+// two seconds, for everybody's marker in its own.  *ok is cleared on expiry.
+__global__ void tp_handshake_kernel(TpPush push, size_t at, int *ok) {
+  const int t = threadIdx.x;
+  const uint32_t tag = 0xFFFFFF00u;
+  if (t < push.ranks)
+    tagged_store(push.peer[t] + at + push.rank, (float)(push.rank + 1), tag);
+  if (t < push.ranks) {
+    const uint2 *p = push.peer[push.rank] + at + t;
+    unsigned long long t0;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (uint32_t it = 0; it < (1u << 28); ++it) {
+      if (tagged_load(p).y == tag)
+        return;
+      unsigned long long now;
+      asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+      if (now - t0 > 2000000000ull)
+        break;
+      __nanosleep(200);
+    }
+    *ok = 0;
+  }
+}
 // end of a step: feed the argmax back and advance the position
 __global__ void advance_kernel(int32_t *token, int32_t *pos,
                                const int32_t *next, int32_t *history,
@@ -1076,7 +1100,7 @@ static int tp_push_setup(b200_model *m) {
   const char *env = std::getenv("BUDDY_B200_TP_SUM");
   int ok = !(env && !strcmp(env, "nccl")) && tp <= kTpMaxRanks;
   cudaStream_t st = m->stream;
-  const size_t pairs = (size_t)kTpRegions * tp * H;
+  const size_t pairs = (size_t)kTpRegions * tp * H + kTpMaxRanks;   // + one marker per rank for the handshake
   char *d_send = nullptr, *d_recv = nullptr;
   float *d_flag = nullptr;
   if (int rc = dev_alloc((void **)&d_send, 64)) return rc;
@@ -1113,6 +1137,24 @@ static int tp_push_setup(b200_model *m) {
       m->tp_opened[r] = p;
       push.peer[r] = (uint2 *)p;
     }
+  }
+  if (ok) {
+    // try the mappings once: a store to every peer, everybody's store seen here
+    int *d_ok = nullptr;
+    const int one = 1;
+    if (int rc = dev_alloc((void **)&d_ok, 4)) return rc;
+    B200_CUDA(cudaMemcpy(d_ok, &one, 4, cudaMemcpyHostToDevice));
+    push.ranks = tp;
+    push.rank = g_nccl.rank;
+    tp_handshake_kernel<<<1, 32, 0, st>>>(push, (size_t)kTpRegions * tp * H, d_ok);
+    int seen = 0;
+    if (cudaStreamSynchronize(st) != cudaSuccess ||
+        cudaMemcpy(&seen, d_ok, 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+      (void)cudaGetLastError();
+      seen = 0;
+    }
+    cudaFree(d_ok);
+    ok = seen;
   }
   // every rank must take the same path (this also lines the ranks up before the first step)
   const float mine_ok = ok ? 1.f : 0.f;
