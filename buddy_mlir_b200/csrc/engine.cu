@@ -228,6 +228,8 @@ struct b200_model {
   int kernels_per_step = 0;
   bool finalized = false;
   float *h_logits_pinned = nullptr;
+  float *h_rows_pinned = nullptr;   // this step's K/V rows, fetched together with the logits
+  bool rows_fresh = false;
   int32_t *h_state_pinned = nullptr;
   // persistent decode-step kernel (batch 1, int8): see mega.cu
   bool mega = false;
@@ -779,6 +781,8 @@ int b200_model_create(const b200_model_config *cfg, b200_model **out) {
   if (rc == B200_OK && (cudaEventCreate(&m->ev0) != cudaSuccess || cudaEventCreate(&m->ev1) != cudaSuccess))
     rc = fail(B200_ECUDA, "event create failed");
   if (rc == B200_OK && (cudaMallocHost((void **)&m->h_logits_pinned, (size_t)c.vocab * 4) != cudaSuccess ||
+                        cudaMallocHost((void **)&m->h_rows_pinned,
+                                       (size_t)2 * c.n_layers * m->kvh * D * 4) != cudaSuccess ||
                         cudaMallocHost((void **)&m->h_state_pinned, 32) != cudaSuccess))
     rc = fail(B200_ENOMEM, "pinned host allocation failed");
   if (rc != B200_OK) {
@@ -813,6 +817,7 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
   cudaFree(m->ll_buf); cudaFree(m->d_trace);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
+  if (m->h_rows_pinned) cudaFreeHost(m->h_rows_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
   if (m->ev0) cudaEventDestroy(m->ev0);
   if (m->ev1) cudaEventDestroy(m->ev1);
@@ -1288,15 +1293,24 @@ int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   if (int rc = run_step(m)) return rc;
   B200_CUDA(cudaEventRecord(m->ev1, m->stream));
-  if (logits_host)
+  m->rows_fresh = false;
+  if (logits_host) {
     B200_CUDA(cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->cfg.vocab * 4,
                               cudaMemcpyDeviceToHost, m->stream));
+    // a caller that wants the logits on the host usually mirrors the new K/V rows too:
+    // they ride along, so that b200_model_read_new_kv_rows needs no second round trip
+    B200_CUDA(cudaMemcpyAsync(m->h_rows_pinned, m->kv_stage,
+                              (size_t)2 * m->cfg.n_layers * m->kvh * m->cfg.head_dim * 4,
+                              cudaMemcpyDeviceToHost, m->stream));
+  }
   B200_CUDA(cudaMemcpyAsync(m->h_state_pinned, m->d_state, 32, cudaMemcpyDeviceToHost, m->stream));
   B200_CUDA(cudaStreamSynchronize(m->stream));
   B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
   if (int rc = check_step_error(m)) return rc;
-  if (logits_host)
+  if (logits_host) {
     memcpy(logits_host, m->h_logits_pinned, (size_t)m->cfg.vocab * 4);
+    m->rows_fresh = true;
+  }
   if (next_token)
     *next_token = m->h_state_pinned[2];
   return B200_OK;
@@ -1312,6 +1326,7 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
       pos < 0 || pos + steps > m->cfg.max_len)
     return fail(B200_EINVAL, "generate: %d steps from position %d exceed max_len %d",
                 steps, pos, m->cfg.max_len);
+  m->rows_fresh = false;
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   for (int s = 0; s < steps; ++s)
@@ -1328,6 +1343,10 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
 int b200_model_read_new_kv_rows(b200_model *m, float *host) {
   if (!m || !host)
     return fail(B200_EINVAL, "read_new_kv_rows: null argument");
+  if (m->rows_fresh) {   // fetched with the last decode's logits
+    memcpy(host, m->h_rows_pinned, (size_t)2 * m->cfg.n_layers * m->kvh * m->cfg.head_dim * 4);
+    return B200_OK;
+  }
   B200_CUDA(cudaMemcpyAsync(host, m->kv_stage,
                             (size_t)2 * m->cfg.n_layers * m->kvh * m->cfg.head_dim * 4,
                             cudaMemcpyDeviceToHost, m->stream));
