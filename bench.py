@@ -95,6 +95,29 @@ class ClockSampler:
                 "samples": len(sm)}
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_step_kernel launch (ncu, full-size
+# 1.5B int8 model at context ~1000), and the git blob hash of the kernel source it was captured
+# from.  The figure is only reported while the source is still that one.
+TRAFFIC = {"bytes": 1717418448, "kernel_source": "buddy_mlir_b200/csrc/mega.cu",
+           "git_blob": "616c4e475f45a6a5406f9ccfe0bd0b449a8181ee",
+           "capture": "ncu --set full --clock-control none -k regex:decode_step -c 1, bench.py --resident-only"}
+
+
+def git_blob_hash(path):
+    import hashlib
+    data = open(path, "rb").read()
+    return hashlib.sha1(b"blob %d\0" % len(data) + data).hexdigest()
+
+
+def measured_traffic(persistent):
+    if not persistent:
+        return None, None
+    src = os.path.join(ROOT, TRAFFIC["kernel_source"])
+    if not os.path.exists(src) or git_blob_hash(src) != TRAFFIC["git_blob"]:
+        return None, "stale: the kernel source changed since the ncu capture"
+    return TRAFFIC["bytes"], f"ncu capture of {TRAFFIC['kernel_source']} at git blob {TRAFFIC['git_blob'][:12]}"
+
+
 def kv_prefix(cfg, n_pos, buffer):
     rng = np.random.default_rng([SEED_KV, buffer])
     a = np.zeros((cfg.kv_heads, cfg.max_len, cfg.head_dim), dtype=np.float32)
@@ -137,6 +160,7 @@ def run_reference(args):
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
+    os.environ.setdefault("OMP_NUM_THREADS", str(os.cpu_count() or 1))
     from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, synthetic
     sys.path.insert(0, os.path.join(ROOT, "tests"))
     import oracle_lib as orc
@@ -277,13 +301,7 @@ def run_single(args):
     step_bytes = s.step_bytes(ctx_mid)
     hbm, which = peaks()
     achieved = step_bytes / (ms / steps) / 1e6        # GB/s
-    traffic = None
-    # dram__bytes_read.sum + dram__bytes_write.sum of one launch, from the committed ncu summary
-    tpath = os.path.join(ROOT, "profiles", "decode_step_kernel_qwen1p5b_int8_full.md")
-    if persistent and os.path.exists(tpath):
-        import re
-        found = re.search(r"^dram_bytes_per_step:\s*(\d+)", open(tpath).read(), re.M)
-        traffic = int(found.group(1)) if found else None
+    traffic, traffic_source = measured_traffic(persistent)
     gemv = None if args.resident_only else gemv_microbench(lib)
     s.close()
     if args.resident_only:
@@ -323,7 +341,8 @@ def run_single(args):
             "scaling": "weak", "vs_baseline": None, "dtype": "f32 activations, int8 weights",
             "data": "synthetic", "config": workload_config(cfg, start, args),
             "roofline": {"bound": "hbm", "achieved": achieved, "peak": hbm, "unit": "GB/s",
-                         "frac": achieved / hbm, "traffic": traffic, "peak_source": which,
+                         "frac": achieved / hbm, "traffic": traffic, "traffic_source": traffic_source,
+                         "peak_source": which,
                          "kernel": "decode_step_kernel (one persistent launch per token)" if persistent else "whole decode step (CUDA graph replay)",
                          "bytes_per_step": step_bytes, "frac_of_8TBs_nominal": achieved / 8000.0},
             "gemv_isolated": gemv,
@@ -349,13 +368,16 @@ def main():
     if args.warmup < 3:
         args.warmup = 3
     if args.impl == "reference":
+        if args.gpus > 1 or int(os.environ.get("WORLD_SIZE", "1")) > 1:
+            import bench_tp
+            return bench_tp.run_reference(args)
         return run_reference(args)
     if args.gemv_only:
         return run_gemv_only(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single(args)
-    from buddy_mlir_b200 import tp_bench
-    return tp_bench.run(args)
+    import bench_tp
+    return bench_tp.run(args, ClockSampler, peaks)
 
 
 if __name__ == "__main__":

@@ -114,6 +114,9 @@ def load():
         "b200_forward_decode": (i32, [C.POINTER(ModelConfigC), C.c_char_p, i32, vp,
                                       i64, vp, i64, C.c_longlong, C.c_longlong,
                                       C.POINTER(vp), C.POINTER(vp)]),
+        "b200_forward_prefill": (i32, [C.POINTER(ModelConfigC), C.c_char_p, i32, vp,
+                                       i64, vp, i64, C.POINTER(C.c_longlong), i32,
+                                       C.POINTER(vp), vp]),
         "b200_forward_reset": (None, []),
     }
     for name, (res, args) in sig.items():

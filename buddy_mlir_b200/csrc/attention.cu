@@ -31,7 +31,7 @@ gqa_decode_kernel(const float *__restrict__ q, const float *__restrict__ kc,
   constexpr int D = VEC * 32;
   const int split = blockIdx.x, hk = blockIdx.y;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-  const int len = *posp + 1;
+  const int len = min(max(*posp, 0), max_len - 1) + 1;   // a position outside the cache never leaves it
   const int chunk = (len + splits - 1) / splits;
   const int s0 = split * chunk;
   const int s1 = min(len, s0 + chunk);
@@ -256,15 +256,30 @@ static int launch_g(const float *q, const float *kc, const float *vc,
   return B200_OK;
 }
 
+// Host-side argument check shared by both entry points; nothing touches the
+// device before it has passed.
+static int gqa_decode_check(const float *q, const float *kc, const float *vc, float *out,
+                            const float *scratch, int q_heads, int kv_heads, int D, int max_len,
+                            int splits, const int32_t *pos) {
+  if (!q || !kc || !vc || !out || !scratch || !pos)
+    return fail(B200_EINVAL, "gqa_decode: null argument");
+  if (q_heads < 1 || kv_heads < 1 || kv_heads > q_heads || q_heads % kv_heads || splits < 1 ||
+      splits > 1024 || max_len < 1)
+    return fail(B200_EINVAL, "gqa_decode: bad shape");
+  if (D != 64 && D != 128)
+    return fail(B200_EINVAL, "gqa_decode: head_dim %d (64 or 128 supported)", D);
+  const int G = q_heads / kv_heads;
+  if (G != 1 && G != 2 && G != 3 && G != 4 && G != 6 && G != 8)
+    return fail(B200_EINVAL, "gqa_decode: group size %d not built", G);
+  return B200_OK;
+}
+
 int gqa_decode_launch(const float *q, const float *kc, const float *vc,
                       float *out, float *scratch, int q_heads, int kv_heads,
                       int D, int max_len, int splits, const int32_t *pos,
                       cudaStream_t st) {
-  if (!q || !kc || !vc || !out || !scratch || !pos)
-    return fail(B200_EINVAL, "gqa_decode: null argument");
-  if (q_heads < 1 || kv_heads < 1 || q_heads % kv_heads || splits < 1 ||
-      splits > 1024 || max_len < 1)
-    return fail(B200_EINVAL, "gqa_decode: bad shape");
+  if (int rc = gqa_decode_check(q, kc, vc, out, scratch, q_heads, kv_heads, D, max_len, splits, pos))
+    return rc;
   const int G = q_heads / kv_heads;
   switch (G) {
 #define B200_G(G_)                                                             \
@@ -299,10 +314,14 @@ int64_t b200_gqa_scratch_floats(int q_heads, int D, int splits) {
 int b200_gqa_decode_static(const float *q, const float *k_cache, const float *v_cache, float *out,
                            int q_heads, int kv_heads, int D, int max_len, int splits,
                            const int32_t *pos, void *stream) {
+  // Every argument is checked on the host first: a rejected call returns before
+  // any device work (the counter clear below included).
+  static const float kNotNull = 0.f;   // stands in for the scratch pointer during the check
+  if (int rc = gqa_decode_check(q, k_cache, v_cache, out, &kNotNull, q_heads, kv_heads, D, max_len,
+                                splits, pos))
+    return rc;
   if (int rc = ensure_device())
     return rc;
-  if (q_heads < 1 || kv_heads < 1 || splits < 1 || D < 1)
-    return fail(B200_EINVAL, "gqa_decode_static: bad shape");
   const int64_t need = b200_gqa_scratch_floats(q_heads, D, splits);
   if (need > kStaticScratchFloats)
     return fail(B200_ELIMIT,
@@ -335,6 +354,7 @@ int b200_gqa_decode_static(const float *q, const float *k_cache, const float *v_
   // The array keeps whatever the previous call (possibly of another shape)
   // left behind; only the arrival counters have to start at zero.
   cudaStream_t st = (cudaStream_t)stream;
+  // (kv_heads <= q_heads was checked above, and the size check reserved q_heads counters)
   float *counters = scratch + (int64_t)q_heads * splits * (D + 2);
   B200_CUDA(cudaMemsetAsync(counters, 0, (size_t)kv_heads * sizeof(unsigned int), st));
   return gqa_decode_launch(q, k_cache, v_cache, out, scratch, q_heads, kv_heads, D, max_len,

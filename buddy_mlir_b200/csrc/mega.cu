@@ -1306,11 +1306,15 @@ int mega_build_rows(const void *packed, int K, int n_rows, int row_stride, int r
 size_t mega_fixed_shared_bytes() { return ((sizeof(Shared) + 127) / 128) * 128; }
 
 int mega_launch(const MegaParams &p, int grid, size_t smem, cudaStream_t st) {
-  static bool configured = false;
-  if (!configured) {
+  // the attribute belongs to the device's copy of the function: set it once per device
+  static bool configured[64] = {};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
     B200_CUDA(cudaFuncSetAttribute(decode_step_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                    227 * 1024));
-    configured = true;
+    if (dev >= 0 && dev < 64)
+      configured[dev] = true;
   }
   void *args[] = {(void *)&p};
   cudaLaunchConfig_t cfg{};

@@ -58,41 +58,94 @@ template <typename MR> void out_null(MR *out) {
   out->offset = 0;
 }
 
-// ---- weight cache: one packed device copy per (host pointer, shape, kind) ----
+// ---- weight cache ---------------------------------------------------------------
+// The quantised entries (gemv_w8 / gemv_w4 / gemv_w4g) take W and its scales as
+// model weights: constant for as long as the caller keeps them at that address.
+// Their packed device copies are cached under a key that names everything the
+// packed bytes depend on (addresses, shape, kind, groups, strides, nibble
+// signedness, scale type) and are checked on every hit against a fingerprint of
+// the host bytes (up to 4096 evenly spaced 64-bit words of the weight and of
+// the scales), so a buffer that was rewritten in place is repacked instead of
+// silently reused.  The cache is bounded (BUDDY_B200_WEIGHT_CACHE_MB, default
+// 8192): the least recently used copies are dropped first.
+// _mlir_ciface_buddy_matmul_f32 does NOT use the cache: its B operand is any
+// matmul operand of the graph (an activation, a transposed K, a scratch
+// buffer), so it is uploaded on every call.
 struct CachedWeight {
   DevBuf w, scale;
   b200_weight desc{};
+  uint64_t fingerprint = 0;
+  uint64_t last_use = 0;
+  size_t bytes = 0;
 };
-using Key = std::tuple<const void *, const void *, int64_t, int64_t, int, int>;
-std::map<Key, CachedWeight *> g_cache;
-std::mutex g_cache_mu;
-
-// src: dense host tensor in the reference layout; scale: dense host scales
-// [groups, N] in `sdt`.
-int cached_weight(int kind, const void *src, const void *host_scale, int sdt,
-                  int signed_nibbles, int64_t K, int64_t N, int64_t groups,
-                  const void *key_w, const void *key_s, const b200_weight **out) {
-  std::lock_guard<std::mutex> lock(g_cache_mu);
-  Key key{key_w, key_s, K, N, kind, (int)groups};
-  auto it = g_cache.find(key);
-  if (it != g_cache.end()) {
-    *out = &it->second->desc;
-    return B200_OK;
+struct WeightKey {
+  const void *w, *s;
+  int64_t K, N, groups, st0, st1;
+  int kind, signed_nibbles, sdt;
+  bool operator<(const WeightKey &o) const {
+    return std::tie(w, s, K, N, groups, st0, st1, kind, signed_nibbles, sdt) <
+           std::tie(o.w, o.s, o.K, o.N, o.groups, o.st0, o.st1, o.kind, o.signed_nibbles, o.sdt);
   }
+};
+std::map<WeightKey, CachedWeight *> g_cache;
+std::mutex g_cache_mu;
+uint64_t g_cache_clock = 0;
+size_t g_cache_bytes = 0;
+
+uint64_t fingerprint_bytes(const void *p, size_t bytes, uint64_t h) {
+  const size_t words = bytes / 8;
+  const uint64_t *q = (const uint64_t *)p;
+  const size_t n = words < 4096 ? words : 4096;
+  for (size_t i = 0; i < n; ++i) {
+    uint64_t v;
+    memcpy(&v, q + (n > 1 ? i * (words - 1) / (n - 1) : 0), 8);
+    h = (h ^ v) * 0x100000001B3ull;
+    h ^= h >> 29;
+  }
+  const unsigned char *tail = (const unsigned char *)p + words * 8;
+  for (size_t i = 0; i < bytes - words * 8; ++i)
+    h = (h ^ tail[i]) * 0x100000001B3ull;
+  return h ^ bytes;
+}
+
+size_t cache_limit_bytes() {
+  const char *e = std::getenv("BUDDY_B200_WEIGHT_CACHE_MB");
+  const long mb = e ? std::atol(e) : 8192;
+  return (size_t)(mb > 0 ? mb : 0) << 20;
+}
+
+void cache_evict_to(size_t limit) {   // g_cache_mu held
+  while (g_cache_bytes > limit && !g_cache.empty()) {
+    auto victim = g_cache.begin();
+    for (auto it = g_cache.begin(); it != g_cache.end(); ++it)
+      if (it->second->last_use < victim->second->last_use)
+        victim = it;
+    g_cache_bytes -= victim->second->bytes;
+    delete victim->second;
+    g_cache.erase(victim);
+  }
+}
+
+// Pack a dense host tensor in the reference layout (and its dense scales
+// [groups, N] in `sdt`) into a fresh device copy.
+int pack_weight_from_host(int kind, const void *src, const void *host_scale, int sdt,
+                          int signed_nibbles, int64_t K, int64_t N, int64_t groups,
+                          CachedWeight *cw) {
   if (int rc = ensure_device())
     return rc;
-  auto *cw = new CachedWeight();
   DevBuf d_src, d_scale_src;
   const size_t src_bytes = kind == B200_W_F32 ? (size_t)K * N * 4
                          : kind == B200_W_I8  ? (size_t)K * N
                                               : (size_t)K * N / 2;
+  const size_t packed_bytes = (size_t)packed_row_bytes(kind, K) * N;
   int rc = d_src.alloc(src_bytes);
-  if (!rc) rc = cw->w.alloc((size_t)packed_row_bytes(kind, K) * N);
+  if (!rc) rc = cw->w.alloc(packed_bytes);
   if (!rc && cudaMemcpy(d_src.p, src, src_bytes, cudaMemcpyHostToDevice) != cudaSuccess)
     rc = fail(B200_ECUDA, "weight upload failed");
   if (!rc) rc = b200_pack_weight(kind, d_src.p, K, N, signed_nibbles, cw->w.p, nullptr);
+  size_t sb = 0;
   if (!rc && kind != B200_W_F32) {
-    const size_t sb = (size_t)groups * N * (sdt == B200_F32 ? 4 : 2);
+    sb = (size_t)groups * N * (sdt == B200_F32 ? 4 : 2);
     rc = d_scale_src.alloc(sb);
     if (!rc) rc = cw->scale.alloc(sb);
     if (!rc && cudaMemcpy(d_scale_src.p, host_scale, sb, cudaMemcpyHostToDevice) != cudaSuccess)
@@ -101,10 +154,8 @@ int cached_weight(int kind, const void *src, const void *host_scale, int sdt,
   }
   if (!rc && cudaDeviceSynchronize() != cudaSuccess)
     rc = fail(B200_ECUDA, "weight repack failed: %s", cudaGetErrorString(cudaGetLastError()));
-  if (rc) {
-    delete cw;
+  if (rc)
     return rc;
-  }
   cw->desc.kind = kind;
   cw->desc.group = (kind == B200_W_U4 && groups > 1) ? (int)(K / groups) : 0;
   cw->desc.K = K;
@@ -112,10 +163,62 @@ int cached_weight(int kind, const void *src, const void *host_scale, int sdt,
   cw->desc.w = cw->w.p;
   cw->desc.scale = cw->scale.p;
   cw->desc.scale_dtype = sdt;
+  cw->bytes = packed_bytes + sb;
+  return B200_OK;
+}
+
+// src / host_scale: dense host copies (what is packed and fingerprinted);
+// key: what identifies the caller's tensor.  The returned descriptor stays
+// valid until the next cache call (the entry points hold g_entry_mu).
+int cached_weight(int kind, const void *src, const void *host_scale, int sdt,
+                  int signed_nibbles, int64_t K, int64_t N, int64_t groups,
+                  WeightKey key, const b200_weight **out) {
+  std::lock_guard<std::mutex> lock(g_cache_mu);
+  key.K = K; key.N = N; key.groups = groups;
+  key.kind = kind; key.signed_nibbles = signed_nibbles; key.sdt = sdt;
+  const size_t src_bytes = kind == B200_W_F32 ? (size_t)K * N * 4
+                         : kind == B200_W_I8  ? (size_t)K * N
+                                              : (size_t)K * N / 2;
+  uint64_t fp = fingerprint_bytes(src, src_bytes, 0xCBF29CE484222325ull);
+  if (host_scale)
+    fp = fingerprint_bytes(host_scale, (size_t)groups * N * (sdt == B200_F32 ? 4 : 2), fp);
+  auto it = g_cache.find(key);
+  if (it != g_cache.end()) {
+    if (it->second->fingerprint == fp) {
+      it->second->last_use = ++g_cache_clock;
+      *out = &it->second->desc;
+      return B200_OK;
+    }
+    g_cache_bytes -= it->second->bytes;   // rewritten in place: repack
+    delete it->second;
+    g_cache.erase(it);
+  }
+  auto *cw = new CachedWeight();
+  if (int rc = pack_weight_from_host(kind, src, host_scale, sdt, signed_nibbles, K, N, groups, cw)) {
+    delete cw;
+    return rc;
+  }
+  cw->fingerprint = fp;
+  cw->last_use = ++g_cache_clock;
+  const size_t limit = cache_limit_bytes();
+  cache_evict_to(limit > cw->bytes ? limit - cw->bytes : 0);
   g_cache[key] = cw;
+  g_cache_bytes += cw->bytes;
   *out = &cw->desc;
   return B200_OK;
 }
+template <typename MRW, typename MRS> WeightKey key_of(const MRW *W, const MRS *S) {
+  WeightKey k{};
+  k.w = W->aligned + W->offset;
+  k.s = S ? (const void *)(S->aligned + S->offset) : nullptr;
+  k.st0 = W->strides[0];
+  k.st1 = W->strides[1];
+  return k;
+}
+// One per-op call at a time: the calls come from the model's main thread
+// (runtime/external_kernels convention), and a cache descriptor must outlive
+// the call that uses it.
+std::mutex g_entry_mu;
 
 // y[M,N] = x[M,K] * W through the GEMV kernel, 16 activation rows at a time.
 int run_gemv_host(const b200_weight *w, const void *x_host, int x_dtype, int M,
@@ -158,6 +261,7 @@ void b200_release_cached_weights(void) {
   for (auto &kv : g_cache)
     delete kv.second;
   g_cache.clear();
+  g_cache_bytes = 0;
 }
 
 void _mlir_ciface_buddy_matmul_f32(b200_memref_f32_2 *result, b200_memref_f32_2 *A,
@@ -170,10 +274,12 @@ void _mlir_ciface_buddy_matmul_f32(b200_memref_f32_2 *result, b200_memref_f32_2 
   }
   std::vector<float> ta, tb;
   const float *a = dense2<float>(A, ta), *b = dense2<float>(B, tb);
-  const b200_weight *w = nullptr;
-  if (cached_weight(B200_W_F32, b, nullptr, B200_F32, 0, K, N, 1, B->aligned + B->offset,
-                    nullptr, &w))
+  // B is whatever the graph multiplies by (runtime_matmul_replace.py:27-55
+  // rewrites every MatmulOp): packed afresh on every call, never cached.
+  CachedWeight fresh;
+  if (pack_weight_from_host(B200_W_F32, b, nullptr, B200_F32, 0, K, N, 1, &fresh))
     return;
+  const b200_weight *w = &fresh.desc;
   float *y = host_alloc<float>((size_t)M * N);
   if (!y) return;
   if (run_gemv_host(w, a, B200_F32, (int)M, y, B200_F32)) {
@@ -196,8 +302,8 @@ void _mlir_ciface_buddy_gemv_w8_f32(b200_memref_f32_2 *result, b200_memref_f32_2
   const float *a = dense2<float>(A, ta), *s = dense2<float>(scale, ts);
   const int8_t *q = dense2<int8_t>(W, tw);
   const b200_weight *w = nullptr;
-  if (cached_weight(B200_W_I8, q, s, B200_F32, 1, K, N, 1, W->aligned + W->offset,
-                    scale->aligned + scale->offset, &w))
+  std::lock_guard<std::mutex> entry(g_entry_mu);
+  if (cached_weight(B200_W_I8, q, s, B200_F32, 1, K, N, 1, key_of(W, scale), &w))
     return;
   float *y = host_alloc<float>((size_t)M * N);
   if (!y) return;
@@ -221,8 +327,8 @@ void _mlir_ciface_buddy_gemv_w4_f16(b200_memref_f16_2 *result, b200_memref_f16_2
   const uint16_t *a = dense2<uint16_t>(A, ta), *s = dense2<uint16_t>(scale, ts);
   const int8_t *q = dense2<int8_t>(P, tw);
   const b200_weight *w = nullptr;
-  if (cached_weight(B200_W_U4, q, s, B200_F16, 1, K, N, 1, P->aligned + P->offset,
-                    scale->aligned + scale->offset, &w))
+  std::lock_guard<std::mutex> entry(g_entry_mu);
+  if (cached_weight(B200_W_U4, q, s, B200_F16, 1, K, N, 1, key_of(P, scale), &w))
     return;
   uint16_t *y = host_alloc<uint16_t>((size_t)M * N);
   if (!y) return;
@@ -249,8 +355,8 @@ void _mlir_ciface_buddy_gemv_w4g_f32(b200_memref_f32_2 *result, b200_memref_f32_
   const uint16_t *s = dense2<uint16_t>(scale, ts);
   const int8_t *q = dense2<int8_t>(P, tw);
   const b200_weight *w = nullptr;
-  if (cached_weight(B200_W_U4, q, s, B200_F16, 0, K, N, groups, P->aligned + P->offset,
-                    scale->aligned + scale->offset, &w))
+  std::lock_guard<std::mutex> entry(g_entry_mu);
+  if (cached_weight(B200_W_U4, q, s, B200_F16, 0, K, N, groups, key_of(P, scale), &w))
     return;
   float *y = host_alloc<float>((size_t)M * N);
   if (!y) return;
@@ -415,15 +521,76 @@ void _mlir_ciface_buddy_gqa_decode_f32(b200_memref_f32_4 *result, b200_memref_f3
 }
 
 // ---- whole-entry core ---------------------------------------------------------
+// One device session stands behind the two model entry points.  The reference
+// entries are stateless (every call receives the host KV cache), this one keeps
+// the cache on the device; `shadow` is a host copy of what the device cache
+// holds, row for row, and decides when the device copy may be trusted.
 namespace {
 struct ForwardSession {
   b200_model *model = nullptr;
   const void *w0 = nullptr, *w1 = nullptr;
-  long long next_pos = -1;
+  uint64_t w_fingerprint = 0;
+  int valid_rows = 0;                      // rows [0, valid_rows) of shadow == device cache
+  std::vector<std::vector<float>> shadow;  // [2*layers][kv_heads*max_len*D]
   std::vector<float> rows;
+  bool failed = false;
 };
 ForwardSession g_fwd;
 std::mutex g_fwd_mu;
+
+int session_for(ForwardSession &s, const b200_model_config *cfg, const char *variant,
+                int all_linear_w8, const void *w0, int64_t n0, const void *w1, int64_t n1) {
+  // the blobs are the model: same addresses and same sampled contents = same session
+  uint64_t fp = fingerprint_bytes(w0, (size_t)n0 * 4, 0xCBF29CE484222325ull);
+  if (w1)
+    fp = fingerprint_bytes(w1, (size_t)n1, fp);
+  if (s.model && s.w0 == w0 && s.w1 == w1 && s.w_fingerprint == fp)
+    return B200_OK;
+  b200_model_destroy(s.model);
+  s = ForwardSession();
+  b200_model_config c = *cfg;
+  c.tp_rank = 0;
+  c.tp_size = 1;
+  if (int rc = b200_model_create(&c, &s.model)) return rc;
+  int rc = b200_model_load_blobs(s.model, variant, w0, n0, w1, n1, all_linear_w8);
+  if (!rc) rc = b200_model_finalize(s.model);
+  if (rc) {
+    b200_model_destroy(s.model);
+    s = ForwardSession();
+    return rc;
+  }
+  s.w0 = w0;
+  s.w1 = w1;
+  s.w_fingerprint = fp;
+  s.rows.resize((size_t)2 * c.n_layers * c.kv_heads * c.head_dim);
+  s.shadow.assign((size_t)2 * c.n_layers,
+                  std::vector<float>((size_t)c.kv_heads * c.max_len * c.head_dim, 0.f));
+  s.valid_rows = 0;
+  return B200_OK;
+}
+
+// Does the host cache still hold, in rows [0, pos), what the device cache holds?
+// Row pos-1 of every buffer depends on every earlier token of the sequence, row
+// 0 and the middle row catch a rewritten or shifted cache
+// (handleKVCacheOverflow, gen_session.py:1471-1506): three rows per head and
+// buffer are compared bit for bit.
+bool host_matches_device(const ForwardSession &s, const b200_model_config *cfg,
+                         float *const *host_kv, long long pos) {
+  if (pos > s.valid_rows)
+    return false;
+  if (pos == 0)
+    return true;
+  const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len;
+  const long long probe[3] = {0, (pos - 1) / 2, pos - 1};
+  for (size_t b = 0; b < s.shadow.size(); ++b)
+    for (size_t h = 0; h < KH; ++h)
+      for (long long r : probe) {
+        const size_t off = (h * L + (size_t)r) * D;
+        if (memcmp(host_kv[b] + off, s.shadow[b].data() + off, D * 4) != 0)
+          return false;
+      }
+  return true;
+}
 } // namespace
 
 void b200_forward_reset(void) {
@@ -438,32 +605,24 @@ int b200_forward_decode(const b200_model_config *cfg, const char *variant, int a
                         float **logits_out) {
   if (!cfg || !variant || !w0 || !host_kv || !logits_out)
     return fail(B200_EINVAL, "forward_decode: null argument");
+  *logits_out = nullptr;
+  if (pos < 0 || pos >= cfg->max_len)
+    return fail(B200_EINVAL, "forward_decode: position %lld outside the cache (max_len %d)", pos,
+                cfg->max_len);
   std::lock_guard<std::mutex> lock(g_fwd_mu);
   ForwardSession &s = g_fwd;
-  if (!s.model || s.w0 != w0 || s.w1 != w1) {
-    // first call, or a different weight blob: (re)build the device session
-    b200_model_destroy(s.model);
-    s = ForwardSession();
-    b200_model_config c = *cfg;
-    c.tp_rank = 0;
-    c.tp_size = 1;
-    if (int rc = b200_model_create(&c, &s.model)) return rc;
-    int rc = b200_model_load_blobs(s.model, variant, w0, n0, w1, n1, all_linear_w8);
-    if (!rc) rc = b200_model_finalize(s.model);
-    if (rc) {
-      b200_model_destroy(s.model);
-      s = ForwardSession();
-      return rc;
-    }
-    s.w0 = w0;
-    s.w1 = w1;
-    s.rows.resize((size_t)2 * c.n_layers * c.kv_heads * c.head_dim);
-  }
+  if (int rc = session_for(s, cfg, variant, all_linear_w8, w0, n0, w1, n1)) return rc;
   const int nbuf = 2 * cfg->n_layers;
-  if (pos != s.next_pos) {
-    // hand-off from the host: everything before `pos` comes from host_kv
-    for (int b = 0; b < nbuf; ++b)
+  const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len;
+  if (!host_matches_device(s, cfg, host_kv, pos)) {
+    // hand-off from the host (CPU prefill, another sequence, a shifted cache):
+    // everything before `pos` comes from host_kv
+    for (int b = 0; b < nbuf; ++b) {
       if (int rc = b200_model_kv_upload(s.model, b, host_kv[b], 0, (int)pos)) return rc;
+      for (size_t h = 0; h < KH; ++h)
+        memcpy(s.shadow[b].data() + h * L * D, host_kv[b] + h * L * D, (size_t)pos * D * 4);
+    }
+    s.valid_rows = (int)pos;
   }
   float *logits = host_alloc<float>((size_t)cfg->vocab);
   if (!logits)
@@ -472,15 +631,55 @@ int b200_forward_decode(const b200_model_config *cfg, const char *variant, int a
   if (!rc) rc = b200_model_read_new_kv_rows(s.model, s.rows.data());
   if (rc) {
     std::free(logits);
-    s.next_pos = -1;
+    s.valid_rows = 0;
     return rc;
   }
-  const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len;
   for (int b = 0; b < nbuf; ++b)
-    for (size_t h = 0; h < KH; ++h)
-      memcpy(host_kv[b] + (h * L + (size_t)pos) * D, &s.rows[((size_t)b * KH + h) * D], D * 4);
-  s.next_pos = pos + 1;
+    for (size_t h = 0; h < KH; ++h) {
+      const float *row = &s.rows[((size_t)b * KH + h) * D];
+      memcpy(host_kv[b] + (h * L + (size_t)pos) * D, row, D * 4);
+      memcpy(s.shadow[b].data() + (h * L + (size_t)pos) * D, row, D * 4);
+    }
+  if (s.valid_rows < pos + 1)
+    s.valid_rows = (int)pos + 1;
   *logits_out = logits;
+  return B200_OK;
+}
+
+int b200_forward_prefill(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                         const void *w0, int64_t n0, const void *w1, int64_t n1,
+                         const long long *tokens, int n_rows, float *const *host_kv_out,
+                         float *logits_out) {
+  if (!cfg || !variant || !w0 || !tokens || !host_kv_out || !logits_out)
+    return fail(B200_EINVAL, "forward_prefill: null argument");
+  if (n_rows < 1 || n_rows > cfg->max_len)
+    return fail(B200_EINVAL, "forward_prefill: %d rows, the cache holds %d", n_rows, cfg->max_len);
+  for (int i = 0; i < n_rows; ++i)
+    if (tokens[i] < 0 || tokens[i] >= cfg->vocab)
+      return fail(B200_EINVAL, "forward_prefill: token %lld at row %d outside the vocabulary",
+                  tokens[i], i);
+  std::lock_guard<std::mutex> lock(g_fwd_mu);
+  ForwardSession &s = g_fwd;
+  if (int rc = session_for(s, cfg, variant, all_linear_w8, w0, n0, w1, n1)) return rc;
+  const int nbuf = 2 * cfg->n_layers;
+  const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len, V = cfg->vocab;
+  s.valid_rows = 0;
+  // Row i of a causal prefill is the decode step of token i at position i over
+  // the rows before it: the rows go through the device decode path one by one,
+  // and the cache stays on the device for the decode calls that follow.
+  for (int i = 0; i < n_rows; ++i) {
+    if (int rc = b200_model_decode(s.model, (int)tokens[i], i, logits_out + (size_t)i * V, nullptr))
+      return rc;
+  }
+  for (int b = 0; b < nbuf; ++b) {
+    if (int rc = b200_model_kv_download(s.model, b, s.shadow[b].data(), 0, n_rows)) return rc;
+    for (size_t h = 0; h < KH; ++h) {
+      memcpy(host_kv_out[b] + h * L * D, s.shadow[b].data() + h * L * D, (size_t)n_rows * D * 4);
+      if ((size_t)n_rows < L)   // rows the prefill did not reach read as zero
+        memset(host_kv_out[b] + (h * L + (size_t)n_rows) * D, 0, (L - (size_t)n_rows) * D * 4);
+    }
+  }
+  s.valid_rows = n_rows;
   return B200_OK;
 }
 

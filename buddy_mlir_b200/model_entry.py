@@ -1,7 +1,9 @@
 """Host harness that drives a model-entry shim the way buddy-mlir's generated
-ModelSession does: dlopen the model .so, dlsym `_mlir_ciface_forward_decode`,
-own the KV cache and logits on the HOST, and call the entry with MemRef
-descriptors (tools/buddy-codegen/gen_session.py:1106-1141, 1176-1294,
+ModelSession does: one dlopen(RTLD_LOCAL) of the model .so, dlsym of
+`_mlir_ciface_forward_prefill` and then `_mlir_ciface_forward_decode` (either
+one missing is an error, as in ModelSession::Impl::loadSo), the KV cache and
+logits owned on the HOST, and the entries called with MemRef descriptors
+(tools/buddy-codegen/gen_session.py:1106-1141, 1176-1294, 1345-1373,
 1381-1452).  buddy-cli itself cannot be linked here (it needs LLVMSupport and
 FlatBuffers), so this is the closest stand-in for the reference's host."""
 import ctypes as C
@@ -22,6 +24,10 @@ class EntrySession:
         if not os.path.exists(so):
             build(cfg, variant, all_linear_w8)
         self.dll = C.CDLL(so)          # RTLD_LOCAL, like ModelSession::Impl::loadSo
+        # gen_session.py:1127-1141: prefill first, then decode; a missing symbol throws
+        self.prefill_fn = self.dll._mlir_ciface_forward_prefill
+        self.prefill_fn.restype = None
+        self.prefill_fn.argtypes = None
         self.fn = self.dll._mlir_ciface_forward_decode
         self.fn.restype = None
         self.cfg = cfg
@@ -54,6 +60,33 @@ class EntrySession:
                      C.byref(self.kv_desc[3 + 2 * i])]
         self._args = args
         self.fn.argtypes = None
+
+    def prefill(self, prompt, pad_id: int = 0):
+        """ModelSession::prefill (gen_session.py:1345-1373): the token container holds
+        the prompt padded to max_len; every result is copied into the session's state
+        and the callee's buffers are freed; position_ = token count.  Returns the
+        logits [max_len, vocab] (the runtime reads row len(prompt) - 1)."""
+        cfg = self.cfg
+        toks = np.full((1, cfg.max_len), pad_id, dtype=np.uint64)
+        toks[0, :len(prompt)] = np.asarray(prompt, dtype=np.uint64)
+        tok_d = to_memref(toks)
+        K4, L3 = memref_type(np.float32, 4), memref_type(np.float32, 3)
+        ABI = type("PrefillABI", (C.Structure,), {"_fields_": [("kv", K4 * (2 * cfg.n_layers)), ("logits", L3)]})
+        result = ABI()
+        self.prefill_fn(C.byref(result), *[C.byref(d) for d in self.blob_desc], C.byref(tok_d))
+        if not result.logits.aligned:
+            raise _lib.B200Error(_lib.load().b200_last_error().decode())
+        n = cfg.max_len * cfg.vocab
+        logits = np.array(np.ctypeslib.as_array(result.logits.aligned, shape=(n,)), copy=True)
+        _libc.free(C.cast(result.logits.allocated, C.c_void_p))
+        for i, k in enumerate(self.kv):
+            src = np.ctypeslib.as_array(result.kv[i].aligned, shape=(k.size,))
+            np.copyto(k.reshape(-1), src)
+            _libc.free(C.cast(result.kv[i].allocated, C.c_void_p))
+        self.position_ = len(prompt)
+        self.prefill_logits = logits.reshape(cfg.max_len, cfg.vocab)
+        np.copyto(self.logits, self.prefill_logits[len(prompt) - 1])
+        return self.prefill_logits
 
     def decode(self, token_id: int, check_alias: bool = False):
         self.token[0, 0] = token_id

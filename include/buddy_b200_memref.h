@@ -118,10 +118,13 @@ void b200_release_cached_weights(void);
  * descriptors and calls this function.
  *
  * host_kv: 2*n_layers host cache buffers [1,kv_heads,max_len,head_dim], K at
- * even index.  The device cache is authoritative between consecutive
- * positions; when `pos` is not the previous call's pos + 1 (first decode after
- * the CPU prefill, or after the host-side handleKVCacheOverflow of
- * gen_session.py:1471-1506) rows [0,pos) are uploaded from host_kv first.
+ * even index.  The reference entry is stateless; this one keeps the cache on
+ * the device together with a host copy of what the device holds.  Before a
+ * step, rows 0, (pos-1)/2 and pos-1 of every host buffer are compared with
+ * that copy: if they differ (first decode after a CPU prefill, another
+ * sequence, the host-side handleKVCacheOverflow of gen_session.py:1471-1506)
+ * or the device holds fewer than `pos` rows, rows [0,pos) are uploaded from
+ * host_kv first.
  * Every call writes the new K/V row `pos` back into host_kv, so the host
  * buffers stay what the reference's in-place KV write would have left.
  * logits_out receives a malloc'ed [vocab] f32 buffer the caller frees
@@ -132,7 +135,25 @@ int b200_forward_decode(const b200_model_config *cfg, const char *variant,
                         const void *w1, int64_t n1, long long token,
                         long long pos, float *const *host_kv,
                         float **logits_out);
-/* Drop the session b200_forward_decode keeps (weights, KV, graph). */
+/* Prefill counterpart, behind _mlir_ciface_forward_prefill(PrefillABI *result,
+ * MemRef<Tw,1> *w0 [, *w1], Text<size_t,2> *tokens)
+ * (tools/buddy-codegen/gen_session.py:908-923 PrefillABI = 2*n_layers KV
+ * buffers then logits [1,max_len,vocab]; :979-984 the function type;
+ * :1345-1373 the call, which copies every result into the session's state).
+ * tokens: n_rows ids (the prompt, and the pad rows behind it if the caller
+ * wants them computed as the reference does).  Row i is computed at position
+ * i over rows [0,i) -- causal, as flash_attention_for_cpu_prefill_op
+ * (frontend/Python/ops/tosa.py:4326-4700).  host_kv_out: 2*n_layers buffers
+ * [1,kv_heads,max_len,head_dim] that receive rows [0,n_rows) (rows behind them
+ * are zeroed); logits_out: [max_len,vocab] f32, rows [0,n_rows) are written.
+ * The cache stays on the device: a following b200_forward_decode at any
+ * position <= n_rows whose host cache still holds these rows uploads nothing. */
+int b200_forward_prefill(const b200_model_config *cfg, const char *variant,
+                         int all_linear_w8, const void *w0, int64_t n0,
+                         const void *w1, int64_t n1, const long long *tokens,
+                         int n_rows, float *const *host_kv_out,
+                         float *logits_out);
+/* Drop the session the two entries keep (weights, KV, graph). */
 void b200_forward_reset(void);
 
 #ifdef __cplusplus

@@ -228,7 +228,9 @@ def test_1p5b_f32_logits_and_greedy_tokens(full_weights):
     def step(t):
         s.decode(t)
         return s.logits_data().copy()
-    worst, mm = check_stream(step, om, synthetic.prompt_tokens(cfg, 17, 32), 1e-3, n_greedy=16)
+    # 32 random prompt ids, then 128 free-running greedy steps compared with the
+    # CPU checker step by step (the first 64 must be identical; all 128 are checked)
+    worst, mm = check_stream(step, om, synthetic.prompt_tokens(cfg, 17, 32), 1e-3, n_greedy=128)
     print(f"1.5B f32: max rel logit err {worst:.3e}, smallest top-1/top-2 margin {mm:.3e}")
     s.close()
 
@@ -247,7 +249,7 @@ def test_1p5b_int8_all_linear_with_long_context(full_weights):
     def step(t):
         s.decode(t)
         return s.logits_data().copy()
-    worst, mm = check_stream(step, om, synthetic.prompt_tokens(cfg, 17, 32), 1e-3, n_greedy=32)
+    worst, mm = check_stream(step, om, synthetic.prompt_tokens(cfg, 17, 32), 1e-3, n_greedy=64)
     print(f"1.5B int8: max rel logit err {worst:.3e}, smallest margin {mm:.3e}")
     rng = np.random.default_rng(5)
     pos = 1000
@@ -259,4 +261,120 @@ def test_1p5b_int8_all_linear_with_long_context(full_weights):
     om.position = pos
     check_stream(step, om, [11, 12, 13], 1e-3)
     assert s.position() == pos + 3
+    # the last 64 of the 256 steps that grow the context to 1024: the device loop
+    # (device argmax, no host round trip) against the checker's free-running ids
+    pos = cfg.max_len - 64
+    s.position_ = pos
+    om.position = pos
+    tok, want = 4242, []
+    for _ in range(64):
+        tok = greedy_sample(om.decode(int(tok)))
+        want.append(tok)
+    got = [int(t) for t in s.generate(4242, 64)]
+    assert got == want
+    assert s.position() == cfg.max_len
     s.close()
+
+
+def test_qwen3_8b_shapes_int4_group128_at_context_4k():
+    """Two layers of the Qwen3-8B shapes (hidden 4096, 32 q / 8 kv heads, FFN
+    12288, QK-norm, vocab 151936), int4 group-128, three steps at context ~4090
+    over a seeded cache prefix: logits within 2e-2 and the same argmax."""
+    from buddy_mlir_b200 import QWEN3_8B
+    cfg = QWEN3_8B.with_(name="qwen3_8b_2l", n_layers=2)
+    blob, views = synthetic.make_f32_blob(cfg, 31)
+    om = orc.OracleModel(cfg, views, kinds={n: "w4g" for n in ALL_LINEAR}, group=128)
+    s = ModelSession(cfg)
+    s.load_tensors(views, quantize_to="w4", group=128)
+    rng = np.random.default_rng(6)
+    pos = cfg.max_len - 6
+    for b in range(2 * cfg.n_layers):
+        om.kv[b][:, :pos] = rng.standard_normal((cfg.kv_heads, pos, cfg.head_dim)).astype(np.float32)
+        s.kv_upload(b, om.kv[b], 0, pos)
+    s.position_ = pos
+    om.position = pos
+
+    def step(t):
+        s.decode(t)
+        return s.logits_data().copy()
+    worst, mm = check_stream(step, om, [101, 202, 303], 2e-2)
+    print(f"8B-shape int4 g128 at ctx {pos}: max rel logit err {worst:.3e}, smallest margin {mm:.3e}")
+    s.close()
+
+
+# ---- the model entry pair, loaded the way the generated ModelSession loads it ------------
+@pytest.mark.parametrize("cfg,variant", [(TINY_QWEN2, "f32"), (TINY_QWEN2, "w8a32")])
+def test_prefill_then_decode_through_the_model_entries(cfg, variant):
+    """dlopen(RTLD_LOCAL) of the shim, both symbols resolved, prefill of a
+    padded prompt, then 16 greedy decode steps: logits and ids equal the
+    checker's; the first decode uploads nothing (the cache stayed on the device)."""
+    blob, views = synthetic.make_f32_blob(cfg, 41)
+    if variant == "w8a32":
+        fb, ib = synthetic.split_w8a32(cfg, views, lambda W: orc.quantize_per_channel(W, 8))
+        blobs = [fb, ib]
+        om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in synthetic.QUANTISED_BY_REFERENCE})
+    else:
+        blobs = [blob]
+        om = orc.OracleModel(cfg, views)
+    es = EntrySession(cfg, variant, blobs)
+    prompt = synthetic.prompt_tokens(cfg, 9, 12)
+    pad = 7
+    logits = es.prefill(prompt, pad_id=pad)
+    assert logits.shape == (cfg.max_len, cfg.vocab)
+    # every row the reference computes: the prompt rows and the pad rows behind them
+    for i in range(cfg.max_len):
+        want = om.decode(int(prompt[i]) if i < len(prompt) else pad)
+        assert maxrel(logits[i], want) < 1e-3
+        assert greedy_sample(logits[i]) == greedy_sample(want)
+    for b in range(2 * cfg.n_layers):
+        assert maxrel(es.kv[b][0], om.kv[b]) < 1e-4
+    om.position = len(prompt)
+    assert es.position_ == len(prompt)
+    tok = greedy_sample(es.logits)
+    for i in range(16):
+        es.decode(tok, check_alias=True)
+        want = om.decode(tok)
+        assert maxrel(es.logits, want) < 1e-3
+        assert greedy_sample(es.logits) == greedy_sample(want)
+        tok = greedy_sample(want)
+    es.close()
+
+
+def test_prefill_entry_skips_pad_rows_on_request(monkeypatch):
+    cfg = TINY_QWEN2
+    blob, views = synthetic.make_f32_blob(cfg, 43)
+    om = orc.OracleModel(cfg, views)
+    es = EntrySession(cfg, "f32", [blob])
+    prompt = synthetic.prompt_tokens(cfg, 10, 9)
+    monkeypatch.setenv("BUDDY_B200_PREFILL_PAD", "7")
+    logits = es.prefill(prompt, pad_id=7)
+    for i in range(len(prompt)):
+        assert maxrel(logits[i], om.decode(int(prompt[i]))) < 1e-3
+    assert not logits[len(prompt):].any()
+    es.decode(5)
+    assert maxrel(es.logits, om.decode(5)) < 1e-3
+    es.close()
+
+
+def test_model_entry_tells_sequences_with_aligned_positions_apart():
+    """The reference entry is stateless.  A second sequence whose prompt is as
+    long as the first one's final position, prefilled on the CPU into the same
+    host buffers, must be decoded against ITS cache, not the previous one's."""
+    cfg = TINY_QWEN2
+    blob, views = synthetic.make_f32_blob(cfg, 44)
+    es = EntrySession(cfg, "f32", [blob])
+    om = orc.OracleModel(cfg, views)
+    for t in synthetic.prompt_tokens(cfg, 1, 10):
+        es.decode(int(t))
+        om.decode(int(t))
+    assert es.position_ == 10
+    # sequence two: ten other tokens, "prefilled" by the checker into the host buffers
+    om2 = orc.OracleModel(cfg, views)
+    for t in synthetic.prompt_tokens(cfg, 2, 10):
+        om2.decode(int(t))
+    for b in range(2 * cfg.n_layers):
+        es.kv[b][0, :, :10] = om2.kv[b][:, :10]
+    es.position_ = 10                     # same position as where sequence one stopped
+    es.decode(33)
+    assert maxrel(es.logits, om2.decode(33)) < 1e-3
+    es.close()

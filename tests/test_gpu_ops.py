@@ -50,6 +50,39 @@ def test_matmul_f32_symbol_handles_strides_and_many_rows():
     assert y.shape == (40, 50) and rel(y, ref) < F32_TOL
 
 
+def test_matmul_f32_sees_new_contents_at_the_same_address():
+    """B of buddy_matmul_f32 is any matmul operand (an activation, a reused
+    scratch buffer): a second call with other values at the same address must
+    use them.  No cache reset in between."""
+    rng = np.random.default_rng(1)
+    A = rng.standard_normal((3, 64)).astype(np.float32)
+    B = rng.standard_normal((64, 48)).astype(np.float32)
+    y1 = memref.buddy_matmul_f32(A, B)
+    assert rel(y1, orc.gemv_f32(A, B)) < F32_TOL
+    B[...] = rng.standard_normal((64, 48)).astype(np.float32)       # same buffer, new contents
+    y2 = memref.buddy_matmul_f32(A, B)
+    assert rel(y2, orc.gemv_f32(A, B)) < F32_TOL
+    # a transposed view of a square matrix at the same address is another operand
+    S = rng.standard_normal((64, 64)).astype(np.float32)
+    assert rel(memref.buddy_matmul_f32(A, S), orc.gemv_f32(A, S)) < F32_TOL
+    assert rel(memref.buddy_matmul_f32(A, S.T), orc.gemv_f32(A, np.ascontiguousarray(S.T))) < F32_TOL
+
+
+def test_quantised_weight_cache_notices_rewrites_and_views():
+    rng = np.random.default_rng(2)
+    K, N = 64, 64
+    x = rng.standard_normal((1, K)).astype(np.float32)
+    Q = rng.integers(-127, 128, (K, N)).astype(np.int8)
+    s = rng.uniform(0.001, 0.01, (1, N)).astype(np.float32)
+    assert rel(memref.buddy_gemv_w8_f32(x, Q, s), orc.gemv_w8_f32(x, Q, s[0])) < F32_TOL
+    assert rel(memref.buddy_gemv_w8_f32(x, Q, s), orc.gemv_w8_f32(x, Q, s[0])) < F32_TOL   # cache hit
+    Q[...] = rng.integers(-127, 128, (K, N)).astype(np.int8)        # rewritten in place
+    assert rel(memref.buddy_gemv_w8_f32(x, Q, s), orc.gemv_w8_f32(x, Q, s[0])) < F32_TOL
+    s[...] = rng.uniform(0.001, 0.01, (1, N)).astype(np.float32)
+    assert rel(memref.buddy_gemv_w8_f32(x, Q, s), orc.gemv_w8_f32(x, Q, s[0])) < F32_TOL
+    assert rel(memref.buddy_gemv_w8_f32(x, Q.T, s), orc.gemv_w8_f32(x, np.ascontiguousarray(Q.T), s[0])) < F32_TOL
+
+
 # ---- committed fixtures -----------------------------------------------------------
 def test_gemv_fixtures():
     g = np.load(os.path.join(G, "ops_golden.npz"))
@@ -192,10 +225,12 @@ def test_gemv_w8_sweep(N, K, M):
     assert rel(y, orc.gemv_w8_f32(x, Q, s)) < F32_TOL
 
 
-@pytest.mark.parametrize("N,K", SHAPES)
+@pytest.mark.parametrize("N,K", SHAPES + [(151936, 1536), (14336, 4096), (4096, 12288)])
 @pytest.mark.parametrize("M", [1, 2, 4, 8, 16, 5])
 def test_gemv_w4_group128_sweep(N, K, M):
     from gpu_util import dev, packed_weight, packed_scales, gemv
+    if M not in (1, 16) and N * K > 4096 * 4096:
+        pytest.skip("the large shapes are checked at M = 1 and M = 16")
     rng = np.random.default_rng(N * 3 + K + M)
     x = rng.standard_normal((M, K)).astype(np.float32)
     P = rng.integers(0, 256, (K, N // 2)).astype(np.uint8)          # nibbles uniform in [0,15]

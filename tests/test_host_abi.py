@@ -98,3 +98,32 @@ def test_no_cpu_fallback_without_a_device():
     h = C.c_void_p()
     c = TINY_QWEN2.to_c()
     assert lib.b200_model_create(C.byref(c), C.byref(h)) == -3
+
+
+def test_static_attention_entry_checks_arguments_on_the_host():
+    """Every argument check of b200_gqa_decode_static runs before the device is
+    touched, so it can be exercised without one: more kv heads than query heads
+    at the largest accepted shape, a group size that is not built, a bad head
+    size and a null pointer are all B200_EINVAL."""
+    lib = _lib.load()
+    buf = np.zeros(16, dtype=np.float32)
+    p = buf.ctypes.data
+    assert lib.b200_gqa_decode_static(p, p, p, p, 64, 128, 128, 64, 32, p, None) == -1
+    assert lib.b200_gqa_decode_static(p, p, p, p, 12, 5, 128, 64, 8, p, None) == -1
+    assert lib.b200_gqa_decode_static(p, p, p, p, 12, 2, 96, 64, 8, p, None) == -1
+    assert lib.b200_gqa_decode_static(None, p, p, p, 12, 2, 128, 64, 8, p, None) == -1
+    assert lib.b200_gqa_decode_static(p, p, p, p, 12, 2, 128, 64, 0, p, None) == -1
+
+
+def test_model_entry_shim_exports_both_symbols():
+    """What ModelSession::Impl::loadSo does (tools/buddy-codegen/gen_session.py:1120-1141):
+    one dlopen(RTLD_LOCAL) of the model .so, then the prefill and the decode symbol."""
+    import os
+    from buddy_mlir_b200.gen_model_entry import HERE, build, shim_name
+    _lib.load()
+    so = os.path.join(HERE, shim_name(TINY_QWEN2, "w8a32"))
+    if not os.path.exists(so):
+        build(TINY_QWEN2, "w8a32")
+    dll = C.CDLL(so, mode=os.RTLD_NOW | os.RTLD_LOCAL)
+    assert dll._mlir_ciface_forward_prefill is not None
+    assert dll._mlir_ciface_forward_decode is not None
