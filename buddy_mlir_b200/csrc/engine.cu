@@ -456,7 +456,7 @@ bool mega_eligible(const b200_model *m, const Layer &L0) {
   if (G != 1 && G != 2 && G != 4 && G != 6 && G != 8)
     return false;
   auto ok = [](const DevLinear &l) {
-    return l.set && l.w.kind == B200_W_I8 && l.w.scale_dtype == B200_F32 && l.w.K % 64 == 0 &&
+    return l.set && l.w.kind == B200_W_I8 && l.w.scale_dtype == B200_F32 && l.w.K % 16 == 0 &&
            l.w.K <= 12288;
   };
   for (const auto &L : m->layers)
@@ -486,58 +486,45 @@ int build_mega(b200_model *m) {
   const int H = c.hidden, QD = c.q_heads * D, KD = c.kv_heads * D, F = c.ffn, V = c.vocab;
   MegaParams &p = m->mp;
   const int Ks[5] = {H, QD, H, F, H}, Ns[5] = {QD + 2 * KD, H, 2 * F, H, V};
-  // the activation vector of a projection is staged from registers: 2 * 512 * 10 values at most;
-  // K is cut into 64-byte chunks
-  int Kmax = 0;
-  for (int i = 0; i < 5; ++i) {
-    if (Ks[i] % 64 != 0 || Ks[i] > 10240)
-      return B200_OK;
-    if (Ks[i] > Kmax) Kmax = Ks[i];
-  }
-  if (H > 1536 || QD > 1536)
+  if (H > 1536 || QD > 1536 || H % 16 != 0 || QD % 16 != 0 || F % 16 != 0)
     return B200_OK;
   int slot_bytes = 0;
   for (int i = 0; i < 5; ++i) {
+    if (i == 3)
+      continue;
     MegaPhase &ph = p.phase[i];
     ph.K = Ks[i];
     ph.N = Ns[i];
+    ph.row_bytes = Ks[i] + kMegaTrailer;
+    ph.mode = 0;
     ph.unit = i == 2 ? 2 : 1;
-    // stages: a block of 8 rows x at most 1536 bytes of k (the ring slot); a stage is shared by
-    // as many warps as keep about 16 pieces of work (one per warp) in a CTA's share
-    const int rows_per_cta = (Ns[i] / ph.unit + grid - 1) / grid * ph.unit;
-    const int nrb = (rows_per_cta + kMegaBlockRows - 1) / kMegaBlockRows;
-    const int chunks = Ks[i] / 64;
-    int nks = chunks;
-    for (int d = chunks; d >= 1; --d)
-      if (chunks % d == 0 && chunks / d <= 24)
-        nks = d;
-    const int per_stage = chunks / nks;
-    int nkw = 1;
-    for (int d = 1; d <= per_stage; ++d)
-      if (per_stage % d == 0 && nrb * nks * d <= 16 && per_stage / d >= 2)
-        nkw = d;
-    if (nks * nkw > 1 && nrb > kMegaAccBlocks) {
-      if (nks > 1)
-        return B200_OK;
-      nkw = 1;
+    ph.rps = 16;   // a stage is 16 rows: 16 warps x 1 row, 4 x 4 or 2 x 8
+    if (ph.rps * ph.row_bytes > slot_bytes)
+      slot_bytes = ph.rps * ph.row_bytes;
+  }
+  {
+    // down projection: long rows, a few per stage, one warp per row
+    MegaPhase &ph = p.phase[3];
+    ph.K = F;
+    ph.N = H;
+    ph.row_bytes = F + kMegaTrailer;
+    ph.mode = 0;
+    ph.unit = 1;
+    ph.rps = slot_bytes / ph.row_bytes;
+    if (ph.rps > 8) ph.rps = 8;
+    if (ph.rps < 1 || (ph.rps & (ph.rps - 1)) != 0) {   // 1, 2, 4 or 8 rows: the warps split evenly over stages
+      if (ph.rps >= 4) ph.rps = 4;
+      else if (ph.rps >= 2) ph.rps = 2;
+      else if (ph.rps < 1) return B200_OK;
     }
-    ph.nks = nks;
-    ph.nkw = nkw;
-    ph.slice_bytes = Ks[i] / nks;
-    ph.swizzle = (ph.slice_bytes % 128 == 0) ? 4 : 0;
-    const int sb = kMegaBlockRows * (ph.slice_bytes + kMegaTrailer);
-    if (sb > slot_bytes) slot_bytes = sb;
   }
   slot_bytes = (slot_bytes + 127) / 128 * 128;
-  // scratch: the three activation planes (stride = 64 mod 128 bytes: planes 0 and 1 then sit in
-  // different shared-memory banks), or the attention staging (q | k | v + the states of the 7
-  // scanning warps; m, l and weights of the split fold)
-  const int plane_stride = (Kmax + 127) / 128 * 128 + 64;
-  int xs_bytes = 3 * plane_stride;
-  if (xs_bytes < (G + 2 + 7 * G) * D * 4) xs_bytes = (G + 2 + 7 * G) * D * 4;
-  if (xs_bytes < (3 * G * splits + 8) * 4) xs_bytes = (3 * G * splits + 8) * 4;
-  xs_bytes = (xs_bytes + 127) / 128 * 128;
-  const size_t fixed = mega_fixed_shared_bytes() + (size_t)xs_bytes;
+  int xs_floats = H > QD ? H : QD;                          // staged activations of a projection
+  if (xs_floats < F) xs_floats = F;
+  if (xs_floats < (G + 2 + 7 * G) * D) xs_floats = (G + 2 + 7 * G) * D;   // staged q | k | v + states of the 7 scanning warps
+  if (xs_floats < 3 * G * splits + 8) xs_floats = 3 * G * splits + 8;   // split fold: m, l, weights
+  xs_floats = (xs_floats + 31) / 32 * 32;
+  const size_t fixed = mega_fixed_shared_bytes() + (size_t)xs_floats * 4;
   int slots = (int)((227 * 1024 - (long)fixed) / slot_bytes);
   if (slots > kMegaMaxSlots) slots = kMegaMaxSlots;
   if (slots < 4)
@@ -547,10 +534,7 @@ int build_mega(b200_model *m) {
     for (int i = 0; i < 4; ++i) {
       int b, n;
       rows_of_host(p.phase[i].N / p.phase[i].unit, cta, grid, b, n);
-      const int nrb = (n * p.phase[i].unit + kMegaBlockRows - 1) / kMegaBlockRows;
-      if (p.phase[i].nks * p.phase[i].nkw > 1 && nrb > kMegaAccBlocks)
-        return B200_OK;
-      per_layer += nrb * p.phase[i].nks;
+      per_layer += (n * p.phase[i].unit + p.phase[i].rps - 1) / p.phase[i].rps;
     }
     if (per_layer > kMegaMaxLayerStages)
       return B200_OK;
@@ -566,7 +550,7 @@ int build_mega(b200_model *m) {
       int b, n;
       rows_of_host(ph.N / ph.unit, cta, grid, b, n);
       table[(size_t)i * grid + cta] = total;
-      total += mega_rows_bytes(ph, n * ph.unit);
+      total += (int64_t)n * ph.unit * ph.row_bytes;
     }
   }
   if (int rc = dev_alloc((void **)&m->mega_stream, total)) return rc;
@@ -576,25 +560,26 @@ int build_mega(b200_model *m) {
   for (int l = 0; l < L; ++l) {
     Layer &Ly = m->layers[l];
     const int64_t *o0 = m->mega_offsets + (size_t)(4 * l) * grid;
-    if (int rc = mega_build_rows(Ly.qkv.w_buf, H, Ns[0], 1, 0, Ns[0], p.phase[0], (const float *)Ly.qkv.scale_buf,
-                                 Ly.qkv.bias_buf, grid, o0, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.qkv.w_buf, H, Ns[0], 1, 0, Ns[0], 1, (const float *)Ly.qkv.scale_buf,
+                                 Ly.qkv.bias_buf, grid, p.phase[0].row_bytes, o0, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_rows(Ly.o.w_buf, QD, H, 1, 0, H, p.phase[1], (const float *)Ly.o.scale_buf, nullptr,
-                                 grid, o0 + grid, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.o.w_buf, QD, H, 1, 0, H, 1, (const float *)Ly.o.scale_buf, nullptr,
+                                 grid, p.phase[1].row_bytes, o0 + grid, m->mega_stream, st))
       return rc;
-    // gate_j -> row 2j, up_j -> row 2j+1: one lane pair then holds the two halves of a SiLU gate
-    if (int rc = mega_build_rows(Ly.gate.w_buf, H, F, 2, 0, 2 * F, p.phase[2], (const float *)Ly.gate.scale_buf,
-                                 nullptr, grid, o0 + 2 * grid, m->mega_stream, st))
+    // gate_j -> row 2j, up_j -> row 2j+1: one warp then holds the pair of a SiLU gate
+    if (int rc = mega_build_rows(Ly.gate.w_buf, H, F, 2, 0, 2 * F, 2, (const float *)Ly.gate.scale_buf,
+                                 nullptr, grid, p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_rows(Ly.up.w_buf, H, F, 2, 1, 2 * F, p.phase[2], (const float *)Ly.up.scale_buf, nullptr,
-                                 grid, o0 + 2 * grid, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.up.w_buf, H, F, 2, 1, 2 * F, 2, (const float *)Ly.up.scale_buf, nullptr,
+                                 grid, p.phase[2].row_bytes, o0 + 2 * grid, m->mega_stream, st))
       return rc;
-    if (int rc = mega_build_rows(Ly.down.w_buf, F, H, 1, 0, H, p.phase[3], (const float *)Ly.down.scale_buf, nullptr,
-                                 grid, o0 + 3 * grid, m->mega_stream, st))
+    if (int rc = mega_build_rows(Ly.down.w_buf, F, H, 1, 0, H, 1, (const float *)Ly.down.scale_buf, nullptr,
+                                 grid, p.phase[3].row_bytes, o0 + 3 * grid, m->mega_stream, st))
       return rc;
   }
-  if (int rc = mega_build_rows(m->lm_head.w_buf, H, V, 1, 0, V, p.phase[4], (const float *)m->lm_head.scale_buf,
-                               nullptr, grid, m->mega_offsets + (size_t)(4 * L) * grid, m->mega_stream, st))
+  if (int rc = mega_build_rows(m->lm_head.w_buf, H, V, 1, 0, V, 1, (const float *)m->lm_head.scale_buf,
+                               nullptr, grid, p.phase[4].row_bytes,
+                               m->mega_offsets + (size_t)(4 * L) * grid, m->mega_stream, st))
     return rc;
   std::vector<const float *> lvec(4 * L);
   for (int l = 0; l < L; ++l) {
@@ -628,8 +613,7 @@ int build_mega(b200_model *m) {
   p.splits = splits;
   p.slots = slots;
   p.slot_bytes = slot_bytes;
-  p.xs_bytes = xs_bytes;
-  p.plane_stride = plane_stride;
+  p.xs_floats = xs_floats;
   p.eps = c.eps;
   p.embed = m->embed; p.inv_freq = m->inv_freq; p.final_norm = m->final_norm;
   p.lvec = m->lvec_dev;

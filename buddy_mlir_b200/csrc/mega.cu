@@ -7,35 +7,25 @@
 //
 //  * Weights.  Each CTA owns a fixed slice of the output rows of every
 //    projection, and ALL weight bytes that CTA will ever need are laid out back
-//    to back in one private stream (built once at load time) as ring stages:
-//    a stage is a block of 16 rows x one K slice, followed by the rows' trailers
-//    (scale, bias, sum of the row's weights).  The stream is pulled with bulk
-//    async copies (cp.async.bulk, completion on mbarriers) into a ring of
-//    shared-memory slots; every warp works on whole stages and refills the slot
-//    it has just finished with the stage one ring-length ahead.  Refills never
+//    to back in one private stream (built once at load time).  The stream is
+//    pulled with bulk async copies (cp.async.bulk, completion on mbarriers)
+//    into a ring of shared-memory slots; the warp that finishes a slot last
+//    immediately refills it with the stage one ring-length ahead.  Refills never
 //    wait for activations, so HBM stays busy across the dependency points of
-//    the graph (the ring holds about half a layer's worth of weights).
+//    the graph (the ring holds about one projection's worth of weights).
 //  * Activations.  There is no grid-wide barrier.  Every activation vector
 //    that crosses CTAs (q|k|v, attention output, the two residual streams, the
 //    SiLU-gated MLP intermediate, attention split partials, argmax candidates)
 //    is stored as 8-byte (value, tag) pairs written with one 64-bit store; the
 //    tag names launch, layer and producer phase.  A consumer simply loads the
 //    pairs it needs and retries until the tags match: data arrival IS the
-//    synchronisation, and CTAs drift apart by at most one phase because every
-//    phase needs all outputs of the one before.  Buffers alternate by layer
-//    parity, so a producer can never overwrite a value a slower CTA still has
-//    to read.
-//  * Math.  The activation vector of a projection is turned, once per phase,
-//    into a 23-bit fixed-point number per element (one power-of-two scale per
-//    vector, taken from its largest magnitude) and stored as three int8 planes
-//    (high, middle, low byte).  The dot products with the int8 weights are
-//    then integer tensor-core instructions (mma.sync m16n8k32 s8: sixteen
-//    weight rows are the rows of A, the three planes are three columns of B), so
-//    one instruction handles 16 rows x 32 k, the accumulation is exact, and
-//    the per-plane sums are recombined in 64-bit integers before the single
-//    conversion to float.  Because integer sums do not depend on their order,
-//    K can be cut over warps freely (shared-memory atomics) and the result is
-//    bit-identical for every schedule.
+//    synchronisation (no fence, no counter, no barrier), and CTAs drift apart
+//    by at most one phase because every phase needs all outputs of the one
+//    before.  Buffers alternate by layer parity, so a producer can never
+//    overwrite a value a slower CTA still has to read.
+//  * Math.  Sixteen warps dequantise from shared memory with the activations
+//    in registers and meet in warp-shuffle reductions; groups of warps work on
+//    different ring slots at the same time.
 //
 // Every wait (mbarrier or tag poll) is bounded: on expiry the kernel records an
 // error code, all later waits fall through, control flow stays identical (so
@@ -44,8 +34,7 @@
 // Arithmetic is that of examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir
 // :46-260 with the int8 GEMV of
 // midend/lib/Conversion/MatMulOptimization/DequantMatMulVectorizationDecode.cpp:250-321
-// (sum over k of x*q, then the per-channel scale) and the attention recurrence
-// of frontend/Python/ops/tosa.py:14245-14594.
+// and the attention recurrence of frontend/Python/ops/tosa.py:14245-14594.
 #include "common.cuh"
 #include "mega.cuh"
 
@@ -58,7 +47,6 @@ namespace {
 constexpr int kCW = 16;           // warps (all of them consume)
 constexpr int kCT = kCW * 32;     // threads
 constexpr int kAW = 7;            // warps that scan the KV cache in the attention phase
-constexpr int kMaxV = 10;         // (value, value) vectors per thread: K <= 2 * 512 * 10
 constexpr uint32_t kSpinLimit = 1u << 26;      // poll count bound, and
 constexpr unsigned long long kWaitNs = 1000000000ull;  // wall-time bound (1 s) of any single wait
 __device__ __forceinline__ unsigned long long now_ns() {
@@ -131,19 +119,6 @@ __device__ __forceinline__ void consumer_sync() {
 __device__ __forceinline__ float4 ldcg4(const float *p) {
   return __ldcg(reinterpret_cast<const float4 *>(p));
 }
-__device__ __forceinline__ uint4 lds128(uint32_t addr) {
-  uint4 v;
-  asm volatile("ld.shared.v4.u32 {%0,%1,%2,%3}, [%4];" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "r"(addr));
-  return v;
-}
-// D (16x8, s32) += A (16x32, s8, row) * B (32x8, s8, col)
-__device__ __forceinline__ void mma_s8(int (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3,
-                                       uint32_t b0, uint32_t b1) {
-  asm volatile(
-      "mma.sync.aligned.m16n8k32.row.col.s32.s8.s8.s32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};"
-      : "+r"(d[0]), "+r"(d[1]), "+r"(d[2]), "+r"(d[3])
-      : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
-}
 
 // ---- tagged (value, tag) pairs ------------------------------------------------------
 __device__ __forceinline__ void ll_store(uint2 *p, float v, uint32_t tag) {
@@ -166,36 +141,28 @@ __device__ __forceinline__ uint4 ll_load2(const uint2 *p) {
   return v;
 }
 
-// One ring stage of this CTA's stream.
-struct StageRef {
-  uint32_t off;      // byte offset inside the layer's part of the stream (or the lm_head's)
-  uint32_t bytes;
-};
-
-// What this CTA does in one projection (fixed for the whole run).
-struct PhaseInfo {
-  int row_begin, nrows, nrb;   // first row, rows, row blocks of 8
-  int nstages;                 // ring stages = nrb * nks
-  int nunits;                  // pieces of work = nstages * nkw (one warp each)
-  int K, slice_bytes, nks, nkw, chunks, swizzle;   // chunks: 64-byte chunks of k per piece of work
-  int first_stage;             // index of the phase's first stage inside a layer (projections 0..3)
+// Where stage g of this CTA's stream lives: stages per projection, rows, bytes.
+struct StreamPlan {
+  int n[5];            // stages of projection p in one layer (p = 4: lm_head)
+  int rows[5];         // rows of projection p owned by this CTA
+  int rps[5], row_bytes[5];
+  long long off[5];    // byte offset of projection p inside a layer's part of the stream
+  long long layer_bytes;
+  int per_layer;       // stages per layer
+  int total;           // stages per token
+  int L;
+  uint2 tab[kMegaMaxLayerStages];   // stage r of a layer: (byte offset inside the layer's part, bytes)
+  int next_l[kMegaMaxSlots], next_r[kMegaMaxSlots];   // per ring slot: the stage it receives next
 };
 
 struct Shared {
   uint64_t full[kMegaMaxSlots];
+  int done[kMegaMaxSlots];              // warps that finished the slot's current stage
   int issued[kMegaMaxSlots];            // stage last requested into the slot
-  int done[kMegaMaxSlots];              // warps that finished their piece of the slot's current stage
-  int next_l[kMegaMaxSlots], next_r[kMegaMaxSlots];   // per ring slot: the stage it receives next
-  PhaseInfo ph[5];
-  StageRef tab[kMegaMaxLayerStages];    // stage r of a layer
-  int per_layer, total, L;
-  long long layer_bytes;
+  StreamPlan plan;
   const uint8_t *stream_base;
-  int accw[kCW][48];                    // per warp: [plane][row] sums of the warp's current stage
-  int acc[kMegaAccBlocks][48];          // per row block: [plane][row] partial sums (K cut over warps)
-  int cnt[kMegaAccBlocks];              // slices of the block that have been added
   float cs[64], sn[64];                 // cos / sin of this step's position
-  float red[2 * kCW];                   // per warp: (sum of squares, largest magnitude)
+  float red[kCW], red2[kCW];
   float bestv[kCW];
   int besti[kCW];
   int abort_flag;
@@ -206,7 +173,7 @@ struct Shared {
 struct Ctx {
   const MegaParams &p;
   Shared &sh;
-  float *xs;          // scratch (shared memory): activation planes, attention staging
+  float *xs;          // staged activations (shared memory)
   uint8_t *ring;
   volatile int *err;
   int ctid, lane, warp;
@@ -240,6 +207,7 @@ __device__ __forceinline__ float ll_wait1(Ctx &c, const uint2 *p, uint32_t tag) 
       *ab = 1;
       break;
     }
+    __nanosleep(it < 4 ? 40 : 200);   // keep the pollers of 148 CTAs from flooding L2
     v = ll_load1(p);
   }
   return __uint_as_float(v.x);
@@ -261,9 +229,89 @@ __device__ __forceinline__ uint4 ll_wait2(Ctx &c, const uint2 *p, uint32_t tag, 
       *ab = 1;
       break;
     }
+    __nanosleep(it < 4 ? 40 : 200);   // keep the pollers of 148 CTAs from flooding L2
     v = ll_load2(p);
   }
   return v;
+}
+
+constexpr float kXScale = 18446744073709551616.0f;          // 2^64
+constexpr float kAccScale = 38685626227668133590597632.0f;  // 2^85
+// Cooperative load of n activations (n even) into shared memory, ready for the
+// row loops: multiplied by the RMSNorm weight (if any) and by 2^64.  `ss`
+// receives this thread's share of sum(x^2) (of the raw values), `sx` its share
+// of sum(x * weight).  The first vector of every thread is polled alone (cheap
+// on L2) before the rest is requested.
+__device__ __forceinline__ void put2(float *dst, const float *nw, int e, float a, float b, float &ss,
+                                     float &sx) {
+  ss = __fadd_rn(ss, __fmul_rn(a, a));
+  ss = __fadd_rn(ss, __fmul_rn(b, b));
+  if (nw != nullptr) {
+    const float2 w = __ldg(reinterpret_cast<const float2 *>(nw + e));
+    a = __fmul_rn(a, w.x);
+    b = __fmul_rn(b, w.y);
+  }
+  sx += a + b;
+  *reinterpret_cast<float2 *>(dst + e) = make_float2(a * kXScale, b * kXScale);
+}
+__device__ __forceinline__ void stage_tagged(Ctx &c, const uint2 *src, uint32_t tag, int n, float *dst,
+                                             const float *nw, float &ss, float &sx) {
+  const int nv = n >> 1;
+  for (int base = 0; base < nv; base += kCT * 4) {
+    uint4 r[4];
+    int idx[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      idx[i] = base + i * kCT + c.ctid;
+    if (idx[0] < nv) {
+      r[0] = ll_load2(src + 2 * idx[0]);
+      r[0] = ll_wait2(c, src + 2 * idx[0], tag, r[0]);
+    }
+#pragma unroll
+    for (int i = 1; i < 4; ++i)
+      if (idx[i] < nv)
+        r[i] = ll_load2(src + 2 * idx[i]);
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (idx[i] < nv) {
+        if (i > 0)
+          r[i] = ll_wait2(c, src + 2 * idx[i], tag, r[i]);
+        put2(dst, nw, 2 * idx[i], __uint_as_float(r[i].x), __uint_as_float(r[i].z), ss, sx);
+      }
+  }
+}
+__device__ __forceinline__ void stage_plain(Ctx &c, const float *src, int n, float *dst, const float *nw,
+                                            float &ss, float &sx) {
+  for (int i = c.ctid * 2; i < n; i += kCT * 2) {
+    const float2 v = __ldg(reinterpret_cast<const float2 *>(src + i));
+    put2(dst, nw, i, v.x, v.y, ss, sx);
+  }
+}
+
+// Streamed rows hold u = q + 128 (the int8 weight with its sign bit flipped).
+// A byte left in place inside an otherwise zeroed word IS a float: bits 0-7
+// give u * 2^-149 (a denormal), bits 8-15 give u * 2^-141, bits 16-23 give
+// u * 2^-133 (the step from denormal to normal numbers is continuous), and
+// the top byte shifted down gives u * 2^-149 again.  So the dequantisation of
+// a weight is ONE logic op (LOP3 / SHF) and its multiply-accumulate one FFMA.
+// The four byte positions accumulate separately and are rescaled when they are
+// added up.  The activations are pre-scaled by 2^64 to keep every product in
+// the normal range (a product is exact up to the single rounding of the FMA),
+// and the offset 128 * sum(x) is subtracted once per row:
+//   sum x*q = 2^85 * (a0 + a1*2^-8 + a2*2^-16 + a3) - 128 * sum x.
+__device__ __forceinline__ void dot_unit(const uint4 &w, const float (&x)[16], float (&a)[4]) {
+  const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+  for (int j = 0; j < 4; ++j) {
+    a[0] = fmaf(x[4 * j + 0], __uint_as_float(ws[j] & 0x000000FFu), a[0]);
+    a[1] = fmaf(x[4 * j + 1], __uint_as_float(ws[j] & 0x0000FF00u), a[1]);
+    a[2] = fmaf(x[4 * j + 2], __uint_as_float(ws[j] & 0x00FF0000u), a[2]);
+    a[3] = fmaf(x[4 * j + 3], __uint_as_float(ws[j] >> 24), a[3]);
+  }
+}
+// a0 + a1 * 2^-8 + a2 * 2^-16 + a3 (the scalings are exact)
+__device__ __forceinline__ float dot_total(const float (&a)[4]) {
+  return (a[0] + a[3]) + fmaf(a[1], 0.00390625f, a[2] * 0.0000152587890625f);
 }
 
 __device__ __forceinline__ void rows_of(const MegaPhase &ph, int cta, int grid, int &begin,
@@ -281,38 +329,37 @@ __device__ __forceinline__ void rows_of(const MegaPhase &ph, int cta, int grid, 
 // turns the cursor into (address, bytes) without divisions.
 __device__ __forceinline__ void issue_stage(Shared &sh, uint8_t *ring, int slot_bytes, int slot,
                                             int g, int n_slots) {
-  if (g >= sh.total)
+  StreamPlan &pl = sh.plan;
+  if (g >= pl.total)
     return;
-  int l = sh.next_l[slot], r = sh.next_r[slot];
+  int l = pl.next_l[slot], r = pl.next_r[slot];
   const uint8_t *src;
   uint32_t bytes;
-  if (l < sh.L) {
-    const StageRef e = sh.tab[r];
-    src = sh.stream_base + (long long)l * sh.layer_bytes + e.off;
-    bytes = e.bytes;
-  } else {   // the lm_head follows the layers: one K slice, blocks of 8 rows
-    const PhaseInfo &pi = sh.ph[4];
-    const int rows = min(kMegaBlockRows, pi.nrows - r * kMegaBlockRows);
-    bytes = (uint32_t)rows * (pi.K + kMegaTrailer);
-    src = sh.stream_base + (long long)sh.L * sh.layer_bytes +
-          (long long)r * kMegaBlockRows * (pi.K + kMegaTrailer);
+  if (l < pl.L) {
+    const uint2 e = pl.tab[r];
+    src = sh.stream_base + (long long)l * pl.layer_bytes + e.x;
+    bytes = e.y;
+  } else {   // the lm_head follows the layers
+    const int rows = min(pl.rps[4], pl.rows[4] - r * pl.rps[4]);
+    bytes = (uint32_t)rows * pl.row_bytes[4];
+    src = sh.stream_base + (long long)pl.L * pl.layer_bytes + (long long)r * pl.rps[4] * pl.row_bytes[4];
   }
   *(volatile int *)&sh.issued[slot] = g;
   mbar_expect_tx(&sh.full[slot], bytes);
   bulk_g2s(ring + (size_t)slot * slot_bytes, src, bytes, &sh.full[slot]);
   r += n_slots;
-  while (l < sh.L && r >= sh.per_layer) {
-    r -= sh.per_layer;
+  while (l < pl.L && r >= pl.per_layer) {
+    r -= pl.per_layer;
     ++l;
   }
-  sh.next_l[slot] = l;
-  sh.next_r[slot] = r;
+  pl.next_l[slot] = l;
+  pl.next_r[slot] = r;
 }
 
 // Wait until stage `want` has landed in `slot`.  The parity of an mbarrier only
-// tells consecutive uses of a slot apart; warps work on different stages and can
-// run more than one use ahead of the warp that still owns the slot, so the wait
-// first makes sure the slot has been re-requested for the wanted stage.
+// tells consecutive uses of a slot apart; warp groups work on different stages
+// and can run more than one use ahead of the group that still owns the slot, so
+// the wait first makes sure the slot has been re-requested for the wanted stage.
 __device__ __forceinline__ bool stage_wait(Shared &sh, int slot, uint32_t parity, int want,
                                            volatile int *err, volatile int *ab) {
   volatile int *iq = &sh.issued[slot];
@@ -358,337 +405,276 @@ struct Epi {
   float *logits;
 };
 
+__device__ __forceinline__ void emit(Ctx &c, const Epi &e, int n, float v, float &bestv,
+                                     int &besti) {
+  if (e.kind == EP_RESIDUAL) {
+    const float r = e.res_ll ? ll_wait1(c, e.res_ll + n, e.res_tag) : __ldg(e.res_plain + n);
+    ll_store(e.dst + n, __fadd_rn(r, v), e.tag);
+  } else if (e.kind == EP_LOGITS) {
+    e.logits[n] = v;
+    if (v > bestv || (v == bestv && n < besti)) {
+      bestv = v;
+      besti = n;
+    }
+  } else {
+    ll_store(e.dst + n, v, e.tag);
+  }
+}
 __device__ __forceinline__ float silu_mul(float g, float u) {
   // subgraph0_decode_simplify.mlir:226-231: (g * sigmoid(g)) * u
   const float s = 1.0f / (1.0f + expf(-g));
   return __fmul_rn(__fmul_rn(g, s), u);
 }
 
-// ---- one projection -----------------------------------------------------------------
-// 1. The activation vector (K values) is fetched by the whole CTA, multiplied by
-//    the RMSNorm weight if there is one, and kept in registers while its largest
-//    magnitude and sum of squares are reduced over the CTA.
-// 2. With qs = 2^22 / 2^ceil(log2(max)) every value becomes the integer
-//    X = rint(v * qs), |X| <= 2^22 (exact: qs is a power of two), stored as
-//    three signed bytes  X = h * 65536 + (m + 128) * 256 + (l + 128)  in three
-//    planes of K bytes in shared memory.
-// 3. Every warp takes pieces of ring stages (16 rows x a k range).  Lane (g, t),
-//    g = lane / 4, t = lane % 4, loads 16 weight bytes of row g and of row g + 8
-//    and, if g < 3, the 16 bytes of plane g at the same k; two m16n8k32
-//    instructions consume them (k runs over the lanes in fragment order, the same
-//    for both operands, which is all a dot product needs).  After the k range,
-//    lanes t = 0 hold the sums of planes 0 and 1 against rows g and g + 8, lanes
-//    t = 1 those of plane 2.
-// 4. The sums go to shared memory ([plane][row]; added atomically when K is cut
-//    into several pieces, the warp that adds the last piece carries on), lanes
-//    0..15 pick up one row each:
-//      sum x*q = (Sh * 65536 + Sm * 256 + Sl + 32896 * sum q) / qs
-//    in 64-bit integers, one conversion to float, then the RMSNorm factor, the
-//    row's scale and bias, and the epilogue.
-// One piece of work of a projection: which stage, which part of it, where it sits.
-struct Piece {
-  int st, sub, rb, ks, slot, rows;
-  uint32_t par;
-};
-__device__ __forceinline__ Piece piece_of(const Ctx &c, const PhaseInfo &pi, int u, int n_slots) {
-  // piece u = (stage st, part sub of its k range); stage st = (row block rb, slice ks)
-  Piece q;
-  q.st = u / pi.nkw;
-  q.sub = u - q.st * pi.nkw;
-  q.rb = q.st / pi.nks;
-  q.ks = q.st - q.rb * pi.nks;
-  const int lap = (c.slot + q.st) / n_slots;
-  q.slot = c.slot + q.st - lap * n_slots;
-  q.par = c.parity ^ (uint32_t)(lap & 1);
-  q.rows = min(kMegaBlockRows, pi.nrows - q.rb * kMegaBlockRows);
-  return q;
+// One visit of a warp to a ring stage: the warp takes rows R*wig .. R*wig+R-1 of
+// the stage.  The activations come from shared memory (already normalised and
+// scaled; four LDS.128 per 16-byte weight unit, shared by the R rows), so the
+// loop needs few registers whatever K is.  The R row sums are reduced across
+// the warp "transposed": at each of the first log2(R) steps a lane hands half of
+// its rows to its partner, so R rows cost R + 4 - log2(R).. shuffles instead of
+// 5 R, and every lane ends up with the total of ONE row:
+//   R = 8: row (lane>>2)&7 with bit order (16, 8, 4);  R = 4: (16, 8);  R = 1: row 0.
+template <int R>
+__device__ __forceinline__ void visit_rows(Ctx &c, const Epi &ep, const uint8_t *base, int rows,
+                                           int row_bytes, int K, int units, int wig, int lane,
+                                           const float *xsm, float off, float rinv, int first_row,
+                                           int local_row, float &bestv, int &besti) {
+  int ro[R];   // byte offsets of the warp's rows (clamped: loads stay inside the stage)
+  float a[R][4];
+#pragma unroll
+  for (int q = 0; q < R; ++q) {
+    ro[q] = min(R * wig + q, rows - 1) * row_bytes + lane * 16;
+    a[q][0] = a[q][1] = a[q][2] = a[q][3] = 0.f;
+  }
+  if (R == 1) {
+    // a single row per warp: four 512-byte blocks in flight, each with its own
+    // accumulators, so that the loads and the FMA chains of the blocks overlap
+    float b[3][4];
+#pragma unroll
+    for (int s = 0; s < 3; ++s)
+      b[s][0] = b[s][1] = b[s][2] = b[s][3] = 0.f;
+#pragma unroll 1
+    for (int i0 = 0; i0 * 32 < units; i0 += 4) {
+#pragma unroll
+      for (int s = 0; s < 4; ++s) {
+        const int i = i0 + s;
+        if (i * 32 + lane < units) {
+          const int qd = min(512, K - 512 * i) >> 2;
+          const float *xp = xsm + 512 * i + 4 * lane;
+          float x[16];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const float4 t = *reinterpret_cast<const float4 *>(xp + j * qd);
+            x[4 * j + 0] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+          }
+          const uint4 w = *reinterpret_cast<const uint4 *>(base + ro[0] + i * 512);
+          if (s == 0)
+            dot_unit(w, x, a[0]);
+          else
+            dot_unit(w, x, b[s - 1]);
+        }
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      a[0][e] = (a[0][e] + b[0][e]) + (b[1][e] + b[2][e]);
+  } else {
+#pragma unroll 3
+    for (int i = 0; i * 32 < units; ++i) {   // K / 512 blocks of 32 sixteen-byte units (the last may be short)
+      const int u = i * 32 + lane;
+      if (u < units) {
+        const int qd = min(512, K - 512 * i) >> 2;   // k distance between the unit's four groups
+        const float *xp = xsm + 512 * i + 4 * lane;
+        float x[16];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const float4 t = *reinterpret_cast<const float4 *>(xp + j * qd);
+          x[4 * j + 0] = t.x; x[4 * j + 1] = t.y; x[4 * j + 2] = t.z; x[4 * j + 3] = t.w;
+        }
+        uint4 w[R];
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+          w[q] = *reinterpret_cast<const uint4 *>(base + ro[q] + i * 512);
+#pragma unroll
+        for (int q = 0; q < R; ++q)
+          dot_unit(w[q], x, a[q]);
+      }
+    }
+  }
+  float v[R];
+#pragma unroll
+  for (int q = 0; q < R; ++q)
+    v[q] = dot_total(a[q]);
+  float tot;
+  int rowc;
+  if (R == 8) {
+    const bool b4 = lane & 16, b3 = lane & 8, b2 = lane & 4;
+    float t[4], s2[2];
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, b4 ? v[q] : v[q + 4], 16);
+      t[q] = (b4 ? v[q + 4] : v[q]) + got;
+    }
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, b3 ? t[q] : t[q + 2], 8);
+      s2[q] = (b3 ? t[q + 2] : t[q]) + got;
+    }
+    const float got = __shfl_xor_sync(0xffffffffu, b2 ? s2[0] : s2[1], 4);
+    tot = (b2 ? s2[1] : s2[0]) + got;
+    tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+    rowc = (b4 ? 4 : 0) + (b3 ? 2 : 0) + (b2 ? 1 : 0);
+  } else if (R == 4) {
+    const bool b4 = lane & 16, b3 = lane & 8;
+    float t[2];
+#pragma unroll
+    for (int q = 0; q < 2; ++q) {
+      const float got = __shfl_xor_sync(0xffffffffu, b4 ? v[q] : v[q + 2], 16);
+      t[q] = (b4 ? v[q + 2] : v[q]) + got;
+    }
+    const float got = __shfl_xor_sync(0xffffffffu, b3 ? t[0] : t[1], 8);
+    tot = (b3 ? t[1] : t[0]) + got;
+    tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 2);
+    tot += __shfl_xor_sync(0xffffffffu, tot, 1);
+    rowc = (b4 ? 2 : 0) + (b3 ? 1 : 0);
+  } else {
+    tot = v[0];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+      tot += __shfl_xor_sync(0xffffffffu, tot, o);
+    rowc = 0;
+  }
+  constexpr int kOwnerMask = R == 8 ? 3 : (R == 4 ? 7 : 31);   // one lane per row finishes it
+  const int row = R * wig + rowc;
+  const int rclamp = min(row, rows - 1);
+  const float2 tr = *reinterpret_cast<const float2 *>(base + (size_t)rclamp * row_bytes + K);
+  // sum x*q = 2^85 * tot - 128 * sum x; the RMSNorm factor applies to the whole row
+  const float dotv = __fmul_rn(fmaf(tot, kAccScale, off), rinv);
+  const float val = __fadd_rn(__fmul_rn(dotv, tr.x), tr.y);
+  if (ep.kind == EP_SILU) {
+    // rows (2j, 2j+1) = (gate_j, up_j) sit in partner lanes
+    const float upv = __shfl_xor_sync(0xffffffffu, val, R == 8 ? 4 : 8);
+    if ((lane & kOwnerMask) == 0 && (rowc & 1) == 0 && row + 1 < rows)
+      ll_store(ep.dst + ((first_row + row) >> 1), silu_mul(val, upv), ep.tag);
+  } else if ((lane & kOwnerMask) == 0 && row < rows) {
+    emit(c, ep, first_row + row, val, bestv, besti);
+  }
 }
 
+// One projection with rows of K <= 1536 weights.  All rows of the CTA are
+// streamed through the ring in stages of 16 rows; R rows per warp and visit:
+// 8 for long phases (two warps per stage, eight stages in flight), 4 for the
+// gate|up pairs of short phases, 1 when the whole phase is one or two stages
+// (q|k|v, o: all 16 warps take one row each).
 __device__ __forceinline__ void gemv_phase(Ctx &c, int phase_index, const XSrc &xs, const Epi &ep,
                                            int tl) {
-  Shared &sh = c.sh;
-  const PhaseInfo &pi = sh.ph[phase_index];
-  const int K = pi.K;
+  const MegaPhase &ph = c.p.phase[phase_index];
+  int row_begin, nrows;
+  rows_of(ph, blockIdx.x, gridDim.x, row_begin, nrows);
+  const int K = ph.K, row_bytes = ph.row_bytes, rps = ph.rps;
+  const int units = K / 16;
   const int n_slots = c.p.slots, slot_bytes = c.p.slot_bytes;
-  const int lane = c.lane, warp = c.warp, ctid = c.ctid;
+  const float eps = c.p.eps;
+  Shared &sh = c.sh;
+  const int lane = c.lane, warp = c.warp;
   uint8_t *const ring = c.ring;
-  int8_t *const planes = reinterpret_cast<int8_t *>(c.xs);
-  const int pstride = c.p.plane_stride;
-  volatile int *ab = &sh.abort_flag;
+  float *const xsm = c.xs;
+  int slot = c.slot, g = c.g;
+  uint32_t parity = c.parity;
+  const int nstages = (nrows + rps - 1) / rps;
+  // rows per warp and visit: 8 when a ring slot is left for each of the 8 stage groups
+  const int R = rps < 16 ? 1
+                         : (nstages >= 5 && n_slots >= 8 ? 8 : ((nstages >= 3 || ep.kind == EP_SILU) ? 4 : 1));
+  const int gw = rps / R;            // warps per group (= per stage)
+  const int NG = kCW / gw;           // stage groups
+  const int grp = warp / gw, wig = warp - grp * gw;
+  const int nrounds = (nstages + NG - 1) / NG;
 
-  // ---- 0. this warp's first piece: the index arithmetic does not depend on the
-  //         activations, so it is done before they are waited for.  (The wait for
-  //         the stage itself must stay behind the CTA barriers below: a stage late
-  //         in a long projection is only requested once an earlier one has been
-  //         consumed, which takes every warp's arrival at those barriers.)
-  Piece pc = piece_of(c, pi, warp, n_slots);
-
-  // ---- 1. fetch the activations: they stay in registers until their largest
-  //         magnitude is known -------------------------------------------------------
-  const int nv = K >> 1;               // vectors of two values
-  float2 v[kMaxV];
-  float ss = 0.f, amax = 0.f;
-#pragma unroll
-  for (int h = 0; h < 2; ++h) {
-    // two batches of requests (all loads of a batch are in flight before the first
-    // tag is looked at); vectors up to K = 512 * kMaxV need only the first
-    uint4 r[kMaxV / 2];
-#pragma unroll
-    for (int i = 0; i < kMaxV / 2; ++i) {
-      const int idx = (h * (kMaxV / 2) + i) * kCT + ctid;
-      if (idx < nv) {
-        if (xs.ll != nullptr) {
-          r[i] = ll_load2(xs.ll + 2 * idx);
-        } else {
-          const float2 t = __ldg(reinterpret_cast<const float2 *>(xs.plain) + idx);
-          r[i] = make_uint4(__float_as_uint(t.x), xs.tag, __float_as_uint(t.y), xs.tag);
-        }
-      }
-    }
-    if (xs.ll != nullptr) {
-      // one retry loop for the batch: reload whatever does not carry the tag yet
-      uint32_t it = 0;
-      unsigned long long t0 = 0;
-      for (;;) {
-        bool ok = true;
-#pragma unroll
-        for (int i = 0; i < kMaxV / 2; ++i) {
-          const int idx = (h * (kMaxV / 2) + i) * kCT + ctid;
-          if (idx < nv && (r[i].y != xs.tag || r[i].w != xs.tag)) {
-            r[i] = ll_load2(xs.ll + 2 * idx);
-            ok = false;
-          }
-        }
-        if (ok || *ab)
-          break;
-        bool give_up = ++it >= kSpinLimit;
-        if ((it & 0x3FF) == 0) {
-          const unsigned long long t = now_ns();
-          if (t0 == 0)
-            t0 = t;
-          give_up = give_up || *c.err != 0 || t - t0 > kWaitNs;
-        }
-        if (give_up) {
-          atomicCAS((int *)c.err, 0, 400 + (int)(xs.tag & 7));
-          *ab = 1;
-          break;
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < kMaxV / 2; ++i) {
-      const int idx = (h * (kMaxV / 2) + i) * kCT + ctid;
-      if (idx < nv) {
-        float a = __uint_as_float(r[i].x), b = __uint_as_float(r[i].z);
-        ss = __fadd_rn(ss, __fmul_rn(a, a));
-        ss = __fadd_rn(ss, __fmul_rn(b, b));
-        if (xs.nw != nullptr) {
-          const float2 w = __ldg(reinterpret_cast<const float2 *>(xs.nw) + idx);
-          a = __fmul_rn(a, w.x);
-          b = __fmul_rn(b, w.y);
-        }
-        amax = fmaxf(amax, fmaxf(fabsf(a), fabsf(b)));
-        v[h * (kMaxV / 2) + i] = make_float2(a, b);
-      }
-    }
-  }
+  // ---- stage the activation vector in shared memory ----------------------------
+  float ss = 0.f, sx = 0.f;
+  if (xs.ll != nullptr)
+    stage_tagged(c, xs.ll, xs.tag, K, xsm, xs.nw, ss, sx);
+  else
+    stage_plain(c, xs.plain, K, xsm, xs.nw, ss, sx);
   ss = warp_sum(ss);
-  amax = warp_max(amax);
-  if (lane == 0)
-    *reinterpret_cast<float2 *>(&sh.red[2 * warp]) = make_float2(ss, amax);
+  sx = warp_sum(sx);
+  if (lane == 0) {
+    sh.red[warp] = ss;
+    sh.red2[warp] = sx;
+  }
   consumer_sync();
   trace(c, tl, 12 + 4 * phase_index);
-  float mult;   // turns the integer row sum into the (normalised) dot product
+  float rinv = 1.f, off;
   {
-    // every warp folds the 16 partial (sum, max) pairs with one shuffle tree
-    float2 part = make_float2(0.f, 0.f);
-    if (lane < kCW)
-      part = *reinterpret_cast<const float2 *>(&sh.red[2 * lane]);
-    float t = part.x, mx = part.y;
+    float t = 0.f, t2 = 0.f;
 #pragma unroll
-    for (int o = 8; o > 0; o >>= 1) {
-      t += __shfl_xor_sync(0xffffffffu, t, o);
-      mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+    for (int w = 0; w < kCW; ++w) {
+      t += sh.red[w];
+      t2 += sh.red2[w];
     }
-    t = __shfl_sync(0xffffffffu, t, 0);
-    mx = __shfl_sync(0xffffffffu, mx, 0);
-    // qs = 2^(148 - e), e the biased exponent of the maximum: |v| < 2^(e - 126), so |v * qs| <= 2^22
-    int e = (int)(__float_as_uint(mx) >> 23);
-    e = min(max(e, 22), 253);
-    const float qs = __uint_as_float((uint32_t)(275 - e) << 23);
-    mult = __uint_as_float((uint32_t)(e - 21) << 23);   // 1 / qs
     // RMSNorm, subgraph0_decode_simplify.mlir:60-72 (the factor multiplies the row sums)
     if (xs.nw != nullptr)
-      mult *= rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), c.p.eps));
-    // ---- 2. the three planes -----------------------------------------------------
-#pragma unroll
-    for (int i = 0; i < kMaxV; ++i) {
-      const int idx = i * kCT + ctid;
-      if (idx < nv) {
-        const int xa = __float2int_rn(v[i].x * qs), xb = __float2int_rn(v[i].y * qs);
-        // bytes 0,1 = high plane of both values, bytes 2,3 = middle plane; then the low plane
-        const uint32_t hm = __byte_perm((uint32_t)xa, (uint32_t)xb, 0x5162) ^ 0x80800000u;
-        const uint32_t lo = __byte_perm((uint32_t)xa, (uint32_t)xb, 0x0040) ^ 0x00008080u;
-        *reinterpret_cast<uint16_t *>(planes + 2 * idx) = (uint16_t)(hm & 0xFFFFu);
-        *reinterpret_cast<uint16_t *>(planes + pstride + 2 * idx) = (uint16_t)(hm >> 16);
-        *reinterpret_cast<uint16_t *>(planes + 2 * pstride + 2 * idx) = (uint16_t)lo;
-      }
-    }
+      rinv = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), eps));
+    off = -128.0f * t2;
   }
-  consumer_sync();
-  trace(c, tl, 13 + 4 * phase_index);
 
-  // ---- 3. the stages -------------------------------------------------------------
-  const int g4 = lane >> 2, t4 = lane & 3;
-  const int nkw = pi.nkw, chunks = pi.chunks, slice = pi.slice_bytes;
-  const int per_block = pi.nks * nkw;     // pieces of work that add into one row block
+  // ---- stream the rows --------------------------------------------------------
+  volatile int *ab = &sh.abort_flag;
   float bestv = -INFINITY;
   int besti = 0x7fffffff;
-#pragma unroll 1
-  for (int u = warp; u < pi.nunits; u += kCW) {
-    if (u != warp)
-      pc = piece_of(c, pi, u, n_slots);
-#ifdef MEGA_FINE_TRACE
-    const bool ftr = phase_index < 4 && u == warp;
-    if (ftr) trace(c, tl, 32 + 8 * phase_index);
-#endif
-    if (!stage_wait(sh, pc.slot, pc.par, c.g + pc.st, c.err, ab))
-      atomicCAS((int *)c.err, 0, 200 + pc.slot);
-#ifdef MEGA_FINE_TRACE
-    if (ftr) trace(c, tl, 33 + 8 * phase_index);
-#endif
-    const int rows = pc.rows, rb = pc.rb;
-    const uint8_t *base = ring + (size_t)pc.slot * slot_bytes;
-    // rows g4 and g4 + 8, clamped: loads stay inside the stage
-    const int r_lo = min(g4, rows - 1), r_hi = min(g4 + 8, rows - 1);
-    const int jb = pc.sub * chunks * 4;    // first 16-byte unit of this warp's k range inside the slice
-    const uint32_t w_lo = smem_u32(base + r_lo * slice), w_hi = smem_u32(base + r_hi * slice);
-    const int swz_lo = (r_lo & 1) ? pi.swizzle : 0, swz_hi = (r_hi & 1) ? pi.swizzle : 0;
-    const uint32_t xrow = smem_u32(planes + min(g4, 2) * pstride + pc.ks * slice + jb * 16);
-    const bool has_b = g4 < 3;
-    int d0[4] = {0, 0, 0, 0}, d1[4] = {0, 0, 0, 0};
-#pragma unroll 2
-    for (int j = 0; j < chunks; ++j) {   // a chunk = 64 k = two instructions
-      const int un = jb + (j << 2) + t4;
-      const uint4 lo = lds128(w_lo + ((un ^ swz_lo) << 4));
-      const uint4 hi = lds128(w_hi + ((un ^ swz_hi) << 4));
-      uint4 x = make_uint4(0u, 0u, 0u, 0u);
-      if (has_b)
-        x = lds128(xrow + (((j << 2) + t4) << 4));
-      mma_s8(d0, lo.x, hi.x, lo.y, hi.y, x.x, x.y);
-      mma_s8(d1, lo.z, hi.z, lo.w, hi.w, x.z, x.w);
-    }
-#ifdef MEGA_FINE_TRACE
-    if (ftr) trace(c, tl, 34 + 8 * phase_index);
-#endif
-    // lane (g4, t4): c0, c1 = row g4 x planes 2*t4, 2*t4 + 1; c2, c3 = row g4 + 8
-    const int s0 = d0[0] + d1[0], s1 = d0[1] + d1[1], s2 = d0[2] + d1[2], s3 = d0[3] + d1[3];
-    // ---- 4. [plane][row] sums to shared memory, one lane per row finishes -----------
-    int *accp = per_block == 1 ? sh.accw[warp] : sh.acc[rb];
-    bool last = true;
-    if (per_block == 1) {
-      if (t4 == 0) {
-        accp[g4] = s0;
-        accp[g4 + 8] = s2;
-        accp[16 + g4] = s1;
-        accp[16 + g4 + 8] = s3;
-      } else if (t4 == 1) {
-        accp[32 + g4] = s0;
-        accp[32 + g4 + 8] = s2;
-      }
-      __syncwarp();
-    } else {
-      if (t4 == 0) {
-        atomicAdd(&accp[g4], s0);
-        atomicAdd(&accp[g4 + 8], s2);
-        atomicAdd(&accp[16 + g4], s1);
-        atomicAdd(&accp[16 + g4 + 8], s3);
-      } else if (t4 == 1) {
-        atomicAdd(&accp[32 + g4], s0);
-        atomicAdd(&accp[32 + g4 + 8], s2);
-      }
-      __syncwarp();
-      int old = 0;
-      if (lane == 0) {
-        __threadfence_block();
-        old = atomicAdd(&sh.cnt[rb], 1);
-      }
-      old = __shfl_sync(0xffffffffu, old, 0);
-      last = old == per_block - 1;
-      if (last)
-        __threadfence_block();
-    }
-#ifdef MEGA_FINE_TRACE
-    if (ftr) trace(c, tl, 35 + 8 * phase_index);
-#endif
-    if (last && lane < kMegaBlockRows) {
-      const int row = lane;
-      const int rc = min(row, rows - 1);
-      const long long Sh = ((volatile int *)accp)[rc], Sm = ((volatile int *)accp)[16 + rc],
-                      Sl = ((volatile int *)accp)[32 + rc];
-      if (per_block != 1) {   // ready for the next projection (all 16 entries: rows beyond the block hold sums of repeated rows)
-        __syncwarp(0x0000ffffu);
-        ((volatile int *)accp)[row] = 0;
-        ((volatile int *)accp)[16 + row] = 0;
-        ((volatile int *)accp)[32 + row] = 0;
-        if (lane == 0)
-          sh.cnt[rb] = 0;
-      }
-      const float4 tr = *reinterpret_cast<const float4 *>(base + rows * slice + rc * kMegaTrailer);
-      const long long T = (Sh << 16) + (Sm << 8) + Sl + 32896ll * (long long)__float_as_int(tr.z);
-      const float dotv = __fmul_rn(__ll2float_rn(T), mult);
-      const float val = __fadd_rn(__fmul_rn(dotv, tr.x), tr.y);
-      const int n = pi.row_begin + rb * kMegaBlockRows + row;
-      if (ep.kind == EP_SILU) {
-        // rows (2j, 2j+1) = (gate_j, up_j) sit in neighbouring lanes
-        const float upv = __shfl_xor_sync(0x0000ffffu, val, 1);
-        if ((row & 1) == 0 && row + 1 < rows)
-          ll_store(ep.dst + (n >> 1), silu_mul(val, upv), ep.tag);
-      } else if (row < rows) {
-        if (ep.kind == EP_RESIDUAL) {
-          const float r = ep.res_ll ? ll_wait1(c, ep.res_ll + n, ep.res_tag) : __ldg(ep.res_plain + n);
-          ll_store(ep.dst + n, __fadd_rn(r, val), ep.tag);
-        } else if (ep.kind == EP_LOGITS) {
-          ep.logits[n] = val;
-          if (val > bestv || (val == bestv && n < besti)) {
-            bestv = val;
-            besti = n;
-          }
-        } else {
-          ll_store(ep.dst + n, val, ep.tag);
-        }
-      }
-    }
-    // Release the stage: the warp that finishes it last refills its slot with the
-    // stage one ring-length ahead.  (No fence on purpose: the slot's bytes were
-    // consumed by arithmetic the values above depend on, so every read has
-    // completed; the counter reset is ordered before the next use of the slot by
-    // the arrival of that stage's data.)
-    __syncwarp();
-#ifdef MEGA_FINE_TRACE
-    if (ftr) trace(c, tl, 36 + 8 * phase_index);
-#endif
-    if (lane == 0 && (nkw == 1 || atomicAdd(&sh.done[pc.slot], 1) == nkw - 1)) {
-      sh.done[pc.slot] = 0;
-      issue_stage(sh, ring, slot_bytes, pc.slot, c.g + pc.st + n_slots, n_slots);
-    }
-#ifdef MEGA_FINE_TRACE
-    if (ftr) trace(c, tl, 37 + 8 * phase_index);
-#endif
+  int my_slot = slot + grp;
+  uint32_t my_par = parity;
+  while (my_slot >= n_slots) {
+    my_slot -= n_slots;
+    my_par ^= 1u;
   }
-  trace(c, tl, 14 + 4 * phase_index);
+  for (int rd = 0; rd < nrounds; ++rd) {
+    const int st = rd * NG + grp;
+    if (st < nstages) {
+      const int r0 = st * rps;
+      const int rows = min(rps, nrows - r0);
+      if (!stage_wait(sh, my_slot, my_par, g + st, c.err, ab))
+        atomicCAS((int *)c.err, 0, 200 + my_slot);
+      const uint8_t *base = ring + (size_t)my_slot * slot_bytes;
+      if (R == 8)
+        visit_rows<8>(c, ep, base, rows, row_bytes, K, units, wig, lane, xsm, off, rinv,
+                      row_begin + r0, r0, bestv, besti);
+      else if (R == 4)
+        visit_rows<4>(c, ep, base, rows, row_bytes, K, units, wig, lane, xsm, off, rinv,
+                      row_begin + r0, r0, bestv, besti);
+      else
+        visit_rows<1>(c, ep, base, rows, row_bytes, K, units, wig, lane, xsm, off, rinv,
+                      row_begin + r0, r0, bestv, besti);
+      // Release the slot; the warp of the group that finishes it last refills it
+      // with the stage one ring-length ahead.  (No fence on purpose: the slot's
+      // bytes were consumed by arithmetic the values above depend on, so every
+      // read has completed; the counter reset is ordered before the next use of
+      // the slot by the arrival of that stage's data.)
+      __syncwarp();
+      if (lane == 0 && atomicAdd(&sh.done[my_slot], 1) == gw - 1) {
+        sh.done[my_slot] = 0;
+        issue_stage(sh, ring, slot_bytes, my_slot, g + st + n_slots, n_slots);
+      }
+    }
+    my_slot += NG;
+    while (my_slot >= n_slots) {
+      my_slot -= n_slots;
+      my_par ^= 1u;
+    }
+  }
   // this phase used `nstages` stages of the ring
-  {
-    int slot = c.slot + pi.nstages;
-    uint32_t parity = c.parity;
-    while (slot >= n_slots) {
-      slot -= n_slots;
-      parity ^= 1u;
-    }
-    c.slot = slot;
-    c.parity = parity;
-    c.g += pi.nstages;
+  g += nstages;
+  slot += nstages % n_slots;
+  parity ^= (uint32_t)((nstages / n_slots) & 1);
+  if (slot >= n_slots) {
+    slot -= n_slots;
+    parity ^= 1u;
   }
+  c.slot = slot;
+  c.parity = parity;
+  c.g = g;
   if (ep.kind == EP_LOGITS) {
     // this warp's first maximum, for the CTA's candidate
 #pragma unroll
@@ -705,7 +691,7 @@ __device__ __forceinline__ void gemv_phase(Ctx &c, int phase_index, const XSrc &
       sh.besti[warp] = besti;
     }
   }
-  // the planes are reused by the next phase
+  // the staged vector is reused by the next phase
   consumer_sync();
 }
 
@@ -869,7 +855,6 @@ __device__ __noinline__ void attention_phase(Ctx &c, int layer, int pos) {
       l[g] = 0.f;
       acc[g][0] = acc[g][1] = acc[g][2] = acc[g][3] = 0.f;
     }
-#pragma unroll 1
     for (int j0 = s0 + warp; j0 < s1; j0 += NB * kAW) {
       if (j0 != s0 + warp) {
         // later rounds: NB rows in flight, all loads issued before the first use
@@ -1089,66 +1074,60 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
   extern __shared__ __align__(128) uint8_t smem_raw[];
   Shared &sh = *reinterpret_cast<Shared *>(smem_raw);
   float *xs = reinterpret_cast<float *>(smem_raw + ((sizeof(Shared) + 127) / 128) * 128);
-  uint8_t *ring = reinterpret_cast<uint8_t *>(xs) + p.xs_bytes;
+  uint8_t *ring = reinterpret_cast<uint8_t *>(xs + p.xs_floats);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   volatile int *err = p.error;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < p.slots; ++s) {
       mbar_init(&sh.full[s], 1);
-      sh.issued[s] = -1;
       sh.done[s] = 0;
+      sh.issued[s] = -1;
     }
     sh.abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    // this CTA's share of every projection and its stage table
+    // this CTA's stream plan
+    StreamPlan &pl = sh.plan;
     long long off = 0;
-    int r = 0;
+    pl.per_layer = 0;
     for (int i = 0; i < 5; ++i) {
-      const MegaPhase &ph = p.phase[i];
-      PhaseInfo &pi = sh.ph[i];
-      rows_of(ph, blockIdx.x, gridDim.x, pi.row_begin, pi.nrows);
-      pi.nrb = (pi.nrows + kMegaBlockRows - 1) / kMegaBlockRows;
-      pi.nstages = pi.nrb * ph.nks;
-      pi.nunits = pi.nstages * ph.nkw;
-      pi.K = ph.K;
-      pi.slice_bytes = ph.slice_bytes;
-      pi.nks = ph.nks;
-      pi.nkw = ph.nkw;
-      pi.chunks = ph.slice_bytes / 64 / ph.nkw;
-      pi.swizzle = ph.swizzle;
-      pi.first_stage = r;
+      int rb, nr;
+      rows_of(p.phase[i], blockIdx.x, gridDim.x, rb, nr);
+      pl.rows[i] = nr;
+      pl.rps[i] = p.phase[i].rps;
+      pl.row_bytes[i] = p.phase[i].row_bytes;
+      pl.n[i] = (nr + pl.rps[i] - 1) / pl.rps[i];
       if (i < 4) {
-        for (int b = 0; b < pi.nrb; ++b) {
-          const int rows = min(kMegaBlockRows, pi.nrows - b * kMegaBlockRows);
-          for (int k = 0; k < ph.nks; ++k, ++r) {
-            const uint32_t bytes = (uint32_t)rows * (ph.slice_bytes + kMegaTrailer);
-            if (r < kMegaMaxLayerStages)
-              sh.tab[r] = StageRef{(uint32_t)off, bytes};
-            off += bytes;
-          }
-        }
+        pl.off[i] = off;
+        off += (long long)nr * pl.row_bytes[i];
+        pl.per_layer += pl.n[i];
+      } else {
+        pl.off[i] = 0;
       }
     }
-    sh.per_layer = r;
-    sh.layer_bytes = off;
-    sh.L = p.L;
-    sh.total = p.L * sh.per_layer + sh.ph[4].nstages;
-    for (int sl = 0; sl < p.slots; ++sl) {
-      int l = 0, rr = sl;
-      while (l < sh.L && rr >= sh.per_layer) {
-        rr -= sh.per_layer;
-        ++l;
+    pl.layer_bytes = off;
+    pl.L = p.L;
+    pl.total = p.L * pl.per_layer + pl.n[4];
+    {
+      int r = 0;
+      for (int i = 0; i < 4; ++i)
+        for (int q = 0; q < pl.n[i]; ++q, ++r) {
+          const int rows = min(pl.rps[i], pl.rows[i] - q * pl.rps[i]);
+          pl.tab[r] = make_uint2((uint32_t)(pl.off[i] + (long long)q * pl.rps[i] * pl.row_bytes[i]),
+                                 (uint32_t)rows * pl.row_bytes[i]);
+        }
+      for (int sl = 0; sl < p.slots; ++sl) {
+        int l = 0, rr = sl;
+        while (l < pl.L && rr >= pl.per_layer) {
+          rr -= pl.per_layer;
+          ++l;
+        }
+        pl.next_l[sl] = l;
+        pl.next_r[sl] = rr;
       }
-      sh.next_l[sl] = l;
-      sh.next_r[sl] = rr;
     }
     sh.stream_base = p.stream + p.cta_off[blockIdx.x];
   }
-  for (int i = threadIdx.x; i < kMegaAccBlocks * 48; i += blockDim.x)
-    (&sh.acc[0][0])[i] = 0;
-  if (threadIdx.x < kMegaAccBlocks)
-    sh.cnt[threadIdx.x] = 0;
   const int token = p.state[0], pos = p.state[1];
   if (threadIdx.x < D / 2) {
     // subgraph0_decode_simplify.mlir:52-59
@@ -1282,22 +1261,16 @@ decode_step_kernel(const __grid_constant__ MegaParams p) {
 }
 
 // ---- stream builder: packed rows of one projection -> per-CTA streams ---------------
-// One CTA per source row.  Source row r is row n = r * row_stride + row_phase of a
-// projection with N_total rows, dealt out to the CTAs in units of ph.unit rows.
-// Inside its CTA's part the row belongs to block b = local / 8, row i = local % 8;
-// slice k of the block is the stage [rows x slice_bytes][rows x 16-byte trailer]
-// at byte  b * 8 * (K + 16 * nks) + k * rows * (slice_bytes + 16).  The row's
-// bytes are its int8 weights in natural k order (the source is the packed-row
-// layout of the GEMV path, see packed_offset), with the two 64-byte halves of
-// every 128 bytes swapped in odd rows when ph.swizzle is set (shared-memory
-// banks: lanes of two rows then read different banks).  Trailer: {scale, bias,
-// sum of the row's weights (int32), 0}.
+// One CTA per source row: copies its K packed bytes (flipping the sign bit:
+// int8 q -> u = q + 128) and appends the 16-byte trailer {scale, bias, 0, 0}.
+// Source row r becomes row r * row_stride + row_phase of a projection with
+// N_total rows, dealt out to the CTAs in units of `unit` rows.
 __global__ void mega_build_rows_kernel(const uint8_t *src, int K, int row_stride, int row_phase,
-                                       int N_total, MegaPhase ph, const float *scale,
-                                       const float *bias, int grid_ctas,
+                                       int N_total, int unit, const float *scale,
+                                       const float *bias, int grid_ctas, int row_bytes,
                                        const int64_t *cta_phase_off, uint8_t *stream) {
   const int n = blockIdx.x * row_stride + row_phase;
-  const int nu = N_total / ph.unit, un = n / ph.unit;
+  const int nu = N_total / unit, un = n / unit;
   const int base = nu / grid_ctas, rem = nu % grid_ctas;
   int cta;
   const int split = rem * (base + 1);
@@ -1305,52 +1278,26 @@ __global__ void mega_build_rows_kernel(const uint8_t *src, int K, int row_stride
     cta = un / (base + 1);
   else
     cta = rem + (un - split) / base;
-  const int begin = (cta * base + min(cta, rem)) * ph.unit;
-  const int nrows = (base + (cta < rem ? 1 : 0)) * ph.unit;
-  const int local = n - begin, b = local / kMegaBlockRows, ri = local % kMegaBlockRows;
-  const int rows = min(kMegaBlockRows, nrows - b * kMegaBlockRows);
-  uint8_t *block = stream + cta_phase_off[cta] +
-                   (int64_t)b * kMegaBlockRows * ((int64_t)K + (int64_t)kMegaTrailer * ph.nks);
-  const uint8_t *srow = src + (int64_t)blockIdx.x * packed_row_bytes(B200_W_I8, K);
-  const int swz = (ri & 1) ? ph.swizzle : 0;
-  int sum = 0;
-  for (int w = threadIdx.x; w < K / 4; w += blockDim.x) {   // 4 consecutive k stay together in a packed row
-    const int k = 4 * w;
-    const uint32_t word = *reinterpret_cast<const uint32_t *>(srow + packed_offset(B200_W_I8, K, k, nullptr));
-    sum += (int)(int8_t)(word & 0xFF) + (int)(int8_t)((word >> 8) & 0xFF) +
-           (int)(int8_t)((word >> 16) & 0xFF) + (int)(int8_t)(word >> 24);
-    const int ks = k / ph.slice_bytes, kk = k - ks * ph.slice_bytes;
-    const int unit16 = (kk >> 4) ^ swz;
-    uint8_t *dst = block + (int64_t)ks * rows * (ph.slice_bytes + kMegaTrailer) +
-                   (int64_t)ri * ph.slice_bytes + unit16 * 16 + (kk & 15);
-    *reinterpret_cast<uint32_t *>(dst) = word;
+  const int begin = (cta * base + min(cta, rem)) * unit;
+  uint8_t *dst = stream + cta_phase_off[cta] + (int64_t)(n - begin) * row_bytes;
+  const uint4 *s4 = reinterpret_cast<const uint4 *>(src + (int64_t)blockIdx.x * K);
+  uint4 *d4 = reinterpret_cast<uint4 *>(dst);
+  for (int i = threadIdx.x; i < K / 16; i += blockDim.x) {
+    uint4 v = s4[i];
+    v.x ^= 0x80808080u; v.y ^= 0x80808080u; v.z ^= 0x80808080u; v.w ^= 0x80808080u;
+    d4[i] = v;
   }
-  __shared__ int s_sum[32];
-#pragma unroll
-  for (int o = 16; o > 0; o >>= 1)
-    sum += __shfl_xor_sync(0xffffffffu, sum, o);
-  if ((threadIdx.x & 31) == 0)
-    s_sum[threadIdx.x >> 5] = sum;
-  __syncthreads();
-  if (threadIdx.x < ph.nks) {
-    int total = 0;
-    for (int w = 0; w < (int)(blockDim.x + 31) / 32; ++w)
-      total += s_sum[w];
-    uint8_t *tr = block + (int64_t)threadIdx.x * rows * (ph.slice_bytes + kMegaTrailer) +
-                  (int64_t)rows * ph.slice_bytes + ri * kMegaTrailer;
-    *reinterpret_cast<float4 *>(tr) = make_float4(scale[blockIdx.x], bias ? bias[blockIdx.x] : 0.f,
-                                                  __int_as_float(total), 0.f);
-  }
+  if (threadIdx.x == 0)
+    *reinterpret_cast<float4 *>(dst + K) =
+        make_float4(scale[blockIdx.x], bias ? bias[blockIdx.x] : 0.f, 0.f, 0.f);
 }
 
 int mega_build_rows(const void *packed, int K, int n_rows, int row_stride, int row_phase,
-                    int N_total, const MegaPhase &ph, const float *scale, const float *bias,
-                    int grid_ctas, const int64_t *cta_phase_off_dev, void *stream_buf,
+                    int N_total, int unit, const float *scale, const float *bias, int grid_ctas,
+                    int row_bytes, const int64_t *cta_phase_off_dev, void *stream_buf,
                     cudaStream_t st) {
-  if (ph.nks > 128)
-    return fail(B200_ELIMIT, "mega_build_rows: %d K slices", ph.nks);
   mega_build_rows_kernel<<<n_rows, 128, 0, st>>>((const uint8_t *)packed, K, row_stride, row_phase,
-                                                 N_total, ph, scale, bias, grid_ctas,
+                                                 N_total, unit, scale, bias, grid_ctas, row_bytes,
                                                  cta_phase_off_dev, (uint8_t *)stream_buf);
   B200_LAUNCH_CHECK();
   return B200_OK;
