@@ -74,6 +74,10 @@ def load():
         "b200_pack_int4": (i32, [vp, i64, vp, vp]),
         "b200_unpack_int4": (i32, [vp, i64, vp, vp]),
         "b200_gemv": (i32, [C.POINTER(Weight), C.POINTER(GemvArgs), vp]),
+        "b200_gemm_w8_workspace_bytes": (i64, [i32, i64]),
+        "b200_gemm_w8": (i32, [C.POINTER(Weight), vp, i32, i64, vp, i64, vp, i64, vp, f32, i32,
+                               vp, i64, vp]),
+        "b200_gemm_w8_status": (i32, [vp, vp]),
         "b200_rmsnorm": (i32, [vp, vp, vp, i64, i64, f32, vp]),
         "b200_silu_mul": (i32, [vp, vp, vp, i64, vp]),
         "b200_rope_kv_write": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, f32, i32,

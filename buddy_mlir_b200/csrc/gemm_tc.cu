@@ -1,0 +1,480 @@
+// Dense weight-only-quantised GEMM on the 5th-generation tensor cores:
+//   C[M,N] = A[M,K] (f32) * dequant(W)[N,K]^T, per-channel scale in the epilogue.
+//
+// This is the prefill / batched-decode path.  buddy-mlir's prefill GEMM
+// (midend/lib/Conversion/MatMulOptimization/MatMulBlisVectorization.cpp:367-530)
+// dequantises w = float(q) * scale while it packs B and then runs f32 FMAs; here
+// the integer part and the scale are separated (sum_k a*q, then * scale[n]),
+// which is the same product up to f32 rounding (the parity tests hold it to
+// 1e-3 of the CPU restatement, as for the decode path).
+//
+// Operands.  int8 -> bf16 is exact (|q| <= 128 needs 8 significant bits), so
+// the weight operand loses nothing.  The f32 activations are split into two
+// bf16 terms, a = hi + lo (hi = bf16(a), lo = bf16(a - hi), 16 significant
+// bits together), and every tile is multiplied twice, once per term, into the
+// same f32 accumulator in tensor memory.  The split runs once per GEMM into a
+// workspace, in the k order of the packed weight rows (a dot product does not
+// care about the order of k as long as both operands agree), so the packed
+// decode weights are used as they are: no second copy of the weights.
+//
+// One CTA computes a 128 x 128 tile of C.  Warp 0 issues the TMA loads
+// (cp.async.bulk.tensor, no multicast) of the two activation tiles (128-byte
+// swizzle) and of the raw int8 weight tile into a 3-stage ring; warps 2..5
+// convert the int8 tile to bf16 in the swizzled layout the tensor core reads;
+// warp 1 issues tcgen05.mma (kind::f16, 128 x 128 x 16 per instruction, two
+// terms x four k steps per stage) and commits the stage back to the loader;
+// after the last k block warps 2..5 read the accumulator with tcgen05.ld,
+// apply scale / bias / residual / SiLU-gate and store f32 rows.
+//
+// Every wait is bounded (poll count and wall time); on expiry the CTA records
+// an error, all roles fall through, tensor memory is released and the host
+// call fails.
+#include "common.cuh"
+
+#include <cuda.h>
+
+#include <mutex>
+
+namespace b200 {
+
+namespace {
+
+constexpr int BM = 128, BN = 128, BK = 64;     // tile; BK bf16 = 128 bytes = one swizzle row
+constexpr int kStages = 3;
+constexpr int kTmemCols = 128;                 // f32 accumulator 128 lanes x 128 columns
+constexpr int kThreads = 192;                  // warp 0 loader, warp 1 mma, warps 2..5 convert + epilogue
+constexpr uint32_t A_BYTES = BM * BK * 2;      // 16 KB per term
+constexpr uint32_t WRAW_BYTES = BN * BK;       // 8 KB
+constexpr uint32_t WB_BYTES = BN * BK * 2;     // 16 KB
+constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + WRAW_BYTES + WB_BYTES;   // 56 KB
+constexpr uint32_t kSpin = 1u << 26;
+constexpr unsigned long long kWaitNs = 2000000000ull;
+
+struct Bars {
+  uint64_t full[kStages];      // TMA bytes of the stage have landed
+  uint64_t ready[kStages];     // the bf16 weight tile has been written (128 arrivals)
+  uint64_t empty[kStages];     // the tensor core is done with the stage
+  uint64_t accum;              // all MMAs have completed
+  uint32_t tmem_base;
+  int abort_flag;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void *p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ unsigned long long now_ns() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+__device__ __forceinline__ void mbar_init(uint64_t *bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t *bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ bool mbar_try(uint64_t *bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+               : "=r"(ok) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+  return ok != 0;
+}
+// Bounded wait; false when it gave up or the CTA already failed.
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *ab, int *err, int code) {
+  unsigned long long t0 = 0;
+  for (uint32_t it = 0; it < kSpin; ++it) {
+    if (mbar_try(bar, parity))
+      return !*ab;
+    if ((it & 0x3FF) == 0x3FF) {
+      if (*ab)
+        return false;
+      const unsigned long long t = now_ns();
+      if (t0 == 0)
+        t0 = t;
+      else if (t - t0 > kWaitNs)
+        break;
+    }
+  }
+  atomicCAS(err, 0, code);
+  *ab = 1;
+  return false;
+}
+__device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, int x, int y, uint64_t *bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+      ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+      : "memory");
+}
+// K-major operand tile in shared memory, 128-byte swizzle, rows of 128 bytes:
+// start address / 16, leading byte offset (unused for swizzled K-major: 1),
+// stride byte offset = 8 rows x 128 B = 1024 B, descriptor version 1, layout 2.
+__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+  uint64_t d = 0;
+  d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)1 << 16;
+  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+// kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128.
+constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+      : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t *bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+
+struct GemmParams {
+  int M, N, K;                 // K = packed k (multiple of 64)
+  const float *scale;          // [N]
+  const float *bias;           // [N] or null
+  const float *residual;       // [M, ldr] or null
+  float *C;                    // [M, ldc]
+  int64_t ldc, ldr;
+  int silu_pairs;              // rows (2j, 2j+1) of W are (gate_j, up_j): C[m, j] = silu(g) * u, ldc counts N/2 columns
+  int *error;
+};
+
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
+                  const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  // 1024-byte alignment of every swizzled tile
+  uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  Bars &bars = *reinterpret_cast<Bars *>(tiles + kStages * STAGE_BYTES);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int nkb = p.K / BK;
+  volatile int *ab = &bars.abort_flag;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) {
+      mbar_init(&bars.full[s], 1);
+      mbar_init(&bars.ready[s], 128);
+      mbar_init(&bars.empty[s], 1);
+    }
+    mbar_init(&bars.accum, 1);
+    bars.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {   // tensor memory: one warp allocates, the same warp frees
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)), "n"(kTmemCols) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = bars.tmem_base;
+
+  if (warp == 0) {
+    // ---- loader ------------------------------------------------------------------
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % kStages, use = kb / kStages;
+        if (use > 0 && !mbar_wait(&bars.empty[s], (use - 1) & 1, ab, p.error, 701))
+          break;
+        uint8_t *st = tiles + s * STAGE_BYTES;
+        mbar_expect_tx(&bars.full[s], 2 * A_BYTES + WRAW_BYTES);
+        tma_load_2d(st, &map_hi, kb * BK, m0, &bars.full[s]);
+        tma_load_2d(st + A_BYTES, &map_lo, kb * BK, m0, &bars.full[s]);
+        tma_load_2d(st + 2 * A_BYTES, &map_w, kb * BK, n0, &bars.full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    // ---- tensor core issue (one thread) ------------------------------------------------
+    if (lane == 0) {
+      for (int kb = 0; kb < nkb; ++kb) {
+        const int s = kb % kStages, use = kb / kStages;
+        if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 702) ||
+            !mbar_wait(&bars.ready[s], use & 1, ab, p.error, 703))
+          break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a_hi = smem_u32(tiles + s * STAGE_BYTES), a_lo = a_hi + A_BYTES,
+                       wb = a_hi + 2 * A_BYTES + WRAW_BYTES;
+#pragma unroll
+        for (int k = 0; k < BK / 16; ++k) {   // 16 bf16 = 32 bytes along the swizzled row
+          const uint64_t db = smem_desc(wb + k * 32);
+          mma_bf16(tmem, smem_desc(a_hi + k * 32), db, (kb | k) != 0);
+          mma_bf16(tmem, smem_desc(a_lo + k * 32), db, 1u);
+        }
+        tc_commit(&bars.empty[s]);   // arrives when the MMAs above have read the stage
+      }
+      tc_commit(&bars.accum);
+    }
+  } else {
+    // ---- int8 -> bf16 conversion of the weight tile, then the epilogue ------------------
+    const int t = threadIdx.x - 64;           // 0..127: weight row of the tile (conversion), accumulator row (epilogue)
+    bool alive = true;
+    for (int kb = 0; kb < nkb && alive; ++kb) {
+      const int s = kb % kStages, use = kb / kStages;
+      if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 704)) {
+        alive = false;
+        break;
+      }
+      uint8_t *st = tiles + s * STAGE_BYTES;
+      const uint4 *raw = reinterpret_cast<const uint4 *>(st + 2 * A_BYTES + t * BK);
+      uint8_t *dst = st + 2 * A_BYTES + WRAW_BYTES + t * 128;   // row t of the swizzled bf16 tile
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {            // 16 int8 -> two 16-byte chunks of bf16
+        const uint4 w = raw[q];
+        const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+        uint32_t o[8];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          // byte u = q + 128 placed in the mantissa of 2^23: (2^23 + u) - (2^23 + 128) = q, exact
+          const float f0 = __uint_as_float(0x4B000000u | (ws[j] & 0xFFu)) - 8388736.0f;
+          const float f1 = __uint_as_float(0x4B000000u | ((ws[j] >> 8) & 0xFFu)) - 8388736.0f;
+          const float f2 = __uint_as_float(0x4B000000u | ((ws[j] >> 16) & 0xFFu)) - 8388736.0f;
+          const float f3 = __uint_as_float(0x4B000000u | (ws[j] >> 24)) - 8388736.0f;
+          // an integer of magnitude <= 128 is its own bf16: keep the upper halves
+          o[2 * j] = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+          o[2 * j + 1] = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+        }
+        // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
+        const int c0 = 2 * q, c1 = 2 * q + 1;
+        *reinterpret_cast<uint4 *>(dst + ((c0 ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4 *>(dst + ((c1 ^ (t & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+      }
+      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
+      mbar_arrive(&bars.ready[s]);
+    }
+    // ---- epilogue: accumulator row (lane of tensor memory) = this thread's output row ----
+    if (alive && mbar_wait(&bars.accum, 0, ab, p.error, 705)) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      // a warp reads the 32 lanes of tensor memory that match its rank within its warpgroup
+      const int quad = warp & 3;
+      const int row = quad * 32 + lane;
+      const int m = m0 + row;
+#pragma unroll 1
+      for (int cb = 0; cb < BN; cb += 32) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)cb;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+              "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+              "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        if (m < p.M) {
+          if (p.silu_pairs) {
+            float *crow = p.C + (int64_t)m * p.ldc + ((n0 + cb) >> 1);
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+              const int n = n0 + cb + j;
+              if (n + 1 < p.N) {
+                float g = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
+                float u = __fmul_rn(__uint_as_float(v[j + 1]), __ldg(p.scale + n + 1));
+                if (p.bias) {
+                  g = __fadd_rn(g, __ldg(p.bias + n));
+                  u = __fadd_rn(u, __ldg(p.bias + n + 1));
+                }
+                const float sg = 1.0f / (1.0f + expf(-g));   // subgraph0_decode_simplify.mlir:226-231
+                crow[j >> 1] = __fmul_rn(__fmul_rn(g, sg), u);
+              }
+            }
+          } else {
+            float *crow = p.C + (int64_t)m * p.ldc + n0 + cb;
+            const float *rrow = p.residual ? p.residual + (int64_t)m * p.ldr + n0 + cb : nullptr;
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const int n = n0 + cb + j;
+              if (n < p.N) {
+                float y = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
+                if (p.bias)
+                  y = __fadd_rn(y, __ldg(p.bias + n));
+                if (rrow)
+                  y = __fadd_rn(rrow[j], y);
+                crow[j] = y;
+              }
+            }
+          }
+        }
+      }
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    if (*ab) {   // copies of an abandoned tile may still be in flight: let them land before the CTA ends
+      const unsigned long long t0 = now_ns();
+      while (now_ns() - t0 < 2000000ull) {
+      }
+    }
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
+  }
+}
+
+// A[M,K] f32 -> hi/lo bf16 [Mpad, Kp] in the k order of the packed weight rows.
+// Optional RMSNorm of every row first (y = w * (x * r), subgraph0_decode_simplify.mlir:60-72).
+__global__ void split_activations_kernel(const float *A, int64_t lda, int M, int K, int Kp,
+                                         const float *norm_w, float eps,
+                                         __nv_bfloat16 *hi, __nv_bfloat16 *lo) {
+  const int m = blockIdx.x;
+  __shared__ float s_red[32];
+  float r = 1.f;
+  const bool live = m < M;
+  if (norm_w != nullptr) {
+    float ss = 0.f;
+    if (live)
+      for (int k = threadIdx.x; k < K; k += blockDim.x) {
+        const float x = A[(int64_t)m * lda + k];
+        ss += x * x;
+      }
+    ss = warp_sum(ss);
+    if ((threadIdx.x & 31) == 0)
+      s_red[threadIdx.x >> 5] = ss;
+    __syncthreads();
+    float t = 0.f;
+    for (int w = 0; w < (int)(blockDim.x + 31) / 32; ++w)
+      t += s_red[w];
+    r = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), eps));
+  }
+  for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
+    float a = 0.f;
+    if (live && k < K) {
+      a = A[(int64_t)m * lda + k];
+      if (norm_w != nullptr)
+        a = __fmul_rn(norm_w[k], __fmul_rn(a, r));
+    }
+    const __nv_bfloat16 h = __float2bfloat16_rn(a);
+    const __nv_bfloat16 l = __float2bfloat16_rn(a - __bfloat162float(h));
+    const int64_t pos = k < K ? packed_offset(B200_W_I8, K, k, nullptr) : k;
+    hi[(int64_t)m * Kp + pos] = h;
+    lo[(int64_t)m * Kp + pos] = l;
+  }
+}
+
+using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
+                              const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
+                              CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeFn encode_fn() {
+  static EncodeFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void *p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeFn>(p);
+  });
+  return fn;
+}
+
+int make_map(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, void *base, uint64_t inner, uint64_t rows,
+             uint64_t pitch_bytes, CUtensorMapSwizzle swz) {
+  EncodeFn fn = encode_fn();
+  if (!fn)
+    return fail(B200_ECUDA, "gemm_w8: cuTensorMapEncodeTiled is not available from this driver");
+  const cuuint64_t dims[2] = {inner, rows};
+  const cuuint64_t strides[1] = {pitch_bytes};
+  const cuuint32_t box[2] = {(cuuint32_t)(elem_bytes == 1 ? BK : BK), 128};
+  const cuuint32_t estr[2] = {1, 1};
+  const CUresult rc = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (rc != CUDA_SUCCESS)
+    return fail(B200_ECUDA, "gemm_w8: cuTensorMapEncodeTiled failed (%d)", (int)rc);
+  return B200_OK;
+}
+
+} // namespace
+
+} // namespace b200
+
+using namespace b200;
+
+extern "C" {
+
+int64_t b200_gemm_w8_workspace_bytes(int M, int64_t K) {
+  if (M < 1 || K < 1)
+    return 0;
+  const int64_t Mp = (M + BM - 1) / BM * BM, Kp = packed_k(B200_W_I8, K);
+  return 2 * Mp * Kp * 2 + 256;   // hi and lo, bf16; + an error word
+}
+
+int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
+                 const float *residual, int64_t ldr, const float *norm_weight, float norm_eps,
+                 int silu_pairs, void *workspace, int64_t workspace_bytes, void *stream) {
+  if (!w || !A || !C || !workspace)
+    return fail(B200_EINVAL, "gemm_w8: null argument");
+  if (w->kind != B200_W_I8 || w->scale_dtype != B200_F32 || !w->scale || !w->w)
+    return fail(B200_EINVAL, "gemm_w8: int8 per-channel weights with f32 scales expected");
+  if (M < 1 || w->K % BK != 0 || w->N < 1 || (silu_pairs && (w->N & 1)))
+    return fail(B200_EINVAL, "gemm_w8: M >= 1, K a multiple of %d, even N for gate/up pairs", BK);
+  if (((uintptr_t)w->w & 15) || ((uintptr_t)workspace & 255))
+    return fail(B200_EINVAL, "gemm_w8: weight rows must be 16-byte aligned, the workspace 256-byte aligned");
+  if (workspace_bytes < b200_gemm_w8_workspace_bytes(M, w->K))
+    return fail(B200_EINVAL, "gemm_w8: workspace too small");
+  if (int rc = ensure_device())
+    return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int K = (int)w->K, N = (int)w->N;
+  const int Mp = (M + BM - 1) / BM * BM;
+  int *err = reinterpret_cast<int *>(workspace);
+  __nv_bfloat16 *hi = reinterpret_cast<__nv_bfloat16 *>((char *)workspace + 256);
+  __nv_bfloat16 *lo = hi + (int64_t)Mp * K;
+  B200_CUDA(cudaMemsetAsync(err, 0, 4, st));
+  split_activations_kernel<<<Mp, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
+  B200_LAUNCH_CHECK();
+  CUtensorMap map_hi, map_lo, map_w;
+  if (int rc = make_map(&map_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hi, K, Mp, (uint64_t)K * 2, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_map(&map_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lo, K, Mp, (uint64_t)K * 2, CU_TENSOR_MAP_SWIZZLE_128B))
+    return rc;
+  if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, const_cast<void *>(w->w), K, N, (uint64_t)K,
+                        CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  GemmParams p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.scale = (const float *)w->scale;
+  p.bias = (const float *)w->bias;
+  p.residual = residual;
+  p.C = C;
+  p.ldc = ldc;
+  p.ldr = ldr;
+  p.silu_pairs = silu_pairs;
+  p.error = err;
+  static bool configured[64] = {};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  const int smem = kStages * STAGE_BYTES + 1024 + 256;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64)
+      configured[dev] = true;
+  }
+  dim3 grid((N + BN - 1) / BN, Mp / BM);
+  gemm_w8_tc_kernel<<<grid, kThreads, smem, st>>>(map_hi, map_lo, map_w, p);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+/* 0, or the code of the first bounded wait that gave up in the last b200_gemm_w8 on this workspace
+ * (reads the error word; synchronises the stream). */
+int b200_gemm_w8_status(void *workspace, void *stream) {
+  if (!workspace)
+    return fail(B200_EINVAL, "gemm_w8_status: null workspace");
+  int code = 0;
+  B200_CUDA(cudaMemcpyAsync(&code, workspace, 4, cudaMemcpyDeviceToHost, (cudaStream_t)stream));
+  B200_CUDA(cudaStreamSynchronize((cudaStream_t)stream));
+  if (code != 0)
+    return fail(B200_ECUDA, "gemm_w8: a bounded wait gave up (code %d)", code);
+  return B200_OK;
+}
+
+} // extern "C"

@@ -149,6 +149,27 @@ typedef struct {
 
 int b200_gemv(const b200_weight *w, const b200_gemv_args *a, void *stream);
 
+/* Dense weight-only GEMM for prefill and batched decode, on the tcgen05 tensor
+ * cores: C[M,N] = A[M,K] * dequant(W)^T (+ bias) (+ residual), or, with
+ * silu_pairs, C[M,N/2] = silu(gate) * up over interleaved (gate, up) rows.
+ * Replaces the prefill matmul of
+ * midend/lib/Conversion/MatMulOptimization/MatMulBlisVectorization.cpp:367-530
+ * (dequantisation fused into the B packing; known answer
+ * examples/BuddyMatmul/dequant-matmul-vectorization-blis-prefill.mlir:113-115).
+ * w: int8 per-channel packed rows as for b200_gemv (f32 scales, optional
+ * bias), K a multiple of 64.  A: f32 [M, lda] on the device; norm_weight (or
+ * NULL): RMSNorm of every row of A first.  The f32 activations are split into
+ * two bf16 terms (16 significant bits), int8 -> bf16 is exact, accumulation is
+ * f32 in tensor memory.  workspace: b200_gemm_w8_workspace_bytes(M, K) bytes,
+ * 256-byte aligned, owned by the caller (it holds the split activations and an
+ * error word).  b200_gemm_w8_status() reports a bounded wait that gave up. */
+int64_t b200_gemm_w8_workspace_bytes(int M, int64_t K);
+int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda,
+                 float *C, int64_t ldc, const float *residual, int64_t ldr,
+                 const float *norm_weight, float norm_eps, int silu_pairs,
+                 void *workspace, int64_t workspace_bytes, void *stream);
+int b200_gemm_w8_status(void *workspace, void *stream);
+
 /* ------------------------------------------------------------------------
  * Small fused ops (f32).
  * ---------------------------------------------------------------------- */

@@ -61,3 +61,22 @@ def gemv(kind, wbuf, sbuf, K, N, x, *, group=0, scale_dtype=_lib.F32, bias=None,
     _lib.check(lib.b200_gemv(C.byref(w), C.byref(a), stream()))
     sync()
     return y
+
+
+def gemm_w8(wbuf, sbuf, K, N, A, *, bias=None, residual=None, norm_w=None, eps=1e-6, silu=False):
+    """C = A * dequant(W)^T through b200_gemm_w8 (the tcgen05 path)."""
+    lib = _lib.load()
+    M = A.shape[0]
+    w = _lib.Weight(_lib.W_I8, 0, K, N, wbuf.data_ptr(), sbuf.data_ptr(), _lib.F32, 0,
+                    bias.data_ptr() if bias is not None else None)
+    ncol = N // 2 if silu else N
+    Cd = torch.zeros((M, ncol), dtype=torch.float32, device="cuda")
+    nbytes = lib.b200_gemm_w8_workspace_bytes(M, K)
+    ws = torch.zeros(nbytes, dtype=torch.uint8, device="cuda")
+    _lib.check(lib.b200_gemm_w8(C.byref(w), ptr(A), M, A.stride(0), ptr(Cd), ncol,
+                                ptr(residual) if residual is not None else None,
+                                residual.stride(0) if residual is not None else 0,
+                                ptr(norm_w) if norm_w is not None else None, eps, int(silu),
+                                ptr(ws), nbytes, stream()))
+    _lib.check(lib.b200_gemm_w8_status(ptr(ws), stream()))
+    return Cd
