@@ -103,6 +103,7 @@ def load():
         "b200_model_read_new_kv_rows": (i32, [vp, vp]),
         "b200_model_decode": (i32, [vp, i32, i32, vp, C.POINTER(C.c_int)]),
         "b200_model_generate": (i32, [vp, i32, i32, i32, vp]),
+        "b200_model_prefill": (i32, [vp, vp, i32, i32, vp, i32, C.POINTER(C.c_int)]),
         "b200_model_last_ms": (f32, [vp]),
         "b200_model_step_bytes": (i64, [vp, i32]),
         "b200_model_kernels_per_step": (i32, [vp]),

@@ -126,6 +126,14 @@ __host__ __device__ inline int64_t packed_offset(int kind, int64_t K, int64_t k,
   return unit_off + el * 4; // f32: one group of 4 floats, byte offset
 }
 
+// prefill.cu: the row-batched small ops around the dense GEMMs
+int embed_rows_launch(const float *table, const int32_t *tokens_dev, float *x, int64_t H, int M, cudaStream_t st);
+int rope_kv_rows_launch(float *qkv, int64_t ld, float *k_cache, float *v_cache, const float *inv_freq,
+                        const float *q_norm, const float *k_norm, float eps, int q_heads, int kv_heads, int D,
+                        int max_len, int pos0, int M, cudaStream_t st);
+int gqa_prefill_launch(const float *qkv, int64_t ld, const float *kc, const float *vc, float *out, int64_t ldo,
+                       int q_heads, int kv_heads, int D, int max_len, int pos0, int M, cudaStream_t st);
+
 __device__ __forceinline__ float load_as_float(const void *p, int dtype,
                                                int64_t i) {
   if (dtype == B200_F32)

@@ -242,6 +242,12 @@ struct b200_model {
   const float **lvec_dev = nullptr;
   uint2 *ll_buf = nullptr;           // tagged activation buffers
   long long *d_trace = nullptr;
+  // prefill (many rows at once): activations of all rows, grown on demand
+  float *pf_x = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_mid = nullptr, *pf_logits = nullptr;
+  void *pf_ws = nullptr;
+  int32_t *pf_tokens = nullptr;
+  int pf_rows = 0, pf_logit_rows = 0;
+  int64_t pf_ws_bytes = 0;
   // tensor-parallel sums by peer stores (see TpPush): this rank's staging buffer and everybody's
   uint2 *tp_ll = nullptr;
   void *tp_opened[kTpMaxRanks] = {};
@@ -816,6 +822,8 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->d_state); cudaFree(m->d_history);
   cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
   cudaFree(m->ll_buf); cudaFree(m->d_trace);
+  cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_logits);
+  cudaFree(m->pf_ws); cudaFree(m->pf_tokens);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
   if (m->h_rows_pinned) cudaFreeHost(m->h_rows_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
@@ -1338,6 +1346,125 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
   B200_CUDA(cudaStreamSynchronize(m->stream));
   B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
   return check_step_error(m);
+}
+
+// One projection over M rows: the dense tensor-core GEMM for int8 per-channel
+// weights, else the GEMV kernel sixteen rows at a time.
+static int linear_rows(b200_model *m, const DevLinear &L, const float *X, int64_t ldx, int M, float *Y,
+                       int64_t ldy, const float *residual, const float *norm_w, bool silu) {
+  if (L.w.kind == B200_W_I8 && L.w.scale_dtype == B200_F32 && L.w.K % 64 == 0)
+    return b200_gemm_w8(&L.w, X, M, ldx, Y, ldy, residual, ldy, norm_w, m->cfg.eps, silu ? 1 : 0, m->pf_ws,
+                        m->pf_ws_bytes, m->stream);
+  for (int m0 = 0; m0 < M; m0 += 16) {
+    b200_gemv_args a{};
+    a.x = X + (int64_t)m0 * ldx;
+    a.x_dtype = B200_F32;
+    a.y_dtype = B200_F32;
+    a.x_ld = ldx;
+    a.y_ld = ldy;
+    a.y = Y + (int64_t)m0 * ldy;
+    a.residual = residual ? residual + (int64_t)m0 * ldy : nullptr;
+    a.norm_weight = norm_w;
+    a.norm_eps = m->cfg.eps;
+    a.M = M - m0 < 16 ? M - m0 : 16;
+    a.silu_pairs = silu ? 1 : 0;
+    if (int rc = b200_gemv(&L.w, &a, m->stream)) return rc;
+  }
+  return B200_OK;
+}
+
+static int prefill_reserve(b200_model *m, int rows, int logit_rows) {
+  const b200_model_config &c = m->cfg;
+  const int D = c.head_dim;
+  const int64_t QKV = (int64_t)(m->qh + 2 * m->kvh) * D;
+  if (rows > m->pf_rows) {
+    cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_ws);
+    cudaFree(m->pf_tokens);
+    m->pf_x = m->pf_qkv = m->pf_att = m->pf_mid = nullptr;
+    m->pf_ws = nullptr;
+    m->pf_tokens = nullptr;
+    m->pf_rows = 0;
+    int64_t Kmax = c.hidden > m->ffn ? c.hidden : m->ffn;
+    if ((int64_t)m->qh * D > Kmax) Kmax = (int64_t)m->qh * D;
+    m->pf_ws_bytes = b200_gemm_w8_workspace_bytes(rows, Kmax);
+    if (int rc = dev_alloc((void **)&m->pf_x, (size_t)rows * c.hidden * 4)) return rc;
+    if (int rc = dev_alloc((void **)&m->pf_qkv, (size_t)rows * QKV * 4)) return rc;
+    if (int rc = dev_alloc((void **)&m->pf_att, (size_t)rows * m->qh * D * 4)) return rc;
+    if (int rc = dev_alloc((void **)&m->pf_mid, (size_t)rows * m->ffn * 4)) return rc;
+    if (int rc = dev_alloc(&m->pf_ws, (size_t)m->pf_ws_bytes)) return rc;
+    B200_CUDA(cudaMemset(m->pf_ws, 0, 256));   // the GEMM's error word (float projections never touch it)
+    if (int rc = dev_alloc((void **)&m->pf_tokens, (size_t)rows * 4)) return rc;
+    m->pf_rows = rows;
+  }
+  if (logit_rows > m->pf_logit_rows) {
+    cudaFree(m->pf_logits);
+    m->pf_logits = nullptr;
+    m->pf_logit_rows = 0;
+    if (int rc = dev_alloc((void **)&m->pf_logits, (size_t)logit_rows * c.vocab * 4)) return rc;
+    m->pf_logit_rows = logit_rows;
+  }
+  return B200_OK;
+}
+
+int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens, int pos0, float *logits_host,
+                       int all_rows, int *next_token) {
+  if (!m || !tokens)
+    return fail(B200_EINVAL, "prefill: null argument");
+  if (!m->finalized)
+    return fail(B200_ESTATE, "prefill: call b200_model_finalize first");
+  if (m->tp != 1)
+    return fail(B200_ESTATE, "prefill: single-GPU sessions only (tensor-parallel sessions feed the prompt through decode)");
+  const b200_model_config &c = m->cfg;
+  if (n_tokens < 1 || pos0 < 0 || pos0 + n_tokens > c.max_len)
+    return fail(B200_EINVAL, "prefill: %d rows from position %d exceed max_len %d", n_tokens, pos0, c.max_len);
+  for (int i = 0; i < n_tokens; ++i)
+    if (tokens[i] < 0 || tokens[i] >= c.vocab)
+      return fail(B200_EINVAL, "prefill: token %d at row %d out of range", tokens[i], i);
+  const int M = n_tokens, D = c.head_dim, H = c.hidden;
+  const int64_t QD = (int64_t)m->qh * D, KD = (int64_t)m->kvh * D, QKV = QD + 2 * KD;
+  const int logit_rows = (all_rows && logits_host) ? M : 1;
+  if (int rc = prefill_reserve(m, M, logit_rows)) return rc;
+  cudaStream_t st = m->stream;
+  B200_CUDA(cudaEventRecord(m->ev0, st));
+  B200_CUDA(cudaMemcpyAsync(m->pf_tokens, tokens, (size_t)M * 4, cudaMemcpyHostToDevice, st));
+  if (int rc = embed_rows_launch(m->embed, m->pf_tokens, m->pf_x, H, M, st)) return rc;
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer &L = m->layers[l];
+    // q | k | v (+ bias) <- RMSNorm(x)
+    if (int rc = linear_rows(m, L.qkv, m->pf_x, H, M, m->pf_qkv, QKV, nullptr, L.in_norm, false)) return rc;
+    if (int rc = rope_kv_rows_launch(m->pf_qkv, QKV, m->kv[2 * l], m->kv[2 * l + 1], m->inv_freq, L.q_norm,
+                                     L.k_norm, c.eps, m->qh, m->kvh, D, c.max_len, pos0, M, st))
+      return rc;
+    if (int rc = gqa_prefill_launch(m->pf_qkv, QKV, m->kv[2 * l], m->kv[2 * l + 1], m->pf_att, QD, m->qh,
+                                    m->kvh, D, c.max_len, pos0, M, st))
+      return rc;
+    // x1 = x + attn @ Wo ; mid = silu(gate) * up <- RMSNorm(x1) ; x2 = x1 + mid @ Wdown
+    if (int rc = linear_rows(m, L.o, m->pf_att, QD, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
+    if (int rc = linear_rows(m, L.gateup, m->pf_x, H, M, m->pf_mid, m->ffn, nullptr, L.post_norm, true)) return rc;
+    if (int rc = linear_rows(m, L.down, m->pf_mid, m->ffn, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
+  }
+  // logits: every row, or the last one only
+  const int first = logit_rows == M ? 0 : M - 1;
+  if (int rc = linear_rows(m, m->lm_head, m->pf_x + (int64_t)first * H, H, logit_rows, m->pf_logits, c.vocab,
+                           nullptr, m->final_norm, false))
+    return rc;
+  // greedy token of the last row, and the device state a following decode / generate continues from
+  const float *last_logits = m->pf_logits + (int64_t)(logit_rows - 1) * c.vocab;
+  if (int rc = b200_argmax_first(last_logits, c.vocab, m->d_state + 2, m->argmax_scratch, st)) return rc;
+  m->h_state_pinned[0] = 0;
+  m->h_state_pinned[1] = pos0 + M;
+  B200_CUDA(cudaMemcpyAsync(m->d_state + 1, m->h_state_pinned + 1, 4, cudaMemcpyHostToDevice, st));
+  B200_CUDA(cudaEventRecord(m->ev1, st));
+  if (logits_host)
+    B200_CUDA(cudaMemcpyAsync(logits_host, m->pf_logits, (size_t)logit_rows * c.vocab * 4, cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaMemcpyAsync(m->h_state_pinned, m->d_state, 32, cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
+  m->rows_fresh = false;
+  if (int rc = b200_gemm_w8_status(m->pf_ws, st)) return rc;
+  if (next_token)
+    *next_token = m->h_state_pinned[2];
+  return B200_OK;
 }
 
 int b200_model_read_new_kv_rows(b200_model *m, float *host) {

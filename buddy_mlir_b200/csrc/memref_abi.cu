@@ -662,13 +662,15 @@ int b200_forward_prefill(const b200_model_config *cfg, const char *variant, int 
   ForwardSession &s = g_fwd;
   if (int rc = session_for(s, cfg, variant, all_linear_w8, w0, n0, w1, n1)) return rc;
   const int nbuf = 2 * cfg->n_layers;
-  const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len, V = cfg->vocab;
+  const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len;
   s.valid_rows = 0;
-  // Row i of a causal prefill is the decode step of token i at position i over
-  // the rows before it: the rows go through the device decode path one by one,
-  // and the cache stays on the device for the decode calls that follow.
-  for (int i = 0; i < n_rows; ++i) {
-    if (int rc = b200_model_decode(s.model, (int)tokens[i], i, logits_out + (size_t)i * V, nullptr))
+  // All rows in one pass (dense GEMMs + causal attention); the cache stays on the
+  // device for the decode calls that follow.
+  {
+    std::vector<int32_t> ids((size_t)n_rows);
+    for (int i = 0; i < n_rows; ++i)
+      ids[(size_t)i] = (int32_t)tokens[i];
+    if (int rc = b200_model_prefill(s.model, ids.data(), n_rows, 0, logits_out, 1, nullptr))
       return rc;
   }
   for (int b = 0; b < nbuf; ++b) {

@@ -130,14 +130,36 @@ class ModelSession:
         self.position_ += steps
         return out
 
-    def prefill(self, tokens):
-        """The reference prefills with a separate compiled function
-        (gen_session.py:1345-1373).  Here the prompt is fed through the decode
-        path token by token, which leaves the same KV cache and last-row
-        logits."""
+    def prefill(self, tokens, dense=None):
+        """ModelSession::prefill (gen_session.py:1345-1373): the whole prompt from
+        position 0; afterwards logits_data() is the last prompt row's logits.
+        dense=True runs all rows at once (tensor-core GEMMs, b200_model_prefill),
+        dense=False feeds the prompt through the decode path token by token;
+        the default takes the dense path for prompts of 16 tokens or more on
+        single-GPU sessions.  Both leave the same KV cache."""
         self.reset_position()
+        if dense is None:
+            dense = len(tokens) >= 16 and self.tp_size == 1
+        if dense:
+            self.prefill_rows(tokens, 0, all_rows=False)
+            return
         for t in tokens:
             self.decode(int(t))
+
+    def prefill_rows(self, tokens, pos0=None, all_rows=True):
+        """Rows at positions pos0.. in one pass; returns the logits ([n, vocab] or the
+        last row) and moves the position behind them."""
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        pos0 = self.position_ if pos0 is None else pos0
+        n = toks.size
+        out = np.zeros((n, self.cfg.vocab) if all_rows else (self.cfg.vocab,), dtype=np.float32)
+        nxt = C.c_int()
+        _lib.check(self.lib.b200_model_prefill(self._h, toks.ctypes.data, n, pos0, out.ctypes.data,
+                                               int(all_rows), C.byref(nxt)))
+        self.position_ = pos0 + n
+        np.copyto(self._logits, out[-1] if all_rows else out)
+        self.last_next_token = nxt.value
+        return out
 
     def reset_position(self):
         self.position_ = 0

@@ -303,6 +303,18 @@ int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
  * receives the `steps` generated ids. */
 int b200_model_generate(b200_model *m, int token, int pos, int steps,
                         int *tokens_out);
+/* Prefill: n_tokens prompt rows at positions pos0 .. pos0 + n_tokens - 1 in one
+ * pass (the reference's compiled forward_prefill,
+ * tools/buddy-codegen/gen_session.py:1345-1373, pipeline
+ * tools/buddy-codegen/compile_pipeline.py:207-220): dense tensor-core GEMMs
+ * (b200_gemm_w8) for int8 projections, causal attention over the cache rows
+ * written so far (frontend/Python/ops/tosa.py:4326-4700), K/V rows left in the
+ * device cache.  logits_host: [n_tokens, vocab] when all_rows != 0, else
+ * [vocab] (the last row), or NULL.  next_token (optional): first maximum of
+ * the last row.  Single-GPU sessions. */
+int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens,
+                       int pos0, float *logits_host, int all_rows,
+                       int *next_token);
 /* Timing of the last decode/generate call, CUDA events on the session's
  * stream (ms). */
 float b200_model_last_ms(const b200_model *m);

@@ -210,6 +210,39 @@ def test_persistent_kernel_matches_checker_and_graph_path(cfg, monkeypatch):
     g.close()
 
 
+# ---- prefill: all prompt rows in one pass (dense GEMMs) --------------------------------------
+@pytest.mark.parametrize("cfg,quant", [(TINY_MEGA, "w8"), (TINY_QWEN2, "w8"), (TINY_QWEN3, "w8"), (TINY_QWEN2, None)])
+def test_dense_prefill_matches_checker_rows_and_cache(cfg, quant):
+    """Every prompt row's logits and the KV rows left behind equal the checker's
+    token-by-token pass; decode then continues from the prefilled cache."""
+    blob, views = synthetic.make_f32_blob(cfg, 51)
+    kinds = {n: "w8" for n in ALL_LINEAR} if quant else None
+    om = orc.OracleModel(cfg, views, kinds=kinds)
+    s = ModelSession(cfg)
+    s.load_tensors(views, quantize_to=quant)
+    prompt = synthetic.prompt_tokens(cfg, 8, 40)
+    logits = s.prefill_rows(prompt, 0, all_rows=True)
+    for i, t in enumerate(prompt):
+        want = om.decode(int(t))
+        assert maxrel(logits[i], want) < 1e-3, i
+        assert greedy_sample(logits[i]) == greedy_sample(want)
+    assert s.last_next_token == greedy_sample(logits[-1])
+    for b in range(2 * cfg.n_layers):
+        assert maxrel(s.kv_download(b)[:, :40], om.kv[b][:, :40]) < 1e-4
+    # a second chunk on top of the first (rows 40..55), then free-running decode
+    more = synthetic.prompt_tokens(cfg, 9, 16)
+    logits = s.prefill_rows(more, all_rows=False)
+    for t in more:
+        want = om.decode(int(t))
+    assert maxrel(logits, want) < 1e-3
+
+    def step(t):
+        s.decode(t)
+        return s.logits_data().copy()
+    check_stream(step, om, [greedy_sample(want)], 1e-3, n_greedy=12)
+    s.close()
+
+
 # ---- full-size shapes -------------------------------------------------------------------
 @pytest.fixture(scope="module")
 def full_weights():
@@ -273,6 +306,14 @@ def test_1p5b_int8_all_linear_with_long_context(full_weights):
     got = [int(t) for t in s.generate(4242, 64)]
     assert got == want
     assert s.position() == cfg.max_len
+    # dense prefill of a 128-token prompt, then 16 greedy steps, against the checker
+    om.position = 0
+    prompt = synthetic.prompt_tokens(cfg, 23, 128)
+    for t in prompt:
+        want_last = om.decode(int(t))
+    s.prefill(prompt, dense=True)
+    assert maxrel(s.logits_data(), want_last) < 1e-3
+    check_stream(step, om, [greedy_sample(want_last)], 1e-3, n_greedy=16)
     s.close()
 
 
