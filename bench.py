@@ -251,6 +251,71 @@ def gemv_microbench(lib, only=None):
     return out
 
 
+GEMM_SHAPES = {
+    # name: (M, N, K): the 1.5B model's projections at the reference's prefill length and at batch 64
+    "qkv_m1024": (1024, 2048, 1536), "o_m1024": (1024, 1536, 1536), "gate_up_m1024": (1024, 17920, 1536),
+    "down_m1024": (1024, 1536, 8960), "lm_head_m1024": (1024, 151936, 1536),
+    "gate_up_m64": (64, 17920, 1536), "down_m64": (64, 1536, 8960), "lm_head_m64": (64, 151936, 1536),
+}
+
+
+def gemm_microbench(lib, only=None):
+    """Isolated b200_gemm_w8 launches (tcgen05 path): activation split + GEMM kernel, CUDA events
+    on the launching stream, int8 weights that do not fit L2 rotated between launches.
+    TFLOP/s counts 2*M*N*K once (every tile is multiplied twice on the tensor cores, once per
+    bf16 term of the f32 activations, so the tensor pipe does twice that)."""
+    import ctypes as C
+    import torch
+    from buddy_mlir_b200 import _lib
+    d = json.load(open(os.path.join(ROOT, "MEASURED_PEAKS.json"))) if os.path.exists(os.path.join(ROOT, "MEASURED_PEAKS.json")) else {}
+    peak = float(d.get("bf16_tflops_sustained", 1400.0))
+    out = {}
+    for name, (M, N, K) in GEMM_SHAPES.items():
+        if only and name != only:
+            continue
+        copies = max(2, int(300e6 // (N * K)) + 1)
+        ws_ = [torch.randint(0, 255, (N * K,), dtype=torch.uint8, device="cuda") for _ in range(copies)]
+        sc = torch.rand(N, device="cuda") * 0.01
+        A = torch.randn(M, K, device="cuda")
+        Cd = torch.zeros(M, N, device="cuda")
+        nb = lib.b200_gemm_w8_workspace_bytes(M, K)
+        ws = torch.zeros(nb, dtype=torch.uint8, device="cuda")
+        st = C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+        def launch(i):
+            w = _lib.Weight(_lib.W_I8, 0, K, N, ws_[i % copies].data_ptr(), sc.data_ptr(), _lib.F32, 0, None)
+            _lib.check(lib.b200_gemm_w8(C.byref(w), A.data_ptr(), M, K, Cd.data_ptr(), N, None, 0, None, 0.0, 0,
+                                        ws.data_ptr(), nb, st))
+        for i in range(3):
+            launch(i)
+        torch.cuda.synchronize()
+        reps = max(4, 2 * copies)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(reps):
+            launch(i)
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.check(lib.b200_gemm_w8_status(ws.data_ptr(), st))
+        us = e0.elapsed_time(e1) * 1000.0 / reps
+        tf = 2.0 * M * N * K / us / 1e6
+        out[name] = {"M": M, "N": N, "K": K, "us": round(us, 1), "TFLOP/s": round(tf, 1),
+                     "frac_of_bf16_sustained": round(tf / peak, 3), "tensor_pipe_frac": round(2 * tf / peak, 3)}
+    return {"shapes": out, "peak_tflops": peak,
+            "note": "frac = algorithmic 2MNK / time / measured sustained bf16 peak; the tensor pipe does twice the "
+                    "algorithmic work (two bf16 terms per f32 activation)"}
+
+
+def run_gemm_only(args):
+    import torch
+    from buddy_mlir_b200 import _lib
+    lib = _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    print(json.dumps({"gemm_isolated": gemm_microbench(lib, args.gemm_shape)}))
+
+
 def run_gemv_only(args):
     """--gemv-only: just the isolated GEMV sweep (one JSON line); --gemv-shape picks one shape,
     which keeps a profiler capture of that kernel small."""
@@ -362,6 +427,8 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--gemv-only", action="store_true", help="run only the isolated GEMV sweep")
     ap.add_argument("--gemv-shape", default=None, help="with --gemv-only: one shape of GEMV_SHAPES")
+    ap.add_argument("--gemm-only", action="store_true", help="run only the isolated dense-GEMM sweep (tcgen05 path)")
+    ap.add_argument("--gemm-shape", default=None, help="with --gemm-only: one shape of GEMM_SHAPES")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the isolated-GEMV, end-to-end and CPU legs (for profiler captures)")
     args = ap.parse_args()
@@ -374,6 +441,8 @@ def main():
         return run_reference(args)
     if args.gemv_only:
         return run_gemv_only(args)
+    if args.gemm_only:
+        return run_gemm_only(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single(args)
     import bench_tp

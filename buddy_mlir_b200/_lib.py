@@ -104,6 +104,15 @@ def load():
         "b200_model_decode": (i32, [vp, i32, i32, vp, C.POINTER(C.c_int)]),
         "b200_model_generate": (i32, [vp, i32, i32, i32, vp]),
         "b200_model_prefill": (i32, [vp, vp, i32, i32, vp, i32, C.POINTER(C.c_int)]),
+        "b200_batch_create": (i32, [vp, i32, i32, i32, i32, C.POINTER(vp)]),
+        "b200_batch_destroy": (None, [vp]),
+        "b200_batch_add": (i32, [vp, C.POINTER(C.c_int)]),
+        "b200_batch_remove": (i32, [vp, i32]),
+        "b200_batch_length": (i32, [vp, i32]),
+        "b200_batch_free_pages": (i32, [vp]),
+        "b200_batch_prefill": (i32, [vp, i32, vp, i32, vp, C.POINTER(C.c_int)]),
+        "b200_batch_decode": (i32, [vp, i32, vp, vp, vp, vp]),
+        "b200_batch_last_ms": (f32, [vp]),
         "b200_model_last_ms": (f32, [vp]),
         "b200_model_step_bytes": (i64, [vp, i32]),
         "b200_model_kernels_per_step": (i32, [vp]),

@@ -134,6 +134,15 @@ int rope_kv_rows_launch(float *qkv, int64_t ld, float *k_cache, float *v_cache, 
 int gqa_prefill_launch(const float *qkv, int64_t ld, const float *kc, const float *vc, float *out, int64_t ldo,
                        int q_heads, int kv_heads, int D, int max_len, int pos0, int M, cudaStream_t st);
 
+int rope_kv_paged_launch(float *qkv, int64_t ld, float *k_pool, float *v_pool, const float *inv_freq,
+                         const float *q_norm, const float *k_norm, float eps, int q_heads, int kv_heads, int D,
+                         int page, const int32_t *row_seq, const int32_t *row_pos, const int32_t *block_table,
+                         int table_stride, int M, cudaStream_t st);
+int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out, int64_t ldo,
+                     int q_heads, int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
+                     const int32_t *block_table, int table_stride, int M, cudaStream_t st);
+int argmax_rows_launch(const float *v, int64_t n, int rows, int32_t *out, cudaStream_t st);
+
 __device__ __forceinline__ float load_as_float(const void *p, int dtype,
                                                int64_t i) {
   if (dtype == B200_F32)

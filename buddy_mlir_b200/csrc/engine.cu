@@ -1467,6 +1467,194 @@ int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens, int p
   return B200_OK;
 }
 
+// ---- batched decode over a paged KV cache ------------------------------------------------
+struct b200_batch {
+  b200_model *m = nullptr;
+  int max_seqs = 0, page = 0, n_pages = 0, table_stride = 0;
+  std::vector<float *> pool;            // [2 * layers] page pools [n_pages][kv_heads][page][D]
+  std::vector<int> free_pages;
+  std::vector<int> len;                 // per sequence: -1 = unused slot
+  std::vector<int32_t> table;           // [max_seqs][table_stride] host mirror
+  int32_t *d_table = nullptr, *d_seq = nullptr, *d_pos = nullptr, *d_next = nullptr;
+  int rows_cap = 0;
+  float last_ms = 0.f;
+};
+
+static int batch_rows(b200_batch *b, int M, const int32_t *tokens, const int32_t *row_seq, const int32_t *row_pos,
+                      bool all_logits, float *logits_host, int32_t *next_host) {
+  b200_model *m = b->m;
+  const b200_model_config &c = m->cfg;
+  const int D = c.head_dim, H = c.hidden;
+  const int64_t QD = (int64_t)m->qh * D, KD = (int64_t)m->kvh * D, QKV = QD + 2 * KD;
+  const int logit_rows = all_logits ? M : 1;
+  if (int rc = prefill_reserve(m, M, logit_rows)) return rc;
+  cudaStream_t st = m->stream;
+  if (M > b->rows_cap) {
+    cudaFree(b->d_seq); cudaFree(b->d_pos); cudaFree(b->d_next);
+    b->d_seq = b->d_pos = b->d_next = nullptr;
+    b->rows_cap = 0;
+    if (int rc = dev_alloc((void **)&b->d_seq, (size_t)M * 4)) return rc;
+    if (int rc = dev_alloc((void **)&b->d_pos, (size_t)M * 4)) return rc;
+    if (int rc = dev_alloc((void **)&b->d_next, (size_t)M * 4)) return rc;
+    b->rows_cap = M;
+  }
+  B200_CUDA(cudaEventRecord(m->ev0, st));
+  B200_CUDA(cudaMemcpyAsync(m->pf_tokens, tokens, (size_t)M * 4, cudaMemcpyHostToDevice, st));
+  B200_CUDA(cudaMemcpyAsync(b->d_seq, row_seq, (size_t)M * 4, cudaMemcpyHostToDevice, st));
+  B200_CUDA(cudaMemcpyAsync(b->d_pos, row_pos, (size_t)M * 4, cudaMemcpyHostToDevice, st));
+  B200_CUDA(cudaMemcpyAsync(b->d_table, b->table.data(), b->table.size() * 4, cudaMemcpyHostToDevice, st));
+  if (int rc = embed_rows_launch(m->embed, m->pf_tokens, m->pf_x, H, M, st)) return rc;
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer &L = m->layers[l];
+    if (int rc = linear_rows(m, L.qkv, m->pf_x, H, M, m->pf_qkv, QKV, nullptr, L.in_norm, false)) return rc;
+    if (int rc = rope_kv_paged_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->inv_freq, L.q_norm,
+                                      L.k_norm, c.eps, m->qh, m->kvh, D, b->page, b->d_seq, b->d_pos, b->d_table,
+                                      b->table_stride, M, st))
+      return rc;
+    if (int rc = gqa_paged_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->pf_att, QD, m->qh, m->kvh,
+                                  D, b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M, st))
+      return rc;
+    if (int rc = linear_rows(m, L.o, m->pf_att, QD, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
+    if (int rc = linear_rows(m, L.gateup, m->pf_x, H, M, m->pf_mid, m->ffn, nullptr, L.post_norm, true)) return rc;
+    if (int rc = linear_rows(m, L.down, m->pf_mid, m->ffn, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
+  }
+  const int first = all_logits ? 0 : M - 1;
+  if (int rc = linear_rows(m, m->lm_head, m->pf_x + (int64_t)first * H, H, logit_rows, m->pf_logits, c.vocab, nullptr,
+                           m->final_norm, false))
+    return rc;
+  if (int rc = argmax_rows_launch(m->pf_logits, c.vocab, logit_rows, b->d_next, st)) return rc;
+  B200_CUDA(cudaEventRecord(m->ev1, st));
+  if (logits_host)
+    B200_CUDA(cudaMemcpyAsync(logits_host, m->pf_logits, (size_t)logit_rows * c.vocab * 4, cudaMemcpyDeviceToHost, st));
+  if (next_host)
+    B200_CUDA(cudaMemcpyAsync(next_host, b->d_next, (size_t)logit_rows * 4, cudaMemcpyDeviceToHost, st));
+  B200_CUDA(cudaStreamSynchronize(st));
+  B200_CUDA(cudaEventElapsedTime(&b->last_ms, m->ev0, m->ev1));
+  return b200_gemm_w8_status(m->pf_ws, st);
+}
+
+// pages for positions [len, len + n) of a sequence
+static int batch_grow(b200_batch *b, int seq, int n) {
+  const int have = (b->len[seq] + b->page - 1) / b->page, want = (b->len[seq] + n + b->page - 1) / b->page;
+  if (want > b->table_stride)
+    return fail(B200_ELIMIT, "batch: sequence %d would exceed the context limit of %d positions", seq,
+                b->table_stride * b->page);
+  if (want - have > (int)b->free_pages.size())
+    return fail(B200_ENOMEM, "batch: the page pool is exhausted (%d pages)", b->n_pages);
+  for (int i = have; i < want; ++i) {
+    b->table[(size_t)seq * b->table_stride + i] = b->free_pages.back();
+    b->free_pages.pop_back();
+  }
+  return B200_OK;
+}
+
+int b200_batch_create(b200_model *m, int max_seqs, int page_size, int n_pages, int max_context, b200_batch **out) {
+  if (!m || !out || max_seqs < 1 || page_size < 1 || n_pages < 1 || max_context < 1)
+    return fail(B200_EINVAL, "batch_create: bad argument");
+  if (!m->finalized || m->tp != 1)
+    return fail(B200_ESTATE, "batch_create: a finalised single-GPU model is required");
+  b200_batch *b = new b200_batch();
+  b->m = m;
+  b->max_seqs = max_seqs;
+  b->page = page_size;
+  b->n_pages = n_pages;
+  b->table_stride = (max_context + page_size - 1) / page_size;
+  b->len.assign(max_seqs, -1);
+  b->table.assign((size_t)max_seqs * b->table_stride, 0);
+  for (int i = n_pages - 1; i >= 0; --i)
+    b->free_pages.push_back(i);
+  const size_t pool_bytes = (size_t)n_pages * m->kvh * page_size * m->cfg.head_dim * 4;
+  b->pool.assign(2 * m->cfg.n_layers, nullptr);
+  int rc = B200_OK;
+  for (auto &p : b->pool)
+    if (rc == B200_OK) rc = dev_alloc((void **)&p, pool_bytes);
+  if (rc == B200_OK) rc = dev_alloc((void **)&b->d_table, b->table.size() * 4);
+  if (rc != B200_OK) {
+    b200_batch_destroy(b);
+    return rc;
+  }
+  *out = b;
+  return B200_OK;
+}
+
+void b200_batch_destroy(b200_batch *b) {
+  if (!b) return;
+  for (auto p : b->pool) cudaFree(p);
+  cudaFree(b->d_table); cudaFree(b->d_seq); cudaFree(b->d_pos); cudaFree(b->d_next);
+  delete b;
+}
+
+int b200_batch_add(b200_batch *b, int *seq) {
+  if (!b || !seq)
+    return fail(B200_EINVAL, "batch_add: null argument");
+  for (int i = 0; i < b->max_seqs; ++i)
+    if (b->len[i] < 0) {
+      b->len[i] = 0;
+      *seq = i;
+      return B200_OK;
+    }
+  return fail(B200_ELIMIT, "batch_add: all %d sequence slots are in use", b->max_seqs);
+}
+
+int b200_batch_remove(b200_batch *b, int seq) {
+  if (!b || seq < 0 || seq >= b->max_seqs || b->len[seq] < 0)
+    return fail(B200_EINVAL, "batch_remove: no such sequence");
+  const int pages = (b->len[seq] + b->page - 1) / b->page;
+  for (int i = 0; i < pages; ++i)
+    b->free_pages.push_back(b->table[(size_t)seq * b->table_stride + i]);
+  b->len[seq] = -1;
+  return B200_OK;
+}
+
+int b200_batch_length(const b200_batch *b, int seq) {
+  return (b && seq >= 0 && seq < b->max_seqs) ? b->len[seq] : -1;
+}
+int b200_batch_free_pages(const b200_batch *b) { return b ? (int)b->free_pages.size() : 0; }
+float b200_batch_last_ms(const b200_batch *b) { return b ? b->last_ms : 0.f; }
+
+int b200_batch_prefill(b200_batch *b, int seq, const int32_t *tokens, int n, float *logits_host, int *next_token) {
+  if (!b || !tokens || n < 1 || seq < 0 || seq >= b->max_seqs || b->len[seq] < 0)
+    return fail(B200_EINVAL, "batch_prefill: bad argument");
+  for (int i = 0; i < n; ++i)
+    if (tokens[i] < 0 || tokens[i] >= b->m->cfg.vocab)
+      return fail(B200_EINVAL, "batch_prefill: token %d at row %d out of range", tokens[i], i);
+  if (int rc = batch_grow(b, seq, n)) return rc;
+  std::vector<int32_t> rs((size_t)n, seq), rp((size_t)n);
+  for (int i = 0; i < n; ++i)
+    rp[(size_t)i] = b->len[seq] + i;
+  int32_t nxt = 0;
+  if (int rc = batch_rows(b, n, tokens, rs.data(), rp.data(), false, logits_host, &nxt)) return rc;
+  b->len[seq] += n;
+  if (next_token) *next_token = nxt;
+  return B200_OK;
+}
+
+int b200_batch_decode(b200_batch *b, int n, const int *seqs, const int32_t *tokens, float *logits_host,
+                      int32_t *next_tokens) {
+  if (!b || !seqs || !tokens || n < 1 || n > b->max_seqs)
+    return fail(B200_EINVAL, "batch_decode: bad argument");
+  std::vector<int32_t> rs((size_t)n), rp((size_t)n);
+  std::vector<char> seen((size_t)b->max_seqs, 0);
+  for (int i = 0; i < n; ++i) {
+    const int s = seqs[i];
+    if (s < 0 || s >= b->max_seqs || b->len[s] < 0 || seen[(size_t)s])
+      return fail(B200_EINVAL, "batch_decode: sequence %d is unknown or listed twice", s);
+    if (tokens[i] < 0 || tokens[i] >= b->m->cfg.vocab)
+      return fail(B200_EINVAL, "batch_decode: token %d of sequence %d out of range", tokens[i], s);
+    seen[(size_t)s] = 1;
+  }
+  for (int i = 0; i < n; ++i)
+    if (int rc = batch_grow(b, seqs[i], 1)) return rc;
+  for (int i = 0; i < n; ++i) {
+    rs[(size_t)i] = seqs[i];
+    rp[(size_t)i] = b->len[seqs[i]];
+  }
+  if (int rc = batch_rows(b, n, tokens, rs.data(), rp.data(), true, logits_host, next_tokens)) return rc;
+  for (int i = 0; i < n; ++i)
+    b->len[seqs[i]] += 1;
+  return B200_OK;
+}
+
 int b200_model_read_new_kv_rows(b200_model *m, float *host) {
   if (!m || !host)
     return fail(B200_EINVAL, "read_new_kv_rows: null argument");

@@ -223,7 +223,10 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       const uint4 *raw = reinterpret_cast<const uint4 *>(st + 2 * A_BYTES + t * BK);
       uint8_t *dst = st + 2 * A_BYTES + WRAW_BYTES + t * 128;   // row t of the swizzled bf16 tile
 #pragma unroll
-      for (int q = 0; q < 4; ++q) {            // 16 int8 -> two 16-byte chunks of bf16
+      for (int qq = 0; qq < 4; ++qq) {         // 16 int8 -> two 16-byte chunks of bf16
+        // rows are 64 bytes apart: neighbouring threads start at different 16-byte units,
+        // so that the eight threads of a quarter warp read eight different bank groups
+        const int q = (qq + (t >> 1)) & 3;
         const uint4 w = raw[q];
         const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
         uint32_t o[8];

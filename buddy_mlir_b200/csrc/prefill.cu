@@ -184,7 +184,245 @@ int launch_prefill_attn(const float *qkv, int64_t ld, const float *kc, const flo
   return B200_OK;
 }
 
+// ---- paged cache: rows of many sequences, K/V in fixed-size pages -------------------
+// Page pool of one cache buffer: [n_pages][kv_heads][page][D] f32.  Row r of the batch
+// belongs to sequence row_seq[r] at position row_pos[r]; block_table[seq][pos / page] is
+// the page that holds the position.  (buddy-mlir has no paged cache; per sequence the
+// arithmetic is that of the contiguous cache above.)
+__global__ void rope_kv_paged_kernel(float *qkv, int64_t ld, float *k_pool, float *v_pool,
+                                     const float *inv_freq, const float *q_norm, const float *k_norm, float eps,
+                                     int q_heads, int kv_heads, int D, int page, const int32_t *row_seq,
+                                     const int32_t *row_pos, const int32_t *block_table, int table_stride) {
+  __shared__ float red[8];
+  const int half = D / 2;
+  const int j = threadIdx.x;
+  const int m = blockIdx.x, head = blockIdx.y;
+  const bool is_q = head < q_heads;
+  const int h = is_q ? head : head - q_heads;
+  float *row = qkv + (int64_t)m * ld;
+  float *p = row + (is_q ? 0 : q_heads * D) + (int64_t)h * D;
+  const float *v = row + (q_heads + kv_heads) * D + (int64_t)h * D;
+  const float *nw = is_q ? q_norm : k_norm;
+  const int pos = row_pos[m];
+  float a = 0.f, b = 0.f;
+  if (j < half) {
+    a = p[j];
+    b = p[j + half];
+  }
+  if (nw != nullptr) {
+    float s = warp_sum(__fadd_rn(__fmul_rn(a, a), __fmul_rn(b, b)));
+    if ((threadIdx.x & 31) == 0)
+      red[threadIdx.x >> 5] = s;
+    __syncthreads();
+    float t = 0.f;
+    for (int i = 0; i < (int)((blockDim.x + 31) >> 5); ++i)
+      t += red[i];
+    const float r = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)D), eps));
+    if (j < half) {
+      a = __fmul_rn(nw[j], __fmul_rn(a, r));
+      b = __fmul_rn(nw[j + half], __fmul_rn(b, r));
+    }
+  }
+  if (j >= half)
+    return;
+  const float th = __fmul_rn(inv_freq[j], (float)pos);
+  const float c = cosf(th), s = sinf(th);
+  const float oa = __fadd_rn(__fmul_rn(a, c), __fmul_rn(-b, s));
+  const float ob = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+  p[j] = oa;
+  p[j + half] = ob;
+  if (!is_q) {
+    const int pg = block_table[(int64_t)row_seq[m] * table_stride + pos / page];
+    const int64_t crow = (((int64_t)pg * kv_heads + h) * page + pos % page) * D;
+    k_pool[crow + j] = oa;
+    k_pool[crow + j + half] = ob;
+    v_pool[crow + j] = v[j];
+    v_pool[crow + j + half] = v[j + half];
+  }
+}
+
+template <int G, int VEC>
+__global__ void __launch_bounds__(128)
+gqa_paged_kernel(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out, int64_t ldo,
+                 int kv_heads, int page, const int32_t *row_seq, const int32_t *row_pos, const int32_t *block_table,
+                 int table_stride) {
+  constexpr int D = VEC * 32, W = 4;
+  const int m = blockIdx.x, hk = blockIdx.y;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int len = row_pos[m] + 1;
+  const int32_t *table = block_table + (int64_t)row_seq[m] * table_stride;
+  const float scale = rsqrtf((float)D);
+  const float *qrow = qkv + (int64_t)m * ld + (int64_t)hk * G * D;
+  float qr[G][VEC];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      qr[g][e] = qrow[g * D + lane * VEC + e];
+  float mx[G], l[G], acc[G][VEC];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    mx[g] = kSeed;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      acc[g][e] = 0.f;
+  }
+  for (int j = warp; j < len; j += W) {
+    const int pg = table[j / page];
+    const int64_t crow = (((int64_t)pg * kv_heads + hk) * page + j % page) * D + lane * VEC;
+    float kr[VEC], vr[VEC];
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) {
+      kr[e] = k_pool[crow + e];
+      vr[e] = v_pool[crow + e];
+    }
+    float s[G];
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      float d = 0.f;
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        d = fmaf(qr[g][e], kr[e], d);
+      s[g] = d;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+      for (int g = 0; g < G; ++g)
+        s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+#pragma unroll
+    for (int g = 0; g < G; ++g) {
+      s[g] *= scale;
+      const float nm = fmaxf(mx[g], s[g]);
+      const float alpha = expf(mx[g] - nm);
+      const float pw = expf(s[g] - nm);
+      l[g] = fmaf(l[g], alpha, pw);
+#pragma unroll
+      for (int e = 0; e < VEC; ++e)
+        acc[g][e] = fmaf(acc[g][e], alpha, pw * vr[e]);
+      mx[g] = nm;
+    }
+  }
+  __shared__ float s_m[W][G], s_l[W][G];
+  __shared__ float s_acc[W][G][D];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      s_m[warp][g] = mx[g];
+      s_l[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      s_acc[warp][g][lane * VEC + e] = acc[g][e];
+  }
+  __syncthreads();
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx - g * D;
+    float M = kSeed;
+#pragma unroll
+    for (int w = 0; w < W; ++w)
+      M = fmaxf(M, s_m[w][g]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const float b = expf(s_m[w][g] - M);
+      L = fmaf(s_l[w][g], b, L);
+      A = fmaf(s_acc[w][g][d], b, A);
+    }
+    out[(int64_t)m * ldo + (int64_t)(hk * G + g) * D + d] = __fdiv_rn(A, L);
+  }
+}
+
+template <int G>
+int launch_paged_attn(const float *qkv, int64_t ld, const float *kp, const float *vp, float *out, int64_t ldo,
+                      int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
+                      const int32_t *block_table, int table_stride, int M, cudaStream_t st) {
+  dim3 grid(M, kv_heads);
+  if (D == 128)
+    gqa_paged_kernel<G, 4><<<grid, 128, 0, st>>>(qkv, ld, kp, vp, out, ldo, kv_heads, page, row_seq, row_pos,
+                                                 block_table, table_stride);
+  else
+    gqa_paged_kernel<G, 2><<<grid, 128, 0, st>>>(qkv, ld, kp, vp, out, ldo, kv_heads, page, row_seq, row_pos,
+                                                 block_table, table_stride);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+// one first-maximum per row of a [rows, n] matrix (Sampler.h:101-104)
+__global__ void argmax_rows_kernel(const float *v, int64_t n, int32_t *out) {
+  const float *row = v + (int64_t)blockIdx.x * n;
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  for (int64_t i = threadIdx.x; i < n; i += blockDim.x) {
+    const float x = row[i];
+    if (x > bv || (x == bv && (int)i < bi)) {
+      bv = x;
+      bi = (int)i;
+    }
+  }
+  __shared__ float sv[32];
+  __shared__ int si[32];
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if ((threadIdx.x & 31) == 0) {
+    sv[threadIdx.x >> 5] = bv;
+    si[threadIdx.x >> 5] = bi;
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w)
+      if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) {
+        bv = sv[w];
+        bi = si[w];
+      }
+    out[blockIdx.x] = bi == 0x7fffffff ? 0 : bi;
+  }
+}
+
 } // namespace
+
+int rope_kv_paged_launch(float *qkv, int64_t ld, float *k_pool, float *v_pool, const float *inv_freq,
+                         const float *q_norm, const float *k_norm, float eps, int q_heads, int kv_heads, int D,
+                         int page, const int32_t *row_seq, const int32_t *row_pos, const int32_t *block_table,
+                         int table_stride, int M, cudaStream_t st) {
+  dim3 grid(M, q_heads + kv_heads);
+  rope_kv_paged_kernel<<<grid, D / 2 < 32 ? 32 : D / 2, 0, st>>>(qkv, ld, k_pool, v_pool, inv_freq, q_norm, k_norm, eps,
+                                                               q_heads, kv_heads, D, page, row_seq, row_pos,
+                                                               block_table, table_stride);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
+int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out, int64_t ldo,
+                     int q_heads, int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
+                     const int32_t *block_table, int table_stride, int M, cudaStream_t st) {
+  if (D != 64 && D != 128)
+    return fail(B200_EINVAL, "gqa_paged: head_dim %d (64 or 128 supported)", D);
+  switch (q_heads / kv_heads) {
+#define B200_G(G_)                                                                                          \
+  case G_:                                                                                                  \
+    return launch_paged_attn<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos,    \
+                                 block_table, table_stride, M, st);
+    B200_G(1) B200_G(2) B200_G(3) B200_G(4) B200_G(6) B200_G(8)
+#undef B200_G
+  default:
+    return fail(B200_EINVAL, "gqa_paged: group size %d not built", q_heads / kv_heads);
+  }
+}
+
+int argmax_rows_launch(const float *v, int64_t n, int rows, int32_t *out, cudaStream_t st) {
+  argmax_rows_kernel<<<rows, 256, 0, st>>>(v, n, out);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
 
 int embed_rows_launch(const float *table, const int32_t *tokens_dev, float *x, int64_t H, int M, cudaStream_t st) {
   if (H % 4 != 0)

@@ -236,3 +236,56 @@ def run_generation(session: ModelSession, prompt_tokens, max_new_tokens: int,
             break
         out.append(tok)
     return out, (count / accum if accum > 0 else 0.0)
+
+
+class BatchSession:
+    """Many sequences of different lengths over one model and a paged KV cache
+    (b200_batch_*): prefill a prompt per sequence, then advance any subset of
+    them by one token per step.  Not part of buddy-mlir's interface (its
+    sessions are single-sequence); per sequence the results are those of
+    ModelSession."""
+
+    def __init__(self, model: ModelSession, max_seqs: int, page_size: int, n_pages: int, max_context: int):
+        self.model, self.lib = model, model.lib
+        self._h = C.c_void_p()
+        _lib.check(self.lib.b200_batch_create(model._h, max_seqs, page_size, n_pages, max_context, C.byref(self._h)))
+
+    def close(self):
+        if self._h:
+            self.lib.b200_batch_destroy(self._h)
+            self._h = C.c_void_p()
+
+    def add(self) -> int:
+        s = C.c_int()
+        _lib.check(self.lib.b200_batch_add(self._h, C.byref(s)))
+        return s.value
+
+    def remove(self, seq: int):
+        _lib.check(self.lib.b200_batch_remove(self._h, seq))
+
+    def length(self, seq: int) -> int:
+        return int(self.lib.b200_batch_length(self._h, seq))
+
+    def free_pages(self) -> int:
+        return int(self.lib.b200_batch_free_pages(self._h))
+
+    def prefill(self, seq: int, tokens, want_logits=True):
+        toks = np.ascontiguousarray(tokens, dtype=np.int32)
+        out = np.zeros(self.model.cfg.vocab, dtype=np.float32) if want_logits else None
+        nxt = C.c_int()
+        _lib.check(self.lib.b200_batch_prefill(self._h, seq, toks.ctypes.data, toks.size,
+                                               out.ctypes.data if want_logits else None, C.byref(nxt)))
+        return out, nxt.value
+
+    def decode(self, seqs, tokens, want_logits=True):
+        sq = np.ascontiguousarray(seqs, dtype=np.int32)
+        tk = np.ascontiguousarray(tokens, dtype=np.int32)
+        n = sq.size
+        out = np.zeros((n, self.model.cfg.vocab), dtype=np.float32) if want_logits else None
+        nxt = np.zeros(n, dtype=np.int32)
+        _lib.check(self.lib.b200_batch_decode(self._h, n, sq.ctypes.data, tk.ctypes.data,
+                                              out.ctypes.data if want_logits else None, nxt.ctypes.data))
+        return out, nxt
+
+    def last_ms(self) -> float:
+        return float(self.lib.b200_batch_last_ms(self._h))

@@ -315,6 +315,36 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
 int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens,
                        int pos0, float *logits_host, int all_rows,
                        int *next_token);
+
+/* Batched decode over a paged KV cache: many sequences of different lengths
+ * advance one token per step through the dense tensor-core GEMMs (the weights
+ * are read once per step for all of them).  buddy-mlir has no paged cache and
+ * no batched decode entry; per sequence the arithmetic is that of
+ * b200_model_decode over a contiguous cache (the parity tests compare every
+ * sequence with the CPU restatement run on its own).  Pages: page_size
+ * positions of all kv heads, per layer and K/V buffer [n_pages][kv_heads]
+ * [page_size][head_dim] f32, handed out from a free list as sequences grow and
+ * returned by b200_batch_remove; a sequence holds at most max_context
+ * positions.  The batch borrows the model's weights and scratch: use one batch
+ * (or the model's own session calls) at a time. */
+typedef struct b200_batch b200_batch;
+int b200_batch_create(b200_model *m, int max_seqs, int page_size, int n_pages,
+                      int max_context, b200_batch **out);
+void b200_batch_destroy(b200_batch *b);
+int b200_batch_add(b200_batch *b, int *seq);
+int b200_batch_remove(b200_batch *b, int seq);
+int b200_batch_length(const b200_batch *b, int seq);
+int b200_batch_free_pages(const b200_batch *b);
+/* Append n prompt tokens to one sequence (one dense pass); logits_host: the
+ * last row [vocab] or NULL. */
+int b200_batch_prefill(b200_batch *b, int seq, const int32_t *tokens, int n,
+                       float *logits_host, int *next_token);
+/* One token for each of n distinct sequences; logits_host [n, vocab] or NULL,
+ * next_tokens [n] (first maximum per row) or NULL. */
+int b200_batch_decode(b200_batch *b, int n, const int *seqs,
+                      const int32_t *tokens, float *logits_host,
+                      int32_t *next_tokens);
+float b200_batch_last_ms(const b200_batch *b);
 /* Timing of the last decode/generate call, CUDA events on the session's
  * stream (ms). */
 float b200_model_last_ms(const b200_model *m);
