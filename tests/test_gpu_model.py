@@ -119,6 +119,26 @@ def test_tiny_w8a32_reference_blobs_through_model_entry():
     es.close()
 
 
+def test_load_weights_from_the_reference_blob_files(tmp_path):
+    """loadWeights from files named and laid out as the reference writes them
+    (tools/buddy-codegen/gen_config.py:51-71: arg0-w8a32-f32.data + arg0-w8a32-i8.data)."""
+    cfg = TINY_QWEN2
+    _, views = synthetic.make_f32_blob(cfg, 78)
+    fb, ib = synthetic.split_w8a32(cfg, views, lambda W: orc.quantize_per_channel(W, 8))
+    fp, ip = tmp_path / "arg0-w8a32-f32.data", tmp_path / "arg0-w8a32-i8.data"
+    fb.tofile(fp)
+    ib.tofile(ip)
+    om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in synthetic.QUANTISED_BY_REFERENCE})
+    s = ModelSession(cfg)
+    s.load_weights([str(fp), str(ip)], "w8a32")
+
+    def step(t):
+        s.decode(t)
+        return s.logits_data().copy()
+    check_stream(step, om, synthetic.prompt_tokens(cfg, 2, 6), 1e-3, n_greedy=6)
+    s.close()
+
+
 def test_tiny_all_linear_w8_quantised_on_device():
     cfg = TINY_QWEN2
     blob, views = synthetic.make_f32_blob(cfg, 8)
