@@ -238,19 +238,18 @@ def run(args, ClockSampler, peaks):
     launches = lib.b200_launch_count() - launches0
     clocks = sampler.stop() if rank == 0 else None
     value = steps / (ms / 1000.0)
-    # end to end: logits to host memory and host argmax every step (rank 0 drives)
+    # end to end: the host drives every step through the public call (token id in, greedy
+    # token id back to host memory); the logits stay sharded on the devices
     s.position_ = start
     tok = 11
     for _ in range(warmup):
-        s.decode(tok)
-        tok = int(np.argmax(s.logits_data()))
+        tok = s.decode_greedy(tok)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
     t0 = time.perf_counter()
     for _ in range(steps):
-        s.decode(tok)
-        tok = int(np.argmax(s.logits_data()))
+        tok = s.decode_greedy(tok)
     torch.cuda.synchronize()
     e2e_dt = torch.tensor([time.perf_counter() - t0], device="cuda")
     if world > 1:
@@ -266,7 +265,8 @@ def run(args, ClockSampler, peaks):
                 "config": dict(workload_config(cfg, start, warmup, world),
                                tp1_tokens_per_s_same_run=tp1,
                                collectives=("2 sums of 16 KB per layer by peer stores from the GEMV epilogue over NVLink "
-                                            "(tagged pairs, no collective library) + 1 NCCL all-gather of logits")
+                                            "(tagged pairs, no collective library) + one (value, index) pair per rank "
+                                            "for the greedy token, also by peer stores")
                                if s.tp_sum_kind() == 2 else
                                "2 NCCL all-reduce of 16 KB per layer + 1 all-gather of logits"),
                 "parity": parity,
@@ -275,7 +275,8 @@ def run(args, ClockSampler, peaks):
                              "kernel": "per-rank decode step (CUDA graph replay), bytes per rank",
                              "bytes_per_step_per_rank": step_bytes},
                 "e2e": {"value": steps / float(e2e_dt.item()), "unit": "tokens/s",
-                        "h2d_bytes_per_step": 16 * world, "d2h_bytes_per_step": cfg.vocab * 4 * world},
+                        "h2d_bytes_per_step": 16 * world, "d2h_bytes_per_step": 32 * world,
+                        "result": "greedy token id per step (device argmax over the vocabulary shards)"},
                 "gpu_launches": int(launches) * world, "kernels_per_step": int(launches // steps),
                 "clocks": clocks}
         print(json.dumps(line))

@@ -149,6 +149,58 @@ __global__ void tp_handshake_kernel(TpPush push, size_t at, int *ok) {
     *ok = 0;
   }
 }
+// Greedy token of a vocabulary-sharded lm_head without gathering the logits: every rank
+// holds the first maximum of its own shard; it stores (value, tag) and (global index, tag)
+// into every rank's buffer, waits (bounded) for all ranks' pairs and keeps the largest
+// value, the lowest index among equals: the MAXLOC reduction of
+// examples/BuddyTensorParallel/buddy-deepseek-r1-distributed.cpp:211-223,602-613.
+// One warp; lane t talks to rank t.  Two slots are used in turn (step parity).
+__global__ void tp_argmax_kernel(TpPush push, size_t at, const float *shard, const int32_t *local_idx,
+                                 int shard_len, int32_t *next, int *err) {
+  const int t = threadIdx.x;
+  const uint32_t step = (uint32_t)(*push.step);
+  const uint32_t tag = 0x40000000u + step;
+  const size_t base = at + (size_t)(step & 1u) * 2 * push.ranks;
+  const int li = *local_idx;
+  if (t < push.ranks) {
+    tagged_store(push.peer[t] + base + 2 * push.rank, shard[li], tag);
+    tagged_store(push.peer[t] + base + 2 * push.rank + 1, __int_as_float(li + push.rank * shard_len), tag);
+  }
+  float bv = -INFINITY;
+  int bi = 0x7fffffff;
+  if (t < push.ranks) {
+    const uint2 *p = push.peer[push.rank] + base + 2 * t;
+    uint2 v = tagged_load(p), w = tagged_load(p + 1);
+    unsigned long long t0 = 0;
+    for (uint32_t it = 1; v.y != tag || w.y != tag; ++it) {
+      if ((it & 0xFF) == 0) {
+        unsigned long long now;
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(now));
+        if (t0 == 0)
+          t0 = now;
+        if (*(volatile int *)err != 0 || now - t0 > 10000000000ull || it > (1u << 30)) {
+          atomicCAS(err, 0, 501);
+          break;
+        }
+      }
+      v = tagged_load(p);
+      w = tagged_load(p + 1);
+    }
+    bv = __uint_as_float(v.x);
+    bi = (int)w.x;
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) {
+    const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+    const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+    if (ov > bv || (ov == bv && oi < bi)) {
+      bv = ov;
+      bi = oi;
+    }
+  }
+  if (t == 0)
+    *next = bi == 0x7fffffff ? 0 : bi;
+}
 // end of a step: feed the argmax back and advance the position
 __global__ void advance_kernel(int32_t *token, int32_t *pos,
                                const int32_t *next, int32_t *history,
@@ -252,6 +304,7 @@ struct b200_model {
   uint2 *tp_ll = nullptr;
   void *tp_opened[kTpMaxRanks] = {};
   TpPush tp_push{};   // ranks == 0: the NCCL all-reduce is used instead
+  size_t tp_argmax_at = 0;   // pair offset of the (value, index) exchange slots inside the staging buffers
 };
 
 namespace {
@@ -430,11 +483,21 @@ int issue_step(b200_model *m, int *n_kernels) {
     if (int rc = gemv(m, m->lm_head, m->x, m->logits_shard, nullptr,
                       m->final_norm, false))
       return rc;
-    B200_NCCL(g_nccl.AllGather(m->logits_shard, m->logits, m->vocab, kNcclFloat,
-                               g_nccl.comm, st));
+    if (m->tp_push.ranks > 0) {
+      // (value, index) exchange by peer stores; the full logits are gathered only on request
+      if (int rc = b200_argmax_first(m->logits_shard, m->vocab, m->d_state + 5, m->argmax_scratch, st))
+        return rc;
+      tp_argmax_kernel<<<1, 32, 0, st>>>(m->tp_push, m->tp_argmax_at, m->logits_shard, m->d_state + 5, m->vocab,
+                                         d_next, m->d_state + 6);
+      B200_LAUNCH_CHECK();
+    } else {
+      B200_NCCL(g_nccl.AllGather(m->logits_shard, m->logits, m->vocab, kNcclFloat,
+                                 g_nccl.comm, st));
+    }
   }
-  if (int rc = b200_argmax_first(m->logits, c.vocab, d_next, m->argmax_scratch, st))
-    return rc;
+  if (m->tp == 1 || m->tp_push.ranks == 0)
+    if (int rc = b200_argmax_first(m->logits, c.vocab, d_next, m->argmax_scratch, st))
+      return rc;
   advance_kernel<<<1, 32, 0, st>>>(d_token, d_pos, d_next, m->d_history, d_count,
                                    m->history_cap, m->d_state + 7);
   B200_LAUNCH_CHECK();
@@ -1113,7 +1176,9 @@ static int tp_push_setup(b200_model *m) {
   const char *env = std::getenv("BUDDY_B200_TP_SUM");
   int ok = !(env && !strcmp(env, "nccl")) && tp <= kTpMaxRanks;
   cudaStream_t st = m->stream;
-  const size_t pairs = (size_t)kTpRegions * tp * H + kTpMaxRanks;   // + one marker per rank for the handshake
+  // + one marker per rank for the handshake + two slots of (value, index) per rank for the argmax
+  const size_t pairs = (size_t)kTpRegions * tp * H + kTpMaxRanks + 4 * kTpMaxRanks;
+  m->tp_argmax_at = (size_t)kTpRegions * tp * H + kTpMaxRanks;
   char *d_send = nullptr, *d_recv = nullptr;
   float *d_flag = nullptr;
   if (int rc = dev_alloc((void **)&d_send, 64)) return rc;
@@ -1302,6 +1367,8 @@ int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
   if (int rc = run_step(m)) return rc;
   B200_CUDA(cudaEventRecord(m->ev1, m->stream));
   m->rows_fresh = false;
+  if (logits_host && m->tp > 1 && m->tp_push.ranks > 0)   // the step itself exchanged only (value, index)
+    B200_NCCL(g_nccl.AllGather(m->logits_shard, m->logits, m->vocab, kNcclFloat, g_nccl.comm, m->stream));
   if (logits_host) {
     B200_CUDA(cudaMemcpyAsync(m->h_logits_pinned, m->logits, (size_t)m->cfg.vocab * 4,
                               cudaMemcpyDeviceToHost, m->stream));

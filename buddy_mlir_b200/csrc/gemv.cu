@@ -405,7 +405,27 @@ gemv_kernel(const GemvP p) {
         acc[r][0] *= kInPlaceAcc;
     }
 
-    if (lane == 0) {
+    if (p.push.ranks > 0) {
+      // This rank's share of a tensor-parallel sum (M = 1).  Every lane holds the row sums
+      // after the shuffle reduction: lane t stores them to rank t's staging buffer, so one
+      // store instruction per row reaches all peers (plain 8-byte stores over NVLink).
+      const uint32_t seq = (uint32_t)(*p.push.step) * p.push.per_step + p.push.index;
+      if (lane < p.push.ranks) {
+        uint2 *dst = p.push.peer[lane] + ((size_t)(seq % kTpRegions) * p.push.ranks + p.push.rank) * p.push.H;
+#pragma unroll
+        for (int r = 0; r < R; ++r) {
+          const int64_t row = row0 + r;
+          if (row >= p.N)
+            continue;
+          float v = acc[r][0];
+          if (!GROUPED && p.scale != nullptr)
+            v = v * load_as_float(p.scale, p.scale_dtype, row);
+          if (p.bias != nullptr)
+            v = p.bias[row] + v;
+          tagged_store(dst + row, v, seq + 1u);
+        }
+      }
+    } else if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {
         const int64_t row = row0 + r;
@@ -455,14 +475,6 @@ gemv_kernel(const GemvP p) {
             if (m < p.M) {
               const int64_t o = (int64_t)m * p.y_ld + row;
               float v = acc[r][m];
-              if (p.push.ranks > 0) {
-                // this rank's share of a tensor-parallel sum (M = 1): one tagged pair per rank
-                const uint32_t seq = (uint32_t)(*p.push.step) * p.push.per_step + p.push.index;
-                const size_t at = ((size_t)(seq % kTpRegions) * p.push.ranks + p.push.rank) * p.push.H + row;
-                for (int t = 0; t < p.push.ranks; ++t)
-                  tagged_store(p.push.peer[t] + at, v, seq + 1u);
-                continue;
-              }
               if (p.residual != nullptr)
                 v = p.residual[o] + v;
               if (p.y_dtype == B200_F32) {
