@@ -316,6 +316,59 @@ def run_gemm_only(args):
     print(json.dumps({"gemm_isolated": gemm_microbench(lib, args.gemm_shape)}))
 
 
+def run_batch_only(args):
+    """--batch-only: batched decode + prefill of the 1.5B int8 model (dense tcgen05 GEMM path):
+    64 sequences with seeded lengths uniform in [128, 2048] in the paged KV cache, a
+    2048-token prefill, then `--steps` decode steps of the whole batch (one JSON line)."""
+    import torch
+    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, _lib, synthetic
+    from buddy_mlir_b200.session import BatchSession, ModelSession
+    _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    blob, _ = synthetic.make_f32_blob(cfg, SEED_W)
+    s = ModelSession(cfg)
+    s.load_blobs("f32", blob, all_linear_w8=True)
+    B, page = 64, 16
+    rng = np.random.default_rng(SEED_P)
+    lengths = rng.integers(128, 2049, B)
+    n_pages = int(sum((int(n) + args.steps + args.warmup + page - 1) // page + 1 for n in lengths)) + 2048 // page + 8
+    bs = BatchSession(s, max_seqs=B + 1, page_size=page, n_pages=n_pages, max_context=2048 + args.steps + args.warmup + 16)
+    # one 2048-token prefill, timed (after a warm-up pass of the same size on a scratch sequence)
+    scratch = bs.add()
+    bs.prefill(scratch, rng.integers(0, cfg.vocab, 2048), want_logits=False)
+    bs.remove(scratch)
+    scratch = bs.add()
+    bs.prefill(scratch, rng.integers(0, cfg.vocab, 2048), want_logits=False)
+    prefill_ms = bs.last_ms()
+    bs.remove(scratch)
+    seqs, toks = [], []
+    for n in lengths:
+        q = bs.add()
+        _, nxt = bs.prefill(q, rng.integers(0, cfg.vocab, int(n)), want_logits=False)
+        seqs.append(q)
+        toks.append(nxt)
+    for _ in range(args.warmup):
+        _, nxt = bs.decode(seqs, toks, want_logits=False)
+        toks = [int(t) for t in nxt]
+    ms = []
+    for _ in range(args.steps):
+        _, nxt = bs.decode(seqs, toks, want_logits=False)
+        ms.append(bs.last_ms())
+        toks = [int(t) for t in nxt]
+    step_ms = float(np.mean(ms))
+    flops = 2.0 * (1310195712 + 233373696)       # per token: the linear layers and the lm_head
+    print(json.dumps({"batched_decode": {"sequences": B, "lengths": "uniform [128, 2048], seeded", "page_size": page,
+                                         "ms_per_step": step_ms, "tokens_per_s": B / (step_ms / 1000.0),
+                                         "steps": args.steps, "weights": "int8 per-channel, every linear layer"},
+                      "prefill_2048": {"ms": prefill_ms, "tokens_per_s": 2048 / (prefill_ms / 1000.0),
+                                       "linear_TFLOP/s": 2048 * flops / (prefill_ms / 1000.0) / 1e12},
+                      "model": "deepseek-r1-distill-qwen-1.5b architecture, seeded weights"}))
+    bs.close()
+    s.close()
+
+
 def run_gemv_only(args):
     """--gemv-only: just the isolated GEMV sweep (one JSON line); --gemv-shape picks one shape,
     which keeps a profiler capture of that kernel small."""
@@ -428,6 +481,7 @@ def main():
     ap.add_argument("--gemv-only", action="store_true", help="run only the isolated GEMV sweep")
     ap.add_argument("--gemv-shape", default=None, help="with --gemv-only: one shape of GEMV_SHAPES")
     ap.add_argument("--gemm-only", action="store_true", help="run only the isolated dense-GEMM sweep (tcgen05 path)")
+    ap.add_argument("--batch-only", action="store_true", help="batched decode (64 sequences, paged KV) + a 2048-token prefill")
     ap.add_argument("--gemm-shape", default=None, help="with --gemm-only: one shape of GEMM_SHAPES")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the isolated-GEMV, end-to-end and CPU legs (for profiler captures)")
@@ -443,6 +497,8 @@ def main():
         return run_gemv_only(args)
     if args.gemm_only:
         return run_gemm_only(args)
+    if args.batch_only:
+        return run_batch_only(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single(args)
     import bench_tp

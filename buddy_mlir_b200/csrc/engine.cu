@@ -1092,6 +1092,10 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
     ni = c.n_layers * quant_layer + H * V;
     nf = common + c.n_layers * (small_layer + qkv) +
          c.n_layers * (H + 2 * F + H) + V;  // + one scale per quantised column
+  } else if (!strcmp(variant, "w4a16")) {
+    // the same split as w8a32: n_float counts f16 elements, n_int packed bytes (two nibbles each)
+    ni = (c.n_layers * quant_layer + H * V) / 2;
+    nf = common + c.n_layers * (small_layer + qkv) + c.n_layers * (H + 2 * F + H) + V;
   } else {
     return fail(B200_EINVAL, "blob_elements: unknown variant '%s'", variant);
   }
@@ -1111,15 +1115,26 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
     return fail(B200_EINVAL, "load_blobs: blob order is defined for Qwen2 models only");
   int64_t want_f = 0, want_i = 0;
   if (int rc = b200_blob_elements(&c, variant, &want_f, &want_i)) return rc;
-  const bool w8 = !strcmp(variant, "w8a32");
-  if (n_float != want_f || (w8 && (n_int != want_i || !int_blob)))
+  const bool w8 = !strcmp(variant, "w8a32"), w4 = !strcmp(variant, "w4a16");
+  if (n_float != want_f || ((w8 || w4) && (n_int != want_i || !int_blob)))
     return fail(B200_EINVAL,
                 "load_blobs(%s): expected %lld float / %lld int8 elements, got %lld / %lld",
                 variant, (long long)want_f, (long long)want_i, (long long)n_float,
                 (long long)n_int);
   const int64_t H = c.hidden, D = c.head_dim, QD = (int64_t)c.q_heads * D,
                 KD = (int64_t)c.kv_heads * D, F = c.ffn, V = c.vocab;
-  const float *fp = (const float *)float_blob;
+  // w4a16: the float blob holds f16 values (tools/buddy-codegen/gen_config.py:51-71); they are
+  // widened once (exact), so that the rest of the walk is the same for every variant.  The
+  // scales stay f16 (they follow the float tensors in the same blob).
+  std::vector<float> widened;
+  const uint16_t *f16_blob = (const uint16_t *)float_blob;
+  if (w4) {
+    widened.resize((size_t)n_float);
+    for (int64_t i = 0; i < n_float; ++i)
+      widened[(size_t)i] = __half2float(__ushort_as_half(f16_blob[i]));
+  }
+  const float *fp0 = w4 ? widened.data() : (const float *)float_blob;
+  const float *fp = fp0;
   const int8_t *ip = (const int8_t *)int_blob;
   const int qf = all_linear_w8 ? B200_W_I8 : -1;  // float linears: keep or quantise
   auto takef = [&](int64_t n) { const float *p = fp; fp += n; return p; };
@@ -1137,6 +1152,8 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   auto qlinear = [&](int l, int slot, int64_t K, int64_t N) {
     if (w8)
       pend.push_back({l, slot, takei(K * N), K, N});
+    else if (w4)
+      pend.push_back({l, slot, takei(K * N / 2), K, N});
     else
       flinear(l, slot, K, N);
   };
@@ -1161,9 +1178,17 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   qlinear(-1, B200_T_LM_HEAD, H, V);
   // quantize.py:577-589: the scaler params follow every original param, in
   // original-weight order.
-  for (auto &p : pend)
-    B200_DO(b200_model_set_linear(m, p.layer, p.slot, B200_W_I8, p.w, takef(p.N),
-                                  B200_F32, 1, p.K, p.N, -1, 0));
+  for (auto &p : pend) {
+    if (w4) {
+      // signed nibbles [K, N/2], per-channel f16 scales straight from the f16 blob
+      const uint16_t *sc = f16_blob + (fp - fp0);
+      fp += p.N;
+      B200_DO(b200_model_set_linear(m, p.layer, p.slot, B200_W_U4, p.w, sc, B200_F16, 1, p.K, p.N, -1, 0));
+    } else {
+      B200_DO(b200_model_set_linear(m, p.layer, p.slot, B200_W_I8, p.w, takef(p.N),
+                                    B200_F32, 1, p.K, p.N, -1, 0));
+    }
+  }
 #undef B200_DO
   return rc;
 }

@@ -106,5 +106,24 @@ def split_w8a32(cfg: ModelConfig, views, quantize):
     return np.concatenate(floats + scales), np.concatenate(ints)
 
 
+def split_w4a16(cfg: ModelConfig, views, quantize):
+    """Reference-faithful w4a16 blobs (tools/buddy-codegen/import_model.py:800-887,
+    gen_config.py:51-71): every float tensor and every scale as f16, the quantised
+    tensors as signed nibbles, two per byte, low nibble first, in flat row-major
+    element order.  quantize(W [K,N] f32) -> (Q [K,N] int8 in [-8,7], scale [N] f32).
+    Returns (f16_blob, packed_int4_blob)."""
+    floats, ints, scales = [], [], []
+    for name, layer, _ in tensor_list(cfg):
+        t = views[(name, layer)]
+        if name in QUANTISED_BY_REFERENCE:
+            q, s = quantize(t)
+            flat = np.ascontiguousarray(q, dtype=np.int8).reshape(-1).view(np.uint8)
+            ints.append(((flat[0::2] & 0x0F) | ((flat[1::2] & 0x0F) << 4)).astype(np.uint8).view(np.int8))
+            scales.append(np.ascontiguousarray(s, dtype=np.float32).astype(np.float16).reshape(-1))
+        else:
+            floats.append(t.reshape(-1).astype(np.float16))
+    return np.concatenate(floats + scales), np.concatenate(ints)
+
+
 def prompt_tokens(cfg: ModelConfig, seed: int, n: int = 32):
     return np.random.default_rng(seed).integers(0, cfg.vocab, size=n).astype(np.int64)

@@ -509,6 +509,17 @@ static void linear(const OrcLinear &L, const float *x, float *y) {
     orc_gemv_w4g_f32(x, (const uint8_t *)L.w, (const uint16_t *)L.scale, y, 1,
                      L.K, L.N, L.group);
     break;
+  case ORC_LIN_W4: {
+    // the w4a16 variant: f16 activations, f16 accumulation
+    // (Int4DequantMatMulVectorizationDecode.cpp:359-430)
+    std::vector<uint16_t> xh((size_t)L.K), yh((size_t)L.N, f16_to_bits((f16)0.0f));
+    for (int64_t k = 0; k < L.K; ++k)
+      xh[(size_t)k] = f16_to_bits((f16)x[k]);
+    orc_gemv_w4_f16(xh.data(), (const int8_t *)L.w, (const uint16_t *)L.scale, yh.data(), 1, L.K, L.N);
+    for (int64_t n = 0; n < L.N; ++n)
+      y[n] = (float)bits_to_f16(yh[(size_t)n]);
+    break;
+  }
   default:
     std::abort();
   }

@@ -8,7 +8,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _SO = os.path.join(ROOT, "oracle", "_build", "libbuddy_oracle.so")
 _REF_SO = os.path.join(ROOT, "oracle", "_ref", "libbuddy_ref_host.so")
 
-LIN_F32, LIN_W8, LIN_W4G = 0, 1, 2
+LIN_F32, LIN_W8, LIN_W4G, LIN_W4 = 0, 1, 2, 3
 
 
 class OrcLinear(C.Structure):
@@ -259,6 +259,11 @@ class OracleModel:
                 L.kind = LIN_W8
                 L.w = hold(Q, np.int8).ctypes.data
                 L.scale = hold(s, np.float32).ctypes.data
+            elif kind == "w4":      # the reference's w4a16: signed nibbles, per-channel f16 scale
+                Q, sc = quantised.get((name, layer)) or quantize_per_channel(W, 4)
+                L.kind = LIN_W4
+                L.w = hold(pack_int4(np.ascontiguousarray(Q, dtype=np.int8).reshape(-1)).reshape(K, N // 2)).ctypes.data
+                L.scale = hold(np.asarray(sc, dtype=np.float32).astype(np.float16)).ctypes.data
             elif kind == "w4g":
                 P, s = quantised.get((name, layer)) or quantize_w4_group(W, group)
                 L.kind, L.group = LIN_W4G, group

@@ -139,6 +139,40 @@ def test_load_weights_from_the_reference_blob_files(tmp_path):
     s.close()
 
 
+def test_tiny_w4a16_reference_blobs():
+    """The reference's int4 flavour (tools/buddy-codegen/gen_config.py:37-71): f16 blob +
+    nibble-packed blob, signed per-channel int4 on o / gate / up / down / lm_head.  The
+    reference accumulates these GEMVs in f16 (Int4DequantMatMulVectorizationDecode.cpp:
+    359-430), this library in f32: logits within 2e-2, and the same greedy token wherever
+    the checker's top-1 / top-2 margin is larger than that tolerance."""
+    cfg = TINY_QWEN2
+    _, views = synthetic.make_f32_blob(cfg, 79)
+    fb, ib = synthetic.split_w4a16(cfg, views, lambda W: orc.quantize_per_channel(W, 4))
+    assert fb.dtype == np.float16 and ib.dtype == np.int8
+    # the checker sees what the blobs hold: f16-rounded float tensors
+    rounded = {k: (v.astype(np.float16).astype(np.float32) if k[0] not in synthetic.QUANTISED_BY_REFERENCE else v)
+               for k, v in views.items()}
+    om = orc.OracleModel(cfg, rounded, kinds={n: "w4" for n in synthetic.QUANTISED_BY_REFERENCE})
+    s = ModelSession(cfg)
+    s.load_blobs("w4a16", fb, ib)
+    worst, agree, total = 0.0, 0, 0
+    tok = None
+    for i, t in enumerate(list(synthetic.prompt_tokens(cfg, 5, 8)) + [None] * 24):
+        t = tok if t is None else int(t)
+        s.decode(t)
+        want = om.decode(t)
+        got = s.logits_data()
+        worst = max(worst, maxrel(got, want))
+        if margin(want) > 2e-2 * float(np.abs(want).max()):
+            assert greedy_sample(got) == greedy_sample(want)
+        agree += int(greedy_sample(got) == greedy_sample(want))
+        total += 1
+        tok = greedy_sample(want)
+    assert worst < 2e-2, worst
+    print(f"w4a16 tiny: max rel logit err {worst:.3e}, greedy agreement {agree}/{total}")
+    s.close()
+
+
 def test_tiny_all_linear_w8_quantised_on_device():
     cfg = TINY_QWEN2
     blob, views = synthetic.make_f32_blob(cfg, 8)

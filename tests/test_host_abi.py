@@ -66,7 +66,10 @@ def test_blob_counts_match_reference_specs():
     assert lib.b200_blob_elements(C.byref(c), b"w8a32", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (322338752, 1455489024)
     assert synthetic.blob_elements(DEEPSEEK_R1_1P5B) == 1777088064
-    assert lib.b200_blob_elements(C.byref(c), b"w4a16", C.byref(nf), C.byref(ni)) != 0
+    # models/deepseek_r1/specs/w4a16.json: 322338752 f16 elements + 727744512 packed bytes
+    assert lib.b200_blob_elements(C.byref(c), b"w4a16", C.byref(nf), C.byref(ni)) == 0
+    assert (nf.value, ni.value) == (322338752, 727744512)
+    assert lib.b200_blob_elements(C.byref(c), b"w8a8", C.byref(nf), C.byref(ni)) != 0
 
 
 def test_w8a32_split_sizes():
