@@ -132,6 +132,14 @@ def load():
                                        i64, vp, i64, C.POINTER(C.c_longlong), i32,
                                        C.POINTER(vp), vp]),
         "b200_forward_reset": (None, []),
+        "b200_rax_open": (i32, [C.c_char_p, C.POINTER(vp)]),
+        "b200_rax_close": (None, [vp]),
+        "b200_rax_count": (i32, [vp]),
+        "b200_rax_manifest_bytes": (C.c_uint64, [vp]),
+        "b200_rax_entry": (i32, [vp, i32, C.c_char_p, i32, C.POINTER(i32), C.POINTER(C.c_uint64),
+                                 C.POINTER(C.c_uint64)]),
+        "b200_rax_find": (i32, [vp, C.c_char_p]),
+        "b200_rax_read": (i32, [vp, i32, vp, C.c_uint64]),
     }
     for name, (res, args) in sig.items():
         fn = getattr(lib, name)

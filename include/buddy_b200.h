@@ -379,6 +379,26 @@ int b200_tp_unique_id(void *id128);
 int b200_tp_init(const void *id128, int rank, int size);
 void b200_tp_shutdown(void);
 
+/* ------------------------------------------------------------------------
+ * Payload section of a buddy-mlir .rax package, without FlatBuffers
+ * (runtime/include/buddy/runtime/core/ModelManifest.h:124-145, 202-310):
+ * [manifest "RAX0"][payload blobs][index "RAXIDX01"][64-byte footer
+ * "RAXPAY01"].  The manifest is not parsed; the payload entries are named
+ * (weight blobs keep their file names), so the weights of a packaged model can
+ * be read straight from the package.  A package without a payload opens with
+ * zero entries.  Host code; no device is needed.
+ * ---------------------------------------------------------------------- */
+typedef struct b200_rax b200_rax;
+int b200_rax_open(const char *path, b200_rax **out);
+void b200_rax_close(b200_rax *r);
+int b200_rax_count(const b200_rax *r);
+uint64_t b200_rax_manifest_bytes(const b200_rax *r);
+int b200_rax_entry(const b200_rax *r, int i, char *name, int name_cap,
+                   int *kind, uint64_t *offset, uint64_t *size);
+/* Index of the first entry whose name ends with name_suffix, or -1. */
+int b200_rax_find(const b200_rax *r, const char *name_suffix);
+int b200_rax_read(const b200_rax *r, int i, void *dst, uint64_t bytes);
+
 #ifdef __cplusplus
 }
 #endif
