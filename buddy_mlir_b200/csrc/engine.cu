@@ -1568,6 +1568,8 @@ struct b200_batch {
   std::vector<int> len;                 // per sequence: -1 = unused slot
   std::vector<int32_t> table;           // [max_seqs][table_stride] host mirror
   int32_t *d_table = nullptr, *d_seq = nullptr, *d_pos = nullptr, *d_next = nullptr;
+  float *d_part = nullptr;              // attention partials of the key-split scan, for up to part_rows rows
+  int part_rows = 0, max_context = 0;
   int rows_cap = 0;
   float last_ms = 0.f;
 };
@@ -1604,7 +1606,8 @@ static int batch_rows(b200_batch *b, int M, const int32_t *tokens, const int32_t
                                       b->table_stride, M, st))
       return rc;
     if (int rc = gqa_paged_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->pf_att, QD, m->qh, m->kvh,
-                                  D, b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M, st))
+                                  D, b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M,
+                                  M <= b->part_rows ? b->d_part : nullptr, b->max_context, st))
       return rc;
     if (int rc = linear_rows(m, L.o, m->pf_att, QD, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
     if (int rc = linear_rows(m, L.gateup, m->pf_x, H, M, m->pf_mid, m->ffn, nullptr, L.post_norm, true)) return rc;
@@ -1661,6 +1664,11 @@ int b200_batch_create(b200_model *m, int max_seqs, int page_size, int n_pages, i
   for (auto &p : b->pool)
     if (rc == B200_OK) rc = dev_alloc((void **)&p, pool_bytes);
   if (rc == B200_OK) rc = dev_alloc((void **)&b->d_table, b->table.size() * 4);
+  b->max_context = b->table_stride * page_size;
+  b->part_rows = max_seqs;
+  if (rc == B200_OK)
+    rc = dev_alloc((void **)&b->d_part,
+                   (size_t)gqa_paged_scratch_floats(b->part_rows, m->qh, m->cfg.head_dim, b->max_context) * 4);
   if (rc != B200_OK) {
     b200_batch_destroy(b);
     return rc;
@@ -1673,6 +1681,7 @@ void b200_batch_destroy(b200_batch *b) {
   if (!b) return;
   for (auto p : b->pool) cudaFree(p);
   cudaFree(b->d_table); cudaFree(b->d_seq); cudaFree(b->d_pos); cudaFree(b->d_next);
+  cudaFree(b->d_part);
   delete b;
 }
 

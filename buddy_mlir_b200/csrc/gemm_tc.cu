@@ -33,27 +33,34 @@
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 namespace b200 {
 
 namespace {
 
-constexpr int BM = 128, BN = 128, BK = 64;     // tile; BK bf16 = 128 bytes = one swizzle row
-constexpr int kStages = 3;
+constexpr int BM = 128, BN = 128;              // output tile of one CTA
+constexpr int kMaxStages = 8;
 constexpr int kTmemCols = 128;                 // f32 accumulator 128 lanes x 128 columns
 constexpr int kThreads = 192;                  // warp 0 loader, warp 1 mma, warps 2..5 convert + epilogue
-constexpr uint32_t A_BYTES = BM * BK * 2;      // 16 KB per term
-constexpr uint32_t WRAW_BYTES = BN * BK;       // 8 KB
-constexpr uint32_t WB_BYTES = BN * BK * 2;     // 16 KB
-constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + WRAW_BYTES + WB_BYTES;   // 56 KB
+constexpr int kMaxPartialTiles = 320;          // split-K: 128 x 128 f32 partial tiles in the workspace
 constexpr uint32_t kSpin = 1u << 26;
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
+// Shared-memory stage for a k block of BKT elements (64: 128-byte swizzle rows, 32: 64-byte rows).
+template <int BKT> struct Tile {
+  static constexpr uint32_t A_BYTES = BM * BKT * 2;      // one bf16 term of the activations
+  static constexpr uint32_t WRAW_BYTES = BN * BKT;       // int8 weights as stored
+  static constexpr uint32_t WB_BYTES = BN * BKT * 2;     // the same tile as bf16
+  static constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + WRAW_BYTES + WB_BYTES;   // 56 KB / 28 KB
+  static constexpr uint32_t ROW_BYTES = BKT * 2;
+};
+
 struct Bars {
-  uint64_t full[kStages];      // TMA bytes of the stage have landed
-  uint64_t ready[kStages];     // the bf16 weight tile has been written (128 arrivals)
-  uint64_t empty[kStages];     // the tensor core is done with the stage
+  uint64_t full[kMaxStages];   // TMA bytes of the stage have landed
+  uint64_t ready[kMaxStages];  // the bf16 weight tile has been written (128 arrivals)
+  uint64_t empty[kMaxStages];  // the tensor core is done with the stage
   uint64_t accum;              // all MMAs have completed
   uint32_t tmem_base;
   int abort_flag;
@@ -106,16 +113,17 @@ __device__ __forceinline__ void tma_load_2d(void *dst, const CUtensorMap *map, i
       ::"r"(smem_u32(dst)), "l"(map), "r"(smem_u32(bar)), "r"(x), "r"(y)
       : "memory");
 }
-// K-major operand tile in shared memory, 128-byte swizzle, rows of 128 bytes:
-// start address / 16, leading byte offset (unused for swizzled K-major: 1),
-// stride byte offset = 8 rows x 128 B = 1024 B, descriptor version 1, layout 2.
-__device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
+// K-major operand tile in shared memory, rows of 128 bytes (128-byte swizzle) or
+// 64 bytes (64-byte swizzle): start address / 16, leading byte offset (unused for
+// swizzled K-major: 1), stride byte offset = 8 rows, descriptor version 1,
+// layout 2 (128-byte swizzle) or 4 (64-byte swizzle).
+template <int BKT> __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) {
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)1 << 16;
-  d |= (uint64_t)(1024 >> 4) << 32;
+  d |= (uint64_t)((8 * Tile<BKT>::ROW_BYTES) >> 4) << 32;
   d |= (uint64_t)1 << 46;
-  d |= (uint64_t)2 << 61;
+  d |= (uint64_t)(BKT == 64 ? 2 : 4) << 61;
   return d;
 }
 // kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128.
@@ -140,23 +148,52 @@ struct GemmParams {
   float *C;                    // [M, ldc]
   int64_t ldc, ldr;
   int silu_pairs;              // rows (2j, 2j+1) of W are (gate_j, up_j): C[m, j] = silu(g) * u, ldc counts N/2 columns
+  int stages;                  // ring depth (<= kMaxStages)
+  int splits;                  // CTAs along K per output tile (gridDim.z); > 1: raw sums go to `partial`
+  float *partial;              // [tiles][splits][128][128] f32
   int *error;
 };
 
-__global__ void __launch_bounds__(kThreads, 1)
+// scale / bias / residual, or the SiLU-gate of a (gate, up) column pair
+__device__ __forceinline__ void store_plain(const GemmParams &p, int m, int n, float acc) {
+  float y = __fmul_rn(acc, __ldg(p.scale + n));
+  if (p.bias)
+    y = __fadd_rn(y, __ldg(p.bias + n));
+  if (p.residual)
+    y = __fadd_rn(p.residual[(int64_t)m * p.ldr + n], y);
+  p.C[(int64_t)m * p.ldc + n] = y;
+}
+__device__ __forceinline__ void store_pair(const GemmParams &p, int m, int n, float ag, float au) {
+  float g = __fmul_rn(ag, __ldg(p.scale + n));
+  float u = __fmul_rn(au, __ldg(p.scale + n + 1));
+  if (p.bias) {
+    g = __fadd_rn(g, __ldg(p.bias + n));
+    u = __fadd_rn(u, __ldg(p.bias + n + 1));
+  }
+  const float sg = 1.0f / (1.0f + expf(-g));   // subgraph0_decode_simplify.mlir:226-231
+  p.C[(int64_t)m * p.ldc + (n >> 1)] = __fmul_rn(__fmul_rn(g, sg), u);
+}
+
+template <int BKT>
+__global__ void __launch_bounds__(kThreads, BKT == 64 ? 1 : 2)
 gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
+  using T = Tile<BKT>;
   extern __shared__ __align__(1024) uint8_t smem[];
   // 1024-byte alignment of every swizzled tile
   uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
-  Bars &bars = *reinterpret_cast<Bars *>(tiles + kStages * STAGE_BYTES);
+  const int stages = p.stages;
+  Bars &bars = *reinterpret_cast<Bars *>(tiles + stages * T::STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
-  const int nkb = p.K / BK;
+  // this CTA's share of the k blocks (split-K: blockIdx.z)
+  const int nkb_all = p.K / BKT;
+  const int kb0 = (int)((int64_t)nkb_all * blockIdx.z / p.splits);
+  const int nkb = (int)((int64_t)nkb_all * (blockIdx.z + 1) / p.splits) - kb0;
   volatile int *ab = &bars.abort_flag;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < stages; ++s) {
       mbar_init(&bars.full[s], 1);
       mbar_init(&bars.ready[s], 128);
       mbar_init(&bars.empty[s], 1);
@@ -177,33 +214,34 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
   if (warp == 0) {
     // ---- loader ------------------------------------------------------------------
     if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % kStages, use = kb / kStages;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % stages, use = i / stages;
         if (use > 0 && !mbar_wait(&bars.empty[s], (use - 1) & 1, ab, p.error, 701))
           break;
-        uint8_t *st = tiles + s * STAGE_BYTES;
-        mbar_expect_tx(&bars.full[s], 2 * A_BYTES + WRAW_BYTES);
-        tma_load_2d(st, &map_hi, kb * BK, m0, &bars.full[s]);
-        tma_load_2d(st + A_BYTES, &map_lo, kb * BK, m0, &bars.full[s]);
-        tma_load_2d(st + 2 * A_BYTES, &map_w, kb * BK, n0, &bars.full[s]);
+        uint8_t *st = tiles + s * T::STAGE_BYTES;
+        const int kx = (kb0 + i) * BKT;
+        mbar_expect_tx(&bars.full[s], 2 * T::A_BYTES + T::WRAW_BYTES);
+        tma_load_2d(st, &map_hi, kx, m0, &bars.full[s]);
+        tma_load_2d(st + T::A_BYTES, &map_lo, kx, m0, &bars.full[s]);
+        tma_load_2d(st + 2 * T::A_BYTES, &map_w, kx, n0, &bars.full[s]);
       }
     }
   } else if (warp == 1) {
     // ---- tensor core issue (one thread) ------------------------------------------------
     if (lane == 0) {
-      for (int kb = 0; kb < nkb; ++kb) {
-        const int s = kb % kStages, use = kb / kStages;
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % stages, use = i / stages;
         if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 702) ||
             !mbar_wait(&bars.ready[s], use & 1, ab, p.error, 703))
           break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        const uint32_t a_hi = smem_u32(tiles + s * STAGE_BYTES), a_lo = a_hi + A_BYTES,
-                       wb = a_hi + 2 * A_BYTES + WRAW_BYTES;
+        const uint32_t a_hi = smem_u32(tiles + s * T::STAGE_BYTES), a_lo = a_hi + T::A_BYTES,
+                       wb = a_hi + 2 * T::A_BYTES + T::WRAW_BYTES;
 #pragma unroll
-        for (int k = 0; k < BK / 16; ++k) {   // 16 bf16 = 32 bytes along the swizzled row
-          const uint64_t db = smem_desc(wb + k * 32);
-          mma_bf16(tmem, smem_desc(a_hi + k * 32), db, (kb | k) != 0);
-          mma_bf16(tmem, smem_desc(a_lo + k * 32), db, 1u);
+        for (int k = 0; k < BKT / 16; ++k) {   // 16 bf16 = 32 bytes along the swizzled row
+          const uint64_t db = smem_desc<BKT>(wb + k * 32);
+          mma_bf16(tmem, smem_desc<BKT>(a_hi + k * 32), db, (i | k) != 0);
+          mma_bf16(tmem, smem_desc<BKT>(a_lo + k * 32), db, 1u);
         }
         tc_commit(&bars.empty[s]);   // arrives when the MMAs above have read the stage
       }
@@ -212,21 +250,24 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
   } else {
     // ---- int8 -> bf16 conversion of the weight tile, then the epilogue ------------------
     const int t = threadIdx.x - 64;           // 0..127: weight row of the tile (conversion), accumulator row (epilogue)
+    constexpr int NQ = BKT / 16;              // 16-byte units of raw weights per row
+    // 16-byte chunk c of row r of a swizzled tile sits at chunk c ^ swz(r)
+    const int swz = BKT == 64 ? (t & 7) : ((t >> 1) & 3);
     bool alive = true;
-    for (int kb = 0; kb < nkb && alive; ++kb) {
-      const int s = kb % kStages, use = kb / kStages;
+    for (int i = 0; i < nkb && alive; ++i) {
+      const int s = i % stages, use = i / stages;
       if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 704)) {
         alive = false;
         break;
       }
-      uint8_t *st = tiles + s * STAGE_BYTES;
-      const uint4 *raw = reinterpret_cast<const uint4 *>(st + 2 * A_BYTES + t * BK);
-      uint8_t *dst = st + 2 * A_BYTES + WRAW_BYTES + t * 128;   // row t of the swizzled bf16 tile
+      uint8_t *st = tiles + s * T::STAGE_BYTES;
+      const uint4 *raw = reinterpret_cast<const uint4 *>(st + 2 * T::A_BYTES + t * BKT);
+      uint8_t *dst = st + 2 * T::A_BYTES + T::WRAW_BYTES + t * T::ROW_BYTES;   // row t of the swizzled bf16 tile
 #pragma unroll
-      for (int qq = 0; qq < 4; ++qq) {         // 16 int8 -> two 16-byte chunks of bf16
-        // rows are 64 bytes apart: neighbouring threads start at different 16-byte units,
-        // so that the eight threads of a quarter warp read eight different bank groups
-        const int q = (qq + (t >> 1)) & 3;
+      for (int qq = 0; qq < NQ; ++qq) {         // 16 int8 -> two 16-byte chunks of bf16
+        // neighbouring rows start at different 16-byte units, so that the eight threads of a
+        // quarter warp read eight different bank groups
+        const int q = (qq + (BKT == 64 ? (t >> 1) : (t >> 2))) & (NQ - 1);
         const uint4 w = raw[q];
         const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
         uint32_t o[8];
@@ -241,10 +282,9 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
           o[2 * j] = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
           o[2 * j + 1] = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
         }
-        // 128-byte swizzle: 16-byte chunk c of row r sits at chunk c ^ (r & 7)
         const int c0 = 2 * q, c1 = 2 * q + 1;
-        *reinterpret_cast<uint4 *>(dst + ((c0 ^ (t & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4 *>(dst + ((c1 ^ (t & 7)) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        *reinterpret_cast<uint4 *>(dst + ((c0 ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4 *>(dst + ((c1 ^ swz) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
       }
       asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
       mbar_arrive(&bars.ready[s]);
@@ -256,6 +296,11 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       const int quad = warp & 3;
       const int row = quad * 32 + lane;
       const int m = m0 + row;
+      float *prow = nullptr;
+      if (p.splits > 1) {
+        const int64_t tile = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
+        prow = p.partial + ((tile * p.splits + blockIdx.z) * BM + row) * BN;
+      }
 #pragma unroll 1
       for (int cb = 0; cb < BN; cb += 32) {
         uint32_t v[32];
@@ -271,37 +316,29 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (m < p.M) {
+        if (prow != nullptr) {
+          // split-K: raw sums of this CTA's k range; gemm_w8_combine_kernel adds the splits
+          if (m < p.M) {
+#pragma unroll
+            for (int j = 0; j < 32; j += 4)
+              *reinterpret_cast<float4 *>(prow + cb + j) =
+                  make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                              __uint_as_float(v[j + 3]));
+          }
+        } else if (m < p.M) {
           if (p.silu_pairs) {
-            float *crow = p.C + (int64_t)m * p.ldc + ((n0 + cb) >> 1);
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
               const int n = n0 + cb + j;
-              if (n + 1 < p.N) {
-                float g = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
-                float u = __fmul_rn(__uint_as_float(v[j + 1]), __ldg(p.scale + n + 1));
-                if (p.bias) {
-                  g = __fadd_rn(g, __ldg(p.bias + n));
-                  u = __fadd_rn(u, __ldg(p.bias + n + 1));
-                }
-                const float sg = 1.0f / (1.0f + expf(-g));   // subgraph0_decode_simplify.mlir:226-231
-                crow[j >> 1] = __fmul_rn(__fmul_rn(g, sg), u);
-              }
+              if (n + 1 < p.N)
+                store_pair(p, m, n, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
             }
           } else {
-            float *crow = p.C + (int64_t)m * p.ldc + n0 + cb;
-            const float *rrow = p.residual ? p.residual + (int64_t)m * p.ldr + n0 + cb : nullptr;
 #pragma unroll
             for (int j = 0; j < 32; ++j) {
               const int n = n0 + cb + j;
-              if (n < p.N) {
-                float y = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
-                if (p.bias)
-                  y = __fadd_rn(y, __ldg(p.bias + n));
-                if (rrow)
-                  y = __fadd_rn(rrow[j], y);
-                crow[j] = y;
-              }
+              if (n < p.N)
+                store_plain(p, m, n, __uint_as_float(v[j]));
             }
           }
         }
@@ -317,6 +354,34 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       }
     }
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
+  }
+}
+
+// Split-K: add the splits of every output tile in split order, then the epilogue.
+__global__ void __launch_bounds__(256)
+gemm_w8_combine_kernel(const GemmParams p, int tiles_x) {
+  const int tile = blockIdx.x;
+  const int m0 = (tile / tiles_x) * BM, n0 = (tile % tiles_x) * BN;
+  const float *base = p.partial + (int64_t)tile * p.splits * BM * BN;
+  for (int idx = threadIdx.x * 2; idx < BM * BN; idx += blockDim.x * 2) {
+    const int r = idx / BN, c = idx % BN;      // c even
+    const int m = m0 + r, n = n0 + c;
+    if (m >= p.M || n >= p.N)
+      continue;
+    float a0 = 0.f, a1 = 0.f;
+    for (int z = 0; z < p.splits; ++z) {
+      const float2 v = *reinterpret_cast<const float2 *>(base + (int64_t)z * BM * BN + idx);
+      a0 = __fadd_rn(a0, v.x);
+      a1 = __fadd_rn(a1, v.y);
+    }
+    if (p.silu_pairs) {
+      if (n + 1 < p.N)
+        store_pair(p, m, n, a0, a1);
+    } else {
+      store_plain(p, m, n, a0);
+      if (n + 1 < p.N)
+        store_plain(p, m, n + 1, a1);
+    }
   }
 }
 
@@ -377,14 +442,14 @@ EncodeFn encode_fn() {
   return fn;
 }
 
-int make_map(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, void *base, uint64_t inner, uint64_t rows,
+int make_map(CUtensorMap *map, CUtensorMapDataType dt, int bk, void *base, uint64_t inner, uint64_t rows,
              uint64_t pitch_bytes, CUtensorMapSwizzle swz) {
   EncodeFn fn = encode_fn();
   if (!fn)
     return fail(B200_ECUDA, "gemm_w8: cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {inner, rows};
   const cuuint64_t strides[1] = {pitch_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)(elem_bytes == 1 ? BK : BK), 128};
+  const cuuint32_t box[2] = {(cuuint32_t)bk, 128};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult rc = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -399,13 +464,47 @@ int make_map(CUtensorMap *map, CUtensorMapDataType dt, int elem_bytes, void *bas
 
 using namespace b200;
 
+template <int BKT>
+static int gemm_launch(const b200_weight *w, __nv_bfloat16 *hi, __nv_bfloat16 *lo, int Mp, GemmParams &p, int stages,
+                       cudaStream_t st) {
+  const int K = p.K, N = p.N;
+  const CUtensorMapSwizzle swz = BKT == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
+  CUtensorMap map_hi, map_lo, map_w;
+  if (int rc = make_map(&map_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, hi, K, Mp, (uint64_t)K * 2, swz))
+    return rc;
+  if (int rc = make_map(&map_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, lo, K, Mp, (uint64_t)K * 2, swz))
+    return rc;
+  if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, BKT, const_cast<void *>(w->w), K, N, (uint64_t)K,
+                        CU_TENSOR_MAP_SWIZZLE_NONE))
+    return rc;
+  static int configured[64] = {};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  const int smem = stages * (int)Tile<BKT>::STAGE_BYTES + 1024 + 256;
+  if (dev < 0 || dev >= 64 || configured[dev] < smem) {
+    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel<BKT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64)
+      configured[dev] = smem;
+  }
+  p.stages = stages;
+  const dim3 grid((N + BN - 1) / BN, Mp / BM, p.splits);
+  gemm_w8_tc_kernel<BKT><<<grid, kThreads, smem, st>>>(map_hi, map_lo, map_w, p);
+  B200_LAUNCH_CHECK();
+  if (p.splits > 1) {
+    gemm_w8_combine_kernel<<<grid.x * grid.y, 256, 0, st>>>(p, (int)grid.x);
+    B200_LAUNCH_CHECK();
+  }
+  return B200_OK;
+}
+
 extern "C" {
 
 int64_t b200_gemm_w8_workspace_bytes(int M, int64_t K) {
   if (M < 1 || K < 1)
     return 0;
   const int64_t Mp = (M + BM - 1) / BM * BM, Kp = packed_k(B200_W_I8, K);
-  return 2 * Mp * Kp * 2 + 256;   // hi and lo, bf16; + an error word
+  // an error word, hi and lo (bf16), and the split-K partial tiles
+  return 256 + 2 * Mp * Kp * 2 + (int64_t)kMaxPartialTiles * BM * BN * 4;
 }
 
 int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
@@ -415,8 +514,8 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
     return fail(B200_EINVAL, "gemm_w8: null argument");
   if (w->kind != B200_W_I8 || w->scale_dtype != B200_F32 || !w->scale || !w->w)
     return fail(B200_EINVAL, "gemm_w8: int8 per-channel weights with f32 scales expected");
-  if (M < 1 || w->K % BK != 0 || w->N < 1 || (silu_pairs && (w->N & 1)))
-    return fail(B200_EINVAL, "gemm_w8: M >= 1, K a multiple of %d, even N for gate/up pairs", BK);
+  if (M < 1 || w->K % 64 != 0 || w->N < 1 || (silu_pairs && (w->N & 1)))
+    return fail(B200_EINVAL, "gemm_w8: M >= 1, K a multiple of 64, even N for gate/up pairs");
   if (((uintptr_t)w->w & 15) || ((uintptr_t)workspace & 255))
     return fail(B200_EINVAL, "gemm_w8: weight rows must be 16-byte aligned, the workspace 256-byte aligned");
   if (workspace_bytes < b200_gemm_w8_workspace_bytes(M, w->K))
@@ -432,14 +531,6 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   B200_CUDA(cudaMemsetAsync(err, 0, 4, st));
   split_activations_kernel<<<Mp, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
   B200_LAUNCH_CHECK();
-  CUtensorMap map_hi, map_lo, map_w;
-  if (int rc = make_map(&map_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, hi, K, Mp, (uint64_t)K * 2, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
-  if (int rc = make_map(&map_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, lo, K, Mp, (uint64_t)K * 2, CU_TENSOR_MAP_SWIZZLE_128B))
-    return rc;
-  if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, const_cast<void *>(w->w), K, N, (uint64_t)K,
-                        CU_TENSOR_MAP_SWIZZLE_NONE))
-    return rc;
   GemmParams p{};
   p.M = M;
   p.N = N;
@@ -451,20 +542,28 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   p.ldc = ldc;
   p.ldr = ldr;
   p.silu_pairs = silu_pairs;
+  p.partial = reinterpret_cast<float *>(lo + (int64_t)Mp * K);
   p.error = err;
-  static bool configured[64] = {};
-  int dev = 0;
-  B200_CUDA(cudaGetDevice(&dev));
-  const int smem = kStages * STAGE_BYTES + 1024 + 256;
-  if (dev < 0 || dev >= 64 || !configured[dev]) {
-    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
-    if (dev >= 0 && dev < 64)
-      configured[dev] = true;
+  // k block, ring depth: experiment switch "bk,stages" (default 32,3: two CTAs per SM)
+  int bk = 32, stages = 3;
+  if (const char *e = getenv("BUDDY_B200_GEMM_CFG"))
+    sscanf(e, "%d,%d", &bk, &stages);
+  if ((bk != 32 && bk != 64) || stages < 2 || stages > (bk == 64 ? 3 : 7))
+    return fail(B200_EINVAL, "gemm_w8: bad BUDDY_B200_GEMM_CFG");
+  // split over K when the output tiles alone leave most SMs idle
+  const int tiles = ((N + BN - 1) / BN) * (Mp / BM), nkb = K / bk;
+  int splits = 1;
+  if (tiles < 100) {
+    splits = kMaxPartialTiles / tiles;
+    if (splits > nkb / 4)
+      splits = nkb / 4;
+    if (splits < 1)
+      splits = 1;
   }
-  dim3 grid((N + BN - 1) / BN, Mp / BM);
-  gemm_w8_tc_kernel<<<grid, kThreads, smem, st>>>(map_hi, map_lo, map_w, p);
-  B200_LAUNCH_CHECK();
-  return B200_OK;
+  if (getenv("BUDDY_B200_GEMM_NOSPLIT"))
+    splits = 1;
+  p.splits = splits;
+  return bk == 64 ? gemm_launch<64>(w, hi, lo, Mp, p, stages, st) : gemm_launch<32>(w, hi, lo, Mp, p, stages, st);
 }
 
 /* 0, or the code of the first bounded wait that gave up in the last b200_gemm_w8 on this workspace

@@ -349,6 +349,176 @@ int launch_paged_attn(const float *qkv, int64_t ld, const float *kp, const float
   return B200_OK;
 }
 
+// The same scan for few rows with long histories (batched decode): the keys of a row
+// are cut into chunks of kPagedChunk positions, one CTA of 8 warps per (row, kv head,
+// chunk); a warp owns every 8th key of the chunk and keeps four K/V rows in flight.
+// Partials (m, l, acc[D]) per query head go to `part`; gqa_paged_combine_kernel folds
+// the chunks of a row in chunk order.
+constexpr int kPagedChunk = 256;
+template <int G, int VEC>
+__global__ void __launch_bounds__(256)
+gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *part,
+                       int kv_heads, int page, const int32_t *row_seq, const int32_t *row_pos,
+                       const int32_t *block_table, int table_stride) {
+  constexpr int D = VEC * 32, W = 8, U = 4;
+  const int m = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
+  const int len = row_pos[m] + 1;
+  const int j0 = sp * kPagedChunk;
+  if (j0 >= len)
+    return;
+  const int j1 = min(len, j0 + kPagedChunk);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int32_t *table = block_table + (int64_t)row_seq[m] * table_stride;
+  const float scale = rsqrtf((float)D);
+  const float *qrow = qkv + (int64_t)m * ld + (int64_t)hk * G * D;
+  float qr[G][VEC];
+#pragma unroll
+  for (int g = 0; g < G; ++g)
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      qr[g][e] = qrow[g * D + lane * VEC + e];
+  float mx[G], l[G], acc[G][VEC];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    mx[g] = kSeed;
+    l[g] = 0.f;
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      acc[g][e] = 0.f;
+  }
+  for (int jb = j0 + warp; jb < j1; jb += W * U) {
+    float kr[U][VEC], vr[U][VEC];
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      const int j = jb + u * W;
+      if (j < j1) {
+        const int pg = table[j / page];
+        const int64_t crow = (((int64_t)pg * kv_heads + hk) * page + j % page) * D + lane * VEC;
+        if (VEC == 4) {
+          const float4 a = *reinterpret_cast<const float4 *>(k_pool + crow);
+          const float4 b = *reinterpret_cast<const float4 *>(v_pool + crow);
+          kr[u][0] = a.x; kr[u][1] = a.y; kr[u][2 % VEC] = a.z; kr[u][3 % VEC] = a.w;
+          vr[u][0] = b.x; vr[u][1] = b.y; vr[u][2 % VEC] = b.z; vr[u][3 % VEC] = b.w;
+        } else {
+#pragma unroll
+          for (int e = 0; e < VEC; ++e) {
+            kr[u][e] = k_pool[crow + e];
+            vr[u][e] = v_pool[crow + e];
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int u = 0; u < U; ++u) {
+      if (jb + u * W >= j1)
+        break;
+      float s[G];
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        float d = 0.f;
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          d = fmaf(qr[g][e], kr[u][e], d);
+        s[g] = d;
+      }
+#pragma unroll
+      for (int o = 16; o > 0; o >>= 1)
+#pragma unroll
+        for (int g = 0; g < G; ++g)
+          s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
+#pragma unroll
+      for (int g = 0; g < G; ++g) {
+        s[g] *= scale;
+        const float nm = fmaxf(mx[g], s[g]);
+        const float alpha = expf(mx[g] - nm);
+        const float pw = expf(s[g] - nm);
+        l[g] = fmaf(l[g], alpha, pw);
+#pragma unroll
+        for (int e = 0; e < VEC; ++e)
+          acc[g][e] = fmaf(acc[g][e], alpha, pw * vr[u][e]);
+        mx[g] = nm;
+      }
+    }
+  }
+  __shared__ float s_m[W][G], s_l[W][G];
+  __shared__ float s_acc[W][G][D];
+#pragma unroll
+  for (int g = 0; g < G; ++g) {
+    if (lane == 0) {
+      s_m[warp][g] = mx[g];
+      s_l[warp][g] = l[g];
+    }
+#pragma unroll
+    for (int e = 0; e < VEC; ++e)
+      s_acc[warp][g][lane * VEC + e] = acc[g][e];
+  }
+  __syncthreads();
+  float *pout = part + (((int64_t)m * kv_heads + hk) * gridDim.z + sp) * G * (D + 2);
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx - g * D;
+    float M = kSeed;
+#pragma unroll
+    for (int w = 0; w < W; ++w)
+      M = fmaxf(M, s_m[w][g]);
+    float L = 0.f, A = 0.f;
+#pragma unroll
+    for (int w = 0; w < W; ++w) {
+      const float b = expf(s_m[w][g] - M);   // a warp that saw no key: l = 0, acc = 0
+      L = fmaf(s_l[w][g], b, L);
+      A = fmaf(s_acc[w][g][d], b, A);
+    }
+    pout[g * (D + 2) + 2 + d] = A;
+    if (d == 0) {
+      pout[g * (D + 2)] = M;
+      pout[g * (D + 2) + 1] = L;
+    }
+  }
+}
+
+template <int G, int D>
+__global__ void __launch_bounds__(128)
+gqa_paged_combine_kernel(const float *part, float *out, int64_t ldo, int kv_heads, int chunks,
+                         const int32_t *row_pos) {
+  const int m = blockIdx.x, hk = blockIdx.y;
+  const int n = (row_pos[m] + kPagedChunk) / kPagedChunk;   // chunks that hold keys of this row
+  const float *pin = part + (((int64_t)m * kv_heads + hk) * chunks) * G * (D + 2);
+  for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
+    const int g = idx / D, d = idx - g * D;
+    float M = kSeed;
+    for (int c = 0; c < n; ++c)
+      M = fmaxf(M, pin[(int64_t)(c * G + g) * (D + 2)]);
+    float L = 0.f, A = 0.f;
+    for (int c = 0; c < n; ++c) {
+      const float *q = pin + (int64_t)(c * G + g) * (D + 2);
+      const float b = expf(q[0] - M);
+      L = fmaf(q[1], b, L);
+      A = fmaf(q[2 + d], b, A);
+    }
+    out[(int64_t)m * ldo + (int64_t)(hk * G + g) * D + d] = __fdiv_rn(A, L);
+  }
+}
+
+template <int G>
+int launch_paged_split(const float *qkv, int64_t ld, const float *kp, const float *vp, float *out, int64_t ldo,
+                       int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
+                       const int32_t *block_table, int table_stride, int M, float *part, int chunks,
+                       cudaStream_t st) {
+  dim3 grid(M, kv_heads, chunks), cgrid(M, kv_heads);
+  if (D == 128) {
+    gqa_paged_split_kernel<G, 4><<<grid, 256, 0, st>>>(qkv, ld, kp, vp, part, kv_heads, page, row_seq, row_pos,
+                                                       block_table, table_stride);
+    B200_LAUNCH_CHECK();
+    gqa_paged_combine_kernel<G, 128><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos);
+  } else {
+    gqa_paged_split_kernel<G, 2><<<grid, 256, 0, st>>>(qkv, ld, kp, vp, part, kv_heads, page, row_seq, row_pos,
+                                                       block_table, table_stride);
+    B200_LAUNCH_CHECK();
+    gqa_paged_combine_kernel<G, 64><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos);
+  }
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 // one first-maximum per row of a [rows, n] matrix (Sampler.h:101-104)
 __global__ void argmax_rows_kernel(const float *v, int64_t n, int32_t *out) {
   const float *row = v + (int64_t)blockIdx.x * n;
@@ -401,14 +571,28 @@ int rope_kv_paged_launch(float *qkv, int64_t ld, float *k_pool, float *v_pool, c
   return B200_OK;
 }
 
+int64_t gqa_paged_scratch_floats(int rows, int q_heads, int D, int max_context) {
+  const int chunks = (max_context + kPagedChunk - 1) / kPagedChunk;
+  return (int64_t)rows * chunks * q_heads * (D + 2);
+}
+
+// scratch: gqa_paged_scratch_floats(M, ..) floats, or null (then, and for more than
+// kPagedSplitRows rows, every row is scanned by one CTA)
 int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out, int64_t ldo,
                      int q_heads, int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
-                     const int32_t *block_table, int table_stride, int M, cudaStream_t st) {
+                     const int32_t *block_table, int table_stride, int M, float *scratch, int max_context,
+                     cudaStream_t st) {
   if (D != 64 && D != 128)
     return fail(B200_EINVAL, "gqa_paged: head_dim %d (64 or 128 supported)", D);
+  constexpr int kPagedSplitRows = 256;
+  const bool split = scratch != nullptr && M <= kPagedSplitRows && max_context > kPagedChunk;
+  const int chunks = (max_context + kPagedChunk - 1) / kPagedChunk;
   switch (q_heads / kv_heads) {
 #define B200_G(G_)                                                                                          \
   case G_:                                                                                                  \
+    if (split)                                                                                              \
+      return launch_paged_split<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos, \
+                                    block_table, table_stride, M, scratch, chunks, st);                     \
     return launch_paged_attn<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos,    \
                                  block_table, table_stride, M, st);
     B200_G(1) B200_G(2) B200_G(3) B200_G(4) B200_G(6) B200_G(8)
