@@ -142,6 +142,9 @@ int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const fl
                      int q_heads, int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
                      const int32_t *block_table, int table_stride, int M, float *scratch, int max_context,
                      cudaStream_t st);
+int gqa_paged_prefill_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out,
+                             int64_t ldo, int q_heads, int kv_heads, int D, int page, const int32_t *seq_table,
+                             int pos0, int M, int max_context, cudaStream_t st);
 int64_t gqa_paged_scratch_floats(int rows, int q_heads, int D, int max_context);
 int argmax_rows_launch(const float *v, int64_t n, int rows, int32_t *out, cudaStream_t st);
 

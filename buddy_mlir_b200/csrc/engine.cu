@@ -1597,6 +1597,9 @@ static int batch_rows(b200_batch *b, int M, const int32_t *tokens, const int32_t
   B200_CUDA(cudaMemcpyAsync(b->d_seq, row_seq, (size_t)M * 4, cudaMemcpyHostToDevice, st));
   B200_CUDA(cudaMemcpyAsync(b->d_pos, row_pos, (size_t)M * 4, cudaMemcpyHostToDevice, st));
   B200_CUDA(cudaMemcpyAsync(b->d_table, b->table.data(), b->table.size() * 4, cudaMemcpyHostToDevice, st));
+  bool one_chunk = M >= 64;
+  for (int r = 1; r < M && one_chunk; ++r)
+    one_chunk = row_seq[r] == row_seq[0] && row_pos[r] == row_pos[0] + r;
   if (int rc = embed_rows_launch(m->embed, m->pf_tokens, m->pf_x, H, M, st)) return rc;
   for (int l = 0; l < c.n_layers; ++l) {
     Layer &L = m->layers[l];
@@ -1605,10 +1608,17 @@ static int batch_rows(b200_batch *b, int M, const int32_t *tokens, const int32_t
                                       L.k_norm, c.eps, m->qh, m->kvh, D, b->page, b->d_seq, b->d_pos, b->d_table,
                                       b->table_stride, M, st))
       return rc;
-    if (int rc = gqa_paged_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->pf_att, QD, m->qh, m->kvh,
-                                  D, b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M,
-                                  M <= b->part_rows ? b->d_part : nullptr, b->max_context, st))
-      return rc;
+    int arc = B200_ESTATE;
+    if (one_chunk)   // a prefill chunk: consecutive positions of one sequence
+      arc = gqa_paged_prefill_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->pf_att, QD, m->qh, m->kvh,
+                                     D, b->page, b->d_table + (size_t)row_seq[0] * b->table_stride, row_pos[0], M,
+                                     b->max_context, st);
+    if (arc == B200_ESTATE)
+      arc = gqa_paged_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->pf_att, QD, m->qh, m->kvh, D,
+                             b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M,
+                             M <= b->part_rows ? b->d_part : nullptr, b->max_context, st);
+    if (arc)
+      return arc;
     if (int rc = linear_rows(m, L.o, m->pf_att, QD, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
     if (int rc = linear_rows(m, L.gateup, m->pf_x, H, M, m->pf_mid, m->ffn, nullptr, L.post_norm, true)) return rc;
     if (int rc = linear_rows(m, L.down, m->pf_mid, m->ffn, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;

@@ -43,17 +43,21 @@ namespace {
 constexpr int BM = 128, BN = 128;              // output tile of one CTA
 constexpr int kMaxStages = 8;
 constexpr int kTmemCols = 128;                 // f32 accumulator 128 lanes x 128 columns
-constexpr int kThreads = 192;                  // warp 0 loader, warp 1 mma, warps 2..5 convert + epilogue
+// warp 0 loader, warp 1 mma, then the conversion + epilogue warps: 8 when the CTA converts
+// the int8 tile itself, 4 (epilogue only) when the weights arrive as bf16
+constexpr int kThreadsConv = 320, kThreadsPre = 192;
 constexpr int kMaxPartialTiles = 320;          // split-K: 128 x 128 f32 partial tiles in the workspace
 constexpr uint32_t kSpin = 1u << 26;
 constexpr unsigned long long kWaitNs = 2000000000ull;
 
 // Shared-memory stage for a k block of BKT elements (64: 128-byte swizzle rows, 32: 64-byte rows).
-template <int BKT> struct Tile {
-  static constexpr uint32_t A_BYTES = BM * BKT * 2;      // one bf16 term of the activations
-  static constexpr uint32_t WRAW_BYTES = BN * BKT;       // int8 weights as stored
-  static constexpr uint32_t WB_BYTES = BN * BKT * 2;     // the same tile as bf16
-  static constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + WRAW_BYTES + WB_BYTES;   // 56 KB / 28 KB
+// PRE: the weight tile is loaded as bf16 (converted by a pass over the weights before the
+// GEMM); else the raw int8 tile is loaded and converted by the CTA.
+template <int BKT, bool PRE> struct Tile {
+  static constexpr uint32_t A_BYTES = BM * BKT * 2;              // one bf16 term of the activations
+  static constexpr uint32_t WRAW_BYTES = PRE ? 0 : BN * BKT;     // int8 weights as stored
+  static constexpr uint32_t WB_BYTES = BN * BKT * 2;             // the weight tile as bf16
+  static constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + WRAW_BYTES + WB_BYTES;
   static constexpr uint32_t ROW_BYTES = BKT * 2;
 };
 
@@ -121,7 +125,7 @@ template <int BKT> __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) 
   uint64_t d = 0;
   d |= (uint64_t)((addr & 0x3FFFFu) >> 4);
   d |= (uint64_t)1 << 16;
-  d |= (uint64_t)((8 * Tile<BKT>::ROW_BYTES) >> 4) << 32;
+  d |= (uint64_t)((8 * BKT * 2) >> 4) << 32;
   d |= (uint64_t)1 << 46;
   d |= (uint64_t)(BKT == 64 ? 2 : 4) << 61;
   return d;
@@ -141,7 +145,8 @@ __device__ __forceinline__ void tc_commit(uint64_t *bar) {
 }
 
 struct GemmParams {
-  int M, N, K;                 // K = packed k (multiple of 64)
+  int M, N, K;                 // N = weight rows covered by this launch; K = packed k (multiple of 64)
+  int n_off;                   // first weight row of the launch: scale, bias, residual and C are indexed n_off + n
   const float *scale;          // [N]
   const float *bias;           // [N] or null
   const float *residual;       // [M, ldr] or null
@@ -152,10 +157,12 @@ struct GemmParams {
   int splits;                  // CTAs along K per output tile (gridDim.z); > 1: raw sums go to `partial`
   float *partial;              // [tiles][splits][128][128] f32
   int *error;
+  int debug;                   // experiment: 1 = no MMA issue, 2 = no TMA loads
 };
 
 // scale / bias / residual, or the SiLU-gate of a (gate, up) column pair
 __device__ __forceinline__ void store_plain(const GemmParams &p, int m, int n, float acc) {
+  n += p.n_off;
   float y = __fmul_rn(acc, __ldg(p.scale + n));
   if (p.bias)
     y = __fadd_rn(y, __ldg(p.bias + n));
@@ -164,6 +171,7 @@ __device__ __forceinline__ void store_plain(const GemmParams &p, int m, int n, f
   p.C[(int64_t)m * p.ldc + n] = y;
 }
 __device__ __forceinline__ void store_pair(const GemmParams &p, int m, int n, float ag, float au) {
+  n += p.n_off;
   float g = __fmul_rn(ag, __ldg(p.scale + n));
   float u = __fmul_rn(au, __ldg(p.scale + n + 1));
   if (p.bias) {
@@ -174,11 +182,12 @@ __device__ __forceinline__ void store_pair(const GemmParams &p, int m, int n, fl
   p.C[(int64_t)m * p.ldc + (n >> 1)] = __fmul_rn(__fmul_rn(g, sg), u);
 }
 
-template <int BKT>
-__global__ void __launch_bounds__(kThreads, BKT == 64 ? 1 : 2)
+template <int BKT, bool PRE>
+__global__ void __launch_bounds__(PRE ? kThreadsPre : kThreadsConv, BKT == 64 ? 1 : 2)
 gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-  using T = Tile<BKT>;
+  using T = Tile<BKT, PRE>;
+  constexpr int kEpiWarps = PRE ? 4 : 8;
   extern __shared__ __align__(1024) uint8_t smem[];
   // 1024-byte alignment of every swizzled tile
   uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
@@ -195,7 +204,7 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
   if (threadIdx.x == 0) {
     for (int s = 0; s < stages; ++s) {
       mbar_init(&bars.full[s], 1);
-      mbar_init(&bars.ready[s], 128);
+      mbar_init(&bars.ready[s], 256);
       mbar_init(&bars.empty[s], 1);
     }
     mbar_init(&bars.accum, 1);
@@ -220,10 +229,14 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
           break;
         uint8_t *st = tiles + s * T::STAGE_BYTES;
         const int kx = (kb0 + i) * BKT;
-        mbar_expect_tx(&bars.full[s], 2 * T::A_BYTES + T::WRAW_BYTES);
+        if (p.debug & 2) {
+          mbar_arrive(&bars.full[s]);
+          continue;
+        }
+        mbar_expect_tx(&bars.full[s], 2 * T::A_BYTES + (PRE ? T::WB_BYTES : T::WRAW_BYTES));
         tma_load_2d(st, &map_hi, kx, m0, &bars.full[s]);
         tma_load_2d(st + T::A_BYTES, &map_lo, kx, m0, &bars.full[s]);
-        tma_load_2d(st + 2 * T::A_BYTES, &map_w, kx, n0, &bars.full[s]);
+        tma_load_2d(st + 2 * T::A_BYTES, &map_w, kx, n0, &bars.full[s]);   // PRE: lands as the bf16 tile
       }
     }
   } else if (warp == 1) {
@@ -231,12 +244,14 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
     if (lane == 0) {
       for (int i = 0; i < nkb; ++i) {
         const int s = i % stages, use = i / stages;
-        if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 702) ||
-            !mbar_wait(&bars.ready[s], use & 1, ab, p.error, 703))
+        if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 702))
+          break;
+        if (!PRE && !mbar_wait(&bars.ready[s], use & 1, ab, p.error, 703))
           break;
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_hi = smem_u32(tiles + s * T::STAGE_BYTES), a_lo = a_hi + T::A_BYTES,
                        wb = a_hi + 2 * T::A_BYTES + T::WRAW_BYTES;
+        if (!(p.debug & 1))
 #pragma unroll
         for (int k = 0; k < BKT / 16; ++k) {   // 16 bf16 = 32 bytes along the swizzled row
           const uint64_t db = smem_desc<BKT>(wb + k * 32);
@@ -248,61 +263,67 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       tc_commit(&bars.accum);
     }
   } else {
-    // ---- int8 -> bf16 conversion of the weight tile, then the epilogue ------------------
-    const int t = threadIdx.x - 64;           // 0..127: weight row of the tile (conversion), accumulator row (epilogue)
-    constexpr int NQ = BKT / 16;              // 16-byte units of raw weights per row
-    // 16-byte chunk c of row r of a swizzled tile sits at chunk c ^ swz(r)
-    const int swz = BKT == 64 ? (t & 7) : ((t >> 1) & 3);
     bool alive = true;
-    for (int i = 0; i < nkb && alive; ++i) {
-      const int s = i % stages, use = i / stages;
-      if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 704)) {
-        alive = false;
-        break;
-      }
-      uint8_t *st = tiles + s * T::STAGE_BYTES;
-      const uint4 *raw = reinterpret_cast<const uint4 *>(st + 2 * T::A_BYTES + t * BKT);
-      uint8_t *dst = st + 2 * T::A_BYTES + T::WRAW_BYTES + t * T::ROW_BYTES;   // row t of the swizzled bf16 tile
-#pragma unroll
-      for (int qq = 0; qq < NQ; ++qq) {         // 16 int8 -> two 16-byte chunks of bf16
-        // neighbouring rows start at different 16-byte units, so that the eight threads of a
-        // quarter warp read eight different bank groups
-        const int q = (qq + (BKT == 64 ? (t >> 1) : (t >> 2))) & (NQ - 1);
-        const uint4 w = raw[q];
-        const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
-        uint32_t o[8];
-#pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          // byte u = q + 128 placed in the mantissa of 2^23: (2^23 + u) - (2^23 + 128) = q, exact
-          const float f0 = __uint_as_float(0x4B000000u | (ws[j] & 0xFFu)) - 8388736.0f;
-          const float f1 = __uint_as_float(0x4B000000u | ((ws[j] >> 8) & 0xFFu)) - 8388736.0f;
-          const float f2 = __uint_as_float(0x4B000000u | ((ws[j] >> 16) & 0xFFu)) - 8388736.0f;
-          const float f3 = __uint_as_float(0x4B000000u | (ws[j] >> 24)) - 8388736.0f;
-          // an integer of magnitude <= 128 is its own bf16: keep the upper halves
-          o[2 * j] = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
-          o[2 * j + 1] = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+    if (!PRE) {
+      // ---- int8 -> bf16 conversion of the weight tile: 256 threads, two per weight row --------
+      const int t = threadIdx.x - 64;           // 0..255
+      const int r = t & 127, half = t >> 7;
+      constexpr int NQ = BKT / 32;              // 16-byte units of raw weights per thread
+      // 16-byte chunk c of row r of a swizzled tile sits at chunk c ^ swz(r)
+      const int swz = BKT == 64 ? (r & 7) : ((r >> 1) & 3);
+      for (int i = 0; i < nkb && alive; ++i) {
+        const int s = i % stages, use = i / stages;
+        if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 704)) {
+          alive = false;
+          break;
         }
-        const int c0 = 2 * q, c1 = 2 * q + 1;
-        *reinterpret_cast<uint4 *>(dst + ((c0 ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
-        *reinterpret_cast<uint4 *>(dst + ((c1 ^ swz) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        uint8_t *st = tiles + s * T::STAGE_BYTES;
+        const uint4 *raw = reinterpret_cast<const uint4 *>(st + 2 * T::A_BYTES + r * BKT);
+        uint8_t *dst = st + 2 * T::A_BYTES + T::WRAW_BYTES + r * T::ROW_BYTES;   // row r of the swizzled bf16 tile
+#pragma unroll
+        for (int qq = 0; qq < NQ; ++qq) {         // 16 int8 -> two 16-byte chunks of bf16
+          // neighbouring rows start at different 16-byte units (fewer bank conflicts on the raw reads)
+          const int q = half * NQ + ((qq + (r >> 1)) & (NQ - 1));
+          const uint4 w = raw[q];
+          const uint32_t ws[4] = {w.x ^ 0x80808080u, w.y ^ 0x80808080u, w.z ^ 0x80808080u, w.w ^ 0x80808080u};
+          uint32_t o[8];
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            // byte u = q + 128 placed in the mantissa of 2^23: (2^23 + u) - (2^23 + 128) = q, exact
+            const float f0 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7440)) - 8388736.0f;
+            const float f1 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7441)) - 8388736.0f;
+            const float f2 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7442)) - 8388736.0f;
+            const float f3 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7443)) - 8388736.0f;
+            // an integer of magnitude <= 128 is its own bf16: keep the upper halves
+            o[2 * j] = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+            o[2 * j + 1] = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+          }
+          const int c0 = 2 * q, c1 = 2 * q + 1;
+          *reinterpret_cast<uint4 *>(dst + ((c0 ^ swz) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          *reinterpret_cast<uint4 *>(dst + ((c1 ^ swz) << 4)) = make_uint4(o[4], o[5], o[6], o[7]);
+        }
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
+        mbar_arrive(&bars.ready[s]);
       }
-      asm volatile("fence.proxy.async.shared::cta;" ::: "memory");   // generic writes -> visible to the tensor core's reads
-      mbar_arrive(&bars.ready[s]);
     }
-    // ---- epilogue: accumulator row (lane of tensor memory) = this thread's output row ----
-    if (alive && mbar_wait(&bars.accum, 0, ab, p.error, 705)) {
+    // ---- epilogue ---------------------------------------------------------------------
+    // A thread owns one accumulator row (its lane of tensor memory).  Scaled values go to a
+    // padded tile in shared memory (the ring is idle by now), then the warps write whole
+    // rows: 128-byte coalesced stores instead of one 4-byte store per thread and column.
+    const bool ok = alive && mbar_wait(&bars.accum, 0, ab, p.error, 705);
+    constexpr int LDS = BN + 1;                       // row stride of the staging tile, in floats
+    float *ep = reinterpret_cast<float *>(tiles);     // [BM][LDS]: 66 KB <= the ring
+    const int width = p.splits > 1 ? BN : (p.silu_pairs ? BN / 2 : BN);
+    if (ok) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-      // a warp reads the 32 lanes of tensor memory that match its rank within its warpgroup
+      // a warp reads the 32 lanes of tensor memory that match its rank within its warpgroup;
+      // with eight epilogue warps two of them share a lane quarter and take half the columns each
       const int quad = warp & 3;
       const int row = quad * 32 + lane;
-      const int m = m0 + row;
-      float *prow = nullptr;
-      if (p.splits > 1) {
-        const int64_t tile = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
-        prow = p.partial + ((tile * p.splits + blockIdx.z) * BM + row) * BN;
-      }
+      const int cb0 = kEpiWarps == 8 ? ((warp - 2) >> 2) * (BN / 2) : 0;
+      const int cb1 = kEpiWarps == 8 ? cb0 + BN / 2 : BN;
 #pragma unroll 1
-      for (int cb = 0; cb < BN; cb += 32) {
+      for (int cb = cb0; cb < cb1; cb += 32) {
         uint32_t v[32];
         const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)cb;
         asm volatile(
@@ -316,30 +337,67 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
             : "r"(taddr)
             : "memory");
         asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-        if (prow != nullptr) {
+        float *erow = ep + row * LDS;
+        if (p.splits > 1) {
           // split-K: raw sums of this CTA's k range; gemm_w8_combine_kernel adds the splits
-          if (m < p.M) {
 #pragma unroll
-            for (int j = 0; j < 32; j += 4)
-              *reinterpret_cast<float4 *>(prow + cb + j) =
-                  make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
-                              __uint_as_float(v[j + 3]));
+          for (int j = 0; j < 32; ++j)
+            erow[cb + j] = __uint_as_float(v[j]);
+        } else if (p.silu_pairs) {
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) {
+            const int n = min(n0 + cb + j, p.N - 2) + p.n_off;   // columns beyond N are not stored
+            float g = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
+            float u = __fmul_rn(__uint_as_float(v[j + 1]), __ldg(p.scale + n + 1));
+            if (p.bias) {
+              g = __fadd_rn(g, __ldg(p.bias + n));
+              u = __fadd_rn(u, __ldg(p.bias + n + 1));
+            }
+            const float sg = 1.0f / (1.0f + expf(-g));   // subgraph0_decode_simplify.mlir:226-231
+            erow[(cb + j) >> 1] = __fmul_rn(__fmul_rn(g, sg), u);
           }
-        } else if (m < p.M) {
-          if (p.silu_pairs) {
+        } else {
 #pragma unroll
-            for (int j = 0; j < 32; j += 2) {
-              const int n = n0 + cb + j;
-              if (n + 1 < p.N)
-                store_pair(p, m, n, __uint_as_float(v[j]), __uint_as_float(v[j + 1]));
-            }
-          } else {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) {
-              const int n = n0 + cb + j;
-              if (n < p.N)
-                store_plain(p, m, n, __uint_as_float(v[j]));
-            }
+          for (int j = 0; j < 32; ++j) {
+            const int n = min(n0 + cb + j, p.N - 1) + p.n_off;
+            float y = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
+            if (p.bias)
+              y = __fadd_rn(y, __ldg(p.bias + n));
+            erow[cb + j] = y;
+          }
+        }
+      }
+    }
+    // all epilogue warps, whether they hold data or gave up: named barrier 1
+    asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+    if (ok) {
+      const int ew = warp - 2;
+      float *dst;
+      int64_t ldd;
+      int cols;                    // valid columns of this tile in the destination
+      if (p.splits > 1) {
+        const int64_t tile = (int64_t)blockIdx.y * gridDim.x + blockIdx.x;
+        dst = p.partial + (tile * p.splits + blockIdx.z) * BM * BN;
+        ldd = BN;
+        cols = BN;
+      } else if (p.silu_pairs) {
+        dst = p.C + (int64_t)m0 * p.ldc + ((n0 + p.n_off) >> 1);
+        ldd = p.ldc;
+        cols = min(BN, p.N - n0) >> 1;
+      } else {
+        dst = p.C + (int64_t)m0 * p.ldc + n0 + p.n_off;
+        ldd = p.ldc;
+        cols = min(BN, p.N - n0);
+      }
+      const float *res = (p.residual && p.splits == 1 && !p.silu_pairs) ? p.residual + (int64_t)m0 * p.ldr + n0 + p.n_off : nullptr;
+      const int rows = p.splits > 1 ? BM : min(BM, p.M - m0);
+      for (int r = ew; r < rows; r += kEpiWarps) {
+        for (int c = lane; c < width; c += 32) {
+          if (c < cols) {
+            float y = ep[r * LDS + c];
+            if (res)
+              y = __fadd_rn(res[(int64_t)r * p.ldr + c], y);
+            dst[(int64_t)r * ldd + c] = y;
           }
         }
       }
@@ -354,6 +412,28 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       }
     }
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
+  }
+}
+
+// int8 rows [rows][K] (packed k order) -> bf16, same order: the weight operand of the
+// dense path.  One 16-byte unit per thread.
+__global__ void __launch_bounds__(256)
+weights_to_bf16_kernel(const uint8_t *w, int64_t units, uint4 *out) {
+  for (int64_t u = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; u < units; u += (int64_t)gridDim.x * blockDim.x) {
+    const uint4 x = __ldg(reinterpret_cast<const uint4 *>(w) + u);
+    const uint32_t ws[4] = {x.x ^ 0x80808080u, x.y ^ 0x80808080u, x.z ^ 0x80808080u, x.w ^ 0x80808080u};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float f0 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7440)) - 8388736.0f;
+      const float f1 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7441)) - 8388736.0f;
+      const float f2 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7442)) - 8388736.0f;
+      const float f3 = __uint_as_float(__byte_perm(ws[j], 0x4B000000u, 0x7443)) - 8388736.0f;
+      o[2 * j] = __byte_perm(__float_as_uint(f0), __float_as_uint(f1), 0x7632);
+      o[2 * j + 1] = __byte_perm(__float_as_uint(f2), __float_as_uint(f3), 0x7632);
+    }
+    out[2 * u] = make_uint4(o[0], o[1], o[2], o[3]);
+    out[2 * u + 1] = make_uint4(o[4], o[5], o[6], o[7]);
   }
 }
 
@@ -464,8 +544,12 @@ int make_map(CUtensorMap *map, CUtensorMapDataType dt, int bk, void *base, uint6
 
 using namespace b200;
 
-template <int BKT>
-static int gemm_launch(const b200_weight *w, __nv_bfloat16 *hi, __nv_bfloat16 *lo, int Mp, GemmParams &p, int stages,
+// Rows of bf16 weights the dense path converts at a time (a slab of the workspace).
+constexpr int64_t kSlabElems = (int64_t)32 << 20;   // 64 MB of bf16
+constexpr int kDenseRows = 256;                      // from this many rows on, convert the weights once per call
+
+template <int BKT, bool PRE>
+static int gemm_launch(const void *wbase, __nv_bfloat16 *hi, __nv_bfloat16 *lo, int Mp, GemmParams &p, int stages,
                        cudaStream_t st) {
   const int K = p.K, N = p.N;
   const CUtensorMapSwizzle swz = BKT == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
@@ -474,21 +558,29 @@ static int gemm_launch(const b200_weight *w, __nv_bfloat16 *hi, __nv_bfloat16 *l
     return rc;
   if (int rc = make_map(&map_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, lo, K, Mp, (uint64_t)K * 2, swz))
     return rc;
-  if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, BKT, const_cast<void *>(w->w), K, N, (uint64_t)K,
-                        CU_TENSOR_MAP_SWIZZLE_NONE))
-    return rc;
+  if (PRE) {
+    if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, const_cast<void *>(wbase), K, N,
+                          (uint64_t)K * 2, swz))
+      return rc;
+  } else {
+    if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, BKT, const_cast<void *>(wbase), K, N, (uint64_t)K,
+                          CU_TENSOR_MAP_SWIZZLE_NONE))
+      return rc;
+  }
   static int configured[64] = {};
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
-  const int smem = stages * (int)Tile<BKT>::STAGE_BYTES + 1024 + 256;
+  const int smem = stages * (int)Tile<BKT, PRE>::STAGE_BYTES + 1024 + 256;
   if (dev < 0 || dev >= 64 || configured[dev] < smem) {
-    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel<BKT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel<BKT, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64)
       configured[dev] = smem;
   }
+  if ((size_t)stages * Tile<BKT, PRE>::STAGE_BYTES < (size_t)BM * (BN + 1) * 4)
+    return fail(B200_EINVAL, "gemm_w8: the ring is smaller than the epilogue's staging tile");
   p.stages = stages;
   const dim3 grid((N + BN - 1) / BN, Mp / BM, p.splits);
-  gemm_w8_tc_kernel<BKT><<<grid, kThreads, smem, st>>>(map_hi, map_lo, map_w, p);
+  gemm_w8_tc_kernel<BKT, PRE><<<grid, PRE ? kThreadsPre : kThreadsConv, smem, st>>>(map_hi, map_lo, map_w, p);
   B200_LAUNCH_CHECK();
   if (p.splits > 1) {
     gemm_w8_combine_kernel<<<grid.x * grid.y, 256, 0, st>>>(p, (int)grid.x);
@@ -503,8 +595,8 @@ int64_t b200_gemm_w8_workspace_bytes(int M, int64_t K) {
   if (M < 1 || K < 1)
     return 0;
   const int64_t Mp = (M + BM - 1) / BM * BM, Kp = packed_k(B200_W_I8, K);
-  // an error word, hi and lo (bf16), and the split-K partial tiles
-  return 256 + 2 * Mp * Kp * 2 + (int64_t)kMaxPartialTiles * BM * BN * 4;
+  // an error word, hi and lo (bf16), the split-K partial tiles, and for the dense path a slab of bf16 weights
+  return 256 + 2 * Mp * Kp * 2 + (int64_t)kMaxPartialTiles * BM * BN * 4 + (M >= kDenseRows ? kSlabElems * 2 : 0);
 }
 
 int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
@@ -528,6 +620,8 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   int *err = reinterpret_cast<int *>(workspace);
   __nv_bfloat16 *hi = reinterpret_cast<__nv_bfloat16 *>((char *)workspace + 256);
   __nv_bfloat16 *lo = hi + (int64_t)Mp * K;
+  float *partial = reinterpret_cast<float *>(lo + (int64_t)Mp * K);
+  __nv_bfloat16 *slab = reinterpret_cast<__nv_bfloat16 *>(partial + (int64_t)kMaxPartialTiles * BM * BN);
   B200_CUDA(cudaMemsetAsync(err, 0, 4, st));
   split_activations_kernel<<<Mp, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
   B200_LAUNCH_CHECK();
@@ -542,28 +636,47 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   p.ldc = ldc;
   p.ldr = ldr;
   p.silu_pairs = silu_pairs;
-  p.partial = reinterpret_cast<float *>(lo + (int64_t)Mp * K);
+  p.partial = partial;
   p.error = err;
-  // k block, ring depth: experiment switch "bk,stages" (default 32,3: two CTAs per SM)
-  int bk = 32, stages = 3;
+  p.splits = 1;
+  if (const char *e = getenv("BUDDY_B200_GEMM_DEBUG"))
+    p.debug = atoi(e);
+  // experiment switch "bk,stages[,dense rows]"
+  int bk = 32, stages = 3, dense_rows = kDenseRows;
   if (const char *e = getenv("BUDDY_B200_GEMM_CFG"))
-    sscanf(e, "%d,%d", &bk, &stages);
-  if ((bk != 32 && bk != 64) || stages < 2 || stages > (bk == 64 ? 3 : 7))
+    sscanf(e, "%d,%d,%d", &bk, &stages, &dense_rows);
+  if ((bk != 32 && bk != 64) || stages < 2 || stages > kMaxStages)
     return fail(B200_EINVAL, "gemm_w8: bad BUDDY_B200_GEMM_CFG");
+  if (dense_rows < kDenseRows)
+    dense_rows = kDenseRows;   // the workspace holds a slab only from kDenseRows rows on
+  if (M >= dense_rows) {
+    // dense path: the weights of a slab of rows become bf16 once, then a plain bf16 x bf16 GEMM over the slab
+    int64_t rows_per_slab = kSlabElems / K / BN * BN;
+    for (int64_t r0 = 0; r0 < N; r0 += rows_per_slab) {
+      const int64_t rows = N - r0 < rows_per_slab ? N - r0 : rows_per_slab;
+      const int64_t units = rows * K / 16;
+      weights_to_bf16_kernel<<<(unsigned)((units + 255) / 256 < 148 * 8 ? (units + 255) / 256 : 148 * 8), 256, 0, st>>>(
+          (const uint8_t *)w->w + r0 * K, units, reinterpret_cast<uint4 *>(slab));
+      B200_LAUNCH_CHECK();
+      p.N = (int)rows;
+      p.n_off = (int)r0;
+      const int rc = bk == 64 ? gemm_launch<64, true>(slab, hi, lo, Mp, p, stages, st)
+                              : gemm_launch<32, true>(slab, hi, lo, Mp, p, stages, st);
+      if (rc)
+        return rc;
+    }
+    return B200_OK;
+  }
   // split over K when the output tiles alone leave most SMs idle
   const int tiles = ((N + BN - 1) / BN) * (Mp / BM), nkb = K / bk;
-  int splits = 1;
   if (tiles < 100) {
-    splits = kMaxPartialTiles / tiles;
+    int splits = kMaxPartialTiles / tiles;
     if (splits > nkb / 4)
       splits = nkb / 4;
-    if (splits < 1)
-      splits = 1;
+    p.splits = splits < 1 ? 1 : splits;
   }
-  if (getenv("BUDDY_B200_GEMM_NOSPLIT"))
-    splits = 1;
-  p.splits = splits;
-  return bk == 64 ? gemm_launch<64>(w, hi, lo, Mp, p, stages, st) : gemm_launch<32>(w, hi, lo, Mp, p, stages, st);
+  return bk == 64 ? gemm_launch<64, false>(w->w, hi, lo, Mp, p, stages, st)
+                  : gemm_launch<32, false>(w->w, hi, lo, Mp, p, stages, st);
 }
 
 /* 0, or the code of the first bounded wait that gave up in the last b200_gemm_w8 on this workspace

@@ -172,6 +172,236 @@ gqa_prefill_kernel(const float *qkv, int64_t ld, const float *kc, const float *v
   }
 }
 
+// Causal attention tiled over query rows (flash style, f32 on the CUDA cores).
+// A CTA takes BQ consecutive query rows of one kv head: R = BQ * G query vectors
+// (row r = query row r / G, head hk * G + r % G) against tiles of 32 keys staged in
+// shared memory, so a K/V row is read once per BQ query rows instead of once per
+// row.  256 threads as 32 x 8: thread (ty, tx) owns query vectors 4ty..4ty+3; for
+// the scores it owns keys 4tx..4tx+3 of the tile, for the output the float4 column
+// chunks tx + 8i.  Per key tile: S = Q K^T (register tile 4 x 4 over D), running
+// max / sum per row across the 8 threads of a row (tosa.py:14245-14252, one update
+// per tile instead of per key), P to shared memory, O += P V (register tile
+// 4 x D/8).  The next K/V tile is fetched into registers while the current one
+// is used.
+template <int G, int D>
+struct PrefillTile {
+  static constexpr int BQ = G >= 6 ? 16 : (G >= 3 ? 32 : 64);
+  static constexpr int R = BQ * G;           // <= 128
+  static constexpr int KT = 32;              // keys per tile
+  static constexpr int LDQ = D + 4, LDK = D + 4, LDP = KT + 4;
+  static constexpr size_t smem_bytes = ((size_t)R * LDQ + (size_t)KT * LDK + (size_t)KT * D + (size_t)R * LDP) * 4;
+};
+
+// PAGED: kc / vc are page pools [n_pages][kv_heads][page][D] and `table` lists the
+// pages of the one sequence all M rows belong to (positions pos0, pos0 + 1, ..).
+template <int G, int D, bool PAGED>
+__global__ void __launch_bounds__(256, 1)
+gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const float *vc, float *out, int64_t ldo,
+                         int max_len, int pos0, int M, const int32_t *table, int page, int kv_heads) {
+  using T = PrefillTile<G, D>;
+  constexpr int R = T::R, KT = T::KT, LDQ = T::LDQ, LDK = T::LDK, LDP = T::LDP, NCH = D / 32;
+  extern __shared__ __align__(16) float sm[];
+  float *Qs = sm, *Ks = Qs + R * LDQ, *Vs = Ks + KT * LDK, *Ps = Vs + KT * D;
+  // heavy tiles (late rows, long histories) first
+  const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y;
+  const int m0 = qt * T::BQ;
+  const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;
+  const bool row_thread = 4 * ty < R;
+  const float scale = rsqrtf((float)D);
+  // keys this tile needs: up to the position of its last live row
+  const int last_m = min(m0 + T::BQ, M) - 1;
+  const int n_keys = min(pos0 + last_m, max_len - 1) + 1;
+  const float *kbase = PAGED ? kc : kc + (int64_t)hk * max_len * D;
+  const float *vbase = PAGED ? vc : vc + (int64_t)hk * max_len * D;
+
+  // ---- stage Q: row r = (query row r / G, head r % G), G heads of a row are contiguous ----
+  for (int idx = tid; idx < R * (D / 4); idx += 256) {
+    const int r = idx / (D / 4), c = idx - r * (D / 4);
+    const int m = m0 + r / G;
+    float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (m < M)
+      v = *reinterpret_cast<const float4 *>(qkv + (int64_t)m * ld + (int64_t)(hk * G + r % G) * D + 4 * c);
+    *reinterpret_cast<float4 *>(Qs + r * LDQ + 4 * c) = v;
+  }
+  // per-thread K/V fetch slots: KT * D / 4 float4 per tile over 256 threads
+  constexpr int NF = KT * (D / 4) / 256;   // 4 (D = 128) or 2 (D = 64)
+  float4 kf[NF], vf[NF];
+  auto fetch = [&](int k0) {
+#pragma unroll
+    for (int i = 0; i < NF; ++i) {
+      const int idx = tid + 256 * i;
+      const int j = idx / (D / 4), c = idx - j * (D / 4);
+      if (k0 + j < n_keys) {
+        const int key = k0 + j;
+        const int64_t roff = PAGED ? (((int64_t)table[key / page] * kv_heads + hk) * page + key % page) * D
+                                   : (int64_t)key * D;
+        kf[i] = __ldg(reinterpret_cast<const float4 *>(kbase + roff + 4 * c));
+        vf[i] = __ldg(reinterpret_cast<const float4 *>(vbase + roff + 4 * c));
+      } else {
+        kf[i] = make_float4(0.f, 0.f, 0.f, 0.f);
+        vf[i] = kf[i];
+      }
+    }
+  };
+  auto stash = [&]() {
+#pragma unroll
+    for (int i = 0; i < NF; ++i) {
+      const int idx = tid + 256 * i;
+      const int j = idx / (D / 4), c = idx - j * (D / 4);
+      *reinterpret_cast<float4 *>(Ks + j * LDK + 4 * c) = kf[i];
+      *reinterpret_cast<float4 *>(Vs + j * D + 4 * c) = vf[i];
+    }
+  };
+
+  float mrow[4], lrow[4], acc[4][NCH * 4];
+  int qpos[4];
+#pragma unroll
+  for (int a = 0; a < 4; ++a) {
+    mrow[a] = kSeed;
+    lrow[a] = 0.f;
+    const int m = m0 + (4 * ty + a) / G;
+    qpos[a] = (row_thread && m < M) ? min(pos0 + m, max_len - 1) : -1;   // -1: every key is masked
+#pragma unroll
+    for (int c = 0; c < NCH * 4; ++c)
+      acc[a][c] = 0.f;
+  }
+
+  fetch(0);
+  for (int k0 = 0; k0 < n_keys; k0 += KT) {
+    __syncthreads();            // the previous tile is no longer read (and Q is staged)
+    stash();
+    __syncthreads();
+    if (k0 + KT < n_keys)
+      fetch(k0 + KT);
+    if (row_thread) {
+      // ---- S = Q K^T for rows 4ty.., keys 4tx.. --------------------------------------
+      float sc[4][4];
+#pragma unroll
+      for (int a = 0; a < 4; ++a)
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          sc[a][b] = 0.f;
+      const float *qp = Qs + (4 * ty) * LDQ, *kp = Ks + (4 * tx) * LDK;
+#pragma unroll 4
+      for (int d = 0; d < D; d += 4) {
+        float4 q4[4], k4[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+          q4[a] = *reinterpret_cast<const float4 *>(qp + a * LDQ + d);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          k4[b] = *reinterpret_cast<const float4 *>(kp + b * LDK + d);
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+#pragma unroll
+          for (int b = 0; b < 4; ++b) {
+            sc[a][b] = fmaf(q4[a].x, k4[b].x, sc[a][b]);
+            sc[a][b] = fmaf(q4[a].y, k4[b].y, sc[a][b]);
+            sc[a][b] = fmaf(q4[a].z, k4[b].z, sc[a][b]);
+            sc[a][b] = fmaf(q4[a].w, k4[b].w, sc[a][b]);
+          }
+      }
+      // ---- running softmax per row: the 8 threads tx = 0..7 of a row hold its 32 scores ----
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        float tm = kSeed;
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int key = k0 + 4 * tx + b;
+          sc[a][b] = key <= qpos[a] ? sc[a][b] * scale : kSeed;
+          tm = fmaxf(tm, sc[a][b]);
+        }
+        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
+        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
+        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 4));
+        const float nm = fmaxf(mrow[a], tm);
+        const float alpha = expf(mrow[a] - nm);
+        float ps = 0.f;
+        float pw[4];
+#pragma unroll
+        for (int b = 0; b < 4; ++b) {
+          const int key = k0 + 4 * tx + b;
+          pw[b] = key <= qpos[a] ? expf(sc[a][b] - nm) : 0.f;
+          ps += pw[b];
+        }
+        ps += __shfl_xor_sync(0xffffffffu, ps, 1);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 2);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+        lrow[a] = fmaf(lrow[a], alpha, ps);
+        mrow[a] = nm;
+#pragma unroll
+        for (int c = 0; c < NCH * 4; ++c)
+          acc[a][c] *= alpha;
+        *reinterpret_cast<float4 *>(Ps + (4 * ty + a) * LDP + 4 * tx) = make_float4(pw[0], pw[1], pw[2], pw[3]);
+      }
+    }
+    // the 8 threads of a row sit in one warp (lanes 8k..8k+7): P of a row is complete after a warp sync
+    __syncwarp();
+    if (row_thread) {
+      // ---- O += P V for rows 4ty.., column chunks tx + 8i -----------------------------
+      const float *pp = Ps + (4 * ty) * LDP;
+#pragma unroll 2
+      for (int j = 0; j < KT; j += 4) {
+        float4 p4[4];
+#pragma unroll
+        for (int a = 0; a < 4; ++a)
+          p4[a] = *reinterpret_cast<const float4 *>(pp + a * LDP + j);
+#pragma unroll
+        for (int jj = 0; jj < 4; ++jj) {
+#pragma unroll
+          for (int i = 0; i < NCH; ++i) {
+            const float4 v4 = *reinterpret_cast<const float4 *>(Vs + (j + jj) * D + 4 * (tx + 8 * i));
+#pragma unroll
+            for (int a = 0; a < 4; ++a) {
+              const float pv = jj == 0 ? p4[a].x : jj == 1 ? p4[a].y : jj == 2 ? p4[a].z : p4[a].w;
+              acc[a][4 * i + 0] = fmaf(pv, v4.x, acc[a][4 * i + 0]);
+              acc[a][4 * i + 1] = fmaf(pv, v4.y, acc[a][4 * i + 1]);
+              acc[a][4 * i + 2] = fmaf(pv, v4.z, acc[a][4 * i + 2]);
+              acc[a][4 * i + 3] = fmaf(pv, v4.w, acc[a][4 * i + 3]);
+            }
+          }
+        }
+      }
+    }
+  }
+  if (row_thread) {
+#pragma unroll
+    for (int a = 0; a < 4; ++a) {
+      const int r = 4 * ty + a;
+      const int m = m0 + r / G;
+      if (m < M) {
+        float *orow = out + (int64_t)m * ldo + (int64_t)(hk * G + r % G) * D;
+#pragma unroll
+        for (int i = 0; i < NCH; ++i)
+          *reinterpret_cast<float4 *>(orow + 4 * (tx + 8 * i)) =
+              make_float4(__fdiv_rn(acc[a][4 * i], lrow[a]), __fdiv_rn(acc[a][4 * i + 1], lrow[a]),
+                          __fdiv_rn(acc[a][4 * i + 2], lrow[a]), __fdiv_rn(acc[a][4 * i + 3], lrow[a]));
+      }
+    }
+  }
+}
+
+template <int G, int D, bool PAGED>
+int launch_prefill_tiled(const float *qkv, int64_t ld, const float *kc, const float *vc, float *out, int64_t ldo,
+                         int kv_heads, int max_len, int pos0, int M, const int32_t *table, int page,
+                         cudaStream_t st) {
+  using T = PrefillTile<G, D>;
+  static bool configured[64] = {};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    B200_CUDA(cudaFuncSetAttribute(gqa_prefill_tiled_kernel<G, D, PAGED>,
+                                   cudaFuncAttributeMaxDynamicSharedMemorySize, (int)T::smem_bytes));
+    if (dev >= 0 && dev < 64)
+      configured[dev] = true;
+  }
+  dim3 grid((M + T::BQ - 1) / T::BQ, kv_heads);
+  gqa_prefill_tiled_kernel<G, D, PAGED><<<grid, 256, T::smem_bytes, st>>>(qkv, ld, kc, vc, out, ldo, max_len, pos0,
+                                                                         M, table, page, kv_heads);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 template <int G>
 int launch_prefill_attn(const float *qkv, int64_t ld, const float *kc, const float *vc, float *out, int64_t ldo,
                         int q_heads, int kv_heads, int D, int max_len, int pos0, int M, cudaStream_t st) {
@@ -350,23 +580,26 @@ int launch_paged_attn(const float *qkv, int64_t ld, const float *kp, const float
 }
 
 // The same scan for few rows with long histories (batched decode): the keys of a row
-// are cut into chunks of kPagedChunk positions, one CTA of 8 warps per (row, kv head,
-// chunk); a warp owns every 8th key of the chunk and keeps four K/V rows in flight.
+// are cut into chunks of `chunk` positions (paged_chunk(): an eighth of the longest
+// context, 32..256), one CTA of 8 warps per (row, kv head, chunk); a warp owns every 8th key of the chunk and keeps four K/V rows in flight.
 // Partials (m, l, acc[D]) per query head go to `part`; gqa_paged_combine_kernel folds
 // the chunks of a row in chunk order.
-constexpr int kPagedChunk = 256;
+__host__ __device__ inline int paged_chunk(int max_context) {
+  const int c = ((max_context + 7) / 8 + 31) / 32 * 32;
+  return c < 32 ? 32 : (c > 256 ? 256 : c);
+}
 template <int G, int VEC>
 __global__ void __launch_bounds__(256)
 gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *part,
                        int kv_heads, int page, const int32_t *row_seq, const int32_t *row_pos,
-                       const int32_t *block_table, int table_stride) {
+                       const int32_t *block_table, int table_stride, int chunk) {
   constexpr int D = VEC * 32, W = 8, U = 4;
   const int m = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int len = row_pos[m] + 1;
-  const int j0 = sp * kPagedChunk;
+  const int j0 = sp * chunk;
   if (j0 >= len)
     return;
-  const int j1 = min(len, j0 + kPagedChunk);
+  const int j1 = min(len, j0 + chunk);
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int32_t *table = block_table + (int64_t)row_seq[m] * table_stride;
   const float scale = rsqrtf((float)D);
@@ -478,9 +711,9 @@ gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const 
 template <int G, int D>
 __global__ void __launch_bounds__(128)
 gqa_paged_combine_kernel(const float *part, float *out, int64_t ldo, int kv_heads, int chunks,
-                         const int32_t *row_pos) {
+                         const int32_t *row_pos, int chunk) {
   const int m = blockIdx.x, hk = blockIdx.y;
-  const int n = (row_pos[m] + kPagedChunk) / kPagedChunk;   // chunks that hold keys of this row
+  const int n = (row_pos[m] + chunk) / chunk;   // chunks that hold keys of this row
   const float *pin = part + (((int64_t)m * kv_heads + hk) * chunks) * G * (D + 2);
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, d = idx - g * D;
@@ -501,19 +734,19 @@ gqa_paged_combine_kernel(const float *part, float *out, int64_t ldo, int kv_head
 template <int G>
 int launch_paged_split(const float *qkv, int64_t ld, const float *kp, const float *vp, float *out, int64_t ldo,
                        int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
-                       const int32_t *block_table, int table_stride, int M, float *part, int chunks,
+                       const int32_t *block_table, int table_stride, int M, float *part, int chunks, int chunk,
                        cudaStream_t st) {
   dim3 grid(M, kv_heads, chunks), cgrid(M, kv_heads);
   if (D == 128) {
     gqa_paged_split_kernel<G, 4><<<grid, 256, 0, st>>>(qkv, ld, kp, vp, part, kv_heads, page, row_seq, row_pos,
-                                                       block_table, table_stride);
+                                                       block_table, table_stride, chunk);
     B200_LAUNCH_CHECK();
-    gqa_paged_combine_kernel<G, 128><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos);
+    gqa_paged_combine_kernel<G, 128><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos, chunk);
   } else {
     gqa_paged_split_kernel<G, 2><<<grid, 256, 0, st>>>(qkv, ld, kp, vp, part, kv_heads, page, row_seq, row_pos,
-                                                       block_table, table_stride);
+                                                       block_table, table_stride, chunk);
     B200_LAUNCH_CHECK();
-    gqa_paged_combine_kernel<G, 64><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos);
+    gqa_paged_combine_kernel<G, 64><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos, chunk);
   }
   B200_LAUNCH_CHECK();
   return B200_OK;
@@ -572,7 +805,8 @@ int rope_kv_paged_launch(float *qkv, int64_t ld, float *k_pool, float *v_pool, c
 }
 
 int64_t gqa_paged_scratch_floats(int rows, int q_heads, int D, int max_context) {
-  const int chunks = (max_context + kPagedChunk - 1) / kPagedChunk;
+  const int chunk = paged_chunk(max_context);
+  const int chunks = (max_context + chunk - 1) / chunk;
   return (int64_t)rows * chunks * q_heads * (D + 2);
 }
 
@@ -585,20 +819,45 @@ int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const fl
   if (D != 64 && D != 128)
     return fail(B200_EINVAL, "gqa_paged: head_dim %d (64 or 128 supported)", D);
   constexpr int kPagedSplitRows = 256;
-  const bool split = scratch != nullptr && M <= kPagedSplitRows && max_context > kPagedChunk;
-  const int chunks = (max_context + kPagedChunk - 1) / kPagedChunk;
+  const int chunk = paged_chunk(max_context);
+  const bool split = scratch != nullptr && M <= kPagedSplitRows && max_context > chunk;
+  const int chunks = (max_context + chunk - 1) / chunk;
   switch (q_heads / kv_heads) {
 #define B200_G(G_)                                                                                          \
   case G_:                                                                                                  \
     if (split)                                                                                              \
       return launch_paged_split<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos, \
-                                    block_table, table_stride, M, scratch, chunks, st);                     \
+                                    block_table, table_stride, M, scratch, chunks, chunk, st);              \
     return launch_paged_attn<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos,    \
                                  block_table, table_stride, M, st);
     B200_G(1) B200_G(2) B200_G(3) B200_G(4) B200_G(6) B200_G(8)
 #undef B200_G
   default:
     return fail(B200_EINVAL, "gqa_paged: group size %d not built", q_heads / kv_heads);
+  }
+}
+
+// M rows of ONE sequence at positions pos0 .. pos0 + M - 1 (a prefill chunk) over the paged
+// pool: the attention kernel tiled over query rows.  seq_table: the sequence's row of the
+// block table (device).  Needs M >= 64 and 16-byte aligned rows; else returns B200_ESTATE
+// untouched and the caller uses gqa_paged_launch.
+int gqa_paged_prefill_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out,
+                             int64_t ldo, int q_heads, int kv_heads, int D, int page, const int32_t *seq_table,
+                             int pos0, int M, int max_context, cudaStream_t st) {
+  if ((D != 64 && D != 128) || M < 64 || (ld & 3) || (ldo & 3) || ((uintptr_t)qkv & 15) || ((uintptr_t)out & 15) ||
+      ((uintptr_t)k_pool & 15) || ((uintptr_t)v_pool & 15))
+    return B200_ESTATE;
+  switch (q_heads / kv_heads) {
+#define B200_G(G_)                                                                                                  \
+  case G_:                                                                                                          \
+    return D == 128 ? launch_prefill_tiled<G_, 128, true>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, max_context, \
+                                                          pos0, M, seq_table, page, st)                             \
+                    : launch_prefill_tiled<G_, 64, true>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, max_context,  \
+                                                         pos0, M, seq_table, page, st);
+    B200_G(1) B200_G(2) B200_G(3) B200_G(4) B200_G(6) B200_G(8)
+#undef B200_G
+  default:
+    return B200_ESTATE;
   }
 }
 
@@ -630,9 +889,17 @@ int gqa_prefill_launch(const float *qkv, int64_t ld, const float *kc, const floa
                        int q_heads, int kv_heads, int D, int max_len, int pos0, int M, cudaStream_t st) {
   if (D != 64 && D != 128)
     return fail(B200_EINVAL, "gqa_prefill: head_dim %d (64 or 128 supported)", D);
+  // many rows: the tiled kernel (needs 16-byte aligned rows); few rows: one CTA per (row, kv head)
+  const bool tiled = M >= 64 && (ld & 3) == 0 && (ldo & 3) == 0 && ((uintptr_t)qkv & 15) == 0 &&
+                     ((uintptr_t)out & 15) == 0 && ((uintptr_t)kc & 15) == 0 && ((uintptr_t)vc & 15) == 0;
   switch (q_heads / kv_heads) {
 #define B200_G(G_)                                                                                      \
   case G_:                                                                                              \
+    if (tiled)                                                                                          \
+      return D == 128 ? launch_prefill_tiled<G_, 128, false>(qkv, ld, kc, vc, out, ldo, kv_heads, max_len, pos0, \
+                                                             M, nullptr, 0, st)                                 \
+                      : launch_prefill_tiled<G_, 64, false>(qkv, ld, kc, vc, out, ldo, kv_heads, max_len, pos0, \
+                                                            M, nullptr, 0, st);                                 \
     return launch_prefill_attn<G_>(qkv, ld, kc, vc, out, ldo, q_heads, kv_heads, D, max_len, pos0, M, st);
     B200_G(1) B200_G(2) B200_G(3) B200_G(4) B200_G(6) B200_G(8)
 #undef B200_G

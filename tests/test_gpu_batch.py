@@ -69,6 +69,35 @@ def test_batched_decode_matches_per_sequence_checker(cfg, quant):
     s.close()
 
 
+@pytest.mark.parametrize("cfg,chunks", [(TINY_MEGA, (70, 66, 5)), (TINY_QWEN2, (70, 40)), (TINY_QWEN3, (93, 20))])
+def test_long_prefill_chunks_take_the_tiled_attention(cfg, chunks):
+    """Chunks of 64 rows and more of one sequence run the attention tiled over
+    query rows through the block table (first chunk from position 0, later ones on
+    top of the pages already filled, ragged last tiles); decode then continues."""
+    _, views = synthetic.make_f32_blob(cfg, 62)
+    kinds = {n: "w8" for n in ALL_LINEAR}
+    s = ModelSession(cfg)
+    s.load_tensors(views, quantize_to="w8")
+    bs = BatchSession(s, max_seqs=2, page_size=8, n_pages=40, max_context=cfg.max_len)
+    om = orc.OracleModel(cfg, views, kinds=kinds)
+    rng = np.random.default_rng(5)
+    q = bs.add()
+    for n in chunks:
+        prompt = rng.integers(0, cfg.vocab, n)
+        for t in prompt:
+            want = om.decode(int(t))
+        got, nxt = bs.prefill(q, prompt)
+        assert maxrel(got, want) < 1e-3 and nxt == greedy_sample(want)
+    tok = nxt
+    for _ in range(6):
+        logits, nx = bs.decode([q], [tok])
+        want = om.decode(int(tok))
+        assert maxrel(logits[0], want) < 1e-3 and int(nx[0]) == greedy_sample(want)
+        tok = int(nx[0])
+    bs.close()
+    s.close()
+
+
 def test_batch_limits_are_reported():
     cfg = TINY_QWEN2
     _, views = synthetic.make_f32_blob(cfg, 62)
