@@ -340,7 +340,10 @@ def run_batch_only(args):
     bs.prefill(scratch, rng.integers(0, cfg.vocab, 2048), want_logits=False)
     bs.remove(scratch)
     scratch = bs.add()
+    # profiler range (ncu --profile-from-start off): the timed prefill and, below, the last decode step
+    torch.cuda.profiler.start()
     bs.prefill(scratch, rng.integers(0, cfg.vocab, 2048), want_logits=False)
+    torch.cuda.profiler.stop()
     prefill_ms = bs.last_ms()
     bs.remove(scratch)
     seqs, toks = [], []
@@ -353,10 +356,13 @@ def run_batch_only(args):
         _, nxt = bs.decode(seqs, toks, want_logits=False)
         toks = [int(t) for t in nxt]
     ms = []
-    for _ in range(args.steps):
+    for i in range(args.steps):
+        if i == args.steps - 1:
+            torch.cuda.profiler.start()
         _, nxt = bs.decode(seqs, toks, want_logits=False)
         ms.append(bs.last_ms())
         toks = [int(t) for t in nxt]
+    torch.cuda.profiler.stop()
     step_ms = float(np.mean(ms))
     flops = 2.0 * (1310195712 + 233373696)       # per token: the linear layers and the lm_head
     print(json.dumps({"batched_decode": {"sequences": B, "lengths": "uniform [128, 2048], seeded", "page_size": page,

@@ -438,49 +438,56 @@ weights_to_bf16_kernel(const uint8_t *w, int64_t units, uint4 *out) {
 }
 
 // Split-K: add the splits of every output tile in split order, then the epilogue.
+// grid (tiles, BM / 8): a CTA of 256 threads takes 8 rows of a tile, a thread 4 columns.
 __global__ void __launch_bounds__(256)
 gemm_w8_combine_kernel(const GemmParams p, int tiles_x) {
   const int tile = blockIdx.x;
   const int m0 = (tile / tiles_x) * BM, n0 = (tile % tiles_x) * BN;
-  const float *base = p.partial + (int64_t)tile * p.splits * BM * BN;
-  for (int idx = threadIdx.x * 2; idx < BM * BN; idx += blockDim.x * 2) {
-    const int r = idx / BN, c = idx % BN;      // c even
-    const int m = m0 + r, n = n0 + c;
-    if (m >= p.M || n >= p.N)
-      continue;
-    float a0 = 0.f, a1 = 0.f;
-    for (int z = 0; z < p.splits; ++z) {
-      const float2 v = *reinterpret_cast<const float2 *>(base + (int64_t)z * BM * BN + idx);
-      a0 = __fadd_rn(a0, v.x);
-      a1 = __fadd_rn(a1, v.y);
-    }
-    if (p.silu_pairs) {
-      if (n + 1 < p.N)
-        store_pair(p, m, n, a0, a1);
-    } else {
-      store_plain(p, m, n, a0);
-      if (n + 1 < p.N)
-        store_plain(p, m, n + 1, a1);
-    }
+  const int r = blockIdx.y * 8 + (threadIdx.x >> 5), c = (threadIdx.x & 31) * 4;
+  const int m = m0 + r, n = n0 + c;
+  if (m >= p.M || n >= p.N)
+    return;
+  const float *base = p.partial + (int64_t)tile * p.splits * BM * BN + r * BN + c;
+  float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+  for (int z = 0; z < p.splits; ++z) {
+    const float4 v = *reinterpret_cast<const float4 *>(base + (int64_t)z * BM * BN);
+    a.x = __fadd_rn(a.x, v.x);
+    a.y = __fadd_rn(a.y, v.y);
+    a.z = __fadd_rn(a.z, v.z);
+    a.w = __fadd_rn(a.w, v.w);
+  }
+  if (p.silu_pairs) {
+    if (n + 1 < p.N)
+      store_pair(p, m, n, a.x, a.y);
+    if (n + 3 < p.N)
+      store_pair(p, m, n + 2, a.z, a.w);
+  } else {
+    store_plain(p, m, n, a.x);
+    if (n + 1 < p.N) store_plain(p, m, n + 1, a.y);
+    if (n + 2 < p.N) store_plain(p, m, n + 2, a.z);
+    if (n + 3 < p.N) store_plain(p, m, n + 3, a.w);
   }
 }
 
 // A[M,K] f32 -> hi/lo bf16 [Mpad, Kp] in the k order of the packed weight rows.
 // Optional RMSNorm of every row first (y = w * (x * r), subgraph0_decode_simplify.mlir:60-72).
-__global__ void split_activations_kernel(const float *A, int64_t lda, int M, int K, int Kp,
-                                         const float *norm_w, float eps,
-                                         __nv_bfloat16 *hi, __nv_bfloat16 *lo) {
+// A thread converts four consecutive k: they share a 16-byte unit of the packed row, so
+// they land on four consecutive bf16.  Rows beyond M are written as zeros.
+__global__ void __launch_bounds__(256)
+split_activations_kernel(const float *A, int64_t lda, int M, int K, int Kp, const float *norm_w, float eps,
+                         __nv_bfloat16 *hi, __nv_bfloat16 *lo) {
   const int m = blockIdx.x;
   __shared__ float s_red[32];
   float r = 1.f;
   const bool live = m < M;
-  if (norm_w != nullptr) {
+  const float *arow = A + (int64_t)m * lda;
+  const bool vec = (K & 3) == 0 && (lda & 3) == 0 && ((uintptr_t)A & 15) == 0;
+  if (norm_w != nullptr && live) {
     float ss = 0.f;
-    if (live)
-      for (int k = threadIdx.x; k < K; k += blockDim.x) {
-        const float x = A[(int64_t)m * lda + k];
-        ss += x * x;
-      }
+    for (int k = threadIdx.x; k < K; k += blockDim.x) {
+      const float x = arow[k];
+      ss += x * x;
+    }
     ss = warp_sum(ss);
     if ((threadIdx.x & 31) == 0)
       s_red[threadIdx.x >> 5] = ss;
@@ -490,18 +497,47 @@ __global__ void split_activations_kernel(const float *A, int64_t lda, int M, int
       t += s_red[w];
     r = rsqrtf(__fadd_rn(__fmul_rn(t, 1.0f / (float)K), eps));
   }
-  for (int k = threadIdx.x; k < Kp; k += blockDim.x) {
-    float a = 0.f;
+  uint2 *hrow = reinterpret_cast<uint2 *>(hi + (int64_t)m * Kp), *lrow = reinterpret_cast<uint2 *>(lo + (int64_t)m * Kp);
+  for (int k = threadIdx.x * 4; k < Kp; k += blockDim.x * 4) {
+    float a[4] = {0.f, 0.f, 0.f, 0.f};
     if (live && k < K) {
-      a = A[(int64_t)m * lda + k];
-      if (norm_w != nullptr)
-        a = __fmul_rn(norm_w[k], __fmul_rn(a, r));
+      if (vec) {
+        const float4 v = *reinterpret_cast<const float4 *>(arow + k);
+        a[0] = v.x; a[1] = v.y; a[2] = v.z; a[3] = v.w;
+      } else {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (k + e < K)
+            a[e] = arow[k + e];
+      }
+      if (norm_w != nullptr) {
+#pragma unroll
+        for (int e = 0; e < 4; ++e)
+          if (k + e < K)
+            a[e] = __fmul_rn(norm_w[k + e], __fmul_rn(a[e], r));
+      }
     }
-    const __nv_bfloat16 h = __float2bfloat16_rn(a);
-    const __nv_bfloat16 l = __float2bfloat16_rn(a - __bfloat162float(h));
-    const int64_t pos = k < K ? packed_offset(B200_W_I8, K, k, nullptr) : k;
-    hi[(int64_t)m * Kp + pos] = h;
-    lo[(int64_t)m * Kp + pos] = l;
+    __nv_bfloat16 h[4], l[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      h[e] = __float2bfloat16_rn(a[e]);
+      l[e] = __float2bfloat16_rn(a[e] - __bfloat162float(h[e]));
+    }
+    // position of k (a multiple of 4) in the packed row: a full block of 512 elements by shifts
+    int64_t pos;
+    if ((k | 511) < (K & ~511)) {
+      const int kk = k & 511;
+      pos = (k & ~511) + ((kk & 127) >> 2) * 16 + (kk >> 7) * 4;
+    } else {
+      pos = k < K ? packed_offset(B200_W_I8, K, k, nullptr) : k;
+    }
+    uint2 hv, lv;
+    hv.x = (uint32_t)__bfloat16_as_ushort(h[0]) | ((uint32_t)__bfloat16_as_ushort(h[1]) << 16);
+    hv.y = (uint32_t)__bfloat16_as_ushort(h[2]) | ((uint32_t)__bfloat16_as_ushort(h[3]) << 16);
+    lv.x = (uint32_t)__bfloat16_as_ushort(l[0]) | ((uint32_t)__bfloat16_as_ushort(l[1]) << 16);
+    lv.y = (uint32_t)__bfloat16_as_ushort(l[2]) | ((uint32_t)__bfloat16_as_ushort(l[3]) << 16);
+    hrow[pos >> 2] = hv;
+    lrow[pos >> 2] = lv;
   }
 }
 
@@ -583,7 +619,7 @@ static int gemm_launch(const void *wbase, __nv_bfloat16 *hi, __nv_bfloat16 *lo, 
   gemm_w8_tc_kernel<BKT, PRE><<<grid, PRE ? kThreadsPre : kThreadsConv, smem, st>>>(map_hi, map_lo, map_w, p);
   B200_LAUNCH_CHECK();
   if (p.splits > 1) {
-    gemm_w8_combine_kernel<<<grid.x * grid.y, 256, 0, st>>>(p, (int)grid.x);
+    gemm_w8_combine_kernel<<<dim3(grid.x * grid.y, BM / 8), 256, 0, st>>>(p, (int)grid.x);
     B200_LAUNCH_CHECK();
   }
   return B200_OK;

@@ -174,20 +174,21 @@ gqa_prefill_kernel(const float *qkv, int64_t ld, const float *kc, const float *v
 
 // Causal attention tiled over query rows (flash style, f32 on the CUDA cores).
 // A CTA takes BQ consecutive query rows of one kv head: R = BQ * G query vectors
-// (row r = query row r / G, head hk * G + r % G) against tiles of 32 keys staged in
+// (row r = query row r / G, head hk * G + r % G) against tiles of 64 keys staged in
 // shared memory, so a K/V row is read once per BQ query rows instead of once per
-// row.  256 threads as 32 x 8: thread (ty, tx) owns query vectors 4ty..4ty+3; for
-// the scores it owns keys 4tx..4tx+3 of the tile, for the output the float4 column
-// chunks tx + 8i.  Per key tile: S = Q K^T (register tile 4 x 4 over D), running
-// max / sum per row across the 8 threads of a row (tosa.py:14245-14252, one update
+// row.  512 threads as 32 x 16: thread (ty, tx) owns query vectors 4ty..4ty+3; for
+// the scores it owns keys tx, tx + 16, tx + 32, tx + 48 of the tile (rows of the K
+// tile 16 apart: no bank conflicts), for the output the float4 column
+// chunks tx + 16i.  Per key tile: S = Q K^T (register tile 4 x 4 over D), running
+// max / sum per row across the 16 threads of a row (tosa.py:14245-14252, one update
 // per tile instead of per key), P to shared memory, O += P V (register tile
-// 4 x D/8).  The next K/V tile is fetched into registers while the current one
+// 4 x D/16).  The next K/V tile is fetched into registers while the current one
 // is used.
 template <int G, int D>
 struct PrefillTile {
   static constexpr int BQ = G >= 6 ? 16 : (G >= 3 ? 32 : 64);
   static constexpr int R = BQ * G;           // <= 128
-  static constexpr int KT = 32;              // keys per tile
+  static constexpr int KT = 64;              // keys per tile
   static constexpr int LDQ = D + 4, LDK = D + 4, LDP = KT + 4;
   static constexpr size_t smem_bytes = ((size_t)R * LDQ + (size_t)KT * LDK + (size_t)KT * D + (size_t)R * LDP) * 4;
 };
@@ -195,17 +196,17 @@ struct PrefillTile {
 // PAGED: kc / vc are page pools [n_pages][kv_heads][page][D] and `table` lists the
 // pages of the one sequence all M rows belong to (positions pos0, pos0 + 1, ..).
 template <int G, int D, bool PAGED>
-__global__ void __launch_bounds__(256, 1)
+__global__ void __launch_bounds__(512, 1)
 gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const float *vc, float *out, int64_t ldo,
                          int max_len, int pos0, int M, const int32_t *table, int page, int kv_heads) {
   using T = PrefillTile<G, D>;
-  constexpr int R = T::R, KT = T::KT, LDQ = T::LDQ, LDK = T::LDK, LDP = T::LDP, NCH = D / 32;
+  constexpr int R = T::R, KT = T::KT, LDQ = T::LDQ, LDK = T::LDK, LDP = T::LDP, NCH = D / 64;
   extern __shared__ __align__(16) float sm[];
   float *Qs = sm, *Ks = Qs + R * LDQ, *Vs = Ks + KT * LDK, *Ps = Vs + KT * D;
   // heavy tiles (late rows, long histories) first
   const int qt = gridDim.x - 1 - blockIdx.x, hk = blockIdx.y;
   const int m0 = qt * T::BQ;
-  const int tid = threadIdx.x, tx = tid & 7, ty = tid >> 3;
+  const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const bool row_thread = 4 * ty < R;
   const float scale = rsqrtf((float)D);
   // keys this tile needs: up to the position of its last live row
@@ -215,7 +216,7 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
   const float *vbase = PAGED ? vc : vc + (int64_t)hk * max_len * D;
 
   // ---- stage Q: row r = (query row r / G, head r % G), G heads of a row are contiguous ----
-  for (int idx = tid; idx < R * (D / 4); idx += 256) {
+  for (int idx = tid; idx < R * (D / 4); idx += 512) {
     const int r = idx / (D / 4), c = idx - r * (D / 4);
     const int m = m0 + r / G;
     float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
@@ -223,13 +224,13 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
       v = *reinterpret_cast<const float4 *>(qkv + (int64_t)m * ld + (int64_t)(hk * G + r % G) * D + 4 * c);
     *reinterpret_cast<float4 *>(Qs + r * LDQ + 4 * c) = v;
   }
-  // per-thread K/V fetch slots: KT * D / 4 float4 per tile over 256 threads
-  constexpr int NF = KT * (D / 4) / 256;   // 4 (D = 128) or 2 (D = 64)
+  // per-thread K/V fetch slots: KT * D / 4 float4 per tile over 512 threads
+  constexpr int NF = KT * (D / 4) / 512;   // 4 (D = 128) or 2 (D = 64)
   float4 kf[NF], vf[NF];
   auto fetch = [&](int k0) {
 #pragma unroll
     for (int i = 0; i < NF; ++i) {
-      const int idx = tid + 256 * i;
+      const int idx = tid + 512 * i;
       const int j = idx / (D / 4), c = idx - j * (D / 4);
       if (k0 + j < n_keys) {
         const int key = k0 + j;
@@ -246,7 +247,7 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
   auto stash = [&]() {
 #pragma unroll
     for (int i = 0; i < NF; ++i) {
-      const int idx = tid + 256 * i;
+      const int idx = tid + 512 * i;
       const int j = idx / (D / 4), c = idx - j * (D / 4);
       *reinterpret_cast<float4 *>(Ks + j * LDK + 4 * c) = kf[i];
       *reinterpret_cast<float4 *>(Vs + j * D + 4 * c) = vf[i];
@@ -274,14 +275,14 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
     if (k0 + KT < n_keys)
       fetch(k0 + KT);
     if (row_thread) {
-      // ---- S = Q K^T for rows 4ty.., keys 4tx.. --------------------------------------
+      // ---- S = Q K^T for rows 4ty.., keys tx + 16b ------------------------------------
       float sc[4][4];
 #pragma unroll
       for (int a = 0; a < 4; ++a)
 #pragma unroll
         for (int b = 0; b < 4; ++b)
           sc[a][b] = 0.f;
-      const float *qp = Qs + (4 * ty) * LDQ, *kp = Ks + (4 * tx) * LDK;
+      const float *qp = Qs + (4 * ty) * LDQ, *kp = Ks + tx * LDK;
 #pragma unroll 4
       for (int d = 0; d < D; d += 4) {
         float4 q4[4], k4[4];
@@ -290,7 +291,7 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
           q4[a] = *reinterpret_cast<const float4 *>(qp + a * LDQ + d);
 #pragma unroll
         for (int b = 0; b < 4; ++b)
-          k4[b] = *reinterpret_cast<const float4 *>(kp + b * LDK + d);
+          k4[b] = *reinterpret_cast<const float4 *>(kp + b * 16 * LDK + d);
 #pragma unroll
         for (int a = 0; a < 4; ++a)
 #pragma unroll
@@ -301,44 +302,48 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
             sc[a][b] = fmaf(q4[a].w, k4[b].w, sc[a][b]);
           }
       }
-      // ---- running softmax per row: the 8 threads tx = 0..7 of a row hold its 32 scores ----
+      // ---- running softmax per row: the 16 threads tx = 0..15 of a row hold its 64 scores ----
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         float tm = kSeed;
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int key = k0 + 4 * tx + b;
+          const int key = k0 + 16 * b + tx;
           sc[a][b] = key <= qpos[a] ? sc[a][b] * scale : kSeed;
           tm = fmaxf(tm, sc[a][b]);
         }
         tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 1));
         tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 2));
         tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 4));
+        tm = fmaxf(tm, __shfl_xor_sync(0xffffffffu, tm, 8));
         const float nm = fmaxf(mrow[a], tm);
         const float alpha = expf(mrow[a] - nm);
         float ps = 0.f;
         float pw[4];
 #pragma unroll
         for (int b = 0; b < 4; ++b) {
-          const int key = k0 + 4 * tx + b;
+          const int key = k0 + 16 * b + tx;
           pw[b] = key <= qpos[a] ? expf(sc[a][b] - nm) : 0.f;
           ps += pw[b];
         }
         ps += __shfl_xor_sync(0xffffffffu, ps, 1);
         ps += __shfl_xor_sync(0xffffffffu, ps, 2);
         ps += __shfl_xor_sync(0xffffffffu, ps, 4);
+        ps += __shfl_xor_sync(0xffffffffu, ps, 8);
         lrow[a] = fmaf(lrow[a], alpha, ps);
         mrow[a] = nm;
 #pragma unroll
         for (int c = 0; c < NCH * 4; ++c)
           acc[a][c] *= alpha;
-        *reinterpret_cast<float4 *>(Ps + (4 * ty + a) * LDP + 4 * tx) = make_float4(pw[0], pw[1], pw[2], pw[3]);
+#pragma unroll
+        for (int b = 0; b < 4; ++b)
+          Ps[(4 * ty + a) * LDP + 16 * b + tx] = pw[b];
       }
     }
-    // the 8 threads of a row sit in one warp (lanes 8k..8k+7): P of a row is complete after a warp sync
+    // the 16 threads of a row sit in one warp: P of a row is complete after a warp sync
     __syncwarp();
     if (row_thread) {
-      // ---- O += P V for rows 4ty.., column chunks tx + 8i -----------------------------
+      // ---- O += P V for rows 4ty.., column chunks tx + 16i ----------------------------
       const float *pp = Ps + (4 * ty) * LDP;
 #pragma unroll 2
       for (int j = 0; j < KT; j += 4) {
@@ -350,7 +355,7 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
         for (int jj = 0; jj < 4; ++jj) {
 #pragma unroll
           for (int i = 0; i < NCH; ++i) {
-            const float4 v4 = *reinterpret_cast<const float4 *>(Vs + (j + jj) * D + 4 * (tx + 8 * i));
+            const float4 v4 = *reinterpret_cast<const float4 *>(Vs + (j + jj) * D + 4 * (tx + 16 * i));
 #pragma unroll
             for (int a = 0; a < 4; ++a) {
               const float pv = jj == 0 ? p4[a].x : jj == 1 ? p4[a].y : jj == 2 ? p4[a].z : p4[a].w;
@@ -373,7 +378,7 @@ gqa_prefill_tiled_kernel(const float *qkv, int64_t ld, const float *kc, const fl
         float *orow = out + (int64_t)m * ldo + (int64_t)(hk * G + r % G) * D;
 #pragma unroll
         for (int i = 0; i < NCH; ++i)
-          *reinterpret_cast<float4 *>(orow + 4 * (tx + 8 * i)) =
+          *reinterpret_cast<float4 *>(orow + 4 * (tx + 16 * i)) =
               make_float4(__fdiv_rn(acc[a][4 * i], lrow[a]), __fdiv_rn(acc[a][4 * i + 1], lrow[a]),
                           __fdiv_rn(acc[a][4 * i + 2], lrow[a]), __fdiv_rn(acc[a][4 * i + 3], lrow[a]));
       }
@@ -396,7 +401,7 @@ int launch_prefill_tiled(const float *qkv, int64_t ld, const float *kc, const fl
       configured[dev] = true;
   }
   dim3 grid((M + T::BQ - 1) / T::BQ, kv_heads);
-  gqa_prefill_tiled_kernel<G, D, PAGED><<<grid, 256, T::smem_bytes, st>>>(qkv, ld, kc, vc, out, ldo, max_len, pos0,
+  gqa_prefill_tiled_kernel<G, D, PAGED><<<grid, 512, T::smem_bytes, st>>>(qkv, ld, kc, vc, out, ldo, max_len, pos0,
                                                                          M, table, page, kv_heads);
   B200_LAUNCH_CHECK();
   return B200_OK;
