@@ -33,7 +33,6 @@
 
 #include <cuda.h>
 
-#include <cstdlib>
 #include <mutex>
 
 namespace b200 {
@@ -42,10 +41,9 @@ namespace {
 
 constexpr int BM = 128, BN = 128;              // output tile of one CTA
 constexpr int kMaxStages = 8;
-constexpr int kTmemCols = 128;                 // f32 accumulator 128 lanes x 128 columns
-// warp 0 loader, warp 1 mma, then the conversion + epilogue warps: 8 when the CTA converts
-// the int8 tile itself, 4 (epilogue only) when the weights arrive as bf16
-constexpr int kThreadsConv = 320, kThreadsPre = 192;
+// warp 0 loader, warp 1 mma, then 8 conversion + epilogue warps (epilogue only when the
+// weights arrive as bf16)
+constexpr int kThreadsConv = 320, kThreadsPre = 320;
 constexpr int kMaxPartialTiles = 320;          // split-K: 128 x 128 f32 partial tiles in the workspace
 constexpr uint32_t kSpin = 1u << 26;
 constexpr unsigned long long kWaitNs = 2000000000ull;
@@ -53,10 +51,10 @@ constexpr unsigned long long kWaitNs = 2000000000ull;
 // Shared-memory stage for a k block of BKT elements (64: 128-byte swizzle rows, 32: 64-byte rows).
 // PRE: the weight tile is loaded as bf16 (converted by a pass over the weights before the
 // GEMM); else the raw int8 tile is loaded and converted by the CTA.
-template <int BKT, bool PRE> struct Tile {
+template <int BKT, bool PRE, int BNT = BN> struct Tile {
   static constexpr uint32_t A_BYTES = BM * BKT * 2;              // one bf16 term of the activations
-  static constexpr uint32_t WRAW_BYTES = PRE ? 0 : BN * BKT;     // int8 weights as stored
-  static constexpr uint32_t WB_BYTES = BN * BKT * 2;             // the weight tile as bf16
+  static constexpr uint32_t WRAW_BYTES = PRE ? 0 : BNT * BKT;    // int8 weights as stored
+  static constexpr uint32_t WB_BYTES = BNT * BKT * 2;            // the weight tile as bf16
   static constexpr uint32_t STAGE_BYTES = 2 * A_BYTES + WRAW_BYTES + WB_BYTES;
   static constexpr uint32_t ROW_BYTES = BKT * 2;
 };
@@ -131,13 +129,17 @@ template <int BKT> __device__ __forceinline__ uint64_t smem_desc(uint32_t addr) 
   return d;
 }
 // kind::f16 instruction descriptor: D = f32, A = B = bf16, both K-major, N = 128, M = 128.
-constexpr uint32_t kIdesc = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+template <int BNT> struct Idesc {
+  static constexpr uint32_t value =
+      (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+};
 
+template <int BNT>
 __device__ __forceinline__ void mma_bf16(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
   asm volatile(
       "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
       " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
-      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdesc), "r"(accumulate)
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(Idesc<BNT>::value), "r"(accumulate)
       : "memory");
 }
 __device__ __forceinline__ void tc_commit(uint64_t *bar) {
@@ -157,7 +159,6 @@ struct GemmParams {
   int splits;                  // CTAs along K per output tile (gridDim.z); > 1: raw sums go to `partial`
   float *partial;              // [tiles][splits][128][128] f32
   int *error;
-  int debug;                   // experiment: 1 = no MMA issue, 2 = no TMA loads
 };
 
 // scale / bias / residual, or the SiLU-gate of a (gate, up) column pair
@@ -182,19 +183,22 @@ __device__ __forceinline__ void store_pair(const GemmParams &p, int m, int n, fl
   p.C[(int64_t)m * p.ldc + (n >> 1)] = __fmul_rn(__fmul_rn(g, sg), u);
 }
 
-template <int BKT, bool PRE>
+// BNT: weight rows (output columns) per CTA: 128, or 256 on the dense path, where one
+// activation tile then feeds twice the tensor-core work per byte brought in from L2.
+template <int BKT, bool PRE, int BNT>
 __global__ void __launch_bounds__(PRE ? kThreadsPre : kThreadsConv, BKT == 64 ? 1 : 2)
 gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_constant__ CUtensorMap map_lo,
                   const __grid_constant__ CUtensorMap map_w, const GemmParams p) {
-  using T = Tile<BKT, PRE>;
-  constexpr int kEpiWarps = PRE ? 4 : 8;
+  using T = Tile<BKT, PRE, BNT>;
+  static_assert(PRE || BNT == BN, "the converting kernel takes 128 weight rows per CTA");
+  constexpr int kEpiWarps = 8;
   extern __shared__ __align__(1024) uint8_t smem[];
   // 1024-byte alignment of every swizzled tile
   uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
   const int stages = p.stages;
   Bars &bars = *reinterpret_cast<Bars *>(tiles + stages * T::STAGE_BYTES);
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BNT;
   // this CTA's share of the k blocks (split-K: blockIdx.z)
   const int nkb_all = p.K / BKT;
   const int kb0 = (int)((int64_t)nkb_all * blockIdx.z / p.splits);
@@ -212,7 +216,7 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) {   // tensor memory: one warp allocates, the same warp frees
-    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)), "n"(kTmemCols) : "memory");
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)), "n"(BNT) : "memory");
     asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -229,10 +233,6 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
           break;
         uint8_t *st = tiles + s * T::STAGE_BYTES;
         const int kx = (kb0 + i) * BKT;
-        if (p.debug & 2) {
-          mbar_arrive(&bars.full[s]);
-          continue;
-        }
         mbar_expect_tx(&bars.full[s], 2 * T::A_BYTES + (PRE ? T::WB_BYTES : T::WRAW_BYTES));
         tma_load_2d(st, &map_hi, kx, m0, &bars.full[s]);
         tma_load_2d(st + T::A_BYTES, &map_lo, kx, m0, &bars.full[s]);
@@ -251,12 +251,11 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         const uint32_t a_hi = smem_u32(tiles + s * T::STAGE_BYTES), a_lo = a_hi + T::A_BYTES,
                        wb = a_hi + 2 * T::A_BYTES + T::WRAW_BYTES;
-        if (!(p.debug & 1))
 #pragma unroll
         for (int k = 0; k < BKT / 16; ++k) {   // 16 bf16 = 32 bytes along the swizzled row
           const uint64_t db = smem_desc<BKT>(wb + k * 32);
-          mma_bf16(tmem, smem_desc<BKT>(a_hi + k * 32), db, (i | k) != 0);
-          mma_bf16(tmem, smem_desc<BKT>(a_lo + k * 32), db, 1u);
+          mma_bf16<BNT>(tmem, smem_desc<BKT>(a_hi + k * 32), db, (i | k) != 0);
+          mma_bf16<BNT>(tmem, smem_desc<BKT>(a_lo + k * 32), db, 1u);
         }
         tc_commit(&bars.empty[s]);   // arrives when the MMAs above have read the stage
       }
@@ -307,25 +306,30 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       }
     }
     // ---- epilogue ---------------------------------------------------------------------
-    // A thread owns one accumulator row (its lane of tensor memory).  Scaled values go to a
-    // padded tile in shared memory (the ring is idle by now), then the warps write whole
-    // rows: 128-byte coalesced stores instead of one 4-byte store per thread and column.
+    // A thread owns one accumulator row (its lane of tensor memory) and half of its columns.
+    // Scaled values go to a padded tile in shared memory (the ring is idle by now; row stride
+    // 132 floats keeps 16-byte stores of neighbouring rows on different banks), then the warps
+    // write whole rows with 16-byte stores.
     const bool ok = alive && mbar_wait(&bars.accum, 0, ab, p.error, 705);
-    constexpr int LDS = BN + 1;                       // row stride of the staging tile, in floats
+    constexpr int LDS = BN + 4;                       // row stride of the staging tile, in floats
     float *ep = reinterpret_cast<float *>(tiles);     // [BM][LDS]: 66 KB <= the ring
     const int width = p.splits > 1 ? BN : (p.silu_pairs ? BN / 2 : BN);
-    if (ok) {
+#pragma unroll 1
+    for (int h = 0; h < BNT / BN; ++h) {   // 128 columns of the accumulator at a time
+    const int n0h = n0 + h * BN;
+    if (h > 0)   // the staging tile is free again once the previous half has been stored
+      asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
+    if (ok && n0h < p.N) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // a warp reads the 32 lanes of tensor memory that match its rank within its warpgroup;
-      // with eight epilogue warps two of them share a lane quarter and take half the columns each
+      // the two warps that share a lane quarter take half the columns each
       const int quad = warp & 3;
       const int row = quad * 32 + lane;
-      const int cb0 = kEpiWarps == 8 ? ((warp - 2) >> 2) * (BN / 2) : 0;
-      const int cb1 = kEpiWarps == 8 ? cb0 + BN / 2 : BN;
+      const int cb0 = ((warp - 2) >> 2) * (BN / 2), cb1 = cb0 + BN / 2;
 #pragma unroll 1
       for (int cb = cb0; cb < cb1; cb += 32) {
         uint32_t v[32];
-        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)cb;
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)(h * BN + cb);
         asm volatile(
             "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
             "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
@@ -341,36 +345,49 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
         if (p.splits > 1) {
           // split-K: raw sums of this CTA's k range; gemm_w8_combine_kernel adds the splits
 #pragma unroll
-          for (int j = 0; j < 32; ++j)
-            erow[cb + j] = __uint_as_float(v[j]);
+          for (int j = 0; j < 32; j += 4)
+            *reinterpret_cast<float4 *>(erow + cb + j) =
+                make_float4(__uint_as_float(v[j]), __uint_as_float(v[j + 1]), __uint_as_float(v[j + 2]),
+                            __uint_as_float(v[j + 3]));
         } else if (p.silu_pairs) {
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) {
-            const int n = min(n0 + cb + j, p.N - 2) + p.n_off;   // columns beyond N are not stored
-            float g = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
-            float u = __fmul_rn(__uint_as_float(v[j + 1]), __ldg(p.scale + n + 1));
-            if (p.bias) {
-              g = __fadd_rn(g, __ldg(p.bias + n));
-              u = __fadd_rn(u, __ldg(p.bias + n + 1));
+          for (int j = 0; j < 32; j += 8) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int n = min(n0h + cb + j + 2 * e, p.N - 2) + p.n_off;   // columns beyond N are not stored
+              const float2 sc2 = __ldg(reinterpret_cast<const float2 *>(p.scale + n));
+              float g = __fmul_rn(__uint_as_float(v[j + 2 * e]), sc2.x);
+              float u = __fmul_rn(__uint_as_float(v[j + 2 * e + 1]), sc2.y);
+              if (p.bias) {
+                g = __fadd_rn(g, __ldg(p.bias + n));
+                u = __fadd_rn(u, __ldg(p.bias + n + 1));
+              }
+              const float sg = 1.0f / (1.0f + expf(-g));   // subgraph0_decode_simplify.mlir:226-231
+              o[e] = __fmul_rn(__fmul_rn(g, sg), u);
             }
-            const float sg = 1.0f / (1.0f + expf(-g));   // subgraph0_decode_simplify.mlir:226-231
-            erow[(cb + j) >> 1] = __fmul_rn(__fmul_rn(g, sg), u);
+            *reinterpret_cast<float4 *>(erow + ((cb + j) >> 1)) = make_float4(o[0], o[1], o[2], o[3]);
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const int n = min(n0 + cb + j, p.N - 1) + p.n_off;
-            float y = __fmul_rn(__uint_as_float(v[j]), __ldg(p.scale + n));
-            if (p.bias)
-              y = __fadd_rn(y, __ldg(p.bias + n));
-            erow[cb + j] = y;
+          for (int j = 0; j < 32; j += 4) {
+            float o[4];
+#pragma unroll
+            for (int e = 0; e < 4; ++e) {
+              const int n = min(n0h + cb + j + e, p.N - 1) + p.n_off;
+              float y = __fmul_rn(__uint_as_float(v[j + e]), __ldg(p.scale + n));
+              if (p.bias)
+                y = __fadd_rn(y, __ldg(p.bias + n));
+              o[e] = y;
+            }
+            *reinterpret_cast<float4 *>(erow + cb + j) = make_float4(o[0], o[1], o[2], o[3]);
           }
         }
       }
     }
     // all epilogue warps, whether they hold data or gave up: named barrier 1
     asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
-    if (ok) {
+    if (ok && n0h < p.N) {
       const int ew = warp - 2;
       float *dst;
       int64_t ldd;
@@ -381,27 +398,49 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
         ldd = BN;
         cols = BN;
       } else if (p.silu_pairs) {
-        dst = p.C + (int64_t)m0 * p.ldc + ((n0 + p.n_off) >> 1);
+        dst = p.C + (int64_t)m0 * p.ldc + ((n0h + p.n_off) >> 1);
         ldd = p.ldc;
-        cols = min(BN, p.N - n0) >> 1;
+        cols = min(BN, p.N - n0h) >> 1;
       } else {
-        dst = p.C + (int64_t)m0 * p.ldc + n0 + p.n_off;
+        dst = p.C + (int64_t)m0 * p.ldc + n0h + p.n_off;
         ldd = p.ldc;
-        cols = min(BN, p.N - n0);
+        cols = min(BN, p.N - n0h);
       }
-      const float *res = (p.residual && p.splits == 1 && !p.silu_pairs) ? p.residual + (int64_t)m0 * p.ldr + n0 + p.n_off : nullptr;
+      const float *res = (p.residual && p.splits == 1 && !p.silu_pairs) ? p.residual + (int64_t)m0 * p.ldr + n0h + p.n_off : nullptr;
       const int rows = p.splits > 1 ? BM : min(BM, p.M - m0);
-      for (int r = ew; r < rows; r += kEpiWarps) {
-        for (int c = lane; c < width; c += 32) {
+      // 16-byte stores when the destination rows allow it
+      const bool v4 = (ldd & 3) == 0 && ((uintptr_t)dst & 15) == 0 && (cols & 3) == 0 &&
+                      (!res || ((p.ldr & 3) == 0 && ((uintptr_t)res & 15) == 0));
+      if (v4) {
+        const int per_row = width / 4;                 // float4 per row: 32 or 16
+        for (int idx = ew * 32 + lane; idx < rows * per_row; idx += kEpiWarps * 32) {
+          const int r = idx / per_row, c = (idx - r * per_row) * 4;
           if (c < cols) {
-            float y = ep[r * LDS + c];
-            if (res)
-              y = __fadd_rn(res[(int64_t)r * p.ldr + c], y);
-            dst[(int64_t)r * ldd + c] = y;
+            float4 y = *reinterpret_cast<const float4 *>(ep + r * LDS + c);
+            if (res) {
+              const float4 q = *reinterpret_cast<const float4 *>(res + (int64_t)r * p.ldr + c);
+              y.x = __fadd_rn(q.x, y.x);
+              y.y = __fadd_rn(q.y, y.y);
+              y.z = __fadd_rn(q.z, y.z);
+              y.w = __fadd_rn(q.w, y.w);
+            }
+            *reinterpret_cast<float4 *>(dst + (int64_t)r * ldd + c) = y;
+          }
+        }
+      } else {
+        for (int r = ew; r < rows; r += kEpiWarps) {
+          for (int c = lane; c < width; c += 32) {
+            if (c < cols) {
+              float y = ep[r * LDS + c];
+              if (res)
+                y = __fadd_rn(res[(int64_t)r * p.ldr + c], y);
+              dst[(int64_t)r * ldd + c] = y;
+            }
           }
         }
       }
     }
+    }   // halves
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
   __syncthreads();
@@ -411,7 +450,7 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
       while (now_ns() - t0 < 2000000ull) {
       }
     }
-    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(kTmemCols) : "memory");
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(BNT) : "memory");
   }
 }
 
@@ -559,13 +598,13 @@ EncodeFn encode_fn() {
 }
 
 int make_map(CUtensorMap *map, CUtensorMapDataType dt, int bk, void *base, uint64_t inner, uint64_t rows,
-             uint64_t pitch_bytes, CUtensorMapSwizzle swz) {
+             uint64_t pitch_bytes, CUtensorMapSwizzle swz, int box_rows = 128) {
   EncodeFn fn = encode_fn();
   if (!fn)
     return fail(B200_ECUDA, "gemm_w8: cuTensorMapEncodeTiled is not available from this driver");
   const cuuint64_t dims[2] = {inner, rows};
   const cuuint64_t strides[1] = {pitch_bytes};
-  const cuuint32_t box[2] = {(cuuint32_t)bk, 128};
+  const cuuint32_t box[2] = {(cuuint32_t)bk, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1, 1};
   const CUresult rc = fn(map, dt, 2, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swz,
                          CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
@@ -584,7 +623,7 @@ using namespace b200;
 constexpr int64_t kSlabElems = (int64_t)32 << 20;   // 64 MB of bf16
 constexpr int kDenseRows = 256;                      // from this many rows on, convert the weights once per call
 
-template <int BKT, bool PRE>
+template <int BKT, bool PRE, int BNT>
 static int gemm_launch(const void *wbase, __nv_bfloat16 *hi, __nv_bfloat16 *lo, int Mp, GemmParams &p, int stages,
                        cudaStream_t st) {
   const int K = p.K, N = p.N;
@@ -596,27 +635,27 @@ static int gemm_launch(const void *wbase, __nv_bfloat16 *hi, __nv_bfloat16 *lo, 
     return rc;
   if (PRE) {
     if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, const_cast<void *>(wbase), K, N,
-                          (uint64_t)K * 2, swz))
+                          (uint64_t)K * 2, swz, BNT))
       return rc;
   } else {
     if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, BKT, const_cast<void *>(wbase), K, N, (uint64_t)K,
-                          CU_TENSOR_MAP_SWIZZLE_NONE))
+                          CU_TENSOR_MAP_SWIZZLE_NONE, BNT))
       return rc;
   }
   static int configured[64] = {};
   int dev = 0;
   B200_CUDA(cudaGetDevice(&dev));
-  const int smem = stages * (int)Tile<BKT, PRE>::STAGE_BYTES + 1024 + 256;
+  const int smem = stages * (int)Tile<BKT, PRE, BNT>::STAGE_BYTES + 1024 + 256;
   if (dev < 0 || dev >= 64 || configured[dev] < smem) {
-    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel<BKT, PRE>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    B200_CUDA(cudaFuncSetAttribute(gemm_w8_tc_kernel<BKT, PRE, BNT>, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
     if (dev >= 0 && dev < 64)
       configured[dev] = smem;
   }
-  if ((size_t)stages * Tile<BKT, PRE>::STAGE_BYTES < (size_t)BM * (BN + 1) * 4)
+  if ((size_t)stages * Tile<BKT, PRE, BNT>::STAGE_BYTES < (size_t)BM * (BN + 4) * 4)
     return fail(B200_EINVAL, "gemm_w8: the ring is smaller than the epilogue's staging tile");
   p.stages = stages;
-  const dim3 grid((N + BN - 1) / BN, Mp / BM, p.splits);
-  gemm_w8_tc_kernel<BKT, PRE><<<grid, PRE ? kThreadsPre : kThreadsConv, smem, st>>>(map_hi, map_lo, map_w, p);
+  const dim3 grid((N + BNT - 1) / BNT, Mp / BM, p.splits);
+  gemm_w8_tc_kernel<BKT, PRE, BNT><<<grid, PRE ? kThreadsPre : kThreadsConv, smem, st>>>(map_hi, map_lo, map_w, p);
   B200_LAUNCH_CHECK();
   if (p.splits > 1) {
     gemm_w8_combine_kernel<<<dim3(grid.x * grid.y, BM / 8), 256, 0, st>>>(p, (int)grid.x);
@@ -675,17 +714,10 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   p.partial = partial;
   p.error = err;
   p.splits = 1;
-  if (const char *e = getenv("BUDDY_B200_GEMM_DEBUG"))
-    p.debug = atoi(e);
-  // experiment switch "bk,stages[,dense rows]"
-  int bk = 32, stages = 3, dense_rows = kDenseRows;
-  if (const char *e = getenv("BUDDY_B200_GEMM_CFG"))
-    sscanf(e, "%d,%d,%d", &bk, &stages, &dense_rows);
-  if ((bk != 32 && bk != 64) || stages < 2 || stages > kMaxStages)
-    return fail(B200_EINVAL, "gemm_w8: bad BUDDY_B200_GEMM_CFG");
-  if (dense_rows < kDenseRows)
-    dense_rows = kDenseRows;   // the workspace holds a slab only from kDenseRows rows on
-  if (M >= dense_rows) {
+  // 32-element k blocks (64-byte swizzle rows), three stages: two CTAs fit on an SM, so one
+  // CTA's epilogue runs under the other's main loop
+  constexpr int kBK = 32, kStages = 3;
+  if (M >= kDenseRows) {
     // dense path: the weights of a slab of rows become bf16 once, then a plain bf16 x bf16 GEMM over the slab
     int64_t rows_per_slab = kSlabElems / K / BN * BN;
     for (int64_t r0 = 0; r0 < N; r0 += rows_per_slab) {
@@ -696,23 +728,37 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
       B200_LAUNCH_CHECK();
       p.N = (int)rows;
       p.n_off = (int)r0;
-      const int rc = bk == 64 ? gemm_launch<64, true>(slab, hi, lo, Mp, p, stages, st)
-                              : gemm_launch<32, true>(slab, hi, lo, Mp, p, stages, st);
+      // 256 weight rows per CTA when that still leaves enough CTAs; else 128, split over K if few
+      const int mt = Mp / BM;
+      const bool wide = ((rows + 255) / 256) * mt >= 256;
+      p.splits = 1;
+      if (!wide) {
+        const int tiles = (int)((rows + BN - 1) / BN) * mt;
+        if (tiles < 148) {
+          int splits = 296 / tiles;
+          if (splits > K / kBK / 16)
+            splits = K / kBK / 16;     // at least 16 k blocks per CTA
+          if (splits * tiles > kMaxPartialTiles)
+            splits = kMaxPartialTiles / tiles;
+          p.splits = splits < 1 ? 1 : splits;
+        }
+      }
+      const int rc = wide ? gemm_launch<kBK, true, 256>(slab, hi, lo, Mp, p, kStages, st)
+                          : gemm_launch<kBK, true, 128>(slab, hi, lo, Mp, p, kStages, st);
       if (rc)
         return rc;
     }
     return B200_OK;
   }
   // split over K when the output tiles alone leave most SMs idle
-  const int tiles = ((N + BN - 1) / BN) * (Mp / BM), nkb = K / bk;
+  const int tiles = ((N + BN - 1) / BN) * (Mp / BM), nkb = K / kBK;
   if (tiles < 100) {
     int splits = kMaxPartialTiles / tiles;
     if (splits > nkb / 4)
       splits = nkb / 4;
     p.splits = splits < 1 ? 1 : splits;
   }
-  return bk == 64 ? gemm_launch<64, false>(w->w, hi, lo, Mp, p, stages, st)
-                  : gemm_launch<32, false>(w->w, hi, lo, Mp, p, stages, st);
+  return gemm_launch<kBK, false, 128>(w->w, hi, lo, Mp, p, kStages, st);
 }
 
 /* 0, or the code of the first bounded wait that gave up in the last b200_gemm_w8 on this workspace
