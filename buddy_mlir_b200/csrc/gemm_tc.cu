@@ -629,9 +629,9 @@ static int gemm_launch(const void *wbase, __nv_bfloat16 *hi, __nv_bfloat16 *lo, 
   const int K = p.K, N = p.N;
   const CUtensorMapSwizzle swz = BKT == 64 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B;
   CUtensorMap map_hi, map_lo, map_w;
-  if (int rc = make_map(&map_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, hi, K, Mp, (uint64_t)K * 2, swz))
+  if (int rc = make_map(&map_hi, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, hi, K, p.M, (uint64_t)K * 2, swz))
     return rc;
-  if (int rc = make_map(&map_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, lo, K, Mp, (uint64_t)K * 2, swz))
+  if (int rc = make_map(&map_lo, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, lo, K, p.M, (uint64_t)K * 2, swz))
     return rc;
   if (PRE) {
     if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, BKT, const_cast<void *>(wbase), K, N,
@@ -698,7 +698,9 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   float *partial = reinterpret_cast<float *>(lo + (int64_t)Mp * K);
   __nv_bfloat16 *slab = reinterpret_cast<__nv_bfloat16 *>(partial + (int64_t)kMaxPartialTiles * BM * BN);
   B200_CUDA(cudaMemsetAsync(err, 0, 4, st));
-  split_activations_kernel<<<Mp, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
+  // rows M..Mp of the last tile are never written: the tensor maps end at row M and the TMA
+  // unit fills what lies beyond with zeros
+  split_activations_kernel<<<M, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
   B200_LAUNCH_CHECK();
   GemmParams p{};
   p.M = M;

@@ -668,8 +668,9 @@ gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const 
       for (int g = 0; g < G; ++g) {
         s[g] *= scale;
         const float nm = fmaxf(mx[g], s[g]);
-        const float alpha = expf(mx[g] - nm);
-        const float pw = expf(s[g] - nm);
+        // fast exponentials (2^-21 relative): the scan is bound by instruction issue
+        const float alpha = __expf(mx[g] - nm);
+        const float pw = __expf(s[g] - nm);
         l[g] = fmaf(l[g], alpha, pw);
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
