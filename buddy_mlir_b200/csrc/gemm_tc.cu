@@ -15,16 +15,28 @@
 // same f32 accumulator in tensor memory.  The split runs once per GEMM into a
 // workspace, in the k order of the packed weight rows (a dot product does not
 // care about the order of k as long as both operands agree), so the packed
-// decode weights are used as they are: no second copy of the weights.
+// decode weights are used as they are: no second copy of the weights is kept.
 //
-// One CTA computes a 128 x 128 tile of C.  Warp 0 issues the TMA loads
-// (cp.async.bulk.tensor, no multicast) of the two activation tiles (128-byte
-// swizzle) and of the raw int8 weight tile into a 3-stage ring; warps 2..5
-// convert the int8 tile to bf16 in the swizzled layout the tensor core reads;
-// warp 1 issues tcgen05.mma (kind::f16, 128 x 128 x 16 per instruction, two
-// terms x four k steps per stage) and commits the stage back to the loader;
-// after the last k block warps 2..5 read the accumulator with tcgen05.ld,
-// apply scale / bias / residual / SiLU-gate and store f32 rows.
+// Two forms of the kernel (template PRE):
+//  * converting (fewer than 256 rows: batched decode, HBM- and latency-bound).  One CTA
+//    computes a 128 x 128 tile of C.  Warp 0 issues the TMA loads (cp.async.bulk.tensor,
+//    no multicast) of the two activation tiles and of the raw int8 weight tile into a
+//    3-stage ring of 32-element k blocks (64-byte swizzle rows); warps 2..9 convert the
+//    int8 tile to bf16 in the swizzled layout the tensor core reads; warp 1 issues
+//    tcgen05.mma (kind::f16, 128 x 128 x 16 per instruction, two terms x two k steps per
+//    stage) and commits the stage back to the loader.  Few output tiles: the k range is
+//    split over gridDim.z CTAs and a second kernel adds the partial tiles in split order.
+//  * dense (256 rows and more: prefill).  A pass over the weights writes a slab of rows as
+//    bf16 first (64 MB of workspace, a few percent of the GEMM's time); the GEMM then loads
+//    both operands with TMA and nothing is converted in the main loop.  The main loop is
+//    bound by the bytes brought from L2 into shared memory, so a CTA takes 256 weight rows
+//    (one activation tile feeds two 128-column halves of a 256-column accumulator) when that
+//    still leaves enough CTAs to fill the machine.
+// Two CTAs are resident per SM (3 x 28 KB or 3 x 32 KB of ring, 128 or 256 of the 512
+// tensor-memory columns each), so one CTA's epilogue runs under the other's main loop.
+// Epilogue: warps 2..9 read the accumulator with tcgen05.ld (a thread owns a row), apply
+// scale / bias / SiLU-gate, stage the tile in the idle ring and write whole rows with
+// 16-byte stores (adding the residual there).
 //
 // Every wait is bounded (poll count and wall time); on expiry the CTA records
 // an error, all roles fall through, tensor memory is released and the host
