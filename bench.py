@@ -301,9 +301,29 @@ def gemm_microbench(lib, only=None):
         tf = 2.0 * M * N * K / us / 1e6
         out[name] = {"M": M, "N": N, "K": K, "us": round(us, 1), "TFLOP/s": round(tf, 1),
                      "frac_of_bf16_sustained": round(tf / peak, 3), "tensor_pipe_frac": round(2 * tf / peak, 3)}
+        # the same shape as W8A8 (int8 activations, integer tensor cores): quantiser + GEMM
+        nb8 = lib.b200_gemm_w8a8_workspace_bytes(M, K)
+        ws8 = torch.zeros(nb8, dtype=torch.uint8, device="cuda")
+
+        def launch8(i):
+            w = _lib.Weight(_lib.W_I8, 0, K, N, ws_[i % copies].data_ptr(), sc.data_ptr(), _lib.F32, 0, None)
+            _lib.check(lib.b200_gemm_w8a8(C.byref(w), A.data_ptr(), M, K, Cd.data_ptr(), N, ws8.data_ptr(), nb8, st))
+        for i in range(3):
+            launch8(i)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(reps):
+            launch8(i)
+        e1.record()
+        torch.cuda.synchronize()
+        _lib.check(lib.b200_gemm_w8_status(ws8.data_ptr(), st))
+        us8 = e0.elapsed_time(e1) * 1000.0 / reps
+        out[name]["w8a8_us"] = round(us8, 1)
+        out[name]["w8a8_TOP/s"] = round(2.0 * M * N * K / us8 / 1e6, 1)
     return {"shapes": out, "peak_tflops": peak,
             "note": "frac = algorithmic 2MNK / time / measured sustained bf16 peak; the tensor pipe does twice the "
-                    "algorithmic work (two bf16 terms per f32 activation)"}
+                    "algorithmic work (two bf16 terms per f32 activation); w8a8_* = the same shape with int8 "
+                    "activations on the integer tensor-core path (no measured int8 peak on this pool: absolute only)"}
 
 
 def run_gemm_only(args):

@@ -78,6 +78,8 @@ def load():
         "b200_gemm_w8": (i32, [C.POINTER(Weight), vp, i32, i64, vp, i64, vp, i64, vp, f32, i32,
                                vp, i64, vp]),
         "b200_gemm_w8_status": (i32, [vp, vp]),
+        "b200_gemm_w8a8_workspace_bytes": (i64, [i32, i64]),
+        "b200_gemm_w8a8": (i32, [vp, vp, i32, i64, vp, i64, vp, i64, vp]),
         "b200_rmsnorm": (i32, [vp, vp, vp, i64, i64, f32, vp]),
         "b200_silu_mul": (i32, [vp, vp, vp, i64, vp]),
         "b200_rope_kv_write": (i32, [vp, vp, vp, vp, vp, vp, vp, vp, f32, i32,
@@ -95,6 +97,8 @@ def load():
         "b200_model_set_linear": (i32, [vp, i32, i32, i32, vp, vp, i32, i32, i64,
                                         i64, i32, i32]),
         "b200_model_load_blobs": (i32, [vp, C.c_char_p, vp, i64, vp, i64, i32]),
+        "b200_model_save_packed": (i32, [vp, C.c_char_p]),
+        "b200_model_load_packed": (i32, [vp, C.c_char_p]),
         "b200_blob_elements": (i32, [C.POINTER(ModelConfigC), C.c_char_p,
                                      C.POINTER(i64), C.POINTER(i64)]),
         "b200_model_finalize": (i32, [vp]),

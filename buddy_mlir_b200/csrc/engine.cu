@@ -15,7 +15,9 @@
 
 #include <dlfcn.h>
 
+#include <algorithm>
 #include <cmath>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <string>
@@ -1278,6 +1280,178 @@ static int tp_push_setup(b200_model *m) {
     m->tp_push = TpPush{};
   }
   return B200_OK;
+}
+
+// ---- repack cache: the packed device layout of every tensor in one file ---------------------
+// Quantising and packing a model's blobs takes seconds; the result depends only on the
+// blobs, the configuration and the tensor-parallel rank.  b200_model_save_packed writes what
+// set_linear / set_vector left on the device (before finalize, which fuses and frees the
+// per-projection buffers); b200_model_load_packed fills a freshly created model from such a
+// file, after which finalize runs as usual.  Layout: header {magic "B2PACK01", config bytes,
+// tp size and rank, record count}, then records {layer, slot, is_linear, kind, group, K, N,
+// scale dtype, byte counts of weights / scales / bias} each followed by its payloads.
+namespace {
+constexpr char kPackMagic[8] = {'B', '2', 'P', 'A', 'C', 'K', '0', '1'};
+struct PackHeader {
+  char magic[8];
+  uint32_t config_bytes;
+  int32_t tp, rank;
+  uint32_t records;
+  b200_model_config cfg;
+};
+struct PackRecord {
+  int32_t layer, slot, is_linear, kind, group, scale_dtype;
+  int64_t K, N;
+  uint64_t w_bytes, scale_bytes, bias_bytes;
+};
+
+int write_device(FILE *f, const void *dev, uint64_t bytes, std::vector<char> &buf) {
+  for (uint64_t off = 0; off < bytes; off += buf.size()) {
+    const size_t n = (size_t)std::min<uint64_t>(buf.size(), bytes - off);
+    B200_CUDA(cudaMemcpy(buf.data(), (const char *)dev + off, n, cudaMemcpyDeviceToHost));
+    if (fwrite(buf.data(), 1, n, f) != n)
+      return fail(B200_EINVAL, "save_packed: write failed");
+  }
+  return B200_OK;
+}
+int read_device(FILE *f, void **dev, uint64_t bytes, std::vector<char> &buf) {
+  if (int rc = dev_alloc(dev, bytes)) return rc;
+  for (uint64_t off = 0; off < bytes; off += buf.size()) {
+    const size_t n = (size_t)std::min<uint64_t>(buf.size(), bytes - off);
+    if (fread(buf.data(), 1, n, f) != n)
+      return fail(B200_EINVAL, "load_packed: the file is truncated");
+    B200_CUDA(cudaMemcpy((char *)*dev + off, buf.data(), n, cudaMemcpyHostToDevice));
+  }
+  return B200_OK;
+}
+struct VecSlot { int layer, slot; float **p; int64_t n; };
+std::vector<VecSlot> vector_slots(b200_model *m) {
+  const b200_model_config &c = m->cfg;
+  std::vector<VecSlot> v = {{-1, B200_T_EMBED, &m->embed, (int64_t)c.vocab * c.hidden},
+                            {-1, B200_T_INV_FREQ, &m->inv_freq, c.head_dim / 2},
+                            {-1, B200_T_FINAL_NORM, &m->final_norm, c.hidden}};
+  for (int l = 0; l < c.n_layers; ++l) {
+    Layer &L = m->layers[l];
+    v.push_back({l, B200_T_IN_NORM, &L.in_norm, c.hidden});
+    v.push_back({l, B200_T_POST_NORM, &L.post_norm, c.hidden});
+    v.push_back({l, B200_T_Q_NORM, &L.q_norm, c.head_dim});
+    v.push_back({l, B200_T_K_NORM, &L.k_norm, c.head_dim});
+  }
+  return v;
+}
+constexpr int kLinearSlots[] = {B200_T_Q, B200_T_K, B200_T_V, B200_T_O, B200_T_GATE, B200_T_UP, B200_T_DOWN};
+} // namespace
+
+int b200_model_save_packed(b200_model *m, const char *path) {
+  if (!m || !path)
+    return fail(B200_EINVAL, "save_packed: null argument");
+  if (m->finalized)
+    return fail(B200_ESTATE, "save_packed: call it before finalize (finalize frees the per-projection buffers)");
+  FILE *f = fopen(path, "wb");
+  if (!f)
+    return fail(B200_EINVAL, "save_packed: cannot create %s", path);
+  std::vector<char> buf((size_t)64 << 20);
+  std::vector<std::pair<PackRecord, DevLinear *>> lin;
+  std::vector<std::pair<PackRecord, float *>> vec;
+  for (const VecSlot &v : vector_slots(m))
+    if (*v.p) {
+      PackRecord r{};
+      r.layer = v.layer; r.slot = v.slot; r.N = v.n; r.w_bytes = (uint64_t)v.n * 4;
+      vec.push_back({r, *v.p});
+    }
+  auto add_linear = [&](int layer, int slot, DevLinear *L) {
+    if (!L->set) return;
+    PackRecord r{};
+    r.layer = layer; r.slot = slot; r.is_linear = 1;
+    r.kind = L->w.kind; r.group = L->w.group; r.scale_dtype = L->w.scale_dtype;
+    r.K = L->w.K; r.N = L->w.N;
+    r.w_bytes = (uint64_t)packed_row_bytes(L->w.kind, L->w.K) * L->w.N;
+    const int64_t ng = (L->w.kind == B200_W_U4 && L->w.group > 0 && L->w.group < L->w.K) ? L->w.K / L->w.group : 1;
+    r.scale_bytes = L->scale_buf ? (uint64_t)L->w.N * ng * (L->w.scale_dtype == B200_F32 ? 4 : 2) : 0;
+    r.bias_bytes = L->bias_buf ? (uint64_t)L->w.N * 4 : 0;
+    lin.push_back({r, L});
+  };
+  for (int l = 0; l < m->cfg.n_layers; ++l)
+    for (int slot : kLinearSlots)
+      add_linear(l, slot, linear_slot(m, l, slot));
+  add_linear(-1, B200_T_LM_HEAD, &m->lm_head);
+  PackHeader h{};
+  memcpy(h.magic, kPackMagic, 8);
+  h.config_bytes = sizeof(b200_model_config);
+  h.tp = m->tp;
+  h.rank = m->rank;
+  h.records = (uint32_t)(vec.size() + lin.size());
+  h.cfg = m->cfg;
+  int rc = fwrite(&h, sizeof h, 1, f) == 1 ? B200_OK : fail(B200_EINVAL, "save_packed: write failed");
+  for (auto &v : vec) {
+    if (rc == B200_OK && fwrite(&v.first, sizeof(PackRecord), 1, f) != 1) rc = fail(B200_EINVAL, "save_packed: write failed");
+    if (rc == B200_OK) rc = write_device(f, v.second, v.first.w_bytes, buf);
+  }
+  for (auto &l : lin) {
+    if (rc == B200_OK && fwrite(&l.first, sizeof(PackRecord), 1, f) != 1) rc = fail(B200_EINVAL, "save_packed: write failed");
+    if (rc == B200_OK) rc = write_device(f, l.second->w_buf, l.first.w_bytes, buf);
+    if (rc == B200_OK && l.first.scale_bytes) rc = write_device(f, l.second->scale_buf, l.first.scale_bytes, buf);
+    if (rc == B200_OK && l.first.bias_bytes) rc = write_device(f, l.second->bias_buf, l.first.bias_bytes, buf);
+  }
+  if (fclose(f) != 0 && rc == B200_OK)
+    rc = fail(B200_EINVAL, "save_packed: close failed");
+  if (rc != B200_OK)
+    remove(path);
+  return rc;
+}
+
+int b200_model_load_packed(b200_model *m, const char *path) {
+  if (!m || !path)
+    return fail(B200_EINVAL, "load_packed: null argument");
+  if (m->finalized)
+    return fail(B200_ESTATE, "load_packed: model already finalised");
+  FILE *f = fopen(path, "rb");
+  if (!f)
+    return fail(B200_EINVAL, "load_packed: cannot open %s", path);
+  std::vector<char> buf((size_t)64 << 20);
+  PackHeader h{};
+  int rc = B200_OK;
+  if (fread(&h, sizeof h, 1, f) != 1 || memcmp(h.magic, kPackMagic, 8) != 0 ||
+      h.config_bytes != sizeof(b200_model_config))
+    rc = fail(B200_EINVAL, "load_packed: %s is not a packed-weights file of this library version", path);
+  else if (memcmp(&h.cfg, &m->cfg, sizeof(b200_model_config)) != 0 || h.tp != m->tp || h.rank != m->rank)
+    rc = fail(B200_EINVAL, "load_packed: the file was written for another configuration or tensor-parallel rank");
+  const std::vector<VecSlot> vs = vector_slots(m);
+  for (uint32_t i = 0; i < h.records && rc == B200_OK; ++i) {
+    PackRecord r{};
+    if (fread(&r, sizeof r, 1, f) != 1) {
+      rc = fail(B200_EINVAL, "load_packed: the file is truncated");
+      break;
+    }
+    if (!r.is_linear) {
+      const VecSlot *slot = nullptr;
+      for (const VecSlot &v : vs)
+        if (v.layer == r.layer && v.slot == r.slot) slot = &v;
+      if (!slot || r.N != slot->n || r.w_bytes != (uint64_t)slot->n * 4) {
+        rc = fail(B200_EINVAL, "load_packed: unexpected vector record (layer %d, slot %d)", r.layer, r.slot);
+        break;
+      }
+      if (*slot->p) { cudaFree(*slot->p); *slot->p = nullptr; }
+      rc = read_device(f, (void **)slot->p, r.w_bytes, buf);
+      continue;
+    }
+    DevLinear *L = linear_slot(m, r.layer, r.slot);
+    if (!L || r.K < 1 || r.N < 1 || r.w_bytes != (uint64_t)packed_row_bytes(r.kind, r.K) * r.N) {
+      rc = fail(B200_EINVAL, "load_packed: unexpected linear record (layer %d, slot %d)", r.layer, r.slot);
+      break;
+    }
+    L->release();
+    rc = read_device(f, &L->w_buf, r.w_bytes, buf);
+    if (rc == B200_OK && r.scale_bytes) rc = read_device(f, &L->scale_buf, r.scale_bytes, buf);
+    if (rc == B200_OK && r.bias_bytes) rc = read_device(f, (void **)&L->bias_buf, r.bias_bytes, buf);
+    if (rc != B200_OK) { L->release(); break; }
+    L->w = b200_weight{};
+    L->w.kind = r.kind; L->w.group = r.group; L->w.K = r.K; L->w.N = r.N;
+    L->w.w = L->w_buf; L->w.scale = L->scale_buf; L->w.scale_dtype = r.scale_dtype; L->w.bias = L->bias_buf;
+    L->set = true;
+  }
+  fclose(f);
+  return rc;
 }
 
 int b200_model_finalize(b200_model *m) {

@@ -45,6 +45,7 @@
 
 #include <cuda.h>
 
+#include <algorithm>
 #include <mutex>
 
 namespace b200 {
@@ -592,6 +593,198 @@ split_activations_kernel(const float *A, int64_t lda, int M, int K, int Kp, cons
   }
 }
 
+// ---- W8A8: int8 activations x int8 weights on the integer tensor-core path -----------------
+// buddy-mlir's QuantizedMatmulOp (frontend/Python/ops/linalg.py:12728-12846): one scale for
+// the whole activation tensor, s = max(absmax / 127, 1e-10), q = clamp(rne(x * (1 / s)), -128,
+// 127), an exact i8 x i8 -> i32 contraction, y = float(acc) * (s * weight_scale[n]) (+ bias).
+// Every step is reproduced operation by operation, so the result is bit-identical to the
+// reference arithmetic.  Both operands are loaded by TMA as stored (64-byte swizzle applied by
+// the copy), tcgen05.mma kind::i8 accumulates s32 in tensor memory: no conversion anywhere.
+constexpr int BK8 = 64;                        // int8 per k block = one 64-byte swizzle row
+constexpr int kStages8 = 5;                    // 5 x 16 KB: the ring also stages the epilogue tile
+constexpr uint32_t kTile8 = BM * BK8;          // 8 KB per operand tile
+constexpr uint32_t kIdescI8 = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+
+__device__ __forceinline__ void mma_i8(uint32_t tmem_d, uint64_t da, uint64_t db, uint32_t accumulate) {
+  asm volatile(
+      "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+      " tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, p;\n}"
+      ::"r"(tmem_d), "l"(da), "l"(db), "r"(kIdescI8), "r"(accumulate)
+      : "memory");
+}
+
+struct W8A8Params {
+  int M, N, K;
+  const float *wscale, *bias;
+  const float *act_scale;      // device scalar written by quantize_activations_kernel
+  float *C;
+  int64_t ldc;
+  int *error;
+};
+
+__global__ void __launch_bounds__(kThreadsPre, 2)
+gemm_w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    const W8A8Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t *tiles = reinterpret_cast<uint8_t *>(((uintptr_t)smem + 1023) & ~(uintptr_t)1023);
+  Bars &bars = *reinterpret_cast<Bars *>(tiles + kStages8 * 2 * kTile8);
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
+  const int nkb = p.K / BK8;
+  volatile int *ab = &bars.abort_flag;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages8; ++s) {
+      mbar_init(&bars.full[s], 1);
+      mbar_init(&bars.empty[s], 1);
+    }
+    mbar_init(&bars.accum, 1);
+    bars.abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) {
+    asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&bars.tmem_base)), "n"(BN) : "memory");
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+  const uint32_t tmem = bars.tmem_base;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages8, use = i / kStages8;
+        if (use > 0 && !mbar_wait(&bars.empty[s], (use - 1) & 1, ab, p.error, 711))
+          break;
+        uint8_t *st = tiles + s * 2 * kTile8;
+        mbar_expect_tx(&bars.full[s], 2 * kTile8);
+        tma_load_2d(st, &map_a, i * BK8, m0, &bars.full[s]);
+        tma_load_2d(st + kTile8, &map_w, i * BK8, n0, &bars.full[s]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      for (int i = 0; i < nkb; ++i) {
+        const int s = i % kStages8, use = i / kStages8;
+        if (!mbar_wait(&bars.full[s], use & 1, ab, p.error, 712))
+          break;
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        const uint32_t a = smem_u32(tiles + s * 2 * kTile8), w = a + kTile8;
+#pragma unroll
+        for (int k = 0; k < BK8 / 32; ++k)   // 32 int8 = 32 bytes along the swizzled row
+          mma_i8(tmem, smem_desc<32>(a + k * 32), smem_desc<32>(w + k * 32), (i | k) != 0);
+        tc_commit(&bars.empty[s]);
+      }
+      tc_commit(&bars.accum);
+    }
+  } else {
+    const bool ok = mbar_wait(&bars.accum, 0, ab, p.error, 713);
+    constexpr int LDS = BN + 4;
+    float *ep = reinterpret_cast<float *>(tiles);   // [BM][LDS] staged in the idle ring
+    if (ok) {
+      asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+      const float sa = *p.act_scale;
+      const int quad = warp & 3;
+      const int row = quad * 32 + lane;
+      const int cb0 = ((warp - 2) >> 2) * (BN / 2), cb1 = cb0 + BN / 2;
+#pragma unroll 1
+      for (int cb = cb0; cb < cb1; cb += 32) {
+        uint32_t v[32];
+        const uint32_t taddr = tmem + ((uint32_t)(quad * 32) << 16) + (uint32_t)cb;
+        asm volatile(
+            "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+            "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+            "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+            : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+              "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+              "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+              "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+            : "r"(taddr)
+            : "memory");
+        asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+        float *erow = ep + row * LDS;
+#pragma unroll
+        for (int j = 0; j < 32; j += 4) {
+          float o[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int n = min(n0 + cb + j + e, p.N - 1);
+            // linalg.py:12836-12846: float(acc) * (act_scale * weight_scale[n])
+            float y = __fmul_rn(__int2float_rn((int)v[j + e]), __fmul_rn(sa, __ldg(p.wscale + n)));
+            if (p.bias)
+              y = __fadd_rn(y, __ldg(p.bias + n));
+            o[e] = y;
+          }
+          *reinterpret_cast<float4 *>(erow + cb + j) = make_float4(o[0], o[1], o[2], o[3]);
+        }
+      }
+    }
+    asm volatile("bar.sync 1, %0;" ::"n"(8 * 32) : "memory");
+    if (ok) {
+      const int ew = warp - 2;
+      const int rows = min(BM, p.M - m0), cols = min(BN, p.N - n0);
+      float *dst = p.C + (int64_t)m0 * p.ldc + n0;
+      for (int r = ew; r < rows; r += 8)
+        for (int c = lane; c < cols; c += 32)
+          dst[(int64_t)r * p.ldc + c] = ep[r * LDS + c];
+    }
+  }
+  asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+  __syncthreads();
+  if (warp == 1) {
+    if (*ab) {
+      const unsigned long long t0 = now_ns();
+      while (now_ns() - t0 < 2000000ull) {
+      }
+    }
+    asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "n"(BN) : "memory");
+  }
+}
+
+// max |x| over the whole tensor (non-negative floats order like their bit patterns)
+__global__ void __launch_bounds__(256)
+absmax_kernel(const float *A, int64_t lda, int M, int K, uint32_t *out) {
+  float mx = 0.f;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < (int64_t)M * K; i += (int64_t)gridDim.x * blockDim.x) {
+    const int m = (int)(i / K), k = (int)(i - (int64_t)m * K);
+    mx = fmaxf(mx, fabsf(A[(int64_t)m * lda + k]));
+  }
+  mx = warp_max(mx);
+  if ((threadIdx.x & 31) == 0)
+    atomicMax(out, __float_as_uint(mx));
+}
+
+// linalg.py:12728-12792 for four consecutive k per thread, written in the k order of the packed
+// weight rows; thread 0 of the grid also leaves the scale for the GEMM's epilogue.
+__global__ void __launch_bounds__(256)
+quantize_activations_kernel(const float *A, int64_t lda, int M, int K, const uint32_t *absmax, float *scale_out,
+                            uint32_t *q) {
+  const float scale = fmaxf(__fmul_rn(__uint_as_float(*absmax), __fdiv_rn(1.0f, 127.0f)), 1e-10f);
+  const float inv = __fdiv_rn(1.0f, scale);
+  if (blockIdx.x == 0 && threadIdx.x == 0)
+    *scale_out = scale;
+  const int m = blockIdx.x;
+  const float *arow = A + (int64_t)m * lda;
+  uint32_t *qrow = q + (int64_t)m * (K / 4);
+  for (int k = threadIdx.x * 4; k < K; k += blockDim.x * 4) {
+    uint32_t pk = 0;
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      float r = rintf(__fmul_rn(arow[k + e], inv));     // the f32 -> i32 cast rounds to nearest even
+      r = fminf(fmaxf(r, -128.0f), 127.0f);
+      pk |= ((uint32_t)(int)r & 0xFFu) << (8 * e);
+    }
+    int64_t pos;
+    if ((k | 511) < (K & ~511)) {
+      const int kk = k & 511;
+      pos = (k & ~511) + ((kk & 127) >> 2) * 16 + (kk >> 7) * 4;
+    } else {
+      pos = packed_offset(B200_W_I8, K, k, nullptr);
+    }
+    qrow[pos >> 2] = pk;
+  }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -773,6 +966,70 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
     p.splits = splits < 1 ? 1 : splits;
   }
   return gemm_launch<kBK, false, 128>(w->w, hi, lo, Mp, p, kStages, st);
+}
+
+/* W8A8 (buddy-mlir's QuantizedMatmulOp): workspace = b200_gemm_w8a8_workspace_bytes(M, K). */
+int64_t b200_gemm_w8a8_workspace_bytes(int M, int64_t K) {
+  if (M < 1 || K < 1)
+    return 0;
+  return 256 + (int64_t)M * K;
+}
+
+int b200_gemm_w8a8(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
+                   void *workspace, int64_t workspace_bytes, void *stream) {
+  if (!w || !A || !C || !workspace)
+    return fail(B200_EINVAL, "gemm_w8a8: null argument");
+  if (w->kind != B200_W_I8 || w->scale_dtype != B200_F32 || !w->scale || !w->w)
+    return fail(B200_EINVAL, "gemm_w8a8: int8 per-channel weights with f32 scales expected");
+  if (M < 1 || w->K % BK8 != 0 || w->N < 1)
+    return fail(B200_EINVAL, "gemm_w8a8: M >= 1 and K a multiple of %d expected", BK8);
+  if (((uintptr_t)w->w & 15) || ((uintptr_t)workspace & 255))
+    return fail(B200_EINVAL, "gemm_w8a8: weight rows must be 16-byte aligned, the workspace 256-byte aligned");
+  if (workspace_bytes < b200_gemm_w8a8_workspace_bytes(M, w->K))
+    return fail(B200_EINVAL, "gemm_w8a8: workspace too small");
+  if (int rc = ensure_device())
+    return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  const int K = (int)w->K, N = (int)w->N;
+  int *err = reinterpret_cast<int *>(workspace);
+  uint32_t *absmax = reinterpret_cast<uint32_t *>(workspace) + 1;
+  float *act_scale = reinterpret_cast<float *>(workspace) + 2;
+  uint32_t *q = reinterpret_cast<uint32_t *>((char *)workspace + 256);
+  B200_CUDA(cudaMemsetAsync(workspace, 0, 16, st));
+  const int64_t total = (int64_t)M * K;
+  absmax_kernel<<<(unsigned)std::min<int64_t>((total + 255) / 256, 148 * 8), 256, 0, st>>>(A, lda, M, K, absmax);
+  B200_LAUNCH_CHECK();
+  quantize_activations_kernel<<<M, 256, 0, st>>>(A, lda, M, K, absmax, act_scale, q);
+  B200_LAUNCH_CHECK();
+  CUtensorMap map_a, map_w;
+  if (int rc = make_map(&map_a, CU_TENSOR_MAP_DATA_TYPE_UINT8, BK8, q, K, M, (uint64_t)K, CU_TENSOR_MAP_SWIZZLE_64B))
+    return rc;
+  if (int rc = make_map(&map_w, CU_TENSOR_MAP_DATA_TYPE_UINT8, BK8, const_cast<void *>(w->w), K, N, (uint64_t)K,
+                        CU_TENSOR_MAP_SWIZZLE_64B))
+    return rc;
+  W8A8Params p{};
+  p.M = M;
+  p.N = N;
+  p.K = K;
+  p.wscale = (const float *)w->scale;
+  p.bias = (const float *)w->bias;
+  p.act_scale = act_scale;
+  p.C = C;
+  p.ldc = ldc;
+  p.error = err;
+  static bool configured[64] = {};
+  int dev = 0;
+  B200_CUDA(cudaGetDevice(&dev));
+  const int smem = kStages8 * 2 * (int)kTile8 + 1024 + 256;
+  if (dev < 0 || dev >= 64 || !configured[dev]) {
+    B200_CUDA(cudaFuncSetAttribute(gemm_w8a8_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    if (dev >= 0 && dev < 64)
+      configured[dev] = true;
+  }
+  const dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
+  gemm_w8a8_tc_kernel<<<grid, kThreadsPre, smem, st>>>(map_a, map_w, p);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
 }
 
 /* 0, or the code of the first bounded wait that gave up in the last b200_gemm_w8 on this workspace

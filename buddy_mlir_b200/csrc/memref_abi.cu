@@ -314,6 +314,43 @@ void _mlir_ciface_buddy_gemv_w8_f32(b200_memref_f32_2 *result, b200_memref_f32_2
   out2(result, y, M, N);
 }
 
+void _mlir_ciface_buddy_matmul_w8a8_f32(b200_memref_f32_2 *result, b200_memref_f32_2 *A,
+                                        b200_memref_i8_2 *W, b200_memref_f32_2 *scale) {
+  out_null(result);
+  const int64_t M = A->sizes[0], K = A->sizes[1], N = W->sizes[1];
+  if (W->sizes[0] != K || scale->sizes[0] * scale->sizes[1] != N || M < 1 || M > 0x7fffffff) {
+    fail(B200_EINVAL, "buddy_matmul_w8a8_f32: shape mismatch");
+    return;
+  }
+  std::vector<float> ta, ts;
+  std::vector<int8_t> tw;
+  const float *a = dense2<float>(A, ta), *s = dense2<float>(scale, ts);
+  const int8_t *q = dense2<int8_t>(W, tw);
+  const b200_weight *w = nullptr;
+  std::lock_guard<std::mutex> entry(g_entry_mu);
+  if (cached_weight(B200_W_I8, q, s, B200_F32, 1, K, N, 1, key_of(W, scale), &w))
+    return;
+  DevBuf da, dc, ws;
+  const int64_t wsb = b200_gemm_w8a8_workspace_bytes((int)M, K);
+  if (da.alloc((size_t)M * K * 4) || dc.alloc((size_t)M * N * 4) || ws.alloc((size_t)wsb))
+    return;
+  if (cudaMemcpy(da.p, a, (size_t)M * K * 4, cudaMemcpyHostToDevice) != cudaSuccess) {
+    fail(B200_ECUDA, "buddy_matmul_w8a8_f32: upload failed");
+    return;
+  }
+  if (b200_gemm_w8a8(w, (const float *)da.p, (int)M, K, (float *)dc.p, N, ws.p, wsb, nullptr) ||
+      b200_gemm_w8_status(ws.p, nullptr))
+    return;
+  float *y = host_alloc<float>((size_t)M * N);
+  if (!y) return;
+  if (cudaMemcpy(y, dc.p, (size_t)M * N * 4, cudaMemcpyDeviceToHost) != cudaSuccess) {
+    fail(B200_ECUDA, "buddy_matmul_w8a8_f32: download failed");
+    std::free(y);
+    return;
+  }
+  out2(result, y, M, N);
+}
+
 void _mlir_ciface_buddy_gemv_w4_f16(b200_memref_f16_2 *result, b200_memref_f16_2 *A,
                                     b200_memref_i8_2 *P, b200_memref_f16_2 *scale) {
   out_null(result);

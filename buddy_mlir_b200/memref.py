@@ -80,6 +80,10 @@ def buddy_gemv_w8_f32(A, W, scale):
     return _call("_mlir_ciface_buddy_gemv_w8_f32", np.float32, 2, A, W, scale)
 
 
+def buddy_matmul_w8a8_f32(A, W, scale):
+    return _call("_mlir_ciface_buddy_matmul_w8a8_f32", np.float32, 2, A, W, scale)
+
+
 def buddy_gemv_w4_f16(A, P, scale):
     return _call("_mlir_ciface_buddy_gemv_w4_f16", np.float16, 2, A, P, scale)
 

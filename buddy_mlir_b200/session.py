@@ -57,14 +57,22 @@ class ModelSession:
 
     # ---- loading -----------------------------------------------------------
     def load_blobs(self, variant: str, float_blob: np.ndarray, int_blob=None,
-                   all_linear_w8: bool = False):
-        """loadWeights (gen_session.py:1301-1338) for in-memory blobs."""
+                   all_linear_w8: bool = False, save_packed=None):
+        """loadWeights (gen_session.py:1301-1338) for in-memory blobs.
+        save_packed: path of a repack-cache file to write before finalising."""
         fb = np.ascontiguousarray(float_blob, dtype=np.float16 if variant == "w4a16" else np.float32)
         ib = None if int_blob is None else np.ascontiguousarray(int_blob, dtype=np.int8)
         _lib.check(self.lib.b200_model_load_blobs(
             self._h, variant.encode(), fb.ctypes.data, fb.size,
             None if ib is None else ib.ctypes.data, 0 if ib is None else ib.size,
             int(all_linear_w8)))
+        if save_packed is not None:
+            _lib.check(self.lib.b200_model_save_packed(self._h, str(save_packed).encode()))
+        self.finalize()
+
+    def load_packed(self, path):
+        """Fill the model from a repack-cache file (b200_model_save_packed) and finalise."""
+        _lib.check(self.lib.b200_model_load_packed(self._h, str(path).encode()))
         self.finalize()
 
     def load_weights(self, paths, variant: str, all_linear_w8: bool = False):

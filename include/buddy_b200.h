@@ -170,6 +170,21 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda,
                  void *workspace, int64_t workspace_bytes, void *stream);
 int b200_gemm_w8_status(void *workspace, void *stream);
 
+/* W8A8 (buddy-mlir's QuantizedMatmulOp / QuantizedAddMMOp,
+ * frontend/Python/ops/linalg.py:12728-12910): the activations get one dynamic
+ * scale for the whole [M, K] tensor, s = max(absmax / 127, 1e-10), are rounded
+ * to int8 (nearest even), contracted exactly with the int8 weights on the
+ * integer tensor-core path (tcgen05.mma kind::i8, s32 accumulator in tensor
+ * memory), and C[m, n] = float(acc) * (s * scale[n]) (+ w->bias[n]).  Every
+ * step follows the reference operation by operation: results are bit-identical
+ * to its arithmetic.  w: int8 per-channel weights in the packed device layout,
+ * K a multiple of 64.  workspace: b200_gemm_w8a8_workspace_bytes(M, K) bytes,
+ * 256-byte aligned; b200_gemm_w8_status() reads its error word as well. */
+int64_t b200_gemm_w8a8_workspace_bytes(int M, int64_t K);
+int b200_gemm_w8a8(const b200_weight *w, const float *A, int M, int64_t lda,
+                   float *C, int64_t ldc, void *workspace,
+                   int64_t workspace_bytes, void *stream);
+
 /* ------------------------------------------------------------------------
  * Small fused ops (f32).
  * ---------------------------------------------------------------------- */
@@ -278,6 +293,16 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
                           const void *float_blob, int64_t n_float,
                           const void *int_blob, int64_t n_int,
                           int all_linear_w8);
+/* Repack cache (the one-time GPU-layout repack of a model's blobs, kept on disk).
+ * save_packed writes the packed device layout of every tensor set so far
+ * (quantised, sharded for this tensor-parallel rank) to `path`; call it after
+ * load_blobs / set_linear / set_vector and BEFORE finalize.  load_packed fills a
+ * freshly created model from such a file instead of walking the blobs; the file
+ * must have been written for the same configuration, tp_size and tp_rank
+ * (B200_EINVAL otherwise).  The file holds nothing but this library's own
+ * layout: a new library version may refuse an old file. */
+int b200_model_save_packed(b200_model *m, const char *path);
+int b200_model_load_packed(b200_model *m, const char *path);
 /* Expected element counts of the blobs for a variant (pure host function). */
 int b200_blob_elements(const b200_model_config *cfg, const char *variant,
                        int64_t *n_float, int64_t *n_int);

@@ -62,6 +62,15 @@ void _mlir_ciface_buddy_gemv_w8_f32(b200_memref_f32_2 *result,
                                     b200_memref_f32_2 *A, b200_memref_i8_2 *W,
                                     b200_memref_f32_2 *scale);
 
+/* W8A8 matmul: what the reference lowers QuantizedMatmulOp to
+ * (frontend/Python/ops/linalg.py:12797-12846): dynamic per-tensor int8
+ * activations, i8 x i8 -> i32, C[m,n] = float(acc) * (act_scale * scale[0,n]).
+ * A [M,K] f32 (K a multiple of 64), W [K,N] int8, scale [1,N] f32.  Runs on the
+ * integer tensor cores; bit-identical to the reference arithmetic. */
+void _mlir_ciface_buddy_matmul_w8a8_f32(b200_memref_f32_2 *result,
+                                        b200_memref_f32_2 *A, b200_memref_i8_2 *W,
+                                        b200_memref_f32_2 *scale);
+
 /* packed-int4 decode matmul, f16 in / f16 out
  * (Int4DequantMatMulVectorizationDecode.cpp:320-562): A [M,K] f16,
  * P [K,N/2] signed nibbles, scale [1,N] f16. Accumulates in f32. */

@@ -291,6 +291,39 @@ void orc_gemm_w8_prefill_f32(const float *A, const int8_t *Q,
     }
 }
 
+// frontend/Python/ops/linalg.py:12728-12846 (QuantizedMatmulOp / QuantizedAddMMOp, the w8a8
+// variant): one dynamic scale for the whole activation tensor, exact i8 x i8 -> i32
+// contraction, result * (act_scale * weight_scale[n]) (+ bias).  The f32 -> i32 cast of the
+// quantiser rounds to nearest even (tosa.cast).
+void orc_matmul_w8a8(const float *A, const int8_t *Q, const float *scale, const float *bias,
+                     float *C, int64_t M, int64_t K, int64_t N) {
+  float amax = 0.0f;
+  for (int64_t i = 0; i < M * K; ++i)
+    amax = std::fmax(amax, std::fabs(A[i]));
+  const float r127 = 1.0f / 127.0f;
+  const float raw = amax * r127;
+  const float s = raw > 1e-10f ? raw : 1e-10f;
+  const float inv = 1.0f / s;
+  std::vector<int8_t> q((size_t)(M * K));
+  for (int64_t i = 0; i < M * K; ++i) {
+    float v = std::nearbyintf(A[i] * inv);
+    v = v < -128.0f ? -128.0f : (v > 127.0f ? 127.0f : v);
+    q[(size_t)i] = (int8_t)v;
+  }
+#pragma omp parallel for schedule(static)
+  for (int64_t m = 0; m < M; ++m)
+    for (int64_t n = 0; n < N; ++n) {
+      int32_t acc = 0;
+      for (int64_t k = 0; k < K; ++k)
+        acc += (int32_t)q[(size_t)(m * K + k)] * (int32_t)Q[k * N + n];
+      const float combined = s * scale[n];
+      float y = (float)acc * combined;
+      if (bias)
+        y = y + bias[n];
+      C[m * N + n] = y;
+    }
+}
+
 // ---------------------------------------------------------------------------
 // subgraph0_decode_simplify.mlir:60-72
 void orc_rmsnorm(const float *x, const float *w, float *y, int64_t H,

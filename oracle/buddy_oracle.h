@@ -85,6 +85,11 @@ void orc_gemv_f32_packed(const float *x, const float *packed, float *y,
 void orc_gemm_w8_prefill_f32(const float *A, const int8_t *Q,
                              const float *scale, float *C, int64_t M,
                              int64_t K, int64_t N);
+/* frontend/Python/ops/linalg.py:12728-12846 (w8a8): dynamic per-tensor int8
+ * activations, i8 x i8 -> i32, * (act_scale * scale[n]) (+ bias, may be NULL). */
+void orc_matmul_w8a8(const float *A, const int8_t *Q, const float *scale,
+                     const float *bias, float *C, int64_t M, int64_t K,
+                     int64_t N);
 
 /* ---- small ops --------------------------------------------------------- */
 /* examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:60-72. */

@@ -175,6 +175,18 @@ def gemm_w8_prefill_f32(A, Q, scale, C0):
     return out
 
 
+def matmul_w8a8(A, Q, scale, bias=None):
+    A = np.ascontiguousarray(A, dtype=np.float32)
+    M, K = A.shape
+    N = Q.shape[1]
+    out = np.zeros((M, N), dtype=np.float32)
+    Q = np.ascontiguousarray(Q, dtype=np.int8)
+    scale = np.ascontiguousarray(scale, dtype=np.float32).reshape(-1)
+    b = None if bias is None else np.ascontiguousarray(bias, dtype=np.float32)
+    lib().orc_matmul_w8a8(_p(A), _p(Q), _p(scale), None if b is None else _p(b), _p(out), i64(M), i64(K), i64(N))
+    return out
+
+
 def rmsnorm(x, w, eps):
     x = np.ascontiguousarray(x, dtype=np.float32).reshape(-1)
     w = np.ascontiguousarray(w, dtype=np.float32)

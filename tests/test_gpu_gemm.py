@@ -76,3 +76,32 @@ def test_gemm_w8_fused_norm_bias_residual_and_silu_pairs():
     want = np.stack([orc.silu_mul(g[i, 0::2], g[i, 1::2]) for i in range(M)])
     y = gemm_w8(w, dev(s), K, N, dev(A), silu=True).cpu().numpy()
     assert y.shape == (M, N // 2) and rel(y, want) < TOL
+
+
+# ---- W8A8: int8 x int8 on the integer tensor cores (QuantizedMatmulOp) ------------------------
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,N,K", [(1, 256, 64), (7, 130, 128), (64, 1536, 1536), (200, 1000, 576), (1024, 2048, 1536)])
+def test_matmul_w8a8_is_bit_identical_to_the_restatement(M, N, K):
+    """frontend/Python/ops/linalg.py:12728-12846: dynamic per-tensor int8 activations, exact
+    integer contraction, one f32 rescale.  Integer work: bit-exact, ragged M and N included."""
+    from buddy_mlir_b200 import memref
+    rng = np.random.default_rng(M * 31 + N)
+    A = (rng.standard_normal((M, K)) * 3).astype(np.float32)
+    A[0, 0] = 11.5                                   # the tensor's absmax, away from the mean
+    Q = rng.integers(-128, 128, (K, N)).astype(np.int8)
+    scale = (rng.random((1, N)).astype(np.float32) + 0.5) * np.float32(0.01)
+    want = orc.matmul_w8a8(A, Q, scale)
+    got = memref.buddy_matmul_w8a8_f32(A, Q, scale)
+    assert got.shape == (M, N)
+    assert np.array_equal(got, want)
+
+
+@pytest.mark.gpu
+def test_matmul_w8a8_all_zero_activations_and_bad_k():
+    from buddy_mlir_b200 import memref
+    Q = np.ones((64, 128), dtype=np.int8)
+    scale = np.ones((1, 128), dtype=np.float32)
+    got = memref.buddy_matmul_w8a8_f32(np.zeros((3, 64), dtype=np.float32), Q, scale)
+    assert np.array_equal(got, np.zeros((3, 128), dtype=np.float32))      # scale clamps at 1e-10, q = 0
+    with pytest.raises(RuntimeError):
+        memref.buddy_matmul_w8a8_f32(np.zeros((3, 40), dtype=np.float32), np.ones((40, 128), dtype=np.int8), scale)

@@ -139,6 +139,38 @@ def test_load_weights_from_the_reference_blob_files(tmp_path):
     s.close()
 
 
+@pytest.mark.parametrize("cfg,all_w8", [(TINY_QWEN2, False), (TINY_MEGA, True), (TINY_QWEN3, False)])
+def test_repack_cache_round_trip(tmp_path, cfg, all_w8):
+    """The packed device layout saved by one session and loaded by another gives
+    bit-identical logits (same kernels, same bytes); a file written for another
+    configuration, a truncated file and a late save are refused."""
+    blob, views = synthetic.make_f32_blob(cfg, 79)
+    fb, ib = synthetic.split_w8a32(cfg, views, lambda W: orc.quantize_per_channel(W, 8))
+    path = tmp_path / "model.b2pack"
+    a = ModelSession(cfg)
+    a.load_blobs("w8a32", fb, ib, all_linear_w8=all_w8, save_packed=path)
+    b = ModelSession(cfg)
+    b.load_packed(path)
+    assert a.uses_persistent_kernel() == b.uses_persistent_kernel()
+    for t in synthetic.prompt_tokens(cfg, 3, 8):
+        a.decode(int(t))
+        b.decode(int(t))
+        assert np.array_equal(a.logits_data(), b.logits_data())
+    with pytest.raises(RuntimeError):            # finalize has freed the per-projection buffers
+        _lib.check(a.lib.b200_model_save_packed(a._h, str(tmp_path / "late.b2pack").encode()))
+    other = TINY_QWEN3 if cfg is not TINY_QWEN3 else TINY_QWEN2
+    c = ModelSession(other)
+    with pytest.raises(RuntimeError):
+        _lib.check(c.lib.b200_model_load_packed(c._h, str(path).encode()))
+    cut = tmp_path / "cut.b2pack"
+    cut.write_bytes(path.read_bytes()[: path.stat().st_size // 2])
+    d = ModelSession(cfg)
+    with pytest.raises(RuntimeError):
+        _lib.check(d.lib.b200_model_load_packed(d._h, str(cut).encode()))
+    for s in (a, b, c, d):
+        s.close()
+
+
 def test_tiny_w4a16_reference_blobs():
     """The reference's int4 flavour (tools/buddy-codegen/gen_config.py:37-71): f16 blob +
     nibble-packed blob, signed per-channel int4 on o / gate / up / down / lm_head.  The

@@ -154,3 +154,29 @@ def test_model_against_huggingface_fixture(cfg, name):
         lo = om.decode(int(t))
         assert np.abs(lo - f["logits"][i]).max() / np.abs(f["logits"][i]).max() < 1e-4
         assert int(np.argmax(lo)) == int(np.argmax(f["logits"][i]))
+
+
+def test_w8a8_restatement_matches_a_stepwise_numpy_evaluation():
+    """frontend/Python/ops/linalg.py:12728-12846 written out once more with numpy f32 scalars:
+    scale = max(absmax * (1/127), 1e-10), q = clip(rint(x * (1/scale))), exact integer matmul,
+    float(acc) * (scale * wscale[n])."""
+    rng = np.random.default_rng(12)
+    A = (rng.standard_normal((5, 96)) * 2).astype(np.float32)
+    Q = rng.integers(-128, 128, (96, 40)).astype(np.int8)
+    ws = (rng.random(40).astype(np.float32) + np.float32(0.25)) * np.float32(0.02)
+    bias = rng.standard_normal(40).astype(np.float32)
+    f = np.float32
+    scale = max(f(np.abs(A).max()) * (f(1.0) / f(127.0)), f(1e-10))
+    inv = f(1.0) / f(scale)
+    q = np.clip(np.rint(A * inv), -128, 127).astype(np.int32)       # np.rint: ties to even
+    acc = q @ Q.astype(np.int32)
+    want = acc.astype(np.float32) * (f(scale) * ws)[None, :]
+    assert np.array_equal(orc.matmul_w8a8(A, Q, ws), want)
+    assert np.array_equal(orc.matmul_w8a8(A, Q, ws, bias), want + bias[None, :])
+    # ties: x * inv exactly halfway rounds to the even integer
+    A2 = np.zeros((1, 64), dtype=np.float32)
+    A2[0, 0], A2[0, 1], A2[0, 2] = 127.0, 2.5, 3.5
+    s2 = max(f(127.0) * (f(1.0) / f(127.0)), f(1e-10))
+    if f(2.5) * (f(1.0) / s2) == f(2.5):                               # only when the scale is exactly 1
+        got = orc.matmul_w8a8(A2, np.eye(64, dtype=np.int8), np.ones(64, dtype=np.float32))
+        assert got[0, 1] == f(2.0) * s2 and got[0, 2] == f(4.0) * s2
