@@ -82,10 +82,11 @@ class ModelSession:
         ib = np.fromfile(paths[1], dtype=np.int8) if len(paths) > 1 else None
         self.load_blobs(variant, fb, ib, all_linear_w8)
 
-    def load_tensors(self, views, quantize_to=None, group=0):
+    def load_tensors(self, views, quantize_to=None, group=0, save_packed=None):
         """Load from a {(name, layer): array} map of f32 tensors in the
         reference's [K,N] layout; quantize_to in (None, 'w8', 'w4') quantises
-        every linear layer on the device."""
+        every linear layer on the device.  save_packed: path of a repack-cache
+        file to write before finalising."""
         qt = {None: -1, "w8": _lib.W_I8, "w4": _lib.W_U4}[quantize_to]
         for name, layer, shape in tensor_list(self.cfg):
             a = np.ascontiguousarray(views[(name, layer)], dtype=np.float32)
@@ -104,6 +105,8 @@ class ModelSession:
                 a = np.ascontiguousarray(views[(name, layer)], dtype=np.float32)
                 _lib.check(self.lib.b200_model_set_vector(
                     self._h, layer, _SLOT[name], a.ctypes.data, a.size))
+        if save_packed is not None:
+            _lib.check(self.lib.b200_model_save_packed(self._h, str(save_packed).encode()))
         self.finalize()
 
     def set_linear_quantised(self, layer, name, kind, w, scale, scale_dtype, signed, K, N, group=0):

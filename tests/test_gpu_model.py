@@ -139,7 +139,7 @@ def test_load_weights_from_the_reference_blob_files(tmp_path):
     s.close()
 
 
-@pytest.mark.parametrize("cfg,all_w8", [(TINY_QWEN2, False), (TINY_MEGA, True), (TINY_QWEN3, False)])
+@pytest.mark.parametrize("cfg,all_w8", [(TINY_QWEN2, False), (TINY_MEGA, True), (TINY_QWEN3, "w4")])
 def test_repack_cache_round_trip(tmp_path, cfg, all_w8):
     """The packed device layout saved by one session and loaded by another gives
     bit-identical logits (same kernels, same bytes); a file written for another
@@ -148,7 +148,10 @@ def test_repack_cache_round_trip(tmp_path, cfg, all_w8):
     fb, ib = synthetic.split_w8a32(cfg, views, lambda W: orc.quantize_per_channel(W, 8))
     path = tmp_path / "model.b2pack"
     a = ModelSession(cfg)
-    a.load_blobs("w8a32", fb, ib, all_linear_w8=all_w8, save_packed=path)
+    if all_w8 == "w4":      # group-wise int4 with QK-norm vectors, from tensors
+        a.load_tensors(views, quantize_to="w4", group=64, save_packed=path)
+    else:
+        a.load_blobs("w8a32", fb, ib, all_linear_w8=all_w8, save_packed=path)
     b = ModelSession(cfg)
     b.load_packed(path)
     assert a.uses_persistent_kernel() == b.uses_persistent_kernel()
