@@ -136,6 +136,7 @@ def load():
                                        i64, vp, i64, C.POINTER(C.c_longlong), i32,
                                        C.POINTER(vp), vp]),
         "b200_forward_reset": (None, []),
+        "b200_forward_status": (i32, []),
         "b200_rax_open": (i32, [C.c_char_p, C.POINTER(vp)]),
         "b200_rax_close": (None, [vp]),
         "b200_rax_count": (i32, [vp]),

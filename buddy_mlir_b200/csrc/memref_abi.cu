@@ -562,6 +562,7 @@ void _mlir_ciface_buddy_gqa_decode_f32(b200_memref_f32_4 *result, b200_memref_f3
 // entries are stateless (every call receives the host KV cache), this one keeps
 // the cache on the device; `shadow` is a host copy of what the device cache
 // holds, row for row, and decides when the device copy may be trusted.
+extern "C++" {
 namespace {
 struct ForwardSession {
   b200_model *model = nullptr;
@@ -570,15 +571,26 @@ struct ForwardSession {
   int valid_rows = 0;                      // rows [0, valid_rows) of shadow == device cache
   std::vector<std::vector<float>> shadow;  // [2*layers][kv_heads*max_len*D]
   std::vector<float> rows;
+  std::vector<float> logits;
   bool failed = false;
 };
 ForwardSession g_fwd;
 std::mutex g_fwd_mu;
+std::atomic<int> g_fwd_status{0};   // first failure of the entry pair since the last reset (sticky)
+inline int note_status(int rc) {
+  if (rc != B200_OK) {
+    int expected = 0;
+    g_fwd_status.compare_exchange_strong(expected, rc);
+  }
+  return rc;
+}
 
 int session_for(ForwardSession &s, const b200_model_config *cfg, const char *variant,
                 int all_linear_w8, const void *w0, int64_t n0, const void *w1, int64_t n1) {
   // the blobs are the model: same addresses and same sampled contents = same session
-  uint64_t fp = fingerprint_bytes(w0, (size_t)n0 * 4, 0xCBF29CE484222325ull);
+  // n0 counts elements of the float blob: f16 in the w4a16 variant
+  const size_t e0 = !strcmp(variant, "w4a16") ? 2 : 4;
+  uint64_t fp = fingerprint_bytes(w0, (size_t)n0 * e0, 0xCBF29CE484222325ull);
   if (w1)
     fp = fingerprint_bytes(w1, (size_t)n1, fp);
   if (s.model && s.w0 == w0 && s.w1 == w1 && s.w_fingerprint == fp)
@@ -606,13 +618,35 @@ int session_for(ForwardSession &s, const b200_model_config *cfg, const char *var
   return B200_OK;
 }
 
+// Host-side element of the cache and the logits: float, or IEEE half as uint16_t (the
+// reference's f16 / w8a16 / w4a16 variants, tools/buddy-codegen/gen_config.py:37-49).
+// The device session and its shadow stay f32; half buffers are converted at the boundary.
+inline void to_host(float *dst, const float *src, size_t n) { memcpy(dst, src, n * 4); }
+inline void to_host(uint16_t *dst, const float *src, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    dst[i] = __half_as_ushort(__float2half_rn(src[i]));
+}
+inline void from_host(float *dst, const float *src, size_t n) { memcpy(dst, src, n * 4); }
+inline void from_host(float *dst, const uint16_t *src, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    dst[i] = __half2float(__ushort_as_half(src[i]));
+}
+inline bool same_row(const float *host, const float *shadow, size_t n) { return memcmp(host, shadow, n * 4) == 0; }
+inline bool same_row(const uint16_t *host, const float *shadow, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    if (host[i] != __half_as_ushort(__float2half_rn(shadow[i])))
+      return false;
+  return true;
+}
+
 // Does the host cache still hold, in rows [0, pos), what the device cache holds?
 // Row pos-1 of every buffer depends on every earlier token of the sequence, row
 // 0 and the middle row catch a rewritten or shifted cache
 // (handleKVCacheOverflow, gen_session.py:1471-1506): three rows per head and
 // buffer are compared bit for bit.
+template <typename T>
 bool host_matches_device(const ForwardSession &s, const b200_model_config *cfg,
-                         float *const *host_kv, long long pos) {
+                         T *const *host_kv, long long pos) {
   if (pos > s.valid_rows)
     return false;
   if (pos == 0)
@@ -623,23 +657,16 @@ bool host_matches_device(const ForwardSession &s, const b200_model_config *cfg,
     for (size_t h = 0; h < KH; ++h)
       for (long long r : probe) {
         const size_t off = (h * L + (size_t)r) * D;
-        if (memcmp(host_kv[b] + off, s.shadow[b].data() + off, D * 4) != 0)
+        if (!same_row(host_kv[b] + off, s.shadow[b].data() + off, D))
           return false;
       }
   return true;
 }
-} // namespace
 
-void b200_forward_reset(void) {
-  std::lock_guard<std::mutex> lock(g_fwd_mu);
-  b200_model_destroy(g_fwd.model);
-  g_fwd = ForwardSession();
-}
-
-int b200_forward_decode(const b200_model_config *cfg, const char *variant, int all_linear_w8,
-                        const void *w0, int64_t n0, const void *w1, int64_t n1,
-                        long long token, long long pos, float *const *host_kv,
-                        float **logits_out) {
+template <typename T>
+int forward_decode(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                   const void *w0, int64_t n0, const void *w1, int64_t n1,
+                   long long token, long long pos, T *const *host_kv, T **logits_out) {
   if (!cfg || !variant || !w0 || !host_kv || !logits_out)
     return fail(B200_EINVAL, "forward_decode: null argument");
   *logits_out = nullptr;
@@ -655,26 +682,28 @@ int b200_forward_decode(const b200_model_config *cfg, const char *variant, int a
     // hand-off from the host (CPU prefill, another sequence, a shifted cache):
     // everything before `pos` comes from host_kv
     for (int b = 0; b < nbuf; ++b) {
-      if (int rc = b200_model_kv_upload(s.model, b, host_kv[b], 0, (int)pos)) return rc;
       for (size_t h = 0; h < KH; ++h)
-        memcpy(s.shadow[b].data() + h * L * D, host_kv[b] + h * L * D, (size_t)pos * D * 4);
+        from_host(s.shadow[b].data() + h * L * D, host_kv[b] + h * L * D, (size_t)pos * D);
+      if (int rc = b200_model_kv_upload(s.model, b, s.shadow[b].data(), 0, (int)pos)) return rc;
     }
     s.valid_rows = (int)pos;
   }
-  float *logits = host_alloc<float>((size_t)cfg->vocab);
-  if (!logits)
-    return B200_ENOMEM;
-  int rc = b200_model_decode(s.model, (int)token, (int)pos, logits, nullptr);
+  std::vector<float> &lf = s.logits;
+  lf.resize((size_t)cfg->vocab);
+  int rc = b200_model_decode(s.model, (int)token, (int)pos, lf.data(), nullptr);
   if (!rc) rc = b200_model_read_new_kv_rows(s.model, s.rows.data());
   if (rc) {
-    std::free(logits);
     s.valid_rows = 0;
     return rc;
   }
+  T *logits = host_alloc<T>((size_t)cfg->vocab);
+  if (!logits)
+    return B200_ENOMEM;
+  to_host(logits, lf.data(), (size_t)cfg->vocab);
   for (int b = 0; b < nbuf; ++b)
     for (size_t h = 0; h < KH; ++h) {
       const float *row = &s.rows[((size_t)b * KH + h) * D];
-      memcpy(host_kv[b] + (h * L + (size_t)pos) * D, row, D * 4);
+      to_host(host_kv[b] + (h * L + (size_t)pos) * D, row, D);
       memcpy(s.shadow[b].data() + (h * L + (size_t)pos) * D, row, D * 4);
     }
   if (s.valid_rows < pos + 1)
@@ -683,10 +712,10 @@ int b200_forward_decode(const b200_model_config *cfg, const char *variant, int a
   return B200_OK;
 }
 
-int b200_forward_prefill(const b200_model_config *cfg, const char *variant, int all_linear_w8,
-                         const void *w0, int64_t n0, const void *w1, int64_t n1,
-                         const long long *tokens, int n_rows, float *const *host_kv_out,
-                         float *logits_out) {
+template <typename T>
+int forward_prefill(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                    const void *w0, int64_t n0, const void *w1, int64_t n1,
+                    const long long *tokens, int n_rows, T *const *host_kv_out, T *logits_out) {
   if (!cfg || !variant || !w0 || !tokens || !host_kv_out || !logits_out)
     return fail(B200_EINVAL, "forward_prefill: null argument");
   if (n_rows < 1 || n_rows > cfg->max_len)
@@ -707,19 +736,63 @@ int b200_forward_prefill(const b200_model_config *cfg, const char *variant, int 
     std::vector<int32_t> ids((size_t)n_rows);
     for (int i = 0; i < n_rows; ++i)
       ids[(size_t)i] = (int32_t)tokens[i];
-    if (int rc = b200_model_prefill(s.model, ids.data(), n_rows, 0, logits_out, 1, nullptr))
-      return rc;
+    if (sizeof(T) == 4) {
+      if (int rc = b200_model_prefill(s.model, ids.data(), n_rows, 0, reinterpret_cast<float *>(logits_out), 1, nullptr))
+        return rc;
+    } else {
+      std::vector<float> lf((size_t)n_rows * cfg->vocab);
+      if (int rc = b200_model_prefill(s.model, ids.data(), n_rows, 0, lf.data(), 1, nullptr))
+        return rc;
+      to_host(logits_out, lf.data(), lf.size());
+    }
   }
   for (int b = 0; b < nbuf; ++b) {
     if (int rc = b200_model_kv_download(s.model, b, s.shadow[b].data(), 0, n_rows)) return rc;
     for (size_t h = 0; h < KH; ++h) {
-      memcpy(host_kv_out[b] + h * L * D, s.shadow[b].data() + h * L * D, (size_t)n_rows * D * 4);
+      to_host(host_kv_out[b] + h * L * D, s.shadow[b].data() + h * L * D, (size_t)n_rows * D);
       if ((size_t)n_rows < L)   // rows the prefill did not reach read as zero
-        memset(host_kv_out[b] + (h * L + (size_t)n_rows) * D, 0, (L - (size_t)n_rows) * D * 4);
+        memset(host_kv_out[b] + (h * L + (size_t)n_rows) * D, 0, (L - (size_t)n_rows) * D * sizeof(T));
     }
   }
   s.valid_rows = n_rows;
   return B200_OK;
+}
+} // namespace
+} // extern "C++"
+
+void b200_forward_reset(void) {
+  std::lock_guard<std::mutex> lock(g_fwd_mu);
+  b200_model_destroy(g_fwd.model);
+  g_fwd = ForwardSession();
+  g_fwd_status.store(0);
+}
+
+int b200_forward_status(void) { return g_fwd_status.load(); }
+
+int b200_forward_decode(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                        const void *w0, int64_t n0, const void *w1, int64_t n1,
+                        long long token, long long pos, float *const *host_kv,
+                        float **logits_out) {
+  return note_status(forward_decode<float>(cfg, variant, all_linear_w8, w0, n0, w1, n1, token, pos, host_kv, logits_out));
+}
+int b200_forward_decode_f16(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                            const void *w0, int64_t n0, const void *w1, int64_t n1,
+                            long long token, long long pos, uint16_t *const *host_kv,
+                            uint16_t **logits_out) {
+  return note_status(forward_decode<uint16_t>(cfg, variant, all_linear_w8, w0, n0, w1, n1, token, pos, host_kv, logits_out));
+}
+int b200_forward_prefill(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                         const void *w0, int64_t n0, const void *w1, int64_t n1,
+                         const long long *tokens, int n_rows, float *const *host_kv_out,
+                         float *logits_out) {
+  return note_status(forward_prefill<float>(cfg, variant, all_linear_w8, w0, n0, w1, n1, tokens, n_rows, host_kv_out, logits_out));
+}
+int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                             const void *w0, int64_t n0, const void *w1, int64_t n1,
+                             const long long *tokens, int n_rows, uint16_t *const *host_kv_out,
+                             uint16_t *logits_out) {
+  return note_status(forward_prefill<uint16_t>(cfg, variant, all_linear_w8, w0, n0, w1, n1, tokens, n_rows, host_kv_out,
+                                   logits_out));
 }
 
 } // extern "C"

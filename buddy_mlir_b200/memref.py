@@ -15,7 +15,8 @@ _libc.free.argtypes = [C.c_void_p]
 
 _CT = {np.dtype(np.float32): C.c_float, np.dtype(np.float16): C.c_uint16,
        np.dtype(np.int8): C.c_int8, np.dtype(np.int64): C.c_longlong,
-       np.dtype(np.uint8): C.c_int8, np.dtype(np.uint64): C.c_size_t}
+       np.dtype(np.uint8): C.c_int8, np.dtype(np.uint64): C.c_size_t,
+       np.dtype(np.uint16): C.c_uint16}
 _cache = {}
 
 

@@ -31,10 +31,15 @@ class EntrySession:
         self.fn = self.dll._mlir_ciface_forward_decode
         self.fn.restype = None
         self.cfg = cfg
+        # host element of the cache and the logits: half (as uint16) for the f16-activation variants
+        self.half = variant == "w4a16"
+        self.ht = np.uint16 if self.half else np.float32
         self.blobs = [np.ascontiguousarray(b) for b in blobs]
+        if self.half:   # the f16 blob travels as the uint16 memref the reference's session builds
+            self.blobs[0] = self.blobs[0].view(np.uint16)
         self.blob_desc = [to_memref(b) for b in self.blobs]
         kvs = (1, cfg.kv_heads, cfg.max_len, cfg.head_dim)
-        self.kv = [np.zeros(kvs, dtype=np.float32) for _ in range(2 * cfg.n_layers)]
+        self.kv = [np.zeros(kvs, dtype=self.ht) for _ in range(2 * cfg.n_layers)]
         self.kv_desc = [to_memref(k) for k in self.kv]
         self.token = np.zeros((1, 1), dtype=np.int64)
         self.cache_position = np.zeros(1, dtype=np.int64)
@@ -42,7 +47,7 @@ class EntrySession:
         self.logits = np.zeros(cfg.vocab, dtype=np.float32)
         self.position_ = 0
         # DecodeABI: cache_position_out, kv0, kv1, (dummy_i, kv, kv)*, logits
-        I1, K4, L3 = memref_type(np.int64, 1), memref_type(np.float32, 4), memref_type(np.float32, 3)
+        I1, K4, L3 = memref_type(np.int64, 1), memref_type(self.ht, 4), memref_type(self.ht, 3)
         fields = [("cache_position_out", I1), ("kv0", K4), ("kv1", K4)]
         for i in range(cfg.n_layers - 1):
             fields += [(f"dummy{i}", I1), (f"kv{2 + 2 * i}", K4), (f"kv{3 + 2 * i}", K4)]
@@ -70,14 +75,13 @@ class EntrySession:
         toks = np.full((1, cfg.max_len), pad_id, dtype=np.uint64)
         toks[0, :len(prompt)] = np.asarray(prompt, dtype=np.uint64)
         tok_d = to_memref(toks)
-        K4, L3 = memref_type(np.float32, 4), memref_type(np.float32, 3)
+        K4, L3 = memref_type(self.ht, 4), memref_type(self.ht, 3)
         ABI = type("PrefillABI", (C.Structure,), {"_fields_": [("kv", K4 * (2 * cfg.n_layers)), ("logits", L3)]})
         result = ABI()
         self.prefill_fn(C.byref(result), *[C.byref(d) for d in self.blob_desc], C.byref(tok_d))
-        if not result.logits.aligned:
-            raise _lib.B200Error(_lib.load().b200_last_error().decode())
+        self._check()
         n = cfg.max_len * cfg.vocab
-        logits = np.array(np.ctypeslib.as_array(result.logits.aligned, shape=(n,)), copy=True)
+        logits = self._floats(np.array(np.ctypeslib.as_array(result.logits.aligned, shape=(n,)), copy=True))
         _libc.free(C.cast(result.logits.allocated, C.c_void_p))
         for i, k in enumerate(self.kv):
             src = np.ctypeslib.as_array(result.kv[i].aligned, shape=(k.size,))
@@ -95,17 +99,30 @@ class EntrySession:
             d[0] = self.position_
         result = self._result
         self.fn(*self._args)
-        if not result.logits.aligned:
-            raise _lib.B200Error(_lib.load().b200_last_error().decode())
         # gen_session.py:1416-1442: copy the logits out, KV results alias the state
         src = np.ctypeslib.as_array(result.logits.aligned, shape=(self.cfg.vocab,))
-        np.copyto(self.logits, src)
+        np.copyto(self.logits, self._floats(src))
         _libc.free(C.cast(result.logits.allocated, C.c_void_p))
+        self._check()
         if check_alias:
             for i, k in enumerate(self.kv):
                 got = getattr(result, f"kv{i}")
                 assert C.addressof(got.aligned.contents) == k.ctypes.data
         self.position_ += 1
+
+    def _floats(self, a):
+        """logitsFloat_ of the generated session (gen_session.py:1531: halfToFloat per element)."""
+        return a.view(np.float16).astype(np.float32) if self.half else a
+
+    def _check(self):
+        """The entries return void; the library keeps the first failure (b200_forward_status)."""
+        lib = _lib.load()
+        if lib.b200_forward_status() != 0:
+            raise _lib.B200Error(lib.b200_last_error().decode())
+
+    def kv_floats(self, i):
+        k = self.kv[i]
+        return k.view(np.float16).astype(np.float32) if self.half else k
 
     def reset_position(self):
         self.position_ = 0

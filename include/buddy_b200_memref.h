@@ -162,7 +162,28 @@ int b200_forward_prefill(const b200_model_config *cfg, const char *variant,
                          const void *w1, int64_t n1, const long long *tokens,
                          int n_rows, float *const *host_kv_out,
                          float *logits_out);
-/* Drop the session the two entries keep (weights, KV, graph). */
+/* The same two entries for the variants whose cache and logits are f16 on the
+ * host (w4a16: tools/buddy-codegen/gen_config.py:37-49; uint16_t holds the IEEE
+ * half bits, as in the reference's generated session).  The device session
+ * stays f32; rows and logits are rounded to half at the boundary, and the host
+ * cache check compares against the rounded rows. */
+int b200_forward_decode_f16(const b200_model_config *cfg, const char *variant,
+                            int all_linear_w8, const void *w0, int64_t n0,
+                            const void *w1, int64_t n1, long long token,
+                            long long pos, uint16_t *const *host_kv,
+                            uint16_t **logits_out);
+int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant,
+                             int all_linear_w8, const void *w0, int64_t n0,
+                             const void *w1, int64_t n1, const long long *tokens,
+                             int n_rows, uint16_t *const *host_kv_out,
+                             uint16_t *logits_out);
+/* The entry symbols return void, so a failure cannot be reported through them:
+ * the shim prints the reason, hands back zero-filled logits of the right shape
+ * (the reference caller copies from the buffer unconditionally,
+ * gen_session.py:1416-1418) and this code stays set -- the first failure since
+ * the last b200_forward_reset(), 0 if none; b200_last_error() has the text. */
+int b200_forward_status(void);
+/* Drop the session the two entries keep (weights, KV, graph) and the status. */
 void b200_forward_reset(void);
 
 #ifdef __cplusplus

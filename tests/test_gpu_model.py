@@ -208,6 +208,62 @@ def test_tiny_w4a16_reference_blobs():
     s.close()
 
 
+def test_w4a16_model_entries_with_half_cache_and_logits():
+    """The w4a16 shim: f16 blob, nibble-packed blob, KV cache and logits as IEEE half
+    (uint16) on the host, exactly the descriptor types the generated session uses for
+    this variant (tools/buddy-codegen/gen_config.py:37-71).  Prefill, then decode steps;
+    an overflow-style rewrite of the host cache is noticed through the rounded rows."""
+    cfg = TINY_QWEN2
+    _, views = synthetic.make_f32_blob(cfg, 80)
+    fb, ib = synthetic.split_w4a16(cfg, views, lambda W: orc.quantize_per_channel(W, 4))
+    rounded = {k: (v.astype(np.float16).astype(np.float32) if k[0] not in synthetic.QUANTISED_BY_REFERENCE else v)
+               for k, v in views.items()}
+    om = orc.OracleModel(cfg, rounded, kinds={n: "w4" for n in synthetic.QUANTISED_BY_REFERENCE})
+    es = EntrySession(cfg, "w4a16", [fb, ib])
+    assert es.kv[0].dtype == np.uint16
+    prompt = synthetic.prompt_tokens(cfg, 11, 10)
+    logits = es.prefill(prompt, pad_id=0)
+    for t in prompt:
+        want = om.decode(int(t))
+    assert maxrel(logits[len(prompt) - 1], want) < 2e-2
+    for b in range(2 * cfg.n_layers):
+        assert maxrel(es.kv_floats(b)[0, :, :len(prompt)], om.kv[b][:, :len(prompt)]) < 2e-2
+    tok = greedy_sample(want)
+    for _ in range(6):
+        es.decode(tok, check_alias=True)
+        want = om.decode(tok)
+        assert maxrel(es.logits, want) < 2e-2
+        if margin(want) > 2e-2 * float(np.abs(want).max()):
+            assert greedy_sample(es.logits) == greedy_sample(want)
+        tok = greedy_sample(want)
+    # the host rewrites its (half) cache, as handleKVCacheOverflow does: the next step must
+    # take the rows from the host again -- here: zeroed history, so the logits change
+    before = es.logits.copy()
+    for k in es.kv:
+        k[...] = 0
+    es.position_ -= 1
+    es.decode(tok)
+    assert not np.array_equal(es.logits, before)
+    es.close()
+
+
+def test_model_entry_failure_leaves_zero_logits_and_a_sticky_status():
+    """The entries return void: after a failure (here a position outside the cache) the
+    caller still gets a logits buffer it can copy from, all zeros, and the status stays
+    set until the session is reset."""
+    cfg = TINY_QWEN2
+    blob, _ = synthetic.make_f32_blob(cfg, 81)
+    es = EntrySession(cfg, "f32", [blob])
+    es.decode(3)
+    es.position_ = cfg.max_len + 5
+    with pytest.raises(RuntimeError):
+        es.decode(3)
+    assert np.array_equal(es.logits, np.zeros(cfg.vocab, dtype=np.float32))
+    assert _lib.load().b200_forward_status() != 0
+    es.close()
+    assert _lib.load().b200_forward_status() == 0
+
+
 def test_tiny_all_linear_w8_quantised_on_device():
     cfg = TINY_QWEN2
     blob, views = synthetic.make_f32_blob(cfg, 8)
