@@ -98,6 +98,7 @@ def load():
                                         i64, i32, i32]),
         "b200_model_load_blobs": (i32, [vp, C.c_char_p, vp, i64, vp, i64, i32]),
         "b200_model_save_packed": (i32, [vp, C.c_char_p]),
+        "b200_model_set_launch_counter": (i32, [vp, C.c_uint32]),
         "b200_model_load_packed": (i32, [vp, C.c_char_p]),
         "b200_blob_elements": (i32, [C.POINTER(ModelConfigC), C.c_char_p,
                                      C.POINTER(i64), C.POINTER(i64)]),

@@ -1961,6 +1961,21 @@ float *b200_model_kv_ptr(b200_model *m, int buffer) {
 }
 
 int b200_model_uses_persistent_kernel(const b200_model *m) { return m && m->mega ? 1 : 0; }
+// Diagnostic: move the persistent kernel's launch counter, the base of the 32-bit tags its
+// CTAs exchange activations under (tag = (launches + 1) * 8 * (layers + 3) + phase), so that
+// the wrap of the tag space (after 2^32 / (8 * (layers + 3)) launches, 17 million tokens for
+// 28 layers) can be crossed in a test instead of in the fifth hour of a server's life.
+int b200_model_set_launch_counter(b200_model *m, uint32_t launches) {
+  if (!m || !m->finalized)
+    return fail(B200_ESTATE, "set_launch_counter: a finalised model is required");
+  if (!m->mega)
+    return fail(B200_ESTATE, "set_launch_counter: the model does not run the persistent kernel");
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  m->h_state_pinned[4] = (int32_t)launches;
+  B200_CUDA(cudaMemcpyAsync(m->d_state + 4, m->h_state_pinned + 4, 4, cudaMemcpyHostToDevice, m->stream));
+  B200_CUDA(cudaStreamSynchronize(m->stream));
+  return B200_OK;
+}
 int b200_model_tp_sum_kind(const b200_model *m) {
   return !m || m->tp <= 1 ? 0 : (m->tp_push.ranks > 0 ? 2 : 1);
 }

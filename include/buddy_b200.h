@@ -381,6 +381,10 @@ int b200_model_kernels_per_step(const b200_model *m);
  * linear layer int8, one GPU); 0 when they replay the multi-kernel CUDA graph.
  * The environment variable BUDDY_B200_DECODE=graph forces the graph. */
 int b200_model_uses_persistent_kernel(const b200_model *m);
+/* Diagnostic: set the persistent kernel's launch counter (the base of the 32-bit
+ * tags its CTAs exchange activations under), e.g. just below the wrap of the tag
+ * space at 2^32 / (8 * (n_layers + 3)) launches, to cross it in a test. */
+int b200_model_set_launch_counter(b200_model *m, uint32_t launches);
 /* How the sums of a tensor-parallel model's row-parallel projections are formed:
  * 0 = single GPU, 1 = NCCL all-reduce, 2 = every rank's GEMV stores its partial
  * results straight into all ranks' staging buffers over NVLink (tagged pairs),

@@ -355,6 +355,33 @@ def test_persistent_kernel_matches_checker_and_graph_path(cfg, monkeypatch):
     g.close()
 
 
+def test_persistent_kernel_crosses_the_wrap_of_its_tag_space():
+    """The CTAs of the persistent kernel exchange activations under 32-bit tags numbered from
+    the launch counter; the counter is preset just below the point where the tags wrap
+    (2^32 / (8 * (layers + 3)) launches) and the steps across it must equal the checker's."""
+    cfg = TINY_MEGA
+    _, views = synthetic.make_f32_blob(cfg, 33)
+    om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in ALL_LINEAR})
+    s = ModelSession(cfg)
+    s.load_tensors(views, quantize_to="w8")
+    assert s.uses_persistent_kernel()
+    wrap = (1 << 32) // (8 * (cfg.n_layers + 3))
+    _lib.check(s.lib.b200_model_set_launch_counter(s._h, wrap - 4))
+    tok = 5
+    for i in range(10):                      # launches wrap-4 .. wrap+5
+        s.decode(tok)
+        want = om.decode(tok)
+        assert maxrel(s.logits_data(), want) < 1e-3, i
+        assert greedy_sample(s.logits_data()) == greedy_sample(want)
+        tok = greedy_sample(want)
+    ids = s.generate(tok, 6)                 # and the multi-step launch path
+    for t in ids:
+        want = om.decode(tok)
+        assert int(t) == greedy_sample(want)
+        tok = int(t)
+    s.close()
+
+
 # ---- prefill: all prompt rows in one pass (dense GEMMs) --------------------------------------
 @pytest.mark.parametrize("cfg,quant,n_prompt", [(TINY_MEGA, "w8", 40), (TINY_QWEN2, "w8", 40), (TINY_QWEN3, "w8", 40),
                                                 (TINY_QWEN2, None, 40), (TINY_MEGA, "w8", 93), (TINY_QWEN2, "w8", 77),
