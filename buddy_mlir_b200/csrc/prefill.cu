@@ -598,7 +598,7 @@ __global__ void __launch_bounds__(256)
 gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *part,
                        int kv_heads, int page, const int32_t *row_seq, const int32_t *row_pos,
                        const int32_t *block_table, int table_stride, int chunk) {
-  constexpr int D = VEC * 32, W = 8, U = 4;
+  constexpr int D = VEC * 32, W = 8;
   const int m = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int len = row_pos[m] + 1;
   const int j0 = sp * chunk;
@@ -608,13 +608,12 @@ gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int32_t *table = block_table + (int64_t)row_seq[m] * table_stride;
   const float scale = rsqrtf((float)D);
+  // the G query vectors of this kv head, shared by every lane (broadcast reads)
+  __shared__ __align__(16) float s_q[G][D];
   const float *qrow = qkv + (int64_t)m * ld + (int64_t)hk * G * D;
-  float qr[G][VEC];
-#pragma unroll
-  for (int g = 0; g < G; ++g)
-#pragma unroll
-    for (int e = 0; e < VEC; ++e)
-      qr[g][e] = qrow[g * D + lane * VEC + e];
+  for (int i = threadIdx.x; i < G * D; i += blockDim.x)
+    s_q[i / D][i % D] = qrow[i];
+  __syncthreads();
   float mx[G], l[G], acc[G][VEC];
 #pragma unroll
   for (int g = 0; g < G; ++g) {
@@ -624,58 +623,67 @@ gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const 
     for (int e = 0; e < VEC; ++e)
       acc[g][e] = 0.f;
   }
-  for (int jb = j0 + warp; jb < j1; jb += W * U) {
-    float kr[U][VEC], vr[U][VEC];
+  // A warp takes 32 keys at a time.  Scores: a lane owns one key and walks its K row (no
+  // cross-lane reduction per key); softmax over the 32 keys with two warp reductions per query
+  // head; values: a lane owns VEC dims, the 32 weights of a head arrive by shuffle.
+  for (int jb = j0 + warp * 32; jb < j1; jb += W * 32) {
+    const int j = jb + lane;
+    const bool live = j < j1;
+    int ridx = 0;     // row of the key inside the pool, in rows of D floats
+    if (live)
+      ridx = (table[j / page] * kv_heads + hk) * page + j % page;
+    const float *kp = k_pool + (int64_t)ridx * D;
+    float sc[G];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      const int j = jb + u * W;
-      if (j < j1) {
-        const int pg = table[j / page];
-        const int64_t crow = (((int64_t)pg * kv_heads + hk) * page + j % page) * D + lane * VEC;
-        if (VEC == 4) {
-          const float4 a = *reinterpret_cast<const float4 *>(k_pool + crow);
-          const float4 b = *reinterpret_cast<const float4 *>(v_pool + crow);
-          kr[u][0] = a.x; kr[u][1] = a.y; kr[u][2 % VEC] = a.z; kr[u][3 % VEC] = a.w;
-          vr[u][0] = b.x; vr[u][1] = b.y; vr[u][2 % VEC] = b.z; vr[u][3 % VEC] = b.w;
-        } else {
+    for (int g = 0; g < G; ++g)
+      sc[g] = 0.f;
+    if (live) {
+#pragma unroll 4
+      for (int d = 0; d < D; d += 4) {
+        const float4 k4 = *reinterpret_cast<const float4 *>(kp + d);
 #pragma unroll
-          for (int e = 0; e < VEC; ++e) {
-            kr[u][e] = k_pool[crow + e];
-            vr[u][e] = v_pool[crow + e];
-          }
+        for (int g = 0; g < G; ++g) {
+          const float4 q4 = *reinterpret_cast<const float4 *>(&s_q[g][d]);
+          sc[g] = fmaf(q4.x, k4.x, sc[g]);
+          sc[g] = fmaf(q4.y, k4.y, sc[g]);
+          sc[g] = fmaf(q4.z, k4.z, sc[g]);
+          sc[g] = fmaf(q4.w, k4.w, sc[g]);
         }
       }
     }
+    float pw[G];
 #pragma unroll
-    for (int u = 0; u < U; ++u) {
-      if (jb + u * W >= j1)
-        break;
-      float s[G];
+    for (int g = 0; g < G; ++g) {
+      const float sv = live ? sc[g] * scale : kSeed;
+      const float nm = fmaxf(mx[g], warp_max(sv));
+      // fast exponentials (2^-21 relative): the scan is bound by instruction issue
+      const float alpha = __expf(mx[g] - nm);
+      pw[g] = live ? __expf(sv - nm) : 0.f;
+      l[g] = fmaf(l[g], alpha, warp_sum(pw[g]));
+      mx[g] = nm;
 #pragma unroll
-      for (int g = 0; g < G; ++g) {
-        float d = 0.f;
+      for (int e = 0; e < VEC; ++e)
+        acc[g][e] *= alpha;
+    }
+    const int nk = min(32, j1 - jb);
+    for (int t = 0; t < nk; ++t) {
+      const int rt = __shfl_sync(0xffffffffu, ridx, t);
+      const float *vp = v_pool + (int64_t)rt * D + lane * VEC;
+      float vr[VEC];
+      if (VEC == 4) {
+        const float4 b = *reinterpret_cast<const float4 *>(vp);
+        vr[0] = b.x; vr[1] = b.y; vr[2 % VEC] = b.z; vr[3 % VEC] = b.w;
+      } else {
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
-          d = fmaf(qr[g][e], kr[u][e], d);
-        s[g] = d;
+          vr[e] = vp[e];
       }
 #pragma unroll
-      for (int o = 16; o > 0; o >>= 1)
-#pragma unroll
-        for (int g = 0; g < G; ++g)
-          s[g] += __shfl_xor_sync(0xffffffffu, s[g], o);
-#pragma unroll
       for (int g = 0; g < G; ++g) {
-        s[g] *= scale;
-        const float nm = fmaxf(mx[g], s[g]);
-        // fast exponentials (2^-21 relative): the scan is bound by instruction issue
-        const float alpha = __expf(mx[g] - nm);
-        const float pw = __expf(s[g] - nm);
-        l[g] = fmaf(l[g], alpha, pw);
+        const float pt = __shfl_sync(0xffffffffu, pw[g], t);
 #pragma unroll
         for (int e = 0; e < VEC; ++e)
-          acc[g][e] = fmaf(acc[g][e], alpha, pw * vr[u][e]);
-        mx[g] = nm;
+          acc[g][e] = fmaf(pt, vr[e], acc[g][e]);
       }
     }
   }
