@@ -140,8 +140,8 @@ int rope_kv_paged_launch(float *qkv, int64_t ld, float *k_pool, float *v_pool, c
                          int table_stride, int M, cudaStream_t st);
 int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out, int64_t ldo,
                      int q_heads, int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
-                     const int32_t *block_table, int table_stride, int M, float *scratch, int max_context,
-                     cudaStream_t st);
+                     const int32_t *block_table, int table_stride, int M, float *scratch, int scratch_rows,
+                     int max_context, cudaStream_t st);
 int gqa_paged_prefill_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out,
                              int64_t ldo, int q_heads, int kv_heads, int D, int page, const int32_t *seq_table,
                              int pos0, int M, int max_context, cudaStream_t st);

@@ -1789,8 +1789,8 @@ static int batch_rows(b200_batch *b, int M, const int32_t *tokens, const int32_t
                                      b->max_context, st);
     if (arc == B200_ESTATE)
       arc = gqa_paged_launch(m->pf_qkv, QKV, b->pool[2 * l], b->pool[2 * l + 1], m->pf_att, QD, m->qh, m->kvh, D,
-                             b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M,
-                             M <= b->part_rows ? b->d_part : nullptr, b->max_context, st);
+                             b->page, b->d_seq, b->d_pos, b->d_table, b->table_stride, M, b->d_part, b->part_rows,
+                             b->max_context, st);
     if (arc)
       return arc;
     if (int rc = linear_rows(m, L.o, m->pf_att, QD, M, m->pf_x, H, m->pf_x, nullptr, false)) return rc;
@@ -1853,6 +1853,8 @@ int b200_batch_create(b200_model *m, int max_seqs, int page_size, int n_pages, i
   if (rc == B200_OK)
     rc = dev_alloc((void **)&b->d_part,
                    (size_t)gqa_paged_scratch_floats(b->part_rows, m->qh, m->cfg.head_dim, b->max_context) * 4);
+  if (rc == B200_OK && cudaMemset(b->d_part, 0, (size_t)b->part_rows * m->qh * 4) != cudaSuccess)   // the counters
+    rc = fail(B200_ECUDA, "batch_create: cudaMemset failed");
   if (rc != B200_OK) {
     b200_batch_destroy(b);
     return rc;

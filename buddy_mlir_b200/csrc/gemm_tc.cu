@@ -332,7 +332,8 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
     const int n0h = n0 + h * BN;
     if (h > 0)   // the staging tile is free again once the previous half has been stored
       asm volatile("bar.sync 1, %0;" ::"n"(kEpiWarps * 32) : "memory");
-    if (ok && n0h < p.N) {
+    // rows of the tile beyond M hold nothing: warps whose 32 lanes are all dead skip the read
+    if (ok && n0h < p.N && (warp & 3) * 32 < p.M - m0) {
       asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
       // a warp reads the 32 lanes of tensor memory that match its rank within its warpgroup;
       // the two warps that share a lane quarter take half the columns each
@@ -420,7 +421,7 @@ gemm_w8_tc_kernel(const __grid_constant__ CUtensorMap map_hi, const __grid_const
         cols = min(BN, p.N - n0h);
       }
       const float *res = (p.residual && p.splits == 1 && !p.silu_pairs) ? p.residual + (int64_t)m0 * p.ldr + n0h + p.n_off : nullptr;
-      const int rows = p.splits > 1 ? BM : min(BM, p.M - m0);
+      const int rows = min(BM, p.M - m0);
       // 16-byte stores when the destination rows allow it
       const bool v4 = (ldd & 3) == 0 && ((uintptr_t)dst & 15) == 0 && (cols & 3) == 0 &&
                       (!res || ((p.ldr & 3) == 0 && ((uintptr_t)res & 15) == 0));

@@ -587,8 +587,8 @@ int launch_paged_attn(const float *qkv, int64_t ld, const float *kp, const float
 // The same scan for few rows with long histories (batched decode): the keys of a row
 // are cut into chunks of `chunk` positions (paged_chunk(): an eighth of the longest
 // context, 32..256), one CTA of 8 warps per (row, kv head, chunk); a warp owns every 8th key of the chunk and keeps four K/V rows in flight.
-// Partials (m, l, acc[D]) per query head go to `part`; gqa_paged_combine_kernel folds
-// the chunks of a row in chunk order.
+// Partials (m, l, acc[D]) per query head go to `part`; the CTA that finishes a row's last
+// chunk folds them in chunk order.
 __host__ __device__ inline int paged_chunk(int max_context) {
   const int c = ((max_context + 7) / 8 + 31) / 32 * 32;
   return c < 32 ? 32 : (c > 256 ? 256 : c);
@@ -597,7 +597,8 @@ template <int G, int VEC>
 __global__ void __launch_bounds__(256)
 gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *part,
                        int kv_heads, int page, const int32_t *row_seq, const int32_t *row_pos,
-                       const int32_t *block_table, int table_stride, int chunk) {
+                       const int32_t *block_table, int table_stride, int chunk, int *counters, float *out,
+                       int64_t ldo) {
   constexpr int D = VEC * 32, W = 8;
   const int m = blockIdx.x, hk = blockIdx.y, sp = blockIdx.z;
   const int len = row_pos[m] + 1;
@@ -720,26 +721,35 @@ gqa_paged_split_kernel(const float *qkv, int64_t ld, const float *k_pool, const 
       pout[g * (D + 2) + 1] = L;
     }
   }
-}
-
-template <int G, int D>
-__global__ void __launch_bounds__(128)
-gqa_paged_combine_kernel(const float *part, float *out, int64_t ldo, int kv_heads, int chunks,
-                         const int32_t *row_pos, int chunk) {
-  const int m = blockIdx.x, hk = blockIdx.y;
-  const int n = (row_pos[m] + chunk) / chunk;   // chunks that hold keys of this row
-  const float *pin = part + (((int64_t)m * kv_heads + hk) * chunks) * G * (D + 2);
+  // The CTA that finishes a row's last chunk folds the chunks in chunk order (the counter
+  // returns to zero for the next launch).
+  const int n = (len + chunk - 1) / chunk;     // chunks that hold keys of this row
+  __shared__ int s_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    int *cnt = counters + m * kv_heads + hk;
+    const int prev = atomicAdd(cnt, 1);
+    s_last = prev == n - 1;
+    if (s_last)
+      *cnt = 0;
+  }
+  __syncthreads();
+  if (!s_last)
+    return;
+  __threadfence();
+  const float *pin = part + (((int64_t)m * kv_heads + hk) * gridDim.z) * G * (D + 2);
   for (int idx = threadIdx.x; idx < G * D; idx += blockDim.x) {
     const int g = idx / D, d = idx - g * D;
     float M = kSeed;
     for (int c = 0; c < n; ++c)
-      M = fmaxf(M, pin[(int64_t)(c * G + g) * (D + 2)]);
+      M = fmaxf(M, __ldcg(pin + (int64_t)(c * G + g) * (D + 2)));
     float L = 0.f, A = 0.f;
     for (int c = 0; c < n; ++c) {
       const float *q = pin + (int64_t)(c * G + g) * (D + 2);
-      const float b = expf(q[0] - M);
-      L = fmaf(q[1], b, L);
-      A = fmaf(q[2 + d], b, A);
+      const float b = expf(__ldcg(q) - M);
+      L = fmaf(__ldcg(q + 1), b, L);
+      A = fmaf(__ldcg(q + 2 + d), b, A);
     }
     out[(int64_t)m * ldo + (int64_t)(hk * G + g) * D + d] = __fdiv_rn(A, L);
   }
@@ -748,20 +758,15 @@ gqa_paged_combine_kernel(const float *part, float *out, int64_t ldo, int kv_head
 template <int G>
 int launch_paged_split(const float *qkv, int64_t ld, const float *kp, const float *vp, float *out, int64_t ldo,
                        int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
-                       const int32_t *block_table, int table_stride, int M, float *part, int chunks, int chunk,
-                       cudaStream_t st) {
-  dim3 grid(M, kv_heads, chunks), cgrid(M, kv_heads);
-  if (D == 128) {
+                       const int32_t *block_table, int table_stride, int M, float *part, int *counters, int chunks,
+                       int chunk, cudaStream_t st) {
+  dim3 grid(M, kv_heads, chunks);
+  if (D == 128)
     gqa_paged_split_kernel<G, 4><<<grid, 256, 0, st>>>(qkv, ld, kp, vp, part, kv_heads, page, row_seq, row_pos,
-                                                       block_table, table_stride, chunk);
-    B200_LAUNCH_CHECK();
-    gqa_paged_combine_kernel<G, 128><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos, chunk);
-  } else {
+                                                       block_table, table_stride, chunk, counters, out, ldo);
+  else
     gqa_paged_split_kernel<G, 2><<<grid, 256, 0, st>>>(qkv, ld, kp, vp, part, kv_heads, page, row_seq, row_pos,
-                                                       block_table, table_stride, chunk);
-    B200_LAUNCH_CHECK();
-    gqa_paged_combine_kernel<G, 64><<<cgrid, 128, 0, st>>>(part, out, ldo, kv_heads, chunks, row_pos, chunk);
-  }
+                                                       block_table, table_stride, chunk, counters, out, ldo);
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
@@ -821,27 +826,31 @@ int rope_kv_paged_launch(float *qkv, int64_t ld, float *k_pool, float *v_pool, c
 int64_t gqa_paged_scratch_floats(int rows, int q_heads, int D, int max_context) {
   const int chunk = paged_chunk(max_context);
   const int chunks = (max_context + chunk - 1) / chunk;
-  return (int64_t)rows * chunks * q_heads * (D + 2);
+  // one completion counter per (row, kv head) in front (zero between launches), then the partials
+  return (int64_t)rows * q_heads + (int64_t)rows * chunks * q_heads * (D + 2);
 }
 
-// scratch: gqa_paged_scratch_floats(M, ..) floats, or null (then, and for more than
-// kPagedSplitRows rows, every row is scanned by one CTA)
+// scratch: gqa_paged_scratch_floats(scratch_rows, ..) floats whose first scratch_rows * q_heads
+// words are zero, or null (then, and for more than scratch_rows or kPagedSplitRows rows, every
+// row is scanned by one CTA)
 int gqa_paged_launch(const float *qkv, int64_t ld, const float *k_pool, const float *v_pool, float *out, int64_t ldo,
                      int q_heads, int kv_heads, int D, int page, const int32_t *row_seq, const int32_t *row_pos,
-                     const int32_t *block_table, int table_stride, int M, float *scratch, int max_context,
-                     cudaStream_t st) {
+                     const int32_t *block_table, int table_stride, int M, float *scratch, int scratch_rows,
+                     int max_context, cudaStream_t st) {
   if (D != 64 && D != 128)
     return fail(B200_EINVAL, "gqa_paged: head_dim %d (64 or 128 supported)", D);
   constexpr int kPagedSplitRows = 256;
   const int chunk = paged_chunk(max_context);
-  const bool split = scratch != nullptr && M <= kPagedSplitRows && max_context > chunk;
+  const bool split = scratch != nullptr && M <= scratch_rows && M <= kPagedSplitRows && max_context > chunk;
+  int *counters = reinterpret_cast<int *>(scratch);
+  float *part = scratch ? scratch + (int64_t)scratch_rows * q_heads : nullptr;
   const int chunks = (max_context + chunk - 1) / chunk;
   switch (q_heads / kv_heads) {
 #define B200_G(G_)                                                                                          \
   case G_:                                                                                                  \
     if (split)                                                                                              \
       return launch_paged_split<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos, \
-                                    block_table, table_stride, M, scratch, chunks, chunk, st);              \
+                                    block_table, table_stride, M, part, counters, chunks, chunk, st);       \
     return launch_paged_attn<G_>(qkv, ld, k_pool, v_pool, out, ldo, kv_heads, D, page, row_seq, row_pos,    \
                                  block_table, table_stride, M, st);
     B200_G(1) B200_G(2) B200_G(3) B200_G(4) B200_G(6) B200_G(8)
