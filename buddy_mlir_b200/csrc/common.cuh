@@ -75,6 +75,12 @@ __device__ __forceinline__ void tagged_store(uint2 *p, float v, uint32_t tag) {
                "r"(tag)
                : "memory");
 }
+// two neighbouring pairs in one 16-byte store (p 16-byte aligned): half the packets on the link
+__device__ __forceinline__ void tagged_store2(uint2 *p, float v0, float v1, uint32_t tag) {
+  asm volatile("st.volatile.global.v4.u32 [%0], {%1, %2, %3, %4};" ::"l"(p), "r"(__float_as_uint(v0)), "r"(tag),
+               "r"(__float_as_uint(v1)), "r"(tag)
+               : "memory");
+}
 __device__ __forceinline__ uint2 tagged_load(const uint2 *p) {
   uint2 v;
   asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");

@@ -786,6 +786,68 @@ quantize_activations_kernel(const float *A, int64_t lda, int M, int K, const uin
   }
 }
 
+// The same split with a warp per row (eight rows per CTA) for aligned rows of up to 2048
+// elements: the row is read once and stays in registers between the RMSNorm statistics and
+// the conversion, and nothing waits on a CTA barrier.
+template <int NV>   // float4 per lane: K <= 128 * NV
+__global__ void __launch_bounds__(256)
+split_activations_warp_kernel(const float *A, int64_t lda, int M, int K, const float *norm_w, float eps,
+                              __nv_bfloat16 *hi, __nv_bfloat16 *lo) {
+  const int lane = threadIdx.x & 31;
+  const int m = blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (m >= M)
+    return;
+  const float *arow = A + (int64_t)m * lda;
+  float4 v[NV];
+  float ss = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (i * 32 + lane) * 4;
+    v[i] = k < K ? *reinterpret_cast<const float4 *>(arow + k) : make_float4(0.f, 0.f, 0.f, 0.f);
+  }
+  float r = 1.f;
+  if (norm_w != nullptr) {
+    // the statistics in the order of the CTA-per-row kernel would differ in rounding only; both
+    // stay far inside the tolerance of the contraction that follows
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      ss += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
+    ss = warp_sum(ss);
+    r = rsqrtf(__fadd_rn(__fmul_rn(ss, 1.0f / (float)K), eps));
+  }
+  uint2 *hrow = reinterpret_cast<uint2 *>(hi + (int64_t)m * K), *lrow = reinterpret_cast<uint2 *>(lo + (int64_t)m * K);
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int k = (i * 32 + lane) * 4;
+    if (k >= K)
+      break;
+    float a[4] = {v[i].x, v[i].y, v[i].z, v[i].w};
+    if (norm_w != nullptr) {
+      const float4 w4 = *reinterpret_cast<const float4 *>(norm_w + k);
+      a[0] = __fmul_rn(w4.x, __fmul_rn(a[0], r));
+      a[1] = __fmul_rn(w4.y, __fmul_rn(a[1], r));
+      a[2] = __fmul_rn(w4.z, __fmul_rn(a[2], r));
+      a[3] = __fmul_rn(w4.w, __fmul_rn(a[3], r));
+    }
+    uint32_t hb[4], lb[4];
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const __nv_bfloat16 h = __float2bfloat16_rn(a[e]);
+      hb[e] = __bfloat16_as_ushort(h);
+      lb[e] = __bfloat16_as_ushort(__float2bfloat16_rn(a[e] - __bfloat162float(h)));
+    }
+    int64_t pos;
+    if ((k | 511) < (K & ~511)) {
+      const int kk = k & 511;
+      pos = (k & ~511) + ((kk & 127) >> 2) * 16 + (kk >> 7) * 4;
+    } else {
+      pos = packed_offset(B200_W_I8, K, k, nullptr);
+    }
+    hrow[pos >> 2] = make_uint2(hb[0] | (hb[1] << 16), hb[2] | (hb[3] << 16));
+    lrow[pos >> 2] = make_uint2(lb[0] | (lb[1] << 16), lb[2] | (lb[3] << 16));
+  }
+}
+
 using EncodeFn = CUresult (*)(CUtensorMap *, CUtensorMapDataType, cuuint32_t, void *, const cuuint64_t *,
                               const cuuint64_t *, const cuuint32_t *, const cuuint32_t *, CUtensorMapInterleave,
                               CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
@@ -906,7 +968,14 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   B200_CUDA(cudaMemsetAsync(err, 0, 4, st));
   // rows M..Mp of the last tile are never written: the tensor maps end at row M and the TMA
   // unit fills what lies beyond with zeros
-  split_activations_kernel<<<M, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
+  const bool warp_rows = (K & 3) == 0 && (lda & 3) == 0 && ((uintptr_t)A & 15) == 0 && K <= 2048 &&
+                         (!norm_weight || ((uintptr_t)norm_weight & 15) == 0);
+  if (warp_rows && K <= 1536)
+    split_activations_warp_kernel<12><<<(M + 7) / 8, 256, 0, st>>>(A, lda, M, K, norm_weight, norm_eps, hi, lo);
+  else if (warp_rows)
+    split_activations_warp_kernel<16><<<(M + 7) / 8, 256, 0, st>>>(A, lda, M, K, norm_weight, norm_eps, hi, lo);
+  else
+    split_activations_kernel<<<M, 256, 0, st>>>(A, lda, M, K, K, norm_weight, norm_eps, hi, lo);
   B200_LAUNCH_CHECK();
   GemmParams p{};
   p.M = M;

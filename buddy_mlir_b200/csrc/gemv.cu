@@ -128,6 +128,7 @@ gemv_kernel(const GemvP p) {
   extern __shared__ __align__(16) float xs[];  // [MT][kc]
   float *c4 = xs + (size_t)MT * p.kc;   // in_place4: zero-point terms, one per 4 activations
   __shared__ float s_red[8 * 16];
+  __shared__ float s_push[8 * 4];   // tensor-parallel push: the CTA's row sums of one iteration
   __shared__ float s_rinv[16];
 
   using DQ = Dequant<KIND>;
@@ -406,25 +407,43 @@ gemv_kernel(const GemvP p) {
     }
 
     if (p.push.ranks > 0) {
-      // This rank's share of a tensor-parallel sum (M = 1).  Every lane holds the row sums
-      // after the shuffle reduction: lane t stores them to rank t's staging buffer, so one
-      // store instruction per row reaches all peers (plain 8-byte stores over NVLink).
+      // This rank's share of a tensor-parallel sum (M = 1).  The CTA's warps hold the sums of
+      // nwarps * R consecutive rows: they are gathered in shared memory and sent to every
+      // rank's staging buffer as 16-byte stores of two (value, tag) pairs (plain stores over
+      // NVLink): a thread serves one peer and two rows, so the CTA's rows reach a peer as one
+      // contiguous run instead of one 8-byte packet per row.
       const uint32_t seq = (uint32_t)(*p.push.step) * p.push.per_step + p.push.index;
-      if (lane < p.push.ranks) {
-        uint2 *dst = p.push.peer[lane] + ((size_t)(seq % kTpRegions) * p.push.ranks + p.push.rank) * p.push.H;
+      if (lane == 0) {
 #pragma unroll
         for (int r = 0; r < R; ++r) {
           const int64_t row = row0 + r;
-          if (row >= p.N)
-            continue;
           float v = acc[r][0];
-          if (!GROUPED && p.scale != nullptr)
-            v = v * load_as_float(p.scale, p.scale_dtype, row);
-          if (p.bias != nullptr)
-            v = p.bias[row] + v;
-          tagged_store(dst + row, v, seq + 1u);
+          if (row < p.N) {
+            if (!GROUPED && p.scale != nullptr)
+              v = v * load_as_float(p.scale, p.scale_dtype, row);
+            if (p.bias != nullptr)
+              v = p.bias[row] + v;
+          }
+          s_push[warp * R + r] = v;
         }
       }
+      __syncthreads();
+      const int rows_cta = nwarps * R;               // even: R >= 2 or an even number of warps
+      const int units = (rows_cta + 1) / 2;          // 16-byte units per peer
+      if ((int)threadIdx.x < p.push.ranks * units) {
+        const int peer = threadIdx.x / units, u = threadIdx.x - peer * units;
+        const int64_t row = base + 2 * u;
+        uint2 *dst = p.push.peer[peer] + ((size_t)(seq % kTpRegions) * p.push.ranks + p.push.rank) * p.push.H;
+        if (row + 1 < p.N && 2 * u + 1 < rows_cta && ((reinterpret_cast<uintptr_t>(dst + row) & 15) == 0))
+          tagged_store2(dst + row, s_push[2 * u], s_push[2 * u + 1], seq + 1u);
+        else {
+          if (row < p.N)
+            tagged_store(dst + row, s_push[2 * u], seq + 1u);
+          if (row + 1 < p.N && 2 * u + 1 < rows_cta)
+            tagged_store(dst + row + 1, s_push[2 * u + 1], seq + 1u);
+        }
+      }
+      __syncthreads();
     } else if (lane == 0) {
 #pragma unroll
       for (int r = 0; r < R; ++r) {

@@ -20,6 +20,7 @@
 // BUDDY_B200_ALL_LINEAR_W8=1 quantises every linear layer of an f32 blob on
 // the device.  Prompts are token ids separated by spaces unless
 // BUDDY_B200_TOKENIZER=deepseek_r1 asks for the reference's tokenizer.
+// BUDDY_B200_PACK_CACHE=<file> keeps the packed device layout of the weights on disk.
 #include "buddy/runtime/core/InferenceRunner.h"
 #include "buddy/runtime/llm/TextGeneration.h"
 
@@ -99,10 +100,23 @@ public:
   }
   ~B200Session() override { b200_model_destroy(model_); }
 
-  // gen_session.py:1301-1338: one file per weight blob, in the variant's order
+  // gen_session.py:1301-1338: one file per weight blob, in the variant's order.
+  // BUDDY_B200_PACK_CACHE=<file>: the packed device layout is read from that file when it
+  // exists (no blob walk, no quantisation) and written there after the first load.
   void loadWeights(const std::vector<std::string> &paths) override {
     if (paths.empty() || paths.size() > 2)
       throw std::runtime_error("[buddy_b200] one (f32) or two (w8a32) weight files expected");
+    const char *cache = std::getenv("BUDDY_B200_PACK_CACHE");
+    if (cache && std::ifstream(cache).good()) {
+      if (b200_model_load_packed(model_, cache) == 0) {
+        check(b200_model_finalize(model_), "finalize");
+        return;
+      }
+      std::cerr << "[buddy_b200] ignoring the pack cache: " << b200_last_error() << "\n";
+      b200_model_destroy(model_);           // a partly filled model: start again from the blobs
+      model_ = nullptr;
+      check(b200_model_create(&cfg_, &model_), "model_create");
+    }
     const std::vector<float> fb = read_file<float>(paths[0]);
     const char *all = std::getenv("BUDDY_B200_ALL_LINEAR_W8");
     if (paths.size() == 1) {
@@ -113,6 +127,8 @@ public:
       check(b200_model_load_blobs(model_, "w8a32", fb.data(), (int64_t)fb.size(), ib.data(), (int64_t)ib.size(), 0),
             "load_blobs(w8a32)");
     }
+    if (cache && b200_model_save_packed(model_, cache) != 0)
+      std::cerr << "[buddy_b200] the pack cache was not written: " << b200_last_error() << "\n";
     check(b200_model_finalize(model_), "finalize");
   }
 

@@ -47,10 +47,14 @@ def test_runner_plugin_generates_the_checkers_tokens(tmp_path, variant):
     want = [greedy_sample(logits)]
     for _ in range(12):
         want.append(greedy_sample(om.decode(want[-1])))
-    env = dict(os.environ, BUDDY_B200_MODEL="tiny_qwen2")
-    out = subprocess.run([HOST, PLUGIN, weights, str(vocab), str(max_new), " ".join(str(int(t)) for t in prompt)],
-                         env=env, capture_output=True, text=True, timeout=300)
-    assert out.returncode == 0, out.stderr[-2000:]
-    line = [l for l in out.stdout.splitlines() if l.startswith("[ids] ")][-1]
-    got = [int(x) for x in line[len("[ids] "):].split()]
-    assert got == want
+    # the first run walks the blobs and writes the pack cache, the second one loads it
+    cache = tmp_path / "weights.b2pack"
+    env = dict(os.environ, BUDDY_B200_MODEL="tiny_qwen2", BUDDY_B200_PACK_CACHE=str(cache))
+    for run in range(2):
+        out = subprocess.run([HOST, PLUGIN, weights, str(vocab), str(max_new), " ".join(str(int(t)) for t in prompt)],
+                             env=env, capture_output=True, text=True, timeout=300)
+        assert out.returncode == 0, out.stderr[-2000:]
+        line = [l for l in out.stdout.splitlines() if l.startswith("[ids] ")][-1]
+        got = [int(x) for x in line[len("[ids] "):].split()]
+        assert got == want, run
+        assert cache.exists() and "pack cache" not in out.stderr
