@@ -968,7 +968,8 @@ int b200_gemm_w8(const b200_weight *w, const float *A, int M, int64_t lda, float
   B200_CUDA(cudaMemsetAsync(err, 0, 4, st));
   // rows M..Mp of the last tile are never written: the tensor maps end at row M and the TMA
   // unit fills what lies beyond with zeros
-  const bool warp_rows = (K & 3) == 0 && (lda & 3) == 0 && ((uintptr_t)A & 15) == 0 && K <= 2048 &&
+  // many rows: a warp per row (less work per row); few rows: a CTA per row (more threads on the few)
+  const bool warp_rows = M >= 512 && (K & 3) == 0 && (lda & 3) == 0 && ((uintptr_t)A & 15) == 0 && K <= 2048 &&
                          (!norm_weight || ((uintptr_t)norm_weight & 15) == 0);
   if (warp_rows && K <= 1536)
     split_activations_warp_kernel<12><<<(M + 7) / 8, 256, 0, st>>>(A, lda, M, K, norm_weight, norm_eps, hi, lo);
