@@ -103,12 +103,21 @@ __global__ void tp_reduce_add_kernel(float *x, const uint2 *buf, int H, int rank
   const uint32_t seq = (uint32_t)(*step) * per_step + index, tag = seq + 1u;
   const uint2 *src = buf + (size_t)(seq % kTpRegions) * ranks * H + n;
   float sum = x[n];
-  for (int r = 0; r < ranks; ++r) {
-    const uint2 *p = src + (size_t)r * H;
-    uint2 v = tagged_load(p);
-    if (v.y != tag) {
+  // every rank's slot is requested before the first one is looked at: the loads overlap instead
+  // of costing one memory round trip per rank
+  uint2 v[kTpMaxRanks];
+#pragma unroll
+  for (int r = 0; r < kTpMaxRanks; ++r)
+    if (r < ranks)
+      v[r] = tagged_load(src + (size_t)r * H);
+#pragma unroll
+  for (int r = 0; r < kTpMaxRanks; ++r) {
+    if (r >= ranks)
+      break;
+    if (v[r].y != tag) {
+      const uint2 *p = src + (size_t)r * H;
       unsigned long long t0 = 0;
-      for (uint32_t it = 1; v.y != tag; ++it) {
+      for (uint32_t it = 1; v[r].y != tag; ++it) {
         if ((it & 0xFF) == 0) {
           unsigned long long t;
           asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
@@ -120,10 +129,10 @@ __global__ void tp_reduce_add_kernel(float *x, const uint2 *buf, int H, int rank
           }
         }
         __nanosleep(100);
-        v = tagged_load(p);
+        v[r] = tagged_load(p);
       }
     }
-    sum = __fadd_rn(sum, __uint_as_float(v.x));
+    sum = __fadd_rn(sum, __uint_as_float(v[r].x));   // rank order: every rank forms the same sum
   }
   x[n] = sum;
 }
