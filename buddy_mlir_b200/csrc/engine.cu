@@ -1099,7 +1099,8 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
   int64_t nf = 0, ni = 0;
   if (!strcmp(variant, "f32")) {
     nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
-  } else if (!strcmp(variant, "w8a32")) {
+  } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16")) {
+    // w8a16: the same split, n_float counts f16 elements (models/deepseek_r1/specs/w8a16.json)
     ni = c.n_layers * quant_layer + H * V;
     nf = common + c.n_layers * (small_layer + qkv) +
          c.n_layers * (H + 2 * F + H) + V;  // + one scale per quantised column
@@ -1126,7 +1127,8 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
     return fail(B200_EINVAL, "load_blobs: blob order is defined for Qwen2 models only");
   int64_t want_f = 0, want_i = 0;
   if (int rc = b200_blob_elements(&c, variant, &want_f, &want_i)) return rc;
-  const bool w8 = !strcmp(variant, "w8a32"), w4 = !strcmp(variant, "w4a16");
+  const bool w8h = !strcmp(variant, "w8a16");
+  const bool w8 = !strcmp(variant, "w8a32") || w8h, w4 = !strcmp(variant, "w4a16");
   if (n_float != want_f || ((w8 || w4) && (n_int != want_i || !int_blob)))
     return fail(B200_EINVAL,
                 "load_blobs(%s): expected %lld float / %lld int8 elements, got %lld / %lld",
@@ -1134,17 +1136,19 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
                 (long long)n_int);
   const int64_t H = c.hidden, D = c.head_dim, QD = (int64_t)c.q_heads * D,
                 KD = (int64_t)c.kv_heads * D, F = c.ffn, V = c.vocab;
-  // w4a16: the float blob holds f16 values (tools/buddy-codegen/gen_config.py:51-71); they are
-  // widened once (exact), so that the rest of the walk is the same for every variant.  The
-  // scales stay f16 (they follow the float tensors in the same blob).
+  // w4a16 / w8a16: the float blob holds f16 values (tools/buddy-codegen/gen_config.py:51-71);
+  // they are widened once (exact), so that the rest of the walk is the same for every variant.
+  // The int4 scales stay f16 (they follow the float tensors in the same blob); the int8 scales
+  // of w8a16 are taken from the widened copy (the same values as f32).
   std::vector<float> widened;
   const uint16_t *f16_blob = (const uint16_t *)float_blob;
-  if (w4) {
+  const bool half_blob = w4 || w8h;
+  if (half_blob) {
     widened.resize((size_t)n_float);
     for (int64_t i = 0; i < n_float; ++i)
       widened[(size_t)i] = __half2float(__ushort_as_half(f16_blob[i]));
   }
-  const float *fp0 = w4 ? widened.data() : (const float *)float_blob;
+  const float *fp0 = half_blob ? widened.data() : (const float *)float_blob;
   const float *fp = fp0;
   const int8_t *ip = (const int8_t *)int_blob;
   const int qf = all_linear_w8 ? B200_W_I8 : -1;  // float linears: keep or quantise

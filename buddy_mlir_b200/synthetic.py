@@ -125,5 +125,13 @@ def split_w4a16(cfg: ModelConfig, views, quantize):
     return np.concatenate(floats + scales), np.concatenate(ints)
 
 
+def split_w8a16(cfg: ModelConfig, views, quantize):
+    """Reference-faithful w8a16 blobs (tools/buddy-codegen/gen_config.py:51-71): the w8a32
+    split with every float tensor and every scale as f16.  quantize(W [K,N] f32) ->
+    (Q [K,N] int8, scale [N] f32).  Returns (f16_blob, int8_blob)."""
+    fb, ib = split_w8a32(cfg, views, quantize)
+    return fb.astype(np.float16), ib
+
+
 def prompt_tokens(cfg: ModelConfig, seed: int, n: int = 32):
     return np.random.default_rng(seed).integers(0, cfg.vocab, size=n).astype(np.int64)

@@ -553,6 +553,17 @@ static void linear(const OrcLinear &L, const float *x, float *y) {
       y[n] = (float)bits_to_f16(yh[(size_t)n]);
     break;
   }
+  case ORC_LIN_W8H: {
+    // the w8a16 variant: f16 activations, f16 accumulation (DequantMatMulVectorizationDecode.cpp:
+    // 250-321 instantiated for f16)
+    std::vector<uint16_t> xh((size_t)L.K), yh((size_t)L.N, f16_to_bits((f16)0.0f));
+    for (int64_t k = 0; k < L.K; ++k)
+      xh[(size_t)k] = f16_to_bits((f16)x[k]);
+    orc_gemv_w8_f16(xh.data(), (const int8_t *)L.w, (const uint16_t *)L.scale, yh.data(), 1, L.K, L.N);
+    for (int64_t n = 0; n < L.N; ++n)
+      y[n] = (float)bits_to_f16(yh[(size_t)n]);
+    break;
+  }
   default:
     std::abort();
   }

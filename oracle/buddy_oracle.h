@@ -116,7 +116,7 @@ int64_t orc_kv_overflow(float **kv, int64_t n_buffers, int64_t kv_heads,
                         int64_t keep, float theta);
 
 /* ---- whole decode step -------------------------------------------------- */
-enum { ORC_LIN_F32 = 0, ORC_LIN_W8 = 1, ORC_LIN_W4G = 2, ORC_LIN_W4 = 3 };   /* W4: signed nibbles, per-channel f16 scale, f16 accumulation (w4a16) */
+enum { ORC_LIN_F32 = 0, ORC_LIN_W8 = 1, ORC_LIN_W4G = 2, ORC_LIN_W4 = 3, ORC_LIN_W8H = 4 };   /* W4: signed nibbles, per-channel f16 scale, f16 accumulation (w4a16); W8H: int8, f16 scale, f16 activations and accumulation (w8a16) */
 
 typedef struct {
   int32_t kind;       /* ORC_LIN_* */

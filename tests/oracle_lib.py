@@ -8,7 +8,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _SO = os.path.join(ROOT, "oracle", "_build", "libbuddy_oracle.so")
 _REF_SO = os.path.join(ROOT, "oracle", "_ref", "libbuddy_ref_host.so")
 
-LIN_F32, LIN_W8, LIN_W4G, LIN_W4 = 0, 1, 2, 3
+LIN_F32, LIN_W8, LIN_W4G, LIN_W4, LIN_W8H = 0, 1, 2, 3, 4
 
 
 class OrcLinear(C.Structure):
@@ -275,6 +275,11 @@ class OracleModel:
                 Q, sc = quantised.get((name, layer)) or quantize_per_channel(W, 4)
                 L.kind = LIN_W4
                 L.w = hold(pack_int4(np.ascontiguousarray(Q, dtype=np.int8).reshape(-1)).reshape(K, N // 2)).ctypes.data
+                L.scale = hold(np.asarray(sc, dtype=np.float32).astype(np.float16)).ctypes.data
+            elif kind == "w8h":     # the reference's w8a16: int8, per-channel f16 scale, f16 activations
+                Q, sc = quantised.get((name, layer)) or quantize_per_channel(W, 8)
+                L.kind = LIN_W8H
+                L.w = hold(Q, np.int8).ctypes.data
                 L.scale = hold(np.asarray(sc, dtype=np.float32).astype(np.float16)).ctypes.data
             elif kind == "w4g":
                 P, s = quantised.get((name, layer)) or quantize_w4_group(W, group)

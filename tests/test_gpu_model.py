@@ -208,6 +208,40 @@ def test_tiny_w4a16_reference_blobs():
     s.close()
 
 
+@pytest.mark.parametrize("through_entry", [False, True])
+def test_tiny_w8a16_reference_blobs(through_entry):
+    """The reference's w8a16 flavour (tools/buddy-codegen/gen_config.py:37-71): the w8a32 split
+    with an f16 float blob and f16 scales, f16 activations / cache / logits.  The reference
+    accumulates these GEMVs in f16, this library in f32: logits within 2e-2, the same greedy
+    token wherever the checker's margin is larger than that; once through the device session,
+    once through the model entries with a half cache."""
+    cfg = TINY_QWEN2
+    _, views = synthetic.make_f32_blob(cfg, 82)
+    fb, ib = synthetic.split_w8a16(cfg, views, lambda W: orc.quantize_per_channel(W, 8))
+    assert fb.dtype == np.float16 and ib.dtype == np.int8
+    rounded = {k: (v.astype(np.float16).astype(np.float32) if k[0] not in synthetic.QUANTISED_BY_REFERENCE else v)
+               for k, v in views.items()}
+    om = orc.OracleModel(cfg, rounded, kinds={n: "w8h" for n in synthetic.QUANTISED_BY_REFERENCE})
+    if through_entry:
+        s = EntrySession(cfg, "w8a16", [fb, ib])
+        step = lambda t: (s.decode(t), s.logits)[1]
+    else:
+        s = ModelSession(cfg)
+        s.load_blobs("w8a16", fb, ib)
+        step = lambda t: (s.decode(t), s.logits_data())[1]
+    worst, tok = 0.0, None
+    for t in list(synthetic.prompt_tokens(cfg, 6, 8)) + [None] * 16:
+        t = tok if t is None else int(t)
+        got = step(t)
+        want = om.decode(t)
+        worst = max(worst, maxrel(got, want))
+        if margin(want) > 2e-2 * float(np.abs(want).max()):
+            assert greedy_sample(got) == greedy_sample(want)
+        tok = greedy_sample(want)
+    assert worst < 2e-2, worst
+    s.close()
+
+
 def test_w4a16_model_entries_with_half_cache_and_logits():
     """The w4a16 shim: f16 blob, nibble-packed blob, KV cache and logits as IEEE half
     (uint16) on the host, exactly the descriptor types the generated session uses for

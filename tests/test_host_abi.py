@@ -69,6 +69,9 @@ def test_blob_counts_match_reference_specs():
     # models/deepseek_r1/specs/w4a16.json: 322338752 f16 elements + 727744512 packed bytes
     assert lib.b200_blob_elements(C.byref(c), b"w4a16", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (322338752, 727744512)
+    # models/deepseek_r1/specs/w8a16.json: f16_elements 322338752, i8_elements 1455489024
+    assert lib.b200_blob_elements(C.byref(c), b"w8a16", C.byref(nf), C.byref(ni)) == 0
+    assert (nf.value, ni.value) == (322338752, 1455489024)
     assert lib.b200_blob_elements(C.byref(c), b"w8a8", C.byref(nf), C.byref(ni)) != 0
 
 
