@@ -1097,7 +1097,8 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
   const int64_t small_layer = 2 * H;
   const int64_t common = V * H + D / 2 + H;  // embedding, inv_freq, final norm
   int64_t nf = 0, ni = 0;
-  if (!strcmp(variant, "f32")) {
+  if (!strcmp(variant, "f32") || !strcmp(variant, "f16")) {
+    // f16: the same single blob with f16 elements (models/deepseek_r1/specs/f16.json)
     nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
   } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16")) {
     // w8a16: the same split, n_float counts f16 elements (models/deepseek_r1/specs/w8a16.json)
@@ -1142,7 +1143,7 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   // of w8a16 are taken from the widened copy (the same values as f32).
   std::vector<float> widened;
   const uint16_t *f16_blob = (const uint16_t *)float_blob;
-  const bool half_blob = w4 || w8h;
+  const bool half_blob = w4 || w8h || !strcmp(variant, "f16");
   if (half_blob) {
     widened.resize((size_t)n_float);
     for (int64_t i = 0; i < n_float; ++i)

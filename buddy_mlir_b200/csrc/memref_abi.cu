@@ -589,8 +589,8 @@ int session_for(ForwardSession &s, const b200_model_config *cfg, const char *var
                 int all_linear_w8, const void *w0, int64_t n0, const void *w1, int64_t n1) {
   // the blobs are the model: same addresses, sizes and sampled contents = same session.  Every
   // call samples 64 words spread over each blob (a few microseconds beside a millisecond step).
-  // n0 counts elements of the float blob: f16 in the w4a16 and w8a16 variants
-  const size_t e0 = (!strcmp(variant, "w4a16") || !strcmp(variant, "w8a16")) ? 2 : 4;
+  // n0 counts elements of the float blob: f16 in the f16, w4a16 and w8a16 variants
+  const size_t e0 = (!strcmp(variant, "w4a16") || !strcmp(variant, "w8a16") || !strcmp(variant, "f16")) ? 2 : 4;
   const uint64_t seed = 0xCBF29CE484222325ull;
   uint64_t quick = fingerprint_bytes(w0, (size_t)n0 * e0, seed, 64);
   if (w1)

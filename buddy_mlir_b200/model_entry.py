@@ -32,7 +32,7 @@ class EntrySession:
         self.fn.restype = None
         self.cfg = cfg
         # host element of the cache and the logits: half (as uint16) for the f16-activation variants
-        self.half = variant in ("w4a16", "w8a16")
+        self.half = variant in ("f16", "w4a16", "w8a16")
         self.ht = np.uint16 if self.half else np.float32
         self.blobs = [np.ascontiguousarray(b) for b in blobs]
         if self.half:   # the f16 blob travels as the uint16 memref the reference's session builds

@@ -242,6 +242,32 @@ def test_tiny_w8a16_reference_blobs(through_entry):
     s.close()
 
 
+def test_tiny_f16_blob_through_the_model_entries():
+    """The reference's f16 flavour (tools/buddy-codegen/gen_config.py:37-71): one f16 blob,
+    half cache and logits.  The device computes in f32 on the widened weights; the checker is
+    the f32 restatement on the same f16-rounded tensors, 2e-2 (the reference's own f16
+    arithmetic has no restatement here: parity of this variant is unpinned beyond that)."""
+    cfg = TINY_QWEN2
+    blob, views = synthetic.make_f32_blob(cfg, 83)
+    rounded = {k: v.astype(np.float16).astype(np.float32) for k, v in views.items()}
+    om = orc.OracleModel(cfg, rounded)
+    es = EntrySession(cfg, "f16", [blob.astype(np.float16)])
+    prompt = synthetic.prompt_tokens(cfg, 7, 9)
+    logits = es.prefill(prompt, pad_id=0)
+    for t in prompt:
+        want = om.decode(int(t))
+    assert maxrel(logits[len(prompt) - 1], want) < 2e-2
+    tok = greedy_sample(want)
+    for _ in range(8):
+        es.decode(tok)
+        want = om.decode(tok)
+        assert maxrel(es.logits, want) < 2e-2
+        if margin(want) > 2e-2 * float(np.abs(want).max()):
+            assert greedy_sample(es.logits) == greedy_sample(want)
+        tok = greedy_sample(want)
+    es.close()
+
+
 def test_w4a16_model_entries_with_half_cache_and_logits():
     """The w4a16 shim: f16 blob, nibble-packed blob, KV cache and logits as IEEE half
     (uint16) on the host, exactly the descriptor types the generated session uses for

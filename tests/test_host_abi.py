@@ -72,6 +72,9 @@ def test_blob_counts_match_reference_specs():
     # models/deepseek_r1/specs/w8a16.json: f16_elements 322338752, i8_elements 1455489024
     assert lib.b200_blob_elements(C.byref(c), b"w8a16", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (322338752, 1455489024)
+    # models/deepseek_r1/specs/f16.json: total 1777088064 (f16 elements)
+    assert lib.b200_blob_elements(C.byref(c), b"f16", C.byref(nf), C.byref(ni)) == 0
+    assert (nf.value, ni.value) == (1777088064, 0)
     assert lib.b200_blob_elements(C.byref(c), b"w8a8", C.byref(nf), C.byref(ni)) != 0
 
 
