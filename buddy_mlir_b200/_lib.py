@@ -138,6 +138,7 @@ def load():
                                        C.POINTER(vp), vp]),
         "b200_forward_reset": (None, []),
         "b200_forward_status": (i32, []),
+        "b200_forward_session_builds": (i32, []),
         "b200_rax_open": (i32, [C.c_char_p, C.POINTER(vp)]),
         "b200_rax_close": (None, [vp]),
         "b200_rax_count": (i32, [vp]),

@@ -1097,7 +1097,9 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
   const int64_t small_layer = 2 * H;
   const int64_t common = V * H + D / 2 + H;  // embedding, inv_freq, final norm
   int64_t nf = 0, ni = 0;
-  if (!strcmp(variant, "f32") || !strcmp(variant, "f16")) {
+  if (!strcmp(variant, "f32") || !strcmp(variant, "f16") || !strcmp(variant, "f32p32")) {
+    // f32p32: the f32 blob with every matmul weight in 32-column panels (the decode file of
+    // the packed-decode spec, frontend/Python/graph/transform/pack_decode_weights.py:32-124)
     // f16: the same single blob with f16 elements (models/deepseek_r1/specs/f16.json)
     nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
   } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16")) {
@@ -1161,9 +1163,23 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
 #define B200_DO(expr) do { if (rc == B200_OK) rc = (expr); } while (0)
   B200_DO(b200_model_set_vector(m, -1, B200_T_EMBED, takef(V * H), V * H));
   B200_DO(b200_model_set_vector(m, -1, B200_T_INV_FREQ, takef(D / 2), D / 2));
+  // f32p32: Bpacked[n / 32][k][n % 32] == B[k, n]; the panels are undone into a scratch copy
+  const bool panels = !strcmp(variant, "f32p32");
+  std::vector<float> plain;
   auto flinear = [&](int l, int slot, int64_t K, int64_t N) {
-    B200_DO(b200_model_set_linear(m, l, slot, B200_W_F32, takef(K * N), nullptr,
-                                  B200_F32, 0, K, N, qf, 0));
+    const float *w = takef(K * N);
+    if (panels && rc == B200_OK) {
+      if (N % 32 != 0) {
+        rc = fail(B200_EINVAL, "load_blobs(f32p32): N = %lld is not a multiple of the panel width", (long long)N);
+        return;
+      }
+      plain.resize((size_t)(K * N));
+      for (int64_t pn = 0; pn < N / 32; ++pn)
+        for (int64_t k = 0; k < K; ++k)
+          memcpy(&plain[(size_t)(k * N + pn * 32)], w + (pn * K + k) * 32, 32 * sizeof(float));
+      w = plain.data();
+    }
+    B200_DO(b200_model_set_linear(m, l, slot, B200_W_F32, w, nullptr, B200_F32, 0, K, N, qf, 0));
   };
   auto qlinear = [&](int l, int slot, int64_t K, int64_t N) {
     if (w8)

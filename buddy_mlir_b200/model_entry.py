@@ -18,11 +18,14 @@ from .memref import _libc, memref_type, to_memref
 
 
 class EntrySession:
-    def __init__(self, cfg: ModelConfig, variant: str, blobs, all_linear_w8: bool = False):
+    def __init__(self, cfg: ModelConfig, variant: str, blobs, all_linear_w8: bool = False, decode_blobs=None):
+        """decode_blobs: the weight files the decode entry gets when they differ from the prefill
+        entry's (the panel-packed copy of the packed-decode spec, gen_session.py:1393)."""
         _lib.load()
-        so = os.path.join(HERE, shim_name(cfg, variant, all_linear_w8))
+        packed = decode_blobs is not None
+        so = os.path.join(HERE, shim_name(cfg, variant, all_linear_w8, packed))
         if not os.path.exists(so):
-            build(cfg, variant, all_linear_w8)
+            build(cfg, variant, all_linear_w8, decode_packed=packed)
         self.dll = C.CDLL(so)          # RTLD_LOCAL, like ModelSession::Impl::loadSo
         # gen_session.py:1127-1141: prefill first, then decode; a missing symbol throws
         self.prefill_fn = self.dll._mlir_ciface_forward_prefill
@@ -38,6 +41,8 @@ class EntrySession:
         if self.half:   # the f16 blob travels as the uint16 memref the reference's session builds
             self.blobs[0] = self.blobs[0].view(np.uint16)
         self.blob_desc = [to_memref(b) for b in self.blobs]
+        self.decode_blobs = [np.ascontiguousarray(b) for b in decode_blobs] if packed else self.blobs
+        self.decode_blob_desc = [to_memref(b) for b in self.decode_blobs] if packed else self.blob_desc
         kvs = (1, cfg.kv_heads, cfg.max_len, cfg.head_dim)
         self.kv = [np.zeros(kvs, dtype=self.ht) for _ in range(2 * cfg.n_layers)]
         self.kv_desc = [to_memref(k) for k in self.kv]
@@ -57,7 +62,7 @@ class EntrySession:
         self._tok_d, self._pos_d = to_memref(self.token), to_memref(self.cache_position)
         self._dum_d = [to_memref(d) for d in self.dummies]
         self._result = self.ABI()
-        args = [C.byref(self._result)] + [C.byref(d) for d in self.blob_desc]
+        args = [C.byref(self._result)] + [C.byref(d) for d in self.decode_blob_desc]
         args += [C.byref(self._tok_d), C.byref(self._pos_d), C.byref(self.kv_desc[0]),
                  C.byref(self.kv_desc[1])]
         for i in range(cfg.n_layers - 1):

@@ -125,6 +125,23 @@ def split_w4a16(cfg: ModelConfig, views, quantize):
     return np.concatenate(floats + scales), np.concatenate(ints)
 
 
+def pack_decode_blob(cfg: ModelConfig, blob, vecsize: int = 32):
+    """The decode file of the packed-decode spec: the f32 blob with every matmul weight
+    [K, N] stored as [N / V][K][V] (frontend/Python/graph/transform/pack_decode_weights.py:
+    32-124: reshape(k, n // V, V).permute(1, 0, 2)), everything else unchanged."""
+    out = np.array(blob, dtype=np.float32, copy=True)
+    off = 0
+    for name, _, shape in tensor_list(cfg):
+        n = int(np.prod(shape))
+        if name in ("q", "k", "v", "o", "gate", "up", "down", "lm_head"):
+            K, N = shape
+            assert N % vecsize == 0
+            w = blob[off:off + n].reshape(K, N // vecsize, vecsize)
+            out[off:off + n] = np.ascontiguousarray(w.transpose(1, 0, 2)).reshape(-1)
+        off += n
+    return out
+
+
 def split_w8a16(cfg: ModelConfig, views, quantize):
     """Reference-faithful w8a16 blobs (tools/buddy-codegen/gen_config.py:51-71): the w8a32
     split with every float tensor and every scale as f16.  quantize(W [K,N] f32) ->

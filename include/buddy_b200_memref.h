@@ -183,6 +183,13 @@ int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant,
  * gen_session.py:1416-1418) and this code stays set -- the first failure since
  * the last b200_forward_reset(), 0 if none; b200_last_error() has the text. */
 int b200_forward_status(void);
+/* Diagnostic: how many times the entry pair has built its device session (upload,
+ * quantise, pack) since the last b200_forward_reset().  Variant "f32p32" is the
+ * f32 blob with every matmul weight in 32-column panels -- the decode file of the
+ * reference's packed-decode spec (pack_decode_weights.py:32-124,
+ * gen_session.py:1290-1300,1393): the decode entry receives it while the prefill
+ * entry receives the plain blob, and both are recognised as one model. */
+int b200_forward_session_builds(void);
 /* Drop the session the two entries keep (weights, KV, graph) and the status. */
 void b200_forward_reset(void);
 

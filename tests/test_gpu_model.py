@@ -268,6 +268,45 @@ def test_tiny_f16_blob_through_the_model_entries():
     es.close()
 
 
+def test_packed_decode_spec_plain_prefill_blob_and_panel_packed_decode_blob():
+    """models/deepseek_r1/specs/f32_packed_decode.json: the prefill entry gets the plain f32
+    blob, the decode entry the copy whose matmul weights sit in 32-column panels
+    (pack_decode_weights.py:32-124, gen_session.py:1393).  Both are one model: the device
+    session is built once, decode continues on the prefilled cache, logits equal the
+    checker's; a decode blob of another model is not mistaken for it."""
+    cfg = TINY_QWEN2
+    blob, views = synthetic.make_f32_blob(cfg, 84)
+    packed = synthetic.pack_decode_blob(cfg, blob)
+    assert not np.array_equal(packed, blob) and np.array_equal(np.sort(packed), np.sort(blob))
+    om = orc.OracleModel(cfg, views)
+    es = EntrySession(cfg, "f32", [blob], decode_blobs=[packed])
+    prompt = synthetic.prompt_tokens(cfg, 12, 7)
+    logits = es.prefill(prompt, pad_id=0)
+    for t in prompt:
+        want = om.decode(int(t))
+    assert maxrel(logits[len(prompt) - 1], want) < 1e-3
+    tok = greedy_sample(want)
+    for _ in range(6):
+        es.decode(tok, check_alias=True)
+        want = om.decode(tok)
+        assert maxrel(es.logits, want) < 1e-3 and greedy_sample(es.logits) == greedy_sample(want)
+        tok = greedy_sample(want)
+    assert _lib.load().b200_forward_session_builds() == 1
+    es.close()
+    # the panels of ANOTHER model: the decode entry must build its own session from them
+    other, oviews = synthetic.make_f32_blob(cfg, 85)
+    es = EntrySession(cfg, "f32", [blob], decode_blobs=[synthetic.pack_decode_blob(cfg, other)])
+    es.prefill(prompt, pad_id=0)
+    om2 = orc.OracleModel(cfg, oviews)
+    for b in range(2 * cfg.n_layers):              # the cache the first model's prefill left on the host
+        om2.kv[b][:, :len(prompt)] = es.kv_floats(b)[0, :, :len(prompt)]
+    om2.position = len(prompt)
+    es.decode(tok)
+    assert maxrel(es.logits, om2.decode(tok)) < 1e-3
+    assert _lib.load().b200_forward_session_builds() == 2
+    es.close()
+
+
 def test_w4a16_model_entries_with_half_cache_and_logits():
     """The w4a16 shim: f16 blob, nibble-packed blob, KV cache and logits as IEEE half
     (uint16) on the host, exactly the descriptor types the generated session uses for
