@@ -13,8 +13,9 @@ first timed position are seeded N(0, 1) (no checkpoint, no dataset).
 
 N > 1 workload: the Qwen3-8B architecture with int4 group-128 weights,
 context 4096, tensor-parallel over the N GPUs (column-parallel q/k/v/gate/up,
-row-parallel o/down, NCCL all-reduce after each, vocab-sharded lm_head):
-strong scaling, one rank per GPU.
+row-parallel o/down with a sum over NVLink peer stores after each, vocab-sharded
+lm_head): strong scaling, one rank per GPU; the line carries a `parity` object
+(the sharded model against the unsharded CPU checker).
 
 `value` is tokens/s with everything resident in HBM (the device-resident
 greedy loop, CUDA events on the session's stream).  `e2e` is the same metric
@@ -24,8 +25,15 @@ greedy argmax on the host as buddy-mlir's runGeneration does.
 
 `--impl reference` times the CPU restatement of buddy-mlir's generated decode
 code (oracle/, OpenMP over the same 32-column tiles) on the host cores, same
-configuration; the reference's compiled path itself cannot be produced
-without its LLVM toolchain.
+configuration, driven and timed by buddy-mlir's own runGeneration + Sampler when
+the prebuilt runner is present (oracle/_ref); the reference's compiled path
+itself cannot be produced without its LLVM toolchain.
+
+Beside the metric, outside the timed region, the N = 1 line reports
+`gemv_isolated` (the GEMV sweep) and `dense_path` (the same model's prefill of
+2048 tokens, batched decode of 64 sequences over the paged cache, and the
+gate|up GEMM at 1024 rows on the tcgen05 path); `--gemv-only`, `--gemm-only`
+and `--batch-only` print those alone.
 """
 import argparse
 import json
@@ -397,25 +405,20 @@ def run_gemm_only(args):
     print(json.dumps({"gemm_isolated": gemm_microbench(lib, args.gemm_shape)}))
 
 
-def run_batch_only(args):
-    """--batch-only: batched decode + prefill of the 1.5B int8 model (dense tcgen05 GEMM path):
-    64 sequences with seeded lengths uniform in [128, 2048] in the paged KV cache, a
-    2048-token prefill, then `--steps` decode steps of the whole batch (one JSON line)."""
+def batch_numbers(blob, steps, warmup):
+    """Batched decode + prefill of the 1.5B int8 model (dense tcgen05 GEMM path): 64 sequences
+    with seeded lengths uniform in [128, 2048] in the paged KV cache, a 2048-token prefill, then
+    `steps` decode steps of the whole batch."""
     import torch
-    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, _lib, synthetic
+    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg
     from buddy_mlir_b200.session import BatchSession, ModelSession
-    _lib.load()
-    if not torch.cuda.is_available():
-        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
-    torch.cuda.set_device(0)
-    blob, _ = synthetic.make_f32_blob(cfg, SEED_W)
     s = ModelSession(cfg)
     s.load_blobs("f32", blob, all_linear_w8=True)
     B, page = 64, 16
     rng = np.random.default_rng(SEED_P)
     lengths = rng.integers(128, 2049, B)
-    n_pages = int(sum((int(n) + args.steps + args.warmup + page - 1) // page + 1 for n in lengths)) + 2048 // page + 8
-    bs = BatchSession(s, max_seqs=B + 1, page_size=page, n_pages=n_pages, max_context=2048 + args.steps + args.warmup + 16)
+    n_pages = int(sum((int(n) + steps + warmup + page - 1) // page + 1 for n in lengths)) + 2048 // page + 8
+    bs = BatchSession(s, max_seqs=B + 1, page_size=page, n_pages=n_pages, max_context=2048 + steps + warmup + 16)
     # one 2048-token prefill, timed (after a warm-up pass of the same size on a scratch sequence)
     scratch = bs.add()
     bs.prefill(scratch, rng.integers(0, cfg.vocab, 2048), want_logits=False)
@@ -433,12 +436,12 @@ def run_batch_only(args):
         _, nxt = bs.prefill(q, rng.integers(0, cfg.vocab, int(n)), want_logits=False)
         seqs.append(q)
         toks.append(nxt)
-    for _ in range(args.warmup):
+    for _ in range(warmup):
         _, nxt = bs.decode(seqs, toks, want_logits=False)
         toks = [int(t) for t in nxt]
     ms = []
-    for i in range(args.steps):
-        if i == args.steps - 1:
+    for i in range(steps):
+        if i == steps - 1:
             torch.cuda.profiler.start()
         _, nxt = bs.decode(seqs, toks, want_logits=False)
         ms.append(bs.last_ms())
@@ -446,14 +449,27 @@ def run_batch_only(args):
     torch.cuda.profiler.stop()
     step_ms = float(np.mean(ms))
     flops = 2.0 * (1310195712 + 233373696)       # per token: the linear layers and the lm_head
-    print(json.dumps({"batched_decode": {"sequences": B, "lengths": "uniform [128, 2048], seeded", "page_size": page,
-                                         "ms_per_step": step_ms, "tokens_per_s": B / (step_ms / 1000.0),
-                                         "steps": args.steps, "weights": "int8 per-channel, every linear layer"},
-                      "prefill_2048": {"ms": prefill_ms, "tokens_per_s": 2048 / (prefill_ms / 1000.0),
-                                       "linear_TFLOP/s": 2048 * flops / (prefill_ms / 1000.0) / 1e12},
-                      "model": "deepseek-r1-distill-qwen-1.5b architecture, seeded weights"}))
+    out = {"batched_decode": {"sequences": B, "lengths": "uniform [128, 2048], seeded", "page_size": page,
+                              "ms_per_step": step_ms, "tokens_per_s": B / (step_ms / 1000.0),
+                              "steps": steps, "weights": "int8 per-channel, every linear layer"},
+           "prefill_2048": {"ms": prefill_ms, "tokens_per_s": 2048 / (prefill_ms / 1000.0),
+                            "linear_TFLOP/s": 2048 * flops / (prefill_ms / 1000.0) / 1e12},
+           "model": "deepseek-r1-distill-qwen-1.5b architecture, seeded weights"}
     bs.close()
     s.close()
+    return out
+
+
+def run_batch_only(args):
+    """--batch-only: the batched decode + prefill numbers alone (one JSON line)."""
+    import torch
+    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, _lib, synthetic
+    _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    blob, _ = synthetic.make_f32_blob(cfg, SEED_W)
+    print(json.dumps(batch_numbers(blob, args.steps, args.warmup)))
 
 
 def run_gemv_only(args):
@@ -540,6 +556,11 @@ def run_single(args):
     d2h = cfg.vocab * 4 + 2 * cfg.n_layers * cfg.kv_heads * cfg.head_dim * 4
     setup_s = time.perf_counter() - t_setup
 
+    # the dense path beside the headline (config 5 of the same model): not part of the metric
+    dense = None
+    if not args.resident_only:
+        dense = batch_numbers(blob, 16, 3)
+        dense["gemm_gate_up_m1024"] = gemm_microbench(lib, "gate_up_m1024")["shapes"]["gate_up_m1024"]
     base = cpu_baseline(cfg, blob, views, start)
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps,
             "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,
@@ -551,6 +572,7 @@ def run_single(args):
                          "kernel": "decode_step_kernel (one persistent launch per token)" if persistent else "whole decode step (CUDA graph replay)",
                          "bytes_per_step": step_bytes, "frac_of_8TBs_nominal": achieved / 8000.0},
             "gemv_isolated": gemv,
+            "dense_path": dense,
             "cpu_baseline": base,
             "e2e": {"value": steps / e2e_dt, "unit": "tokens/s", "h2d_bytes_per_step": 16,
                     "d2h_bytes_per_step": d2h, "tokens_match_resident_run": same},
