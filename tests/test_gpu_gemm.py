@@ -37,7 +37,8 @@ def test_prefill_known_answer_rows_of_eight():
 
 
 @pytest.mark.parametrize("M,N,K", [(128, 128, 64), (1, 256, 128), (64, 1536, 1536), (200, 2048, 1536),
-                                   (1024, 1536, 8960), (1024, 17920, 1536), (100, 3000, 1536)])
+                                   (1024, 1536, 8960), (1024, 17920, 1536), (100, 3000, 1536),
+                                   (513, 700, 1600), (300, 2500, 2048)])
 def test_gemm_w8_matches_prefill_restatement(M, N, K):
     from gpu_util import dev, packed_weight, gemm_w8
     if M * N * K > 3e9:
@@ -56,10 +57,12 @@ def test_gemm_w8_matches_prefill_restatement(M, N, K):
     print(f"gemm {M}x{N}x{K}: max rel err {rel(y[rows], want):.2e}")
 
 
-def test_gemm_w8_fused_norm_bias_residual_and_silu_pairs():
+@pytest.mark.parametrize("M,K,N", [(70, 1536, 512), (600, 1600, 768)])
+def test_gemm_w8_fused_norm_bias_residual_and_silu_pairs(M, K, N):
+    """Few rows: the converting kernel (split over K); many rows: the dense kernel with the
+    warp-per-row activation split, a K that ends in a partial block of the packed rows."""
     from gpu_util import dev, packed_weight, gemm_w8
     rng = np.random.default_rng(5)
-    M, K, N = 70, 1536, 512
     A = rng.standard_normal((M, K)).astype(np.float32)
     Q = rng.integers(-127, 128, (K, N)).astype(np.int8)
     s = rng.uniform(0.001, 0.01, N).astype(np.float32)
