@@ -695,9 +695,11 @@ inline bool same_row(const uint16_t *host, const float *shadow, size_t n) {
 // 0 and the middle row catch a rewritten or shifted cache
 // (handleKVCacheOverflow, gen_session.py:1471-1506): three rows per head and
 // buffer are compared bit for bit.
+// HL: rows per kv head of the HOST buffers (max_len, or the cache size of a tier of the
+// tiered-cache spec); the shadow and the device cache always hold max_len rows.
 template <typename T>
 bool host_matches_device(const ForwardSession &s, const b200_model_config *cfg,
-                         T *const *host_kv, long long pos) {
+                         T *const *host_kv, long long pos, size_t HL) {
   if (pos > s.valid_rows)
     return false;
   if (pos == 0)
@@ -706,35 +708,34 @@ bool host_matches_device(const ForwardSession &s, const b200_model_config *cfg,
   const long long probe[3] = {0, (pos - 1) / 2, pos - 1};
   for (size_t b = 0; b < s.shadow.size(); ++b)
     for (size_t h = 0; h < KH; ++h)
-      for (long long r : probe) {
-        const size_t off = (h * L + (size_t)r) * D;
-        if (!same_row(host_kv[b] + off, s.shadow[b].data() + off, D))
+      for (long long r : probe)
+        if (!same_row(host_kv[b] + (h * HL + (size_t)r) * D, s.shadow[b].data() + (h * L + (size_t)r) * D, D))
           return false;
-      }
   return true;
 }
 
 template <typename T>
 int forward_decode(const b200_model_config *cfg, const char *variant, int all_linear_w8,
                    const void *w0, int64_t n0, const void *w1, int64_t n1,
-                   long long token, long long pos, T *const *host_kv, T **logits_out) {
+                   long long token, long long pos, T *const *host_kv, T **logits_out, int host_len = 0) {
   if (!cfg || !variant || !w0 || !host_kv || !logits_out)
     return fail(B200_EINVAL, "forward_decode: null argument");
   *logits_out = nullptr;
-  if (pos < 0 || pos >= cfg->max_len)
-    return fail(B200_EINVAL, "forward_decode: position %lld outside the cache (max_len %d)", pos,
-                cfg->max_len);
+  const size_t HL = host_len > 0 ? (size_t)host_len : (size_t)cfg->max_len;
+  if (pos < 0 || pos >= cfg->max_len || (size_t)pos >= HL)
+    return fail(B200_EINVAL, "forward_decode: position %lld outside the cache (max_len %d, host rows %zu)", pos,
+                cfg->max_len, HL);
   std::lock_guard<std::mutex> lock(g_fwd_mu);
   ForwardSession &s = g_fwd;
   if (int rc = session_for(s, cfg, variant, all_linear_w8, w0, n0, w1, n1)) return rc;
   const int nbuf = 2 * cfg->n_layers;
   const size_t D = cfg->head_dim, KH = cfg->kv_heads, L = cfg->max_len;
-  if (!host_matches_device(s, cfg, host_kv, pos)) {
+  if (!host_matches_device(s, cfg, host_kv, pos, HL)) {
     // hand-off from the host (CPU prefill, another sequence, a shifted cache):
     // everything before `pos` comes from host_kv
     for (int b = 0; b < nbuf; ++b) {
       for (size_t h = 0; h < KH; ++h)
-        from_host(s.shadow[b].data() + h * L * D, host_kv[b] + h * L * D, (size_t)pos * D);
+        from_host(s.shadow[b].data() + h * L * D, host_kv[b] + h * HL * D, (size_t)pos * D);
       if (int rc = b200_model_kv_upload(s.model, b, s.shadow[b].data(), 0, (int)pos)) return rc;
     }
     s.valid_rows = (int)pos;
@@ -759,7 +760,7 @@ int forward_decode(const b200_model_config *cfg, const char *variant, int all_li
   for (int b = 0; b < nbuf; ++b)
     for (size_t h = 0; h < KH; ++h) {
       const float *row = &s.rows[((size_t)b * KH + h) * D];
-      to_host(host_kv[b] + (h * L + (size_t)pos) * D, row, D);
+      to_host(host_kv[b] + (h * HL + (size_t)pos) * D, row, D);
       memcpy(s.shadow[b].data() + (h * L + (size_t)pos) * D, row, D * 4);
     }
   if (s.valid_rows < pos + 1)
@@ -771,11 +772,13 @@ int forward_decode(const b200_model_config *cfg, const char *variant, int all_li
 template <typename T>
 int forward_prefill(const b200_model_config *cfg, const char *variant, int all_linear_w8,
                     const void *w0, int64_t n0, const void *w1, int64_t n1,
-                    const long long *tokens, int n_rows, T *const *host_kv_out, T *logits_out) {
+                    const long long *tokens, int n_rows, T *const *host_kv_out, T *logits_out,
+                    int host_len = 0) {
   if (!cfg || !variant || !w0 || !tokens || !host_kv_out || !logits_out)
     return fail(B200_EINVAL, "forward_prefill: null argument");
-  if (n_rows < 1 || n_rows > cfg->max_len)
-    return fail(B200_EINVAL, "forward_prefill: %d rows, the cache holds %d", n_rows, cfg->max_len);
+  const size_t HL = host_len > 0 ? (size_t)host_len : (size_t)cfg->max_len;
+  if (n_rows < 1 || n_rows > cfg->max_len || (size_t)n_rows > HL)
+    return fail(B200_EINVAL, "forward_prefill: %d rows, the cache holds %d (host rows %zu)", n_rows, cfg->max_len, HL);
   for (int i = 0; i < n_rows; ++i)
     if (tokens[i] < 0 || tokens[i] >= cfg->vocab)
       return fail(B200_EINVAL, "forward_prefill: token %lld at row %d outside the vocabulary",
@@ -805,9 +808,9 @@ int forward_prefill(const b200_model_config *cfg, const char *variant, int all_l
   for (int b = 0; b < nbuf; ++b) {
     if (int rc = b200_model_kv_download(s.model, b, s.shadow[b].data(), 0, n_rows)) return rc;
     for (size_t h = 0; h < KH; ++h) {
-      to_host(host_kv_out[b] + h * L * D, s.shadow[b].data() + h * L * D, (size_t)n_rows * D);
-      if ((size_t)n_rows < L)   // rows the prefill did not reach read as zero
-        memset(host_kv_out[b] + (h * L + (size_t)n_rows) * D, 0, (L - (size_t)n_rows) * D * sizeof(T));
+      to_host(host_kv_out[b] + h * HL * D, s.shadow[b].data() + h * L * D, (size_t)n_rows * D);
+      if ((size_t)n_rows < HL)   // rows the prefill did not reach read as zero
+        memset(host_kv_out[b] + (h * HL + (size_t)n_rows) * D, 0, (HL - (size_t)n_rows) * D * sizeof(T));
     }
   }
   s.valid_rows = n_rows;
@@ -844,6 +847,23 @@ int b200_forward_prefill(const b200_model_config *cfg, const char *variant, int 
                          const long long *tokens, int n_rows, float *const *host_kv_out,
                          float *logits_out) {
   return note_status(forward_prefill<float>(cfg, variant, all_linear_w8, w0, n0, w1, n1, tokens, n_rows, host_kv_out, logits_out));
+}
+// The tiered-cache spec (models/deepseek_r1/specs/f32_tiered_kv_cache.json,
+// gen_session.py:303-800): one prefill / decode symbol per cache size; the host buffers of a
+// tier hold host_len rows per kv head, the device session always holds max_len rows.
+int b200_forward_decode_tier(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                             const void *w0, int64_t n0, const void *w1, int64_t n1,
+                             long long token, long long pos, float *const *host_kv, int host_len,
+                             float **logits_out) {
+  return note_status(forward_decode<float>(cfg, variant, all_linear_w8, w0, n0, w1, n1, token, pos, host_kv,
+                                           logits_out, host_len));
+}
+int b200_forward_prefill_tier(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                              const void *w0, int64_t n0, const void *w1, int64_t n1,
+                              const long long *tokens, int n_rows, float *const *host_kv_out, int host_len,
+                              float *logits_out) {
+  return note_status(forward_prefill<float>(cfg, variant, all_linear_w8, w0, n0, w1, n1, tokens, n_rows,
+                                            host_kv_out, logits_out, host_len));
 }
 int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant, int all_linear_w8,
                              const void *w0, int64_t n0, const void *w1, int64_t n1,

@@ -134,3 +134,94 @@ class EntrySession:
 
     def close(self):
         _lib.load().b200_forward_reset()
+
+
+class TieredEntrySession:
+    """The host side of the tiered-cache spec (models/deepseek_r1/specs/f32_tiered_kv_cache.json)
+    as gen_session.py:303-800 generates it: one prefill / decode symbol per cache size
+    (`_mlir_ciface_forward_prefill_<size>`, `_mlir_ciface_forward_decode_<size>`), the smallest
+    tier that holds the sequence is used, and the host cache is copied into the next tier's
+    buffers when the sequence outgrows the current one."""
+
+    def __init__(self, cfg: ModelConfig, blob, tiers):
+        _lib.load()
+        so = os.path.join(HERE, shim_name(cfg, "f32", tiers=tiers))
+        if not os.path.exists(so):
+            build(cfg, "f32", tiers=tiers)
+        self.dll = C.CDLL(so)
+        self.cfg, self.tiers = cfg, list(tiers)
+        self.prefill_fns = [getattr(self.dll, f"_mlir_ciface_forward_prefill_{t}") for t in tiers]
+        self.decode_fns = [getattr(self.dll, f"_mlir_ciface_forward_decode_{t}") for t in tiers]
+        for f in self.prefill_fns + self.decode_fns:
+            f.restype, f.argtypes = None, None
+        self.blob = np.ascontiguousarray(blob, dtype=np.float32)
+        self.blob_desc = to_memref(self.blob)
+        nl = 2 * cfg.n_layers
+        self.kv = [[np.zeros((1, cfg.kv_heads, t, cfg.head_dim), dtype=np.float32) for _ in range(nl)] for t in tiers]
+        self.token = np.zeros((1, 1), dtype=np.int64)
+        self.cache_position = np.zeros(1, dtype=np.int64)
+        self.dummies = [np.zeros(1, dtype=np.int64) for _ in range(cfg.n_layers - 1)]
+        self.logits = np.zeros(cfg.vocab, dtype=np.float32)
+        self.position_, self.slot = 0, 0
+        I1, K4, L3 = memref_type(np.int64, 1), memref_type(np.float32, 4), memref_type(np.float32, 3)
+        fields = [("cache_position_out", I1), ("kv0", K4), ("kv1", K4)]
+        for i in range(cfg.n_layers - 1):
+            fields += [(f"dummy{i}", I1), (f"kv{2 + 2 * i}", K4), (f"kv{3 + 2 * i}", K4)]
+        fields.append(("logits", L3))
+        self.DecodeABI = type("DecodeABI", (C.Structure,), {"_fields_": fields})
+        self.PrefillABI = type("PrefillABI", (C.Structure,), {"_fields_": [("kv", K4 * nl), ("logits", L3)]})
+
+    def _check(self):
+        lib = _lib.load()
+        if lib.b200_forward_status() != 0:
+            raise _lib.B200Error(lib.b200_last_error().decode())
+
+    def prefill(self, prompt, pad_id: int = 0):
+        cfg, n = self.cfg, len(prompt)
+        self.slot = next(i for i, t in enumerate(self.tiers) if n <= t)        # selectPrefillSize
+        S = self.tiers[self.slot]
+        toks = np.full((1, S), pad_id, dtype=np.uint64)
+        toks[0, :n] = np.asarray(prompt, dtype=np.uint64)
+        tok_d = to_memref(toks)
+        result = self.PrefillABI()
+        self.prefill_fns[self.slot](C.byref(result), C.byref(self.blob_desc), C.byref(tok_d))
+        self._check()
+        logits = np.array(np.ctypeslib.as_array(result.logits.aligned, shape=(S * cfg.vocab,)), copy=True)
+        _libc.free(C.cast(result.logits.allocated, C.c_void_p))
+        for i, k in enumerate(self.kv[self.slot]):                             # copyKVCache(prefill -> decode)
+            assert tuple(result.kv[i].sizes) == (1, cfg.kv_heads, S, cfg.head_dim)
+            src = np.ctypeslib.as_array(result.kv[i].aligned, shape=(k.size,)).reshape(k.shape)
+            k[:, :, :n] = src[:, :, :n]
+            _libc.free(C.cast(result.kv[i].allocated, C.c_void_p))
+        self.position_ = n
+        self.prefill_logits = logits.reshape(S, cfg.vocab)
+        np.copyto(self.logits, self.prefill_logits[n - 1])
+        return self.prefill_logits
+
+    def decode(self, token_id: int):
+        cfg = self.cfg
+        need = next((i for i, t in enumerate(self.tiers) if self.position_ + 1 < t), len(self.tiers) - 1)  # selectDecodeSize
+        if need != self.slot:
+            for old, new in zip(self.kv[self.slot], self.kv[need]):            # copyKVCache(tier -> tier)
+                new[:, :, :self.position_] = old[:, :, :self.position_]
+            self.slot = need
+        self.token[0, 0] = token_id
+        self.cache_position[0] = self.position_
+        for d in self.dummies:
+            d[0] = self.position_
+        kv = self.kv[self.slot]
+        kvd = [to_memref(k) for k in kv]
+        result = self.DecodeABI()
+        args = [C.byref(result), C.byref(self.blob_desc), C.byref(to_memref(self.token)),
+                C.byref(to_memref(self.cache_position)), C.byref(kvd[0]), C.byref(kvd[1])]
+        dd = [to_memref(d) for d in self.dummies]
+        for i in range(cfg.n_layers - 1):
+            args += [C.byref(dd[i]), C.byref(kvd[2 + 2 * i]), C.byref(kvd[3 + 2 * i])]
+        self.decode_fns[self.slot](*args)
+        np.copyto(self.logits, np.ctypeslib.as_array(result.logits.aligned, shape=(cfg.vocab,)))
+        _libc.free(C.cast(result.logits.allocated, C.c_void_p))
+        self._check()
+        self.position_ += 1
+
+    def close(self):
+        _lib.load().b200_forward_reset()

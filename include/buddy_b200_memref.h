@@ -177,6 +177,22 @@ int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant,
                              const void *w1, int64_t n1, const long long *tokens,
                              int n_rows, uint16_t *const *host_kv_out,
                              uint16_t *logits_out);
+/* The same two entries for the tiered-cache spec
+ * (models/deepseek_r1/specs/f32_tiered_kv_cache.json; gen_session.py:303-800
+ * resolves _mlir_ciface_forward_prefill_<size> / _mlir_ciface_forward_decode_<size>
+ * for every cache size and moves the host cache to a larger tier as the
+ * sequence grows): host_len = rows per kv head of the host buffers of the tier;
+ * the device session keeps max_len rows whatever the tier. */
+int b200_forward_decode_tier(const b200_model_config *cfg, const char *variant,
+                             int all_linear_w8, const void *w0, int64_t n0,
+                             const void *w1, int64_t n1, long long token,
+                             long long pos, float *const *host_kv, int host_len,
+                             float **logits_out);
+int b200_forward_prefill_tier(const b200_model_config *cfg, const char *variant,
+                              int all_linear_w8, const void *w0, int64_t n0,
+                              const void *w1, int64_t n1, const long long *tokens,
+                              int n_rows, float *const *host_kv_out, int host_len,
+                              float *logits_out);
 /* The entry symbols return void, so a failure cannot be reported through them:
  * the shim prints the reason, hands back zero-filled logits of the right shape
  * (the reference caller copies from the buffer unconditionally,

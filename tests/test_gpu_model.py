@@ -9,7 +9,7 @@ import pytest
 
 import oracle_lib as orc
 from buddy_mlir_b200 import (DEEPSEEK_R1_1P5B, TINY_MEGA, TINY_QWEN2, TINY_QWEN3, _lib, synthetic)
-from buddy_mlir_b200.model_entry import EntrySession
+from buddy_mlir_b200.model_entry import EntrySession, TieredEntrySession
 from buddy_mlir_b200.session import ModelSession, greedy_sample, run_generation
 
 pytestmark = pytest.mark.gpu
@@ -304,6 +304,35 @@ def test_packed_decode_spec_plain_prefill_blob_and_panel_packed_decode_blob():
     es.decode(tok)
     assert maxrel(es.logits, om2.decode(tok)) < 1e-3
     assert _lib.load().b200_forward_session_builds() == 2
+    es.close()
+
+
+def test_tiered_cache_spec_entries_per_cache_size():
+    """models/deepseek_r1/specs/f32_tiered_kv_cache.json: one prefill / decode symbol per cache
+    size; the host moves its cache to a larger tier as the sequence grows (gen_session.py:
+    303-800).  The prompt lands in the 32-row tier, decode crosses into the 64- and the 128-row
+    tiers; logits equal the checker's all the way and the device session is built once."""
+    from buddy_mlir_b200.gen_model_entry import TINY_TIERS
+    cfg = TINY_QWEN2
+    blob, views = synthetic.make_f32_blob(cfg, 86)
+    om = orc.OracleModel(cfg, views)
+    es = TieredEntrySession(cfg, blob, TINY_TIERS)
+    prompt = synthetic.prompt_tokens(cfg, 16, 27)
+    logits = es.prefill(prompt, pad_id=0)
+    assert logits.shape == (32, cfg.vocab) and es.slot == 0
+    for t in prompt:
+        want = om.decode(int(t))
+    assert maxrel(logits[len(prompt) - 1], want) < 1e-3
+    tok = greedy_sample(want)
+    seen = set()
+    for _ in range(45):                      # positions 27 .. 71: tiers 32 -> 64 -> 128
+        es.decode(tok)
+        seen.add(es.tiers[es.slot])
+        want = om.decode(tok)
+        assert maxrel(es.logits, want) < 1e-3 and greedy_sample(es.logits) == greedy_sample(want)
+        tok = greedy_sample(want)
+    assert seen == {32, 64, 128}
+    assert _lib.load().b200_forward_session_builds() == 1
     es.close()
 
 
