@@ -561,6 +561,18 @@ def run_single(args):
     if not args.resident_only:
         dense = batch_numbers(blob, 16, 3)
         dense["gemm_gate_up_m1024"] = gemm_microbench(lib, "gate_up_m1024")["shapes"]["gate_up_m1024"]
+        # time to first token through the reference's ABI: _mlir_ciface_forward_prefill computes all
+        # max_len rows, as the reference's prefill graph does, and returns [1, max_len, vocab] logits
+        # and the KV buffers in host memory
+        es = EntrySession(cfg, "f32", [blob], all_linear_w8=True)
+        prompt = synthetic.prompt_tokens(cfg, SEED_P, 32)
+        es.prefill(prompt)
+        es.prefill(prompt)
+        dense["entry_prefill"] = {"ms": 1000.0 * es.last_prefill_call_s, "rows": cfg.max_len,
+                                  "d2h_bytes": cfg.max_len * cfg.vocab * 4 +
+                                  2 * cfg.n_layers * cfg.kv_heads * cfg.max_len * cfg.head_dim * 4,
+                                  "call": "_mlir_ciface_forward_prefill, host buffers, all max_len rows"}
+        es.close()
     base = cpu_baseline(cfg, blob, views, start)
     line = {"metric": METRIC, "value": value, "unit": "tokens/s", "n_gpus": 1, "steps": steps,
             "warmup": warmup, "ms_per_step": ms / steps, "higher_is_better": True,

@@ -796,7 +796,17 @@ int forward_prefill(const b200_model_config *cfg, const char *variant, int all_l
     for (int i = 0; i < n_rows; ++i)
       ids[(size_t)i] = (int32_t)tokens[i];
     if (sizeof(T) == 4) {
-      if (int rc = b200_model_prefill(s.model, ids.data(), n_rows, 0, reinterpret_cast<float *>(logits_out), 1, nullptr))
+      // [rows, vocab] f32 is hundreds of megabytes: pinned for the duration of the copy, the
+      // device-to-host transfer runs at link speed instead of through a bounce buffer
+      const size_t bytes = (size_t)n_rows * cfg->vocab * 4;
+      const bool pinned = bytes >= ((size_t)32 << 20) &&
+                          cudaHostRegister(logits_out, bytes, cudaHostRegisterDefault) == cudaSuccess;
+      if (!pinned)
+        (void)cudaGetLastError();
+      const int rc = b200_model_prefill(s.model, ids.data(), n_rows, 0, reinterpret_cast<float *>(logits_out), 1, nullptr);
+      if (pinned)
+        cudaHostUnregister(logits_out);
+      if (rc)
         return rc;
     } else {
       std::vector<float> lf((size_t)n_rows * cfg->vocab);
