@@ -97,6 +97,8 @@ def load():
         "b200_model_set_linear": (i32, [vp, i32, i32, i32, vp, vp, i32, i32, i64,
                                         i64, i32, i32]),
         "b200_model_load_blobs": (i32, [vp, C.c_char_p, vp, i64, vp, i64, i32]),
+        "b200_model_set_activation_int8": (i32, [vp, i32]),
+        "b200_model_activation_int8": (i32, [vp]),
         "b200_model_save_packed": (i32, [vp, C.c_char_p]),
         "b200_model_set_launch_counter": (i32, [vp, C.c_uint32]),
         "b200_model_load_packed": (i32, [vp, C.c_char_p]),

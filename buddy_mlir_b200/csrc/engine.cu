@@ -307,6 +307,8 @@ struct b200_model {
   long long *d_trace = nullptr;
   // prefill (many rows at once): activations of all rows, grown on demand
   float *pf_x = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_mid = nullptr, *pf_logits = nullptr;
+  float *pf_norm = nullptr, *pf_tmp = nullptr;   // W8A8 only: normalised rows, a projection's raw result
+  bool act_int8 = false;   // the w8a8 variant: int8 projections quantise their activations per call
   void *pf_ws = nullptr;
   int32_t *pf_tokens = nullptr;
   int pf_rows = 0, pf_logit_rows = 0;
@@ -897,7 +899,7 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
   cudaFree(m->ll_buf); cudaFree(m->d_trace);
   cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_logits);
-  cudaFree(m->pf_ws); cudaFree(m->pf_tokens);
+  cudaFree(m->pf_ws); cudaFree(m->pf_tokens); cudaFree(m->pf_norm); cudaFree(m->pf_tmp);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
   if (m->h_rows_pinned) cudaFreeHost(m->h_rows_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
@@ -1102,8 +1104,9 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
     // the packed-decode spec, frontend/Python/graph/transform/pack_decode_weights.py:32-124)
     // f16: the same single blob with f16 elements (models/deepseek_r1/specs/f16.json)
     nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
-  } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16")) {
-    // w8a16: the same split, n_float counts f16 elements (models/deepseek_r1/specs/w8a16.json)
+  } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16") || !strcmp(variant, "w8a8")) {
+    // w8a16: the same split, n_float counts f16 elements (models/deepseek_r1/specs/w8a16.json);
+    // w8a8: the files of w8a32 (tools/buddy-codegen/gen_config.py:63-66), the graph differs
     ni = c.n_layers * quant_layer + H * V;
     nf = common + c.n_layers * (small_layer + qkv) +
          c.n_layers * (H + 2 * F + H) + V;  // + one scale per quantised column
@@ -1131,7 +1134,10 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   int64_t want_f = 0, want_i = 0;
   if (int rc = b200_blob_elements(&c, variant, &want_f, &want_i)) return rc;
   const bool w8h = !strcmp(variant, "w8a16");
-  const bool w8 = !strcmp(variant, "w8a32") || w8h, w4 = !strcmp(variant, "w4a16");
+  const bool w8q = !strcmp(variant, "w8a8");
+  const bool w8 = !strcmp(variant, "w8a32") || w8h || w8q, w4 = !strcmp(variant, "w4a16");
+  if (w8q && m->tp != 1)
+    return fail(B200_EINVAL, "load_blobs(w8a8): single-GPU sessions only");
   if (n_float != want_f || ((w8 || w4) && (n_int != want_i || !int_blob)))
     return fail(B200_EINVAL,
                 "load_blobs(%s): expected %lld float / %lld int8 elements, got %lld / %lld",
@@ -1222,8 +1228,20 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
     }
   }
 #undef B200_DO
+  if (rc == B200_OK && w8q)
+    m->act_int8 = true;
   return rc;
 }
+
+int b200_model_set_activation_int8(b200_model *m, int enabled) {
+  if (!m)
+    return fail(B200_EINVAL, "set_activation_int8: null model");
+  if (enabled && m->tp != 1)
+    return fail(B200_ESTATE, "set_activation_int8: single-GPU sessions only");
+  m->act_int8 = enabled != 0;
+  return B200_OK;
+}
+int b200_model_activation_int8(const b200_model *m) { return m && m->act_int8 ? 1 : 0; }
 
 // Staging buffers for the peer-store sums: allocate this rank's, trade CUDA IPC
 // handles through NCCL, map the peers'.  All ranks agree (a min-reduction) on
@@ -1583,6 +1601,8 @@ int b200_model_kv_download(b200_model *m, int buffer, float *host, int pos0,
   return kv_copy(m, buffer, host, pos0, n_pos, false);
 }
 
+static int decode_row_int8(b200_model *m, int token, int pos, float *logits_host, int *next_token);
+
 int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
                       int *next_token) {
   if (!m)
@@ -1591,6 +1611,8 @@ int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
     return fail(B200_ESTATE, "decode: call b200_model_finalize first");
   if (token < 0 || token >= m->cfg.vocab || pos < 0 || pos >= m->cfg.max_len)
     return fail(B200_EINVAL, "decode: token %d / position %d out of range", token, pos);
+  if (m->act_int8)
+    return decode_row_int8(m, token, pos, logits_host, next_token);
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   if (int rc = run_step(m)) return rc;
@@ -1631,6 +1653,17 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
     return fail(B200_EINVAL, "generate: %d steps from position %d exceed max_len %d",
                 steps, pos, m->cfg.max_len);
   m->rows_fresh = false;
+  if (m->act_int8) {   // one row per step through the row path, the next token fed back by the host
+    float ms = 0.f;
+    for (int s = 0; s < steps; ++s) {
+      int next = 0;
+      if (int rc = decode_row_int8(m, s == 0 ? token : tokens_out[s - 1], pos + s, nullptr, &next)) return rc;
+      tokens_out[s] = next;
+      ms += m->last_ms;
+    }
+    m->last_ms = ms;
+    return B200_OK;
+  }
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   for (int s = 0; s < steps; ++s)
@@ -1644,10 +1677,75 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
   return check_step_error(m);
 }
 
+// y = r + t over M rows of N (the residual sum after a W8A8 projection)
+__global__ void add_rows_kernel(const float *__restrict__ t, const float *r, int64_t ldr, float *y, int64_t ldy,
+                                int64_t N, int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / N, col = i - row * N;
+    y[row * ldy + col] = __fadd_rn(r[row * ldr + col], t[i]);
+  }
+}
+// y[row, j] = silu(t[row, 2j]) * t[row, 2j + 1]: gate and up interleaved by output column
+// (subgraph0_decode_simplify.mlir:226-231)
+__global__ void silu_pairs_rows_kernel(const float2 *__restrict__ t, float *y, int64_t ldy, int64_t half,
+                                       int64_t total) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = i / half, col = i - row * half;
+    const float2 gu = t[i];
+    const float s = 1.0f / (1.0f + expf(-gu.x));
+    y[row * ldy + col] = __fmul_rn(__fmul_rn(gu.x, s), gu.y);
+  }
+}
+// the K/V rows a one-row pass wrote at `pos`, gathered as [2 * layers][kv_heads * D] (what the
+// decode step's own staging area holds for b200_model_read_new_kv_rows)
+__global__ void gather_kv_row_kernel(float *const *kv, float *stage, int max_len, int D, int n, int pos) {
+  const int b = blockIdx.x;                       // n = kv_heads * D
+  for (int i = threadIdx.x; i < n; i += blockDim.x) {
+    const int h = i / D, d = i - h * D;
+    stage[(size_t)b * n + i] = kv[b][((size_t)h * max_len + pos) * D + d];
+  }
+}
+
+// A W8A8 projection over M rows (QuantizedMatmulOp / QuantizedAddMMOp of the w8a8 graphs,
+// frontend/Python/graph/transform/quantization/passes.py:54-140): the normalised rows are one
+// activation tensor with one dynamic scale; norm, residual and SiLU stay f32 operations beside it.
+static int linear_rows_int8(b200_model *m, const DevLinear &L, const float *X, int64_t ldx, int M, float *Y,
+                            int64_t ldy, const float *residual, const float *norm_w, bool silu) {
+  cudaStream_t st = m->stream;
+  const int64_t K = L.w.K, N = L.w.N;
+  const float *A = X;
+  int64_t lda = ldx;
+  if (norm_w) {
+    if (ldx != K)
+      return fail(B200_EINVAL, "w8a8 projection: normalised rows must be contiguous");
+    if (int rc = b200_rmsnorm(X, norm_w, m->pf_norm, M, K, m->cfg.eps, st)) return rc;
+    A = m->pf_norm;
+    lda = K;
+  }
+  const bool staged = residual || silu;
+  if (int rc = b200_gemm_w8a8(&L.w, A, M, lda, staged ? m->pf_tmp : Y, staged ? N : ldy, m->pf_ws, m->pf_ws_bytes, st))
+    return rc;
+  if (!staged)
+    return B200_OK;
+  const int64_t total = silu ? (int64_t)M * (N / 2) : (int64_t)M * N;
+  const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 16);
+  if (silu)
+    silu_pairs_rows_kernel<<<blocks, 256, 0, st>>>((const float2 *)m->pf_tmp, Y, ldy, N / 2, total);
+  else
+    add_rows_kernel<<<blocks, 256, 0, st>>>(m->pf_tmp, residual, ldy, Y, ldy, N, total);
+  B200_LAUNCH_CHECK();
+  return B200_OK;
+}
+
 // One projection over M rows: the dense tensor-core GEMM for int8 per-channel
 // weights, else the GEMV kernel sixteen rows at a time.
 static int linear_rows(b200_model *m, const DevLinear &L, const float *X, int64_t ldx, int M, float *Y,
                        int64_t ldy, const float *residual, const float *norm_w, bool silu) {
+  if (m->act_int8 && L.w.kind == B200_W_I8 && L.w.scale_dtype == B200_F32) {
+    if (L.w.K % 64 != 0)
+      return fail(B200_EINVAL, "w8a8 projection: K = %lld is not a multiple of 64", (long long)L.w.K);
+    return linear_rows_int8(m, L, X, ldx, M, Y, ldy, residual, norm_w, silu);
+  }
   if (L.w.kind == B200_W_I8 && L.w.scale_dtype == B200_F32 && L.w.K % 64 == 0)
     return b200_gemm_w8(&L.w, X, M, ldx, Y, ldy, residual, ldy, norm_w, m->cfg.eps, silu ? 1 : 0, m->pf_ws,
                         m->pf_ws_bytes, m->stream);
@@ -1673,16 +1771,18 @@ static int prefill_reserve(b200_model *m, int rows, int logit_rows) {
   const b200_model_config &c = m->cfg;
   const int D = c.head_dim;
   const int64_t QKV = (int64_t)(m->qh + 2 * m->kvh) * D;
-  if (rows > m->pf_rows) {
+  if (m->act_int8 && !m->pf_norm && rows < m->pf_rows)   // switched on after a first pass: regrow with its buffers
+    rows = m->pf_rows;
+  if (rows > m->pf_rows || (m->act_int8 && !m->pf_norm)) {
     cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_ws);
-    cudaFree(m->pf_tokens);
-    m->pf_x = m->pf_qkv = m->pf_att = m->pf_mid = nullptr;
+    cudaFree(m->pf_tokens); cudaFree(m->pf_norm); cudaFree(m->pf_tmp);
+    m->pf_x = m->pf_qkv = m->pf_att = m->pf_mid = m->pf_norm = m->pf_tmp = nullptr;
     m->pf_ws = nullptr;
     m->pf_tokens = nullptr;
     m->pf_rows = 0;
     int64_t Kmax = c.hidden > m->ffn ? c.hidden : m->ffn;
     if ((int64_t)m->qh * D > Kmax) Kmax = (int64_t)m->qh * D;
-    m->pf_ws_bytes = b200_gemm_w8_workspace_bytes(rows, Kmax);
+    m->pf_ws_bytes = std::max(b200_gemm_w8_workspace_bytes(rows, Kmax), b200_gemm_w8a8_workspace_bytes(rows, Kmax));
     if (int rc = dev_alloc((void **)&m->pf_x, (size_t)rows * c.hidden * 4)) return rc;
     if (int rc = dev_alloc((void **)&m->pf_qkv, (size_t)rows * QKV * 4)) return rc;
     if (int rc = dev_alloc((void **)&m->pf_att, (size_t)rows * m->qh * D * 4)) return rc;
@@ -1690,6 +1790,11 @@ static int prefill_reserve(b200_model *m, int rows, int logit_rows) {
     if (int rc = dev_alloc(&m->pf_ws, (size_t)m->pf_ws_bytes)) return rc;
     B200_CUDA(cudaMemset(m->pf_ws, 0, 256));   // the GEMM's error word (float projections never touch it)
     if (int rc = dev_alloc((void **)&m->pf_tokens, (size_t)rows * 4)) return rc;
+    if (m->act_int8) {
+      const int64_t Nmax = 2 * (int64_t)m->ffn > c.hidden ? 2 * (int64_t)m->ffn : c.hidden;
+      if (int rc = dev_alloc((void **)&m->pf_norm, (size_t)rows * c.hidden * 4)) return rc;
+      if (int rc = dev_alloc((void **)&m->pf_tmp, (size_t)rows * Nmax * 4)) return rc;
+    }
     m->pf_rows = rows;
   }
   if (logit_rows > m->pf_logit_rows) {
@@ -1718,7 +1823,8 @@ int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens, int p
       return fail(B200_EINVAL, "prefill: token %d at row %d out of range", tokens[i], i);
   const int M = n_tokens, D = c.head_dim, H = c.hidden;
   const int64_t QD = (int64_t)m->qh * D, KD = (int64_t)m->kvh * D, QKV = QD + 2 * KD;
-  const int logit_rows = (all_rows && logits_host) ? M : 1;
+  // w8a8: the activation scale of the last projection belongs to all rows, so all of them are computed
+  const int logit_rows = ((all_rows && logits_host) || m->act_int8) ? M : 1;
   if (int rc = prefill_reserve(m, M, logit_rows)) return rc;
   cudaStream_t st = m->stream;
   B200_CUDA(cudaEventRecord(m->ev0, st));
@@ -1751,8 +1857,10 @@ int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens, int p
   m->h_state_pinned[1] = pos0 + M;
   B200_CUDA(cudaMemcpyAsync(m->d_state + 1, m->h_state_pinned + 1, 4, cudaMemcpyHostToDevice, st));
   B200_CUDA(cudaEventRecord(m->ev1, st));
-  if (logits_host)
+  if (logits_host && all_rows)
     B200_CUDA(cudaMemcpyAsync(logits_host, m->pf_logits, (size_t)logit_rows * c.vocab * 4, cudaMemcpyDeviceToHost, st));
+  else if (logits_host)
+    B200_CUDA(cudaMemcpyAsync(logits_host, last_logits, (size_t)c.vocab * 4, cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaMemcpyAsync(m->h_state_pinned, m->d_state, 32, cudaMemcpyDeviceToHost, st));
   B200_CUDA(cudaStreamSynchronize(st));
   B200_CUDA(cudaEventElapsedTime(&m->last_ms, m->ev0, m->ev1));
@@ -1760,6 +1868,19 @@ int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens, int p
   if (int rc = b200_gemm_w8_status(m->pf_ws, st)) return rc;
   if (next_token)
     *next_token = m->h_state_pinned[2];
+  return B200_OK;
+}
+
+// A decode step of the w8a8 variant: one row through the row path (every int8 projection
+// quantises its one-row activation tensor), then the new K/V rows are staged the way the
+// decode step's own kernels leave them.
+static int decode_row_int8(b200_model *m, int token, int pos, float *logits_host, int *next_token) {
+  const int32_t t = token;
+  if (int rc = b200_model_prefill(m, &t, 1, pos, logits_host, 0, next_token)) return rc;
+  const int n = m->kvh * m->cfg.head_dim;
+  gather_kv_row_kernel<<<2 * m->cfg.n_layers, n < 1024 ? n : 1024, 0, m->stream>>>(
+      m->kv_dev, m->kv_stage, m->cfg.max_len, m->cfg.head_dim, n, pos);
+  B200_LAUNCH_CHECK();
   return B200_OK;
 }
 

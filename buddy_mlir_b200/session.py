@@ -70,6 +70,11 @@ class ModelSession:
             _lib.check(self.lib.b200_model_save_packed(self._h, str(save_packed).encode()))
         self.finalize()
 
+    def set_activation_int8(self, enabled: bool = True):
+        """Run this session with the arithmetic of the w8a8 graphs: int8 projections quantise
+        their activations, one dynamic scale per activation tensor (load_blobs("w8a8") does it)."""
+        _lib.check(self.lib.b200_model_set_activation_int8(self._h, int(enabled)))
+
     def load_packed(self, path):
         """Fill the model from a repack-cache file (b200_model_save_packed) and finalise."""
         _lib.check(self.lib.b200_model_load_packed(self._h, str(path).encode()))

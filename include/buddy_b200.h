@@ -287,7 +287,9 @@ int b200_model_set_linear(b200_model *m, int layer, int slot, int src_kind,
  * table tools/buddy-codegen/gen_config.py:51-71) and load every tensor.
  * variant: "f32" or "f16" (one blob of f32 / f16 elements), "w8a32" (float blob + int8 blob: o, gate, up,
  * down and lm_head quantised, q/k/v float, scales at the end of the float
- * blob), "w8a16" (the same split, the float blob and the scales as f16) or
+ * blob), "w8a8" (the files of w8a32; the session then quantises the activations of
+ * the int8 projections as well, see b200_model_set_activation_int8), "w8a16"
+ * (the same split, the float blob and the scales as f16) or
  * "w4a16" (f16 blob + nibble-packed signed int4 blob, f16 scales); n_float
  * counts elements of the float blob whatever their width. all_linear_w8 != 0 additionally quantises every remaining f32 linear
  * layer to int8 on the device. */
@@ -295,6 +297,17 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
                           const void *float_blob, int64_t n_float,
                           const void *int_blob, int64_t n_int,
                           int all_linear_w8);
+/* The w8a8 graphs (tools/buddy-codegen/import_model.py:669-675,
+ * frontend/Python/graph/transform/quantization/passes.py:54-140): every int8
+ * per-channel projection becomes QuantizedMatmulOp: its activation tensor
+ * (all rows of a prefill, the one row of a decode step) gets one dynamic int8
+ * scale and the contraction runs on the integer tensor cores (b200_gemm_w8a8).
+ * enabled != 0 routes prefill, decode and generate of this session through
+ * that arithmetic (decode as a one-row pass over the row kernels, not the
+ * persistent decode kernel).  Single-GPU sessions.  Not stored by
+ * b200_model_save_packed: set it again after b200_model_load_packed. */
+int b200_model_set_activation_int8(b200_model *m, int enabled);
+int b200_model_activation_int8(const b200_model *m);
 /* Repack cache (the one-time GPU-layout repack of a model's blobs, kept on disk).
  * save_packed writes the packed device layout of every tensor set so far
  * (quantised, sharded for this tensor-parallel rank) to `path`; call it after

@@ -564,12 +564,81 @@ static void linear(const OrcLinear &L, const float *x, float *y) {
       y[n] = (float)bits_to_f16(yh[(size_t)n]);
     break;
   }
+  case ORC_LIN_W8Q:
+    // the w8a8 variant: the row is the whole activation tensor of a decode step
+    orc_matmul_w8a8(x, (const int8_t *)L.w, (const float *)L.scale, nullptr, y, 1, L.K, L.N);
+    break;
   default:
     std::abort();
   }
   if (L.bias)
     for (int64_t n = 0; n < L.N; ++n)
       y[n] = L.bias[n] + y[n];
+}
+
+// M rows through one projection: row by row, except where the activation scale
+// belongs to the whole [M, K] tensor
+static void linear_rows(const OrcLinear &L, const float *X, float *Y, int64_t M) {
+  if (L.kind == ORC_LIN_W8Q) {
+    orc_matmul_w8a8(X, (const int8_t *)L.w, (const float *)L.scale, nullptr, Y, M, L.K, L.N);
+    if (L.bias)
+      for (int64_t r = 0; r < M; ++r)
+        for (int64_t n = 0; n < L.N; ++n)
+          Y[r * L.N + n] = L.bias[n] + Y[r * L.N + n];
+    return;
+  }
+  for (int64_t r = 0; r < M; ++r)
+    linear(L, X + r * L.K, Y + r * L.N);
+}
+
+void orc_prefill_rows(const OrcModel *m, const int64_t *tokens, int64_t M, float **kv, float *logits) {
+  const int64_t H = m->hidden, D = m->head_dim, F = m->ffn;
+  const int64_t QD = m->q_heads * D, KD = m->kv_heads * D;
+  std::vector<float> x((size_t)(M * H)), h((size_t)(M * H)), q((size_t)(M * QD)), k((size_t)(M * KD)),
+      v((size_t)(M * KD)), att((size_t)(M * QD)), o((size_t)(M * H)), g((size_t)(M * F)), u((size_t)(M * F)),
+      mid((size_t)(M * F));
+  for (int64_t r = 0; r < M; ++r)
+    std::memcpy(&x[(size_t)(r * H)], m->embed + tokens[r] * H, (size_t)H * sizeof(float));
+  for (int64_t l = 0; l < m->n_layers; ++l) {
+    const OrcLayer &L = m->layers[l];
+    for (int64_t r = 0; r < M; ++r)
+      orc_rmsnorm(&x[(size_t)(r * H)], L.in_norm, &h[(size_t)(r * H)], H, m->eps);
+    linear_rows(L.q, h.data(), q.data(), M);
+    linear_rows(L.k, h.data(), k.data(), M);
+    linear_rows(L.v, h.data(), v.data(), M);
+    float *Kc = kv[2 * l], *Vc = kv[2 * l + 1];
+    for (int64_t r = 0; r < M; ++r) {
+      float *qr = &q[(size_t)(r * QD)], *kr = &k[(size_t)(r * KD)], *vr = &v[(size_t)(r * KD)];
+      if (L.q_norm)
+        for (int64_t i = 0; i < m->q_heads; ++i)
+          orc_rmsnorm(qr + i * D, L.q_norm, qr + i * D, D, m->eps);
+      if (L.k_norm)
+        for (int64_t i = 0; i < m->kv_heads; ++i)
+          orc_rmsnorm(kr + i * D, L.k_norm, kr + i * D, D, m->eps);
+      orc_rope(qr, m->q_heads, D, m->inv_freq, r);
+      orc_rope(kr, m->kv_heads, D, m->inv_freq, r);
+      for (int64_t i = 0; i < m->kv_heads; ++i) {
+        std::memcpy(Kc + (i * m->max_len + r) * D, kr + i * D, (size_t)D * sizeof(float));
+        std::memcpy(Vc + (i * m->max_len + r) * D, vr + i * D, (size_t)D * sizeof(float));
+      }
+    }
+    for (int64_t r = 0; r < M; ++r)   // causal: row r sees keys 0..r
+      orc_gqa_decode(&q[(size_t)(r * QD)], Kc, Vc, &att[(size_t)(r * QD)], m->q_heads, m->kv_heads, m->max_len, D, r);
+    linear_rows(L.o, att.data(), o.data(), M);
+    for (int64_t i = 0; i < M * H; ++i)
+      x[(size_t)i] = x[(size_t)i] + o[(size_t)i];
+    for (int64_t r = 0; r < M; ++r)
+      orc_rmsnorm(&x[(size_t)(r * H)], L.post_norm, &h[(size_t)(r * H)], H, m->eps);
+    linear_rows(L.gate, h.data(), g.data(), M);
+    linear_rows(L.up, h.data(), u.data(), M);
+    orc_silu_mul(g.data(), u.data(), mid.data(), M * F);
+    linear_rows(L.down, mid.data(), o.data(), M);
+    for (int64_t i = 0; i < M * H; ++i)
+      x[(size_t)i] = x[(size_t)i] + o[(size_t)i];
+  }
+  for (int64_t r = 0; r < M; ++r)
+    orc_rmsnorm(&x[(size_t)(r * H)], m->final_norm, &h[(size_t)(r * H)], H, m->eps);
+  linear_rows(m->lm_head, h.data(), logits, M);
 }
 
 void orc_decode_step(const OrcModel *m, int64_t token, int64_t pos, float **kv,

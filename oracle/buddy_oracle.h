@@ -116,7 +116,7 @@ int64_t orc_kv_overflow(float **kv, int64_t n_buffers, int64_t kv_heads,
                         int64_t keep, float theta);
 
 /* ---- whole decode step -------------------------------------------------- */
-enum { ORC_LIN_F32 = 0, ORC_LIN_W8 = 1, ORC_LIN_W4G = 2, ORC_LIN_W4 = 3, ORC_LIN_W8H = 4 };   /* W4: signed nibbles, per-channel f16 scale, f16 accumulation (w4a16); W8H: int8, f16 scale, f16 activations and accumulation (w8a16) */
+enum { ORC_LIN_F32 = 0, ORC_LIN_W8 = 1, ORC_LIN_W4G = 2, ORC_LIN_W4 = 3, ORC_LIN_W8H = 4, ORC_LIN_W8Q = 5 };   /* W4: signed nibbles, per-channel f16 scale, f16 accumulation (w4a16); W8H: int8, f16 scale, f16 activations and accumulation (w8a16); W8Q: int8 weights and dynamically quantised int8 activations, one scale per activation tensor (w8a8, orc_matmul_w8a8) */
 
 typedef struct {
   int32_t kind;       /* ORC_LIN_* */
@@ -148,6 +148,14 @@ typedef struct {
  * updated in place at row pos. logits: [vocab]. */
 void orc_decode_step(const OrcModel *m, int64_t token, int64_t pos, float **kv,
                      float *logits);
+/* The prefill graph over M rows at positions 0..M-1 (the same operations as the
+ * decode step, row-batched; tools/buddy-codegen/import_model.py:640-680 builds
+ * both graphs from one model).  It differs from M decode steps only where an
+ * operation looks at the whole activation tensor: a W8Q projection takes its
+ * activation scale over all M rows (frontend/Python/ops/linalg.py:12728-12846).
+ * kv rows 0..M-1 are written; logits: [M, vocab]. */
+void orc_prefill_rows(const OrcModel *m, const int64_t *tokens, int64_t M,
+                      float **kv, float *logits);
 /* Number of OpenMP threads the routines above will use. */
 int orc_num_threads(void);
 

@@ -8,7 +8,7 @@ ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
 _SO = os.path.join(ROOT, "oracle", "_build", "libbuddy_oracle.so")
 _REF_SO = os.path.join(ROOT, "oracle", "_ref", "libbuddy_ref_host.so")
 
-LIN_F32, LIN_W8, LIN_W4G, LIN_W4, LIN_W8H = 0, 1, 2, 3, 4
+LIN_F32, LIN_W8, LIN_W4G, LIN_W4, LIN_W8H, LIN_W8Q = 0, 1, 2, 3, 4, 5
 
 
 class OrcLinear(C.Structure):
@@ -266,9 +266,9 @@ class OracleModel:
             if kind == "f32":
                 L.kind = LIN_F32
                 L.w = hold(W, np.float32).ctypes.data
-            elif kind == "w8":
+            elif kind in ("w8", "w8q"):     # w8q: the reference's w8a8, int8 activations as well
                 Q, s = quantised.get((name, layer)) or quantize_per_channel(W, 8)
-                L.kind = LIN_W8
+                L.kind = LIN_W8 if kind == "w8" else LIN_W8Q
                 L.w = hold(Q, np.int8).ctypes.data
                 L.scale = hold(s, np.float32).ctypes.data
             elif kind == "w4":      # the reference's w4a16: signed nibbles, per-channel f16 scale
@@ -319,6 +319,14 @@ class OracleModel:
                    for _ in range(2 * cfg.n_layers)]
         self.kv_arr = _kv_ptr_array(self.kv)
         self.position = 0
+
+    def prefill(self, tokens):
+        """The prefill graph over len(tokens) rows from position 0: logits [rows, vocab]."""
+        toks = np.ascontiguousarray(tokens, dtype=np.int64)
+        logits = np.empty((len(toks), self.cfg.vocab), dtype=np.float32)
+        lib().orc_prefill_rows(C.byref(self.m), toks.ctypes.data_as(C.c_void_p), i64(len(toks)), self.kv_arr, _p(logits))
+        self.position = len(toks)
+        return logits
 
     def decode(self, token, pos=None):
         pos = self.position if pos is None else pos

@@ -180,3 +180,30 @@ def test_w8a8_restatement_matches_a_stepwise_numpy_evaluation():
     if f(2.5) * (f(1.0) / s2) == f(2.5):                               # only when the scale is exactly 1
         got = orc.matmul_w8a8(A2, np.eye(64, dtype=np.int8), np.ones(64, dtype=np.float32))
         assert got[0, 1] == f(2.0) * s2 and got[0, 2] == f(4.0) * s2
+
+
+def test_prefill_rows_is_the_decode_graph_row_by_row_except_for_tensor_wide_scales():
+    """orc_prefill_rows: bit-identical to decode steps for float and weight-only projections;
+    a w8a8 projection takes its activation scale over all rows, so one row equals the decode
+    step and many rows differ from it by quantisation noise only."""
+    from buddy_mlir_b200 import TINY_QWEN2, synthetic
+    cfg = TINY_QWEN2
+    _, views = synthetic.make_f32_blob(cfg, 21)
+    toks = [int(t) for t in synthetic.prompt_tokens(cfg, 3, 9)]
+    for kinds in ({}, {n: "w8" for n in synthetic.QUANTISED_BY_REFERENCE}):
+        a, b = orc.OracleModel(cfg, views, kinds=kinds), orc.OracleModel(cfg, views, kinds=kinds)
+        rows = a.prefill(toks)
+        for i, t in enumerate(toks):
+            assert np.array_equal(rows[i], b.decode(t))
+        for ka, kb in zip(a.kv, b.kv):
+            assert np.array_equal(ka, kb)
+    q = {n: "w8q" for n in synthetic.QUANTISED_BY_REFERENCE}
+    a, b = orc.OracleModel(cfg, views, kinds=q), orc.OracleModel(cfg, views, kinds=q)
+    assert np.array_equal(a.prefill(toks[:1])[0], b.decode(toks[0]))
+    a, b = orc.OracleModel(cfg, views, kinds=q), orc.OracleModel(cfg, views, kinds=q)
+    rows = a.prefill(toks)
+    steps = np.stack([b.decode(t) for t in toks])
+    assert not np.array_equal(rows, steps)
+    w8 = orc.OracleModel(cfg, views, kinds={n: "w8" for n in synthetic.QUANTISED_BY_REFERENCE}).prefill(toks)
+    for x in (rows, steps):     # int8 activations: within a few percent of the weight-only model
+        assert np.abs(x - w8).max() < 0.1 * np.abs(w8).max()
