@@ -29,6 +29,10 @@ int gqa_decode_launch(const float *q, const float *kc, const float *vc,
                       float *out, float *scratch, int q_heads, int kv_heads,
                       int D, int max_len, int splits, const int32_t *pos,
                       cudaStream_t st);
+int quantize_row_launch(const float *x, const float *norm_w, float eps, int64_t K, uint32_t *q, float *scale,
+                        cudaStream_t st);
+int gemv_i8_launch(const b200_weight *w, const uint32_t *q, const float *act_scale, const float *residual, float *y,
+                   int silu_pairs, cudaStream_t st);
 int rope_kv_write_launch(float *q, float *k, const float *v, float *k_cache,
                          float *v_cache, const float *inv_freq,
                          const float *q_norm, const float *k_norm, float eps,
@@ -309,6 +313,11 @@ struct b200_model {
   float *pf_x = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_mid = nullptr, *pf_logits = nullptr;
   float *pf_norm = nullptr, *pf_tmp = nullptr;   // W8A8 only: normalised rows, a projection's raw result
   bool act_int8 = false;   // the w8a8 variant: int8 projections quantise their activations per call
+  uint32_t *q_row = nullptr;   // decode: the quantised activation row of the current projection
+  float *q_scale = nullptr;    //         and its scale
+  cudaGraph_t graph_q = nullptr;      // the decode step with int8 activations, captured on first use
+  cudaGraphExec_t exec_q = nullptr;
+  int kernels_per_step_q = 0;
   void *pf_ws = nullptr;
   int32_t *pf_tokens = nullptr;
   int pf_rows = 0, pf_logit_rows = 0;
@@ -453,6 +462,20 @@ int gemv_tp_sum(b200_model *m, const DevLinear &L, const float *input, int index
   return B200_OK;
 }
 
+// One projection of a single-GPU decode step: under the w8a8 arithmetic an int8 per-channel layer
+// quantises its input row (after the fused RMSNorm) and contracts in integers; everything else
+// takes the float GEMV.
+int proj(b200_model *m, const DevLinear &L, const float *x, float *y, const float *residual, const float *norm_w,
+         bool silu) {
+  if (m->act_int8 && L.w.kind == B200_W_I8 && L.w.scale_dtype == B200_F32) {
+    if (L.w.K % 64 != 0)
+      return fail(B200_EINVAL, "w8a8 projection: K = %lld is not a multiple of 64", (long long)L.w.K);
+    if (int rc = quantize_row_launch(x, norm_w, m->cfg.eps, L.w.K, m->q_row, m->q_scale, m->stream)) return rc;
+    return gemv_i8_launch(&L.w, m->q_row, m->q_scale, residual, y, silu ? 1 : 0, m->stream);
+  }
+  return gemv(m, L, x, y, residual, norm_w, silu);
+}
+
 // Issue every kernel of one decode step on m->stream.
 int issue_step(b200_model *m, int *n_kernels) {
   const b200_model_config &c = m->cfg;
@@ -466,7 +489,7 @@ int issue_step(b200_model *m, int *n_kernels) {
   for (int l = 0; l < c.n_layers; ++l) {
     Layer &L = m->layers[l];
     float *q = m->qkv, *k = m->qkv + QD, *v = m->qkv + QD + KD;
-    if (int rc = gemv(m, L.qkv, m->x, m->qkv, nullptr, L.in_norm, false)) return rc;
+    if (int rc = proj(m, L.qkv, m->x, m->qkv, nullptr, L.in_norm, false)) return rc;
     if (int rc = rope_kv_write_launch(q, k, v, m->kv[2 * l], m->kv[2 * l + 1],
                                       m->inv_freq, L.q_norm, L.k_norm, c.eps,
                                       m->qh, m->kvh, D, c.max_len, d_pos,
@@ -478,19 +501,19 @@ int issue_step(b200_model *m, int *n_kernels) {
                                    m->splits, d_pos, st))
       return rc;
     if (m->tp == 1) {
-      if (int rc = gemv(m, L.o, m->attn, m->x, m->x, nullptr, false)) return rc;
+      if (int rc = proj(m, L.o, m->attn, m->x, m->x, nullptr, false)) return rc;
     } else {
       if (int rc = gemv_tp_sum(m, L.o, m->attn, 2 * l)) return rc;
     }
-    if (int rc = gemv(m, L.gateup, m->x, m->mid, nullptr, L.post_norm, true)) return rc;
+    if (int rc = proj(m, L.gateup, m->x, m->mid, nullptr, L.post_norm, true)) return rc;
     if (m->tp == 1) {
-      if (int rc = gemv(m, L.down, m->mid, m->x, m->x, nullptr, false)) return rc;
+      if (int rc = proj(m, L.down, m->mid, m->x, m->x, nullptr, false)) return rc;
     } else {
       if (int rc = gemv_tp_sum(m, L.down, m->mid, 2 * l + 1)) return rc;
     }
   }
   if (m->tp == 1) {
-    if (int rc = gemv(m, m->lm_head, m->x, m->logits, nullptr, m->final_norm, false))
+    if (int rc = proj(m, m->lm_head, m->x, m->logits, nullptr, m->final_norm, false))
       return rc;
   } else {
     if (int rc = gemv(m, m->lm_head, m->x, m->logits_shard, nullptr,
@@ -723,7 +746,46 @@ int build_mega(b200_model *m) {
   return B200_OK;
 }
 
+int set_state(b200_model *m, int token, int pos);
+
+// The decode step of the w8a8 arithmetic: the same kernels as the float step except for the int8
+// projections, captured into a graph of its own the first time it is needed.  The caller has
+// set the device state (token, position); the warm-up pass outside capture runs that very step
+// (it writes the K/V row the real step writes again), then the state is put back.
+int run_step_int8(b200_model *m) {
+  if (!m->exec_q) {
+    const b200_model_config &c = m->cfg;
+    int64_t Kmax = c.hidden > m->ffn ? c.hidden : m->ffn;
+    if ((int64_t)m->qh * c.head_dim > Kmax) Kmax = (int64_t)m->qh * c.head_dim;
+    if (!m->q_row) {
+      if (int rc = dev_alloc((void **)&m->q_row, (size_t)Kmax)) return rc;
+      if (int rc = dev_alloc((void **)&m->q_scale, 16)) return rc;
+    }
+    const int token = m->h_state_pinned[0], pos = m->h_state_pinned[1];
+    if (int rc = issue_step(m, &m->kernels_per_step_q)) return rc;
+    B200_CUDA(cudaStreamSynchronize(m->stream));
+    if (int rc = set_state(m, token, pos)) return rc;
+    B200_CUDA(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    int rc = issue_step(m, nullptr);
+    cudaGraph_t g = nullptr;
+    cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+    if (rc != B200_OK) {
+      if (g) cudaGraphDestroy(g);
+      return rc;
+    }
+    if (e != cudaSuccess)
+      return fail(B200_ECUDA, "graph capture (w8a8 step): %s", cudaGetErrorString(e));
+    m->graph_q = g;
+    B200_CUDA(cudaGraphInstantiate(&m->exec_q, m->graph_q, 0));
+  }
+  B200_CUDA(cudaGraphLaunch(m->exec_q, m->stream));
+  count_launch(m->kernels_per_step_q);
+  return B200_OK;
+}
+
 int run_step(b200_model *m) {
+  if (m->act_int8)
+    return run_step_int8(m);
   if (m->mega)
     return mega_launch(m->mp, m->mega_grid, m->mega_smem, m->stream);
   B200_CUDA(cudaGraphLaunch(m->exec, m->stream));
@@ -900,6 +962,9 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->ll_buf); cudaFree(m->d_trace);
   cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_logits);
   cudaFree(m->pf_ws); cudaFree(m->pf_tokens); cudaFree(m->pf_norm); cudaFree(m->pf_tmp);
+  cudaFree(m->q_row); cudaFree(m->q_scale);
+  if (m->exec_q) cudaGraphExecDestroy(m->exec_q);
+  if (m->graph_q) cudaGraphDestroy(m->graph_q);
   if (m->h_logits_pinned) cudaFreeHost(m->h_logits_pinned);
   if (m->h_rows_pinned) cudaFreeHost(m->h_rows_pinned);
   if (m->h_state_pinned) cudaFreeHost(m->h_state_pinned);
@@ -1548,7 +1613,14 @@ int b200_model_finalize(b200_model *m) {
   if (m->tp > 1)
     if (int rc = tp_push_setup(m)) return rc;
   // Warm every kernel once outside capture (sets shared-memory attributes),
-  // then capture the step.
+  // then capture the step.  This is the float-activation step; the step of the w8a8
+  // arithmetic is captured when it is first run.
+  struct FloatStep {
+    b200_model *m;
+    bool saved;
+    explicit FloatStep(b200_model *mm) : m(mm), saved(mm->act_int8) { m->act_int8 = false; }
+    ~FloatStep() { m->act_int8 = saved; }
+  } float_step(m);
   if (int rc = set_state(m, 0, 0)) return rc;
   if (int rc = issue_step(m, &m->kernels_per_step)) return rc;
   B200_CUDA(cudaStreamSynchronize(m->stream));
@@ -1601,8 +1673,6 @@ int b200_model_kv_download(b200_model *m, int buffer, float *host, int pos0,
   return kv_copy(m, buffer, host, pos0, n_pos, false);
 }
 
-static int decode_row_int8(b200_model *m, int token, int pos, float *logits_host, int *next_token);
-
 int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
                       int *next_token) {
   if (!m)
@@ -1611,8 +1681,6 @@ int b200_model_decode(b200_model *m, int token, int pos, float *logits_host,
     return fail(B200_ESTATE, "decode: call b200_model_finalize first");
   if (token < 0 || token >= m->cfg.vocab || pos < 0 || pos >= m->cfg.max_len)
     return fail(B200_EINVAL, "decode: token %d / position %d out of range", token, pos);
-  if (m->act_int8)
-    return decode_row_int8(m, token, pos, logits_host, next_token);
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   if (int rc = run_step(m)) return rc;
@@ -1653,17 +1721,6 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
     return fail(B200_EINVAL, "generate: %d steps from position %d exceed max_len %d",
                 steps, pos, m->cfg.max_len);
   m->rows_fresh = false;
-  if (m->act_int8) {   // one row per step through the row path, the next token fed back by the host
-    float ms = 0.f;
-    for (int s = 0; s < steps; ++s) {
-      int next = 0;
-      if (int rc = decode_row_int8(m, s == 0 ? token : tokens_out[s - 1], pos + s, nullptr, &next)) return rc;
-      tokens_out[s] = next;
-      ms += m->last_ms;
-    }
-    m->last_ms = ms;
-    return B200_OK;
-  }
   if (int rc = set_state(m, token, pos)) return rc;
   B200_CUDA(cudaEventRecord(m->ev0, m->stream));
   for (int s = 0; s < steps; ++s)
@@ -1694,15 +1751,6 @@ __global__ void silu_pairs_rows_kernel(const float2 *__restrict__ t, float *y, i
     const float2 gu = t[i];
     const float s = 1.0f / (1.0f + expf(-gu.x));
     y[row * ldy + col] = __fmul_rn(__fmul_rn(gu.x, s), gu.y);
-  }
-}
-// the K/V rows a one-row pass wrote at `pos`, gathered as [2 * layers][kv_heads * D] (what the
-// decode step's own staging area holds for b200_model_read_new_kv_rows)
-__global__ void gather_kv_row_kernel(float *const *kv, float *stage, int max_len, int D, int n, int pos) {
-  const int b = blockIdx.x;                       // n = kv_heads * D
-  for (int i = threadIdx.x; i < n; i += blockDim.x) {
-    const int h = i / D, d = i - h * D;
-    stage[(size_t)b * n + i] = kv[b][((size_t)h * max_len + pos) * D + d];
   }
 }
 
@@ -1868,19 +1916,6 @@ int b200_model_prefill(b200_model *m, const int32_t *tokens, int n_tokens, int p
   if (int rc = b200_gemm_w8_status(m->pf_ws, st)) return rc;
   if (next_token)
     *next_token = m->h_state_pinned[2];
-  return B200_OK;
-}
-
-// A decode step of the w8a8 variant: one row through the row path (every int8 projection
-// quantises its one-row activation tensor), then the new K/V rows are staged the way the
-// decode step's own kernels leave them.
-static int decode_row_int8(b200_model *m, int token, int pos, float *logits_host, int *next_token) {
-  const int32_t t = token;
-  if (int rc = b200_model_prefill(m, &t, 1, pos, logits_host, 0, next_token)) return rc;
-  const int n = m->kvh * m->cfg.head_dim;
-  gather_kv_row_kernel<<<2 * m->cfg.n_layers, n < 1024 ? n : 1024, 0, m->stream>>>(
-      m->kv_dev, m->kv_stage, m->cfg.max_len, m->cfg.head_dim, n, pos);
-  B200_LAUNCH_CHECK();
   return B200_OK;
 }
 

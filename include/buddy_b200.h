@@ -303,8 +303,10 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
  * (all rows of a prefill, the one row of a decode step) gets one dynamic int8
  * scale and the contraction runs on the integer tensor cores (b200_gemm_w8a8).
  * enabled != 0 routes prefill, decode and generate of this session through
- * that arithmetic (decode as a one-row pass over the row kernels, not the
- * persistent decode kernel).  Single-GPU sessions.  Not stored by
+ * that arithmetic (a decode step quantises each projection's input row and
+ * contracts it by dp4a over the int8 weight rows, as a CUDA graph of its own;
+ * the persistent decode kernel serves the float-activation variants only).
+ * Single-GPU sessions.  Not stored by
  * b200_model_save_packed: set it again after b200_model_load_packed. */
 int b200_model_set_activation_int8(b200_model *m, int enabled);
 int b200_model_activation_int8(const b200_model *m);

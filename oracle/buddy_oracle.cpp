@@ -310,17 +310,30 @@ void orc_matmul_w8a8(const float *A, const int8_t *Q, const float *scale, const 
     v = v < -128.0f ? -128.0f : (v > 127.0f ? 127.0f : v);
     q[(size_t)i] = (int8_t)v;
   }
-#pragma omp parallel for schedule(static)
+  // exact integer sums: the order of the k loop does not matter, so it runs outermost over a
+  // block of columns (contiguous weight rows) instead of striding down one column at a time
+  const int64_t NB = 512, nblocks = (N + NB - 1) / NB;
+#pragma omp parallel for collapse(2) schedule(static)
   for (int64_t m = 0; m < M; ++m)
-    for (int64_t n = 0; n < N; ++n) {
-      int32_t acc = 0;
-      for (int64_t k = 0; k < K; ++k)
-        acc += (int32_t)q[(size_t)(m * K + k)] * (int32_t)Q[k * N + n];
-      const float combined = s * scale[n];
-      float y = (float)acc * combined;
-      if (bias)
-        y = y + bias[n];
-      C[m * N + n] = y;
+    for (int64_t nb = 0; nb < nblocks; ++nb) {
+      const int64_t n0 = nb * NB, nn = std::min(NB, N - n0);
+      int32_t acc[512];
+      for (int64_t j = 0; j < nn; ++j)
+        acc[j] = 0;
+      for (int64_t k = 0; k < K; ++k) {
+        const int32_t a = (int32_t)q[(size_t)(m * K + k)];
+        const int8_t *w = Q + k * N + n0;
+        for (int64_t j = 0; j < nn; ++j)
+          acc[j] += a * (int32_t)w[j];
+      }
+      for (int64_t j = 0; j < nn; ++j) {
+        const int64_t n = n0 + j;
+        const float combined = s * scale[n];
+        float y = (float)acc[j] * combined;
+        if (bias)
+          y = y + bias[n];
+        C[m * N + n] = y;
+      }
     }
 }
 
