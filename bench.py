@@ -467,6 +467,9 @@ def batch_numbers(blob, steps, warmup):
     s.generate(int(toks[0]), 8)
     s.generate(int(toks[1]), 32)
     q_step_ms = s.last_ms() / 32
+    torch.cuda.profiler.start()      # two more steps as a profiler range of their own
+    s.generate(int(toks[2]), 2)
+    torch.cuda.profiler.stop()
     out["w8a8"] = {"prefill_1024": {"ms": q_prefill_ms, "tokens_per_s": cfg.max_len / (q_prefill_ms / 1000.0)},
                    "decode": {"ms_per_step": q_step_ms, "tokens_per_s": 1000.0 / q_step_ms, "context": "520..552",
                               "path": "CUDA graph: row quantisation + dp4a GEMV per projection"}}

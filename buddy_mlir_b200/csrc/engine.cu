@@ -33,6 +33,9 @@ int quantize_row_launch(const float *x, const float *norm_w, float eps, int64_t 
                         cudaStream_t st);
 int gemv_i8_launch(const b200_weight *w, const uint32_t *q, const float *act_scale, const float *residual, float *y,
                    int silu_pairs, cudaStream_t st);
+bool gemv_i8_fusable(int64_t K);
+int gemv_i8_fused_launch(const b200_weight *w, const float *x, const float *norm_w, float eps, const float *residual,
+                         float *y, int silu_pairs, cudaStream_t st);
 int rope_kv_write_launch(float *q, float *k, const float *v, float *k_cache,
                          float *v_cache, const float *inv_freq,
                          const float *q_norm, const float *k_norm, float eps,
@@ -470,6 +473,8 @@ int proj(b200_model *m, const DevLinear &L, const float *x, float *y, const floa
   if (m->act_int8 && L.w.kind == B200_W_I8 && L.w.scale_dtype == B200_F32) {
     if (L.w.K % 64 != 0)
       return fail(B200_EINVAL, "w8a8 projection: K = %lld is not a multiple of 64", (long long)L.w.K);
+    if (gemv_i8_fusable(L.w.K))
+      return gemv_i8_fused_launch(&L.w, x, norm_w, m->cfg.eps, residual, y, silu ? 1 : 0, m->stream);
     if (int rc = quantize_row_launch(x, norm_w, m->cfg.eps, L.w.K, m->q_row, m->q_scale, m->stream)) return rc;
     return gemv_i8_launch(&L.w, m->q_row, m->q_scale, residual, y, silu ? 1 : 0, m->stream);
   }
