@@ -33,7 +33,7 @@ Beside the metric, outside the timed region, the N = 1 line reports
 `gemv_isolated` (the GEMV sweep) and `dense_path` (the same model's prefill of
 2048 tokens, batched decode of 64 sequences over the paged cache, and the
 gate|up GEMM at 1024 rows on the tcgen05 path); `--gemv-only`, `--gemm-only`
-and `--batch-only` print those alone.
+and `--batch-only` print those alone; `--w8a8-only` prints the w8a8 numbers alone.
 """
 import argparse
 import json
@@ -456,8 +456,17 @@ def batch_numbers(blob, steps, warmup):
                             "linear_TFLOP/s": 2048 * flops / (prefill_ms / 1000.0) / 1e12},
            "model": "deepseek-r1-distill-qwen-1.5b architecture, seeded weights"}
     bs.close()
-    # the same weights under the arithmetic of the w8a8 graphs (int8 activations, one dynamic
-    # scale per activation tensor, integer tensor cores): a 1024-row prefill and decode steps
+    out["w8a8"] = w8a8_numbers(s, rng)
+    s.close()
+    return out
+
+
+def w8a8_numbers(s, rng):
+    """The session's weights under the arithmetic of the w8a8 graphs (int8 activations, one
+    dynamic scale per activation tensor): a max_len-row prefill on the integer tensor cores and
+    decode steps of one row (dp4a GEMV per projection, a CUDA graph)."""
+    import torch
+    cfg = s.cfg
     s.set_activation_int8(True)
     toks = rng.integers(0, cfg.vocab, cfg.max_len)
     s.prefill_rows(toks, 0, all_rows=False)
@@ -470,12 +479,30 @@ def batch_numbers(blob, steps, warmup):
     torch.cuda.profiler.start()      # two more steps as a profiler range of their own
     s.generate(int(toks[2]), 2)
     torch.cuda.profiler.stop()
-    out["w8a8"] = {"prefill_1024": {"ms": q_prefill_ms, "tokens_per_s": cfg.max_len / (q_prefill_ms / 1000.0)},
-                   "decode": {"ms_per_step": q_step_ms, "tokens_per_s": 1000.0 / q_step_ms, "context": "520..552",
-                              "path": "CUDA graph: row quantisation + dp4a GEMV per projection"}}
     s.set_activation_int8(False)
+    weight_bytes = 1310195712 + 233373696       # int8 linear layers + lm_head, read once per step
+    return {"prefill_1024": {"ms": q_prefill_ms, "tokens_per_s": cfg.max_len / (q_prefill_ms / 1000.0)},
+            "decode": {"ms_per_step": q_step_ms, "tokens_per_s": 1000.0 / q_step_ms, "context": "520..552",
+                       "weight_GB/s": weight_bytes / (q_step_ms / 1000.0) / 1e9,
+                       "path": "CUDA graph: one dp4a GEMV per projection, the row quantised inside it"}}
+
+
+def run_w8a8_only(args):
+    """--w8a8-only: the w8a8 numbers of the 1.5B int8 model alone (one JSON line; a small
+    device footprint, which keeps a profiler capture of its kernels short)."""
+    import torch
+    from buddy_mlir_b200 import DEEPSEEK_R1_1P5B as cfg, _lib, synthetic
+    from buddy_mlir_b200.session import ModelSession
+    _lib.load()
+    if not torch.cuda.is_available():
+        raise SystemExit("bench.py needs a CUDA device; the library has no CPU path")
+    torch.cuda.set_device(0)
+    blob, _ = synthetic.make_f32_blob(cfg, SEED_W)
+    s = ModelSession(cfg)
+    s.load_blobs("f32", blob, all_linear_w8=True)
+    print(json.dumps({"w8a8": w8a8_numbers(s, np.random.default_rng(SEED_P)),
+                      "model": "deepseek-r1-distill-qwen-1.5b architecture, seeded weights, every linear layer int8"}))
     s.close()
-    return out
 
 
 def run_batch_only(args):
@@ -621,6 +648,7 @@ def main():
     ap.add_argument("--gemv-shape", default=None, help="with --gemv-only: one shape of GEMV_SHAPES")
     ap.add_argument("--gemm-only", action="store_true", help="run only the isolated dense-GEMM sweep (tcgen05 path)")
     ap.add_argument("--batch-only", action="store_true", help="batched decode (64 sequences, paged KV) + a 2048-token prefill")
+    ap.add_argument("--w8a8-only", action="store_true", help="the w8a8 arithmetic on the 1.5B int8 model: prefill and decode")
     ap.add_argument("--gemm-shape", default=None, help="with --gemm-only: one shape of GEMM_SHAPES")
     ap.add_argument("--resident-only", action="store_true",
                     help="skip the isolated-GEMV, end-to-end and CPU legs (for profiler captures)")
@@ -638,6 +666,8 @@ def main():
         return run_gemm_only(args)
     if args.batch_only:
         return run_batch_only(args)
+    if args.w8a8_only:
+        return run_w8a8_only(args)
     if args.gpus == 1 and int(os.environ.get("WORLD_SIZE", "1")) == 1:
         return run_single(args)
     import bench_tp

@@ -279,9 +279,8 @@ int gemv_i8_launch(const b200_weight *w, const uint32_t *q, const float *act_sca
   return B200_OK;
 }
 
-// The fused form: every CTA reads the whole f32 row, which pays up to a few thousand elements
-// (beyond that one quantize_row_kernel launch is cheaper than the copies of its work).
-bool gemv_i8_fusable(int64_t K) { return K <= 4096; }
+// Fits the fused form: the int8 row and its f32 source in 48 KB of shared memory.
+bool gemv_i8_fusable(int64_t K) { return K * 5 <= 48 * 1024; }
 
 // One launch per projection: x (f32, not y) is normalised and quantised inside every CTA.
 int gemv_i8_fused_launch(const b200_weight *w, const float *x, const float *norm_w, float eps, const float *residual,
