@@ -1169,10 +1169,11 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
   const int64_t small_layer = 2 * H;
   const int64_t common = V * H + D / 2 + H;  // embedding, inv_freq, final norm
   int64_t nf = 0, ni = 0;
-  if (!strcmp(variant, "f32") || !strcmp(variant, "f16") || !strcmp(variant, "f32p32")) {
+  if (!strcmp(variant, "f32") || !strcmp(variant, "f16") || !strcmp(variant, "bf16") || !strcmp(variant, "f32p32")) {
     // f32p32: the f32 blob with every matmul weight in 32-column panels (the decode file of
     // the packed-decode spec, frontend/Python/graph/transform/pack_decode_weights.py:32-124)
-    // f16: the same single blob with f16 elements (models/deepseek_r1/specs/f16.json)
+    // f16 / bf16: the same single blob with 16-bit elements (models/deepseek_r1/specs/f16.json;
+    // bf16 = the high halves of the f32 values, tools/buddy-codegen/import_model.py:700-707)
     nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
   } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16") || !strcmp(variant, "w8a8")) {
     // w8a16: the same split, n_float counts f16 elements (models/deepseek_r1/specs/w8a16.json);
@@ -1221,11 +1222,18 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   // of w8a16 are taken from the widened copy (the same values as f32).
   std::vector<float> widened;
   const uint16_t *f16_blob = (const uint16_t *)float_blob;
-  const bool half_blob = w4 || w8h || !strcmp(variant, "f16");
+  const bool bf16_blob = !strcmp(variant, "bf16");
+  const bool half_blob = w4 || w8h || !strcmp(variant, "f16") || bf16_blob;
   if (half_blob) {
     widened.resize((size_t)n_float);
-    for (int64_t i = 0; i < n_float; ++i)
-      widened[(size_t)i] = __half2float(__ushort_as_half(f16_blob[i]));
+    for (int64_t i = 0; i < n_float; ++i) {
+      if (bf16_blob) {
+        const uint32_t u = (uint32_t)f16_blob[i] << 16;
+        memcpy(&widened[(size_t)i], &u, 4);
+      } else {
+        widened[(size_t)i] = __half2float(__ushort_as_half(f16_blob[i]));
+      }
+    }
   }
   const float *fp0 = half_blob ? widened.data() : (const float *)float_blob;
   const float *fp = fp0;

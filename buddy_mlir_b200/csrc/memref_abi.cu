@@ -623,7 +623,8 @@ int session_for(ForwardSession &s, const b200_model_config *cfg, const char *var
   // the blobs are the model: same addresses, sizes and sampled contents = same session.  Every
   // call samples 64 words spread over each blob (a few microseconds beside a millisecond step).
   // n0 counts elements of the float blob: f16 in the f16, w4a16 and w8a16 variants
-  const size_t e0 = (!strcmp(variant, "w4a16") || !strcmp(variant, "w8a16") || !strcmp(variant, "f16")) ? 2 : 4;
+  const size_t e0 = (!strcmp(variant, "w4a16") || !strcmp(variant, "w8a16") || !strcmp(variant, "f16") ||
+                     !strcmp(variant, "bf16")) ? 2 : 4;
   const uint64_t seed = 0xCBF29CE484222325ull;
   uint64_t quick = fingerprint_bytes(w0, (size_t)n0 * e0, seed, 64);
   if (w1)
@@ -681,6 +682,32 @@ inline void from_host(float *dst, const float *src, size_t n) { memcpy(dst, src,
 inline void from_host(float *dst, const uint16_t *src, size_t n) {
   for (size_t i = 0; i < n; ++i)
     dst[i] = __half2float(__ushort_as_half(src[i]));
+}
+// bfloat16 on the host (the bf16 variant): the same 16 bits of storage, another conversion
+struct Bf16 { uint16_t bits; };
+static_assert(sizeof(Bf16) == 2, "Bf16 must alias uint16_t storage");
+inline uint16_t bf16_rn(float f) {       // round to nearest even, as arith.truncf does
+  uint32_t u;
+  memcpy(&u, &f, 4);
+  if ((u & 0x7F800000u) == 0x7F800000u)       // inf / nan: keep the class
+    return (uint16_t)((u >> 16) | ((u & 0xFFFFu) ? 0x40u : 0u));
+  return (uint16_t)((u + 0x7FFFu + ((u >> 16) & 1u)) >> 16);
+}
+inline void to_host(Bf16 *dst, const float *src, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    dst[i].bits = bf16_rn(src[i]);
+}
+inline void from_host(float *dst, const Bf16 *src, size_t n) {
+  for (size_t i = 0; i < n; ++i) {
+    const uint32_t u = (uint32_t)src[i].bits << 16;
+    memcpy(&dst[i], &u, 4);
+  }
+}
+inline bool same_row(const Bf16 *host, const float *shadow, size_t n) {
+  for (size_t i = 0; i < n; ++i)
+    if (host[i].bits != bf16_rn(shadow[i]))
+      return false;
+  return true;
 }
 inline bool same_row(const float *host, const float *shadow, size_t n) { return memcmp(host, shadow, n * 4) == 0; }
 inline bool same_row(const uint16_t *host, const float *shadow, size_t n) {
@@ -874,6 +901,24 @@ int b200_forward_prefill_tier(const b200_model_config *cfg, const char *variant,
                               float *logits_out) {
   return note_status(forward_prefill<float>(cfg, variant, all_linear_w8, w0, n0, w1, n1, tokens, n_rows,
                                             host_kv_out, logits_out, host_len));
+}
+// bfloat16 cache and logits on the host, carried as uint16_t (the reference's bf16 variant,
+// tools/buddy-codegen/gen_config.py:40-44)
+int b200_forward_decode_bf16(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                             const void *w0, int64_t n0, const void *w1, int64_t n1,
+                             long long token, long long pos, uint16_t *const *host_kv,
+                             uint16_t **logits_out) {
+  return note_status(forward_decode<Bf16>(cfg, variant, all_linear_w8, w0, n0, w1, n1, token, pos,
+                                          reinterpret_cast<Bf16 *const *>(host_kv),
+                                          reinterpret_cast<Bf16 **>(logits_out)));
+}
+int b200_forward_prefill_bf16(const b200_model_config *cfg, const char *variant, int all_linear_w8,
+                              const void *w0, int64_t n0, const void *w1, int64_t n1,
+                              const long long *tokens, int n_rows, uint16_t *const *host_kv_out,
+                              uint16_t *logits_out) {
+  return note_status(forward_prefill<Bf16>(cfg, variant, all_linear_w8, w0, n0, w1, n1, tokens, n_rows,
+                                           reinterpret_cast<Bf16 *const *>(host_kv_out),
+                                           reinterpret_cast<Bf16 *>(logits_out)));
 }
 int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant, int all_linear_w8,
                              const void *w0, int64_t n0, const void *w1, int64_t n1,

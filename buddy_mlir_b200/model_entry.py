@@ -35,7 +35,8 @@ class EntrySession:
         self.fn.restype = None
         self.cfg = cfg
         # host element of the cache and the logits: half (as uint16) for the f16-activation variants
-        self.half = variant in ("f16", "w4a16", "w8a16")
+        self.half = variant in ("f16", "bf16", "w4a16", "w8a16")
+        self.bf16 = variant == "bf16"
         self.ht = np.uint16 if self.half else np.float32
         self.blobs = [np.ascontiguousarray(b) for b in blobs]
         if self.half:   # the f16 blob travels as the uint16 memref the reference's session builds
@@ -120,6 +121,8 @@ class EntrySession:
 
     def _floats(self, a):
         """logitsFloat_ of the generated session (gen_session.py:1531: halfToFloat per element)."""
+        if self.bf16:   # bfloat16 = the high half of an f32
+            return (a.astype(np.uint32) << 16).view(np.float32)
         return a.view(np.float16).astype(np.float32) if self.half else a
 
     def _check(self):
@@ -129,8 +132,7 @@ class EntrySession:
             raise _lib.B200Error(lib.b200_last_error().decode())
 
     def kv_floats(self, i):
-        k = self.kv[i]
-        return k.view(np.float16).astype(np.float32) if self.half else k
+        return self._floats(self.kv[i])
 
     def reset_position(self):
         self.position_ = 0

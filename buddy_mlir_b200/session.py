@@ -60,7 +60,10 @@ class ModelSession:
                    all_linear_w8: bool = False, save_packed=None):
         """loadWeights (gen_session.py:1301-1338) for in-memory blobs.
         save_packed: path of a repack-cache file to write before finalising."""
-        fb = np.ascontiguousarray(float_blob, dtype=np.float16 if variant in ("f16", "w4a16", "w8a16") else np.float32)
+        if variant == "bf16":
+            fb = np.ascontiguousarray(float_blob, dtype=np.uint16)     # the high halves of the f32 values
+        else:
+            fb = np.ascontiguousarray(float_blob, dtype=np.float16 if variant in ("f16", "w4a16", "w8a16") else np.float32)
         ib = None if int_blob is None else np.ascontiguousarray(int_blob, dtype=np.int8)
         _lib.check(self.lib.b200_model_load_blobs(
             self._h, variant.encode(), fb.ctypes.data, fb.size,
@@ -83,7 +86,8 @@ class ModelSession:
     def load_weights(self, paths, variant: str, all_linear_w8: bool = False):
         """loadWeights from the reference's files (arg0*.data; table in
         tools/buddy-codegen/gen_config.py:51-71)."""
-        fb = np.fromfile(paths[0], dtype=np.float16 if variant in ("f16", "w4a16", "w8a16") else np.float32)
+        fb = np.fromfile(paths[0], dtype=np.uint16 if variant == "bf16" else
+                         np.float16 if variant in ("f16", "w4a16", "w8a16") else np.float32)
         ib = np.fromfile(paths[1], dtype=np.int8) if len(paths) > 1 else None
         self.load_blobs(variant, fb, ib, all_linear_w8)
 

@@ -285,7 +285,7 @@ int b200_model_set_linear(b200_model *m, int layer, int slot, int src_kind,
 /* Walk buddy-mlir's flat weight blobs (frontend/Python/graph/graph.py:836-863,
  * frontend/Python/graph/transform/quantization/quantize.py:577-589; file
  * table tools/buddy-codegen/gen_config.py:51-71) and load every tensor.
- * variant: "f32" or "f16" (one blob of f32 / f16 elements), "w8a32" (float blob + int8 blob: o, gate, up,
+ * variant: "f32", "f16" or "bf16" (one blob of f32 / f16 / bf16 elements), "w8a32" (float blob + int8 blob: o, gate, up,
  * down and lm_head quantised, q/k/v float, scales at the end of the float
  * blob), "w8a8" (the files of w8a32; the session then quantises the activations of
  * the int8 projections as well, see b200_model_set_activation_int8), "w8a16"

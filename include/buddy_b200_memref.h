@@ -177,6 +177,19 @@ int b200_forward_prefill_f16(const b200_model_config *cfg, const char *variant,
                              const void *w1, int64_t n1, const long long *tokens,
                              int n_rows, uint16_t *const *host_kv_out,
                              uint16_t *logits_out);
+/* And with bfloat16 cache and logits, again carried as uint16_t (the bf16
+ * variant, tools/buddy-codegen/gen_config.py:40-44; values leave the device
+ * session rounded to nearest even). */
+int b200_forward_decode_bf16(const b200_model_config *cfg, const char *variant,
+                             int all_linear_w8, const void *w0, int64_t n0,
+                             const void *w1, int64_t n1, long long token,
+                             long long pos, uint16_t *const *host_kv,
+                             uint16_t **logits_out);
+int b200_forward_prefill_bf16(const b200_model_config *cfg, const char *variant,
+                              int all_linear_w8, const void *w0, int64_t n0,
+                              const void *w1, int64_t n1, const long long *tokens,
+                              int n_rows, uint16_t *const *host_kv_out,
+                              uint16_t *logits_out);
 /* The same two entries for the tiered-cache spec
  * (models/deepseek_r1/specs/f32_tiered_kv_cache.json; gen_session.py:303-800
  * resolves _mlir_ciface_forward_prefill_<size> / _mlir_ciface_forward_decode_<size>

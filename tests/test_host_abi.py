@@ -75,6 +75,9 @@ def test_blob_counts_match_reference_specs():
     # models/deepseek_r1/specs/f16.json: total 1777088064 (f16 elements)
     assert lib.b200_blob_elements(C.byref(c), b"f16", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (1777088064, 0)
+    # the bf16 variant: the same walk with bfloat16 elements (tools/buddy-codegen/gen_config.py:54)
+    assert lib.b200_blob_elements(C.byref(c), b"bf16", C.byref(nf), C.byref(ni)) == 0
+    assert (nf.value, ni.value) == (1777088064, 0)
     # models/deepseek_r1/specs/w8a8.json: linear_elements 1455489024, other_elements 322338752
     assert lib.b200_blob_elements(C.byref(c), b"w8a8", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (322338752, 1455489024)
