@@ -16,7 +16,9 @@
 // copied.  Model shapes: BUDDY_B200_MODEL = a stock name (deepseek_r1_1p5b,
 // tiny_qwen2) or "hidden=..,n_layers=..,q_heads=..,kv_heads=..,head_dim=..,
 // ffn=..,vocab=..,max_len=..[,qkv_bias=0|1]".  RunConfig::weightsPath: one
-// file (f32 variant) or "float.data,int8.data" (w8a32);
+// file (f32 variant) or "float.data,int8.data" (w8a32); BUDDY_B200_VARIANT
+// names another of the reference's variants (f16, bf16, w8a8, w8a16, w4a16:
+// tools/buddy-codegen/gen_config.py:37-71) whose files those then are.
 // BUDDY_B200_ALL_LINEAR_W8=1 quantises every linear layer of an f32 blob on
 // the device.  Prompts are token ids separated by spaces unless
 // BUDDY_B200_TOKENIZER=deepseek_r1 asks for the reference's tokenizer.
@@ -24,6 +26,7 @@
 #include "buddy/runtime/core/InferenceRunner.h"
 #include "buddy/runtime/llm/TextGeneration.h"
 
+#include <algorithm>
 #include <cstdlib>
 #include <cstring>
 #include <fstream>
@@ -106,9 +109,16 @@ public:
   void loadWeights(const std::vector<std::string> &paths) override {
     if (paths.empty() || paths.size() > 2)
       throw std::runtime_error("[buddy_b200] one (f32) or two (w8a32) weight files expected");
+    const char *venv = std::getenv("BUDDY_B200_VARIANT");
+    const std::string variant = venv && venv[0] ? venv : (paths.size() == 1 ? "f32" : "w8a32");
+    const bool two_files = variant == "w8a32" || variant == "w8a8" || variant == "w8a16" || variant == "w4a16";
+    if (two_files != (paths.size() == 2))
+      throw std::runtime_error("[buddy_b200] variant " + variant + " takes " + (two_files ? "two weight files" : "one weight file"));
     const char *cache = std::getenv("BUDDY_B200_PACK_CACHE");
     if (cache && std::ifstream(cache).good()) {
       if (b200_model_load_packed(model_, cache) == 0) {
+        if (variant == "w8a8")     // the arithmetic is not part of the packed weights
+          check(b200_model_set_activation_int8(model_, 1), "set_activation_int8");
         check(b200_model_finalize(model_), "finalize");
         return;
       }
@@ -117,15 +127,19 @@ public:
       model_ = nullptr;
       check(b200_model_create(&cfg_, &model_), "model_create");
     }
-    const std::vector<float> fb = read_file<float>(paths[0]);
+    // the float blob holds 16-bit elements in the f16-activation variants and in bf16
+    const size_t fsize = (variant == "f32" || variant == "w8a32" || variant == "w8a8") ? 4 : 2;
+    const std::vector<char> fb = read_file<char>(paths[0]);
     const char *all = std::getenv("BUDDY_B200_ALL_LINEAR_W8");
-    if (paths.size() == 1) {
-      check(b200_model_load_blobs(model_, "f32", fb.data(), (int64_t)fb.size(), nullptr, 0, all && all[0] == '1'),
-            "load_blobs(f32)");
+    if (!two_files) {
+      check(b200_model_load_blobs(model_, variant.c_str(), fb.data(), (int64_t)(fb.size() / fsize), nullptr, 0,
+                                  variant == "f32" && all && all[0] == '1'),
+            "load_blobs");
     } else {
       const std::vector<int8_t> ib = read_file<int8_t>(paths[1]);
-      check(b200_model_load_blobs(model_, "w8a32", fb.data(), (int64_t)fb.size(), ib.data(), (int64_t)ib.size(), 0),
-            "load_blobs(w8a32)");
+      check(b200_model_load_blobs(model_, variant.c_str(), fb.data(), (int64_t)(fb.size() / fsize), ib.data(),
+                                  (int64_t)ib.size(), 0),
+            "load_blobs");
     }
     if (cache && b200_model_save_packed(model_, cache) != 0)
       std::cerr << "[buddy_b200] the pack cache was not written: " << b200_last_error() << "\n";
@@ -137,11 +151,18 @@ public:
     const int n = (int)tokens.getTokenCnt();
     if (n < 1 || n > cfg_.max_len)
       throw std::runtime_error("[buddy_b200] prompt length outside 1..max_len");
-    std::vector<int32_t> ids((size_t)n);
-    for (int i = 0; i < n; ++i)
+    // The w8a8 prefill graph takes its activation scales over every row of the token container,
+    // padding included (gen_session.py:1345-1373 passes the whole container), so all of it runs.
+    int rows = n;
+    if (b200_model_activation_int8(model_))
+      rows = (int)std::min<size_t>(tokens.getSize(), (size_t)cfg_.max_len);
+    if (rows < n)
+      rows = n;
+    std::vector<int32_t> ids((size_t)rows);
+    for (int i = 0; i < rows; ++i)
       ids[(size_t)i] = (int32_t)tokens.getData()[i];
-    prefill_rows_.assign((size_t)n * cfg_.vocab, 0.f);
-    check(b200_model_prefill(model_, ids.data(), n, 0, prefill_rows_.data(), 1, nullptr), "prefill");
+    prefill_rows_.assign((size_t)rows * cfg_.vocab, 0.f);
+    check(b200_model_prefill(model_, ids.data(), rows, 0, prefill_rows_.data(), 1, nullptr), "prefill");
     position_ = n;
     last_is_decode_ = false;
   }

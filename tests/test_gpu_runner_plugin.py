@@ -21,17 +21,18 @@ PLUGIN = os.path.join(ROOT, "buddy_mlir_b200", "libbuddy_b200_runner.so")
 
 @pytest.mark.skipif(not (os.path.exists(HOST) and os.path.exists(PLUGIN)),
                     reason="the plugin and its host are built where a buddy-mlir checkout is present")
-@pytest.mark.parametrize("variant", ["f32", "w8a32"])
+@pytest.mark.parametrize("variant", ["f32", "w8a32", "w8a8"])
 def test_runner_plugin_generates_the_checkers_tokens(tmp_path, variant):
     cfg = TINY_QWEN2
     blob, views = synthetic.make_f32_blob(cfg, 91)
-    if variant == "w8a32":
+    if variant in ("w8a32", "w8a8"):     # the same two files; w8a8 quantises the activations as well
         fb, ib = synthetic.split_w8a32(cfg, views, lambda W: orc.quantize_per_channel(W, 8))
-        fpath, ipath = tmp_path / "arg0-w8a32-f32.data", tmp_path / "arg0-w8a32-i8.data"
+        fpath, ipath = tmp_path / f"arg0-{variant}-f32.data", tmp_path / f"arg0-{variant}-i8.data"
         fb.tofile(fpath)
         ib.tofile(ipath)
         weights = f"{fpath},{ipath}"
-        om = orc.OracleModel(cfg, views, kinds={n: "w8" for n in synthetic.QUANTISED_BY_REFERENCE})
+        kind = "w8" if variant == "w8a32" else "w8q"
+        om = orc.OracleModel(cfg, views, kinds={n: kind for n in synthetic.QUANTISED_BY_REFERENCE})
     else:
         fpath = tmp_path / "arg0.data"
         blob.tofile(fpath)
@@ -41,15 +42,16 @@ def test_runner_plugin_generates_the_checkers_tokens(tmp_path, variant):
     vocab.write_text("".join(f"t{i}\n" for i in range(cfg.vocab)))
     prompt = synthetic.prompt_tokens(cfg, 13, 20)
     max_new = len(prompt) + 12           # runGeneration: maxSteps = maxNewTokens - promptTokens
-    # the checker's greedy continuation
-    for t in prompt:
-        logits = om.decode(int(t))
+    # the checker's greedy continuation (the prefill graph: a w8a8 projection scales over all rows)
+    logits = om.prefill([int(t) for t in prompt])[-1]
     want = [greedy_sample(logits)]
     for _ in range(12):
         want.append(greedy_sample(om.decode(want[-1])))
     # the first run walks the blobs and writes the pack cache, the second one loads it
     cache = tmp_path / "weights.b2pack"
     env = dict(os.environ, BUDDY_B200_MODEL="tiny_qwen2", BUDDY_B200_PACK_CACHE=str(cache))
+    if variant == "w8a8":
+        env["BUDDY_B200_VARIANT"] = "w8a8"
     for run in range(2):
         out = subprocess.run([HOST, PLUGIN, weights, str(vocab), str(max_new), " ".join(str(int(t)) for t in prompt)],
                              env=env, capture_output=True, text=True, timeout=300)
