@@ -1950,6 +1950,10 @@ struct b200_batch {
 static int batch_rows(b200_batch *b, int M, const int32_t *tokens, const int32_t *row_seq, const int32_t *row_pos,
                       bool all_logits, float *logits_host, int32_t *next_host) {
   b200_model *m = b->m;
+  // A w8a8 projection scales its whole activation tensor: rows of unrelated sequences in one
+  // batch would share that scale, and each sequence's result would depend on its neighbours.
+  if (m->act_int8)
+    return fail(B200_ESTATE, "batch: the w8a8 arithmetic is defined per sequence (one prefill or decode tensor at a time)");
   const b200_model_config &c = m->cfg;
   const int D = c.head_dim, H = c.hidden;
   const int64_t QD = (int64_t)m->qh * D, KD = (int64_t)m->kvh * D, QKV = QD + 2 * KD;

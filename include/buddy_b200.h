@@ -306,7 +306,8 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
  * that arithmetic (a decode step quantises each projection's input row and
  * contracts it by dp4a over the int8 weight rows, as a CUDA graph of its own;
  * the persistent decode kernel serves the float-activation variants only).
- * Single-GPU sessions.  Not stored by
+ * Single-GPU sessions; the batched entry points (b200_batch_*) refuse such a
+ * session, since rows of unrelated sequences would share one scale.  Not stored by
  * b200_model_save_packed: set it again after b200_model_load_packed. */
 int b200_model_set_activation_int8(b200_model *m, int enabled);
 int b200_model_activation_int8(const b200_model *m);

@@ -299,6 +299,44 @@ def test_tiny_w8a8_device_session_prefill_and_decode():
     s.close()
 
 
+def test_w8a8_switch_leaves_no_residue_in_a_session_of_the_persistent_kernel():
+    """The same session alternates between the float step (persistent kernel) and the int8 step
+    (its own CUDA graph): after switching back, the float logits are bit for bit those of a
+    session that never switched; the batched entry points refuse a w8a8 session."""
+    from buddy_mlir_b200.session import BatchSession
+    cfg = TINY_MEGA
+    _, views = synthetic.make_f32_blob(cfg, 89)
+    toks = [int(t) for t in synthetic.prompt_tokens(cfg, 10, 6)]
+
+    def fresh():
+        s = ModelSession(cfg)
+        s.load_tensors(views, quantize_to="w8")
+        assert s.uses_persistent_kernel()
+        return s
+    a = fresh()
+    ref = []
+    for t in toks:
+        a.decode(t)
+        ref.append(a.logits_data().copy())
+    a.close()
+    b = fresh()
+    om = orc.OracleModel(cfg, views, kinds={n: "w8q" for n in ALL_LINEAR})
+    b.set_activation_int8(True)
+    for t in toks[:3]:
+        b.decode(t)
+        assert maxrel(b.logits_data(), om.decode(t)) < W8A8_TOL
+    bs = BatchSession(b, max_seqs=2, page_size=16, n_pages=16, max_context=64)
+    with pytest.raises(_lib.B200Error):
+        bs.prefill(bs.add(), toks, want_logits=False)
+    bs.close()
+    b.set_activation_int8(False)
+    b.reset_position()
+    for i, t in enumerate(toks):
+        b.decode(t)
+        assert np.array_equal(b.logits_data(), ref[i]), i
+    b.close()
+
+
 def test_tiny_w8a8_through_the_model_entries():
     """The generated entry pair of the w8a8 spec: the prefill entry quantises over all max_len
     rows of the padded token container, as the reference's prefill graph does."""
