@@ -152,6 +152,10 @@ int gqa_paged_prefill_launch(const float *qkv, int64_t ld, const float *k_pool, 
                              int64_t ldo, int q_heads, int kv_heads, int D, int page, const int32_t *seq_table,
                              int pos0, int M, int max_context, cudaStream_t st);
 int64_t gqa_paged_scratch_floats(int rows, int q_heads, int D, int max_context);
+// gemm_tc.cu: b200_gemm_w8a8 with the residual sum or the SiLU pair folded into the store
+int gemm_w8a8_fused(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
+                    const float *residual, int64_t ldr, int silu_pairs, void *workspace, int64_t workspace_bytes,
+                    cudaStream_t stream);
 int argmax_rows_launch(const float *v, int64_t n, int rows, int32_t *out, cudaStream_t st);
 
 __device__ __forceinline__ float load_as_float(const void *p, int dtype,

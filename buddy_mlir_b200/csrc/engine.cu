@@ -314,7 +314,7 @@ struct b200_model {
   long long *d_trace = nullptr;
   // prefill (many rows at once): activations of all rows, grown on demand
   float *pf_x = nullptr, *pf_qkv = nullptr, *pf_att = nullptr, *pf_mid = nullptr, *pf_logits = nullptr;
-  float *pf_norm = nullptr, *pf_tmp = nullptr;   // W8A8 only: normalised rows, a projection's raw result
+  float *pf_norm = nullptr;   // W8A8 only: the normalised rows of a projection
   bool act_int8 = false;   // the w8a8 variant: int8 projections quantise their activations per call
   uint32_t *q_row = nullptr;   // decode: the quantised activation row of the current projection
   float *q_scale = nullptr;    //         and its scale
@@ -966,7 +966,7 @@ void b200_model_destroy(b200_model *m) {
   cudaFree(m->mega_stream); cudaFree(m->mega_offsets); cudaFree(m->lvec_dev);
   cudaFree(m->ll_buf); cudaFree(m->d_trace);
   cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_logits);
-  cudaFree(m->pf_ws); cudaFree(m->pf_tokens); cudaFree(m->pf_norm); cudaFree(m->pf_tmp);
+  cudaFree(m->pf_ws); cudaFree(m->pf_tokens); cudaFree(m->pf_norm);
   cudaFree(m->q_row); cudaFree(m->q_scale);
   if (m->exec_q) cudaGraphExecDestroy(m->exec_q);
   if (m->graph_q) cudaGraphDestroy(m->graph_q);
@@ -1747,33 +1747,14 @@ int b200_model_generate(b200_model *m, int token, int pos, int steps,
   return check_step_error(m);
 }
 
-// y = r + t over M rows of N (the residual sum after a W8A8 projection)
-__global__ void add_rows_kernel(const float *__restrict__ t, const float *r, int64_t ldr, float *y, int64_t ldy,
-                                int64_t N, int64_t total) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / N, col = i - row * N;
-    y[row * ldy + col] = __fadd_rn(r[row * ldr + col], t[i]);
-  }
-}
-// y[row, j] = silu(t[row, 2j]) * t[row, 2j + 1]: gate and up interleaved by output column
-// (subgraph0_decode_simplify.mlir:226-231)
-__global__ void silu_pairs_rows_kernel(const float2 *__restrict__ t, float *y, int64_t ldy, int64_t half,
-                                       int64_t total) {
-  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = i / half, col = i - row * half;
-    const float2 gu = t[i];
-    const float s = 1.0f / (1.0f + expf(-gu.x));
-    y[row * ldy + col] = __fmul_rn(__fmul_rn(gu.x, s), gu.y);
-  }
-}
-
 // A W8A8 projection over M rows (QuantizedMatmulOp / QuantizedAddMMOp of the w8a8 graphs,
 // frontend/Python/graph/transform/quantization/passes.py:54-140): the normalised rows are one
-// activation tensor with one dynamic scale; norm, residual and SiLU stay f32 operations beside it.
+// activation tensor with one dynamic scale; the norm is an f32 kernel before it, the residual sum
+// or the SiLU pair an f32 operation in the GEMM's store.
 static int linear_rows_int8(b200_model *m, const DevLinear &L, const float *X, int64_t ldx, int M, float *Y,
                             int64_t ldy, const float *residual, const float *norm_w, bool silu) {
   cudaStream_t st = m->stream;
-  const int64_t K = L.w.K, N = L.w.N;
+  const int64_t K = L.w.K;
   const float *A = X;
   int64_t lda = ldx;
   if (norm_w) {
@@ -1783,19 +1764,7 @@ static int linear_rows_int8(b200_model *m, const DevLinear &L, const float *X, i
     A = m->pf_norm;
     lda = K;
   }
-  const bool staged = residual || silu;
-  if (int rc = b200_gemm_w8a8(&L.w, A, M, lda, staged ? m->pf_tmp : Y, staged ? N : ldy, m->pf_ws, m->pf_ws_bytes, st))
-    return rc;
-  if (!staged)
-    return B200_OK;
-  const int64_t total = silu ? (int64_t)M * (N / 2) : (int64_t)M * N;
-  const unsigned blocks = (unsigned)std::min<int64_t>((total + 255) / 256, 148 * 16);
-  if (silu)
-    silu_pairs_rows_kernel<<<blocks, 256, 0, st>>>((const float2 *)m->pf_tmp, Y, ldy, N / 2, total);
-  else
-    add_rows_kernel<<<blocks, 256, 0, st>>>(m->pf_tmp, residual, ldy, Y, ldy, N, total);
-  B200_LAUNCH_CHECK();
-  return B200_OK;
+  return gemm_w8a8_fused(&L.w, A, M, lda, Y, ldy, residual, ldy, silu ? 1 : 0, m->pf_ws, m->pf_ws_bytes, st);
 }
 
 // One projection over M rows: the dense tensor-core GEMM for int8 per-channel
@@ -1836,8 +1805,8 @@ static int prefill_reserve(b200_model *m, int rows, int logit_rows) {
     rows = m->pf_rows;
   if (rows > m->pf_rows || (m->act_int8 && !m->pf_norm)) {
     cudaFree(m->pf_x); cudaFree(m->pf_qkv); cudaFree(m->pf_att); cudaFree(m->pf_mid); cudaFree(m->pf_ws);
-    cudaFree(m->pf_tokens); cudaFree(m->pf_norm); cudaFree(m->pf_tmp);
-    m->pf_x = m->pf_qkv = m->pf_att = m->pf_mid = m->pf_norm = m->pf_tmp = nullptr;
+    cudaFree(m->pf_tokens); cudaFree(m->pf_norm);
+    m->pf_x = m->pf_qkv = m->pf_att = m->pf_mid = m->pf_norm = nullptr;
     m->pf_ws = nullptr;
     m->pf_tokens = nullptr;
     m->pf_rows = 0;
@@ -1851,11 +1820,8 @@ static int prefill_reserve(b200_model *m, int rows, int logit_rows) {
     if (int rc = dev_alloc(&m->pf_ws, (size_t)m->pf_ws_bytes)) return rc;
     B200_CUDA(cudaMemset(m->pf_ws, 0, 256));   // the GEMM's error word (float projections never touch it)
     if (int rc = dev_alloc((void **)&m->pf_tokens, (size_t)rows * 4)) return rc;
-    if (m->act_int8) {
-      const int64_t Nmax = 2 * (int64_t)m->ffn > c.hidden ? 2 * (int64_t)m->ffn : c.hidden;
+    if (m->act_int8)
       if (int rc = dev_alloc((void **)&m->pf_norm, (size_t)rows * c.hidden * 4)) return rc;
-      if (int rc = dev_alloc((void **)&m->pf_tmp, (size_t)rows * Nmax * 4)) return rc;
-    }
     m->pf_rows = rows;
   }
   if (logit_rows > m->pf_logit_rows) {

@@ -620,6 +620,9 @@ struct W8A8Params {
   const float *act_scale;      // device scalar written by quantize_activations_kernel
   float *C;
   int64_t ldc;
+  const float *residual;       // optional: C = residual + y (may be C itself)
+  int64_t ldr;
+  int silu_pairs;              // columns are (gate, up) pairs: C[m, j] = silu(y[m, 2j]) * y[m, 2j + 1]
   int *error;
 };
 
@@ -724,10 +727,25 @@ gemm_w8a8_tc_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (ok) {
       const int ew = warp - 2;
       const int rows = min(BM, p.M - m0), cols = min(BN, p.N - n0);
-      float *dst = p.C + (int64_t)m0 * p.ldc + n0;
-      for (int r = ew; r < rows; r += 8)
-        for (int c = lane; c < cols; c += 32)
-          dst[(int64_t)r * p.ldc + c] = ep[r * LDS + c];
+      if (p.silu_pairs) {   // subgraph0_decode_simplify.mlir:226-231 on neighbouring columns
+        float *dst = p.C + (int64_t)m0 * p.ldc + (n0 >> 1);
+        for (int r = ew; r < rows; r += 8)
+          for (int c = lane; c < (cols >> 1); c += 32) {
+            const float g = ep[r * LDS + 2 * c], u = ep[r * LDS + 2 * c + 1];
+            const float s = 1.0f / (1.0f + expf(-g));
+            dst[(int64_t)r * p.ldc + c] = __fmul_rn(__fmul_rn(g, s), u);
+          }
+      } else {
+        float *dst = p.C + (int64_t)m0 * p.ldc + n0;
+        const float *res = p.residual ? p.residual + (int64_t)m0 * p.ldr + n0 : nullptr;
+        for (int r = ew; r < rows; r += 8)
+          for (int c = lane; c < cols; c += 32) {
+            float y = ep[r * LDS + c];
+            if (res)
+              y = __fadd_rn(res[(int64_t)r * p.ldr + c], y);
+            dst[(int64_t)r * p.ldc + c] = y;
+          }
+      }
     }
   }
   asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -1048,8 +1066,23 @@ int64_t b200_gemm_w8a8_workspace_bytes(int M, int64_t K) {
 
 int b200_gemm_w8a8(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
                    void *workspace, int64_t workspace_bytes, void *stream) {
+  return b200::gemm_w8a8_fused(w, A, M, lda, C, ldc, nullptr, 0, 0, workspace, workspace_bytes, (cudaStream_t)stream);
+}
+
+} // extern "C"
+
+namespace b200 {
+// b200_gemm_w8a8 with the f32 operations that follow a projection in the model folded into the
+// store: residual != NULL gives C = residual + y (in place allowed), silu_pairs gives
+// C[m, j] = silu(y[m, 2j]) * y[m, 2j + 1] over N / 2 columns.  The same roundings as the
+// separate operations.
+int gemm_w8a8_fused(const b200_weight *w, const float *A, int M, int64_t lda, float *C, int64_t ldc,
+                    const float *residual, int64_t ldr, int silu_pairs, void *workspace, int64_t workspace_bytes,
+                    cudaStream_t stream) {
   if (!w || !A || !C || !workspace)
     return fail(B200_EINVAL, "gemm_w8a8: null argument");
+  if (silu_pairs && ((w->N & 1) || residual))
+    return fail(B200_EINVAL, "gemm_w8a8: gate / up pairs need an even N and take no residual");
   if (w->kind != B200_W_I8 || w->scale_dtype != B200_F32 || !w->scale || !w->w)
     return fail(B200_EINVAL, "gemm_w8a8: int8 per-channel weights with f32 scales expected");
   if (M < 1 || w->K % BK8 != 0 || w->N < 1)
@@ -1087,6 +1120,9 @@ int b200_gemm_w8a8(const b200_weight *w, const float *A, int M, int64_t lda, flo
   p.act_scale = act_scale;
   p.C = C;
   p.ldc = ldc;
+  p.residual = residual;
+  p.ldr = ldr;
+  p.silu_pairs = silu_pairs;
   p.error = err;
   static bool configured[64] = {};
   int dev = 0;
@@ -1102,6 +1138,9 @@ int b200_gemm_w8a8(const b200_weight *w, const float *A, int M, int64_t lda, flo
   B200_LAUNCH_CHECK();
   return B200_OK;
 }
+} // namespace b200
+
+extern "C" {
 
 /* 0, or the code of the first bounded wait that gave up in the last b200_gemm_w8 on this workspace
  * (reads the error word; synchronises the stream). */
