@@ -1245,8 +1245,9 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   std::vector<Pending> pend;
   int rc = B200_OK;
 #define B200_DO(expr) do { if (rc == B200_OK) rc = (expr); } while (0)
+  // Order: the module's parameters as the traced graph first uses them, then its buffers
+  // (frontend/Python/frontend.py:922-933): embedding, layers, final norm, lm_head, inv_freq.
   B200_DO(b200_model_set_vector(m, -1, B200_T_EMBED, takef(V * H), V * H));
-  B200_DO(b200_model_set_vector(m, -1, B200_T_INV_FREQ, takef(D / 2), D / 2));
   // f32p32: Bpacked[n / 32][k][n % 32] == B[k, n]; the panels are undone into a scratch copy
   const bool panels = !strcmp(variant, "f32p32");
   std::vector<float> plain;
@@ -1275,15 +1276,12 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   };
   for (int l = 0; l < c.n_layers && rc == B200_OK; ++l) {
     B200_DO(b200_model_set_vector(m, l, B200_T_IN_NORM, takef(H), H));
-    const float *bq = c.qkv_bias ? takef(QD) : nullptr;
     flinear(l, B200_T_Q, H, QD);
-    if (bq) B200_DO(b200_model_set_vector(m, l, B200_T_Q_BIAS, bq, QD));
-    const float *bk = c.qkv_bias ? takef(KD) : nullptr;
+    if (c.qkv_bias) B200_DO(b200_model_set_vector(m, l, B200_T_Q_BIAS, takef(QD), QD));
     flinear(l, B200_T_K, H, KD);
-    if (bk) B200_DO(b200_model_set_vector(m, l, B200_T_K_BIAS, bk, KD));
-    const float *bv = c.qkv_bias ? takef(KD) : nullptr;
+    if (c.qkv_bias) B200_DO(b200_model_set_vector(m, l, B200_T_K_BIAS, takef(KD), KD));
     flinear(l, B200_T_V, H, KD);
-    if (bv) B200_DO(b200_model_set_vector(m, l, B200_T_V_BIAS, bv, KD));
+    if (c.qkv_bias) B200_DO(b200_model_set_vector(m, l, B200_T_V_BIAS, takef(KD), KD));
     qlinear(l, B200_T_O, QD, H);
     B200_DO(b200_model_set_vector(m, l, B200_T_POST_NORM, takef(H), H));
     qlinear(l, B200_T_GATE, H, F);
@@ -1292,6 +1290,7 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   }
   B200_DO(b200_model_set_vector(m, -1, B200_T_FINAL_NORM, takef(H), H));
   qlinear(-1, B200_T_LM_HEAD, H, V);
+  B200_DO(b200_model_set_vector(m, -1, B200_T_INV_FREQ, takef(D / 2), D / 2));
   // quantize.py:577-589: the scaler params follow every original param, in
   // original-weight order.
   for (auto &p : pend) {

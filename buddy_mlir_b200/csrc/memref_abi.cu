@@ -597,7 +597,8 @@ bool panels_of_same_model(const b200_model_config &c, const float *plain, const 
     if (memcmp(plain + e, packed + e, 4) != 0)
       return false;
   }
-  struct { int64_t off, K, N; } w[2] = {{V * H + D / 2 + H + (c.qkv_bias ? QD : 0), H, QD}, {total - H * V, H, V}};
+  // blob order: embedding, layer 0 {input norm, Wq, ...}, ..., lm_head, inv_freq
+  struct { int64_t off, K, N; } w[2] = {{V * H + H, H, QD}, {total - D / 2 - H * V, H, V}};
   for (auto &t : w) {
     if (t.N % 32 != 0)
       return false;

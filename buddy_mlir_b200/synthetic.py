@@ -1,11 +1,18 @@
 """Seeded synthetic weights in buddy-mlir's flat-blob order.
 
 Order of the f32 blob (frontend/Python/graph/graph.py:836-863 packs the params
-in graph order; the order itself is read off the argument list of
-examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:4): embedding,
-inv_freq, per layer {input norm, q bias, Wq, k bias, Wk, v bias, Wv, Wo,
-post-attention norm, Wgate, Wup, Wdown}, final norm, lm_head.  Every matmul
-weight is [K,N] row-major (eliminate_weight_transpose.py:163-219).
+in graph order; the frontend lists the module's parameters in the order the
+traced graph first uses them and its buffers after them,
+frontend/Python/frontend.py:922-933): embedding, per layer {input norm, Wq,
+q bias, Wk, k bias, Wv, v bias, Wo, post-attention norm, Wgate, Wup, Wdown},
+final norm, lm_head, inv_freq (the rotary buffer).  Every matmul weight is
+[K,N] row-major (eliminate_weight_transpose.py:163-219).  This is the order
+buddy-mlir's own importer (tools/buddy-codegen/import_model.py) produces for a
+Qwen2 model with the transformers version it pins; tests/golden holds digests
+of its blobs for the small model (make_reference_blobs.py).  The argument list
+of the older examples/BuddyDeepSeekR1/subgraph0_decode_simplify.mlir:4 shows
+another order (inv_freq second, bias before weight): files written by that
+flow are not in this order.
 
 For the w8a32 variant the same walk is split by dtype
 (tools/buddy-codegen/import_model.py:818-887): o, gate, up, down and lm_head go
@@ -25,19 +32,19 @@ QUANTISED_BY_REFERENCE = ("o", "gate", "up", "down", "lm_head")
 def tensor_list(cfg: ModelConfig):
     """[(name, layer, shape)] in blob order."""
     H, QD, KD, F, V, D = cfg.hidden, cfg.q_dim, cfg.kv_dim, cfg.ffn, cfg.vocab, cfg.head_dim
-    out = [("embed", -1, (V, H)), ("inv_freq", -1, (D // 2,))]
+    out = [("embed", -1, (V, H))]
     for l in range(cfg.n_layers):
         out.append(("in_norm", l, (H,)))
         if cfg.qkv_bias:
-            out += [("q_bias", l, (QD,)), ("q", l, (H, QD)), ("k_bias", l, (KD,)),
-                    ("k", l, (H, KD)), ("v_bias", l, (KD,)), ("v", l, (H, KD))]
+            out += [("q", l, (H, QD)), ("q_bias", l, (QD,)), ("k", l, (H, KD)),
+                    ("k_bias", l, (KD,)), ("v", l, (H, KD)), ("v_bias", l, (KD,))]
         else:
             out += [("q", l, (H, QD)), ("k", l, (H, KD)), ("v", l, (H, KD))]
         if cfg.qk_norm:
             out += [("q_norm", l, (D,)), ("k_norm", l, (D,))]
         out += [("o", l, (QD, H)), ("post_norm", l, (H,)), ("gate", l, (H, F)),
                 ("up", l, (H, F)), ("down", l, (F, H))]
-    out += [("final_norm", -1, (H,)), ("lm_head", -1, (H, V))]
+    out += [("final_norm", -1, (H,)), ("lm_head", -1, (H, V)), ("inv_freq", -1, (D // 2,))]
     return out
 
 

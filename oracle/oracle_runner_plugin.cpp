@@ -97,8 +97,10 @@ public:
     f.read(reinterpret_cast<char *>(blob_.data()), (std::streamsize)(blob_.size() * 4));
     const char *all = std::getenv("ORC_RUNNER_ALL_LINEAR_W8");
     const bool w8 = all && all[0] == '1';
-    // blob walk: embedding, inv_freq, per layer {in norm, [q bias,] Wq, [k bias,] Wk, [v bias,] Wv, Wo,
-    // post norm, Wgate, Wup, Wdown}, final norm, lm_head; every matmul weight [K,N] row-major
+    // blob walk (parameters as the traced graph first uses them, then the rotary buffer,
+    // frontend/Python/frontend.py:922-933): embedding, per layer {in norm, Wq, [q bias,] Wk, [k bias,]
+    // Wv, [v bias,] Wo, post norm, Wgate, Wup, Wdown}, final norm, lm_head, inv_freq; every matmul
+    // weight [K,N] row-major
     const int64_t H = s_.hidden, D = s_.head_dim, QD = s_.q_heads * D, KD = s_.kv_heads * D, F = s_.ffn, V = s_.vocab;
     size_t off = 0;
     auto take = [&](int64_t count) {
@@ -108,12 +110,12 @@ public:
       off += (size_t)count;
       return p;
     };
-    auto linear = [&](int64_t K, int64_t N, const float *bias) {
+    auto linear = [&](int64_t K, int64_t N, bool with_bias) {
       OrcLinear L{};
       L.K = K;
       L.N = N;
-      L.bias = bias;
       const float *W = take(K * N);
+      L.bias = with_bias ? take(N) : nullptr;
       if (w8) {
         q_.emplace_back((size_t)(K * N));
         sc_.emplace_back((size_t)N);
@@ -131,25 +133,22 @@ public:
     model_.hidden = H; model_.n_layers = s_.n_layers; model_.q_heads = s_.q_heads; model_.kv_heads = s_.kv_heads;
     model_.head_dim = D; model_.ffn = F; model_.vocab = V; model_.max_len = s_.max_len; model_.eps = s_.eps;
     model_.embed = take(V * H);
-    model_.inv_freq = take(D / 2);
     layers_.assign((size_t)s_.n_layers, OrcLayer{});
     for (auto &L : layers_) {
       L.in_norm = take(H);
-      const float *qb = s_.qkv_bias ? take(QD) : nullptr;
-      L.q = linear(H, QD, qb);
-      const float *kb = s_.qkv_bias ? take(KD) : nullptr;
-      L.k = linear(H, KD, kb);
-      const float *vb = s_.qkv_bias ? take(KD) : nullptr;
-      L.v = linear(H, KD, vb);
-      L.o = linear(QD, H, nullptr);
+      L.q = linear(H, QD, s_.qkv_bias);
+      L.k = linear(H, KD, s_.qkv_bias);
+      L.v = linear(H, KD, s_.qkv_bias);
+      L.o = linear(QD, H, false);
       L.post_norm = take(H);
-      L.gate = linear(H, F, nullptr);
-      L.up = linear(H, F, nullptr);
-      L.down = linear(F, H, nullptr);
+      L.gate = linear(H, F, false);
+      L.up = linear(H, F, false);
+      L.down = linear(F, H, false);
     }
     model_.layers = layers_.data();
     model_.final_norm = take(H);
-    model_.lm_head = linear(H, V, nullptr);
+    model_.lm_head = linear(H, V, false);
+    model_.inv_freq = take(D / 2);
     if (off != blob_.size())
       throw std::runtime_error("[oracle runner] the blob is longer than the model");
   }

@@ -72,6 +72,23 @@ def quantize_per_channel(W, bits=8):
     return Q, s
 
 
+def quantize_per_channel_half(W, bits=8):
+    """The quantiser as the reference runs it for its f16-activation variants (w8a16, w4a16):
+    the module is converted to half before the graphs are traced
+    (tools/buddy-codegen/import_model.py:118-145), so absmax, scale = absmax / qmax and
+    round(w / scale) are half-precision operations (:830-850; each computed in f32 and rounded
+    to half, as torch does on the CPU).  The clamp at 1e-10 rounds to zero in half and does
+    nothing.  W [K,N] f32 -> (Q [K,N] int8, scale [N] f16)."""
+    Wh = np.asarray(W, dtype=np.float32).astype(np.float16)
+    qmax = np.float32(127.0 if bits == 8 else 7.0)
+    amax = np.abs(Wh).max(axis=0, keepdims=True)
+    scale = (amax.astype(np.float32) / qmax).astype(np.float16)
+    ratio = (Wh.astype(np.float32) / scale.astype(np.float32)).astype(np.float16)
+    lo, hi = (-128, 127) if bits == 8 else (-8, 7)
+    Q = np.clip(np.rint(ratio.astype(np.float32)), lo, hi).astype(np.int8)
+    return Q, scale.reshape(-1)
+
+
 def pack_int4(flat):
     flat = np.ascontiguousarray(flat, dtype=np.int8).reshape(-1)
     out = np.empty(flat.size // 2, dtype=np.int8)

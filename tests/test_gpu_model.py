@@ -254,10 +254,14 @@ def _w8a8_case(seed):
 # projection (RMSNorm sums, exp, sin / cos) differ from the checker's by a few ulp, so a value
 # within that distance of a rounding boundary (about 3e-5 of all values) falls to the other side
 # and moves one term of one dot product by a level: 1 / (127 sqrt(K)) of the output's magnitude
-# per flip, 5e-4 at K = 256.  Most steps see none (errors near 1e-7), some see one or two; 5e-3
-# of the logits' magnitude bounds them.  The greedy token is compared wherever the checker's
-# margin is larger than that.
-W8A8_TOL = 5e-3
+# per flip, 5e-4 at K = 256, and the projections after it amplify that (their own roundings
+# move).  Most runs see no flip and agree to 1e-7; on the CPU alone, the checker against itself
+# with the embedding one ulp off reaches 1.0e-2 over twelve decode steps for one seed in three
+# of this small model.  The bound is the checker's own quantisation noise (w8a8 against
+# weight-only logits: 1.9e-2 to 2.6e-2 here) with a little room: what a wiring error would
+# exceed and a rounding flip cannot.  Bit-exactness is established per projection
+# (test_gpu_gemm.py); the greedy token is compared wherever the checker's margin is larger.
+W8A8_TOL = 3e-2
 
 
 def test_tiny_w8a8_device_session_prefill_and_decode():
@@ -782,11 +786,14 @@ def test_1p5b_w8a8_prefill_rows_and_decode_steps(full_weights):
     At these widths the w8a8 graphs are chaotic in the last bit: one activation that rounds to
     the other level perturbs the next projection's input by about 1e-3, which moves a few
     percent of ITS roundings, and after three or four projections the two computations round
-    independently (the weight-only graphs move by 2e-6 under the same change).  The yardstick
-    is therefore the checker itself: its logits for an embedding table one ulp off differ from
-    its logits for the original by 1.5e-2 after one layer, 3e-2 after two, and by the whole
-    quantisation noise at full depth.  The device must be as close to the checker as the
-    checker is to itself (within a factor of three of that distance), at two layers and at 28."""
+    independently (the weight-only graphs move by 2e-6 under the same change).  On the CPU
+    alone, the checker's logits for an embedding table one ulp off differ from its logits for
+    the original by nothing when no rounding happens to flip, and otherwise by 1.5e-2 after one
+    layer, 3e-2 after two and 1.2e-1 at full depth: the distance of two computations that round
+    independently, which is at most the quantisation noise of each.  That noise (the w8a8
+    checker against the weight-only checker on the same input) is the yardstick: the device
+    must be within twice it, at two layers and at 28; the checker's own one-ulp distance is
+    printed beside it."""
     kinds = {n: "w8q" for n in ALL_LINEAR}
     for cfg, views, blob in ((DEEPSEEK_R1_1P5B.with_(name="r1_two_layers", n_layers=2, vocab=32768), None, None),
                              (DEEPSEEK_R1_1P5B,) + tuple(reversed(full_weights))):
@@ -797,6 +804,7 @@ def test_1p5b_w8a8_prefill_rows_and_decode_steps(full_weights):
         prompt = [int(t) for t in synthetic.prompt_tokens(cfg, 19, 48)]
         want = om.prefill(prompt)
         itself = maxrel(orc.OracleModel(cfg, _one_ulp_off(views), kinds=kinds, quantised=quant).prefill(prompt), want)
+        noise = maxrel(want, orc.OracleModel(cfg, views, kinds={n: "w8" for n in ALL_LINEAR}, quantised=quant).prefill(prompt))
         s = ModelSession(cfg)
         s.load_blobs("f32", blob, all_linear_w8=True)
         s.set_activation_int8(True)
@@ -808,9 +816,10 @@ def test_1p5b_w8a8_prefill_rows_and_decode_steps(full_weights):
             w = om.decode(tok)
             step = max(step, maxrel(s.logits_data(), w))
             tok = greedy_sample(w)
-        print(f"{cfg.name} w8a8: prefill max rel {rows:.3e}, decode {step:.3e}; the checker against itself one ulp "
-              f"off {itself:.3e}; {s.last_ms():.2f} ms for the last decode step")
-        assert rows < 3 * itself and step < 3 * itself, (rows, step, itself)
+        print(f"{cfg.name} w8a8: prefill max rel {rows:.3e}, decode {step:.3e}; quantisation noise of the checker "
+              f"{noise:.3e}, the checker against itself one ulp off {itself:.3e}; {s.last_ms():.2f} ms for the last "
+              f"decode step")
+        assert rows < 2 * noise and step < 2 * noise, (rows, step, noise)
         s.close()
 
 

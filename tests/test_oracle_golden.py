@@ -207,3 +207,36 @@ def test_prefill_rows_is_the_decode_graph_row_by_row_except_for_tensor_wide_scal
     w8 = orc.OracleModel(cfg, views, kinds={n: "w8" for n in synthetic.QUANTISED_BY_REFERENCE}).prefill(toks)
     for x in (rows, steps):     # int8 activations: within a few percent of the weight-only model
         assert np.abs(x - w8).max() < 0.1 * np.abs(w8).max()
+
+
+def test_blobs_equal_what_the_reference_importer_writes():
+    """tests/golden/reference_importer_tiny_qwen2.npz holds digests of the weight files that
+    buddy-mlir's own importer (tools/buddy-codegen/import_model.py: TorchDynamo trace,
+    eliminate_transpose, the quantisation passes, extract_*_weights) produced for the small
+    Qwen2 model with the seeded weights: the tensor order, the [K,N] layout, which tensors are
+    quantised, the quantiser's codes and scales, the nibble packing and the position of the
+    scales must all be the same here, for every variant, bit for bit."""
+    import hashlib
+    from buddy_mlir_b200 import TINY_QWEN2 as cfg, synthetic
+    f = np.load(os.path.join(G, "reference_importer_tiny_qwen2.npz"))
+    sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
+    assert [f"{n}:{l}" for n, l, _ in synthetic.tensor_list(cfg)] == list(f["order"])
+    assert sorted({str(n).split(":")[0] for n in f["quantised"]}) == sorted(synthetic.QUANTISED_BY_REFERENCE)
+    blob, views = synthetic.make_f32_blob(cfg, int(f["seed_w"]))
+    # the rotary buffer is the one tensor the HuggingFace module computes for itself
+    assert np.allclose(views[("inv_freq", -1)], f["inv_freq"], rtol=1e-6, atol=0)
+    views[("inv_freq", -1)][:] = f["inv_freq"]
+    assert blob.size == int(f["f32_params_size"]) and sha(blob) == str(f["f32_params_sha256"])
+    q8 = lambda W: orc.quantize_per_channel(W, 8)
+    fb, ib = synthetic.split_w8a32(cfg, views, q8)
+    assert np.array_equal(fb[-f["w8a32_scales"].size:], f["w8a32_scales"])
+    for variant in ("w8a32", "w8a8"):       # the same files, another graph
+        assert sha(fb) == str(f[f"{variant}_f32_params_sha256"])
+        assert sha(ib) == str(f[f"{variant}_i8_params_sha256"])
+    # f16-activation variants: the reference quantises the half module in half precision
+    fb, ib = synthetic.split_w8a16(cfg, views, lambda W: orc.quantize_per_channel_half(W, 8))
+    assert fb.dtype == np.float16 and sha(fb) == str(f["w8a16_f16_params_sha256"])
+    assert sha(ib) == str(f["w8a16_i8_params_sha256"])
+    fb, ib = synthetic.split_w4a16(cfg, views, lambda W: orc.quantize_per_channel_half(W, 4))
+    assert fb.dtype == np.float16 and sha(fb) == str(f["w4a16_f16_params_sha256"])
+    assert ib.size == int(f["w4a16_i4_params_size"]) and sha(ib) == str(f["w4a16_i4_params_sha256"])
