@@ -285,6 +285,12 @@ int b200_model_set_linear(b200_model *m, int layer, int slot, int src_kind,
 /* Walk buddy-mlir's flat weight blobs (frontend/Python/graph/graph.py:836-863,
  * frontend/Python/graph/transform/quantization/quantize.py:577-589; file
  * table tools/buddy-codegen/gen_config.py:51-71) and load every tensor.
+ * Tensor order (Qwen2), as tools/buddy-codegen/import_model.py writes it: the
+ * parameters in the order the traced graph first uses them, then the rotary
+ * buffer (frontend/Python/frontend.py:922-933): embedding, per layer {input
+ * norm, Wq, q bias, Wk, k bias, Wv, v bias, Wo, post-attention norm, Wgate,
+ * Wup, Wdown}, final norm, lm_head, inv_freq; every matmul weight [K,N]
+ * row-major; the scales of the quantised tensors follow in that tensor order.
  * variant: "f32", "f16" or "bf16" (one blob of f32 / f16 / bf16 elements), "w8a32" (float blob + int8 blob: o, gate, up,
  * down and lm_head quantised, q/k/v float, scales at the end of the float
  * blob), "w8a8" (the files of w8a32; the session then quantises the activations of
