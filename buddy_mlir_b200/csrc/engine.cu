@@ -1173,7 +1173,8 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
     // f32p32: the f32 blob with every matmul weight in 32-column panels (the decode file of
     // the packed-decode spec, frontend/Python/graph/transform/pack_decode_weights.py:32-124)
     // f16 / bf16: the same single blob with 16-bit elements (models/deepseek_r1/specs/f16.json;
-    // bf16 = the high halves of the f32 values, tools/buddy-codegen/import_model.py:700-707)
+    // bf16: the module is converted with .bfloat16() before tracing, the writer keeps the high
+    // halves of those values, tools/buddy-codegen/import_model.py:118-145, 700-707)
     nf = common + c.n_layers * (small_layer + qkv + quant_layer) + H * V;
   } else if (!strcmp(variant, "w8a32") || !strcmp(variant, "w8a16") || !strcmp(variant, "w8a8")) {
     // w8a16: the same split, n_float counts f16 elements (models/deepseek_r1/specs/w8a16.json);

@@ -157,5 +157,18 @@ def split_w8a16(cfg: ModelConfig, views, quantize):
     return fb.astype(np.float16), ib
 
 
+def to_bf16(a):
+    """f32 -> bfloat16 bits (uint16), round to nearest even: what the reference's bf16 files hold
+    (the module is converted with .bfloat16() before tracing, tools/buddy-codegen/import_model.py:
+    118-145; the writer then keeps the high halves of the already-rounded values, :700-707)."""
+    u = np.ascontiguousarray(a, dtype=np.float32).view(np.uint32)
+    return ((u + np.uint32(0x7FFF) + ((u >> np.uint32(16)) & np.uint32(1))) >> np.uint32(16)).astype(np.uint16)
+
+
+def from_bf16(bits):
+    """bfloat16 bits (uint16) -> f32, exact."""
+    return (np.ascontiguousarray(bits, dtype=np.uint16).astype(np.uint32) << np.uint32(16)).view(np.float32)
+
+
 def prompt_tokens(cfg: ModelConfig, seed: int, n: int = 32):
     return np.random.default_rng(seed).integers(0, cfg.vocab, size=n).astype(np.int64)

@@ -17,7 +17,8 @@ Output: reference_importer_tiny_qwen2.npz
                    by comparing contents with the seeded tensors
   quantised        the names the quantisation pass turned into int8
   <variant>_<bucket>_sha256, _size   digest and element count of every bucket the importer
-                   returns (f32: params; w8a32 / w8a8: f32_params, i8_params; w8a16: f16_params,
+                   returns (f32 / f16 / bf16: params, and for f32 decode_packed, the decode file of
+                   the packed-decode spec; w8a32 / w8a8: f32_params, i8_params; w8a16: f16_params,
                    i8_params; w4a16: f16_params, i4_params)
   w8a32_scales     the scale section at the end of the w8a32 float bucket
   inv_freq         the rotary buffer as the HuggingFace module computed it (the one tensor that
@@ -72,7 +73,7 @@ def load_importer():
     return mod
 
 
-def hf_model(cfg, views, half):
+def hf_model(cfg, views, act):
     import torch
     import transformers
     hc = transformers.Qwen2Config(
@@ -96,8 +97,10 @@ def hf_model(cfg, views, half):
             sd[p + f"mlp.{n}_proj.weight"] = t(views[(n, l)].T)
     missing, unexpected = model.load_state_dict(sd, strict=False)
     assert not unexpected and all("rotary" in m or "inv_freq" in m for m in missing), (missing, unexpected)
-    if half:                       # load_model, import_model.py:118-145
+    if act == "f16":               # load_model, import_model.py:118-145
         model = model.half()
+    elif act == "bf16":
+        model = model.bfloat16()
     model.config.use_cache = False
     return model
 
@@ -123,20 +126,26 @@ def main():
     cfg = TINY_QWEN2
     _, views = synthetic.make_f32_blob(cfg, SEED_W)
     out = {"seed_w": SEED_W}
-    activation = {"f32": "f32", "w8a32": "f32", "w8a8": "f32", "w8a16": "f16", "w4a16": "f16"}
+    activation = {"f32": "f32", "f16": "f16", "bf16": "bf16", "w8a32": "f32", "w8a8": "f32", "w8a16": "f16",
+                  "w4a16": "f16"}
     for variant, act in activation.items():
         config = {"shape": {"max_token_len": cfg.max_len}, "variant": variant, "precision": {"activation_type": act}}
-        model = hf_model(cfg, views, half=(act == "f16"))
+        model = hf_model(cfg, views, act)
         gp, gd, params = imp.compile_graphs(model, config)
         imp.apply_pre_transforms(gp[0], gd[0])
-        if variant == "f32":
+        if variant in ("f32", "f16", "bf16"):
             buckets = imp.extract_plain_weights(params, config)
-            out["order"] = np.array([name_of(p.detach().numpy(), views) for p in params])
-            assert "?" not in out["order"], out["order"]
-            out["inv_freq"] = params[list(out["order"]).index("inv_freq:-1")].detach().numpy().copy()
         else:
             imp.apply_quantization(gp[0], gd[0], variant)
             buckets = imp.extract_quantized_weights(gp[0], params, config)
+        if variant == "f32":
+            out["order"] = np.array([name_of(p.detach().numpy(), views) for p in params])
+            assert "?" not in out["order"], out["order"]
+            out["inv_freq"] = params[list(out["order"]).index("inv_freq:-1")].detach().numpy().copy()
+            # the decode file of the packed-decode spec: the decode graph's own parameter list after
+            # pack_decode_matmul_weights (import_model.py:463-481, 1214-1226)
+            imp.pack_decode_weights(gd[0], {"vector_size": 32})
+            buckets["decode_packed"] = np.concatenate([p.detach().numpy().reshape(-1) for p in gd[0]._params_ref])
         if variant == "w8a32":
             from buddy.compiler.graph.type import TensorDType
             names = [name_of(p.detach().numpy(), views) for p in params]

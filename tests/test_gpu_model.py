@@ -390,16 +390,16 @@ def test_tiny_f16_blob_through_the_model_entries():
 
 def test_tiny_bf16_blob_through_the_model_entries():
     """The reference's bf16 flavour (tools/buddy-codegen/gen_config.py:40-44,54): one blob of
-    bfloat16 values made by keeping the high 16 bits of the f32 ones (import_model.py:700-707),
+    bfloat16 values (the module converted with .bfloat16(), import_model.py:118-145, 700-707),
     bfloat16 cache and logits on the host.  The device computes in f32 on the widened weights
-    and rounds at the boundary; the checker is the f32 restatement on the same truncated
+    and rounds at the boundary; the checker is the f32 restatement on the same rounded
     tensors, 2e-2 (bf16 keeps 8 bits: 4e-3 per value; the reference's own bf16 arithmetic has
     no restatement here: parity of this variant is unpinned beyond that)."""
     cfg = TINY_QWEN2
     blob, views = synthetic.make_f32_blob(cfg, 88)
-    high = (blob.view(np.uint32) >> 16).astype(np.uint16)
-    truncated = {k: ((np.ascontiguousarray(v).view(np.uint32) >> 16) << 16).view(np.float32) for k, v in views.items()}
-    om = orc.OracleModel(cfg, truncated)
+    high = synthetic.to_bf16(blob)
+    rounded = {k: synthetic.from_bf16(synthetic.to_bf16(v)).reshape(v.shape) for k, v in views.items()}
+    om = orc.OracleModel(cfg, rounded)
     es = EntrySession(cfg, "bf16", [high])
     prompt = synthetic.prompt_tokens(cfg, 7, 9)
     logits = es.prefill(prompt, pad_id=0)

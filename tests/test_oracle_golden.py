@@ -227,6 +227,11 @@ def test_blobs_equal_what_the_reference_importer_writes():
     assert np.allclose(views[("inv_freq", -1)], f["inv_freq"], rtol=1e-6, atol=0)
     views[("inv_freq", -1)][:] = f["inv_freq"]
     assert blob.size == int(f["f32_params_size"]) and sha(blob) == str(f["f32_params_sha256"])
+    # the 16-bit files of the same walk, and the panel-packed decode file of the packed-decode spec
+    assert sha(blob.astype(np.float16)) == str(f["f16_params_sha256"])
+    assert sha(synthetic.to_bf16(blob)) == str(f["bf16_params_sha256"])
+    assert np.array_equal(synthetic.from_bf16(synthetic.to_bf16(blob)).view(np.uint32) & 0xFFFF, np.zeros(blob.size, np.uint32))
+    assert sha(synthetic.pack_decode_blob(cfg, blob)) == str(f["f32_decode_packed_sha256"])
     q8 = lambda W: orc.quantize_per_channel(W, 8)
     fb, ib = synthetic.split_w8a32(cfg, views, q8)
     assert np.array_equal(fb[-f["w8a32_scales"].size:], f["w8a32_scales"])
