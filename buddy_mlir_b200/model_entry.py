@@ -112,6 +112,9 @@ class EntrySession:
         src = np.ctypeslib.as_array(result.logits.aligned, shape=(self.cfg.vocab,))
         np.copyto(self.logits, self._floats(src))
         _libc.free(C.cast(result.logits.allocated, C.c_void_p))
+        # a null descriptor for the next call, as resetDecodeResultABI leaves it (gen_session.py:
+        # 1434-1446): a descriptor that still names a buffer would be filled in place
+        C.memset(C.byref(result.logits), 0, C.sizeof(result.logits))
         self._check()
         if check_alias:
             for i, k in enumerate(self.kv):
