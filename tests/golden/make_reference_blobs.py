@@ -23,6 +23,9 @@ Output: reference_importer_tiny_qwen2.npz
   w8a32_scales     the scale section at the end of the w8a32 float bucket
   inv_freq         the rotary buffer as the HuggingFace module computed it (the one tensor that
                    is not loaded from the seeded weights)
+  prefill_inputs, prefill_outputs, decode_inputs, decode_outputs
+                   "<shape>:<dtype>" of the traced graphs' inputs (after the parameters) and, with the
+                   producing operation, of their outputs: the entry ABI of the compiled model
 """
 import hashlib
 import importlib.abc
@@ -117,6 +120,11 @@ def name_of(arr, views):
     return "?"
 
 
+def signature(node):
+    dtype = str(node.tensor_meta["dtype"]).split(".")[-1].lower()
+    return "x".join(str(int(s)) for s in node.tensor_meta["shape"]) + ":" + dtype
+
+
 def digest(a):
     return hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
 
@@ -142,6 +150,14 @@ def main():
             out["order"] = np.array([name_of(p.detach().numpy(), views) for p in params])
             assert "?" not in out["order"], out["order"]
             out["inv_freq"] = params[list(out["order"]).index("inv_freq:-1")].detach().numpy().copy()
+            # the signatures of the two traced graphs: what _mlir_ciface_forward_prefill / _decode
+            # receive after the weight blobs, and what their result structs hold
+            for phase, g in (("prefill", gp[0]), ("decode", gd[0])):
+                out[f"{phase}_inputs"] = np.array([signature(n) for n in g.inputs])
+                ret = [n for n in g.body if type(n).__name__ == "OutputOp"][0]
+                out[f"{phase}_outputs"] = np.array([signature(g.node_table[a]) + ":" + type(g.node_table[a]).__name__
+                                                    for a in ret.args])
+                print(phase, "inputs", list(out[f"{phase}_inputs"]), "outputs", list(out[f"{phase}_outputs"]))
             # the decode file of the packed-decode spec: the decode graph's own parameter list after
             # pack_decode_matmul_weights (import_model.py:463-481, 1214-1226)
             imp.pack_decode_weights(gd[0], {"vector_size": 32})

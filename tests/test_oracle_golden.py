@@ -245,3 +245,38 @@ def test_blobs_equal_what_the_reference_importer_writes():
     fb, ib = synthetic.split_w4a16(cfg, views, lambda W: orc.quantize_per_channel_half(W, 4))
     assert fb.dtype == np.float16 and sha(fb) == str(f["w4a16_f16_params_sha256"])
     assert ib.size == int(f["w4a16_i4_params_size"]) and sha(ib) == str(f["w4a16_i4_params_sha256"])
+
+
+def test_entry_abi_is_the_signature_of_the_reference_traced_graphs():
+    """The same fixture holds the inputs and outputs of the prefill and decode graphs as
+    buddy-mlir's importer traced them for the small model: what the compiled model's
+    _mlir_ciface_forward_prefill / _mlir_ciface_forward_decode take after the weight blobs and
+    what their result structs hold.  The generated shim must declare exactly that: tokens
+    [1, max_len]; per call token [1,1], position [1], then the K and V cache of layer 0 and, for
+    every further layer, a one-element counter followed by its K and V cache; results in the
+    same order (position + 1, caches, counters + 1) with the logits last."""
+    import re
+    from buddy_mlir_b200 import TINY_QWEN2 as cfg, gen_model_entry
+    f = np.load(os.path.join(G, "reference_importer_tiny_qwen2.npz"))
+    kv = f"1x{cfg.kv_heads}x{cfg.max_len}x{cfg.head_dim}:float32"
+    assert list(f["prefill_inputs"]) == [f"1x{cfg.max_len}:int64"]
+    assert [s.rsplit(":", 1)[0] for s in f["prefill_outputs"]] == [kv] * (2 * cfg.n_layers) + [f"1x{cfg.max_len}x{cfg.vocab}:float32"]
+    want_in = ["1x1:int64", "1:int64", kv, kv]
+    for _ in range(cfg.n_layers - 1):
+        want_in += ["1:int64", kv, kv]
+    assert list(f["decode_inputs"]) == want_in
+    outs = [s.rsplit(":", 1) for s in f["decode_outputs"]]
+    assert [o[0] for o in outs] == want_in[1:] + [f"1x1x{cfg.vocab}:float32"]
+    assert [o[1] for o in outs if o[0] == "1:int64"] == ["AddOp"] * cfg.n_layers      # counters come back + 1
+    # the shim's declaration of the same
+    src = gen_model_entry.source(cfg, "f32")
+    sig = re.search(r"_mlir_ciface_forward_decode\(DecodeABI \*result,(.*?)\) \{", src, re.S).group(1)
+    params = [p.strip().split()[0] for p in sig.split(",")]
+    kinds = {"b200_memref_i64_2": "1x1:int64", "b200_memref_i64_1": "1:int64", "b200_memref_f32_4": kv}
+    assert params[0] == "b200_memref_f32_1" and [kinds[p] for p in params[1:]] == want_in
+    abi = re.search(r"struct DecodeABI \{(.*?)\};", src, re.S).group(1)
+    fields = []
+    for line in abi.strip().splitlines():
+        typ, names = line.strip().rstrip(";").split(None, 1)
+        fields += [typ] * len(names.split(","))
+    assert [kinds.get(t, t) for t in fields] == want_in[1:] + ["b200_memref_f32_3"]
