@@ -23,6 +23,9 @@ Output: reference_importer_tiny_qwen2.npz
   w8a32_scales     the scale section at the end of the w8a32 float bucket
   inv_freq         the rotary buffer as the HuggingFace module computed it (the one tensor that
                    is not loaded from the seeded weights)
+  w8a8_prefill_ops, w8a8_decode_ops
+                   "<operation>:<weight>:<activation shape>" of every integer matmul the w8a8 pass
+                   left in the two graphs
   prefill_inputs, prefill_outputs, decode_inputs, decode_outputs
                    "<shape>:<dtype>" of the traced graphs' inputs (after the parameters) and, with the
                    producing operation, of their outputs: the entry ABI of the compiled model
@@ -169,6 +172,22 @@ def main():
                                          if node.tensor_meta.get("dtype") == TensorDType.Int8])
             n_scales = sum(int(np.prod(node.tensor_meta["shape"])) for node in gp[0].params[len(params):])
             out["w8a32_scales"] = buckets["f32_params"][-n_scales:].copy()
+        if variant == "w8a8":
+            # which projections the w8a8 pass turned into integer matmuls, and the activation tensor
+            # each of them quantises as a whole (its shape: all rows of the prefill, one row of a decode)
+            for phase, g in (("prefill", gp[0]), ("decode", gd[0])):
+                # both graphs were traced from the same module: the same parameters in the same order
+                assert all(list(node.tensor_meta["shape"]) == list(p.shape) for node, p in zip(g.params, params))
+                names = {node.name: name_of(p.detach().numpy(), views) for node, p in zip(g.params, params)}
+                rows = []
+                for node in g.body:
+                    kind = type(node).__name__
+                    if kind in ("QuantizedMatmulOp", "QuantizedAddMMOp"):
+                        act, weight = (node.args[0], node.args[1]) if kind == "QuantizedMatmulOp" else (node.args[1], node.args[2])
+                        shape = "x".join(str(int(s)) for s in g.node_table[act].tensor_meta["shape"])
+                        rows.append(f"{kind}:{names.get(weight, weight)}:{shape}")
+                out[f"w8a8_{phase}_ops"] = np.array(rows)
+                print("w8a8", phase, rows)
         for tag, arr in buckets.items():
             out[f"{variant}_{tag}_sha256"] = digest(arr)
             out[f"{variant}_{tag}_size"] = arr.size

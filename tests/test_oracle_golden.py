@@ -280,3 +280,20 @@ def test_entry_abi_is_the_signature_of_the_reference_traced_graphs():
         typ, names = line.strip().rstrip(";").split(None, 1)
         fields += [typ] * len(names.split(","))
     assert [kinds.get(t, t) for t in fields] == want_in[1:] + ["b200_memref_f32_3"]
+
+
+def test_w8a8_graphs_quantise_the_projections_and_tensors_this_library_does():
+    """What buddy-mlir's w8a8 pass leaves in the traced graphs of the small model (same fixture):
+    o, gate, up, down of every layer and the lm_head are integer matmuls, q / k / v stay float;
+    the activation each of them quantises with ONE scale is the whole [max_len, K] tensor in the
+    prefill graph (the lm_head included, every row) and the single row in the decode graph --
+    the two cases b200_model_set_activation_int8 implements."""
+    from buddy_mlir_b200 import TINY_QWEN2 as cfg, synthetic
+    f = np.load(os.path.join(G, "reference_importer_tiny_qwen2.npz"))
+    K = {"o": cfg.q_dim, "gate": cfg.hidden, "up": cfg.hidden, "down": cfg.ffn, "lm_head": cfg.hidden}
+    for phase, rows in (("prefill", cfg.max_len), ("decode", 1)):
+        got = sorted(str(s) for s in f[f"w8a8_{phase}_ops"])
+        want = [f"QuantizedMatmulOp:{n}:{l}:{rows}x{K[n]}" for n in ("o", "gate", "up", "down") for l in range(cfg.n_layers)]
+        want.append(f"QuantizedMatmulOp:lm_head:-1:{rows}x{K['lm_head']}")
+        assert got == sorted(want)
+    assert {s.split(":")[1] for s in f["w8a8_prefill_ops"]} == set(synthetic.QUANTISED_BY_REFERENCE)
