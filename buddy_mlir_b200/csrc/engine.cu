@@ -1166,7 +1166,7 @@ int b200_blob_elements(const b200_model_config *cfg, const char *variant,
                 KD = (int64_t)c.kv_heads * D, F = c.ffn, V = c.vocab;
   const int64_t qkv = H * QD + 2 * H * KD + (c.qkv_bias ? QD + 2 * KD : 0);
   const int64_t quant_layer = QD * H + 2 * H * F + F * H;
-  const int64_t small_layer = 2 * H;
+  const int64_t small_layer = 2 * H + (c.qk_norm ? 2 * D : 0);   // the layer norms (+ Qwen3's head norms)
   const int64_t common = V * H + D / 2 + H;  // embedding, inv_freq, final norm
   int64_t nf = 0, ni = 0;
   if (!strcmp(variant, "f32") || !strcmp(variant, "f16") || !strcmp(variant, "bf16") || !strcmp(variant, "f32p32")) {
@@ -1201,8 +1201,6 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   if (!m || !variant || !float_blob)
     return fail(B200_EINVAL, "load_blobs: null argument");
   const b200_model_config &c = m->cfg;
-  if (c.qk_norm)
-    return fail(B200_EINVAL, "load_blobs: blob order is defined for Qwen2 models only");
   int64_t want_f = 0, want_i = 0;
   if (int rc = b200_blob_elements(&c, variant, &want_f, &want_i)) return rc;
   const bool w8h = !strcmp(variant, "w8a16");
@@ -1277,10 +1275,14 @@ int b200_model_load_blobs(b200_model *m, const char *variant,
   };
   for (int l = 0; l < c.n_layers && rc == B200_OK; ++l) {
     B200_DO(b200_model_set_vector(m, l, B200_T_IN_NORM, takef(H), H));
+    // Qwen3: the head norms follow the projection they normalise (in norm, Wq, q norm, Wk, k norm,
+    // Wv, Wo, ...: the importer's order for transformers.Qwen3ForCausalLM)
     flinear(l, B200_T_Q, H, QD);
     if (c.qkv_bias) B200_DO(b200_model_set_vector(m, l, B200_T_Q_BIAS, takef(QD), QD));
+    if (c.qk_norm) B200_DO(b200_model_set_vector(m, l, B200_T_Q_NORM, takef(D), D));
     flinear(l, B200_T_K, H, KD);
     if (c.qkv_bias) B200_DO(b200_model_set_vector(m, l, B200_T_K_BIAS, takef(KD), KD));
+    if (c.qk_norm) B200_DO(b200_model_set_vector(m, l, B200_T_K_NORM, takef(D), D));
     flinear(l, B200_T_V, H, KD);
     if (c.qkv_bias) B200_DO(b200_model_set_vector(m, l, B200_T_V_BIAS, takef(KD), KD));
     qlinear(l, B200_T_O, QD, H);

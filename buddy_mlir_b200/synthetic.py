@@ -35,13 +35,21 @@ def tensor_list(cfg: ModelConfig):
     out = [("embed", -1, (V, H))]
     for l in range(cfg.n_layers):
         out.append(("in_norm", l, (H,)))
+        # Qwen3: the head norms follow the projection they normalise (the importer's order for
+        # transformers.Qwen3ForCausalLM: in norm, Wq, q norm, Wk, k norm, Wv, Wo, ...)
+        out.append(("q", l, (H, QD)))
         if cfg.qkv_bias:
-            out += [("q", l, (H, QD)), ("q_bias", l, (QD,)), ("k", l, (H, KD)),
-                    ("k_bias", l, (KD,)), ("v", l, (H, KD)), ("v_bias", l, (KD,))]
-        else:
-            out += [("q", l, (H, QD)), ("k", l, (H, KD)), ("v", l, (H, KD))]
+            out.append(("q_bias", l, (QD,)))
         if cfg.qk_norm:
-            out += [("q_norm", l, (D,)), ("k_norm", l, (D,))]
+            out.append(("q_norm", l, (D,)))
+        out.append(("k", l, (H, KD)))
+        if cfg.qkv_bias:
+            out.append(("k_bias", l, (KD,)))
+        if cfg.qk_norm:
+            out.append(("k_norm", l, (D,)))
+        out.append(("v", l, (H, KD)))
+        if cfg.qkv_bias:
+            out.append(("v_bias", l, (KD,)))
         out += [("o", l, (QD, H)), ("post_norm", l, (H,)), ("gate", l, (H, F)),
                 ("up", l, (H, F)), ("down", l, (F, H))]
     out += [("final_norm", -1, (H,)), ("lm_head", -1, (H, V)), ("inv_freq", -1, (D // 2,))]

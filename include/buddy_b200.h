@@ -291,6 +291,7 @@ int b200_model_set_linear(b200_model *m, int layer, int slot, int src_kind,
  * norm, Wq, q bias, Wk, k bias, Wv, v bias, Wo, post-attention norm, Wgate,
  * Wup, Wdown}, final norm, lm_head, inv_freq; every matmul weight [K,N]
  * row-major; the scales of the quantised tensors follow in that tensor order.
+ * Qwen3 (no biases, head norms): input norm, Wq, q norm, Wk, k norm, Wv, Wo, ...
  * variant: "f32", "f16" or "bf16" (one blob of f32 / f16 / bf16 elements), "w8a32" (float blob + int8 blob: o, gate, up,
  * down and lm_head quantised, q/k/v float, scales at the end of the float
  * blob), "w8a8" (the files of w8a32; the session then quantises the activations of

@@ -26,6 +26,7 @@ Output: reference_importer_tiny_qwen2.npz
   w8a8_prefill_ops, w8a8_decode_ops
                    "<operation>:<weight>:<activation shape>" of every integer matmul the w8a8 pass
                    left in the two graphs
+  qwen3_order      the same order for the small Qwen3 model (head norms, no biases)
   prefill_inputs, prefill_outputs, decode_inputs, decode_outputs
                    "<shape>:<dtype>" of the traced graphs' inputs (after the parameters) and, with the
                    producing operation, of their outputs: the entry ABI of the compiled model
@@ -82,12 +83,16 @@ def load_importer():
 def hf_model(cfg, views, act):
     import torch
     import transformers
-    hc = transformers.Qwen2Config(
+    common = dict(
         hidden_size=cfg.hidden, intermediate_size=cfg.ffn, num_hidden_layers=cfg.n_layers,
         num_attention_heads=cfg.q_heads, num_key_value_heads=cfg.kv_heads, vocab_size=cfg.vocab,
         max_position_embeddings=cfg.max_len, rms_norm_eps=cfg.eps, rope_theta=cfg.rope_theta,
         tie_word_embeddings=False, head_dim=cfg.head_dim)
-    model = transformers.Qwen2ForCausalLM(hc).float().eval()
+    if cfg.qk_norm:
+        model = transformers.Qwen3ForCausalLM(transformers.Qwen3Config(**common, attention_bias=False))
+    else:
+        model = transformers.Qwen2ForCausalLM(transformers.Qwen2Config(**common))
+    model = model.float().eval()
     t = lambda a: torch.from_numpy(np.ascontiguousarray(a))   # noqa: E731
     sd = {"model.embed_tokens.weight": t(views[("embed", -1)]), "model.norm.weight": t(views[("final_norm", -1)]),
           "lm_head.weight": t(views[("lm_head", -1)].T)}
@@ -97,8 +102,12 @@ def hf_model(cfg, views, act):
         sd[p + "post_attention_layernorm.weight"] = t(views[("post_norm", l)])
         for n in ("q", "k", "v", "o"):
             sd[p + f"self_attn.{n}_proj.weight"] = t(views[(n, l)].T)
-        for n in ("q", "k", "v"):
-            sd[p + f"self_attn.{n}_proj.bias"] = t(views[(f"{n}_bias", l)])
+        if cfg.qkv_bias:
+            for n in ("q", "k", "v"):
+                sd[p + f"self_attn.{n}_proj.bias"] = t(views[(f"{n}_bias", l)])
+        if cfg.qk_norm:
+            sd[p + "self_attn.q_norm.weight"] = t(views[("q_norm", l)])
+            sd[p + "self_attn.k_norm.weight"] = t(views[("k_norm", l)])
         for n in ("gate", "up", "down"):
             sd[p + f"mlp.{n}_proj.weight"] = t(views[(n, l)].T)
     missing, unexpected = model.load_state_dict(sd, strict=False)
@@ -193,6 +202,14 @@ def main():
             out[f"{variant}_{tag}_size"] = arr.size
             out[f"{variant}_{tag}_dtype"] = str(arr.dtype)
             print(f"{variant}: {tag} {arr.dtype} x {arr.size}")
+    # Qwen3 (head norms, no biases): the parameter order only
+    from buddy_mlir_b200 import TINY_QWEN3
+    _, views3 = synthetic.make_f32_blob(TINY_QWEN3, SEED_W)
+    config = {"shape": {"max_token_len": TINY_QWEN3.max_len}, "variant": "f32", "precision": {"activation_type": "f32"}}
+    _, _, params3 = imp.compile_graphs(hf_model(TINY_QWEN3, views3, "f32"), config)
+    out["qwen3_order"] = np.array([name_of(p.detach().numpy(), views3) for p in params3])
+    assert "?" not in out["qwen3_order"], out["qwen3_order"]
+    print("qwen3 order:", list(out["qwen3_order"]))
     path = os.path.join(HERE, "reference_importer_tiny_qwen2.npz")
     np.savez_compressed(path, **out)
     print("order:", list(out["order"]))

@@ -61,6 +61,22 @@ def test_tiny_f32_against_huggingface_fixture(cfg, name):
     s.close()
 
 
+def test_qwen3_blob_is_walked_in_the_importers_order():
+    """A Qwen3 model (head norms, no biases) from its flat blob: the same logits as the same
+    tensors loaded by name."""
+    cfg = TINY_QWEN3
+    blob, views = synthetic.make_f32_blob(cfg, 31)
+    a, b = ModelSession(cfg), ModelSession(cfg)
+    a.load_blobs("f32", blob)
+    b.load_tensors(views)
+    for t in synthetic.prompt_tokens(cfg, 4, 6):
+        a.decode(int(t))
+        b.decode(int(t))
+        assert np.array_equal(a.logits_data(), b.logits_data())
+    a.close()
+    b.close()
+
+
 def test_tiny_f32_greedy_and_device_loop():
     cfg = TINY_QWEN2
     blob, views = synthetic.make_f32_blob(cfg, 5)

@@ -59,7 +59,8 @@ def bc():
         yield types.SimpleNamespace(graph=g, ops=g.operation, quant=q)
     finally:
         sys.meta_path.remove(finder)
-        for k in [k for k in sys.modules if k == "buddy" or k.startswith("buddy.") or k.startswith("buddy_mlir")]:
+        for k in [k for k in sys.modules
+                  if k in ("buddy", "buddy_mlir") or k.startswith("buddy.") or k.startswith("buddy_mlir.")]:
             sys.modules.pop(k)
         for k, v in saved.items():
             if v is not None:

@@ -78,6 +78,12 @@ def test_blob_counts_match_reference_specs():
     # the bf16 variant: the same walk with bfloat16 elements (tools/buddy-codegen/gen_config.py:54)
     assert lib.b200_blob_elements(C.byref(c), b"bf16", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (1777088064, 0)
+    # Qwen3 shapes (head norms, no biases): the count of the walk synthetic.tensor_list describes
+    from buddy_mlir_b200 import QWEN3_8B, TINY_QWEN3
+    for q3 in (TINY_QWEN3, QWEN3_8B):
+        c3 = q3.to_c()
+        assert lib.b200_blob_elements(C.byref(c3), b"f32", C.byref(nf), C.byref(ni)) == 0
+        assert (nf.value, ni.value) == (synthetic.blob_elements(q3), 0)
     # models/deepseek_r1/specs/w8a8.json: linear_elements 1455489024, other_elements 322338752
     assert lib.b200_blob_elements(C.byref(c), b"w8a8", C.byref(nf), C.byref(ni)) == 0
     assert (nf.value, ni.value) == (322338752, 1455489024)

@@ -221,6 +221,8 @@ def test_blobs_equal_what_the_reference_importer_writes():
     f = np.load(os.path.join(G, "reference_importer_tiny_qwen2.npz"))
     sha = lambda a: hashlib.sha256(np.ascontiguousarray(a).tobytes()).hexdigest()
     assert [f"{n}:{l}" for n, l, _ in synthetic.tensor_list(cfg)] == list(f["order"])
+    from buddy_mlir_b200 import TINY_QWEN3
+    assert [f"{n}:{l}" for n, l, _ in synthetic.tensor_list(TINY_QWEN3)] == list(f["qwen3_order"])
     assert sorted({str(n).split(":")[0] for n in f["quantised"]}) == sorted(synthetic.QUANTISED_BY_REFERENCE)
     blob, views = synthetic.make_f32_blob(cfg, int(f["seed_w"]))
     # the rotary buffer is the one tensor the HuggingFace module computes for itself
