@@ -76,3 +76,44 @@ def test_generated_session_comes_through_the_shim_without_a_gpu(tmp_path, flavou
     ids = [int(x) for x in line[len("[ids] "):].split()]
     assert len(ids) == 70 - 40 + 1                       # the first token and 30 decode steps
     assert "no CUDA device" in out.stderr and ids == [0] * len(ids)
+
+
+@pytest.mark.parametrize("flavour", ["f32", "w8a32", "w8a8", "f32_tiered", "f32_packed"])
+def test_generated_session_over_the_same_shim_source_with_the_checkers_numbers(tmp_path, flavour):
+    """The same generated sessions, the same shim SOURCE, but linked against
+    oracle/oracle_forward_backend.cpp, which implements the b200_forward_* contract with the CPU
+    restatement: the whole host side of the model entry -- the reference's session, its
+    generation loop and sampler, and this library's shim with its result-ownership rules
+    (allocated, aliased, filled in place; the tiered session moving its cache between sizes
+    while it decodes) -- runs with real numbers on a machine without a GPU, and the ids must be
+    the restatement's own greedy ids.  (w8a8: the prefill scales over all rows of the padded
+    token container.)"""
+    cfg = TINY_QWEN2
+    host = os.path.join(ROOT, "oracle", "_ref", f"session_host_{flavour}")
+    shim = os.path.join(ROOT, "oracle", "_build", "shims", os.path.basename(shim_of(flavour, cfg)))
+    if not (os.path.exists(host) and os.path.exists(shim)):
+        pytest.skip("the generated sessions are built where a buddy-mlir checkout is present")
+    blob, views = synthetic.make_f32_blob(cfg, 93)
+    vocab = tmp_path / "vocab.txt"
+    vocab.write_text("".join(f"t{i}\n" for i in range(cfg.vocab)))
+    prompt = [int(t) for t in synthetic.prompt_tokens(cfg, 15, 20)]
+    n_new = 48                     # the tiered session moves from 32 rows to 64 and on to 128
+    kind = {"w8a32": "w8", "w8a8": "w8q"}.get(flavour)
+    om = orc.OracleModel(cfg, views, kinds={n: kind for n in synthetic.QUANTISED_BY_REFERENCE} if kind else None)
+    if flavour == "w8a8":          # one activation scale per projection over the whole padded container
+        logits = om.prefill(prompt + [0] * (cfg.max_len - len(prompt)))[len(prompt) - 1]
+        om.position = len(prompt)
+    else:
+        for t in prompt:
+            logits = om.decode(t)
+    want = [int(np.argmax(logits))]
+    for _ in range(n_new):
+        want.append(int(np.argmax(om.decode(want[-1]))))
+    env = dict(os.environ, MALLOC_CHECK_="3", MALLOC_PERTURB_="165")
+    out = subprocess.run([host, shim, weight_files(flavour, cfg, blob, views, str(tmp_path)), str(vocab),
+                          str(len(prompt) + n_new), "0", " ".join(str(t) for t in prompt)],
+                         capture_output=True, text=True, timeout=600, env=env)
+    assert out.returncode == 0, (out.returncode, out.stderr[-1500:])
+    assert "failed" not in out.stderr, out.stderr[-1500:]
+    line = [l for l in out.stdout.splitlines() if l.startswith("[ids] ")][-1]
+    assert [int(x) for x in line[len("[ids] "):].split()] == want
