@@ -148,3 +148,39 @@ def test_model_entry_shim_exports_both_symbols():
     dll = C.CDLL(so, mode=os.RTLD_NOW | os.RTLD_LOCAL)
     assert dll._mlir_ciface_forward_prefill is not None
     assert dll._mlir_ciface_forward_decode is not None
+
+
+def test_shim_arguments_from_the_reference_variant_specs():
+    """gen_model_entry.from_spec reads the two inputs of buddy-mlir's own gen_config.py: every
+    spec under models/deepseek_r1/specs/ of a checkout, with the published config of
+    DeepSeek-R1-Distill-Qwen-1.5B, gives the 1.5B shapes and the variant, cache sizes and decode
+    packing the stock shims are built with."""
+    import glob
+    import json
+    import os
+    from buddy_mlir_b200 import gen_model_entry as g
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.environ.get("BUDDY_MLIR_ROOT") or os.path.join(os.path.dirname(root), "reference")
+    specs = sorted(glob.glob(os.path.join(ref, "models", "deepseek_r1", "specs", "*.json")))
+    if not specs:
+        import pytest
+        pytest.skip("needs a buddy-mlir checkout for its spec files")
+    hf = {"model_type": "qwen2", "hidden_size": 1536, "intermediate_size": 8960, "num_hidden_layers": 28,
+          "num_attention_heads": 12, "num_key_value_heads": 2, "vocab_size": 151936, "rms_norm_eps": 1e-6,
+          "rope_theta": 10000, "max_position_embeddings": 131072}
+    seen = set()
+    for path in specs:
+        with open(path) as f:
+            spec = json.load(f)
+        cfg, kw = g.from_spec(spec, hf)
+        assert cfg.with_(name=DEEPSEEK_R1_1P5B.name) == DEEPSEEK_R1_1P5B, path
+        assert kw["variant"] == spec["variant"]
+        name = os.path.basename(path)
+        assert kw.get("tiers") == (g.R1_TIERS if "tiered" in name else None)
+        assert kw.get("decode_packed", False) == ("packed_decode" in name)
+        seen.add((kw["variant"], "tiers" in kw, kw.get("decode_packed", False)))
+        g.source(DEEPSEEK_R1_1P5B, **kw)           # the shim source generates for every spec
+    assert {v for v, _, _ in seen} == {"f32", "f16", "w8a32", "w8a8", "w8a16", "w4a16"}
+    q3 = dict(hf, model_type="qwen3", head_dim=128, attention_bias=False)
+    cfg, _ = g.from_spec({"variant": "f32", "max_token_len": 4096}, q3)
+    assert cfg.qk_norm and not cfg.qkv_bias and cfg.head_dim == 128 and cfg.max_len == 4096
