@@ -184,3 +184,54 @@ def test_shim_arguments_from_the_reference_variant_specs():
     q3 = dict(hf, model_type="qwen3", head_dim=128, attention_bias=False)
     cfg, _ = g.from_spec({"variant": "f32", "max_token_len": 4096}, q3)
     assert cfg.qk_norm and not cfg.qkv_bias and cfg.head_dim == 128 and cfg.max_len == 4096
+
+
+def test_reference_manifest_generator_takes_the_shim_and_the_runner_plugin():
+    """buddy-mlir's own tools/buddy-codegen/gen_config.py + gen_manifest.py, run on the w8a32
+    spec of the 1.5B model with this library's files in place of the compiled model: the
+    manifest text names the model-entry shim as the code object, the kernels library as its
+    dependency and the runner plugin as the runner library, with the weight files, KV buffers
+    and entry arguments the shim serves (what a maintainer packs with rax-pack)."""
+    import json
+    import os
+    import sys
+    import pytest
+    from buddy_mlir_b200 import gen_model_entry as g
+    root = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+    ref = os.environ.get("BUDDY_MLIR_ROOT") or os.path.join(os.path.dirname(root), "reference")
+    tools = os.path.join(ref, "tools", "buddy-codegen")
+    spec_path = os.path.join(ref, "models", "deepseek_r1", "specs", "w8a32.json")
+    if not os.path.exists(spec_path):
+        pytest.skip("needs a buddy-mlir checkout for its generators")
+    sys.path.insert(0, tools)
+    try:
+        import gen_config
+        import gen_manifest
+    finally:
+        sys.path.remove(tools)
+    with open(spec_path) as f:
+        spec = json.load(f)
+    hf = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "hidden_size": 1536, "intermediate_size": 8960,
+          "num_hidden_layers": 28, "num_attention_heads": 12, "num_key_value_heads": 2, "vocab_size": 151936,
+          "rms_norm_eps": 1e-6, "rope_theta": 10000, "eos_token_id": 151643}
+    hf_path = os.path.join(os.environ.get("TMPDIR", "/tmp"), "b200_hf_config_1p5b.json")
+    with open(hf_path, "w") as f:
+        json.dump(hf, f)
+    config = gen_config.gen_config(spec, hf_path)
+    cfg, kw = g.from_spec(spec, hf)
+    shim = g.shim_name(cfg, kw["variant"])
+    config["compilation"]["so_name"] = shim
+    text = gen_manifest.gen_manifest(config, dep_shared_libs=["libbuddy_b200_kernels.so"],
+                                     runner_library="libbuddy_b200_runner.so")
+    assert f'uri = "file:{shim}"' in text and 'rhal.codeobj @model_kernels' in text
+    assert 'uri = "file:libbuddy_b200_kernels.so"' in text
+    assert 'runner_library = "file:libbuddy_b200_runner.so"' in text
+    # the weight files and element counts the shim's loader expects for this variant
+    lib = _lib.load()
+    nf, ni = C.c_int64(), C.c_int64()
+    assert lib.b200_blob_elements(C.byref(cfg.to_c()), b"w8a32", C.byref(nf), C.byref(ni)) == 0
+    assert f"tensor<{nf.value}xf32>" in text and 'uri = "file:arg0-w8a32-f32.data"' in text
+    assert f"tensor<{ni.value}xi8>" in text and 'uri = "file:arg0-w8a32-i8.data"' in text
+    # 56 cache buffers [1, kv_heads, max_len, head_dim] and both entries dispatched to the code object
+    assert text.count(f"tensor<1x{cfg.kv_heads}x{cfg.max_len}x{cfg.head_dim}xf32>") == 2 * cfg.n_layers
+    assert text.count('dispatch = "model_kernels"') == 2
